@@ -1,0 +1,120 @@
+"""Builds and loads the C-ABI shared library (`libbonsai_attn.so`).
+
+The library is compiled in-tree with nvcc for sm_100a only. Loading never falls
+back to anything else: if the shared object is missing and cannot be built, the
+import of the compute API fails.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import glob
+import os
+import subprocess
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+LIB_PATH = os.path.join(HERE, "libbonsai_attn.so")
+HEADER = os.path.join(os.path.dirname(HERE), "include", "bonsai_attn.h")
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-shared", "-Xcompiler", "-fPIC",
+]
+
+
+def sources():
+    return sorted(glob.glob(os.path.join(CSRC, "*.cu")))
+
+
+def needs_build() -> bool:
+    if not os.path.exists(LIB_PATH):
+        return True
+    built = os.path.getmtime(LIB_PATH)
+    deps = sources() + glob.glob(os.path.join(CSRC, "*.cuh")) + [HEADER]
+    return any(os.path.getmtime(p) > built for p in deps)
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    """Compile every .cu under csrc/ into one shared object."""
+    if not force and not needs_build():
+        return LIB_PATH
+    nvcc = os.environ.get("NVCC", "nvcc")
+    cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB_PATH] + sources()
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
+    if verbose:
+        print(res.stderr)
+    return LIB_PATH
+
+
+class Config(C.Structure):
+    """`bp_attn_config` of include/bonsai_attn.h."""
+    _fields_ = [
+        ("n_layer", C.c_uint32), ("n_head", C.c_uint32), ("n_kv_head", C.c_uint32), ("head_dim", C.c_uint32),
+        ("max_seq", C.c_uint32), ("rms_eps", C.c_float), ("rope_freq_base", C.c_float),
+        ("max_prefill", C.c_uint32), ("n_shards", C.c_uint32), ("shard", C.c_uint32), ("device", C.c_int32),
+    ]
+
+
+class ErrorDetail(C.Structure):
+    _fields_ = [("status", C.c_int32), ("pos", C.c_uint32), ("n", C.c_uint32), ("max", C.c_uint32),
+                ("cuda_error", C.c_int32)]
+
+
+_vp, _u32, _u64, _int = C.c_void_p, C.c_uint32, C.c_uint64, C.c_int
+
+# name -> (restype, argtypes); must list every symbol the header declares.
+SIGNATURES = {
+    "bp_attn_create": (_int, [C.POINTER(Config), C.POINTER(_vp)]),
+    "bp_attn_destroy": (None, [_vp]),
+    "bp_q_norm_rope": (_int, [_vp, _vp, _vp, _vp, _u32, _u32]),
+    "bp_kv_writeback": (_int, [_vp, _vp, _u32, _vp, _vp, _vp, _u32, _u32]),
+    "bp_attn_decode": (_int, [_vp, _vp, _u32, _vp, _vp, _u32]),
+    "bp_attn_prefill": (_int, [_vp, _vp, _u32, _vp, _vp, _u32]),
+    "bp_attn_max_prefill": (_u32, [_vp]),
+    "bp_decode_step_host": (_int, [_vp, _u32, _vp, _vp, _vp, _vp, _vp, _u32, _vp]),
+    "bp_prefill_layer_host": (_int, [_vp, _u32, _vp, _vp, _vp, _vp, _vp, _u32, _vp]),
+    "bp_kv_export": (_int, [_vp, _u32, _u32, _u32, _u32, _vp]),
+    "bp_kv_import": (_int, [_vp, _u32, _u32, _u32, _u32, _vp]),
+    "bp_snapshot_payload_bytes": (_u64, [_u32, _u32, _u32]),
+    "bp_snapshot_payload_offset": (_u64, [_u32] * 6),
+    "bp_snapshot_size": (_u64, [_vp, _u32]),
+    "bp_snapshot_capture": (_int, [_vp, _u32, _vp, _u64]),
+    "bp_snapshot_apply": (_int, [_vp, _vp, _u64, C.POINTER(_u32)]),
+    "bp_ctx_status": (_int, [_vp]),
+    "bp_ctx_inject_lost": (None, [_vp]),
+    "bp_last_error_detail": (None, [_vp, C.POINTER(ErrorDetail)]),
+    "bp_last_error_message": (C.c_char_p, [_vp]),
+    "bp_strerror": (C.c_char_p, [_int]),
+    "bp_kv_device_ptr": (_vp, [_vp, _u32]),
+    "bp_kv_buffer_bytes": (_u64, [_vp]),
+    "bp_rope_device_ptr": (_vp, [_vp]),
+    "bp_rope_table_copy": (_int, [_vp, _vp]),
+    "bp_set_variant": (_int, [_vp, _u32]),
+    "bp_last_launch_count": (_u32, [_vp]),
+    "bp_decode_num_splits": (_u32, [_vp, _u32]),
+}
+
+_LIB = None
+
+
+def load() -> C.CDLL:
+    """Load the shared library, building it first when sources are newer."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    path = LIB_PATH
+    if needs_build():
+        try:
+            path = build()
+        except (RuntimeError, FileNotFoundError) as e:
+            if not os.path.exists(LIB_PATH):
+                raise ImportError(f"libbonsai_attn.so is missing and could not be built: {e}") from e
+    lib = C.CDLL(path)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError here = the header and the library disagree
+        fn.restype = res
+        fn.argtypes = args
+    _LIB = lib
+    return lib

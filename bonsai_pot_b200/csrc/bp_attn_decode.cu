@@ -1,0 +1,553 @@
+// Single-token GQA decode attention over the Q8_0 KV cache: split-KV partial
+// pass + log-sum-exp combine. Replaces attention_split.wgsl and
+// attention_merge.wgsl of the reference (src/forward.rs:822-856).
+//
+// Production kernel (decode_mma_kernel), HBM-bound by design:
+//   * One CTA owns a contiguous token range (a "split") for ALL KV heads of the
+//     context, so the CTA streams whole cache rows: HBM sees long sequential
+//     reads of the qs-section and of the d-section.
+//   * A producer warp moves the rows into shared memory with tiled TMA loads
+//     (128-byte swizzle, completion on mbarriers, a ring of stages); no load
+//     uses cluster multicast.
+//   * Each compute warp owns one KV head and a 16-token sub-tile per stage and
+//     computes on the tensor cores with warp-level MMA: S = Q K^T with the
+//     (<= 8) query heads of the group padded to M = 16, O^T = V^T P^T with the
+//     head dims on M. int8 is expanded to f16 bit patterns with two logic ops
+//     per pair (see k_pair / v_pairs); the Q8_0 block scales stay in f32 and
+//     multiply the per-block accumulators (K) or fold into P (V).
+//   * Softmax runs in the exp2 domain with the running max shared by the four
+//     lanes of a quad (warp shuffles), rescaling O only when a max moves.
+//   * Partials (o[128], m, l per head and split) go to the context's scratch and
+//     a second small kernel combines them; with one split the kernel writes the
+//     f16 output itself.
+//
+// A plain CUDA-core kernel (attn_scalar_kernel) is kept as an on-device
+// cross-check (variant 1); it is also the first-generation prefill kernel.
+#include "bp_common.cuh"
+#include "bp_ptx.cuh"
+#include "bp_q8.cuh"
+
+namespace {
+
+using namespace bp;
+
+constexpr unsigned FULL = 0xffffffffu;
+constexpr float NEG_BIG = -1e30f;  // the reference's initial running max
+
+// ------------------------------------------------------------------------
+// Cross-check kernel: one block per (split, query head, token); 4 warps take
+// tokens round-robin, lane l holds dims 4l..4l+3. f32 throughout, dequantising
+// as scale * f32(int8) like load_k / load_v (attention_split.wgsl:87-109).
+// ------------------------------------------------------------------------
+__global__ void __launch_bounds__(128)
+attn_scalar_kernel(const __half* __restrict__ q, const float* __restrict__ k_d,
+                   const uint32_t* __restrict__ k_qs, const float* __restrict__ v_d,
+                   const uint32_t* __restrict__ v_qs, float* __restrict__ partials,
+                   __half* __restrict__ out, uint32_t n_head, uint32_t n_kv_head, uint32_t cur_pos,
+                   uint32_t tps, uint32_t is_prefill, float scale) {
+  const uint32_t split = blockIdx.x, h = blockIdx.y, tok = blockIdx.z;
+  const uint32_t n_splits = gridDim.x;
+  const uint32_t g = h / (n_head / n_kv_head);
+  const uint32_t kv_dim = n_kv_head * BP_HEAD_DIM, nb = kv_dim / BP_QK8;
+  const uint32_t n_keys = is_prefill ? tok + 1 : cur_pos;
+  const uint32_t t0 = split * tps;
+  const uint32_t t1 = min(t0 + tps, n_keys);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+  const __half* qrow = q + (static_cast<size_t>(tok) * n_head + h) * BP_HEAD_DIM;
+  float qf[4];
+  {
+    const uint2 qr = *reinterpret_cast<const uint2*>(qrow + 4 * lane);
+    const __half2* qh = reinterpret_cast<const __half2*>(&qr);
+    const float2 a = __half22float2(qh[0]), b = __half22float2(qh[1]);
+    qf[0] = a.x; qf[1] = a.y; qf[2] = b.x; qf[3] = b.y;
+  }
+  float m_run = NEG_BIG, l_run = 0.f, o[4] = {0.f, 0.f, 0.f, 0.f};
+  for (uint32_t t = t0 + warp; t < t1; t += 4) {
+    const size_t word = (static_cast<size_t>(t) * kv_dim + g * BP_HEAD_DIM) / 4 + lane;
+    const size_t blk = static_cast<size_t>(t) * nb + g * 4 + (lane >> 3);
+    const uint32_t kw = k_qs[word], vw = v_qs[word];
+    const float ks = k_d[blk], vs = v_d[blk];
+    float dot = 0.f;
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+      const float kf = ks * static_cast<float>(static_cast<int8_t>(kw >> (8 * c)));
+      dot += kf * qf[c];
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) dot += __shfl_xor_sync(FULL, dot, off);
+    const float s = dot * scale;
+    const float m_new = fmaxf(m_run, s);
+    const float corr = __expf(m_run - m_new), w = __expf(s - m_new);
+    l_run = l_run * corr + w;
+    m_run = m_new;
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+      const float vf = vs * static_cast<float>(static_cast<int8_t>(vw >> (8 * c)));
+      o[c] = o[c] * corr + w * vf;
+    }
+  }
+  __shared__ float sm_o[4][BP_HEAD_DIM];
+  __shared__ float sm_m[4], sm_l[4];
+#pragma unroll
+  for (int c = 0; c < 4; c++) sm_o[warp][4 * lane + c] = o[c];
+  if (lane == 0) { sm_m[warp] = m_run; sm_l[warp] = l_run; }
+  __syncthreads();
+  const int d = threadIdx.x;
+  const float m_all = fmaxf(fmaxf(sm_m[0], sm_m[1]), fmaxf(sm_m[2], sm_m[3]));
+  float oo = 0.f, ll = 0.f;
+#pragma unroll
+  for (int w = 0; w < 4; w++) {
+    const float e = __expf(sm_m[w] - m_all);
+    oo += sm_o[w][d] * e;
+    ll += sm_l[w] * e;
+  }
+  if (n_splits == 1) {
+    out[(static_cast<size_t>(tok) * n_head + h) * BP_HEAD_DIM + d] = __float2half_rn(oo * (1.0f / ll));
+  } else {
+    float* dst = partials + ((static_cast<size_t>(tok) * n_splits + split) * n_head + h) * BP_PART_STRIDE;
+    dst[d] = oo;
+    if (d == 0) { dst[128] = m_all * 1.4426950408889634f; dst[129] = ll; }  // m kept in log2 units
+  }
+}
+
+// Log-sum-exp combine over splits (attention_merge.wgsl:70-130). One block per
+// query head; thread d owns output dim d. m is stored in log2 units.
+__global__ void __launch_bounds__(128)
+attn_combine_kernel(const float* __restrict__ partials, __half* __restrict__ out, uint32_t n_head,
+                    uint32_t n_splits) {
+  const uint32_t h = blockIdx.x, d = threadIdx.x;
+  const float* base = partials + static_cast<size_t>(h) * BP_PART_STRIDE;
+  const size_t stride = static_cast<size_t>(n_head) * BP_PART_STRIDE;
+  float m_all = NEG_BIG;
+  for (uint32_t s = 0; s < n_splits; s++) m_all = fmaxf(m_all, base[s * stride + 128]);
+  float o = 0.f, l = 0.f;
+#pragma unroll 4
+  for (uint32_t s = 0; s < n_splits; s++) {
+    const float* p = base + s * stride;
+    const float e = ex2(p[128] - m_all);
+    o += p[d] * e;
+    l += p[129] * e;
+  }
+  out[static_cast<size_t>(h) * BP_HEAD_DIM + d] = __float2half_rn(o * (1.0f / l));
+}
+
+// ------------------------------------------------------------------------
+// Production kernel.
+// ------------------------------------------------------------------------
+constexpr int NW = 8;                               // compute warps per CTA
+constexpr int MAX_STAGES = 5;
+constexpr uint32_t SUBTILE = 16;                    // tokens per warp per stage
+constexpr uint32_t STAGE_QS = NW * SUBTILE * 128;   // bytes of K (or V) quants per stage
+constexpr uint32_t STAGE_D = NW * SUBTILE * 16;     // bytes of K (or V) scales per stage
+constexpr uint32_t STAGE_BYTES = 2 * STAGE_QS + 2 * STAGE_D;
+constexpr uint32_t MERGE_BYTES = NW * 8 * BP_HEAD_DIM * 4 + NW * 8 * 8;
+
+struct DecodeParams {
+  const __half* q;
+  __half* out;
+  float* partials;
+  uint32_t* err;       // device word: set non-zero when a bounded wait gives up
+  uint32_t row_base;   // layer * max_seq
+  uint32_t cur_pos;
+  uint32_t tps;        // tokens per split, a multiple of the stage size
+  uint32_t n_stages;
+  uint32_t n_head, nkv, qpg;
+  uint32_t d_swz;      // 1 when the scale tiles are 128 B wide and swizzled
+  float sm_scale_log2; // softmax scale * log2(e)
+};
+
+template <bool DENORM>
+__global__ void __launch_bounds__((NW + 1) * 32, 1)
+decode_mma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_constant__ CUtensorMap map_kd,
+                  const __grid_constant__ CUtensorMap map_vq, const __grid_constant__ CUtensorMap map_vd,
+                  const DecodeParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[MAX_STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[MAX_STAGES];
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t nkv = p.nkv, wph = NW / nkv, st_tok = SUBTILE * wph;
+  const uint32_t ns = p.n_stages;
+
+  const uint32_t split = blockIdx.x, n_splits = gridDim.x;
+  const uint32_t tok_begin = split * p.tps;
+  const uint32_t tok_end = min(tok_begin + p.tps, p.cur_pos);
+  const uint32_t n_iter = (tok_end - tok_begin + st_tok - 1) / st_tok;
+
+  if (threadIdx.x == 0) {
+    for (uint32_t s = 0; s < ns; s++) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), NW);
+    }
+    fence_barrier_init();
+  }
+  __syncthreads();
+
+  if (warp == NW) {
+    // ---------------- producer ----------------
+    if (lane == 0) {
+      prefetch_tensormap(&map_kq);
+      prefetch_tensormap(&map_vq);
+      prefetch_tensormap(&map_kd);
+      prefetch_tensormap(&map_vd);
+      bool ok = true;
+      for (uint32_t it = 0; it < n_iter && ok; it++) {
+        const uint32_t s = it % ns, use = it / ns;
+        if (use > 0) ok = mbar_wait(smem_u32(&empty_bar[s]), (use - 1) & 1);
+        if (!ok) break;
+        const uint32_t bar = smem_u32(&full_bar[s]);
+        const uint32_t stage = smem_base + s * STAGE_BYTES;
+        const int row = static_cast<int>(p.row_base + tok_begin + it * st_tok);
+        mbar_arrive_expect_tx(bar, STAGE_BYTES);
+        for (uint32_t g = 0; g < nkv; g++) {
+          tma_load_3d(stage + g * (st_tok * 128), &map_kq, bar, 0, static_cast<int>(g), row);
+          tma_load_3d(stage + STAGE_QS + g * (st_tok * 128), &map_vq, bar, 0, static_cast<int>(g), row);
+        }
+        tma_load_2d(stage + 2 * STAGE_QS, &map_kd, bar, 0, row);
+        tma_load_2d(stage + 2 * STAGE_QS + STAGE_D, &map_vd, bar, 0, row);
+      }
+      if (!ok) atomicExch(p.err, 1u);
+    }
+  } else {
+    // ---------------- compute ----------------
+    const int r = lane >> 2, qd = lane & 3;
+    const uint32_t g = warp % nkv, slot = warp / nkv;
+    const bool row_valid = static_cast<uint32_t>(r) < p.qpg;
+
+    // A fragments of Q for the 8 k-slices (block b, half s): slice (b, s) covers
+    // dims 32b + 8*quad + 4s + {0,1,2,3}; a0 = (dim+0, dim+2), a2 = (dim+1, dim+3)
+    // to match the byte order k_pair produces. Rows >= qpg are zero.
+    uint32_t qa0[4][2], qa2[4][2];
+    float qcorr[4];
+    {
+      const __half* qrow = p.q + (static_cast<size_t>(g) * p.qpg + (row_valid ? r : 0)) * BP_HEAD_DIM;
+#pragma unroll
+      for (int b = 0; b < 4; b++) {
+        float bsum = 0.f;
+#pragma unroll
+        for (int s = 0; s < 2; s++) {
+          uint2 hv = make_uint2(0u, 0u);
+          if (row_valid) hv = *reinterpret_cast<const uint2*>(qrow + 32 * b + 8 * qd + 4 * s);
+          qa0[b][s] = prmt(hv.x, hv.y, 0x5410);  // (h0, h2)
+          qa2[b][s] = prmt(hv.x, hv.y, 0x7632);  // (h1, h3)
+          const float2 f0 = __half22float2(*reinterpret_cast<__half2*>(&hv.x));
+          const float2 f1 = __half22float2(*reinterpret_cast<__half2*>(&hv.y));
+          bsum += (f0.x + f0.y) + (f1.x + f1.y);
+        }
+        bsum += __shfl_xor_sync(FULL, bsum, 1);
+        bsum += __shfl_xor_sync(FULL, bsum, 2);
+        qcorr[b] = DENORM ? bsum * (128.0f / 16777216.0f) : 0.f;
+      }
+    }
+    // In the DENORM path accumulators carry a factor 2^-24.
+    const float s_mul = p.sm_scale_log2 * (DENORM ? 16777216.0f : 1.0f);
+
+    float m_run = NEG_BIG, l_run = 0.f;
+    float psum[4] = {0.f, 0.f, 0.f, 0.f};
+    float oacc[4][2][4];
+#pragma unroll
+    for (int b = 0; b < 4; b++)
+#pragma unroll
+      for (int t = 0; t < 2; t++)
+#pragma unroll
+        for (int c = 0; c < 4; c++) oacc[b][t][c] = 0.f;
+
+    bool ok = true;
+    for (uint32_t it = 0; it < n_iter; it++) {
+      const uint32_t s = it % ns, use = it / ns;
+      ok = mbar_wait(smem_u32(&full_bar[s]), use & 1);
+      if (!ok) break;
+      const uint32_t stage = smem_base + s * STAGE_BYTES;
+      const uint32_t tile_tok0 = tok_begin + it * st_tok + slot * SUBTILE;
+      if (tile_tok0 < tok_end) {
+        const uint32_t ktile = stage + g * (st_tok * 128) + slot * (SUBTILE * 128);
+        const uint32_t vtile = ktile + STAGE_QS;
+        const uint32_t kd_tile = stage + 2 * STAGE_QS;
+        const uint32_t vd_tile = kd_tile + STAGE_D;
+        const uint32_t rb = 16 * nkv;
+
+        // ---- S = Q K^T, one accumulator per (token tile, Q8_0 block) ----
+        float acc[2][4][4];
+#pragma unroll
+        for (int t = 0; t < 2; t++) {
+          const uint32_t row = 2 * (r ^ (r >> 2)) + t;
+#pragma unroll
+          for (int b = 0; b < 4; b++) {
+#pragma unroll
+            for (int c = 0; c < 4; c++) acc[t][b][c] = 0.f;
+            const uint32_t off = row * 128 + (((2 * b + (qd >> 1)) ^ (row & 7)) << 4) + ((qd & 1) << 3);
+            const uint2 w = lds64(ktile + off);
+            uint32_t b0, b1;
+            k_pair<DENORM>(w.x, b0, b1);
+            mma_16816(acc[t][b], qa0[b][0], 0u, qa2[b][0], 0u, b0, b1);
+            k_pair<DENORM>(w.y, b0, b1);
+            mma_16816(acc[t][b], qa0[b][1], 0u, qa2[b][1], 0u, b0, b1);
+          }
+        }
+
+        // ---- scores of this lane: head r, tokens 4*quad + (j ^ (quad & 2)) ----
+        float sc[4];
+        float4 sv[4];
+        const bool tail = tile_tok0 + SUBTILE > tok_end;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          const uint32_t rowj = 4 * qd + (j ^ (qd & 2));
+          uint32_t o = (slot * SUBTILE + rowj) * rb + g * 16;
+          if (p.d_swz) o = swz128(o);
+          const float4 sk = lds128f(kd_tile + o);
+          sv[j] = lds128f(vd_tile + o);
+          const int t = j & 1, c = j >> 1;
+          float sj = sk.x * (acc[t][0][c] - qcorr[0]);
+          sj = fmaf(sk.y, acc[t][1][c] - qcorr[1], sj);
+          sj = fmaf(sk.z, acc[t][2][c] - qcorr[2], sj);
+          sj = fmaf(sk.w, acc[t][3][c] - qcorr[3], sj);
+          sc[j] = sj * s_mul;
+          if (tail && tile_tok0 + rowj >= tok_end) {
+            sc[j] = NEG_BIG;
+            sv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+        }
+        float m_loc = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
+        m_loc = fmaxf(m_loc, __shfl_xor_sync(FULL, m_loc, 1));
+        m_loc = fmaxf(m_loc, __shfl_xor_sync(FULL, m_loc, 2));
+        const float m_new = fmaxf(m_run, m_loc);
+        const float corr = ex2(m_run - m_new);
+        const bool moved = m_new > m_run;
+        m_run = m_new;
+        float pj[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) pj[j] = ex2(sc[j] - m_new);
+        l_run = l_run * corr + ((pj[0] + pj[1]) + (pj[2] + pj[3]));
+
+        if (__any_sync(FULL, moved)) {
+          const float ca = __shfl_sync(FULL, corr, 8 * qd);
+          const float cb = __shfl_sync(FULL, corr, 8 * qd + 4);
+#pragma unroll
+          for (int b = 0; b < 4; b++) {
+            psum[b] *= corr;
+#pragma unroll
+            for (int t = 0; t < 2; t++) {
+              oacc[b][t][0] *= ca; oacc[b][t][1] *= cb;
+              oacc[b][t][2] *= ca; oacc[b][t][3] *= cb;
+            }
+          }
+        }
+
+        // ---- O^T += V^T P'^T, P' = p * (V block scale), per Q8_0 block ----
+#pragma unroll
+        for (int b = 0; b < 4; b++) {
+          const float sb0 = b == 0 ? sv[0].x : b == 1 ? sv[0].y : b == 2 ? sv[0].z : sv[0].w;
+          const float sb1 = b == 0 ? sv[1].x : b == 1 ? sv[1].y : b == 2 ? sv[1].z : sv[1].w;
+          const float sb2 = b == 0 ? sv[2].x : b == 1 ? sv[2].y : b == 2 ? sv[2].z : sv[2].w;
+          const float sb3 = b == 0 ? sv[3].x : b == 1 ? sv[3].y : b == 2 ? sv[3].z : sv[3].w;
+          const float p0 = pj[0] * sb0, p1 = pj[1] * sb1, p2 = pj[2] * sb2, p3 = pj[3] * sb3;
+          __half2 h01 = __floats2half2_rn(p0, p1), h23 = __floats2half2_rn(p2, p3);
+          if (DENORM) {  // sum what the MMA will actually see, so the +128 offset cancels exactly
+            const float2 r01 = __half22float2(h01), r23 = __half22float2(h23);
+            psum[b] += (r01.x + r01.y) + (r23.x + r23.y);
+          }
+          const uint32_t pb0 = *reinterpret_cast<uint32_t*>(&h01);
+          const uint32_t pb1 = *reinterpret_cast<uint32_t*>(&h23);
+
+          uint32_t e[4], o[4];
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            const uint32_t rowj = 4 * qd + (j ^ (qd & 2));
+            const uint32_t off = rowj * 128 + (((2 * b + (r >> 2)) ^ (rowj & 7)) << 4) + ((r & 3) << 2);
+            const uint32_t x = lds32(vtile + off) ^ 0x80808080u;
+            e[j] = x & 0x00ff00ffu;
+            o[j] = x & 0xff00ff00u;
+            if (!DENORM) { e[j] |= 0x64006400u; o[j] |= 0x00640064u; }
+          }
+          // dims 32b + 4r + {0 (row r), 2 (row r+8)}
+          mma_16816(oacc[b][0], v_fix<DENORM>(prmt(e[0], e[1], 0x5410)), v_fix<DENORM>(prmt(e[0], e[1], 0x7632)),
+                    v_fix<DENORM>(prmt(e[2], e[3], 0x5410)), v_fix<DENORM>(prmt(e[2], e[3], 0x7632)), pb0, pb1);
+          // dims 32b + 4r + {1 (row r), 3 (row r+8)}
+          mma_16816(oacc[b][1], v_fix<DENORM>(prmt(o[0], o[1], 0x4501)), v_fix<DENORM>(prmt(o[0], o[1], 0x6723)),
+                    v_fix<DENORM>(prmt(o[2], o[3], 0x4501)), v_fix<DENORM>(prmt(o[2], o[3], 0x6723)), pb0, pb1);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&empty_bar[s]));
+    }
+    if (!ok && lane == 0) atomicExch(p.err, 1u);
+
+    // ---- warp result -> merge buffer (placed after the stage ring) ----
+    l_run += __shfl_xor_sync(FULL, l_run, 1);
+    l_run += __shfl_xor_sync(FULL, l_run, 2);
+    float pa[4], pb[4];
+#pragma unroll
+    for (int b = 0; b < 4; b++) {
+      float ps = psum[b];
+      ps += __shfl_xor_sync(FULL, ps, 1);
+      ps += __shfl_xor_sync(FULL, ps, 2);
+      pa[b] = __shfl_sync(FULL, ps, 8 * qd) * 128.0f;
+      pb[b] = __shfl_sync(FULL, ps, 8 * qd + 4) * 128.0f;
+    }
+    float* mo = reinterpret_cast<float*>(smem_gen + ns * STAGE_BYTES);
+    float* mm = mo + NW * 8 * BP_HEAD_DIM;
+    float* ml = mm + NW * 8;
+    const float os = DENORM ? 16777216.0f : 1.0f;
+#pragma unroll
+    for (int b = 0; b < 4; b++) {
+      const int dim = 32 * b + 4 * r;
+      if (static_cast<uint32_t>(2 * qd) < p.qpg) {
+        float4 v = make_float4(oacc[b][0][0] * os - pa[b], oacc[b][1][0] * os - pa[b],
+                               oacc[b][0][2] * os - pa[b], oacc[b][1][2] * os - pa[b]);
+        *reinterpret_cast<float4*>(mo + (warp * 8 + 2 * qd) * BP_HEAD_DIM + dim) = v;
+      }
+      if (static_cast<uint32_t>(2 * qd + 1) < p.qpg) {
+        float4 v = make_float4(oacc[b][0][1] * os - pb[b], oacc[b][1][1] * os - pb[b],
+                               oacc[b][0][3] * os - pb[b], oacc[b][1][3] * os - pb[b]);
+        *reinterpret_cast<float4*>(mo + (warp * 8 + 2 * qd + 1) * BP_HEAD_DIM + dim) = v;
+      }
+    }
+    if (qd == 0 && row_valid) {
+      mm[warp * 8 + r] = m_run;
+      ml[warp * 8 + r] = l_run;
+    }
+  }
+  __syncthreads();
+
+  // ---- merge the warps of each KV head, write the split's partial ----
+  {
+    const float* mo = reinterpret_cast<const float*>(smem_gen + ns * STAGE_BYTES);
+    const float* mm = mo + NW * 8 * BP_HEAD_DIM;
+    const float* ml = mm + NW * 8;
+    const uint32_t total = p.n_head * BP_HEAD_DIM;
+    for (uint32_t idx = threadIdx.x; idx < total; idx += blockDim.x) {
+      const uint32_t h = idx >> 7, d = idx & 127;
+      const uint32_t g = h / p.qpg, hq = h % p.qpg;
+      float m_all = NEG_BIG;
+      for (uint32_t sl = 0; sl < wph; sl++) m_all = fmaxf(m_all, mm[(sl * nkv + g) * 8 + hq]);
+      float o = 0.f, l = 0.f;
+      for (uint32_t sl = 0; sl < wph; sl++) {
+        const uint32_t w = sl * nkv + g;
+        const float e = ex2(mm[w * 8 + hq] - m_all);
+        o += mo[(w * 8 + hq) * BP_HEAD_DIM + d] * e;
+        l += ml[w * 8 + hq] * e;
+      }
+      if (n_splits == 1) {
+        p.out[idx] = __float2half_rn(o * (1.0f / l));
+      } else {
+        float* dst = p.partials + (static_cast<size_t>(split) * p.n_head + h) * BP_PART_STRIDE;
+        dst[d] = o;
+        if (d == 0) { dst[128] = m_all; dst[129] = l; }
+      }
+    }
+  }
+  // The producer drains its own copies before the CTA retires (all of them have
+  // already completed unless a wait above gave up).
+  if (warp == NW && lane == 0) {
+    const uint32_t first = n_iter > ns ? n_iter - ns : 0;
+    for (uint32_t it = first; it < n_iter; it++)
+      if (!mbar_wait(smem_u32(&full_bar[it % ns]), (it / ns) & 1, 1u << 20)) atomicExch(p.err, 2u);
+  }
+}
+
+}  // namespace
+
+// Split policy. A stage holds 16 * (8 / n_kv_head) tokens; a split is a whole
+// number of stages, chosen so that the grid is at most one CTA per SM.
+static uint32_t stage_tokens(const bp_attn_ctx* c) { return SUBTILE * (NW / c->cfg.n_kv_head); }
+
+uint32_t bp_decode_max_splits(const bp_attn_ctx* c) { return static_cast<uint32_t>(c->sm_count); }
+
+static uint32_t stages_per_split(const bp_attn_ctx* c, uint32_t cur_pos) {
+  const uint32_t st = stage_tokens(c);
+  const uint32_t n_st = (cur_pos + st - 1) / st;
+  const uint32_t ctas = static_cast<uint32_t>(c->sm_count);
+  return (n_st + ctas - 1) / ctas;
+}
+
+uint32_t bp_decode_splits(const bp_attn_ctx* c, uint32_t cur_pos) {
+  if (c->variant == 1) {
+    const uint32_t tps = 256;
+    return (cur_pos + tps - 1) / tps > bp_decode_max_splits(c) ? bp_decode_max_splits(c)
+                                                               : (cur_pos + tps - 1) / tps;
+  }
+  const uint32_t st = stage_tokens(c);
+  const uint32_t n_st = (cur_pos + st - 1) / st;
+  const uint32_t spp = stages_per_split(c, cur_pos);
+  return (n_st + spp - 1) / spp;
+}
+
+cudaError_t bp_launch_scalar_attention(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, const __half* q,
+                                       __half* out, uint32_t cur_pos, uint32_t m, bool is_prefill,
+                                       uint32_t* launches) {
+  const float* k_d = reinterpret_cast<const float*>(c->kv[0] + bp_d_off(c, layer));
+  const float* v_d = reinterpret_cast<const float*>(c->kv[1] + bp_d_off(c, layer));
+  const uint32_t* k_qs = reinterpret_cast<const uint32_t*>(c->kv[0] + bp_qs_off(c, layer));
+  const uint32_t* v_qs = reinterpret_cast<const uint32_t*>(c->kv[1] + bp_qs_off(c, layer));
+  const float scale = 1.0f / sqrtf(static_cast<float>(BP_HEAD_DIM));
+  uint32_t n_splits = 1, tps = cur_pos;
+  if (!is_prefill) {
+    n_splits = bp_decode_splits(c, cur_pos);
+    tps = (cur_pos + n_splits - 1) / n_splits;
+  } else {
+    tps = m;
+  }
+  dim3 grid(n_splits, c->cfg.n_head, m);
+  attn_scalar_kernel<<<grid, 128, 0, s>>>(q, k_d, k_qs, v_d, v_qs, c->partials, out, c->cfg.n_head,
+                                          c->cfg.n_kv_head, cur_pos, tps, is_prefill ? 1u : 0u, scale);
+  *launches += 1;
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  if (n_splits > 1) {
+    attn_combine_kernel<<<c->cfg.n_head, 128, 0, s>>>(c->partials, out, c->cfg.n_head, n_splits);
+    *launches += 1;
+    e = cudaGetLastError();
+  }
+  return e;
+}
+
+uint32_t bp_decode_stage_tokens(const bp_attn_ctx* c) { return stage_tokens(c); }
+
+// Opt the production kernels into their dynamic shared memory on the context's device.
+cudaError_t bp_decode_init(bp_attn_ctx*) {
+  const int max_smem = MAX_STAGES * STAGE_BYTES + MERGE_BYTES + 1024;
+  cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(decode_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+}
+
+cudaError_t bp_launch_decode(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, const __half* q,
+                             __half* out, uint32_t cur_pos, uint32_t* launches) {
+  if (c->variant == 1) return bp_launch_scalar_attention(c, s, layer, q, out, cur_pos, 1, false, launches);
+  if (!c->have_maps) return cudaErrorNotSupported;
+
+  const bool denorm = c->variant != 2;
+  const uint32_t st = stage_tokens(c);
+  const uint32_t spp = stages_per_split(c, cur_pos);
+  const uint32_t n_splits = bp_decode_splits(c, cur_pos);
+  DecodeParams p;
+  p.q = q;
+  p.out = out;
+  p.partials = c->partials;
+  p.err = c->err_dev;
+  p.row_base = layer * c->cfg.max_seq;
+  p.cur_pos = cur_pos;
+  p.tps = spp * st;
+  p.n_stages = spp < MAX_STAGES ? spp : MAX_STAGES;
+  p.n_head = c->cfg.n_head;
+  p.nkv = c->cfg.n_kv_head;
+  p.qpg = c->qpg;
+  p.d_swz = (16 * c->cfg.n_kv_head == 128) ? 1u : 0u;
+  p.sm_scale_log2 = (1.0f / sqrtf(static_cast<float>(BP_HEAD_DIM))) * 1.4426950408889634f;
+  const size_t smem = static_cast<size_t>(p.n_stages) * STAGE_BYTES + MERGE_BYTES + 1024;
+
+  auto kern = denorm ? decode_mma_kernel<true> : decode_mma_kernel<false>;
+  kern<<<n_splits, (NW + 1) * 32, smem, s>>>(c->map_qs[0], c->map_d[0], c->map_qs[1], c->map_d[1], p);
+  *launches += 1;
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  if (n_splits > 1) {
+    attn_combine_kernel<<<c->cfg.n_head, 128, 0, s>>>(c->partials, out, c->cfg.n_head, n_splits);
+    *launches += 1;
+    e = cudaGetLastError();
+  }
+  return e;
+}

@@ -1,0 +1,65 @@
+// Shared declarations of the attention library: the context object, launch
+// entry points of each kernel file, and small device helpers.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/bonsai_attn.h"
+
+constexpr uint32_t BP_HEAD_DIM = 128;
+constexpr uint32_t BP_QK8 = 32;          // Q8_0 block size
+constexpr uint32_t BP_PART_STRIDE = 132; // floats per (split, head) partial: o[128], m, l, pad
+
+struct bp_attn_ctx {
+  bp_attn_config cfg;
+  uint32_t q_dim, kv_dim, nb, qpg;  // qpg = query heads per KV head
+  uint64_t d_total, kv_bytes;
+  uint8_t* kv[2];    // device: kv_k, kv_v (d-section then qs-section)
+  __half* rope;      // device: [max_seq][64][2] (cos, sin)
+  float* partials;   // device: split-KV scratch [max_splits][n_head][BP_PART_STRIDE]
+  uint32_t* tickets; // device: one arrival counter per layer (self-resetting)
+  uint32_t* err_host; // pinned, mapped: kernels store a non-zero code here when a bounded wait gives up
+  uint32_t* err_dev;  // device alias of err_host
+  uint32_t max_splits;
+  // TMA descriptors over the cache, built once: quants as (128 B, kv heads,
+  // rows), scales as (row bytes, rows); rows run over all layers.
+  CUtensorMap map_qs[2];
+  CUtensorMap map_d[2];
+  bool have_maps;
+  // staging for the *_host entry points
+  __half *stage_q, *stage_k, *stage_v, *stage_out, *stage_wq, *stage_wk;
+  uint32_t stage_rows;
+  cudaStream_t host_stream;
+  int sm_count;
+  uint32_t variant;
+  uint32_t last_launches;
+  int status;  // latched device-lost status, BP_OK otherwise
+  bp_error_detail detail;
+  char msg[256];
+};
+
+// Byte offset of layer `il`'s scales / quants inside a cache buffer
+// (kv_layer_offsets, src/forward.rs:53-58).
+__host__ __device__ inline uint64_t bp_d_off(const bp_attn_ctx* c, uint32_t il) {
+  return (uint64_t)il * c->cfg.max_seq * c->nb * 4u;
+}
+__host__ __device__ inline uint64_t bp_qs_off(const bp_attn_ctx* c, uint32_t il) {
+  return c->d_total + (uint64_t)il * c->cfg.max_seq * c->kv_dim;
+}
+
+// Kernel launchers (one per kernel file). Each returns the cudaError_t of its
+// launches and adds the number of kernels launched to *launches.
+cudaError_t bp_launch_q_norm_rope(bp_attn_ctx* c, cudaStream_t s, __half* q, const __half* w,
+                                  uint32_t pos_base, uint32_t m, uint32_t* launches);
+cudaError_t bp_launch_kv_writeback(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, const __half* k,
+                                   const __half* v, const __half* w, uint32_t pos_base, uint32_t m,
+                                   uint32_t* launches);
+cudaError_t bp_launch_decode(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, const __half* q,
+                             __half* out, uint32_t cur_pos, uint32_t* launches);
+cudaError_t bp_launch_prefill(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, const __half* q,
+                              __half* out, uint32_t m, uint32_t* launches);
+uint32_t bp_decode_splits(const bp_attn_ctx* c, uint32_t cur_pos);
+uint32_t bp_decode_max_splits(const bp_attn_ctx* c);

@@ -1,0 +1,546 @@
+// Host side of the attention library: the context that owns the KV cache, the
+// RoPE table and the split-KV scratch (the part of `Model` this path needs,
+// src/model.rs:1148-1248), the guards of the five dispatch sites, the
+// host-buffer entry points, cache import/export and the KvSnapshot blob.
+#include <math.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <new>
+#include <vector>
+
+#include "bp_common.cuh"
+
+cudaError_t bp_decode_init(bp_attn_ctx* c);
+cudaError_t bp_prefill_init(bp_attn_ctx* c);
+uint32_t bp_decode_stage_tokens(const bp_attn_ctx* c);
+uint32_t bp_prefill_stage_tokens();
+
+namespace {
+
+constexpr char SNAP_MAGIC[8] = {'B', 'O', 'N', 'S', 'A', 'I', 'K', 'V'};
+constexpr uint32_t SNAP_VERSION = 1;
+constexpr uint64_t SNAP_HEADER = 32;
+
+int fail(bp_attn_ctx* c, int status, const char* msg, uint32_t pos = 0, uint32_t n = 0,
+         uint32_t max = 0, int cuda_error = 0) {
+  if (c) {
+    c->detail.status = status;
+    c->detail.pos = pos;
+    c->detail.n = n;
+    c->detail.max = max;
+    c->detail.cuda_error = cuda_error;
+    snprintf(c->msg, sizeof c->msg, "%s", msg);
+  }
+  return status;
+}
+
+int fail_config(bp_attn_ctx* c, const char* what) {
+  char buf[224];
+  snprintf(buf, sizeof buf, "invalid config: %s", what);
+  return fail(c, BP_ERR_CONFIG, buf);
+}
+
+int fail_overflow(bp_attn_ctx* c, uint32_t pos, uint32_t n, uint32_t max) {
+  char buf[224];
+  snprintf(buf, sizeof buf, "context overflow: pos %u + tokens %u > max_seq %u", pos, n, max);
+  return fail(c, BP_ERR_CONTEXT_OVERFLOW, buf, pos, n, max);
+}
+
+// A failed CUDA call whose error is sticky means the context is gone for good:
+// latch it, as the reference latches a lost wgpu device (src/model.rs:1081-1099).
+int fail_cuda(bp_attn_ctx* c, cudaError_t e, const char* where) {
+  char buf[224];
+  snprintf(buf, sizeof buf, "CUDA error in %s: %s", where, cudaGetErrorString(e));
+  if (c && (e == cudaErrorIllegalAddress || e == cudaErrorLaunchFailure ||
+            e == cudaErrorIllegalInstruction || e == cudaErrorECCUncorrectable ||
+            e == cudaErrorHardwareStackError || e == cudaErrorMisalignedAddress)) {
+    c->status = BP_ERR_DEVICE_LOST;
+    snprintf(buf, sizeof buf, "device lost (%s in %s)", cudaGetErrorString(e), where);
+    return fail(c, BP_ERR_DEVICE_LOST, buf, 0, 0, 0, static_cast<int>(e));
+  }
+  return fail(c, BP_ERR_CUDA, buf, 0, 0, 0, static_cast<int>(e));
+}
+
+#define BP_CUDA(c, call)                                   \
+  do {                                                     \
+    cudaError_t e_ = (call);                               \
+    if (e_ != cudaSuccess) return fail_cuda(c, e_, #call); \
+  } while (0)
+
+// Every entry point starts here (check_device, src/model.rs:1733-1741).
+int enter(bp_attn_ctx* c) {
+  if (!c) return BP_ERR_NULL;
+  if (c->status != BP_OK) return fail(c, c->status, "device lost: context is unusable, create a new one");
+  return BP_OK;
+}
+
+int bind_device(bp_attn_ctx* c) {
+  BP_CUDA(c, cudaSetDevice(c->cfg.device));
+  return BP_OK;
+}
+
+// f32 -> f16, round to nearest even (the cast of src/model.rs:1149).
+uint16_t f32_to_f16(float f) {
+  __half h = __float2half_rn(f);  // host path of cuda_fp16.h rounds to nearest even
+  uint16_t u;
+  memcpy(&u, &h, 2);
+  return u;
+}
+
+typedef CUresult (*encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                    CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                    CUtensorMapFloatOOBfill);
+
+encode_tiled_fn get_encode() {
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+      qres != cudaDriverEntryPointSuccess)
+    return nullptr;
+  return reinterpret_cast<encode_tiled_fn>(fn);
+}
+
+}  // namespace
+
+// Tensor maps over one cache buffer. Quants: u8 (128 B, kv heads, rows) with a
+// (128, 1, rows_box) box; scales: u8 (row bytes, rows) with an (inner, rows_box)
+// box at byte offset `inner`-aligned. Rows run over all layers.
+bool bp_make_kv_maps(bp_attn_ctx* c, int kind, uint32_t rows_box, uint32_t d_inner, bool d_swizzle,
+                     CUtensorMap* map_qs, CUtensorMap* map_d) {
+  static encode_tiled_fn encode = get_encode();
+  if (!encode) return false;
+  const cuuint64_t rows = static_cast<cuuint64_t>(c->cfg.n_layer) * c->cfg.max_seq;
+  {
+    cuuint64_t dims[3] = {128, c->cfg.n_kv_head, rows};
+    cuuint64_t strides[2] = {128, c->kv_dim};
+    cuuint32_t box[3] = {128, 1, rows_box};
+    cuuint32_t es[3] = {1, 1, 1};
+    if (encode(map_qs, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, c->kv[kind] + c->d_total, dims, strides, box, es,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return false;
+  }
+  {
+    const uint32_t rb = c->nb * 4;
+    cuuint64_t dims[2] = {rb, rows};
+    cuuint64_t strides[1] = {rb};
+    cuuint32_t box[2] = {d_inner, rows_box};
+    cuuint32_t es[2] = {1, 1};
+    if (encode(map_d, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, c->kv[kind], dims, strides, box, es,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, d_swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return false;
+  }
+  return true;
+}
+
+extern "C" {
+
+const char* bp_strerror(int status) {
+  switch (status) {
+    case BP_OK: return "ok";
+    case BP_ERR_CONFIG: return "invalid config";
+    case BP_ERR_CONTEXT_OVERFLOW: return "context overflow";
+    case BP_ERR_PREFILL_TOO_LARGE: return "prefill batch exceeds max_prefill_tokens";
+    case BP_ERR_DEVICE_LOST: return "device lost";
+    case BP_ERR_CUDA: return "CUDA error";
+    case BP_ERR_TIMEOUT: return "device-side wait timed out";
+    case BP_ERR_NULL: return "null pointer argument";
+    default: return "unknown status";
+  }
+}
+
+int bp_attn_create(const bp_attn_config* cfg, bp_attn_ctx** out) {
+  if (!cfg || !out) return BP_ERR_NULL;
+  *out = nullptr;
+  bp_attn_ctx* c = new (std::nothrow) bp_attn_ctx();
+  if (!c) return BP_ERR_CUDA;
+  memset(c, 0, sizeof *c);
+  c->cfg = *cfg;
+  *out = c;  // returned even on failure so the caller can read the message; destroy it either way
+
+  // Validation, in the reference's words where it has them.
+  if (cfg->head_dim != 128)
+    return fail_config(c, "kv_writeback_fused.wgsl / q_norm_rope_fused.wgsl assume head_dim == 128");
+  if (cfg->n_layer == 0 || cfg->n_head == 0 || cfg->n_kv_head == 0) return fail_config(c, "n_layer, n_head and n_kv_head must be > 0");
+  if (cfg->n_head % cfg->n_kv_head != 0) return fail_config(c, "n_head must be a multiple of n_kv_head");
+  if ((cfg->n_kv_head * cfg->head_dim) % 32 != 0) return fail_config(c, "kv_dim must be a multiple of 32 (Q8_0 block size)");
+  if (cfg->max_seq == 0) return fail_config(c, "max_seq must be > 0");
+  if (cfg->n_head / cfg->n_kv_head > 8) return fail_config(c, "at most 8 query heads per KV head are supported");
+  if (cfg->n_kv_head != 1 && cfg->n_kv_head != 2 && cfg->n_kv_head != 4 && cfg->n_kv_head != 8)
+    return fail_config(c, "a context holds 1, 2, 4 or 8 KV heads");
+  if (cfg->n_shards == 0 || cfg->shard >= cfg->n_shards) return fail_config(c, "shard must be < n_shards and n_shards > 0");
+  if (!(cfg->rms_eps >= 0.0f) || !(cfg->rope_freq_base > 0.0f)) return fail_config(c, "rms_eps must be >= 0 and rope_freq_base > 0");
+  if (static_cast<uint64_t>(cfg->n_layer) * cfg->max_seq >= (1ull << 31)) return fail_config(c, "n_layer * max_seq must be < 2^31");
+
+  c->q_dim = cfg->n_head * cfg->head_dim;
+  c->kv_dim = cfg->n_kv_head * cfg->head_dim;
+  c->nb = c->kv_dim / BP_QK8;
+  c->qpg = cfg->n_head / cfg->n_kv_head;
+  c->d_total = static_cast<uint64_t>(cfg->n_layer) * cfg->max_seq * c->nb * 4u;
+  c->kv_bytes = c->d_total + static_cast<uint64_t>(cfg->n_layer) * cfg->max_seq * c->kv_dim;
+
+  int n_dev = 0;
+  cudaError_t e = cudaGetDeviceCount(&n_dev);
+  if (e != cudaSuccess || n_dev == 0)
+    return fail(c, BP_ERR_CUDA, "no CUDA device: this library has no CPU path", 0, 0, 0, static_cast<int>(e));
+  if (cfg->device < 0 || cfg->device >= n_dev) return fail_config(c, "device ordinal out of range");
+  BP_CUDA(c, cudaSetDevice(cfg->device));
+  cudaDeviceProp prop;
+  BP_CUDA(c, cudaGetDeviceProperties(&prop, cfg->device));
+  if (prop.major != 10) return fail(c, BP_ERR_CUDA, "this library is built for sm_100a (B200) only");
+  c->sm_count = prop.multiProcessorCount;
+
+  BP_CUDA(c, cudaMalloc(&c->kv[0], c->kv_bytes));
+  BP_CUDA(c, cudaMalloc(&c->kv[1], c->kv_bytes));
+
+  // RoPE table: build_rope_table (src/model.rs:1756-1769) in f64, cast to f32
+  // then to f16 (src/model.rs:1148-1149).
+  {
+    const size_t n = static_cast<size_t>(cfg->max_seq) * cfg->head_dim;
+    std::vector<uint16_t> table(n);
+    const uint32_t half = cfg->head_dim / 2;
+    std::vector<double> theta(half);
+    for (uint32_t j = 0; j < half; j++)
+      theta[j] = pow(static_cast<double>(cfg->rope_freq_base), -2.0 * static_cast<double>(j) / static_cast<double>(cfg->head_dim));
+    for (uint32_t p = 0; p < cfg->max_seq; p++) {
+      for (uint32_t j = 0; j < half; j++) {
+        const double angle = static_cast<double>(p) * theta[j];
+        table[static_cast<size_t>(p) * cfg->head_dim + 2 * j] = f32_to_f16(static_cast<float>(cos(angle)));
+        table[static_cast<size_t>(p) * cfg->head_dim + 2 * j + 1] = f32_to_f16(static_cast<float>(sin(angle)));
+      }
+    }
+    BP_CUDA(c, cudaMalloc(&c->rope, n * 2));
+    BP_CUDA(c, cudaMemcpy(c->rope, table.data(), n * 2, cudaMemcpyHostToDevice));
+  }
+
+  c->max_splits = bp_decode_max_splits(c);
+  BP_CUDA(c, cudaMalloc(&c->partials, static_cast<size_t>(c->max_splits) * cfg->n_head * BP_PART_STRIDE * sizeof(float)));
+  BP_CUDA(c, cudaMalloc(&c->tickets, (cfg->n_layer + 1) * sizeof(uint32_t)));
+  BP_CUDA(c, cudaMemset(c->tickets, 0, (cfg->n_layer + 1) * sizeof(uint32_t)));
+  BP_CUDA(c, cudaHostAlloc(&c->err_host, sizeof(uint32_t), cudaHostAllocMapped));
+  *c->err_host = 0;
+  BP_CUDA(c, cudaHostGetDevicePointer(&c->err_dev, c->err_host, 0));
+
+  c->have_maps = true;
+  for (int kind = 0; kind < 2 && c->have_maps; kind++) {
+    c->have_maps = bp_make_kv_maps(c, kind, bp_decode_stage_tokens(c), c->nb * 4, c->nb * 4 == 128,
+                                   &c->map_qs[kind], &c->map_d[kind]);
+  }
+  if (!c->have_maps) return fail(c, BP_ERR_CUDA, "cuTensorMapEncodeTiled failed for the KV cache");
+  BP_CUDA(c, bp_decode_init(c));
+  BP_CUDA(c, bp_prefill_init(c));
+  BP_CUDA(c, cudaStreamCreateWithFlags(&c->host_stream, cudaStreamNonBlocking));
+  return BP_OK;
+}
+
+void bp_attn_destroy(bp_attn_ctx* c) {
+  if (!c) return;
+  if (c->kv[0] || c->rope) cudaSetDevice(c->cfg.device);
+  cudaFree(c->kv[0]);
+  cudaFree(c->kv[1]);
+  cudaFree(c->rope);
+  cudaFree(c->partials);
+  cudaFree(c->tickets);
+  if (c->err_host) cudaFreeHost(c->err_host);
+  cudaFree(c->stage_q);
+  cudaFree(c->stage_k);
+  cudaFree(c->stage_v);
+  cudaFree(c->stage_out);
+  cudaFree(c->stage_wq);
+  cudaFree(c->stage_wk);
+  if (c->host_stream) cudaStreamDestroy(c->host_stream);
+  delete c;
+}
+
+int bp_q_norm_rope(bp_attn_ctx* c, void* stream, void* q, const void* w_q_norm, uint32_t pos_base, uint32_t m) {
+  if (int s = enter(c)) return s;
+  if (!q || !w_q_norm) return fail(c, BP_ERR_NULL, "null pointer argument");
+  if (m == 0) return BP_OK;
+  if (static_cast<uint64_t>(pos_base) + m > c->cfg.max_seq) return fail_overflow(c, pos_base, m, c->cfg.max_seq);
+  c->last_launches = 0;
+  BP_CUDA(c, bp_launch_q_norm_rope(c, static_cast<cudaStream_t>(stream), static_cast<__half*>(q),
+                                   static_cast<const __half*>(w_q_norm), pos_base, m, &c->last_launches));
+  return BP_OK;
+}
+
+int bp_kv_writeback(bp_attn_ctx* c, void* stream, uint32_t layer, const void* k_cur, const void* v_cur,
+                    const void* w_k_norm, uint32_t pos_base, uint32_t m) {
+  if (int s = enter(c)) return s;
+  if (!k_cur || !v_cur || !w_k_norm) return fail(c, BP_ERR_NULL, "null pointer argument");
+  if (layer >= c->cfg.n_layer) return fail_config(c, "layer index out of range");
+  if (static_cast<uint64_t>(pos_base) + m > c->cfg.max_seq) return fail_overflow(c, pos_base, m, c->cfg.max_seq);
+  if (m == 0) return BP_OK;
+  c->last_launches = 0;
+  BP_CUDA(c, bp_launch_kv_writeback(c, static_cast<cudaStream_t>(stream), layer, static_cast<const __half*>(k_cur),
+                                    static_cast<const __half*>(v_cur), static_cast<const __half*>(w_k_norm),
+                                    pos_base, m, &c->last_launches));
+  return BP_OK;
+}
+
+int bp_attn_decode(bp_attn_ctx* c, void* stream, uint32_t layer, const void* q, void* out, uint32_t cur_pos) {
+  if (int s = enter(c)) return s;
+  if (!q || !out) return fail(c, BP_ERR_NULL, "null pointer argument");
+  if (layer >= c->cfg.n_layer) return fail_config(c, "layer index out of range");
+  if (cur_pos == 0) return fail_config(c, "decode attention needs at least one key (cur_pos >= 1)");
+  if (cur_pos > c->cfg.max_seq) return fail_overflow(c, cur_pos - 1, 1, c->cfg.max_seq);
+  c->last_launches = 0;
+  BP_CUDA(c, bp_launch_decode(c, static_cast<cudaStream_t>(stream), layer, static_cast<const __half*>(q),
+                              static_cast<__half*>(out), cur_pos, &c->last_launches));
+  return BP_OK;
+}
+
+uint32_t bp_attn_max_prefill(const bp_attn_ctx* c) {
+  if (!c) return 0;
+  return c->cfg.max_prefill ? (c->cfg.max_prefill < c->cfg.max_seq ? c->cfg.max_prefill : c->cfg.max_seq) : c->cfg.max_seq;
+}
+
+int bp_attn_prefill(bp_attn_ctx* c, void* stream, uint32_t layer, const void* q, void* out, uint32_t m) {
+  if (int s = enter(c)) return s;
+  if (!q || !out) return fail(c, BP_ERR_NULL, "null pointer argument");
+  if (layer >= c->cfg.n_layer) return fail_config(c, "layer index out of range");
+  if (m == 0) return fail_config(c, "prefill needs at least one token");
+  if (c->cfg.max_prefill && m > c->cfg.max_prefill) {
+    char buf[224];
+    snprintf(buf, sizeof buf, "prefill batch %u exceeds max_prefill_tokens %u", m, c->cfg.max_prefill);
+    return fail(c, BP_ERR_PREFILL_TOO_LARGE, buf, 0, m, c->cfg.max_prefill);
+  }
+  if (m > c->cfg.max_seq) return fail_overflow(c, 0, m, c->cfg.max_seq);
+  c->last_launches = 0;
+  BP_CUDA(c, bp_launch_prefill(c, static_cast<cudaStream_t>(stream), layer, static_cast<const __half*>(q),
+                               static_cast<__half*>(out), m, &c->last_launches));
+  return BP_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Host-buffer entry points.
+// ---------------------------------------------------------------------------
+static int ensure_stage(bp_attn_ctx* c, uint32_t rows) {
+  if (rows <= c->stage_rows) return BP_OK;
+  cudaFree(c->stage_q); cudaFree(c->stage_k); cudaFree(c->stage_v); cudaFree(c->stage_out);
+  c->stage_q = c->stage_k = c->stage_v = c->stage_out = nullptr;
+  c->stage_rows = 0;
+  BP_CUDA(c, cudaMalloc(&c->stage_q, static_cast<size_t>(rows) * c->q_dim * 2));
+  BP_CUDA(c, cudaMalloc(&c->stage_out, static_cast<size_t>(rows) * c->q_dim * 2));
+  BP_CUDA(c, cudaMalloc(&c->stage_k, static_cast<size_t>(rows) * c->kv_dim * 2));
+  BP_CUDA(c, cudaMalloc(&c->stage_v, static_cast<size_t>(rows) * c->kv_dim * 2));
+  if (!c->stage_wq) {
+    BP_CUDA(c, cudaMalloc(&c->stage_wq, BP_HEAD_DIM * 2));
+    BP_CUDA(c, cudaMalloc(&c->stage_wk, BP_HEAD_DIM * 2));
+  }
+  c->stage_rows = rows;
+  return BP_OK;
+}
+
+static int layer_host(bp_attn_ctx* c, uint32_t layer, const void* q, const void* k, const void* v, const void* wq,
+                      const void* wk, uint32_t pos_base, uint32_t m, bool prefill, void* out) {
+  if (int s = enter(c)) return s;
+  if (!q || !k || !v || !wq || !wk || !out) return fail(c, BP_ERR_NULL, "null pointer argument");
+  if (layer >= c->cfg.n_layer) return fail_config(c, "layer index out of range");
+  if (m == 0) return fail_config(c, "at least one token is needed");
+  if (prefill && c->cfg.max_prefill && m > c->cfg.max_prefill) {
+    char buf[224];
+    snprintf(buf, sizeof buf, "prefill batch %u exceeds max_prefill_tokens %u", m, c->cfg.max_prefill);
+    return fail(c, BP_ERR_PREFILL_TOO_LARGE, buf, 0, m, c->cfg.max_prefill);
+  }
+  if (static_cast<uint64_t>(pos_base) + m > c->cfg.max_seq) return fail_overflow(c, pos_base, m, c->cfg.max_seq);
+  if (int s = bind_device(c)) return s;
+  if (int s = ensure_stage(c, m)) return s;
+  cudaStream_t st = c->host_stream;
+  const size_t qb = static_cast<size_t>(m) * c->q_dim * 2, kb = static_cast<size_t>(m) * c->kv_dim * 2;
+  BP_CUDA(c, cudaMemcpyAsync(c->stage_q, q, qb, cudaMemcpyHostToDevice, st));
+  BP_CUDA(c, cudaMemcpyAsync(c->stage_k, k, kb, cudaMemcpyHostToDevice, st));
+  BP_CUDA(c, cudaMemcpyAsync(c->stage_v, v, kb, cudaMemcpyHostToDevice, st));
+  BP_CUDA(c, cudaMemcpyAsync(c->stage_wq, wq, BP_HEAD_DIM * 2, cudaMemcpyHostToDevice, st));
+  BP_CUDA(c, cudaMemcpyAsync(c->stage_wk, wk, BP_HEAD_DIM * 2, cudaMemcpyHostToDevice, st));
+  uint32_t launches = 0;
+  BP_CUDA(c, bp_launch_q_norm_rope(c, st, c->stage_q, c->stage_wq, pos_base, m, &launches));
+  BP_CUDA(c, bp_launch_kv_writeback(c, st, layer, c->stage_k, c->stage_v, c->stage_wk, pos_base, m, &launches));
+  if (prefill) {
+    BP_CUDA(c, bp_launch_prefill(c, st, layer, c->stage_q, c->stage_out, m, &launches));
+  } else {
+    BP_CUDA(c, bp_launch_decode(c, st, layer, c->stage_q, c->stage_out, pos_base + 1, &launches));
+  }
+  BP_CUDA(c, cudaMemcpyAsync(out, c->stage_out, qb, cudaMemcpyDeviceToHost, st));
+  BP_CUDA(c, cudaStreamSynchronize(st));
+  c->last_launches = launches;
+  if (*c->err_host) return fail(c, BP_ERR_TIMEOUT, "a bounded device-side wait gave up");
+  return BP_OK;
+}
+
+int bp_decode_step_host(bp_attn_ctx* c, uint32_t layer, const void* q, const void* k, const void* v, const void* wq,
+                        const void* wk, uint32_t pos, void* out) {
+  return layer_host(c, layer, q, k, v, wq, wk, pos, 1, false, out);
+}
+
+int bp_prefill_layer_host(bp_attn_ctx* c, uint32_t layer, const void* q, const void* k, const void* v,
+                          const void* wq, const void* wk, uint32_t m, void* out) {
+  return layer_host(c, layer, q, k, v, wq, wk, 0, m, true, out);
+}
+
+// ---------------------------------------------------------------------------
+// Cache sections and snapshots.
+// ---------------------------------------------------------------------------
+static int kv_copy(bp_attn_ctx* c, uint32_t kind, uint32_t layer, uint32_t sect, uint32_t pos, void* host, bool to_host) {
+  if (int s = enter(c)) return s;
+  if (!host && pos) return fail(c, BP_ERR_NULL, "null pointer argument");
+  if (kind > 1 || sect > 1) return fail_config(c, "kind and sect must be 0 or 1");
+  if (layer >= c->cfg.n_layer) return fail_config(c, "layer index out of range");
+  if (pos > c->cfg.max_seq) return fail_overflow(c, 0, pos, c->cfg.max_seq);
+  if (pos == 0) return BP_OK;
+  if (int s = bind_device(c)) return s;
+  uint8_t* dev = c->kv[kind] + (sect == 0 ? bp_d_off(c, layer) : bp_qs_off(c, layer));
+  const size_t bytes = static_cast<size_t>(pos) * (sect == 0 ? c->nb * 4u : c->kv_dim);
+  if (to_host) {
+    BP_CUDA(c, cudaMemcpy(host, dev, bytes, cudaMemcpyDeviceToHost));
+  } else {
+    BP_CUDA(c, cudaMemcpy(dev, host, bytes, cudaMemcpyHostToDevice));
+  }
+  return BP_OK;
+}
+
+int bp_kv_export(bp_attn_ctx* c, uint32_t kind, uint32_t layer, uint32_t sect, uint32_t pos, void* host) {
+  return kv_copy(c, kind, layer, sect, pos, host, true);
+}
+int bp_kv_import(bp_attn_ctx* c, uint32_t kind, uint32_t layer, uint32_t sect, uint32_t pos, const void* host) {
+  return kv_copy(c, kind, layer, sect, pos, const_cast<void*>(host), false);
+}
+
+uint64_t bp_snapshot_payload_bytes(uint32_t n_layer, uint32_t kv_dim, uint32_t pos) {
+  const uint64_t d_layer = static_cast<uint64_t>(pos) * (kv_dim / 32) * 4u;
+  const uint64_t qs_layer = static_cast<uint64_t>(pos) * kv_dim;
+  return 2u * static_cast<uint64_t>(n_layer) * (d_layer + qs_layer);
+}
+
+uint64_t bp_snapshot_payload_offset(uint32_t n_layer, uint32_t kv_dim, uint32_t pos, uint32_t kind, uint32_t il,
+                                    uint32_t sect) {
+  const uint64_t d_layer = static_cast<uint64_t>(pos) * (kv_dim / 32) * 4u;
+  const uint64_t qs_layer = static_cast<uint64_t>(pos) * kv_dim;
+  const uint64_t layer_bytes = d_layer + qs_layer;
+  const uint64_t base = static_cast<uint64_t>(kind) * n_layer * layer_bytes + static_cast<uint64_t>(il) * layer_bytes;
+  return sect == 0 ? base : base + d_layer;
+}
+
+uint64_t bp_snapshot_size(const bp_attn_ctx* c, uint32_t pos) {
+  if (!c) return 0;
+  return SNAP_HEADER + bp_snapshot_payload_bytes(c->cfg.n_layer, c->kv_dim * c->cfg.n_shards, pos);
+}
+
+// Strided copies between this shard's columns of the global rows and its dense
+// device rows: `width` bytes at byte `col` of every `pitch`-byte global row.
+static cudaError_t shard_copy(void* host_row0, size_t pitch, size_t col, uint8_t* dev, size_t width, uint32_t rows,
+                              bool to_host) {
+  if (to_host)
+    return cudaMemcpy2D(static_cast<uint8_t*>(host_row0) + col, pitch, dev, width, width, rows, cudaMemcpyDeviceToHost);
+  return cudaMemcpy2D(dev, width, static_cast<uint8_t*>(host_row0) + col, pitch, width, rows, cudaMemcpyHostToDevice);
+}
+
+int bp_snapshot_capture(bp_attn_ctx* c, uint32_t pos, void* blob, uint64_t blob_bytes) {
+  if (int s = enter(c)) return s;
+  if (!blob) return fail(c, BP_ERR_NULL, "null pointer argument");
+  if (pos > c->cfg.max_seq) return fail_overflow(c, 0, pos, c->cfg.max_seq);
+  if (blob_bytes < bp_snapshot_size(c, pos)) return fail_config(c, "snapshot buffer is too small");
+  if (int s = bind_device(c)) return s;
+  const uint32_t kv_dim_g = c->kv_dim * c->cfg.n_shards;
+  uint8_t* b = static_cast<uint8_t*>(blob);
+  memcpy(b, SNAP_MAGIC, 8);
+  const uint32_t hdr[6] = {SNAP_VERSION, c->cfg.n_layer, kv_dim_g, c->cfg.max_seq, pos, 0};
+  memcpy(b + 8, hdr, 24);
+  if (pos == 0) return BP_OK;
+  uint8_t* payload = b + SNAP_HEADER;
+  for (uint32_t kind = 0; kind < 2; kind++) {
+    for (uint32_t il = 0; il < c->cfg.n_layer; il++) {
+      uint8_t* d_dst = payload + bp_snapshot_payload_offset(c->cfg.n_layer, kv_dim_g, pos, kind, il, 0);
+      uint8_t* q_dst = payload + bp_snapshot_payload_offset(c->cfg.n_layer, kv_dim_g, pos, kind, il, 1);
+      BP_CUDA(c, shard_copy(d_dst, static_cast<size_t>(kv_dim_g / 32) * 4, static_cast<size_t>(c->cfg.shard) * c->nb * 4,
+                            c->kv[kind] + bp_d_off(c, il), c->nb * 4, pos, true));
+      BP_CUDA(c, shard_copy(q_dst, kv_dim_g, static_cast<size_t>(c->cfg.shard) * c->kv_dim,
+                            c->kv[kind] + bp_qs_off(c, il), c->kv_dim, pos, true));
+    }
+  }
+  return BP_OK;
+}
+
+int bp_snapshot_apply(bp_attn_ctx* c, const void* blob, uint64_t blob_bytes, uint32_t* pos_out) {
+  if (int s = enter(c)) return s;
+  if (!blob) return fail(c, BP_ERR_NULL, "null pointer argument");
+  const uint8_t* b = static_cast<const uint8_t*>(blob);
+  if (blob_bytes < SNAP_HEADER) return fail_config(c, "KvSnapshot blob too short: missing header");
+  if (memcmp(b, SNAP_MAGIC, 8) != 0) return fail_config(c, "KvSnapshot blob has wrong magic");
+  uint32_t hdr[6];
+  memcpy(hdr, b + 8, 24);
+  if (hdr[0] != SNAP_VERSION) return fail_config(c, "KvSnapshot blob has unsupported version");
+  if (hdr[5] != 0) return fail_config(c, "KvSnapshot blob has non-zero reserved field");
+  const uint32_t n_layer = hdr[1], kv_dim_g = hdr[2], pos = hdr[4];
+  if (blob_bytes - SNAP_HEADER != bp_snapshot_payload_bytes(n_layer, kv_dim_g, pos))
+    return fail_config(c, "KvSnapshot blob payload length does not match header");
+  if (n_layer != c->cfg.n_layer || kv_dim_g != c->kv_dim * c->cfg.n_shards)
+    return fail_config(c, "KvSnapshot does not match model: n_layer or kv_dim differs");
+  if (pos > c->cfg.max_seq) return fail_overflow(c, 0, pos, c->cfg.max_seq);
+  if (int s = bind_device(c)) return s;
+  uint8_t* payload = const_cast<uint8_t*>(b) + SNAP_HEADER;
+  for (uint32_t kind = 0; kind < 2 && pos; kind++) {
+    for (uint32_t il = 0; il < n_layer; il++) {
+      uint8_t* d_src = payload + bp_snapshot_payload_offset(n_layer, kv_dim_g, pos, kind, il, 0);
+      uint8_t* q_src = payload + bp_snapshot_payload_offset(n_layer, kv_dim_g, pos, kind, il, 1);
+      BP_CUDA(c, shard_copy(d_src, static_cast<size_t>(kv_dim_g / 32) * 4, static_cast<size_t>(c->cfg.shard) * c->nb * 4,
+                            c->kv[kind] + bp_d_off(c, il), c->nb * 4, pos, false));
+      BP_CUDA(c, shard_copy(q_src, kv_dim_g, static_cast<size_t>(c->cfg.shard) * c->kv_dim,
+                            c->kv[kind] + bp_qs_off(c, il), c->kv_dim, pos, false));
+    }
+  }
+  if (pos_out) *pos_out = pos;
+  return BP_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Status and introspection.
+// ---------------------------------------------------------------------------
+int bp_ctx_status(const bp_attn_ctx* c) {
+  if (!c) return BP_ERR_NULL;
+  if (c->status != BP_OK) return c->status;
+  // Meaningful once the stream that ran the kernels has been synchronised.
+  if (c->err_host && *c->err_host) return BP_ERR_TIMEOUT;
+  return BP_OK;
+}
+
+void bp_ctx_inject_lost(bp_attn_ctx* c) {
+  if (!c) return;
+  c->status = BP_ERR_DEVICE_LOST;
+  fail(c, BP_ERR_DEVICE_LOST, "device lost (injected by bp_ctx_inject_lost)");
+}
+
+void bp_last_error_detail(const bp_attn_ctx* c, bp_error_detail* out) {
+  if (c && out) *out = c->detail;
+}
+const char* bp_last_error_message(const bp_attn_ctx* c) { return c ? c->msg : ""; }
+
+void* bp_kv_device_ptr(bp_attn_ctx* c, uint32_t kind) { return (c && kind < 2) ? c->kv[kind] : nullptr; }
+uint64_t bp_kv_buffer_bytes(const bp_attn_ctx* c) { return c ? c->kv_bytes : 0; }
+const void* bp_rope_device_ptr(const bp_attn_ctx* c) { return c ? c->rope : nullptr; }
+
+int bp_rope_table_copy(bp_attn_ctx* c, void* host_f16) {
+  if (int s = enter(c)) return s;
+  if (!host_f16) return fail(c, BP_ERR_NULL, "null pointer argument");
+  if (int s = bind_device(c)) return s;
+  BP_CUDA(c, cudaMemcpy(host_f16, c->rope, static_cast<size_t>(c->cfg.max_seq) * BP_HEAD_DIM * 2, cudaMemcpyDeviceToHost));
+  return BP_OK;
+}
+
+int bp_set_variant(bp_attn_ctx* c, uint32_t variant) {
+  if (!c) return BP_ERR_NULL;
+  if (variant > 2) return fail_config(c, "unknown kernel variant");
+  c->variant = variant;
+  return BP_OK;
+}
+
+uint32_t bp_last_launch_count(const bp_attn_ctx* c) { return c ? c->last_launches : 0; }
+uint32_t bp_decode_num_splits(const bp_attn_ctx* c, uint32_t cur_pos) {
+  if (!c || cur_pos == 0) return 0;
+  return bp_decode_splits(c, cur_pos);
+}
+
+}  // extern "C"

@@ -1,0 +1,190 @@
+/*
+ * bonsai_attn.h - C ABI of the B200 (sm_100a) attention hot path for bonsai-pot.
+ *
+ * The reference engine (Rust + WGSL on wgpu) has no plugin seam for this path:
+ * its five attention dispatch sites are private functions of src/forward.rs
+ * that record compute dispatches on buffers owned by `Model`. This header cuts
+ * the seam at those five sites. Each entry point names the reference interface
+ * it replaces (paths relative to the reference repository). A Rust `-sys`
+ * crate, or any other FFI, binds exactly these symbols.
+ *
+ * Conventions (mirroring the reference):
+ *   - One opaque context owns the KV cache (`kv_k`, `kv_v`), the RoPE table and
+ *     the split-KV scratch, as `Model` does (src/model.rs:1184-1248). Callers
+ *     own the activations and pass raw DEVICE pointers to IEEE binary16 data
+ *     (pointer = the reference's `act` buffer + element offset).
+ *   - A context is not thread-safe and serves one sequence at a time
+ *     (src/session.rs:69-88). Every call is asynchronous on the CUDA stream it
+ *     is given (`void*` = `cudaStream_t`, NULL = the default stream); nothing
+ *     synchronises except the `*_host` calls, import/export and snapshots.
+ *   - Guards run before any GPU work and return a status, never abort
+ *     (src/session.rs:163-176, src/forward.rs:982-994). A lost device latches:
+ *     every later call returns BP_ERR_DEVICE_LOST (src/model.rs:1733-1741).
+ *   - KV cache bytes are the reference's: per buffer a d-section of FP32 block
+ *     scales followed by a qs-section of int8 quants (src/forward.rs:40-58).
+ *   - There is no CPU fallback: without a CUDA device every compute entry point
+ *     returns BP_ERR_CUDA.
+ */
+#ifndef BONSAI_ATTN_H
+#define BONSAI_ATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct bp_attn_ctx bp_attn_ctx;
+
+/* Status codes; the comment names the `PotError` variant each one carries
+ * (src/error.rs:7-40). */
+enum {
+  BP_OK = 0,
+  BP_ERR_CONFIG = 1,            /* PotError::Config(&str) */
+  BP_ERR_CONTEXT_OVERFLOW = 2,  /* PotError::ContextOverflow { pos, n, max } */
+  BP_ERR_PREFILL_TOO_LARGE = 3, /* PotError::PrefillTooLarge { n, max } */
+  BP_ERR_DEVICE_LOST = 4,       /* PotError::DeviceLost */
+  BP_ERR_CUDA = 5,              /* a CUDA runtime/driver call failed (no reference counterpart) */
+  BP_ERR_TIMEOUT = 6,           /* a bounded device-side wait gave up (multi-GPU exchange) */
+  BP_ERR_NULL = 7               /* a required pointer argument was NULL */
+};
+
+/* The fields of the reference's `Config` + `LoadOptions` that this path reads
+ * (src/model.rs:534-566, 658-837). Validation rules are the reference's:
+ * head_dim == 128 (src/model.rs:1179-1183), kv_dim % 32 == 0
+ * (src/model.rs:1174-1178), n_head % n_kv_head == 0 (src/model.rs:672-676),
+ * max_seq > 0. */
+typedef struct bp_attn_config {
+  uint32_t n_layer;
+  uint32_t n_head;    /* query heads held by THIS context (a shard holds n_head_global / n_shards) */
+  uint32_t n_kv_head; /* KV heads held by THIS context */
+  uint32_t head_dim;  /* must be 128 */
+  uint32_t max_seq;
+  float rms_eps;
+  float rope_freq_base;
+  uint32_t max_prefill; /* 0 = no cap; 512 reproduces the reference's M_MAX (src/model.rs:502) */
+  uint32_t n_shards;    /* KV-head shards the model is split into: 1, 2, 4 or 8 */
+  uint32_t shard;       /* index of this shard, < n_shards */
+  int32_t device;       /* CUDA device ordinal */
+} bp_attn_config;
+
+/* Struct fields of the last error (ContextOverflow / PrefillTooLarge). */
+typedef struct bp_error_detail {
+  int32_t status;
+  uint32_t pos, n, max;
+  int32_t cuda_error;
+} bp_error_detail;
+
+/* Replaces the KV-cache / RoPE-table / attn_partials part of
+ * `Model::load_with_options` (src/model.rs:1148-1165, 1174-1248, 1756-1769).
+ * Cache contents are undefined after creation, as in the reference. */
+int bp_attn_create(const bp_attn_config* cfg, bp_attn_ctx** out);
+void bp_attn_destroy(bp_attn_ctx* ctx);
+
+/* `dispatch_q_norm_rope_fused` (src/forward.rs:392-413, params
+ * src/model.rs:255-262, kernel src/shaders/q_norm_rope_fused.wgsl).
+ * q: device f16 [m][n_head*128], normalised and rotated in place. */
+int bp_q_norm_rope(bp_attn_ctx* ctx, void* stream, void* q, const void* w_q_norm, uint32_t pos_base,
+                   uint32_t m);
+
+/* `dispatch_kv_writeback_fused` (src/forward.rs:359-388, params
+ * src/model.rs:265-276, kernel src/shaders/kv_writeback_fused.wgsl).
+ * k_cur, v_cur: device f16 [m][n_kv_head*128]; writes cache rows
+ * [pos_base, pos_base + m) of `layer`. pos_base + m > max_seq gives
+ * BP_ERR_CONTEXT_OVERFLOW. */
+int bp_kv_writeback(bp_attn_ctx* ctx, void* stream, uint32_t layer, const void* k_cur,
+                    const void* v_cur, const void* w_k_norm, uint32_t pos_base, uint32_t m);
+
+/* The `attention_split` + `attention_merge` pair of `layer_post_kv_in_pass`
+ * (src/forward.rs:822-856, params src/model.rs:213-234). q, out: device f16
+ * [n_head*128]. cur_pos = pos + 1 keys are attended (the new token included);
+ * 1 <= cur_pos <= max_seq. */
+int bp_attn_decode(bp_attn_ctx* ctx, void* stream, uint32_t layer, const void* q, void* out,
+                   uint32_t cur_pos);
+
+/* `dispatch_attention(.., pos = 0, m_tokens = m, is_prefill = true)`
+ * (src/forward.rs:501-532, params src/model.rs:195-210, kernel
+ * src/shaders/attention.wgsl). q, out: device f16 [m][n_head*128]; token i
+ * attends to cache rows [0, i]. m > max_prefill (when non-zero) gives
+ * BP_ERR_PREFILL_TOO_LARGE, m > max_seq gives BP_ERR_CONTEXT_OVERFLOW. */
+int bp_attn_prefill(bp_attn_ctx* ctx, void* stream, uint32_t layer, const void* q, void* out,
+                    uint32_t m);
+
+/* Largest m `bp_attn_prefill` accepts (the reference's
+ * `Model::max_prefill_tokens`, src/model.rs:502). */
+uint32_t bp_attn_max_prefill(const bp_attn_ctx* ctx);
+
+/* One decode step of one layer with HOST buffers: copies q, k_cur, v_cur
+ * (f16, pinned or pageable) to the device, runs q_norm_rope, kv_writeback at
+ * row `pos`, decode attention over pos + 1 keys, copies the f16 [n_head*128]
+ * result back and synchronises. This is the sequence of
+ * `encode_step_matvec` for one layer (src/forward.rs:612-631) as seen from a
+ * host that keeps its activations in host memory. */
+int bp_decode_step_host(bp_attn_ctx* ctx, uint32_t layer, const void* q_host, const void* k_host,
+                        const void* v_host, const void* w_q_norm_host, const void* w_k_norm_host,
+                        uint32_t pos, void* out_host);
+
+/* One prefill pass of one layer with HOST buffers (the three dispatches of
+ * `layer_step_matmul_in_pass`, src/forward.rs:1141-1172): q [m][n_head*128],
+ * k, v [m][n_kv_head*128] in, out [m][n_head*128] back, synchronised. */
+int bp_prefill_layer_host(bp_attn_ctx* ctx, uint32_t layer, const void* q_host, const void* k_host,
+                          const void* v_host, const void* w_q_norm_host, const void* w_k_norm_host,
+                          uint32_t m, void* out_host);
+
+/* Cache section copies, the per-layer copies of `kv_snapshot::capture` /
+ * `apply` (src/kv_snapshot.rs:204-372). kind: 0 = K, 1 = V; sect: 0 = d
+ * (FP32 scales, pos * kv_dim/32 * 4 bytes), 1 = qs (int8, pos * kv_dim
+ * bytes); rows [0, pos). `host` is host memory. Synchronous. */
+int bp_kv_export(bp_attn_ctx* ctx, uint32_t kind, uint32_t layer, uint32_t sect, uint32_t pos,
+                 void* host);
+int bp_kv_import(bp_attn_ctx* ctx, uint32_t kind, uint32_t layer, uint32_t sect, uint32_t pos,
+                 const void* host);
+
+/* `KvSnapshot` blob ("BONSAIKV" v1): 32-byte header + payload
+ * (src/kv_snapshot.rs:8-17, 30-32, 69-80, 150-169). */
+uint64_t bp_snapshot_payload_bytes(uint32_t n_layer, uint32_t kv_dim, uint32_t pos);
+uint64_t bp_snapshot_payload_offset(uint32_t n_layer, uint32_t kv_dim, uint32_t pos, uint32_t kind,
+                                    uint32_t layer, uint32_t sect);
+/* Size of the whole blob (header included) for `pos` tokens of this context. */
+uint64_t bp_snapshot_size(const bp_attn_ctx* ctx, uint32_t pos);
+/* `Session::snapshot` -> `KvSnapshot::to_bytes`: writes bp_snapshot_size bytes.
+ * On a sharded context the blob is written in the GLOBAL row order: header
+ * kv_dim = n_shards * local kv_dim, and only this shard's columns of each row
+ * are touched, so n_shards calls on the same buffer assemble the full blob. */
+int bp_snapshot_capture(bp_attn_ctx* ctx, uint32_t pos, void* blob, uint64_t blob_bytes);
+/* `KvSnapshot::from_bytes` + `validate_against` + `kv_snapshot::apply`
+ * (src/kv_snapshot.rs:104-140, 184-199, 312-372). Returns the restored `pos`
+ * in *pos_out. Header errors give BP_ERR_CONFIG, pos > max_seq gives
+ * BP_ERR_CONTEXT_OVERFLOW { pos: 0, n: pos, max }. */
+int bp_snapshot_apply(bp_attn_ctx* ctx, const void* blob, uint64_t blob_bytes, uint32_t* pos_out);
+
+/* `Model::is_device_lost` / `check_device` (src/model.rs:1719-1741): BP_OK or
+ * the latched status. */
+int bp_ctx_status(const bp_attn_ctx* ctx);
+/* Host-side stand-in for `Model::__destroy_device_for_test`
+ * (src/model.rs:1743-1751): latches BP_ERR_DEVICE_LOST without touching the
+ * GPU, so every later call fails fast. */
+void bp_ctx_inject_lost(bp_attn_ctx* ctx);
+void bp_last_error_detail(const bp_attn_ctx* ctx, bp_error_detail* out);
+/* Display text of the last error, in the wording of src/error.rs:7-40. */
+const char* bp_last_error_message(const bp_attn_ctx* ctx);
+const char* bp_strerror(int status);
+
+/* Introspection for tests, benchmarks and an exchange layer built on top. */
+void* bp_kv_device_ptr(bp_attn_ctx* ctx, uint32_t kind);       /* whole kv_k / kv_v buffer */
+uint64_t bp_kv_buffer_bytes(const bp_attn_ctx* ctx);           /* size of each */
+const void* bp_rope_device_ptr(const bp_attn_ctx* ctx);        /* f16 [max_seq][64][2] */
+int bp_rope_table_copy(bp_attn_ctx* ctx, void* host_f16);      /* host copy of the same */
+/* Selects the kernel family: 0 = production kernels (default), 1 = the plain
+ * CUDA-core kernels kept as an on-device cross-check. */
+int bp_set_variant(bp_attn_ctx* ctx, uint32_t variant);
+/* Number of kernels the last compute call launched. */
+uint32_t bp_last_launch_count(const bp_attn_ctx* ctx);
+/* Number of split-KV partitions `bp_attn_decode` uses at `cur_pos`. */
+uint32_t bp_decode_num_splits(const bp_attn_ctx* ctx, uint32_t cur_pos);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BONSAI_ATTN_H */
