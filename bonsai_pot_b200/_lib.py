@@ -74,6 +74,7 @@ SIGNATURES = {
     "bp_attn_prefill": (_int, [_vp, _vp, _u32, _vp, _vp, _u32]),
     "bp_attn_max_prefill": (_u32, [_vp]),
     "bp_decode_step_host": (_int, [_vp, _u32, _vp, _vp, _vp, _vp, _vp, _u32, _vp]),
+    "bp_decode_token_host": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _vp]),
     "bp_prefill_layer_host": (_int, [_vp, _u32, _vp, _vp, _vp, _vp, _vp, _u32, _vp]),
     "bp_kv_export": (_int, [_vp, _u32, _u32, _u32, _u32, _vp]),
     "bp_kv_import": (_int, [_vp, _u32, _u32, _u32, _u32, _vp]),

@@ -115,6 +115,11 @@ class AttnContext:
         self._check(self._lib.bp_decode_step_host(self._h, layer_il, _ptr(q), _ptr(k_cur), _ptr(v_cur),
                                                   _ptr(w_q_norm), _ptr(w_k_norm), pos, _ptr(out)))
 
+    def decode_token_host(self, q, k_cur, v_cur, w_q_norm, w_k_norm, pos, out):
+        """All layers of one decode token: q/out [n_layer][q_dim], k/v [n_layer][kv_dim], host memory."""
+        self._check(self._lib.bp_decode_token_host(self._h, _ptr(q), _ptr(k_cur), _ptr(v_cur), _ptr(w_q_norm),
+                                                   _ptr(w_k_norm), pos, _ptr(out)))
+
     def prefill_layer_host(self, layer_il, q, k_cur, v_cur, w_q_norm, w_k_norm, m_tokens, out):
         self._check(self._lib.bp_prefill_layer_host(self._h, layer_il, _ptr(q), _ptr(k_cur), _ptr(v_cur),
                                                     _ptr(w_q_norm), _ptr(w_k_norm), m_tokens, _ptr(out)))

@@ -54,6 +54,9 @@ __host__ __device__ inline uint64_t bp_qs_off(const bp_attn_ctx* c, uint32_t il)
 // launches and adds the number of kernels launched to *launches.
 cudaError_t bp_launch_q_norm_rope(bp_attn_ctx* c, cudaStream_t s, __half* q, const __half* w,
                                   uint32_t pos_base, uint32_t m, uint32_t* launches);
+// Same kernel over `rows` rows that all sit at the SAME position `pos` (one row per layer of one token).
+cudaError_t bp_launch_q_norm_rope_rows(bp_attn_ctx* c, cudaStream_t s, __half* q, const __half* w,
+                                       uint32_t pos, uint32_t rows, uint32_t* launches);
 cudaError_t bp_launch_kv_writeback(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, const __half* k,
                                    const __half* v, const __half* w, uint32_t pos_base, uint32_t m,
                                    uint32_t* launches);

@@ -376,6 +376,37 @@ int bp_decode_step_host(bp_attn_ctx* c, uint32_t layer, const void* q, const voi
   return layer_host(c, layer, q, k, v, wq, wk, pos, 1, false, out);
 }
 
+int bp_decode_token_host(bp_attn_ctx* c, const void* q, const void* k, const void* v, const void* wq, const void* wk,
+                         uint32_t pos, void* out) {
+  if (int s = enter(c)) return s;
+  if (!q || !k || !v || !wq || !wk || !out) return fail(c, BP_ERR_NULL, "null pointer argument");
+  if (static_cast<uint64_t>(pos) + 1 > c->cfg.max_seq) return fail_overflow(c, pos, 1, c->cfg.max_seq);
+  if (int s = bind_device(c)) return s;
+  const uint32_t nl = c->cfg.n_layer;
+  if (int s = ensure_stage(c, nl)) return s;  // one staging row per layer
+  cudaStream_t st = c->host_stream;
+  const size_t qb = static_cast<size_t>(nl) * c->q_dim * 2, kb = static_cast<size_t>(nl) * c->kv_dim * 2;
+  BP_CUDA(c, cudaMemcpyAsync(c->stage_q, q, qb, cudaMemcpyHostToDevice, st));
+  BP_CUDA(c, cudaMemcpyAsync(c->stage_k, k, kb, cudaMemcpyHostToDevice, st));
+  BP_CUDA(c, cudaMemcpyAsync(c->stage_v, v, kb, cudaMemcpyHostToDevice, st));
+  BP_CUDA(c, cudaMemcpyAsync(c->stage_wq, wq, BP_HEAD_DIM * 2, cudaMemcpyHostToDevice, st));
+  BP_CUDA(c, cudaMemcpyAsync(c->stage_wk, wk, BP_HEAD_DIM * 2, cudaMemcpyHostToDevice, st));
+  uint32_t launches = 0;
+  // Q norm + RoPE of all layers' queries is one launch: every layer's row sits at the same position.
+  BP_CUDA(c, bp_launch_q_norm_rope_rows(c, st, c->stage_q, c->stage_wq, pos, nl, &launches));
+  for (uint32_t il = 0; il < nl; il++) {
+    BP_CUDA(c, bp_launch_kv_writeback(c, st, il, c->stage_k + static_cast<size_t>(il) * c->kv_dim,
+                                      c->stage_v + static_cast<size_t>(il) * c->kv_dim, c->stage_wk, pos, 1, &launches));
+    BP_CUDA(c, bp_launch_decode(c, st, il, c->stage_q + static_cast<size_t>(il) * c->q_dim,
+                                c->stage_out + static_cast<size_t>(il) * c->q_dim, pos + 1, &launches));
+  }
+  BP_CUDA(c, cudaMemcpyAsync(out, c->stage_out, qb, cudaMemcpyDeviceToHost, st));
+  BP_CUDA(c, cudaStreamSynchronize(st));
+  c->last_launches = launches;
+  if (*c->err_host) return fail(c, BP_ERR_TIMEOUT, "a bounded device-side wait gave up");
+  return BP_OK;
+}
+
 int bp_prefill_layer_host(bp_attn_ctx* c, uint32_t layer, const void* q, const void* k, const void* v,
                           const void* wq, const void* wk, uint32_t m, void* out) {
   return layer_host(c, layer, q, k, v, wq, wk, 0, m, true, out);

@@ -127,11 +127,11 @@ kv_writeback_kernel(const __half* __restrict__ k_cur, const __half* __restrict__
 __global__ void __launch_bounds__(256)
 q_norm_rope_kernel(__half* __restrict__ q, const __half* __restrict__ w_q_norm,
                    const __half* __restrict__ rope, uint32_t n_head, uint32_t pos_base, uint32_t m,
-                   float eps) {
+                   uint32_t pos_step, float eps) {
   const int lane = threadIdx.x & 31;
   const uint32_t unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (unit >= m * n_head) return;
-  const uint32_t tok = unit / n_head;
+  const uint32_t tok = (unit / n_head) * pos_step;  // pos_step 0: every row is at pos_base
   __half* row = q + static_cast<size_t>(unit) * BP_HEAD_DIM;  // [m][n_head][128] is dense
   const Rot4 qp =
       norm_rope(row, w_q_norm, rope + static_cast<size_t>(pos_base + tok) * BP_HEAD_DIM, eps, lane);
@@ -148,7 +148,16 @@ q_norm_rope_kernel(__half* __restrict__ q, const __half* __restrict__ w_q_norm,
 cudaError_t bp_launch_q_norm_rope(bp_attn_ctx* c, cudaStream_t s, __half* q, const __half* w,
                                   uint32_t pos_base, uint32_t m, uint32_t* launches) {
   const uint32_t units = m * c->cfg.n_head;
-  q_norm_rope_kernel<<<(units + 7) / 8, 256, 0, s>>>(q, w, c->rope, c->cfg.n_head, pos_base, m,
+  q_norm_rope_kernel<<<(units + 7) / 8, 256, 0, s>>>(q, w, c->rope, c->cfg.n_head, pos_base, m, 1u,
+                                                     c->cfg.rms_eps);
+  *launches += 1;
+  return cudaGetLastError();
+}
+
+cudaError_t bp_launch_q_norm_rope_rows(bp_attn_ctx* c, cudaStream_t s, __half* q, const __half* w,
+                                       uint32_t pos, uint32_t rows, uint32_t* launches) {
+  const uint32_t units = rows * c->cfg.n_head;
+  q_norm_rope_kernel<<<(units + 7) / 8, 256, 0, s>>>(q, w, c->rope, c->cfg.n_head, pos, rows, 0u,
                                                      c->cfg.rms_eps);
   *launches += 1;
   return cudaGetLastError();

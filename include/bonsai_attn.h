@@ -125,6 +125,15 @@ int bp_decode_step_host(bp_attn_ctx* ctx, uint32_t layer, const void* q_host, co
                         const void* v_host, const void* w_q_norm_host, const void* w_k_norm_host,
                         uint32_t pos, void* out_host);
 
+/* One decode token through ALL layers with HOST buffers: the attention part of
+ * one `Session::step` (src/forward.rs:578-672), which the reference submits as
+ * a single command buffer per token. q_host, out_host: f16 [n_layer][n_head*128];
+ * k_host, v_host: f16 [n_layer][n_kv_head*128]. One host-to-device copy per
+ * input, the kernels of every layer in order, one copy back, one synchronise. */
+int bp_decode_token_host(bp_attn_ctx* ctx, const void* q_host, const void* k_host, const void* v_host,
+                         const void* w_q_norm_host, const void* w_k_norm_host, uint32_t pos,
+                         void* out_host);
+
 /* One prefill pass of one layer with HOST buffers (the three dispatches of
  * `layer_step_matmul_in_pass`, src/forward.rs:1141-1172): q [m][n_head*128],
  * k, v [m][n_kv_head*128] in, out [m][n_head*128] back, synchronised. */

@@ -409,3 +409,23 @@ def test_host_entry_points_equal_the_device_path():
         ctx.prefill_layer_host(0, c["q"], c["k"], c["v"], c["w"], c["w"], m, out_p)
         exact = O.attn_exact(sh, c["qn"], c["kv_k"], c["kv_v"], 0, m, 0)
         assert within_tolerance(out_p, exact)[0]
+
+
+def test_token_host_entry_point_equals_per_layer_calls():
+    sh = O.Shape(n_layer=3, max_seq=512)
+    rng_cases = [build_decode_case(sh, seed=10, cfg_id=1, layer=il, n_past=300) for il in range(3)]
+    q = np.concatenate([c["q"] for c in rng_cases]); k = np.concatenate([c["k_new"] for c in rng_cases])
+    v = np.concatenate([c["v_new"] for c in rng_cases])
+    w = synth.ones_weight()
+    with make_ctx(sh) as ctx:
+        for il, c in enumerate(rng_cases):
+            load_cache(ctx, sh, c["kv_k"], c["kv_v"], il, 300)
+        out = np.zeros((3, sh.q_dim), dtype=np.float16)
+        ctx.decode_token_host(q, k, v, w, w, 300, out)
+        for il, c in enumerate(rng_cases):
+            exact = O.attn_exact(sh, c["qn"], c["kv_k"], c["kv_v"], il, 1, 300)[0]
+            assert within_tolerance(out[il], exact)[0]
+            (kd, kq), _ = read_cache(ctx, sh, il, 301)
+            assert np.array_equal(kq[300], sh.qs_section(c["kv_k"], il)[300])
+        with pytest.raises(bp.ContextOverflow):
+            ctx.decode_token_host(q, k, v, w, w, 512, out)
