@@ -112,24 +112,57 @@ attn_scalar_kernel(const __half* __restrict__ q, const float* __restrict__ k_d,
 }
 
 // Log-sum-exp combine over splits (attention_merge.wgsl:70-130). One block per
-// query head; thread d owns output dim d. m is stored in log2 units.
-__global__ void __launch_bounds__(128)
+// query head, 4 groups of 128 threads: group k takes splits k, k+4, ... so that
+// many independent loads are in flight; thread d of a group owns output dim d.
+// m is stored in log2 units. n_splits <= COMBINE_MAX_SPLITS.
+constexpr uint32_t COMBINE_MAX_SPLITS = 256;
+constexpr uint32_t COMBINE_GROUPS = 4;
+
+__global__ void __launch_bounds__(128 * COMBINE_GROUPS)
 attn_combine_kernel(const float* __restrict__ partials, __half* __restrict__ out, uint32_t n_head,
                     uint32_t n_splits) {
-  const uint32_t h = blockIdx.x, d = threadIdx.x;
+  __shared__ float w_sh[COMBINE_MAX_SPLITS];
+  __shared__ float red[16];
+  __shared__ float o_sh[COMBINE_GROUPS][BP_HEAD_DIM];
+  const uint32_t h = blockIdx.x, tid = threadIdx.x, d = tid & 127, grp = tid >> 7;
+  const int lane = tid & 31, warp = tid >> 5;
   const float* base = partials + static_cast<size_t>(h) * BP_PART_STRIDE;
   const size_t stride = static_cast<size_t>(n_head) * BP_PART_STRIDE;
-  float m_all = NEG_BIG;
-  for (uint32_t s = 0; s < n_splits; s++) m_all = fmaxf(m_all, base[s * stride + 128]);
-  float o = 0.f, l = 0.f;
-#pragma unroll 4
-  for (uint32_t s = 0; s < n_splits; s++) {
-    const float* p = base + s * stride;
-    const float e = ex2(p[128] - m_all);
-    o += p[d] * e;
-    l += p[129] * e;
+
+  float m_s = NEG_BIG, l_s = 0.f;
+  if (tid < n_splits) {
+    m_s = base[tid * stride + 128];
+    l_s = base[tid * stride + 129];
   }
-  out[static_cast<size_t>(h) * BP_HEAD_DIM + d] = __float2half_rn(o * (1.0f / l));
+  float m_all = m_s;
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) m_all = fmaxf(m_all, __shfl_xor_sync(FULL, m_all, off));
+  if (lane == 0) red[warp] = m_all;
+  __syncthreads();
+  m_all = red[0];
+#pragma unroll
+  for (int w = 1; w < 16; w++) m_all = fmaxf(m_all, red[w]);
+  __syncthreads();
+  const float wgt = ex2(m_s - m_all);
+  if (tid < n_splits) w_sh[tid] = wgt;
+  float l = l_s * wgt;
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) l += __shfl_xor_sync(FULL, l, off);
+  if (lane == 0) red[warp] = l;
+  __syncthreads();
+  l = 0.f;
+#pragma unroll
+  for (int w = 0; w < 16; w++) l += red[w];
+
+  float o = 0.f;
+#pragma unroll 8
+  for (uint32_t s = grp; s < n_splits; s += COMBINE_GROUPS) o = fmaf(base[s * stride + d], w_sh[s], o);
+  o_sh[grp][d] = o;
+  __syncthreads();
+  if (grp == 0) {
+    o = (o_sh[0][d] + o_sh[1][d]) + (o_sh[2][d] + o_sh[3][d]);
+    out[static_cast<size_t>(h) * BP_HEAD_DIM + d] = __float2half_rn(o * (1.0f / l));
+  }
 }
 
 // ------------------------------------------------------------------------
@@ -454,12 +487,15 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_const
 // number of stages, chosen so that the grid is at most one CTA per SM.
 static uint32_t stage_tokens(const bp_attn_ctx* c) { return SUBTILE * (NW / c->cfg.n_kv_head); }
 
-uint32_t bp_decode_max_splits(const bp_attn_ctx* c) { return static_cast<uint32_t>(c->sm_count); }
+uint32_t bp_decode_max_splits(const bp_attn_ctx* c) {
+  const uint32_t sms = static_cast<uint32_t>(c->sm_count);
+  return sms < COMBINE_MAX_SPLITS ? sms : COMBINE_MAX_SPLITS;
+}
 
 static uint32_t stages_per_split(const bp_attn_ctx* c, uint32_t cur_pos) {
   const uint32_t st = stage_tokens(c);
   const uint32_t n_st = (cur_pos + st - 1) / st;
-  const uint32_t ctas = static_cast<uint32_t>(c->sm_count);
+  const uint32_t ctas = bp_decode_max_splits(c);
   return (n_st + ctas - 1) / ctas;
 }
 
@@ -497,7 +533,7 @@ cudaError_t bp_launch_scalar_attention(bp_attn_ctx* c, cudaStream_t s, uint32_t 
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   if (n_splits > 1) {
-    attn_combine_kernel<<<c->cfg.n_head, 128, 0, s>>>(c->partials, out, c->cfg.n_head, n_splits);
+    attn_combine_kernel<<<c->cfg.n_head, 128 * COMBINE_GROUPS, 0, s>>>(c->partials, out, c->cfg.n_head, n_splits);
     *launches += 1;
     e = cudaGetLastError();
   }
@@ -545,7 +581,7 @@ cudaError_t bp_launch_decode(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, con
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   if (n_splits > 1) {
-    attn_combine_kernel<<<c->cfg.n_head, 128, 0, s>>>(c->partials, out, c->cfg.n_head, n_splits);
+    attn_combine_kernel<<<c->cfg.n_head, 128 * COMBINE_GROUPS, 0, s>>>(c->partials, out, c->cfg.n_head, n_splits);
     *launches += 1;
     e = cudaGetLastError();
   }

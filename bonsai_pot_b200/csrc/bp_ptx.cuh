@@ -68,7 +68,7 @@ __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
 // D = A(16x16, row) * B(16x8, col) + C, f16 inputs, f32 accumulate.
 __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                           uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
       "{%0,%1,%2,%3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
@@ -91,22 +91,17 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
   return r;
 }
+// Shared-memory loads by 32-bit shared-window address. They are ordinary C++
+// loads (the compiler may schedule them freely between barriers and knows they
+// read memory), not opaque asm.
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
-  uint32_t v;
-  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
-  return v;
+  return *static_cast<const uint32_t*>(__cvta_shared_to_generic(addr));
 }
 __device__ __forceinline__ uint2 lds64(uint32_t addr) {
-  uint2 v;
-  asm volatile("ld.shared.v2.b32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
-  return v;
+  return *static_cast<const uint2*>(__cvta_shared_to_generic(addr));
 }
 __device__ __forceinline__ float4 lds128f(uint32_t addr) {
-  float4 v;
-  asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
-               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-               : "r"(addr));
-  return v;
+  return *static_cast<const float4*>(__cvta_shared_to_generic(addr));
 }
 // Byte offset -> position inside a 1024-byte-aligned tile written by TMA with
 // the 128-byte swizzle: the 16-byte chunk index is xor-ed with (row mod 8).
