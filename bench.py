@@ -442,6 +442,7 @@ def extras(torch, bp, stream, hbm_peak, tflops_peak, peak_kind):
 
 
 def main():
+    global N_LAYER
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
@@ -452,7 +453,6 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the ctx-32768 and prefill side measurements")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
-    global N_LAYER
     N_LAYER = args.layers
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
