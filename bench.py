@@ -250,6 +250,10 @@ def run_ours(args):
 
     ctx = bp.AttnContext(n_layer=N_LAYER, n_head=nh_l, n_kv_head=nkv_l, max_seq=ctx_len, n_shards=world, shard=rank,
                          device=local_rank)
+    if args.decode_warps:
+        ctx.set_option("decode_warps", args.decode_warps)
+    if args.decode_hpc:
+        ctx.set_option("decode_heads_per_cta", args.decode_hpc)
     gen = torch.Generator(device="cuda")
     gen.manual_seed(1234 + rank)
     fill_cache(ctx, torch, N_LAYER, kv_dim_l, ctx_len - 1, gen)
@@ -371,7 +375,7 @@ def run_ours(args):
                        "call": "bp_decode_token_host (pinned host activations in, f16 outputs back, one sync per token)"}
         # ---- the other configurations, briefly ----
         if not args.no_extras:
-            line["also"] = extras(torch, bp, stream, hbm_peak, tflops_peak, peak_kind)
+            line["also"] = extras(torch, bp, stream, hbm_peak, tflops_peak, peak_kind, args)
         # ---- CPU baseline on this box's cores (bounded sample) ----
         if not args.no_cpu:
             try:
@@ -388,7 +392,7 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-def extras(torch, bp, stream, hbm_peak, tflops_peak, peak_kind):
+def extras(torch, bp, stream, hbm_peak, tflops_peak, peak_kind, args):
     """Long-context decode (ctx 32768) and the prefill pass (pp 512 / 2048) on one GPU."""
     out = {}
     gen = torch.Generator(device="cuda")
@@ -397,6 +401,10 @@ def extras(torch, bp, stream, hbm_peak, tflops_peak, peak_kind):
     # decode at 32K: 4 layers allocated and swept (302 MB > L2)
     nl, ctx_len = 4, 32768
     with bp.AttnContext(n_layer=nl, max_seq=ctx_len) as c:
+        if args.decode_warps:
+            c.set_option("decode_warps", args.decode_warps)
+        if args.decode_hpc:
+            c.set_option("decode_heads_per_cta", args.decode_hpc)
         fill_cache(c, torch, nl, KV_DIM, ctx_len, gen)
         q = torch.randn(nl, Q_DIM, generator=gen, device="cuda").half()
         o = torch.zeros(nl, Q_DIM, dtype=torch.float16, device="cuda")
@@ -450,6 +458,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ctx", type=int, default=4096, help="context length of the decode stack")
     ap.add_argument("--layers", type=int, default=N_LAYER, help="layers of the stack (smaller only for profiler captures)")
+    ap.add_argument("--decode-warps", type=int, default=0, help="override the decode kernel's compute warps per CTA")
+    ap.add_argument("--decode-hpc", type=int, default=0, help="override the decode kernel's KV heads per CTA")
     ap.add_argument("--no-extras", action="store_true", help="skip the ctx-32768 and prefill side measurements")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()

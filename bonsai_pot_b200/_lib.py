@@ -93,6 +93,7 @@ SIGNATURES = {
     "bp_rope_device_ptr": (_vp, [_vp]),
     "bp_rope_table_copy": (_int, [_vp, _vp]),
     "bp_set_variant": (_int, [_vp, _u32]),
+    "bp_set_option": (_int, [_vp, C.c_char_p, _u32]),
     "bp_last_launch_count": (_u32, [_vp]),
     "bp_decode_num_splits": (_u32, [_vp, _u32]),
 }

@@ -158,6 +158,10 @@ class AttnContext:
     def set_variant(self, variant):
         self._check(self._lib.bp_set_variant(self._h, variant))
 
+    def set_option(self, name, value):
+        """Decode tuning knobs: "decode_warps" (8/16), "decode_heads_per_cta"."""
+        self._check(self._lib.bp_set_option(self._h, name.encode(), value))
+
     def last_launch_count(self):
         return self._lib.bp_last_launch_count(self._h)
 

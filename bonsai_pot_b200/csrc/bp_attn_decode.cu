@@ -168,13 +168,21 @@ attn_combine_kernel(const float* __restrict__ partials, __half* __restrict__ out
 // ------------------------------------------------------------------------
 // Production kernel.
 // ------------------------------------------------------------------------
-constexpr int NW = 8;                               // compute warps per CTA
 constexpr int MAX_STAGES = 5;
-constexpr uint32_t SUBTILE = 16;                    // tokens per warp per stage
-constexpr uint32_t STAGE_QS = NW * SUBTILE * 128;   // bytes of K (or V) quants per stage
-constexpr uint32_t STAGE_D = NW * SUBTILE * 16;     // bytes of K (or V) scales per stage
-constexpr uint32_t STAGE_BYTES = 2 * STAGE_QS + 2 * STAGE_D;
-constexpr uint32_t MERGE_BYTES = NW * 8 * BP_HEAD_DIM * 4 + NW * 8 * 8;
+constexpr uint32_t SUBTILE = 16;  // tokens per warp per stage
+constexpr uint32_t SMEM_LIMIT = 227 * 1024;
+
+template <int NW_>
+struct Geo {
+  static constexpr uint32_t STAGE_QS = NW_ * SUBTILE * 128;  // bytes of K (or V) quants per stage
+  static constexpr uint32_t STAGE_D = NW_ * SUBTILE * 16;    // bytes of K (or V) scales per stage
+  static constexpr uint32_t STAGE_BYTES = 2 * STAGE_QS + 2 * STAGE_D;
+  static constexpr uint32_t MERGE_BYTES = NW_ * 8 * BP_HEAD_DIM * 4 + NW_ * 8 * 8;
+  static constexpr uint32_t max_stages() {
+    uint32_t n = (SMEM_LIMIT - MERGE_BYTES - 1024) / STAGE_BYTES;
+    return n > MAX_STAGES ? MAX_STAGES : n;
+  }
+};
 
 struct DecodeParams {
   const __half* q;
@@ -185,16 +193,134 @@ struct DecodeParams {
   uint32_t cur_pos;
   uint32_t tps;        // tokens per split, a multiple of the stage size
   uint32_t n_stages;
-  uint32_t n_head, nkv, qpg;
+  uint32_t n_head;     // query heads of the context
+  uint32_t hpc;        // KV heads per CTA (blockIdx.y selects the group of heads)
+  uint32_t qpg;
   uint32_t d_swz;      // 1 when the scale tiles are 128 B wide and swizzled
   float sm_scale_log2; // softmax scale * log2(e)
 };
 
-template <bool DENORM>
-__global__ void __launch_bounds__((NW + 1) * 32, 1)
+// Running state of one compute warp: softmax statistics of head `lane / 4`,
+// and O^T accumulators (dims on rows, heads 2*quad, 2*quad+1 on columns).
+struct WarpAcc {
+  float m_run, l_run;
+  float oacc[4][2][4];
+  float pacc[4][4];  // DENORM only: sum of P' per block, from an all-ones A operand
+};
+
+// One 16-token sub-tile of one KV head. ktile/vtile: 16 x 128 B swizzled int8
+// tiles; kd/vd: this warp's rows of the scale tiles. koff/voff/soff are
+// per-lane byte offsets computed once per kernel (block b adds an xor of b<<5).
+template <bool DENORM, bool TAIL>
+__device__ __forceinline__ void process_tile(WarpAcc& w, uint32_t ktile, uint32_t vtile, uint32_t kd, uint32_t vd,
+                                             const uint32_t (&koff)[2], const uint32_t (&voff)[4],
+                                             const uint32_t (&soff)[4], const uint32_t (&qa0)[4][2],
+                                             const uint32_t (&qa2)[4][2], const float (&qcorr)[4], float s_mul,
+                                             uint32_t valid, int qd) {
+  // ---- S = Q K^T, one accumulator per (token tile, Q8_0 block) ----
+  float acc[2][4][4];
+#pragma unroll
+  for (int t = 0; t < 2; t++) {
+#pragma unroll
+    for (int b = 0; b < 4; b++) {
+#pragma unroll
+      for (int c = 0; c < 4; c++) acc[t][b][c] = 0.f;
+      const uint2 kw = lds64(ktile + (koff[t] ^ (b << 5)));
+      uint32_t b0, b1;
+      k_pair<DENORM>(kw.x, b0, b1);
+      mma_16816(acc[t][b], qa0[b][0], 0u, qa2[b][0], 0u, b0, b1);
+      k_pair<DENORM>(kw.y, b0, b1);
+      mma_16816(acc[t][b], qa0[b][1], 0u, qa2[b][1], 0u, b0, b1);
+    }
+  }
+  // ---- scores of this lane: head lane/4, token slots j = 0..3 ----
+  float sc[4];
+  float4 sv[4];
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    const float4 sk = lds128f(kd + soff[j]);
+    sv[j] = lds128f(vd + soff[j]);
+    const int t = j & 1, c = j >> 1;
+    float sj = sk.x * (acc[t][0][c] - qcorr[0]);
+    sj = fmaf(sk.y, acc[t][1][c] - qcorr[1], sj);
+    sj = fmaf(sk.z, acc[t][2][c] - qcorr[2], sj);
+    sj = fmaf(sk.w, acc[t][3][c] - qcorr[3], sj);
+    sc[j] = sj * s_mul;
+    if (TAIL) {
+      const uint32_t rowj = 4 * qd + (j ^ (qd & 2));
+      if (rowj >= valid) {
+        sc[j] = NEG_BIG;
+        sv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+  }
+  float m_loc = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
+  m_loc = fmaxf(m_loc, __shfl_xor_sync(FULL, m_loc, 1));
+  m_loc = fmaxf(m_loc, __shfl_xor_sync(FULL, m_loc, 2));
+  const float m_new = fmaxf(w.m_run, m_loc);
+  const float corr = ex2(w.m_run - m_new);
+  const bool moved = m_new > w.m_run;
+  w.m_run = m_new;
+  float pj[4];
+#pragma unroll
+  for (int j = 0; j < 4; j++) pj[j] = ex2(sc[j] - m_new);
+  w.l_run = w.l_run * corr + ((pj[0] + pj[1]) + (pj[2] + pj[3]));
+
+  if (__any_sync(FULL, moved)) {
+    const float ca = __shfl_sync(FULL, corr, 8 * qd);
+    const float cb = __shfl_sync(FULL, corr, 8 * qd + 4);
+#pragma unroll
+    for (int b = 0; b < 4; b++) {
+#pragma unroll
+      for (int t = 0; t < 2; t++) {
+        w.oacc[b][t][0] *= ca; w.oacc[b][t][1] *= cb;
+        w.oacc[b][t][2] *= ca; w.oacc[b][t][3] *= cb;
+      }
+      if (DENORM) {
+        w.pacc[b][0] *= ca; w.pacc[b][1] *= cb;
+        w.pacc[b][2] *= ca; w.pacc[b][3] *= cb;
+      }
+    }
+  }
+
+  // ---- O^T += V^T P'^T, P' = p * (V block scale), per Q8_0 block ----
+#pragma unroll
+  for (int b = 0; b < 4; b++) {
+    const float sb0 = b == 0 ? sv[0].x : b == 1 ? sv[0].y : b == 2 ? sv[0].z : sv[0].w;
+    const float sb1 = b == 0 ? sv[1].x : b == 1 ? sv[1].y : b == 2 ? sv[1].z : sv[1].w;
+    const float sb2 = b == 0 ? sv[2].x : b == 1 ? sv[2].y : b == 2 ? sv[2].z : sv[2].w;
+    const float sb3 = b == 0 ? sv[3].x : b == 1 ? sv[3].y : b == 2 ? sv[3].z : sv[3].w;
+    __half2 h01 = __floats2half2_rn(pj[0] * sb0, pj[1] * sb1);
+    __half2 h23 = __floats2half2_rn(pj[2] * sb2, pj[3] * sb3);
+    const uint32_t pb0 = *reinterpret_cast<uint32_t*>(&h01);
+    const uint32_t pb1 = *reinterpret_cast<uint32_t*>(&h23);
+    // With an A operand of all ones (2^-24 each) the tensor core itself sums the
+    // rounded P' of the 16 tokens: the +128 of the V bytes then cancels exactly.
+    if (DENORM) mma_16816(w.pacc[b], 0x00010001u, 0x00010001u, 0x00010001u, 0x00010001u, pb0, pb1);
+
+    uint32_t e[4], o[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const uint32_t x = lds32(vtile + (voff[j] ^ (b << 5))) ^ 0x80808080u;
+      e[j] = x & 0x00ff00ffu;
+      o[j] = x & 0xff00ff00u;
+      if (!DENORM) { e[j] |= 0x64006400u; o[j] |= 0x00640064u; }
+    }
+    // dims 32b + 4r + {0 (row r), 2 (row r+8)}
+    mma_16816(w.oacc[b][0], v_fix<DENORM>(prmt(e[0], e[1], 0x5410)), v_fix<DENORM>(prmt(e[0], e[1], 0x7632)),
+              v_fix<DENORM>(prmt(e[2], e[3], 0x5410)), v_fix<DENORM>(prmt(e[2], e[3], 0x7632)), pb0, pb1);
+    // dims 32b + 4r + {1 (row r), 3 (row r+8)}
+    mma_16816(w.oacc[b][1], v_fix<DENORM>(prmt(o[0], o[1], 0x4501)), v_fix<DENORM>(prmt(o[0], o[1], 0x6723)),
+              v_fix<DENORM>(prmt(o[2], o[3], 0x4501)), v_fix<DENORM>(prmt(o[2], o[3], 0x6723)), pb0, pb1);
+  }
+}
+
+template <int NW_, bool DENORM>
+__global__ void __launch_bounds__((NW_ + 1) * 32, 1)
 decode_mma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_constant__ CUtensorMap map_kd,
                   const __grid_constant__ CUtensorMap map_vq, const __grid_constant__ CUtensorMap map_vd,
                   const DecodeParams p) {
+  using G = Geo<NW_>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[MAX_STAGES];
   __shared__ __align__(8) uint64_t empty_bar[MAX_STAGES];
@@ -202,8 +328,9 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_const
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t nkv = p.nkv, wph = NW / nkv, st_tok = SUBTILE * wph;
+  const uint32_t hpc = p.hpc, wph = NW_ / hpc, st_tok = SUBTILE * wph;
   const uint32_t ns = p.n_stages;
+  const uint32_t g0 = blockIdx.y * hpc;  // first KV head of this CTA
 
   const uint32_t split = blockIdx.x, n_splits = gridDim.x;
   const uint32_t tok_begin = split * p.tps;
@@ -213,13 +340,13 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_const
   if (threadIdx.x == 0) {
     for (uint32_t s = 0; s < ns; s++) {
       mbar_init(smem_u32(&full_bar[s]), 1);
-      mbar_init(smem_u32(&empty_bar[s]), NW);
+      mbar_init(smem_u32(&empty_bar[s]), NW_);
     }
     fence_barrier_init();
   }
   __syncthreads();
 
-  if (warp == NW) {
+  if (warp == NW_) {
     // ---------------- producer ----------------
     if (lane == 0) {
       prefetch_tensormap(&map_kq);
@@ -232,22 +359,22 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_const
         if (use > 0) ok = mbar_wait(smem_u32(&empty_bar[s]), (use - 1) & 1);
         if (!ok) break;
         const uint32_t bar = smem_u32(&full_bar[s]);
-        const uint32_t stage = smem_base + s * STAGE_BYTES;
+        const uint32_t stage = smem_base + s * G::STAGE_BYTES;
         const int row = static_cast<int>(p.row_base + tok_begin + it * st_tok);
-        mbar_arrive_expect_tx(bar, STAGE_BYTES);
-        for (uint32_t g = 0; g < nkv; g++) {
-          tma_load_3d(stage + g * (st_tok * 128), &map_kq, bar, 0, static_cast<int>(g), row);
-          tma_load_3d(stage + STAGE_QS + g * (st_tok * 128), &map_vq, bar, 0, static_cast<int>(g), row);
-        }
-        tma_load_2d(stage + 2 * STAGE_QS, &map_kd, bar, 0, row);
-        tma_load_2d(stage + 2 * STAGE_QS + STAGE_D, &map_vd, bar, 0, row);
+        mbar_arrive_expect_tx(bar, G::STAGE_BYTES);
+        tma_load_2d(stage + 2 * G::STAGE_QS, &map_kd, bar, static_cast<int>(g0 * 16), row);
+        for (uint32_t g = 0; g < hpc; g++)
+          tma_load_3d(stage + g * (st_tok * 128), &map_kq, bar, 0, static_cast<int>(g0 + g), row);
+        tma_load_2d(stage + 2 * G::STAGE_QS + G::STAGE_D, &map_vd, bar, static_cast<int>(g0 * 16), row);
+        for (uint32_t g = 0; g < hpc; g++)
+          tma_load_3d(stage + G::STAGE_QS + g * (st_tok * 128), &map_vq, bar, 0, static_cast<int>(g0 + g), row);
       }
       if (!ok) atomicExch(p.err, 1u);
     }
   } else {
     // ---------------- compute ----------------
     const int r = lane >> 2, qd = lane & 3;
-    const uint32_t g = warp % nkv, slot = warp / nkv;
+    const uint32_t g = warp % hpc, slot = warp / hpc;
     const bool row_valid = static_cast<uint32_t>(r) < p.qpg;
 
     // A fragments of Q for the 8 k-slices (block b, half s): slice (b, s) covers
@@ -256,7 +383,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_const
     uint32_t qa0[4][2], qa2[4][2];
     float qcorr[4];
     {
-      const __half* qrow = p.q + (static_cast<size_t>(g) * p.qpg + (row_valid ? r : 0)) * BP_HEAD_DIM;
+      const __half* qrow = p.q + (static_cast<size_t>(g0 + g) * p.qpg + (row_valid ? r : 0)) * BP_HEAD_DIM;
 #pragma unroll
       for (int b = 0; b < 4; b++) {
         float bsum = 0.f;
@@ -278,129 +405,50 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_const
     // In the DENORM path accumulators carry a factor 2^-24.
     const float s_mul = p.sm_scale_log2 * (DENORM ? 16777216.0f : 1.0f);
 
-    float m_run = NEG_BIG, l_run = 0.f;
-    float psum[4] = {0.f, 0.f, 0.f, 0.f};
-    float oacc[4][2][4];
+    // Per-lane byte offsets inside a sub-tile (block b is an xor with b << 5).
+    // K (B operand): lane (r, quad) reads token row 2*(r ^ (r>>2)) + t, 8 bytes of block 0.
+    // V (A operand) and scales: quad owns token rows 4*quad + (j ^ (quad & 2)).
+    uint32_t koff[2], voff[4], soff[4];
+    const uint32_t rb = 16 * hpc;
 #pragma unroll
-    for (int b = 0; b < 4; b++)
+    for (int t = 0; t < 2; t++) {
+      const uint32_t row = 2 * (r ^ (r >> 2)) + t;
+      koff[t] = row * 128 + ((((qd >> 1)) ^ (row & 7)) << 4) + ((qd & 1) << 3);
+    }
 #pragma unroll
-      for (int t = 0; t < 2; t++)
+    for (int j = 0; j < 4; j++) {
+      const uint32_t rowj = 4 * qd + (j ^ (qd & 2));
+      voff[j] = rowj * 128 + ((((r >> 2)) ^ (rowj & 7)) << 4) + ((r & 3) << 2);
+      const uint32_t o = (slot * SUBTILE + rowj) * rb + g * 16;
+      soff[j] = p.d_swz ? swz128(o) : o;
+    }
+
+    WarpAcc w;
+    w.m_run = NEG_BIG;
+    w.l_run = 0.f;
 #pragma unroll
-        for (int c = 0; c < 4; c++) oacc[b][t][c] = 0.f;
+    for (int b = 0; b < 4; b++) {
+#pragma unroll
+      for (int c = 0; c < 4; c++) { w.oacc[b][0][c] = 0.f; w.oacc[b][1][c] = 0.f; w.pacc[b][c] = 0.f; }
+    }
 
     bool ok = true;
     for (uint32_t it = 0; it < n_iter; it++) {
       const uint32_t s = it % ns, use = it / ns;
       ok = mbar_wait(smem_u32(&full_bar[s]), use & 1);
       if (!ok) break;
-      const uint32_t stage = smem_base + s * STAGE_BYTES;
+      const uint32_t stage = smem_base + s * G::STAGE_BYTES;
       const uint32_t tile_tok0 = tok_begin + it * st_tok + slot * SUBTILE;
       if (tile_tok0 < tok_end) {
         const uint32_t ktile = stage + g * (st_tok * 128) + slot * (SUBTILE * 128);
-        const uint32_t vtile = ktile + STAGE_QS;
-        const uint32_t kd_tile = stage + 2 * STAGE_QS;
-        const uint32_t vd_tile = kd_tile + STAGE_D;
-        const uint32_t rb = 16 * nkv;
-
-        // ---- S = Q K^T, one accumulator per (token tile, Q8_0 block) ----
-        float acc[2][4][4];
-#pragma unroll
-        for (int t = 0; t < 2; t++) {
-          const uint32_t row = 2 * (r ^ (r >> 2)) + t;
-#pragma unroll
-          for (int b = 0; b < 4; b++) {
-#pragma unroll
-            for (int c = 0; c < 4; c++) acc[t][b][c] = 0.f;
-            const uint32_t off = row * 128 + (((2 * b + (qd >> 1)) ^ (row & 7)) << 4) + ((qd & 1) << 3);
-            const uint2 w = lds64(ktile + off);
-            uint32_t b0, b1;
-            k_pair<DENORM>(w.x, b0, b1);
-            mma_16816(acc[t][b], qa0[b][0], 0u, qa2[b][0], 0u, b0, b1);
-            k_pair<DENORM>(w.y, b0, b1);
-            mma_16816(acc[t][b], qa0[b][1], 0u, qa2[b][1], 0u, b0, b1);
-          }
-        }
-
-        // ---- scores of this lane: head r, tokens 4*quad + (j ^ (quad & 2)) ----
-        float sc[4];
-        float4 sv[4];
-        const bool tail = tile_tok0 + SUBTILE > tok_end;
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-          const uint32_t rowj = 4 * qd + (j ^ (qd & 2));
-          uint32_t o = (slot * SUBTILE + rowj) * rb + g * 16;
-          if (p.d_swz) o = swz128(o);
-          const float4 sk = lds128f(kd_tile + o);
-          sv[j] = lds128f(vd_tile + o);
-          const int t = j & 1, c = j >> 1;
-          float sj = sk.x * (acc[t][0][c] - qcorr[0]);
-          sj = fmaf(sk.y, acc[t][1][c] - qcorr[1], sj);
-          sj = fmaf(sk.z, acc[t][2][c] - qcorr[2], sj);
-          sj = fmaf(sk.w, acc[t][3][c] - qcorr[3], sj);
-          sc[j] = sj * s_mul;
-          if (tail && tile_tok0 + rowj >= tok_end) {
-            sc[j] = NEG_BIG;
-            sv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-          }
-        }
-        float m_loc = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
-        m_loc = fmaxf(m_loc, __shfl_xor_sync(FULL, m_loc, 1));
-        m_loc = fmaxf(m_loc, __shfl_xor_sync(FULL, m_loc, 2));
-        const float m_new = fmaxf(m_run, m_loc);
-        const float corr = ex2(m_run - m_new);
-        const bool moved = m_new > m_run;
-        m_run = m_new;
-        float pj[4];
-#pragma unroll
-        for (int j = 0; j < 4; j++) pj[j] = ex2(sc[j] - m_new);
-        l_run = l_run * corr + ((pj[0] + pj[1]) + (pj[2] + pj[3]));
-
-        if (__any_sync(FULL, moved)) {
-          const float ca = __shfl_sync(FULL, corr, 8 * qd);
-          const float cb = __shfl_sync(FULL, corr, 8 * qd + 4);
-#pragma unroll
-          for (int b = 0; b < 4; b++) {
-            psum[b] *= corr;
-#pragma unroll
-            for (int t = 0; t < 2; t++) {
-              oacc[b][t][0] *= ca; oacc[b][t][1] *= cb;
-              oacc[b][t][2] *= ca; oacc[b][t][3] *= cb;
-            }
-          }
-        }
-
-        // ---- O^T += V^T P'^T, P' = p * (V block scale), per Q8_0 block ----
-#pragma unroll
-        for (int b = 0; b < 4; b++) {
-          const float sb0 = b == 0 ? sv[0].x : b == 1 ? sv[0].y : b == 2 ? sv[0].z : sv[0].w;
-          const float sb1 = b == 0 ? sv[1].x : b == 1 ? sv[1].y : b == 2 ? sv[1].z : sv[1].w;
-          const float sb2 = b == 0 ? sv[2].x : b == 1 ? sv[2].y : b == 2 ? sv[2].z : sv[2].w;
-          const float sb3 = b == 0 ? sv[3].x : b == 1 ? sv[3].y : b == 2 ? sv[3].z : sv[3].w;
-          const float p0 = pj[0] * sb0, p1 = pj[1] * sb1, p2 = pj[2] * sb2, p3 = pj[3] * sb3;
-          __half2 h01 = __floats2half2_rn(p0, p1), h23 = __floats2half2_rn(p2, p3);
-          if (DENORM) {  // sum what the MMA will actually see, so the +128 offset cancels exactly
-            const float2 r01 = __half22float2(h01), r23 = __half22float2(h23);
-            psum[b] += (r01.x + r01.y) + (r23.x + r23.y);
-          }
-          const uint32_t pb0 = *reinterpret_cast<uint32_t*>(&h01);
-          const uint32_t pb1 = *reinterpret_cast<uint32_t*>(&h23);
-
-          uint32_t e[4], o[4];
-#pragma unroll
-          for (int j = 0; j < 4; j++) {
-            const uint32_t rowj = 4 * qd + (j ^ (qd & 2));
-            const uint32_t off = rowj * 128 + (((2 * b + (r >> 2)) ^ (rowj & 7)) << 4) + ((r & 3) << 2);
-            const uint32_t x = lds32(vtile + off) ^ 0x80808080u;
-            e[j] = x & 0x00ff00ffu;
-            o[j] = x & 0xff00ff00u;
-            if (!DENORM) { e[j] |= 0x64006400u; o[j] |= 0x00640064u; }
-          }
-          // dims 32b + 4r + {0 (row r), 2 (row r+8)}
-          mma_16816(oacc[b][0], v_fix<DENORM>(prmt(e[0], e[1], 0x5410)), v_fix<DENORM>(prmt(e[0], e[1], 0x7632)),
-                    v_fix<DENORM>(prmt(e[2], e[3], 0x5410)), v_fix<DENORM>(prmt(e[2], e[3], 0x7632)), pb0, pb1);
-          // dims 32b + 4r + {1 (row r), 3 (row r+8)}
-          mma_16816(oacc[b][1], v_fix<DENORM>(prmt(o[0], o[1], 0x4501)), v_fix<DENORM>(prmt(o[0], o[1], 0x6723)),
-                    v_fix<DENORM>(prmt(o[2], o[3], 0x4501)), v_fix<DENORM>(prmt(o[2], o[3], 0x6723)), pb0, pb1);
+        const uint32_t vtile = ktile + G::STAGE_QS;
+        const uint32_t kd_tile = stage + 2 * G::STAGE_QS;
+        const uint32_t vd_tile = kd_tile + G::STAGE_D;
+        if (tile_tok0 + SUBTILE <= tok_end) {
+          process_tile<DENORM, false>(w, ktile, vtile, kd_tile, vd_tile, koff, voff, soff, qa0, qa2, qcorr, s_mul, 16u, qd);
+        } else {
+          process_tile<DENORM, true>(w, ktile, vtile, kd_tile, vd_tile, koff, voff, soff, qa0, qa2, qcorr, s_mul,
+                                     tok_end - tile_tok0, qd);
         }
       }
       __syncwarp();
@@ -409,37 +457,31 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_const
     if (!ok && lane == 0) atomicExch(p.err, 1u);
 
     // ---- warp result -> merge buffer (placed after the stage ring) ----
+    float l_run = w.l_run;
     l_run += __shfl_xor_sync(FULL, l_run, 1);
     l_run += __shfl_xor_sync(FULL, l_run, 2);
-    float pa[4], pb[4];
-#pragma unroll
-    for (int b = 0; b < 4; b++) {
-      float ps = psum[b];
-      ps += __shfl_xor_sync(FULL, ps, 1);
-      ps += __shfl_xor_sync(FULL, ps, 2);
-      pa[b] = __shfl_sync(FULL, ps, 8 * qd) * 128.0f;
-      pb[b] = __shfl_sync(FULL, ps, 8 * qd + 4) * 128.0f;
-    }
-    float* mo = reinterpret_cast<float*>(smem_gen + ns * STAGE_BYTES);
-    float* mm = mo + NW * 8 * BP_HEAD_DIM;
-    float* ml = mm + NW * 8;
+    float* mo = reinterpret_cast<float*>(smem_gen + ns * G::STAGE_BYTES);
+    float* mm = mo + NW_ * 8 * BP_HEAD_DIM;
+    float* ml = mm + NW_ * 8;
     const float os = DENORM ? 16777216.0f : 1.0f;
 #pragma unroll
     for (int b = 0; b < 4; b++) {
       const int dim = 32 * b + 4 * r;
+      const float pa = DENORM ? w.pacc[b][0] * 128.0f : 0.f;  // head 2*quad
+      const float pb = DENORM ? w.pacc[b][1] * 128.0f : 0.f;  // head 2*quad + 1
       if (static_cast<uint32_t>(2 * qd) < p.qpg) {
-        float4 v = make_float4(oacc[b][0][0] * os - pa[b], oacc[b][1][0] * os - pa[b],
-                               oacc[b][0][2] * os - pa[b], oacc[b][1][2] * os - pa[b]);
+        float4 v = make_float4((w.oacc[b][0][0] - pa) * os, (w.oacc[b][1][0] - pa) * os,
+                               (w.oacc[b][0][2] - pa) * os, (w.oacc[b][1][2] - pa) * os);
         *reinterpret_cast<float4*>(mo + (warp * 8 + 2 * qd) * BP_HEAD_DIM + dim) = v;
       }
       if (static_cast<uint32_t>(2 * qd + 1) < p.qpg) {
-        float4 v = make_float4(oacc[b][0][1] * os - pb[b], oacc[b][1][1] * os - pb[b],
-                               oacc[b][0][3] * os - pb[b], oacc[b][1][3] * os - pb[b]);
+        float4 v = make_float4((w.oacc[b][0][1] - pb) * os, (w.oacc[b][1][1] - pb) * os,
+                               (w.oacc[b][0][3] - pb) * os, (w.oacc[b][1][3] - pb) * os);
         *reinterpret_cast<float4*>(mo + (warp * 8 + 2 * qd + 1) * BP_HEAD_DIM + dim) = v;
       }
     }
     if (qd == 0 && row_valid) {
-      mm[warp * 8 + r] = m_run;
+      mm[warp * 8 + r] = w.m_run;
       ml[warp * 8 + r] = l_run;
     }
   }
@@ -447,24 +489,25 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_const
 
   // ---- merge the warps of each KV head, write the split's partial ----
   {
-    const float* mo = reinterpret_cast<const float*>(smem_gen + ns * STAGE_BYTES);
-    const float* mm = mo + NW * 8 * BP_HEAD_DIM;
-    const float* ml = mm + NW * 8;
-    const uint32_t total = p.n_head * BP_HEAD_DIM;
+    const float* mo = reinterpret_cast<const float*>(smem_gen + ns * G::STAGE_BYTES);
+    const float* mm = mo + NW_ * 8 * BP_HEAD_DIM;
+    const float* ml = mm + NW_ * 8;
+    const uint32_t total = hpc * p.qpg * BP_HEAD_DIM;  // outputs of this CTA
     for (uint32_t idx = threadIdx.x; idx < total; idx += blockDim.x) {
-      const uint32_t h = idx >> 7, d = idx & 127;
-      const uint32_t g = h / p.qpg, hq = h % p.qpg;
+      const uint32_t hl = idx >> 7, d = idx & 127;
+      const uint32_t g = hl / p.qpg, hq = hl % p.qpg;
       float m_all = NEG_BIG;
-      for (uint32_t sl = 0; sl < wph; sl++) m_all = fmaxf(m_all, mm[(sl * nkv + g) * 8 + hq]);
+      for (uint32_t sl = 0; sl < wph; sl++) m_all = fmaxf(m_all, mm[(sl * hpc + g) * 8 + hq]);
       float o = 0.f, l = 0.f;
       for (uint32_t sl = 0; sl < wph; sl++) {
-        const uint32_t w = sl * nkv + g;
-        const float e = ex2(mm[w * 8 + hq] - m_all);
-        o += mo[(w * 8 + hq) * BP_HEAD_DIM + d] * e;
-        l += ml[w * 8 + hq] * e;
+        const uint32_t wi = sl * hpc + g;
+        const float e = ex2(mm[wi * 8 + hq] - m_all);
+        o += mo[(wi * 8 + hq) * BP_HEAD_DIM + d] * e;
+        l += ml[wi * 8 + hq] * e;
       }
+      const uint32_t h = g0 * p.qpg + hl;  // query head within the context
       if (n_splits == 1) {
-        p.out[idx] = __float2half_rn(o * (1.0f / l));
+        p.out[static_cast<size_t>(h) * BP_HEAD_DIM + d] = __float2half_rn(o * (1.0f / l));
       } else {
         float* dst = p.partials + (static_cast<size_t>(split) * p.n_head + h) * BP_PART_STRIDE;
         dst[d] = o;
@@ -474,7 +517,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_const
   }
   // The producer drains its own copies before the CTA retires (all of them have
   // already completed unless a wait above gave up).
-  if (warp == NW && lane == 0) {
+  if (warp == NW_ && lane == 0) {
     const uint32_t first = n_iter > ns ? n_iter - ns : 0;
     for (uint32_t it = first; it < n_iter; it++)
       if (!mbar_wait(smem_u32(&full_bar[it % ns]), (it / ns) & 1, 1u << 20)) atomicExch(p.err, 2u);
@@ -483,9 +526,11 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_const
 
 }  // namespace
 
-// Split policy. A stage holds 16 * (8 / n_kv_head) tokens; a split is a whole
-// number of stages, chosen so that the grid is at most one CTA per SM.
-static uint32_t stage_tokens(const bp_attn_ctx* c) { return SUBTILE * (NW / c->cfg.n_kv_head); }
+// Launch geometry. A stage holds 16 * (NW / hpc) tokens of `hpc` KV heads; a
+// split is a whole number of stages, chosen so that the grid is at most one CTA
+// per SM. nw (8 or 16 compute warps) and hpc (KV heads per CTA) are context
+// options.
+static uint32_t stage_tokens(const bp_attn_ctx* c) { return SUBTILE * (c->opt_nw / c->opt_hpc); }
 
 uint32_t bp_decode_max_splits(const bp_attn_ctx* c) {
   const uint32_t sms = static_cast<uint32_t>(c->sm_count);
@@ -495,15 +540,16 @@ uint32_t bp_decode_max_splits(const bp_attn_ctx* c) {
 static uint32_t stages_per_split(const bp_attn_ctx* c, uint32_t cur_pos) {
   const uint32_t st = stage_tokens(c);
   const uint32_t n_st = (cur_pos + st - 1) / st;
-  const uint32_t ctas = bp_decode_max_splits(c);
+  const uint32_t groups = c->cfg.n_kv_head / c->opt_hpc;
+  uint32_t ctas = bp_decode_max_splits(c) / groups;
+  if (ctas == 0) ctas = 1;
   return (n_st + ctas - 1) / ctas;
 }
 
 uint32_t bp_decode_splits(const bp_attn_ctx* c, uint32_t cur_pos) {
   if (c->variant == 1) {
-    const uint32_t tps = 256;
-    return (cur_pos + tps - 1) / tps > bp_decode_max_splits(c) ? bp_decode_max_splits(c)
-                                                               : (cur_pos + tps - 1) / tps;
+    const uint32_t tps = 256, n = (cur_pos + tps - 1) / tps;
+    return n > bp_decode_max_splits(c) ? bp_decode_max_splits(c) : n;
   }
   const uint32_t st = stage_tokens(c);
   const uint32_t n_st = (cur_pos + st - 1) / st;
@@ -542,12 +588,31 @@ cudaError_t bp_launch_scalar_attention(bp_attn_ctx* c, cudaStream_t s, uint32_t 
 
 uint32_t bp_decode_stage_tokens(const bp_attn_ctx* c) { return stage_tokens(c); }
 
+template <int NW_>
+static cudaError_t set_smem_attr() {
+  const int max_smem = Geo<NW_>::max_stages() * Geo<NW_>::STAGE_BYTES + Geo<NW_>::MERGE_BYTES + 1024;
+  cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<NW_, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(decode_mma_kernel<NW_, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+}
+
 // Opt the production kernels into their dynamic shared memory on the context's device.
 cudaError_t bp_decode_init(bp_attn_ctx*) {
-  const int max_smem = MAX_STAGES * STAGE_BYTES + MERGE_BYTES + 1024;
-  cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+  cudaError_t e = set_smem_attr<8>();
   if (e != cudaSuccess) return e;
-  return cudaFuncSetAttribute(decode_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+  return set_smem_attr<16>();
+}
+
+template <int NW_>
+static cudaError_t launch_mma(bp_attn_ctx* c, cudaStream_t s, DecodeParams& p, uint32_t spp, uint32_t n_splits,
+                              bool denorm) {
+  using G = Geo<NW_>;
+  p.n_stages = spp < G::max_stages() ? spp : G::max_stages();
+  const size_t smem = static_cast<size_t>(p.n_stages) * G::STAGE_BYTES + G::MERGE_BYTES + 1024;
+  dim3 grid(n_splits, c->cfg.n_kv_head / c->opt_hpc);
+  auto kern = denorm ? decode_mma_kernel<NW_, true> : decode_mma_kernel<NW_, false>;
+  kern<<<grid, (NW_ + 1) * 32, smem, s>>>(c->map_qs[0], c->map_d[0], c->map_qs[1], c->map_d[1], p);
+  return cudaGetLastError();
 }
 
 cudaError_t bp_launch_decode(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, const __half* q,
@@ -555,7 +620,6 @@ cudaError_t bp_launch_decode(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, con
   if (c->variant == 1) return bp_launch_scalar_attention(c, s, layer, q, out, cur_pos, 1, false, launches);
   if (!c->have_maps) return cudaErrorNotSupported;
 
-  const bool denorm = c->variant != 2;
   const uint32_t st = stage_tokens(c);
   const uint32_t spp = stages_per_split(c, cur_pos);
   const uint32_t n_splits = bp_decode_splits(c, cur_pos);
@@ -567,18 +631,15 @@ cudaError_t bp_launch_decode(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, con
   p.row_base = layer * c->cfg.max_seq;
   p.cur_pos = cur_pos;
   p.tps = spp * st;
-  p.n_stages = spp < MAX_STAGES ? spp : MAX_STAGES;
+  p.n_stages = 1;
   p.n_head = c->cfg.n_head;
-  p.nkv = c->cfg.n_kv_head;
+  p.hpc = c->opt_hpc;
   p.qpg = c->qpg;
-  p.d_swz = (16 * c->cfg.n_kv_head == 128) ? 1u : 0u;
+  p.d_swz = (16 * c->opt_hpc == 128) ? 1u : 0u;
   p.sm_scale_log2 = (1.0f / sqrtf(static_cast<float>(BP_HEAD_DIM))) * 1.4426950408889634f;
-  const size_t smem = static_cast<size_t>(p.n_stages) * STAGE_BYTES + MERGE_BYTES + 1024;
-
-  auto kern = denorm ? decode_mma_kernel<true> : decode_mma_kernel<false>;
-  kern<<<n_splits, (NW + 1) * 32, smem, s>>>(c->map_qs[0], c->map_d[0], c->map_qs[1], c->map_d[1], p);
+  cudaError_t e = c->opt_nw == 16 ? launch_mma<16>(c, s, p, spp, n_splits, c->variant != 2)
+                                  : launch_mma<8>(c, s, p, spp, n_splits, c->variant != 2);
   *launches += 1;
-  cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   if (n_splits > 1) {
     attn_combine_kernel<<<c->cfg.n_head, 128 * COMBINE_GROUPS, 0, s>>>(c->partials, out, c->cfg.n_head, n_splits);

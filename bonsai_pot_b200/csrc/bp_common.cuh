@@ -35,6 +35,8 @@ struct bp_attn_ctx {
   cudaStream_t host_stream;
   int sm_count;
   uint32_t variant;
+  uint32_t opt_nw;   // decode: compute warps per CTA (8 or 16)
+  uint32_t opt_hpc;  // decode: KV heads per CTA (divides n_kv_head)
   uint32_t last_launches;
   int status;  // latched device-lost status, BP_OK otherwise
   bp_error_detail detail;

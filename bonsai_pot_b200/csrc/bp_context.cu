@@ -137,6 +137,16 @@ bool bp_make_kv_maps(bp_attn_ctx* c, int kind, uint32_t rows_box, uint32_t d_inn
   return true;
 }
 
+// (Re)builds the decode tensor maps for the current nw / hpc options.
+static bool rebuild_decode_maps(bp_attn_ctx* c) {
+  c->have_maps = true;
+  const uint32_t inner = 16 * c->opt_hpc;
+  for (int kind = 0; kind < 2 && c->have_maps; kind++)
+    c->have_maps = bp_make_kv_maps(c, kind, bp_decode_stage_tokens(c), inner, inner == 128, &c->map_qs[kind],
+                                   &c->map_d[kind]);
+  return c->have_maps;
+}
+
 extern "C" {
 
 const char* bp_strerror(int status) {
@@ -225,12 +235,9 @@ int bp_attn_create(const bp_attn_config* cfg, bp_attn_ctx** out) {
   *c->err_host = 0;
   BP_CUDA(c, cudaHostGetDevicePointer(&c->err_dev, c->err_host, 0));
 
-  c->have_maps = true;
-  for (int kind = 0; kind < 2 && c->have_maps; kind++) {
-    c->have_maps = bp_make_kv_maps(c, kind, bp_decode_stage_tokens(c), c->nb * 4, c->nb * 4 == 128,
-                                   &c->map_qs[kind], &c->map_d[kind]);
-  }
-  if (!c->have_maps) return fail(c, BP_ERR_CUDA, "cuTensorMapEncodeTiled failed for the KV cache");
+  c->opt_nw = 8;
+  c->opt_hpc = cfg->n_kv_head;
+  if (!rebuild_decode_maps(c)) return fail(c, BP_ERR_CUDA, "cuTensorMapEncodeTiled failed for the KV cache");
   BP_CUDA(c, bp_decode_init(c));
   BP_CUDA(c, bp_prefill_init(c));
   BP_CUDA(c, cudaStreamCreateWithFlags(&c->host_stream, cudaStreamNonBlocking));
@@ -565,6 +572,24 @@ int bp_set_variant(bp_attn_ctx* c, uint32_t variant) {
   if (!c) return BP_ERR_NULL;
   if (variant > 2) return fail_config(c, "unknown kernel variant");
   c->variant = variant;
+  return BP_OK;
+}
+
+int bp_set_option(bp_attn_ctx* c, const char* name, uint32_t value) {
+  if (!c || !name) return BP_ERR_NULL;
+  if (strcmp(name, "decode_warps") == 0) {
+    if (value != 8 && value != 16) return fail_config(c, "decode_warps must be 8 or 16");
+    c->opt_nw = value;
+  } else if (strcmp(name, "decode_heads_per_cta") == 0) {
+    if (value == 0 || c->cfg.n_kv_head % value != 0 || (value & (value - 1)) != 0)
+      return fail_config(c, "decode_heads_per_cta must be a power of two that divides n_kv_head");
+    c->opt_hpc = value;
+  } else {
+    return fail_config(c, "unknown option");
+  }
+  if (c->opt_hpc > c->opt_nw) c->opt_hpc = c->opt_nw;
+  if (bind_device(c) != BP_OK) return BP_ERR_CUDA;
+  if (!rebuild_decode_maps(c)) return fail(c, BP_ERR_CUDA, "cuTensorMapEncodeTiled failed for the KV cache");
   return BP_OK;
 }
 

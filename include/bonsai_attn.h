@@ -188,6 +188,10 @@ int bp_rope_table_copy(bp_attn_ctx* ctx, void* host_f16);      /* host copy of t
 /* Selects the kernel family: 0 = production kernels (default), 1 = the plain
  * CUDA-core kernels kept as an on-device cross-check. */
 int bp_set_variant(bp_attn_ctx* ctx, uint32_t variant);
+/* Tuning knobs of the decode kernel: "decode_warps" (8 or 16 compute warps per
+ * CTA) and "decode_heads_per_cta" (KV heads streamed by one CTA; a power of two
+ * dividing n_kv_head). Results do not depend on them beyond rounding. */
+int bp_set_option(bp_attn_ctx* ctx, const char* name, uint32_t value);
 /* Number of kernels the last compute call launched. */
 uint32_t bp_last_launch_count(const bp_attn_ctx* ctx);
 /* Number of split-KV partitions `bp_attn_decode` uses at `cur_pos`. */

@@ -429,3 +429,20 @@ def test_token_host_entry_point_equals_per_layer_calls():
             assert np.array_equal(kq[300], sh.qs_section(c["kv_k"], il)[300])
         with pytest.raises(bp.ContextOverflow):
             ctx.decode_token_host(q, k, v, w, w, 512, out)
+
+
+@pytest.mark.parametrize("warps,hpc", [(16, 8), (8, 4), (8, 2), (16, 1), (8, 1)])
+def test_decode_tuning_options_do_not_change_results(warps, hpc):
+    sh = O.Shape(n_layer=2, max_seq=4096)
+    case = build_decode_case(sh, seed=11, cfg_id=1, layer=1, n_past=3000)
+    with make_ctx(sh) as ctx:
+        load_cache(ctx, sh, case["kv_k"], case["kv_v"], 1, 3001)
+        ctx.set_option("decode_warps", warps)
+        ctx.set_option("decode_heads_per_cta", hpc)
+        for cur_pos in (1, 17, 100, 777, 3001):
+            got = run_decode(ctx, sh, dict(case, cur_pos=cur_pos), 1)
+            exact = O.attn_exact(sh, case["qn"], case["kv_k"], case["kv_v"], 1, 1, cur_pos - 1)[0]
+            ok, max_abs, max_rel = within_tolerance(got, exact)
+            assert ok, (warps, hpc, cur_pos, max_abs, max_rel)
+        with pytest.raises(bp.ConfigError):
+            ctx.set_option("decode_warps", 12)
