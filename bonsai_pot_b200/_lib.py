@@ -96,6 +96,7 @@ SIGNATURES = {
     "bp_set_option": (_int, [_vp, C.c_char_p, _u32]),
     "bp_last_launch_count": (_u32, [_vp]),
     "bp_decode_num_splits": (_u32, [_vp, _u32]),
+    "bp_attn_decode_static_scratch": (_int, [_vp, _vp, _vp, _vp, _vp] + [_u32] * 6),
 }
 
 _LIB = None

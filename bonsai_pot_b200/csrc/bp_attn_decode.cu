@@ -648,3 +648,76 @@ cudaError_t bp_launch_decode(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, con
   }
   return e;
 }
+
+// ---------------------------------------------------------------------------
+// Decode attention for callers that must not allocate.
+//
+// Some hosts cannot call cudaMalloc where they run this step: a real-time
+// serving loop that has handed all device memory to its own arena, a plugin
+// that is loaded into a process whose allocator is owned by someone else, or a
+// caller that sits inside a region where allocation is forbidden. For them the
+// split-KV scratch (one partial per split and query head) lives in a fixed
+// array that is part of the library image: every GPU that loads the library
+// holds these NOALLOC_SCRATCH_FLOATS * 4 bytes (about 1.1 MB) until the process
+// exits. The price is a hard limit on the problem size (at most 64 query heads;
+// the number of splits is capped at 32) and no re-entrancy: all calls share the
+// one array, so two calls that overlap on the GPU (different streams, or
+// different host threads) race on it. Nothing in the array has to be zero on
+// entry: each call overwrites every partial it later reads, and what the
+// previous call left behind is never read.
+// ---------------------------------------------------------------------------
+namespace {
+constexpr uint32_t NOALLOC_MAX_HEADS = 64;
+constexpr uint32_t NOALLOC_MAX_SPLITS = 32;
+constexpr uint32_t NOALLOC_SCRATCH_FLOATS = NOALLOC_MAX_SPLITS * NOALLOC_MAX_HEADS * BP_PART_STRIDE;
+constexpr int NOALLOC_MAX_DEVICES = 64;
+static __device__ __align__(256) float g_noalloc_scratch[NOALLOC_SCRATCH_FLOATS];
+// Device address of the array above, per device. In host code the array's name
+// is only a handle for the runtime; the address a kernel can use comes from
+// cudaGetSymbolAddress with that device current.
+float* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {};
+}  // namespace
+
+extern "C" int bp_attn_decode_static_scratch(void* stream, const void* q, const void* kv_k, const void* kv_v,
+                                             void* out, uint32_t n_layer, uint32_t max_seq, uint32_t n_head,
+                                             uint32_t n_kv_head, uint32_t layer, uint32_t cur_pos) {
+  if (!q || !kv_k || !kv_v || !out) return BP_ERR_NULL;
+  if (n_head == 0 || n_kv_head == 0 || n_head % n_kv_head != 0 || n_layer == 0 || max_seq == 0 || layer >= n_layer)
+    return BP_ERR_CONFIG;
+  if (n_head > NOALLOC_MAX_HEADS) return BP_ERR_CONFIG;  // beyond the fixed scratch: use bp_attn_decode
+  if (cur_pos == 0) return BP_ERR_CONFIG;
+  if (cur_pos > max_seq) return BP_ERR_CONTEXT_OVERFLOW;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) return BP_ERR_CUDA;
+  if (!g_noalloc_ptr[dev]) {
+    // First call on this device: resolve the array's device address (this does
+    // not allocate). Make this first call outside any stream capture.
+    float* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_scratch) != cudaSuccess || !p) return BP_ERR_CUDA;
+    g_noalloc_ptr[dev] = p;
+  }
+  const uint32_t kv_dim = n_kv_head * BP_HEAD_DIM, nb = kv_dim / BP_QK8;
+  const uint64_t d_total = static_cast<uint64_t>(n_layer) * max_seq * nb * 4u;
+  const uint64_t d_off = static_cast<uint64_t>(layer) * max_seq * nb * 4u;
+  const uint64_t qs_off = d_total + static_cast<uint64_t>(layer) * max_seq * kv_dim;
+  const uint8_t* kb = static_cast<const uint8_t*>(kv_k);
+  const uint8_t* vb = static_cast<const uint8_t*>(kv_v);
+  uint32_t n_splits = (cur_pos + 255) / 256;
+  if (n_splits > NOALLOC_MAX_SPLITS) n_splits = NOALLOC_MAX_SPLITS;
+  const uint32_t tps = (cur_pos + n_splits - 1) / n_splits;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  dim3 grid(n_splits, n_head, 1);
+  attn_scalar_kernel<<<grid, 128, 0, st>>>(static_cast<const __half*>(q), reinterpret_cast<const float*>(kb + d_off),
+                                           reinterpret_cast<const uint32_t*>(kb + qs_off),
+                                           reinterpret_cast<const float*>(vb + d_off),
+                                           reinterpret_cast<const uint32_t*>(vb + qs_off), g_noalloc_ptr[dev],
+                                           static_cast<__half*>(out), n_head, n_kv_head, cur_pos, tps, 0u,
+                                           1.0f / sqrtf(static_cast<float>(BP_HEAD_DIM)));
+  if (cudaGetLastError() != cudaSuccess) return BP_ERR_CUDA;
+  if (n_splits > 1) {
+    attn_combine_kernel<<<n_head, 128 * COMBINE_GROUPS, 0, st>>>(g_noalloc_ptr[dev], static_cast<__half*>(out),
+                                                                 n_head, n_splits);
+    if (cudaGetLastError() != cudaSuccess) return BP_ERR_CUDA;
+  }
+  return BP_OK;
+}

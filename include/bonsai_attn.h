@@ -197,6 +197,23 @@ uint32_t bp_last_launch_count(const bp_attn_ctx* ctx);
 /* Number of split-KV partitions `bp_attn_decode` uses at `cur_pos`. */
 uint32_t bp_decode_num_splits(const bp_attn_ctx* ctx, uint32_t cur_pos);
 
+/* No counterpart in the reference. Decode attention (the same result as
+ * bp_attn_decode) for callers that cannot allocate device memory where they
+ * call it - a host whose allocator owns all of the GPU, a plugin inside someone
+ * else's process, a no-allocation region of a serving loop. It takes no
+ * context: the caller passes the query, the two whole cache buffers in the
+ * reference layout (d-section then qs-section, see bp_kv_device_ptr) and the
+ * output, and the split-KV scratch is a fixed array inside the library image
+ * (about 1.1 MB on every GPU that loads the library, held until exit). The call
+ * itself allocates nothing. Limits: n_head <= 64 (BP_ERR_CONFIG beyond that;
+ * use bp_attn_decode), head_dim 128. The first call on a device looks up the
+ * array's device address; make that call before any stream capture. All calls
+ * share the one array: calls that overlap on the GPU race, so keep them on one
+ * stream. Nothing has to be cleared between calls. Asynchronous on `stream`. */
+int bp_attn_decode_static_scratch(void* stream, const void* q, const void* kv_k, const void* kv_v, void* out,
+                                  uint32_t n_layer, uint32_t max_seq, uint32_t n_head, uint32_t n_kv_head,
+                                  uint32_t layer, uint32_t cur_pos);
+
 #ifdef __cplusplus
 }
 #endif
