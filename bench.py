@@ -254,10 +254,13 @@ def run_ours(args):
         ctx.set_option("decode_warps", args.decode_warps)
     if args.decode_hpc:
         ctx.set_option("decode_heads_per_cta", args.decode_hpc)
+    if args.decode_uhpc:
+        ctx.set_option("decode_umma_heads_per_cta", args.decode_uhpc)
     gen = torch.Generator(device="cuda")
     gen.manual_seed(1234 + rank)
     fill_cache(ctx, torch, N_LAYER, kv_dim_l, ctx_len - 1, gen)
 
+    ctx.set_variant(args.variant)
     w = torch.ones(128, dtype=torch.float16, device="cuda")
     q_raw = torch.randn(N_LAYER, q_dim_l, generator=gen, device="cuda").half()
     k_new = torch.randn(N_LAYER, kv_dim_l, generator=gen, device="cuda").half()
@@ -405,7 +408,10 @@ def extras(torch, bp, stream, hbm_peak, tflops_peak, peak_kind, args):
             c.set_option("decode_warps", args.decode_warps)
         if args.decode_hpc:
             c.set_option("decode_heads_per_cta", args.decode_hpc)
+        if args.decode_uhpc:
+            c.set_option("decode_umma_heads_per_cta", args.decode_uhpc)
         fill_cache(c, torch, nl, KV_DIM, ctx_len, gen)
+        c.set_variant(args.variant)
         q = torch.randn(nl, Q_DIM, generator=gen, device="cuda").half()
         o = torch.zeros(nl, Q_DIM, dtype=torch.float16, device="cuda")
         def sweep():
@@ -460,6 +466,8 @@ def main():
     ap.add_argument("--layers", type=int, default=N_LAYER, help="layers of the stack (smaller only for profiler captures)")
     ap.add_argument("--decode-warps", type=int, default=0, help="override the decode kernel's compute warps per CTA")
     ap.add_argument("--decode-hpc", type=int, default=0, help="override the decode kernel's KV heads per CTA")
+    ap.add_argument("--decode-uhpc", type=int, default=0, help="override the tcgen05 decode kernel's KV heads per CTA")
+    ap.add_argument("--variant", type=int, default=0, help="decode kernel family (0 = production)")
     ap.add_argument("--no-extras", action="store_true", help="skip the ctx-32768 and prefill side measurements")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()

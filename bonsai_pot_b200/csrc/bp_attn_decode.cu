@@ -547,6 +547,7 @@ static uint32_t stages_per_split(const bp_attn_ctx* c, uint32_t cur_pos) {
 }
 
 uint32_t bp_decode_splits(const bp_attn_ctx* c, uint32_t cur_pos) {
+  if (bp_use_umma(c)) return bp_decode_umma_splits(c, cur_pos);
   if (c->variant == 1) {
     const uint32_t tps = 256, n = (cur_pos + tps - 1) / tps;
     return n > bp_decode_max_splits(c) ? bp_decode_max_splits(c) : n;
@@ -618,6 +619,18 @@ static cudaError_t launch_mma(bp_attn_ctx* c, cudaStream_t s, DecodeParams& p, u
 cudaError_t bp_launch_decode(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, const __half* q,
                              __half* out, uint32_t cur_pos, uint32_t* launches) {
   if (c->variant == 1) return bp_launch_scalar_attention(c, s, layer, q, out, cur_pos, 1, false, launches);
+  if (bp_use_umma(c)) {
+    uint32_t n_splits = 1;
+    cudaError_t e = bp_launch_decode_umma(c, s, layer, q, out, cur_pos, &n_splits);
+    *launches += 1;
+    if (e != cudaSuccess) return e;
+    if (n_splits > 1) {
+      attn_combine_kernel<<<c->cfg.n_head, 128 * COMBINE_GROUPS, 0, s>>>(c->partials, out, c->cfg.n_head, n_splits);
+      *launches += 1;
+      e = cudaGetLastError();
+    }
+    return e;
+  }
   if (!c->have_maps) return cudaErrorNotSupported;
 
   const uint32_t st = stage_tokens(c);

@@ -1,0 +1,491 @@
+// Split-KV decode attention on the 5th-generation tensor cores (tcgen05, int8
+// UMMA, accumulators in TMEM). Same contract as decode_mma_kernel: one CTA per
+// (token range, group of KV heads) writes a partial (o, m, l) per query head.
+//
+// Why: with warp-level MMA every cache byte passes through registers and costs
+// ALU work to become an f16 operand. Here the int8 tiles that TMA drops into
+// shared memory ARE the tensor-core operands:
+//   S^T[token][head]  = K tile (A, K-major, 128 tokens x 32 dims of one Q8_0 block)
+//                       x Q^T (B, 15-bit integer Q split into a high and a low byte row)
+//   O^T[dim][head]    = V tile (A, MN-major: the 128 dims of a token row are contiguous)
+//                       x P'^T (B, P' = p * V block scale as a 23-bit integer in three byte rows)
+// so the only per-byte work left on the SM is none at all; per TOKEN the
+// softmax warps do about 350 instructions per 128 tokens of one KV head.
+// The integer products are exact; Q is quantised to 15 bits per block of 32 dims
+// (finer than its f16 input) and P' to 23 bits of the stage's largest V scale.
+//
+// Roles (320 threads): warp 0 TMA producer, warp 1 UMMA issuer + TMEM owner,
+// warps 2-5 softmax (thread = token row = TMEM lane), warps 6-9 accumulate
+// (thread = head dim = TMEM lane). Every mbarrier wait is bounded; after a
+// timeout the CTA stops waiting, drains and frees TMEM, and reports through the
+// error word.
+#include "bp_common.cuh"
+#include "bp_ptx.cuh"
+
+namespace {
+
+using namespace bp;
+
+constexpr unsigned FULL = 0xffffffffu;
+constexpr float NEG_BIG = -1e30f;
+constexpr uint32_t UT = 128;                 // tokens per stage = UMMA M
+constexpr uint32_t TILE_B = UT * 128;        // int8 tile of one head and stage: 16 KB
+constexpr uint32_t U_MAX_STAGES = 6;
+constexpr uint32_t U_THREADS = 320;
+constexpr uint32_t TMEM_COLS = 256;          // D1: 2 x 64 columns, D2: 2 x 64 columns
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+constexpr uint32_t U_SMEM_BUDGET = 226 * 1024;  // dynamic shared memory; the static part needs the rest of 227 KB
+
+struct UmmaParams {
+  const __half* q;
+  __half* out;
+  float* partials;
+  uint32_t* err;
+  uint32_t row_base, cur_pos, tps, n_stages, n_head, qpg;
+  float sm_scale_log2;
+};
+
+template <uint32_t HPC>
+struct ULayout {
+  static constexpr uint32_t SCALE_B = UT * HPC * 16;                   // scale rows of one stage (K or V)
+  static constexpr uint32_t STAGE_B = 2 * HPC * TILE_B + 2 * SCALE_B;  // 73,728 B for HPC = 2
+  static constexpr uint32_t Q_B = HPC * 2048;                          // Q^T tiles: 16 rows x 128 B per head
+  static constexpr uint32_t P_B = 2 * 4 * 2048;                        // P'^T tiles: 2 buffers x 4 blocks
+  static constexpr uint32_t MISC_B = 2048;
+  static constexpr uint32_t tail() { return Q_B + P_B + MISC_B; }
+  static constexpr uint32_t total(uint32_t stages) { return stages * STAGE_B + tail() + 1024; }
+};
+
+struct Misc {            // small shared state, lives in the MISC_B region
+  float sq[8][4][4];     // Q block scales [head][query head][block] (pre-multiplied by the softmax scale)
+  int xchg[2][4][8];     // per-warp maxima of a job: 4 score maxima, 4 V-scale maxima
+  float info[2][8];      // per job buffer: corr[4], dequantisation factor of P' per block [4]
+  float lsum[8][4][4];   // final l per (head, query head, warp)
+  float mfin[8][4];
+};
+
+__device__ __forceinline__ float s32_to_f32(uint32_t x) {  // exact for |x| < 2^22
+  return __int_as_float(static_cast<int>(x) + 0x4B400000) - 12582912.0f;
+}
+__device__ __forceinline__ int f32_order(float f) {  // monotone map float -> int
+  const int b = __float_as_int(f);
+  return b >= 0 ? b : b ^ 0x7fffffff;
+}
+__device__ __forceinline__ float f32_unorder(int k) { return __int_as_float(k >= 0 ? k : k ^ 0x7fffffff); }
+
+template <uint32_t HPC>
+__global__ void __launch_bounds__(U_THREADS, 1)
+decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_constant__ CUtensorMap map_kd,
+                   const __grid_constant__ CUtensorMap map_vq, const __grid_constant__ CUtensorMap map_vd,
+                   const UmmaParams p) {
+  using L = ULayout<HPC>;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[U_MAX_STAGES], empty_bar[U_MAX_STAGES];
+  __shared__ __align__(8) uint64_t s_ready[2], s_free[2], p_ready[2], p_free[2], o_ready[2], o_free[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ volatile uint32_t abort_s;
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t ns = p.n_stages;
+  const uint32_t g0 = blockIdx.y * HPC;
+  const uint32_t split = blockIdx.x, n_splits = gridDim.x;
+  const uint32_t tok_begin = split * p.tps;
+  const uint32_t tok_end = min(tok_begin + p.tps, p.cur_pos);
+  const uint32_t n_iter = (tok_end - tok_begin + UT - 1) / UT;
+  const uint32_t n_jobs = n_iter * HPC;
+
+  const uint32_t q_tiles = smem_base + ns * L::STAGE_B;   // 1024-aligned (STAGE_B is a multiple of 1024)
+  const uint32_t p_tiles = q_tiles + L::Q_B;
+  Misc* misc = reinterpret_cast<Misc*>(smem_gen + ns * L::STAGE_B + L::Q_B + L::P_B);
+
+  // ---- set-up: barriers, TMEM, zeroed operand tiles, quantised Q ----
+  if (threadIdx.x == 0) {
+    for (uint32_t s = 0; s < ns; s++) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int b = 0; b < 2; b++) {
+      mbar_init(smem_u32(&s_ready[b]), 1);
+      mbar_init(smem_u32(&s_free[b]), 4);
+      mbar_init(smem_u32(&p_ready[b]), 4);
+      mbar_init(smem_u32(&p_free[b]), 1);
+      mbar_init(smem_u32(&o_ready[b]), 1);
+      mbar_init(smem_u32(&o_free[b]), 4);
+    }
+    abort_s = 0;
+    fence_barrier_init();
+  }
+  {
+    uint4* z = reinterpret_cast<uint4*>(smem_gen + ns * L::STAGE_B);
+    for (uint32_t i = threadIdx.x; i < (L::Q_B + L::P_B) / 16; i += U_THREADS) z[i] = make_uint4(0, 0, 0, 0);
+  }
+  if (warp == 1) tmem_alloc(smem_u32(&tmem_base_s), TMEM_COLS);
+  __syncthreads();
+  // Q of head (g, hq), block b: 15-bit integers = 128 * hi + lo against the block's absmax;
+  // hi bytes go to row hq, lo bytes to row 4 + hq of the head's Q^T tile (swizzled 128-byte rows).
+  if (threadIdx.x < HPC * p.qpg * 4) {
+    const uint32_t b = threadIdx.x & 3, hq = (threadIdx.x >> 2) % p.qpg, g = (threadIdx.x >> 2) / p.qpg;
+    const __half* src = p.q + (static_cast<size_t>(g0 + g) * p.qpg + hq) * BP_HEAD_DIM + 32 * b;
+    float v[32], amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(src + 8 * i);
+      const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const float2 f = __half22float2(h2[j]);
+        v[8 * i + 2 * j] = f.x;
+        v[8 * i + 2 * j + 1] = f.y;
+        amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+      }
+    }
+    const float sq = amax / 16383.0f, inv = amax > 0.f ? 16383.0f / amax : 0.f;
+    uint32_t hi[8], lo[8];
+#pragma unroll
+    for (int w = 0; w < 8; w++) {
+      hi[w] = 0; lo[w] = 0;
+#pragma unroll
+      for (int c = 0; c < 4; c++) {
+        const int qi = __float2int_rn(v[4 * w + c] * inv);
+        hi[w] |= (static_cast<uint32_t>(qi >> 7) & 0xffu) << (8 * c);
+        lo[w] |= (static_cast<uint32_t>(qi) & 0x7fu) << (8 * c);
+      }
+    }
+    uint8_t* tile = smem_gen + ns * L::STAGE_B + g * 2048;
+#pragma unroll
+    for (int c = 0; c < 2; c++) {  // two 16-byte chunks of the block
+      const uint32_t off_hi = hq * 128 + 32 * b + 16 * c, off_lo = (4 + hq) * 128 + 32 * b + 16 * c;
+      *reinterpret_cast<uint4*>(tile + swz128(off_hi)) = make_uint4(hi[4 * c], hi[4 * c + 1], hi[4 * c + 2], hi[4 * c + 3]);
+      *reinterpret_cast<uint4*>(tile + swz128(off_lo)) = make_uint4(lo[4 * c], lo[4 * c + 1], lo[4 * c + 2], lo[4 * c + 3]);
+    }
+    misc->sq[g][hq][b] = sq * p.sm_scale_log2;
+  }
+  fence_proxy_async();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_s;
+
+  // A wait that degrades to a no-op once any warp of the CTA has timed out.
+  auto wait = [&](uint64_t* bar, uint32_t parity) {
+    if (abort_s) return;
+    if (!mbar_wait(smem_u32(bar), parity, WAIT_LIMIT)) {
+      abort_s = 1;
+      atomicExch(p.err, 3u);
+    }
+  };
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      prefetch_tensormap(&map_kq);
+      prefetch_tensormap(&map_vq);
+      prefetch_tensormap(&map_kd);
+      prefetch_tensormap(&map_vd);
+      for (uint32_t it = 0; it < n_iter; it++) {
+        const uint32_t s = it % ns, use = it / ns;
+        if (use > 0) wait(&empty_bar[s], (use - 1) & 1);
+        if (abort_s) break;
+        const uint32_t bar = smem_u32(&full_bar[s]);
+        const uint32_t stage = smem_base + s * L::STAGE_B;
+        const int row = static_cast<int>(p.row_base + tok_begin + it * UT);
+        mbar_arrive_expect_tx(bar, L::STAGE_B);
+        tma_load_2d(stage + 2 * HPC * TILE_B, &map_kd, bar, static_cast<int>(g0 * 16), row);
+        tma_load_2d(stage + 2 * HPC * TILE_B + L::SCALE_B, &map_vd, bar, static_cast<int>(g0 * 16), row);
+        for (uint32_t g = 0; g < HPC; g++) {
+          tma_load_3d(stage + g * TILE_B, &map_kq, bar, 0, static_cast<int>(g0 + g), row);
+          tma_load_3d(stage + (HPC + g) * TILE_B, &map_vq, bar, 0, static_cast<int>(g0 + g), row);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- UMMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t IDESC_QK = umma_idesc(2, 1, 1, 0, 0, 128, 16);  // s32 += s8 (K-major) x s8
+      constexpr uint32_t IDESC_PV = umma_idesc(2, 1, 0, 1, 0, 128, 16);  // s32 += s8 (MN-major) x u8
+      auto issue_qk = [&](uint32_t j) {
+        const uint32_t it = j / HPC, g = j % HPC, buf = j & 1, u = j >> 1, s = it % ns;
+        if (g == 0) wait(&full_bar[s], (it / ns) & 1);
+        if (u > 0) wait(&s_free[buf], (u - 1) & 1);
+        tc_fence_after();
+        const uint32_t ktile = smem_base + s * L::STAGE_B + g * TILE_B;
+        const uint32_t qtile = q_tiles + g * 2048;
+#pragma unroll
+        for (uint32_t b = 0; b < 4; b++)
+          umma_i8(tmem + buf * 64 + 16 * b, umma_desc_sw128(ktile + 32 * b, 16, 1024),
+                  umma_desc_sw128(qtile + 32 * b, 16, 1024), IDESC_QK, 0u);
+        umma_commit(smem_u32(&s_ready[buf]));
+      };
+      if (n_jobs > 0) issue_qk(0);
+      for (uint32_t j = 0; j < n_jobs; j++) {
+        if (j + 1 < n_jobs) issue_qk(j + 1);
+        const uint32_t it = j / HPC, g = j % HPC, buf = j & 1, u = j >> 1, s = it % ns;
+        wait(&p_ready[buf], u & 1);
+        if (u > 0) wait(&o_free[buf], (u - 1) & 1);
+        tc_fence_after();
+        const uint32_t vtile = smem_base + s * L::STAGE_B + (HPC + g) * TILE_B;
+#pragma unroll
+        for (uint32_t b = 0; b < 4; b++) {
+          const uint32_t ptile = p_tiles + (buf * 4 + b) * 2048;
+#pragma unroll
+          for (uint32_t k = 0; k < 4; k++)
+            umma_i8(tmem + 128 + buf * 64 + 16 * b, umma_desc_sw128(vtile + k * 32 * 128, 16, 1024),
+                    umma_desc_sw128(ptile + 32 * k, 16, 1024), IDESC_PV, k);
+        }
+        umma_commit(smem_u32(&o_ready[buf]));
+        umma_commit(smem_u32(&p_free[buf]));
+        if (g == HPC - 1) umma_commit(smem_u32(&empty_bar[s]));
+      }
+    }
+  } else if (warp < 6) {
+    // ---------------- softmax: thread = token row ----------------
+    const uint32_t quad = warp & 3, t = quad * 32 + lane;
+    const uint32_t lane_addr = (quad * 32) << 16;
+    float m_run[HPC][4], l_part[HPC][4];
+#pragma unroll
+    for (uint32_t g = 0; g < HPC; g++)
+#pragma unroll
+      for (int h = 0; h < 4; h++) { m_run[g][h] = NEG_BIG; l_part[g][h] = 0.f; }
+
+    for (uint32_t it = 0; it < n_iter; it++) {
+      const uint32_t s = it % ns;
+      const uint8_t* stage = smem_gen + s * L::STAGE_B;
+      const bool valid = tok_begin + it * UT + t < tok_end;
+#pragma unroll
+      for (uint32_t g = 0; g < HPC; g++) {
+        const uint32_t j = it * HPC + g, buf = j & 1, u = j >> 1;
+        wait(&s_ready[buf], u & 1);
+        tc_fence_after();
+        uint32_t d[4][8];
+#pragma unroll
+        for (uint32_t b = 0; b < 4; b++) tmem_ld8(tmem + lane_addr + buf * 64 + 16 * b, d[b]);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&s_free[buf]));
+
+        const float4 sk = *reinterpret_cast<const float4*>(stage + 2 * HPC * TILE_B + (t * HPC + g) * 16);
+        float4 sv = *reinterpret_cast<const float4*>(stage + 2 * HPC * TILE_B + L::SCALE_B + (t * HPC + g) * 16);
+        const float skb[4] = {sk.x, sk.y, sk.z, sk.w};
+        float sc[4];
+#pragma unroll
+        for (int h = 0; h < 4; h++) {
+          float acc = 0.f;
+#pragma unroll
+          for (int b = 0; b < 4; b++) {
+            const float dot = fmaf(s32_to_f32(d[b][h]), 128.0f, s32_to_f32(d[b][4 + h]));
+            acc = fmaf(dot, skb[b] * misc->sq[g][h][b], acc);
+          }
+          sc[h] = valid ? acc : NEG_BIG;
+        }
+        if (!valid) sv = make_float4(0.f, 0.f, 0.f, 0.f);
+        const float svb[4] = {sv.x, sv.y, sv.z, sv.w};
+
+        // maxima over the 128 tokens of the stage: 4 score maxima, 4 V-scale maxima
+        int red[8];
+#pragma unroll
+        for (int h = 0; h < 4; h++) red[h] = __reduce_max_sync(FULL, f32_order(sc[h]));
+#pragma unroll
+        for (int b = 0; b < 4; b++) red[4 + b] = static_cast<int>(__reduce_max_sync(FULL, __float_as_uint(svb[b])));
+        if (lane == 0) {
+          int4* dst = reinterpret_cast<int4*>(misc->xchg[j & 1][quad]);
+          dst[0] = make_int4(red[0], red[1], red[2], red[3]);
+          dst[1] = make_int4(red[4], red[5], red[6], red[7]);
+        }
+        named_bar_sync(1, 128);
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+          const int4* src = reinterpret_cast<const int4*>(misc->xchg[j & 1][w]);
+          const int4 a = src[0], c = src[1];
+          red[0] = max(red[0], a.x); red[1] = max(red[1], a.y); red[2] = max(red[2], a.z); red[3] = max(red[3], a.w);
+          red[4] = max(red[4], c.x); red[5] = max(red[5], c.y); red[6] = max(red[6], c.z); red[7] = max(red[7], c.w);
+        }
+        float pj[4], corr[4];
+#pragma unroll
+        for (int h = 0; h < 4; h++) {
+          const float m_new = fmaxf(m_run[g][h], f32_unorder(red[h]));
+          corr[h] = ex2(m_run[g][h] - m_new);
+          pj[h] = ex2(sc[h] - m_new);
+          l_part[g][h] = l_part[g][h] * corr[h] + pj[h];
+          m_run[g][h] = m_new;
+        }
+        float qscale[4], deq[4];
+#pragma unroll
+        for (int b = 0; b < 4; b++) {
+          const float vmax = __int_as_float(red[4 + b]);
+          qscale[b] = vmax > 0.f ? 8388607.0f / vmax : 0.f;
+          deq[b] = vmax * (1.0f / 8388607.0f);
+        }
+        // the P' buffer and the info slot are free once job j-2 has been consumed
+        if (u > 0) {
+          wait(&p_free[buf], (u - 1) & 1);
+          wait(&o_free[buf], (u - 1) & 1);
+        }
+        if (t == 0) {
+          *reinterpret_cast<float4*>(&misc->info[buf][0]) = make_float4(corr[0], corr[1], corr[2], corr[3]);
+          *reinterpret_cast<float4*>(&misc->info[buf][4]) = make_float4(deq[0], deq[1], deq[2], deq[3]);
+        }
+        // P'[h][b] = p[h] * sV[b] as a 23-bit integer: the low three bytes of (x * qscale + 2^23)
+        uint8_t* pt = smem_gen + ns * L::STAGE_B + L::Q_B + buf * 4 * 2048;
+        // byte rows of block b's tile: hi -> row h, mid -> row 4 + h, lo -> row 8 + h;
+        // this token's column inside a swizzled row n is t ^ ((n & 7) << 4)
+#pragma unroll
+        for (int b = 0; b < 4; b++) {
+          uint8_t* tile = pt + b * 2048;
+#pragma unroll
+          for (int h = 0; h < 4; h++) {
+            const uint32_t bits = __float_as_uint(fmaf(pj[h] * svb[b], qscale[b], 8388608.0f));
+            tile[h * 128 + (t ^ (h << 4))] = static_cast<uint8_t>(bits >> 16);
+            tile[(4 + h) * 128 + (t ^ ((4 + h) << 4))] = static_cast<uint8_t>(bits >> 8);
+            tile[(8 + h) * 128 + (t ^ (h << 4))] = static_cast<uint8_t>(bits);
+          }
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&p_ready[buf]));
+      }
+    }
+    // ---- l of every (head, query head): sum over the 128 token rows ----
+#pragma unroll
+    for (uint32_t g = 0; g < HPC; g++)
+#pragma unroll
+      for (int h = 0; h < 4; h++) {
+        float l = l_part[g][h];
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) l += __shfl_xor_sync(FULL, l, off);
+        if (lane == 0) misc->lsum[g][h][quad] = l;
+        if (t == 0) misc->mfin[g][h] = m_run[g][h];
+      }
+  } else {
+    // ---------------- accumulate: thread = head dim ----------------
+    const uint32_t quad = warp & 3, dim = quad * 32 + lane;
+    const uint32_t lane_addr = (quad * 32) << 16;
+    float o[HPC][4];
+#pragma unroll
+    for (uint32_t g = 0; g < HPC; g++)
+#pragma unroll
+      for (int h = 0; h < 4; h++) o[g][h] = 0.f;
+    for (uint32_t it = 0; it < n_iter; it++) {
+#pragma unroll
+      for (uint32_t g = 0; g < HPC; g++) {
+        const uint32_t j = it * HPC + g, buf = j & 1, u = j >> 1;
+        wait(&o_ready[buf], u & 1);
+        tc_fence_after();
+        uint32_t d[16];
+        tmem_ld16(tmem + lane_addr + 128 + buf * 64 + 16 * quad, d);  // this warp's dims are Q8_0 block `quad`
+        tmem_ld_wait();
+        const float4 corr = *reinterpret_cast<const float4*>(&misc->info[buf][0]);
+        const float deq = misc->info[buf][4 + quad];
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&o_free[buf]));
+        const float cr[4] = {corr.x, corr.y, corr.z, corr.w};
+#pragma unroll
+        for (int h = 0; h < 4; h++) {
+          float v = fmaf(s32_to_f32(d[h]), 65536.0f, fmaf(s32_to_f32(d[4 + h]), 256.0f, s32_to_f32(d[8 + h])));
+          o[g][h] = fmaf(o[g][h], cr[h], v * deq);
+        }
+      }
+    }
+    // stash O for the epilogue: o_fin[g][h][dim]
+    float* o_fin = reinterpret_cast<float*>(smem_gen);  // stage 0 is free by now (all jobs consumed)
+    __syncwarp();
+#pragma unroll
+    for (uint32_t g = 0; g < HPC; g++)
+#pragma unroll
+      for (int h = 0; h < 4; h++) o_fin[(g * 4 + h) * BP_HEAD_DIM + dim] = o[g][h];
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  // ---- epilogue: partial (o, m, l) per query head, or the final output ----
+  {
+    const float* o_fin = reinterpret_cast<const float*>(smem_gen);
+    const uint32_t total = HPC * p.qpg * BP_HEAD_DIM;
+    for (uint32_t idx = threadIdx.x; idx < total; idx += U_THREADS) {
+      const uint32_t hl = idx >> 7, d = idx & 127;
+      const uint32_t g = hl / p.qpg, hq = hl % p.qpg;
+      const float l = (misc->lsum[g][hq][0] + misc->lsum[g][hq][1]) + (misc->lsum[g][hq][2] + misc->lsum[g][hq][3]);
+      const float o = o_fin[(g * 4 + hq) * BP_HEAD_DIM + d];
+      const uint32_t h = (g0 + g) * p.qpg + hq;
+      if (n_splits == 1) {
+        p.out[static_cast<size_t>(h) * BP_HEAD_DIM + d] = __float2half_rn(o * (1.0f / l));
+      } else {
+        float* dst = p.partials + (static_cast<size_t>(split) * p.n_head + h) * BP_PART_STRIDE;
+        dst[d] = o;
+        if (d == 0) { dst[128] = misc->mfin[g][hq]; dst[129] = l; }
+      }
+    }
+  }
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, TMEM_COLS);
+}
+
+}  // namespace
+
+uint32_t bp_decode_umma_stage_tokens() { return UT; }
+
+template <uint32_t HPC>
+static cudaError_t umma_attr() {
+  return cudaFuncSetAttribute(decode_umma_kernel<HPC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              static_cast<int>(U_SMEM_BUDGET));
+}
+
+cudaError_t bp_decode_umma_init(bp_attn_ctx*) {
+  cudaError_t e = umma_attr<1>();
+  if (e != cudaSuccess) return e;
+  return umma_attr<2>();
+}
+
+template <uint32_t HPC>
+static uint32_t umma_max_stages() {
+  uint32_t n = (U_SMEM_BUDGET - ULayout<HPC>::tail() - 1024) / ULayout<HPC>::STAGE_B;
+  return n > U_MAX_STAGES ? U_MAX_STAGES : n;
+}
+
+// Geometry of the UMMA decode: stages of 128 tokens; the grid is
+// (splits, n_kv_head / hpc) with splits * groups <= number of SMs.
+static uint32_t umma_spp(const bp_attn_ctx* c, uint32_t cur_pos) {
+  const uint32_t n_st = (cur_pos + UT - 1) / UT;
+  const uint32_t groups = c->cfg.n_kv_head / c->opt_uhpc;
+  uint32_t ctas = bp_decode_max_splits(c) / groups;
+  if (ctas == 0) ctas = 1;
+  return (n_st + ctas - 1) / ctas;
+}
+
+uint32_t bp_decode_umma_splits(const bp_attn_ctx* c, uint32_t cur_pos) {
+  const uint32_t n_st = (cur_pos + UT - 1) / UT;
+  const uint32_t spp = umma_spp(c, cur_pos);
+  return (n_st + spp - 1) / spp;
+}
+
+template <uint32_t HPC>
+static cudaError_t launch_umma(bp_attn_ctx* c, cudaStream_t s, UmmaParams& p, uint32_t spp, uint32_t n_splits) {
+  p.n_stages = spp < umma_max_stages<HPC>() ? spp : umma_max_stages<HPC>();
+  const size_t smem = ULayout<HPC>::total(p.n_stages);
+  dim3 grid(n_splits, c->cfg.n_kv_head / HPC);
+  decode_umma_kernel<HPC><<<grid, U_THREADS, smem, s>>>(c->umap_qs[0], c->umap_d[0], c->umap_qs[1], c->umap_d[1], p);
+  return cudaGetLastError();
+}
+
+cudaError_t bp_launch_decode_umma(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, const __half* q, __half* out,
+                                  uint32_t cur_pos, uint32_t* n_splits_out) {
+  const uint32_t spp = umma_spp(c, cur_pos);
+  const uint32_t n_splits = bp_decode_umma_splits(c, cur_pos);
+  UmmaParams p;
+  p.q = q;
+  p.out = out;
+  p.partials = c->partials;
+  p.err = c->err_dev;
+  p.row_base = layer * c->cfg.max_seq;
+  p.cur_pos = cur_pos;
+  p.tps = spp * UT;
+  p.n_stages = 1;
+  p.n_head = c->cfg.n_head;
+  p.qpg = c->qpg;
+  p.sm_scale_log2 = (1.0f / sqrtf(static_cast<float>(BP_HEAD_DIM))) * 1.4426950408889634f;
+  *n_splits_out = n_splits;
+  return c->opt_uhpc == 2 ? launch_umma<2>(c, s, p, spp, n_splits) : launch_umma<1>(c, s, p, spp, n_splits);
+}

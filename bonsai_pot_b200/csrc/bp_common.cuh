@@ -29,6 +29,9 @@ struct bp_attn_ctx {
   CUtensorMap map_qs[2];
   CUtensorMap map_d[2];
   bool have_maps;
+  CUtensorMap umap_qs[2];  // tcgen05 decode: 128-token boxes
+  CUtensorMap umap_d[2];
+  bool have_umaps;
   // staging for the *_host entry points
   __half *stage_q, *stage_k, *stage_v, *stage_out, *stage_wq, *stage_wk;
   uint32_t stage_rows;
@@ -37,6 +40,7 @@ struct bp_attn_ctx {
   uint32_t variant;
   uint32_t opt_nw;   // decode: compute warps per CTA (8 or 16)
   uint32_t opt_hpc;  // decode: KV heads per CTA (divides n_kv_head)
+  uint32_t opt_uhpc; // tcgen05 decode: KV heads per CTA (1 or 2)
   uint32_t last_launches;
   int status;  // latched device-lost status, BP_OK otherwise
   bp_error_detail detail;
@@ -68,3 +72,11 @@ cudaError_t bp_launch_prefill(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, co
                               __half* out, uint32_t m, uint32_t* launches);
 uint32_t bp_decode_splits(const bp_attn_ctx* c, uint32_t cur_pos);
 uint32_t bp_decode_max_splits(const bp_attn_ctx* c);
+
+// tcgen05 decode (bp_attn_decode_umma.cu)
+cudaError_t bp_decode_umma_init(bp_attn_ctx* c);
+uint32_t bp_decode_umma_stage_tokens();
+uint32_t bp_decode_umma_splits(const bp_attn_ctx* c, uint32_t cur_pos);
+cudaError_t bp_launch_decode_umma(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, const __half* q, __half* out,
+                                  uint32_t cur_pos, uint32_t* n_splits_out);
+inline bool bp_use_umma(const bp_attn_ctx* c) { return c->variant == 0 && c->qpg == 4 && c->have_umaps; }

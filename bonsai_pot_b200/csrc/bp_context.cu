@@ -144,6 +144,10 @@ static bool rebuild_decode_maps(bp_attn_ctx* c) {
   for (int kind = 0; kind < 2 && c->have_maps; kind++)
     c->have_maps = bp_make_kv_maps(c, kind, bp_decode_stage_tokens(c), inner, inner == 128, &c->map_qs[kind],
                                    &c->map_d[kind]);
+  c->have_umaps = true;
+  for (int kind = 0; kind < 2 && c->have_umaps; kind++)
+    c->have_umaps = bp_make_kv_maps(c, kind, bp_decode_umma_stage_tokens(), 16 * c->opt_uhpc, false,
+                                    &c->umap_qs[kind], &c->umap_d[kind]);
   return c->have_maps;
 }
 
@@ -237,8 +241,10 @@ int bp_attn_create(const bp_attn_config* cfg, bp_attn_ctx** out) {
 
   c->opt_nw = 8;
   c->opt_hpc = cfg->n_kv_head;
+  c->opt_uhpc = cfg->n_kv_head >= 2 ? 2 : 1;
   if (!rebuild_decode_maps(c)) return fail(c, BP_ERR_CUDA, "cuTensorMapEncodeTiled failed for the KV cache");
   BP_CUDA(c, bp_decode_init(c));
+  BP_CUDA(c, bp_decode_umma_init(c));
   BP_CUDA(c, bp_prefill_init(c));
   BP_CUDA(c, cudaStreamCreateWithFlags(&c->host_stream, cudaStreamNonBlocking));
   return BP_OK;
@@ -570,7 +576,7 @@ int bp_rope_table_copy(bp_attn_ctx* c, void* host_f16) {
 
 int bp_set_variant(bp_attn_ctx* c, uint32_t variant) {
   if (!c) return BP_ERR_NULL;
-  if (variant > 2) return fail_config(c, "unknown kernel variant");
+  if (variant > 3) return fail_config(c, "unknown kernel variant");
   c->variant = variant;
   return BP_OK;
 }
@@ -584,6 +590,10 @@ int bp_set_option(bp_attn_ctx* c, const char* name, uint32_t value) {
     if (value == 0 || c->cfg.n_kv_head % value != 0 || (value & (value - 1)) != 0)
       return fail_config(c, "decode_heads_per_cta must be a power of two that divides n_kv_head");
     c->opt_hpc = value;
+  } else if (strcmp(name, "decode_umma_heads_per_cta") == 0) {
+    if ((value != 1 && value != 2) || c->cfg.n_kv_head % value != 0)
+      return fail_config(c, "decode_umma_heads_per_cta must be 1 or 2 and divide n_kv_head");
+    c->opt_uhpc = value;
   } else {
     return fail_config(c, "unknown option");
   }

@@ -185,8 +185,10 @@ void* bp_kv_device_ptr(bp_attn_ctx* ctx, uint32_t kind);       /* whole kv_k / k
 uint64_t bp_kv_buffer_bytes(const bp_attn_ctx* ctx);           /* size of each */
 const void* bp_rope_device_ptr(const bp_attn_ctx* ctx);        /* f16 [max_seq][64][2] */
 int bp_rope_table_copy(bp_attn_ctx* ctx, void* host_f16);      /* host copy of the same */
-/* Selects the kernel family: 0 = production kernels (default), 1 = the plain
- * CUDA-core kernels kept as an on-device cross-check. */
+/* Selects the decode kernel family: 0 = production (tcgen05 int8 UMMA; falls
+ * back to 3 when the context has other than 4 query heads per KV head), 1 = plain
+ * CUDA-core cross-check kernels, 2 = warp-MMA kernel with the conservative int8
+ * expansion, 3 = warp-MMA kernel. */
 int bp_set_variant(bp_attn_ctx* ctx, uint32_t variant);
 /* Tuning knobs of the decode kernel: "decode_warps" (8 or 16 compute warps per
  * CTA) and "decode_heads_per_cta" (KV heads streamed by one CTA; a power of two

@@ -123,7 +123,7 @@ def run_decode(ctx, sh, case, layer, variant=0):
     return host(out)
 
 
-@pytest.mark.parametrize("variant", [0, 1, 2])
+@pytest.mark.parametrize("variant", [0, 1, 2, 3])
 def test_decode_every_small_position(variant):
     """cur_pos 1..72 and the tile edges around 128/256/512: every tail length of
     the 16-token sub-tile and of the split is exercised."""
@@ -177,7 +177,7 @@ def test_decode_long_context(ctx_len, layer):
     exact = O.attn_exact(sh, case["qn"], case["kv_k"], case["kv_v"], layer, 1, ctx_len - 1)[0]
     with make_ctx(sh) as ctx:
         load_cache(ctx, sh, case["kv_k"], case["kv_v"], layer, ctx_len)
-        for variant in (0, 1):
+        for variant in (0, 1, 3):
             got = run_decode(ctx, sh, case, layer, variant)
             ok, max_abs, max_rel = within_tolerance(got, exact)
             assert ok, (variant, max_abs, max_rel)
@@ -204,7 +204,7 @@ def test_decode_on_a_kv_head_shard(n_kv_head):
         for kind, kv in enumerate((case["kv_k"], case["kv_v"])):
             ctx.kv_import(kind, 0, 0, n_past + 1, np.ascontiguousarray(full.d_section(kv, 0)[:n_past + 1, bcols]))
             ctx.kv_import(kind, 0, 1, n_past + 1, np.ascontiguousarray(full.qs_section(kv, 0)[:n_past + 1, cols]))
-        for variant in (0, 1):
+        for variant in (0, 1, 3):
             ctx.set_variant(variant)
             out = torch.zeros(sh.q_dim, dtype=torch.float16, device="cuda")
             ctx.dispatch_attention_decode(0, dev(case["qn"][:, qcols]), out, n_past + 1)
@@ -439,7 +439,13 @@ def test_decode_tuning_options_do_not_change_results(warps, hpc):
         load_cache(ctx, sh, case["kv_k"], case["kv_v"], 1, 3001)
         ctx.set_option("decode_warps", warps)
         ctx.set_option("decode_heads_per_cta", hpc)
+        ctx.set_option("decode_umma_heads_per_cta", 1 if hpc == 1 else 2)
         for cur_pos in (1, 17, 100, 777, 3001):
+            for variant in (0, 3):
+                got = run_decode(ctx, sh, dict(case, cur_pos=cur_pos), 1, variant)
+                exact = O.attn_exact(sh, case["qn"], case["kv_k"], case["kv_v"], 1, 1, cur_pos - 1)[0]
+                ok, max_abs, max_rel = within_tolerance(got, exact)
+                assert ok, (warps, hpc, variant, cur_pos, max_abs, max_rel)
             got = run_decode(ctx, sh, dict(case, cur_pos=cur_pos), 1)
             exact = O.attn_exact(sh, case["qn"], case["kv_k"], case["kv_v"], 1, 1, cur_pos - 1)[0]
             ok, max_abs, max_rel = within_tolerance(got, exact)
