@@ -94,6 +94,7 @@ SIGNATURES = {
     "bp_rope_table_copy": (_int, [_vp, _vp]),
     "bp_set_variant": (_int, [_vp, _u32]),
     "bp_set_option": (_int, [_vp, C.c_char_p, _u32]),
+    "bp_debug_counters": (_int, [_vp, C.POINTER(C.c_uint64)]),
     "bp_last_launch_count": (_u32, [_vp]),
     "bp_decode_num_splits": (_u32, [_vp, _u32]),
     "bp_attn_decode_static_scratch": (_int, [_vp, _vp, _vp, _vp, _vp] + [_u32] * 6),

@@ -162,6 +162,12 @@ class AttnContext:
         """Decode tuning knobs: "decode_warps" (8/16), "decode_heads_per_cta"."""
         self._check(self._lib.bp_set_option(self._h, name.encode(), value))
 
+    def debug_counters(self):
+        """64 cycle counters of the last tcgen05 decode launch (option "debug_counters" must be 1)."""
+        buf = (C.c_uint64 * 64)()
+        self._check(self._lib.bp_debug_counters(self._h, buf))
+        return list(buf)
+
     def last_launch_count(self):
         return self._lib.bp_last_launch_count(self._h)
 

@@ -43,6 +43,7 @@ struct UmmaParams {
   uint32_t* err;
   uint32_t row_base, cur_pos, tps, n_stages, n_head, qpg;
   float sm_scale_log2;
+  unsigned long long* dbg;  // optional cycle counters of CTA (0, 0); null in normal use
 };
 
 template <uint32_t HPC>
@@ -169,12 +170,17 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
   const uint32_t tmem = tmem_base_s;
 
   // A wait that degrades to a no-op once any warp of the CTA has timed out.
-  auto wait = [&](uint64_t* bar, uint32_t parity) {
+  const bool dbg_on = p.dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && lane == 0;
+  long long t_wait[6] = {0, 0, 0, 0, 0, 0};
+  const long long t_start = clock64();
+  auto wait = [&](uint64_t* bar, uint32_t parity, int slot) {
     if (abort_s) return;
+    const long long t0 = dbg_on ? clock64() : 0;
     if (!mbar_wait(smem_u32(bar), parity, WAIT_LIMIT)) {
       abort_s = 1;
       atomicExch(p.err, 3u);
     }
+    if (dbg_on) t_wait[slot] += clock64() - t0;
   };
 
   if (warp == 0) {
@@ -186,7 +192,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
       prefetch_tensormap(&map_vd);
       for (uint32_t it = 0; it < n_iter; it++) {
         const uint32_t s = it % ns, use = it / ns;
-        if (use > 0) wait(&empty_bar[s], (use - 1) & 1);
+        if (use > 0) wait(&empty_bar[s], (use - 1) & 1, 0);
         if (abort_s) break;
         const uint32_t bar = smem_u32(&full_bar[s]);
         const uint32_t stage = smem_base + s * L::STAGE_B;
@@ -204,11 +210,11 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
     // ---------------- UMMA issuer ----------------
     if (lane == 0) {
       constexpr uint32_t IDESC_QK = umma_idesc(2, 1, 1, 0, 0, 128, 16);  // s32 += s8 (K-major) x s8
-      constexpr uint32_t IDESC_PV = umma_idesc(2, 1, 0, 1, 0, 128, 16);  // s32 += s8 (MN-major) x u8
+      constexpr uint32_t IDESC_PV = umma_idesc(2, 1, 0, 1, 0, 128, 64);  // s32 += s8 (MN-major) x u8, 4 blocks x 16 columns
       auto issue_qk = [&](uint32_t j) {
         const uint32_t it = j / HPC, g = j % HPC, buf = j & 1, u = j >> 1, s = it % ns;
-        if (g == 0) wait(&full_bar[s], (it / ns) & 1);
-        if (u > 0) wait(&s_free[buf], (u - 1) & 1);
+        if (g == 0) wait(&full_bar[s], (it / ns) & 1, 0);
+        if (u > 0) wait(&s_free[buf], (u - 1) & 1, 1);
         tc_fence_after();
         const uint32_t ktile = smem_base + s * L::STAGE_B + g * TILE_B;
         const uint32_t qtile = q_tiles + g * 2048;
@@ -222,18 +228,18 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
       for (uint32_t j = 0; j < n_jobs; j++) {
         if (j + 1 < n_jobs) issue_qk(j + 1);
         const uint32_t it = j / HPC, g = j % HPC, buf = j & 1, u = j >> 1, s = it % ns;
-        wait(&p_ready[buf], u & 1);
-        if (u > 0) wait(&o_free[buf], (u - 1) & 1);
+        wait(&p_ready[buf], u & 1, 2);
+        if (u > 0) wait(&o_free[buf], (u - 1) & 1, 3);
         tc_fence_after();
         const uint32_t vtile = smem_base + s * L::STAGE_B + (HPC + g) * TILE_B;
+        // The four blocks' P' tiles are 16 consecutive rows each of one 64-row K-major operand, so one
+        // N = 64 UMMA per 32 tokens serves all of them and the V tile is read once. Only the
+        // diagonal (dims of block b) x (columns of block b) part of the result is used.
+        const uint32_t ptile = p_tiles + buf * 4 * 2048;
 #pragma unroll
-        for (uint32_t b = 0; b < 4; b++) {
-          const uint32_t ptile = p_tiles + (buf * 4 + b) * 2048;
-#pragma unroll
-          for (uint32_t k = 0; k < 4; k++)
-            umma_i8(tmem + 128 + buf * 64 + 16 * b, umma_desc_sw128(vtile + k * 32 * 128, 16, 1024),
-                    umma_desc_sw128(ptile + 32 * k, 16, 1024), IDESC_PV, k);
-        }
+        for (uint32_t k = 0; k < 4; k++)
+          umma_i8(tmem + 128 + buf * 64, umma_desc_sw128(vtile + k * 32 * 128, 16, 1024),
+                  umma_desc_sw128(ptile + 32 * k, 16, 1024), IDESC_PV, k);
         umma_commit(smem_u32(&o_ready[buf]));
         umma_commit(smem_u32(&p_free[buf]));
         if (g == HPC - 1) umma_commit(smem_u32(&empty_bar[s]));
@@ -256,7 +262,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
 #pragma unroll
       for (uint32_t g = 0; g < HPC; g++) {
         const uint32_t j = it * HPC + g, buf = j & 1, u = j >> 1;
-        wait(&s_ready[buf], u & 1);
+        wait(&s_ready[buf], u & 1, 0);
         tc_fence_after();
         uint32_t d[4][8];
 #pragma unroll
@@ -320,8 +326,8 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
         }
         // the P' buffer and the info slot are free once job j-2 has been consumed
         if (u > 0) {
-          wait(&p_free[buf], (u - 1) & 1);
-          wait(&o_free[buf], (u - 1) & 1);
+          wait(&p_free[buf], (u - 1) & 1, 1);
+          wait(&o_free[buf], (u - 1) & 1, 2);
         }
         if (t == 0) {
           *reinterpret_cast<float4*>(&misc->info[buf][0]) = make_float4(corr[0], corr[1], corr[2], corr[3]);
@@ -371,7 +377,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
 #pragma unroll
       for (uint32_t g = 0; g < HPC; g++) {
         const uint32_t j = it * HPC + g, buf = j & 1, u = j >> 1;
-        wait(&o_ready[buf], u & 1);
+        wait(&o_ready[buf], u & 1, 0);
         tc_fence_after();
         uint32_t d[16];
         tmem_ld16(tmem + lane_addr + 128 + buf * 64 + 16 * quad, d);  // this warp's dims are Q8_0 block `quad`
@@ -398,6 +404,13 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
       for (int h = 0; h < 4; h++) o_fin[(g * 4 + h) * BP_HEAD_DIM + dim] = o[g][h];
   }
 
+  if (dbg_on && (warp == 0 || warp == 1 || warp == 2 || warp == 6)) {
+    // per role: total cycles in the main loop, then cycles spent in each kind of wait
+    const uint32_t role = warp == 0 ? 0 : warp == 1 ? 1 : warp == 2 ? 2 : 3;
+    p.dbg[role * 8 + 0] = static_cast<unsigned long long>(clock64() - t_start);
+    for (int i = 0; i < 6; i++) p.dbg[role * 8 + 1 + i] = static_cast<unsigned long long>(t_wait[i]);
+    p.dbg[role * 8 + 7] = n_jobs;
+  }
   tc_fence_before();
   __syncthreads();
   // ---- epilogue: partial (o, m, l) per query head, or the final output ----
@@ -486,6 +499,7 @@ cudaError_t bp_launch_decode_umma(bp_attn_ctx* c, cudaStream_t s, uint32_t layer
   p.n_head = c->cfg.n_head;
   p.qpg = c->qpg;
   p.sm_scale_log2 = (1.0f / sqrtf(static_cast<float>(BP_HEAD_DIM))) * 1.4426950408889634f;
+  p.dbg = c->dbg_on ? c->dbg_dev : nullptr;
   *n_splits_out = n_splits;
   return c->opt_uhpc == 2 ? launch_umma<2>(c, s, p, spp, n_splits) : launch_umma<1>(c, s, p, spp, n_splits);
 }

@@ -24,6 +24,8 @@ struct bp_attn_ctx {
   uint32_t* err_host; // pinned, mapped: kernels store a non-zero code here when a bounded wait gives up
   uint32_t* err_dev;  // device alias of err_host
   uint32_t max_splits;
+  unsigned long long* dbg_dev;  // 64 cycle counters written by a kernel when dbg_on
+  bool dbg_on;
   // TMA descriptors over the cache, built once: quants as (128 B, kv heads,
   // rows), scales as (row bytes, rows); rows run over all layers.
   CUtensorMap map_qs[2];

@@ -235,6 +235,8 @@ int bp_attn_create(const bp_attn_config* cfg, bp_attn_ctx** out) {
   BP_CUDA(c, cudaMalloc(&c->partials, static_cast<size_t>(c->max_splits) * cfg->n_head * BP_PART_STRIDE * sizeof(float)));
   BP_CUDA(c, cudaMalloc(&c->tickets, (cfg->n_layer + 1) * sizeof(uint32_t)));
   BP_CUDA(c, cudaMemset(c->tickets, 0, (cfg->n_layer + 1) * sizeof(uint32_t)));
+  BP_CUDA(c, cudaMalloc(&c->dbg_dev, 64 * sizeof(unsigned long long)));
+  BP_CUDA(c, cudaMemset(c->dbg_dev, 0, 64 * sizeof(unsigned long long)));
   BP_CUDA(c, cudaHostAlloc(&c->err_host, sizeof(uint32_t), cudaHostAllocMapped));
   *c->err_host = 0;
   BP_CUDA(c, cudaHostGetDevicePointer(&c->err_dev, c->err_host, 0));
@@ -258,6 +260,7 @@ void bp_attn_destroy(bp_attn_ctx* c) {
   cudaFree(c->rope);
   cudaFree(c->partials);
   cudaFree(c->tickets);
+  cudaFree(c->dbg_dev);
   if (c->err_host) cudaFreeHost(c->err_host);
   cudaFree(c->stage_q);
   cudaFree(c->stage_k);
@@ -590,6 +593,9 @@ int bp_set_option(bp_attn_ctx* c, const char* name, uint32_t value) {
     if (value == 0 || c->cfg.n_kv_head % value != 0 || (value & (value - 1)) != 0)
       return fail_config(c, "decode_heads_per_cta must be a power of two that divides n_kv_head");
     c->opt_hpc = value;
+  } else if (strcmp(name, "debug_counters") == 0) {
+    c->dbg_on = value != 0;
+    return BP_OK;
   } else if (strcmp(name, "decode_umma_heads_per_cta") == 0) {
     if ((value != 1 && value != 2) || c->cfg.n_kv_head % value != 0)
       return fail_config(c, "decode_umma_heads_per_cta must be 1 or 2 and divide n_kv_head");
@@ -600,6 +606,14 @@ int bp_set_option(bp_attn_ctx* c, const char* name, uint32_t value) {
   if (c->opt_hpc > c->opt_nw) c->opt_hpc = c->opt_nw;
   if (bind_device(c) != BP_OK) return BP_ERR_CUDA;
   if (!rebuild_decode_maps(c)) return fail(c, BP_ERR_CUDA, "cuTensorMapEncodeTiled failed for the KV cache");
+  return BP_OK;
+}
+
+int bp_debug_counters(bp_attn_ctx* c, uint64_t* out64) {
+  if (int s = enter(c)) return s;
+  if (!out64) return fail(c, BP_ERR_NULL, "null pointer argument");
+  if (int s = bind_device(c)) return s;
+  BP_CUDA(c, cudaMemcpy(out64, c->dbg_dev, 64 * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
   return BP_OK;
 }
 

@@ -194,6 +194,11 @@ int bp_set_variant(bp_attn_ctx* ctx, uint32_t variant);
  * CTA) and "decode_heads_per_cta" (KV heads streamed by one CTA; a power of two
  * dividing n_kv_head). Results do not depend on them beyond rounding. */
 int bp_set_option(bp_attn_ctx* ctx, const char* name, uint32_t value);
+/* Development aid: with the option "debug_counters" set to 1 the tcgen05 decode
+ * kernel's first CTA records, per warp role (producer, UMMA issuer, softmax,
+ * accumulate), its cycles in the main loop and in each kind of wait; this call
+ * synchronises and copies the 64 counters (8 per role) to the host. */
+int bp_debug_counters(bp_attn_ctx* ctx, uint64_t* out64);
 /* Number of kernels the last compute call launched. */
 uint32_t bp_last_launch_count(const bp_attn_ctx* ctx);
 /* Number of split-KV partitions `bp_attn_decode` uses at `cur_pos`. */
