@@ -14,8 +14,8 @@
 // The integer products are exact; Q is quantised to 15 bits per block of 32 dims
 // (finer than its f16 input) and P' to 23 bits of the stage's largest V scale.
 //
-// Roles (320 threads): warp 0 TMA producer, warp 1 UMMA issuer + TMEM owner,
-// warps 2-5 softmax (thread = token row = TMEM lane), warps 6-9 accumulate
+// Roles (800 threads): warp 0 TMA producer, warps 1-2 QK issuers (warp 1 owns TMEM), warps 3-4 PV
+// issuers, warps 5-20 four softmax groups (thread = token row = TMEM lane), warps 21-24 accumulate
 // (thread = head dim = TMEM lane). Every mbarrier wait is bounded; after a
 // timeout the CTA stops waiting, drains and frees TMEM, and reports through the
 // error word.
@@ -31,8 +31,11 @@ constexpr float NEG_BIG = -1e30f;
 constexpr uint32_t UT = 128;                 // tokens per stage = UMMA M
 constexpr uint32_t TILE_B = UT * 128;        // int8 tile of one head and stage: 16 KB
 constexpr uint32_t U_MAX_STAGES = 6;
-constexpr uint32_t U_THREADS = 320;
-constexpr uint32_t TMEM_COLS = 256;          // D1: 2 x 64 columns, D2: 2 x 64 columns
+constexpr uint32_t NGRP = 4;                     // softmax groups working on different jobs in parallel
+constexpr uint32_t NISS = 2;                     // UMMA issuer warps per kind (QK, PV)
+constexpr uint32_t U_FIRST_SM_WARP = 1 + 2 * NISS;  // warp 0 producer, then the issuers
+constexpr uint32_t U_THREADS = (U_FIRST_SM_WARP + 4 * NGRP + 4) * 32;
+constexpr uint32_t TMEM_COLS = 512;          // per softmax group: D1 (64 columns) and D2 (64 columns)
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 constexpr uint32_t U_SMEM_BUDGET = 226 * 1024;  // dynamic shared memory; the static part needs the rest of 227 KB
 
@@ -51,18 +54,18 @@ struct ULayout {
   static constexpr uint32_t SCALE_B = UT * HPC * 16;                   // scale rows of one stage (K or V)
   static constexpr uint32_t STAGE_B = 2 * HPC * TILE_B + 2 * SCALE_B;  // 73,728 B for HPC = 2
   static constexpr uint32_t Q_B = HPC * 2048;                          // Q^T tiles: 16 rows x 128 B per head
-  static constexpr uint32_t P_B = 2 * 4 * 2048;                        // P'^T tiles: 2 buffers x 4 blocks
-  static constexpr uint32_t MISC_B = 2048;
+  static constexpr uint32_t P_B = NGRP * 4 * 2048;                     // P'^T tiles: one per group x 4 blocks
+  static constexpr uint32_t MISC_B = 4096;
   static constexpr uint32_t tail() { return Q_B + P_B + MISC_B; }
   static constexpr uint32_t total(uint32_t stages) { return stages * STAGE_B + tail() + 1024; }
 };
 
 struct Misc {            // small shared state, lives in the MISC_B region
   float sq[8][4][4];     // Q block scales [head][query head][block] (pre-multiplied by the softmax scale)
-  int xchg[2][4][8];     // per-warp maxima of a job: 4 score maxima, 4 V-scale maxima
-  float info[2][8];      // per job buffer: corr[4], dequantisation factor of P' per block [4]
-  float lsum[8][4][4];   // final l per (head, query head, warp)
-  float mfin[8][4];
+  int xchg[NGRP][2][4][8];  // [softmax group][job parity][warp]: 4 score maxima, 4 V-scale maxima
+  float info[NGRP][8];      // per group: corr[4], dequantisation factor of P' per block [4]
+  float lsum[NGRP][4][4];   // final l per (softmax group, query head, warp)
+  float mfin[NGRP][4];
 };
 
 __device__ __forceinline__ float s32_to_f32(uint32_t x) {  // exact for |x| < 2^22
@@ -82,13 +85,19 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
   using L = ULayout<HPC>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[U_MAX_STAGES], empty_bar[U_MAX_STAGES];
-  __shared__ __align__(8) uint64_t s_ready[2], s_free[2], p_ready[2], p_free[2], o_ready[2], o_free[2];
+  __shared__ __align__(8) uint64_t s_ready[4], s_free[4], p_ready[4], p_free[4], o_ready[4], o_free[4];
   __shared__ uint32_t tmem_base_s;
   __shared__ volatile uint32_t abort_s;
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  unsigned long long t_entry_ns = 0;
+  const long long t_entry = clock64();
+  if (p.dbg != nullptr && threadIdx.x == 0) {
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_entry_ns));
+    atomicMin(&p.dbg[32], t_entry_ns);
+  }
   const uint32_t ns = p.n_stages;
   const uint32_t g0 = blockIdx.y * HPC;
   const uint32_t split = blockIdx.x, n_splits = gridDim.x;
@@ -105,9 +114,9 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
   if (threadIdx.x == 0) {
     for (uint32_t s = 0; s < ns; s++) {
       mbar_init(smem_u32(&full_bar[s]), 1);
-      mbar_init(smem_u32(&empty_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), HPC);  // one tcgen05.commit per job of the stage
     }
-    for (int b = 0; b < 2; b++) {
+    for (int b = 0; b < 4; b++) {
       mbar_init(smem_u32(&s_ready[b]), 1);
       mbar_init(smem_u32(&s_free[b]), 4);
       mbar_init(smem_u32(&p_ready[b]), 4);
@@ -169,18 +178,22 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
   tc_fence_after();
   const uint32_t tmem = tmem_base_s;
 
-  // A wait that degrades to a no-op once any warp of the CTA has timed out.
+  // Jobs: job j = (stage it, head g) with j = it * HPC + g. NGRP softmax groups
+  // work in parallel; job j belongs to group w = j % NGRP, so a group always
+  // sees the same head (w % HPC). Each group owns one D1, one D2 and one P'
+  // buffer; its k-th job (k = j / NGRP) completes phase k of its barriers.
   const bool dbg_on = p.dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && lane == 0;
-  long long t_wait[6] = {0, 0, 0, 0, 0, 0};
+  long long t_w0 = 0, t_w1 = 0, t_w2 = 0;
   const long long t_start = clock64();
-  auto wait = [&](uint64_t* bar, uint32_t parity, int slot) {
+  // A wait that degrades to a no-op once any warp of the CTA has timed out.
+  auto wait = [&](uint64_t* bar, uint32_t parity, long long& acct) {
     if (abort_s) return;
     const long long t0 = dbg_on ? clock64() : 0;
     if (!mbar_wait(smem_u32(bar), parity, WAIT_LIMIT)) {
       abort_s = 1;
       atomicExch(p.err, 3u);
     }
-    if (dbg_on) t_wait[slot] += clock64() - t0;
+    if (dbg_on) acct += clock64() - t0;
   };
 
   if (warp == 0) {
@@ -190,9 +203,9 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
       prefetch_tensormap(&map_vq);
       prefetch_tensormap(&map_kd);
       prefetch_tensormap(&map_vd);
+      uint32_t s = 0, use = 0;
       for (uint32_t it = 0; it < n_iter; it++) {
-        const uint32_t s = it % ns, use = it / ns;
-        if (use > 0) wait(&empty_bar[s], (use - 1) & 1, 0);
+        if (use > 0) wait(&empty_bar[s], (use - 1) & 1, t_w0);
         if (abort_s) break;
         const uint32_t bar = smem_u32(&full_bar[s]);
         const uint32_t stage = smem_base + s * L::STAGE_B;
@@ -204,213 +217,221 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
           tma_load_3d(stage + g * TILE_B, &map_kq, bar, 0, static_cast<int>(g0 + g), row);
           tma_load_3d(stage + (HPC + g) * TILE_B, &map_vq, bar, 0, static_cast<int>(g0 + g), row);
         }
+        if (++s == ns) { s = 0; use++; }
       }
     }
-  } else if (warp == 1) {
-    // ---------------- UMMA issuer ----------------
+  } else if (warp < 1 + NISS) {
+    // ---------------- QK issuers: S^T[token][(block, byte row, head)] = K tile x Q^T ----------------
+    // One UMMA per Q8_0 block (K = 32 dims). Issuer q takes the jobs j = q (mod NISS); issuing is
+    // serial scalar work (about 100 instructions per job), hence more than one issuer.
     if (lane == 0) {
-      constexpr uint32_t IDESC_QK = umma_idesc(2, 1, 1, 0, 0, 128, 16);  // s32 += s8 (K-major) x s8
-      constexpr uint32_t IDESC_PV = umma_idesc(2, 1, 0, 1, 0, 128, 64);  // s32 += s8 (MN-major) x u8, 4 blocks x 16 columns
-      auto issue_qk = [&](uint32_t j) {
-        const uint32_t it = j / HPC, g = j % HPC, buf = j & 1, u = j >> 1, s = it % ns;
-        if (g == 0) wait(&full_bar[s], (it / ns) & 1, 0);
-        if (u > 0) wait(&s_free[buf], (u - 1) & 1, 1);
+      constexpr uint32_t IDESC_QK = umma_idesc(2, 1, 1, 0, 0, 128, 16);  // s32 = s8 (K-major) x s8
+      const uint64_t dbase = umma_desc_sw128(0, 16, 1024);               // + (shared address >> 4)
+      const uint32_t q = warp - 1;
+      for (uint32_t j = q; j < n_jobs; j += NISS) {
+        const uint32_t it = j / HPC, g = j % HPC, bi = j % NGRP, k = j / NGRP, s = it % ns, use = it / ns;
+        wait(&full_bar[s], use & 1, t_w0);
+        if (k > 0) wait(&s_free[bi], (k - 1) & 1, t_w1);
         tc_fence_after();
-        const uint32_t ktile = smem_base + s * L::STAGE_B + g * TILE_B;
-        const uint32_t qtile = q_tiles + g * 2048;
+        const uint64_t ka = dbase + ((smem_base + s * L::STAGE_B + g * TILE_B) >> 4);
+        const uint64_t qb = dbase + ((q_tiles + g * 2048) >> 4);
 #pragma unroll
-        for (uint32_t b = 0; b < 4; b++)
-          umma_i8(tmem + buf * 64 + 16 * b, umma_desc_sw128(ktile + 32 * b, 16, 1024),
-                  umma_desc_sw128(qtile + 32 * b, 16, 1024), IDESC_QK, 0u);
-        umma_commit(smem_u32(&s_ready[buf]));
-      };
-      if (n_jobs > 0) issue_qk(0);
-      for (uint32_t j = 0; j < n_jobs; j++) {
-        if (j + 1 < n_jobs) issue_qk(j + 1);
-        const uint32_t it = j / HPC, g = j % HPC, buf = j & 1, u = j >> 1, s = it % ns;
-        wait(&p_ready[buf], u & 1, 2);
-        if (u > 0) wait(&o_free[buf], (u - 1) & 1, 3);
-        tc_fence_after();
-        const uint32_t vtile = smem_base + s * L::STAGE_B + (HPC + g) * TILE_B;
-        // The four blocks' P' tiles are 16 consecutive rows each of one 64-row K-major operand, so one
-        // N = 64 UMMA per 32 tokens serves all of them and the V tile is read once. Only the
-        // diagonal (dims of block b) x (columns of block b) part of the result is used.
-        const uint32_t ptile = p_tiles + buf * 4 * 2048;
-#pragma unroll
-        for (uint32_t k = 0; k < 4; k++)
-          umma_i8(tmem + 128 + buf * 64, umma_desc_sw128(vtile + k * 32 * 128, 16, 1024),
-                  umma_desc_sw128(ptile + 32 * k, 16, 1024), IDESC_PV, k);
-        umma_commit(smem_u32(&o_ready[buf]));
-        umma_commit(smem_u32(&p_free[buf]));
-        if (g == HPC - 1) umma_commit(smem_u32(&empty_bar[s]));
+        for (uint32_t b = 0; b < 4; b++) umma_i8(tmem + bi * 64 + 16 * b, ka + 2 * b, qb + 2 * b, IDESC_QK, 0u);
+        umma_commit(smem_u32(&s_ready[bi]));
       }
     }
-  } else if (warp < 6) {
-    // ---------------- softmax: thread = token row ----------------
+  } else if (warp < 1 + 2 * NISS) {
+    // ---------------- PV issuers: O^T[dim][(block, byte row, head)] (+)= V tile x P'^T ----------------
+    // The four blocks' P' tiles are 16 consecutive rows each of one 64-row K-major operand, so one
+    // N = 64 UMMA per 32 tokens serves all of them and the V tile is read once; only the
+    // (dims of block b) x (columns of block b) part of the result is used.
+    if (lane == 0) {
+      constexpr uint32_t IDESC_PV = umma_idesc(2, 1, 0, 1, 0, 128, 64);  // s32 += s8 (MN-major) x u8
+      const uint64_t dbase = umma_desc_sw128(0, 16, 1024);
+      const uint32_t q = warp - 1 - NISS;
+      for (uint32_t j = q; j < n_jobs; j += NISS) {
+        const uint32_t it = j / HPC, g = j % HPC, bi = j % NGRP, k = j / NGRP, s = it % ns;
+        wait(&p_ready[bi], k & 1, t_w0);
+        if (k > 0) wait(&o_free[bi], (k - 1) & 1, t_w1);
+        tc_fence_after();
+        const uint64_t va = dbase + ((smem_base + s * L::STAGE_B + (HPC + g) * TILE_B) >> 4);
+        const uint64_t pb = dbase + ((p_tiles + bi * 4 * 2048) >> 4);
+#pragma unroll
+        for (uint32_t kk = 0; kk < 4; kk++)
+          umma_i8(tmem + NGRP * 64 + bi * 64, va + kk * (32 * 128 >> 4), pb + 2 * kk, IDESC_PV, kk);
+        umma_commit(smem_u32(&o_ready[bi]));
+        umma_commit(smem_u32(&p_free[bi]));
+        umma_commit(smem_u32(&empty_bar[s]));  // one arrival per job of the stage
+      }
+    }
+  }
+  else if (warp < U_FIRST_SM_WARP + 4 * NGRP) {
+    // ---------------- softmax group w: thread = token row ----------------
+    const uint32_t w = (warp - U_FIRST_SM_WARP) >> 2;  // four consecutive warps per group
     const uint32_t quad = warp & 3, t = quad * 32 + lane;
     const uint32_t lane_addr = (quad * 32) << 16;
-    float m_run[HPC][4], l_part[HPC][4];
+    float m_run[4], l_part[4];
 #pragma unroll
-    for (uint32_t g = 0; g < HPC; g++)
-#pragma unroll
-      for (int h = 0; h < 4; h++) { m_run[g][h] = NEG_BIG; l_part[g][h] = 0.f; }
+    for (int h = 0; h < 4; h++) { m_run[h] = NEG_BIG; l_part[h] = 0.f; }
 
-    for (uint32_t it = 0; it < n_iter; it++) {
-      const uint32_t s = it % ns;
-      const uint8_t* stage = smem_gen + s * L::STAGE_B;
+    for (uint32_t j = w; j < n_jobs; j += NGRP) {
+      const uint32_t it = j / HPC, g = j % HPC, bi = w, k = j / NGRP;
+      const uint8_t* stage = smem_gen + (it % ns) * L::STAGE_B;
       const bool valid = tok_begin + it * UT + t < tok_end;
+      wait(&s_ready[bi], k & 1, t_w0);
+      tc_fence_after();
+      uint32_t d[4][8];
 #pragma unroll
-      for (uint32_t g = 0; g < HPC; g++) {
-        const uint32_t j = it * HPC + g, buf = j & 1, u = j >> 1;
-        wait(&s_ready[buf], u & 1, 0);
-        tc_fence_after();
-        uint32_t d[4][8];
-#pragma unroll
-        for (uint32_t b = 0; b < 4; b++) tmem_ld8(tmem + lane_addr + buf * 64 + 16 * b, d[b]);
-        tmem_ld_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&s_free[buf]));
+      for (uint32_t b = 0; b < 4; b++) tmem_ld8(tmem + lane_addr + bi * 64 + 16 * b, d[b]);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&s_free[bi]));
 
-        const float4 sk = *reinterpret_cast<const float4*>(stage + 2 * HPC * TILE_B + (t * HPC + g) * 16);
-        float4 sv = *reinterpret_cast<const float4*>(stage + 2 * HPC * TILE_B + L::SCALE_B + (t * HPC + g) * 16);
-        const float skb[4] = {sk.x, sk.y, sk.z, sk.w};
-        float sc[4];
-#pragma unroll
-        for (int h = 0; h < 4; h++) {
-          float acc = 0.f;
-#pragma unroll
-          for (int b = 0; b < 4; b++) {
-            const float dot = fmaf(s32_to_f32(d[b][h]), 128.0f, s32_to_f32(d[b][4 + h]));
-            acc = fmaf(dot, skb[b] * misc->sq[g][h][b], acc);
-          }
-          sc[h] = valid ? acc : NEG_BIG;
-        }
-        if (!valid) sv = make_float4(0.f, 0.f, 0.f, 0.f);
-        const float svb[4] = {sv.x, sv.y, sv.z, sv.w};
-
-        // maxima over the 128 tokens of the stage: 4 score maxima, 4 V-scale maxima
-        int red[8];
-#pragma unroll
-        for (int h = 0; h < 4; h++) red[h] = __reduce_max_sync(FULL, f32_order(sc[h]));
-#pragma unroll
-        for (int b = 0; b < 4; b++) red[4 + b] = static_cast<int>(__reduce_max_sync(FULL, __float_as_uint(svb[b])));
-        if (lane == 0) {
-          int4* dst = reinterpret_cast<int4*>(misc->xchg[j & 1][quad]);
-          dst[0] = make_int4(red[0], red[1], red[2], red[3]);
-          dst[1] = make_int4(red[4], red[5], red[6], red[7]);
-        }
-        named_bar_sync(1, 128);
-#pragma unroll
-        for (int w = 0; w < 4; w++) {
-          const int4* src = reinterpret_cast<const int4*>(misc->xchg[j & 1][w]);
-          const int4 a = src[0], c = src[1];
-          red[0] = max(red[0], a.x); red[1] = max(red[1], a.y); red[2] = max(red[2], a.z); red[3] = max(red[3], a.w);
-          red[4] = max(red[4], c.x); red[5] = max(red[5], c.y); red[6] = max(red[6], c.z); red[7] = max(red[7], c.w);
-        }
-        float pj[4], corr[4];
-#pragma unroll
-        for (int h = 0; h < 4; h++) {
-          const float m_new = fmaxf(m_run[g][h], f32_unorder(red[h]));
-          corr[h] = ex2(m_run[g][h] - m_new);
-          pj[h] = ex2(sc[h] - m_new);
-          l_part[g][h] = l_part[g][h] * corr[h] + pj[h];
-          m_run[g][h] = m_new;
-        }
-        float qscale[4], deq[4];
-#pragma unroll
-        for (int b = 0; b < 4; b++) {
-          const float vmax = __int_as_float(red[4 + b]);
-          qscale[b] = vmax > 0.f ? 8388607.0f / vmax : 0.f;
-          deq[b] = vmax * (1.0f / 8388607.0f);
-        }
-        // the P' buffer and the info slot are free once job j-2 has been consumed
-        if (u > 0) {
-          wait(&p_free[buf], (u - 1) & 1, 1);
-          wait(&o_free[buf], (u - 1) & 1, 2);
-        }
-        if (t == 0) {
-          *reinterpret_cast<float4*>(&misc->info[buf][0]) = make_float4(corr[0], corr[1], corr[2], corr[3]);
-          *reinterpret_cast<float4*>(&misc->info[buf][4]) = make_float4(deq[0], deq[1], deq[2], deq[3]);
-        }
-        // P'[h][b] = p[h] * sV[b] as a 23-bit integer: the low three bytes of (x * qscale + 2^23)
-        uint8_t* pt = smem_gen + ns * L::STAGE_B + L::Q_B + buf * 4 * 2048;
-        // byte rows of block b's tile: hi -> row h, mid -> row 4 + h, lo -> row 8 + h;
-        // this token's column inside a swizzled row n is t ^ ((n & 7) << 4)
-#pragma unroll
-        for (int b = 0; b < 4; b++) {
-          uint8_t* tile = pt + b * 2048;
-#pragma unroll
-          for (int h = 0; h < 4; h++) {
-            const uint32_t bits = __float_as_uint(fmaf(pj[h] * svb[b], qscale[b], 8388608.0f));
-            tile[h * 128 + (t ^ (h << 4))] = static_cast<uint8_t>(bits >> 16);
-            tile[(4 + h) * 128 + (t ^ ((4 + h) << 4))] = static_cast<uint8_t>(bits >> 8);
-            tile[(8 + h) * 128 + (t ^ (h << 4))] = static_cast<uint8_t>(bits);
-          }
-        }
-        fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&p_ready[buf]));
-      }
-    }
-    // ---- l of every (head, query head): sum over the 128 token rows ----
-#pragma unroll
-    for (uint32_t g = 0; g < HPC; g++)
+      const float4 sk = *reinterpret_cast<const float4*>(stage + 2 * HPC * TILE_B + (t * HPC + g) * 16);
+      float4 sv = *reinterpret_cast<const float4*>(stage + 2 * HPC * TILE_B + L::SCALE_B + (t * HPC + g) * 16);
+      const float skb[4] = {sk.x, sk.y, sk.z, sk.w};
+      float sc[4];
 #pragma unroll
       for (int h = 0; h < 4; h++) {
-        float l = l_part[g][h];
+        const float4 sq4 = *reinterpret_cast<const float4*>(&misc->sq[g][h][0]);
+        const float sqb[4] = {sq4.x, sq4.y, sq4.z, sq4.w};
+        float acc = 0.f;
 #pragma unroll
-        for (int off = 16; off >= 1; off >>= 1) l += __shfl_xor_sync(FULL, l, off);
-        if (lane == 0) misc->lsum[g][h][quad] = l;
-        if (t == 0) misc->mfin[g][h] = m_run[g][h];
+        for (int b = 0; b < 4; b++) {
+          const float dot = fmaf(s32_to_f32(d[b][h]), 128.0f, s32_to_f32(d[b][4 + h]));
+          acc = fmaf(dot, skb[b] * sqb[b], acc);
+        }
+        sc[h] = valid ? acc : NEG_BIG;
       }
+      if (!valid) sv = make_float4(0.f, 0.f, 0.f, 0.f);
+      const float svb[4] = {sv.x, sv.y, sv.z, sv.w};
+
+      // maxima over the 128 tokens of the stage: 4 score maxima, 4 V-scale maxima
+      int red[8];
+#pragma unroll
+      for (int h = 0; h < 4; h++) red[h] = __reduce_max_sync(FULL, f32_order(sc[h]));
+#pragma unroll
+      for (int b = 0; b < 4; b++) red[4 + b] = static_cast<int>(__reduce_max_sync(FULL, __float_as_uint(svb[b])));
+      if (lane == 0) {
+        int4* dst = reinterpret_cast<int4*>(misc->xchg[w][k & 1][quad]);
+        dst[0] = make_int4(red[0], red[1], red[2], red[3]);
+        dst[1] = make_int4(red[4], red[5], red[6], red[7]);
+      }
+      named_bar_sync(1 + w, 128);
+#pragma unroll
+      for (int ww = 0; ww < 4; ww++) {
+        const int4* src = reinterpret_cast<const int4*>(misc->xchg[w][k & 1][ww]);
+        const int4 a = src[0], c = src[1];
+        red[0] = max(red[0], a.x); red[1] = max(red[1], a.y); red[2] = max(red[2], a.z); red[3] = max(red[3], a.w);
+        red[4] = max(red[4], c.x); red[5] = max(red[5], c.y); red[6] = max(red[6], c.z); red[7] = max(red[7], c.w);
+      }
+      float pj[4], corr[4];
+#pragma unroll
+      for (int h = 0; h < 4; h++) {
+        const float m_new = fmaxf(m_run[h], f32_unorder(red[h]));
+        corr[h] = ex2(m_run[h] - m_new);
+        pj[h] = ex2(sc[h] - m_new);
+        l_part[h] = l_part[h] * corr[h] + pj[h];
+        m_run[h] = m_new;
+      }
+      float qscale[4], deq[4];
+#pragma unroll
+      for (int b = 0; b < 4; b++) {
+        const float vmax = __int_as_float(red[4 + b]);
+        qscale[b] = vmax > 0.f ? 8388607.0f / vmax : 0.f;
+        deq[b] = vmax * (1.0f / 8388607.0f);
+      }
+      // the group's P' buffer and info slot are free once its previous job has been consumed
+      if (k > 0) {
+        wait(&p_free[bi], (k - 1) & 1, t_w1);
+        wait(&o_free[bi], (k - 1) & 1, t_w2);
+      }
+      if (t == 0) {
+        *reinterpret_cast<float4*>(&misc->info[bi][0]) = make_float4(corr[0], corr[1], corr[2], corr[3]);
+        *reinterpret_cast<float4*>(&misc->info[bi][4]) = make_float4(deq[0], deq[1], deq[2], deq[3]);
+      }
+      // P'[h][b] = p[h] * sV[b] as a 23-bit integer: the low three bytes of (x * qscale + 2^23).
+      // Byte rows of block b's tile: hi -> row h, mid -> row 4 + h, lo -> row 8 + h; this token's
+      // column inside a swizzled row n is t ^ ((n & 7) << 4).
+      uint8_t* pt = smem_gen + ns * L::STAGE_B + L::Q_B + bi * 4 * 2048;
+#pragma unroll
+      for (int b = 0; b < 4; b++) {
+        uint8_t* tile = pt + b * 2048;
+#pragma unroll
+        for (int h = 0; h < 4; h++) {
+          const uint32_t bits = __float_as_uint(fmaf(pj[h] * svb[b], qscale[b], 8388608.0f));
+          tile[h * 128 + (t ^ (h << 4))] = static_cast<uint8_t>(bits >> 16);
+          tile[(4 + h) * 128 + (t ^ ((4 + h) << 4))] = static_cast<uint8_t>(bits >> 8);
+          tile[(8 + h) * 128 + (t ^ (h << 4))] = static_cast<uint8_t>(bits);
+        }
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&p_ready[bi]));
+    }
+    // ---- l of every query head of this group: sum over the 128 token rows ----
+#pragma unroll
+    for (int h = 0; h < 4; h++) {
+      float l = l_part[h];
+#pragma unroll
+      for (int off = 16; off >= 1; off >>= 1) l += __shfl_xor_sync(FULL, l, off);
+      if (lane == 0) misc->lsum[w][h][quad] = l;
+      if (t == 0) misc->mfin[w][h] = m_run[h];
+    }
   } else {
     // ---------------- accumulate: thread = head dim ----------------
     const uint32_t quad = warp & 3, dim = quad * 32 + lane;
     const uint32_t lane_addr = (quad * 32) << 16;
-    float o[HPC][4];
+    float o[NGRP][4];
 #pragma unroll
-    for (uint32_t g = 0; g < HPC; g++)
+    for (uint32_t w = 0; w < NGRP; w++)
 #pragma unroll
-      for (int h = 0; h < 4; h++) o[g][h] = 0.f;
-    for (uint32_t it = 0; it < n_iter; it++) {
+      for (int h = 0; h < 4; h++) o[w][h] = 0.f;
+    for (uint32_t j0 = 0; j0 < n_jobs; j0 += NGRP) {
 #pragma unroll
-      for (uint32_t g = 0; g < HPC; g++) {
-        const uint32_t j = it * HPC + g, buf = j & 1, u = j >> 1;
-        wait(&o_ready[buf], u & 1, 0);
-        tc_fence_after();
-        uint32_t d[16];
-        tmem_ld16(tmem + lane_addr + 128 + buf * 64 + 16 * quad, d);  // this warp's dims are Q8_0 block `quad`
-        tmem_ld_wait();
-        const float4 corr = *reinterpret_cast<const float4*>(&misc->info[buf][0]);
-        const float deq = misc->info[buf][4 + quad];
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&o_free[buf]));
-        const float cr[4] = {corr.x, corr.y, corr.z, corr.w};
+      for (uint32_t w = 0; w < NGRP; w++) {
+        const uint32_t j = j0 + w;
+        if (j < n_jobs) {
+          const uint32_t bi = w, k = j / NGRP;
+          wait(&o_ready[bi], k & 1, t_w0);
+          tc_fence_after();
+          uint32_t d[16];
+          tmem_ld16(tmem + lane_addr + NGRP * 64 + bi * 64 + 16 * quad, d);  // this warp's dims are Q8_0 block `quad`
+          tmem_ld_wait();
+          const float4 corr = *reinterpret_cast<const float4*>(&misc->info[bi][0]);
+          const float deq = misc->info[bi][4 + quad];
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&o_free[bi]));
+          const float cr[4] = {corr.x, corr.y, corr.z, corr.w};
 #pragma unroll
-        for (int h = 0; h < 4; h++) {
-          float v = fmaf(s32_to_f32(d[h]), 65536.0f, fmaf(s32_to_f32(d[4 + h]), 256.0f, s32_to_f32(d[8 + h])));
-          o[g][h] = fmaf(o[g][h], cr[h], v * deq);
+          for (int h = 0; h < 4; h++) {
+            const float v = fmaf(s32_to_f32(d[h]), 65536.0f, fmaf(s32_to_f32(d[4 + h]), 256.0f, s32_to_f32(d[8 + h])));
+            o[w][h] = fmaf(o[w][h], cr[h], v * deq);
+          }
         }
       }
     }
-    // stash O for the epilogue: o_fin[g][h][dim]
-    float* o_fin = reinterpret_cast<float*>(smem_gen);  // stage 0 is free by now (all jobs consumed)
+    // stash O for the epilogue: o_fin[group][h][dim]; the stage ring is idle by now
+    float* o_fin = reinterpret_cast<float*>(smem_gen);
     __syncwarp();
 #pragma unroll
-    for (uint32_t g = 0; g < HPC; g++)
+    for (uint32_t w = 0; w < NGRP; w++)
 #pragma unroll
-      for (int h = 0; h < 4; h++) o_fin[(g * 4 + h) * BP_HEAD_DIM + dim] = o[g][h];
+      for (int h = 0; h < 4; h++) o_fin[(w * 4 + h) * BP_HEAD_DIM + dim] = o[w][h];
   }
 
-  if (dbg_on && (warp == 0 || warp == 1 || warp == 2 || warp == 6)) {
-    // per role: total cycles in the main loop, then cycles spent in each kind of wait
-    const uint32_t role = warp == 0 ? 0 : warp == 1 ? 1 : warp == 2 ? 2 : 3;
+  if (dbg_on && (warp == 0 || warp == 1 || warp == 1 + NISS || warp == U_FIRST_SM_WARP)) {
+    // per role: cycles in the main loop, then cycles in each kind of wait
+    const uint32_t role = warp == 0 ? 0 : warp == 1 ? 1 : warp == 1 + NISS ? 2 : 3;
     p.dbg[role * 8 + 0] = static_cast<unsigned long long>(clock64() - t_start);
-    for (int i = 0; i < 6; i++) p.dbg[role * 8 + 1 + i] = static_cast<unsigned long long>(t_wait[i]);
+    p.dbg[role * 8 + 1] = static_cast<unsigned long long>(t_w0);
+    p.dbg[role * 8 + 2] = static_cast<unsigned long long>(t_w1);
+    p.dbg[role * 8 + 3] = static_cast<unsigned long long>(t_w2);
     p.dbg[role * 8 + 7] = n_jobs;
   }
+  const long long t_loop_end = clock64();
   tc_fence_before();
   __syncthreads();
   // ---- epilogue: partial (o, m, l) per query head, or the final output ----
@@ -420,20 +441,36 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
     for (uint32_t idx = threadIdx.x; idx < total; idx += U_THREADS) {
       const uint32_t hl = idx >> 7, d = idx & 127;
       const uint32_t g = hl / p.qpg, hq = hl % p.qpg;
-      const float l = (misc->lsum[g][hq][0] + misc->lsum[g][hq][1]) + (misc->lsum[g][hq][2] + misc->lsum[g][hq][3]);
-      const float o = o_fin[(g * 4 + hq) * BP_HEAD_DIM + d];
+      // the groups w with w % HPC == g hold disjoint token subsets of head g: merge them
+      float m = NEG_BIG;
+      for (uint32_t w = g; w < NGRP; w += HPC) m = fmaxf(m, misc->mfin[w][hq]);
+      float o = 0.f, l = 0.f;
+      for (uint32_t w = g; w < NGRP; w += HPC) {
+        const float e = ex2(misc->mfin[w][hq] - m);
+        l += ((misc->lsum[w][hq][0] + misc->lsum[w][hq][1]) + (misc->lsum[w][hq][2] + misc->lsum[w][hq][3])) * e;
+        o += o_fin[(w * 4 + hq) * BP_HEAD_DIM + d] * e;
+      }
       const uint32_t h = (g0 + g) * p.qpg + hq;
       if (n_splits == 1) {
         p.out[static_cast<size_t>(h) * BP_HEAD_DIM + d] = __float2half_rn(o * (1.0f / l));
       } else {
         float* dst = p.partials + (static_cast<size_t>(split) * p.n_head + h) * BP_PART_STRIDE;
         dst[d] = o;
-        if (d == 0) { dst[128] = misc->mfin[g][hq]; dst[129] = l; }
+        if (d == 0) { dst[128] = m; dst[129] = l; }
       }
     }
   }
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem, TMEM_COLS);
+  if (p.dbg != nullptr && threadIdx.x == 0) {
+    unsigned long long t_exit_ns;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_exit_ns));
+    atomicMax(&p.dbg[33], t_exit_ns);
+    atomicMax(&p.dbg[34], static_cast<unsigned long long>(t_start - t_entry));      // set-up cycles
+    atomicMax(&p.dbg[35], static_cast<unsigned long long>(t_loop_end - t_start));   // main loop cycles (warp 0)
+    atomicMax(&p.dbg[36], static_cast<unsigned long long>(clock64() - t_loop_end)); // epilogue cycles
+    atomicMax(&p.dbg[37], t_exit_ns - t_entry_ns);                                   // longest CTA, ns
+  }
 }
 
 }  // namespace

@@ -595,6 +595,10 @@ int bp_set_option(bp_attn_ctx* c, const char* name, uint32_t value) {
     c->opt_hpc = value;
   } else if (strcmp(name, "debug_counters") == 0) {
     c->dbg_on = value != 0;
+    if (bind_device(c) != BP_OK) return BP_ERR_CUDA;
+    unsigned long long init[64] = {};
+    init[32] = ~0ull;  // slot 32 is a minimum
+    BP_CUDA(c, cudaMemcpy(c->dbg_dev, init, sizeof init, cudaMemcpyHostToDevice));
     return BP_OK;
   } else if (strcmp(name, "decode_umma_heads_per_cta") == 0) {
     if ((value != 1 && value != 2) || c->cfg.n_kv_head % value != 0)
