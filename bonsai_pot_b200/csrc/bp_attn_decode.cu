@@ -623,13 +623,7 @@ cudaError_t bp_launch_decode(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, con
     uint32_t n_splits = 1;
     cudaError_t e = bp_launch_decode_umma(c, s, layer, q, out, cur_pos, &n_splits);
     *launches += 1;
-    if (e != cudaSuccess) return e;
-    if (n_splits > 1) {
-      attn_combine_kernel<<<c->cfg.n_head, 128 * COMBINE_GROUPS, 0, s>>>(c->partials, out, c->cfg.n_head, n_splits);
-      *launches += 1;
-      e = cudaGetLastError();
-    }
-    return e;
+    return e;  // the kernel combines its own splits
   }
   if (!c->have_maps) return cudaErrorNotSupported;
 

@@ -37,6 +37,7 @@ constexpr uint32_t U_FIRST_SM_WARP = 1 + 2 * NISS;  // warp 0 producer, then the
 constexpr uint32_t U_THREADS = (U_FIRST_SM_WARP + 4 * NGRP + 4) * 32;
 constexpr uint32_t TMEM_COLS = 512;          // per softmax group: D1 (64 columns) and D2 (64 columns)
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
+constexpr uint32_t COMBINE_MAX = 256;         // most splits the in-kernel combine handles
 constexpr uint32_t U_SMEM_BUDGET = 226 * 1024;  // dynamic shared memory; the static part needs the rest of 227 KB
 
 struct UmmaParams {
@@ -44,6 +45,7 @@ struct UmmaParams {
   __half* out;
   float* partials;
   uint32_t* err;
+  uint32_t* tickets;  // one arrival counter per group of KV heads (grid y); the last CTA to arrive combines
   uint32_t row_base, cur_pos, tps, n_stages, n_head, qpg;
   float sm_scale_log2;
   unsigned long long* dbg;  // optional cycle counters of CTA (0, 0); null in normal use
@@ -86,6 +88,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[U_MAX_STAGES], empty_bar[U_MAX_STAGES];
   __shared__ __align__(8) uint64_t s_ready[4], s_free[4], p_ready[4], p_free[4], o_ready[4], o_free[4];
+  __shared__ __align__(8) uint64_t q_bar;
   __shared__ uint32_t tmem_base_s;
   __shared__ volatile uint32_t abort_s;
 
@@ -124,6 +127,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
       mbar_init(smem_u32(&o_ready[b]), 1);
       mbar_init(smem_u32(&o_free[b]), 4);
     }
+    mbar_init(smem_u32(&q_bar), 1);
     abort_s = 0;
     fence_barrier_init();
   }
@@ -132,51 +136,56 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
     for (uint32_t i = threadIdx.x; i < (L::Q_B + L::P_B) / 16; i += U_THREADS) z[i] = make_uint4(0, 0, 0, 0);
   }
   if (warp == 1) tmem_alloc(smem_u32(&tmem_base_s), TMEM_COLS);
-  __syncthreads();
-  // Q of head (g, hq), block b: 15-bit integers = 128 * hi + lo against the block's absmax;
-  // hi bytes go to row hq, lo bytes to row 4 + hq of the head's Q^T tile (swizzled 128-byte rows).
-  if (threadIdx.x < HPC * p.qpg * 4) {
-    const uint32_t b = threadIdx.x & 3, hq = (threadIdx.x >> 2) % p.qpg, g = (threadIdx.x >> 2) / p.qpg;
-    const __half* src = p.q + (static_cast<size_t>(g0 + g) * p.qpg + hq) * BP_HEAD_DIM + 32 * b;
-    float v[32], amax = 0.f;
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-      const uint4 raw = *reinterpret_cast<const uint4*>(src + 8 * i);
-      const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
-#pragma unroll
-      for (int j = 0; j < 4; j++) {
-        const float2 f = __half22float2(h2[j]);
-        v[8 * i + 2 * j] = f.x;
-        v[8 * i + 2 * j + 1] = f.y;
-        amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
-      }
-    }
-    const float sq = amax / 16383.0f, inv = amax > 0.f ? 16383.0f / amax : 0.f;
-    uint32_t hi[8], lo[8];
-#pragma unroll
-    for (int w = 0; w < 8; w++) {
-      hi[w] = 0; lo[w] = 0;
-#pragma unroll
-      for (int c = 0; c < 4; c++) {
-        const int qi = __float2int_rn(v[4 * w + c] * inv);
-        hi[w] |= (static_cast<uint32_t>(qi >> 7) & 0xffu) << (8 * c);
-        lo[w] |= (static_cast<uint32_t>(qi) & 0x7fu) << (8 * c);
-      }
-    }
-    uint8_t* tile = smem_gen + ns * L::STAGE_B + g * 2048;
-#pragma unroll
-    for (int c = 0; c < 2; c++) {  // two 16-byte chunks of the block
-      const uint32_t off_hi = hq * 128 + 32 * b + 16 * c, off_lo = (4 + hq) * 128 + 32 * b + 16 * c;
-      *reinterpret_cast<uint4*>(tile + swz128(off_hi)) = make_uint4(hi[4 * c], hi[4 * c + 1], hi[4 * c + 2], hi[4 * c + 3]);
-      *reinterpret_cast<uint4*>(tile + swz128(off_lo)) = make_uint4(lo[4 * c], lo[4 * c + 1], lo[4 * c + 2], lo[4 * c + 3]);
-    }
-    misc->sq[g][hq][b] = sq * p.sm_scale_log2;
-  }
   fence_proxy_async();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_base_s;
+  // Q of head (g, hq), block b: 15-bit integers = 128 * hi + lo against the block's absmax; hi bytes
+  // go to row hq, lo bytes to row 4 + hq of the head's Q^T tile (swizzled 128-byte rows). Done by one
+  // warp while the producer already streams the first stages; the QK issuers wait on q_bar.
+  auto prepare_q = [&]() {
+    if (lane < HPC * p.qpg * 4) {
+      const uint32_t b = lane & 3, hq = (lane >> 2) % p.qpg, g = (lane >> 2) / p.qpg;
+      const __half* src = p.q + (static_cast<size_t>(g0 + g) * p.qpg + hq) * BP_HEAD_DIM + 32 * b;
+      float v[32], amax = 0.f;
+  #pragma unroll
+      for (int i = 0; i < 4; i++) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(src + 8 * i);
+        const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
+  #pragma unroll
+        for (int j = 0; j < 4; j++) {
+          const float2 f = __half22float2(h2[j]);
+          v[8 * i + 2 * j] = f.x;
+          v[8 * i + 2 * j + 1] = f.y;
+          amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+        }
+      }
+      const float sq = amax / 16383.0f, inv = amax > 0.f ? 16383.0f / amax : 0.f;
+      uint32_t hi[8], lo[8];
+  #pragma unroll
+      for (int w = 0; w < 8; w++) {
+        hi[w] = 0; lo[w] = 0;
+  #pragma unroll
+        for (int c = 0; c < 4; c++) {
+          const int qi = __float2int_rn(v[4 * w + c] * inv);
+          hi[w] |= (static_cast<uint32_t>(qi >> 7) & 0xffu) << (8 * c);
+          lo[w] |= (static_cast<uint32_t>(qi) & 0x7fu) << (8 * c);
+        }
+      }
+      uint8_t* tile = smem_gen + ns * L::STAGE_B + g * 2048;
+  #pragma unroll
+      for (int c = 0; c < 2; c++) {  // two 16-byte chunks of the block
+        const uint32_t off_hi = hq * 128 + 32 * b + 16 * c, off_lo = (4 + hq) * 128 + 32 * b + 16 * c;
+        *reinterpret_cast<uint4*>(tile + swz128(off_hi)) = make_uint4(hi[4 * c], hi[4 * c + 1], hi[4 * c + 2], hi[4 * c + 3]);
+        *reinterpret_cast<uint4*>(tile + swz128(off_lo)) = make_uint4(lo[4 * c], lo[4 * c + 1], lo[4 * c + 2], lo[4 * c + 3]);
+      }
+      misc->sq[g][hq][b] = sq * p.sm_scale_log2;
+    }
+    fence_proxy_async();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(smem_u32(&q_bar));
+  };
 
   // Jobs: job j = (stage it, head g) with j = it * HPC + g. NGRP softmax groups
   // work in parallel; job j belongs to group w = j % NGRP, so a group always
@@ -228,6 +237,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
       constexpr uint32_t IDESC_QK = umma_idesc(2, 1, 1, 0, 0, 128, 16);  // s32 = s8 (K-major) x s8
       const uint64_t dbase = umma_desc_sw128(0, 16, 1024);               // + (shared address >> 4)
       const uint32_t q = warp - 1;
+      wait(&q_bar, 0, t_w2);
       for (uint32_t j = q; j < n_jobs; j += NISS) {
         const uint32_t it = j / HPC, g = j % HPC, bi = j % NGRP, k = j / NGRP, s = it % ns, use = it / ns;
         wait(&full_bar[s], use & 1, t_w0);
@@ -273,6 +283,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
     float m_run[4], l_part[4];
 #pragma unroll
     for (int h = 0; h < 4; h++) { m_run[h] = NEG_BIG; l_part[h] = 0.f; }
+    wait(&q_bar, 0, t_w2);  // the Q block scales in misc->sq are written by prepare_q
 
     for (uint32_t j = w; j < n_jobs; j += NGRP) {
       const uint32_t it = j / HPC, g = j % HPC, bi = w, k = j / NGRP;
@@ -381,6 +392,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
     }
   } else {
     // ---------------- accumulate: thread = head dim ----------------
+    if (warp == U_FIRST_SM_WARP + 4 * NGRP) prepare_q();
     const uint32_t quad = warp & 3, dim = quad * 32 + lane;
     const uint32_t lane_addr = (quad * 32) << 16;
     float o[NGRP][4];
@@ -460,6 +472,58 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
       }
     }
   }
+  // ---- log-sum-exp combine over the splits (attention_merge.wgsl:70-130), done by the CTA of
+  //      this head group that finishes last: every CTA publishes its partial, then takes a ticket.
+  if (n_splits > 1) {
+    __shared__ uint32_t is_last_s;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const uint32_t t = atomicAdd(&p.tickets[blockIdx.y], 1u);
+      is_last_s = (t == n_splits - 1) ? 1u : 0u;
+      if (is_last_s) p.tickets[blockIdx.y] = 0;  // self-resetting: the next launch starts from zero
+    }
+    __syncthreads();
+    if (is_last_s) {
+      __threadfence();
+      // (m, l) of every split and head of this CTA's heads -> shared memory (one load round), then
+      // each thread owns one output element and sums over the splits with its loads batched.
+      float* ms = reinterpret_cast<float*>(smem_gen);           // [heads][n_splits], stage ring is idle
+      float* ls = ms + HPC * 4 * COMBINE_MAX;
+      const uint32_t n_hl = HPC * p.qpg;
+      const size_t stride = static_cast<size_t>(p.n_head) * BP_PART_STRIDE;
+      for (uint32_t i = threadIdx.x; i < n_hl * n_splits; i += U_THREADS) {
+        const uint32_t hl = i / n_splits, s = i % n_splits;
+        const float* src = p.partials + s * stride + static_cast<size_t>(g0 * p.qpg + hl) * BP_PART_STRIDE + 128;
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(src));
+        ms[hl * COMBINE_MAX + s] = ml.x;
+        ls[hl * COMBINE_MAX + s] = ml.y;
+      }
+      __syncthreads();
+      for (uint32_t idx = threadIdx.x; idx < n_hl * BP_HEAD_DIM; idx += U_THREADS) {
+        const uint32_t hl = idx >> 7, d = idx & 127;
+        const uint32_t h = g0 * p.qpg + hl;
+        const float* base = p.partials + static_cast<size_t>(h) * BP_PART_STRIDE + d;
+        float m_all = NEG_BIG;
+        for (uint32_t s = 0; s < n_splits; s++) m_all = fmaxf(m_all, ms[hl * COMBINE_MAX + s]);
+        float o = 0.f, l = 0.f;
+        for (uint32_t s0 = 0; s0 < n_splits; s0 += 8) {
+          float v[8];
+#pragma unroll
+          for (uint32_t k = 0; k < 8; k++) v[k] = s0 + k < n_splits ? __ldcg(base + (s0 + k) * stride) : 0.f;
+#pragma unroll
+          for (uint32_t k = 0; k < 8; k++) {
+            if (s0 + k < n_splits) {
+              const float e = ex2(ms[hl * COMBINE_MAX + s0 + k] - m_all);
+              o = fmaf(v[k], e, o);
+              l = fmaf(ls[hl * COMBINE_MAX + s0 + k], e, l);
+            }
+          }
+        }
+        p.out[static_cast<size_t>(h) * BP_HEAD_DIM + d] = __float2half_rn(o * (1.0f / l));
+      }
+    }
+  }
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem, TMEM_COLS);
   if (p.dbg != nullptr && threadIdx.x == 0) {
@@ -529,6 +593,7 @@ cudaError_t bp_launch_decode_umma(bp_attn_ctx* c, cudaStream_t s, uint32_t layer
   p.out = out;
   p.partials = c->partials;
   p.err = c->err_dev;
+  p.tickets = c->tickets;
   p.row_base = layer * c->cfg.max_seq;
   p.cur_pos = cur_pos;
   p.tps = spp * UT;

@@ -20,7 +20,7 @@ struct bp_attn_ctx {
   uint8_t* kv[2];    // device: kv_k, kv_v (d-section then qs-section)
   __half* rope;      // device: [max_seq][64][2] (cos, sin)
   float* partials;   // device: split-KV scratch [max_splits][n_head][BP_PART_STRIDE]
-  uint32_t* tickets; // device: one arrival counter per layer (self-resetting)
+  uint32_t* tickets; // device: arrival counters of the in-kernel split combine (self-resetting)
   uint32_t* err_host; // pinned, mapped: kernels store a non-zero code here when a bounded wait gives up
   uint32_t* err_dev;  // device alias of err_host
   uint32_t max_splits;
@@ -34,6 +34,9 @@ struct bp_attn_ctx {
   CUtensorMap umap_qs[2];  // tcgen05 decode: 128-token boxes
   CUtensorMap umap_d[2];
   bool have_umaps;
+  CUtensorMap pmap_qs[2];  // tcgen05 prefill: 128-key boxes, one head
+  CUtensorMap pmap_d[2];
+  bool have_pmaps;
   // staging for the *_host entry points
   __half *stage_q, *stage_k, *stage_v, *stage_out, *stage_wq, *stage_wk;
   uint32_t stage_rows;

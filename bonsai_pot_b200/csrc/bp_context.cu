@@ -233,8 +233,8 @@ int bp_attn_create(const bp_attn_config* cfg, bp_attn_ctx** out) {
 
   c->max_splits = bp_decode_max_splits(c);
   BP_CUDA(c, cudaMalloc(&c->partials, static_cast<size_t>(c->max_splits) * cfg->n_head * BP_PART_STRIDE * sizeof(float)));
-  BP_CUDA(c, cudaMalloc(&c->tickets, (cfg->n_layer + 1) * sizeof(uint32_t)));
-  BP_CUDA(c, cudaMemset(c->tickets, 0, (cfg->n_layer + 1) * sizeof(uint32_t)));
+  BP_CUDA(c, cudaMalloc(&c->tickets, 64 * sizeof(uint32_t)));
+  BP_CUDA(c, cudaMemset(c->tickets, 0, 64 * sizeof(uint32_t)));
   BP_CUDA(c, cudaMalloc(&c->dbg_dev, 64 * sizeof(unsigned long long)));
   BP_CUDA(c, cudaMemset(c->dbg_dev, 0, 64 * sizeof(unsigned long long)));
   BP_CUDA(c, cudaHostAlloc(&c->err_host, sizeof(uint32_t), cudaHostAllocMapped));
