@@ -410,6 +410,42 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def prefill_bench(torch, bp, stream, tflops_peak, peak_kind, pp, nl):
+    """One prefill pass per layer (Q norm+RoPE, KV write-back, causal attention) over `nl` layers."""
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(7 + pp)
+    w = torch.ones(128, dtype=torch.float16, device="cuda")
+    with bp.AttnContext(n_layer=nl, max_seq=pp) as c:
+        q = torch.randn(nl, pp, Q_DIM, generator=gen, device="cuda").half()
+        k = torch.randn(nl, pp, KV_DIM, generator=gen, device="cuda").half()
+        v = torch.randn(nl, pp, KV_DIM, generator=gen, device="cuda").half()
+        qw = q.clone()
+        o = torch.zeros(nl, pp, Q_DIM, dtype=torch.float16, device="cuda")
+
+        def full_pass():
+            for il in range(nl):
+                c.dispatch_q_norm_rope_fused(qw[il], w, 0, pp, stream=stream)
+                c.dispatch_kv_writeback_fused(il, k[il], v[il], w, 0, pp, stream=stream)
+                c.dispatch_attention(il, qw[il], o[il], pp, stream=stream)
+
+        def attn_only():
+            for il in range(nl):
+                c.dispatch_attention(il, qw[il], o[il], pp, stream=stream)
+
+        full_g, attn_g = graphed(torch, full_pass, stream), graphed(torch, attn_only, stream)
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                full_g()
+            reps = 10
+            dt_full = time_region(torch, full_g, reps, stream) / (reps * nl)
+            dt_attn = time_region(torch, attn_g, reps, stream) / (reps * nl)
+        flops = 8192 * pp * (pp + 1)
+        return {"us_per_layer_pass": round(dt_full * 1e6, 2), "us_per_layer_attention": round(dt_attn * 1e6, 2),
+                "tflops_pass": round(flops / dt_full / 1e12, 2), "tflops_attention": round(flops / dt_attn / 1e12, 2),
+                "frac_of_peak": round(flops / dt_attn / 1e12 / tflops_peak, 4), "peak_kind": peak_kind,
+                "frac_of_2250_spec": round(flops / dt_attn / 1e12 / 2250.0, 4)}
+
+
 def extras(torch, bp, stream, hbm_peak, tflops_peak, peak_kind, args):
     """Long-context decode (ctx 32768) and the prefill pass (pp 512 / 2048) on one GPU."""
     out = {}
@@ -442,33 +478,7 @@ def extras(torch, bp, stream, hbm_peak, tflops_peak, peak_kind, args):
                                   "frac_of_peak": round(gbs / hbm_peak, 4), "peak_kind": peak_kind,
                                   "frac_of_8000_spec": round(gbs / 8000.0, 4), "splits": c.decode_num_splits(ctx_len)}
     for pp in (512, 2048):
-        nl = 4
-        with bp.AttnContext(n_layer=nl, max_seq=pp) as c:
-            q = torch.randn(nl, pp, Q_DIM, generator=gen, device="cuda").half()
-            k = torch.randn(nl, pp, KV_DIM, generator=gen, device="cuda").half()
-            v = torch.randn(nl, pp, KV_DIM, generator=gen, device="cuda").half()
-            qw = q.clone()
-            o = torch.zeros(nl, pp, Q_DIM, dtype=torch.float16, device="cuda")
-            def full_pass():
-                for il in range(nl):
-                    c.dispatch_q_norm_rope_fused(qw[il], w, 0, pp, stream=stream)
-                    c.dispatch_kv_writeback_fused(il, k[il], v[il], w, 0, pp, stream=stream)
-                    c.dispatch_attention(il, qw[il], o[il], pp, stream=stream)
-            def attn_only():
-                for il in range(nl):
-                    c.dispatch_attention(il, qw[il], o[il], pp, stream=stream)
-            full_g, attn_g = graphed(torch, full_pass, stream), graphed(torch, attn_only, stream)
-            with torch.cuda.stream(stream):
-                for _ in range(3):
-                    full_g()
-                reps = 10
-                dt_full = time_region(torch, full_g, reps, stream) / (reps * nl)
-                dt_attn = time_region(torch, attn_g, reps, stream) / (reps * nl)
-            flops = 8192 * pp * (pp + 1)
-            out[f"prefill_pp{pp}"] = {"us_per_layer_pass": round(dt_full * 1e6, 2), "us_per_layer_attention": round(dt_attn * 1e6, 2),
-                                      "tflops_pass": round(flops / dt_full / 1e12, 2), "tflops_attention": round(flops / dt_attn / 1e12, 2),
-                                      "frac_of_peak": round(flops / dt_attn / 1e12 / tflops_peak, 4), "peak_kind": peak_kind,
-                                      "frac_of_2250_spec": round(flops / dt_attn / 1e12 / 2250.0, 4)}
+        out[f"prefill_pp{pp}"] = prefill_bench(torch, bp, stream, tflops_peak, peak_kind, pp, 4)
     return out
 
 
@@ -485,12 +495,20 @@ def main():
     ap.add_argument("--decode-hpc", type=int, default=0, help="override the decode kernel's KV heads per CTA")
     ap.add_argument("--decode-uhpc", type=int, default=0, help="override the tcgen05 decode kernel's KV heads per CTA")
     ap.add_argument("--variant", type=int, default=0, help="decode kernel family (0 = production)")
+    ap.add_argument("--prefill-only", type=int, default=0, metavar="PP",
+                    help="run only the prefill pass at this prompt length and print its JSON (profiler captures)")
     ap.add_argument("--no-extras", action="store_true", help="skip the ctx-32768 and prefill side measurements")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     N_LAYER = args.layers
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    if args.impl == "reference":
+    if args.prefill_only:
+        import torch
+        import bonsai_pot_b200 as bp
+        hbm_peak, tflops_peak, peak_kind = measured_peaks()
+        torch.cuda.set_device(0)
+        print(json.dumps(prefill_bench(torch, bp, torch.cuda.Stream(), tflops_peak, peak_kind, args.prefill_only, min(args.layers, 4))))
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -623,7 +623,15 @@ cudaError_t bp_launch_decode(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, con
     uint32_t n_splits = 1;
     cudaError_t e = bp_launch_decode_umma(c, s, layer, q, out, cur_pos, &n_splits);
     *launches += 1;
-    return e;  // the kernel combines its own splits
+    if (e != cudaSuccess) return e;
+    // A fused "last CTA combines" epilogue was measured slower than this second small kernel:
+    // code that a CTA runs once is fetched cold, and the ticket + combine path cost more than a launch.
+    if (n_splits > 1) {
+      attn_combine_kernel<<<c->cfg.n_head, 128 * COMBINE_GROUPS, 0, s>>>(c->partials, out, c->cfg.n_head, n_splits);
+      *launches += 1;
+      e = cudaGetLastError();
+    }
+    return e;
   }
   if (!c->have_maps) return cudaErrorNotSupported;
 

@@ -37,7 +37,6 @@ constexpr uint32_t U_FIRST_SM_WARP = 1 + 2 * NISS;  // warp 0 producer, then the
 constexpr uint32_t U_THREADS = (U_FIRST_SM_WARP + 4 * NGRP + 4) * 32;
 constexpr uint32_t TMEM_COLS = 512;          // per softmax group: D1 (64 columns) and D2 (64 columns)
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
-constexpr uint32_t COMBINE_MAX = 256;         // most splits the in-kernel combine handles
 constexpr uint32_t U_SMEM_BUDGET = 226 * 1024;  // dynamic shared memory; the static part needs the rest of 227 KB
 
 struct UmmaParams {
@@ -45,7 +44,6 @@ struct UmmaParams {
   __half* out;
   float* partials;
   uint32_t* err;
-  uint32_t* tickets;  // one arrival counter per group of KV heads (grid y); the last CTA to arrive combines
   uint32_t row_base, cur_pos, tps, n_stages, n_head, qpg;
   float sm_scale_log2;
   unsigned long long* dbg;  // optional cycle counters of CTA (0, 0); null in normal use
@@ -79,6 +77,16 @@ __device__ __forceinline__ int f32_order(float f) {  // monotone map float -> in
 }
 __device__ __forceinline__ float f32_unorder(int k) { return __int_as_float(k >= 0 ? k : k ^ 0x7fffffff); }
 
+// Bounded mbarrier wait shared by every role (one copy of the code: the kernel's instruction
+// footprint matters, cold instruction fetches cost more than the waits themselves).
+__device__ __noinline__ void cta_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* err) {
+  if (*abort_flag) return;
+  if (!mbar_wait(smem_u32(bar), parity, WAIT_LIMIT)) {
+    *abort_flag = 1;
+    atomicExch(err, 3u);
+  }
+}
+
 template <uint32_t HPC>
 __global__ void __launch_bounds__(U_THREADS, 1)
 decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_constant__ CUtensorMap map_kd,
@@ -96,7 +104,6 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   unsigned long long t_entry_ns = 0;
-  const long long t_entry = clock64();
   if (p.dbg != nullptr && threadIdx.x == 0) {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_entry_ns));
     atomicMin(&p.dbg[32], t_entry_ns);
@@ -148,37 +155,25 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
     if (lane < HPC * p.qpg * 4) {
       const uint32_t b = lane & 3, hq = (lane >> 2) % p.qpg, g = (lane >> 2) / p.qpg;
       const __half* src = p.q + (static_cast<size_t>(g0 + g) * p.qpg + hq) * BP_HEAD_DIM + 32 * b;
-      float v[32], amax = 0.f;
-  #pragma unroll
-      for (int i = 0; i < 4; i++) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(src + 8 * i);
-        const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
-  #pragma unroll
-        for (int j = 0; j < 4; j++) {
-          const float2 f = __half22float2(h2[j]);
-          v[8 * i + 2 * j] = f.x;
-          v[8 * i + 2 * j + 1] = f.y;
-          amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
-        }
+      // two passes over the 32 values, kept as rolled loops: this runs once per CTA and its
+      // instructions are fetched cold, so code size is what it costs
+      float amax = 0.f;
+#pragma unroll 1
+      for (int i = 0; i < 16; i++) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(src + 2 * i));
+        amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
       }
       const float sq = amax / 16383.0f, inv = amax > 0.f ? 16383.0f / amax : 0.f;
-      uint32_t hi[8], lo[8];
-  #pragma unroll
-      for (int w = 0; w < 8; w++) {
-        hi[w] = 0; lo[w] = 0;
-  #pragma unroll
-        for (int c = 0; c < 4; c++) {
-          const int qi = __float2int_rn(v[4 * w + c] * inv);
-          hi[w] |= (static_cast<uint32_t>(qi >> 7) & 0xffu) << (8 * c);
-          lo[w] |= (static_cast<uint32_t>(qi) & 0x7fu) << (8 * c);
-        }
-      }
       uint8_t* tile = smem_gen + ns * L::STAGE_B + g * 2048;
-  #pragma unroll
-      for (int c = 0; c < 2; c++) {  // two 16-byte chunks of the block
-        const uint32_t off_hi = hq * 128 + 32 * b + 16 * c, off_lo = (4 + hq) * 128 + 32 * b + 16 * c;
-        *reinterpret_cast<uint4*>(tile + swz128(off_hi)) = make_uint4(hi[4 * c], hi[4 * c + 1], hi[4 * c + 2], hi[4 * c + 3]);
-        *reinterpret_cast<uint4*>(tile + swz128(off_lo)) = make_uint4(lo[4 * c], lo[4 * c + 1], lo[4 * c + 2], lo[4 * c + 3]);
+#pragma unroll 1
+      for (int i = 0; i < 16; i++) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(src + 2 * i));
+        const int q0 = __float2int_rn(f.x * inv), q1 = __float2int_rn(f.y * inv);
+        const uint32_t col = 32 * b + 2 * i;
+        const uint16_t hi = static_cast<uint16_t>((static_cast<uint32_t>(q0 >> 7) & 0xffu) | ((static_cast<uint32_t>(q1 >> 7) & 0xffu) << 8));
+        const uint16_t lo = static_cast<uint16_t>((static_cast<uint32_t>(q0) & 0x7fu) | ((static_cast<uint32_t>(q1) & 0x7fu) << 8));
+        *reinterpret_cast<uint16_t*>(tile + swz128(hq * 128 + col)) = hi;
+        *reinterpret_cast<uint16_t*>(tile + swz128((4 + hq) * 128 + col)) = lo;
       }
       misc->sq[g][hq][b] = sq * p.sm_scale_log2;
     }
@@ -191,19 +186,8 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
   // work in parallel; job j belongs to group w = j % NGRP, so a group always
   // sees the same head (w % HPC). Each group owns one D1, one D2 and one P'
   // buffer; its k-th job (k = j / NGRP) completes phase k of its barriers.
-  const bool dbg_on = p.dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && lane == 0;
-  long long t_w0 = 0, t_w1 = 0, t_w2 = 0;
-  const long long t_start = clock64();
   // A wait that degrades to a no-op once any warp of the CTA has timed out.
-  auto wait = [&](uint64_t* bar, uint32_t parity, long long& acct) {
-    if (abort_s) return;
-    const long long t0 = dbg_on ? clock64() : 0;
-    if (!mbar_wait(smem_u32(bar), parity, WAIT_LIMIT)) {
-      abort_s = 1;
-      atomicExch(p.err, 3u);
-    }
-    if (dbg_on) acct += clock64() - t0;
-  };
+  auto wait = [&](uint64_t* bar, uint32_t parity) { cta_wait(bar, parity, &abort_s, p.err); };
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -214,7 +198,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
       prefetch_tensormap(&map_vd);
       uint32_t s = 0, use = 0;
       for (uint32_t it = 0; it < n_iter; it++) {
-        if (use > 0) wait(&empty_bar[s], (use - 1) & 1, t_w0);
+        if (use > 0) wait(&empty_bar[s], (use - 1) & 1);
         if (abort_s) break;
         const uint32_t bar = smem_u32(&full_bar[s]);
         const uint32_t stage = smem_base + s * L::STAGE_B;
@@ -237,11 +221,11 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
       constexpr uint32_t IDESC_QK = umma_idesc(2, 1, 1, 0, 0, 128, 16);  // s32 = s8 (K-major) x s8
       const uint64_t dbase = umma_desc_sw128(0, 16, 1024);               // + (shared address >> 4)
       const uint32_t q = warp - 1;
-      wait(&q_bar, 0, t_w2);
+      wait(&q_bar, 0);
       for (uint32_t j = q; j < n_jobs; j += NISS) {
         const uint32_t it = j / HPC, g = j % HPC, bi = j % NGRP, k = j / NGRP, s = it % ns, use = it / ns;
-        wait(&full_bar[s], use & 1, t_w0);
-        if (k > 0) wait(&s_free[bi], (k - 1) & 1, t_w1);
+        wait(&full_bar[s], use & 1);
+        if (k > 0) wait(&s_free[bi], (k - 1) & 1);
         tc_fence_after();
         const uint64_t ka = dbase + ((smem_base + s * L::STAGE_B + g * TILE_B) >> 4);
         const uint64_t qb = dbase + ((q_tiles + g * 2048) >> 4);
@@ -261,8 +245,8 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
       const uint32_t q = warp - 1 - NISS;
       for (uint32_t j = q; j < n_jobs; j += NISS) {
         const uint32_t it = j / HPC, g = j % HPC, bi = j % NGRP, k = j / NGRP, s = it % ns;
-        wait(&p_ready[bi], k & 1, t_w0);
-        if (k > 0) wait(&o_free[bi], (k - 1) & 1, t_w1);
+        wait(&p_ready[bi], k & 1);
+        if (k > 0) wait(&o_free[bi], (k - 1) & 1);
         tc_fence_after();
         const uint64_t va = dbase + ((smem_base + s * L::STAGE_B + (HPC + g) * TILE_B) >> 4);
         const uint64_t pb = dbase + ((p_tiles + bi * 4 * 2048) >> 4);
@@ -283,13 +267,13 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
     float m_run[4], l_part[4];
 #pragma unroll
     for (int h = 0; h < 4; h++) { m_run[h] = NEG_BIG; l_part[h] = 0.f; }
-    wait(&q_bar, 0, t_w2);  // the Q block scales in misc->sq are written by prepare_q
+    wait(&q_bar, 0);  // the Q block scales in misc->sq are written by prepare_q
 
     for (uint32_t j = w; j < n_jobs; j += NGRP) {
       const uint32_t it = j / HPC, g = j % HPC, bi = w, k = j / NGRP;
       const uint8_t* stage = smem_gen + (it % ns) * L::STAGE_B;
       const bool valid = tok_begin + it * UT + t < tok_end;
-      wait(&s_ready[bi], k & 1, t_w0);
+      wait(&s_ready[bi], k & 1);
       tc_fence_after();
       uint32_t d[4][8];
 #pragma unroll
@@ -355,8 +339,8 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
       }
       // the group's P' buffer and info slot are free once its previous job has been consumed
       if (k > 0) {
-        wait(&p_free[bi], (k - 1) & 1, t_w1);
-        wait(&o_free[bi], (k - 1) & 1, t_w2);
+        wait(&p_free[bi], (k - 1) & 1);
+        wait(&o_free[bi], (k - 1) & 1);
       }
       if (t == 0) {
         *reinterpret_cast<float4*>(&misc->info[bi][0]) = make_float4(corr[0], corr[1], corr[2], corr[3]);
@@ -406,7 +390,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
         const uint32_t j = j0 + w;
         if (j < n_jobs) {
           const uint32_t bi = w, k = j / NGRP;
-          wait(&o_ready[bi], k & 1, t_w0);
+          wait(&o_ready[bi], k & 1);
           tc_fence_after();
           uint32_t d[16];
           tmem_ld16(tmem + lane_addr + NGRP * 64 + bi * 64 + 16 * quad, d);  // this warp's dims are Q8_0 block `quad`
@@ -434,16 +418,6 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
       for (int h = 0; h < 4; h++) o_fin[(w * 4 + h) * BP_HEAD_DIM + dim] = o[w][h];
   }
 
-  if (dbg_on && (warp == 0 || warp == 1 || warp == 1 + NISS || warp == U_FIRST_SM_WARP)) {
-    // per role: cycles in the main loop, then cycles in each kind of wait
-    const uint32_t role = warp == 0 ? 0 : warp == 1 ? 1 : warp == 1 + NISS ? 2 : 3;
-    p.dbg[role * 8 + 0] = static_cast<unsigned long long>(clock64() - t_start);
-    p.dbg[role * 8 + 1] = static_cast<unsigned long long>(t_w0);
-    p.dbg[role * 8 + 2] = static_cast<unsigned long long>(t_w1);
-    p.dbg[role * 8 + 3] = static_cast<unsigned long long>(t_w2);
-    p.dbg[role * 8 + 7] = n_jobs;
-  }
-  const long long t_loop_end = clock64();
   tc_fence_before();
   __syncthreads();
   // ---- epilogue: partial (o, m, l) per query head, or the final output ----
@@ -472,68 +446,13 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
       }
     }
   }
-  // ---- log-sum-exp combine over the splits (attention_merge.wgsl:70-130), done by the CTA of
-  //      this head group that finishes last: every CTA publishes its partial, then takes a ticket.
-  if (n_splits > 1) {
-    __shared__ uint32_t is_last_s;
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      const uint32_t t = atomicAdd(&p.tickets[blockIdx.y], 1u);
-      is_last_s = (t == n_splits - 1) ? 1u : 0u;
-      if (is_last_s) p.tickets[blockIdx.y] = 0;  // self-resetting: the next launch starts from zero
-    }
-    __syncthreads();
-    if (is_last_s) {
-      __threadfence();
-      // (m, l) of every split and head of this CTA's heads -> shared memory (one load round), then
-      // each thread owns one output element and sums over the splits with its loads batched.
-      float* ms = reinterpret_cast<float*>(smem_gen);           // [heads][n_splits], stage ring is idle
-      float* ls = ms + HPC * 4 * COMBINE_MAX;
-      const uint32_t n_hl = HPC * p.qpg;
-      const size_t stride = static_cast<size_t>(p.n_head) * BP_PART_STRIDE;
-      for (uint32_t i = threadIdx.x; i < n_hl * n_splits; i += U_THREADS) {
-        const uint32_t hl = i / n_splits, s = i % n_splits;
-        const float* src = p.partials + s * stride + static_cast<size_t>(g0 * p.qpg + hl) * BP_PART_STRIDE + 128;
-        const float2 ml = __ldcg(reinterpret_cast<const float2*>(src));
-        ms[hl * COMBINE_MAX + s] = ml.x;
-        ls[hl * COMBINE_MAX + s] = ml.y;
-      }
-      __syncthreads();
-      for (uint32_t idx = threadIdx.x; idx < n_hl * BP_HEAD_DIM; idx += U_THREADS) {
-        const uint32_t hl = idx >> 7, d = idx & 127;
-        const uint32_t h = g0 * p.qpg + hl;
-        const float* base = p.partials + static_cast<size_t>(h) * BP_PART_STRIDE + d;
-        float m_all = NEG_BIG;
-        for (uint32_t s = 0; s < n_splits; s++) m_all = fmaxf(m_all, ms[hl * COMBINE_MAX + s]);
-        float o = 0.f, l = 0.f;
-        for (uint32_t s0 = 0; s0 < n_splits; s0 += 8) {
-          float v[8];
-#pragma unroll
-          for (uint32_t k = 0; k < 8; k++) v[k] = s0 + k < n_splits ? __ldcg(base + (s0 + k) * stride) : 0.f;
-#pragma unroll
-          for (uint32_t k = 0; k < 8; k++) {
-            if (s0 + k < n_splits) {
-              const float e = ex2(ms[hl * COMBINE_MAX + s0 + k] - m_all);
-              o = fmaf(v[k], e, o);
-              l = fmaf(ls[hl * COMBINE_MAX + s0 + k], e, l);
-            }
-          }
-        }
-        p.out[static_cast<size_t>(h) * BP_HEAD_DIM + d] = __float2half_rn(o * (1.0f / l));
-      }
-    }
-  }
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem, TMEM_COLS);
-  if (p.dbg != nullptr && threadIdx.x == 0) {
+  if (p.dbg != nullptr && threadIdx.x == 0) {  // development aid: span of the launch in ns
     unsigned long long t_exit_ns;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_exit_ns));
     atomicMax(&p.dbg[33], t_exit_ns);
-    atomicMax(&p.dbg[34], static_cast<unsigned long long>(t_start - t_entry));      // set-up cycles
-    atomicMax(&p.dbg[35], static_cast<unsigned long long>(t_loop_end - t_start));   // main loop cycles (warp 0)
-    atomicMax(&p.dbg[36], static_cast<unsigned long long>(clock64() - t_loop_end)); // epilogue cycles
-    atomicMax(&p.dbg[37], t_exit_ns - t_entry_ns);                                   // longest CTA, ns
+    atomicMax(&p.dbg[37], t_exit_ns - t_entry_ns);
   }
 }
 
@@ -593,7 +512,6 @@ cudaError_t bp_launch_decode_umma(bp_attn_ctx* c, cudaStream_t s, uint32_t layer
   p.out = out;
   p.partials = c->partials;
   p.err = c->err_dev;
-  p.tickets = c->tickets;
   p.row_base = layer * c->cfg.max_seq;
   p.cur_pos = cur_pos;
   p.tps = spp * UT;
