@@ -1,21 +1,28 @@
 // Batched-prefill causal attention over the Q8_0 KV cache. Replaces
 // attention.wgsl (dispatch_attention with is_prefill = 1, src/forward.rs:501-532).
 //
-// Flash attention on the 5th-generation tensor cores (tcgen05.mma kind::f16,
-// accumulators in TMEM). One CTA owns one KV head and a tile of 128 query rows:
-// the 128 / qpg consecutive tokens of the tile times the qpg query heads of the
-// group, so every dequantised K/V tile is shared by all heads of the group.
-// Per tile of 128 keys:
-//   producer warp   TMA: int8 K and V tiles (128-byte swizzle) + their FP32 block scales
-//   dequant warps   int8 -> f16 (value * block scale), written as UMMA operand tiles:
-//                   K as the K-major B operand of S = Q K^T, V as the MN-major B operand of O += P V
-//   issuer warp     8 UMMAs (M 128, N 128, K 16) for S into TMEM, 8 for O
-//   softmax warps   thread = query row = TMEM lane: scale, causal mask, online max / sum,
-//                   P as f16 into the K-major A operand tile; O is rescaled in TMEM
-//                   (tcgen05.ld / st) only when a row maximum moved
-// Inside each group of four head dims the operand tiles hold the order
-// (d0, d2, d1, d3): that is what the cheapest int8 expansion yields, it is applied
-// to Q as well (the contraction does not care) and undone when O is written.
+// Two launches per layer:
+//
+// 1. prefill_expand_kernel: the m cache rows the batch just wrote are expanded
+//    once, int8 * FP32 block scale -> f16, into a context-owned scratch
+//    [K | V][rows][kv_dim]. Every key tile is used by m / 32 query tiles, so
+//    expanding it once per layer instead of once per use takes the int8 work
+//    out of the attention loop; the scratch (8 MB at 2048 tokens) stays in L2.
+//
+// 2. prefill_umma_kernel: flash attention on the 5th-generation tensor cores
+//    (tcgen05.mma kind::f16, accumulators in TMEM). A work item is one KV head
+//    and NQ query tiles of 128 rows each; a tile's rows are 128 / qpg
+//    consecutive tokens times the qpg query heads of the group. Persistent
+//    CTAs fetch items, longest first, from a global counter. Per tile of 128
+//    keys and per query tile X:
+//      producer warp   TMA: f16 K and V tiles (128-byte swizzle) straight into UMMA operand layout
+//      issuer warp     S_X = Q_X K^T (8 UMMAs M 128, N 128, K 16) into TMEM;
+//                      O_X += P_X V with P_X read from TMEM as the A operand
+//      softmax group X thread = query row = TMEM lane: scale, causal mask, online max / sum,
+//                      P as f16 written over S_X in TMEM; O_X is rescaled in TMEM only when
+//                      a row maximum grew by more than 2^8 (P stays below 2^8 meanwhile)
+//    With NQ = 2 the tensor core works on one query tile while the other one's
+//    softmax runs.
 // Every wait is bounded; a timeout sets the context's error word and the CTA
 // winds down and frees its TMEM.
 #include "bp_common.cuh"
@@ -24,8 +31,7 @@
 cudaError_t bp_launch_scalar_attention(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, const __half* q,
                                        __half* out, uint32_t cur_pos, uint32_t m, bool is_prefill,
                                        uint32_t* launches);
-bool bp_make_kv_maps(bp_attn_ctx* c, int kind, uint32_t rows_box, uint32_t d_inner, bool d_swizzle,
-                     CUtensorMap* map_qs, CUtensorMap* map_d);
+void* bp_tensor_map_encoder();
 
 namespace {
 
@@ -34,19 +40,26 @@ using namespace bp;
 constexpr unsigned FULL = 0xffffffffu;
 constexpr float NEG_BIG = -1e30f;
 constexpr uint32_t BM = 128, BN = 128;
-constexpr uint32_t P_THREADS = 320;              // producer, issuer, 4 dequant warps, 4 softmax warps
-constexpr uint32_t P_TMEM_COLS = 512;            // S: 2 x 128 columns, O: 128 columns
+constexpr uint32_t P_TMEM_COLS = 512;            // S_A, S_B, O_A, O_B: 128 columns each
 constexpr uint32_t P_WAIT_LIMIT = 1u << 22;
 constexpr uint32_t OPER_B = 2 * 16384;           // one f16 operand tile: 2 chunks of [128 rows][128 B]
-constexpr uint32_t I8_STAGE_B = 2 * 16384 + 2 * 2048;  // int8 K, V tiles + their scale rows
-constexpr uint32_t OFF_Q = 0, OFF_KF = OPER_B, OFF_VF = 2 * OPER_B, OFF_P = 3 * OPER_B, OFF_I8 = 4 * OPER_B;
-constexpr uint32_t P_SMEM = OFF_I8 + 2 * I8_STAGE_B + 1024;
+constexpr uint32_t KV_SLOTS = 2;
+constexpr uint32_t TM_S = 0, TM_O = 256;         // TMEM columns: S_X at TM_S + 128 X, O_X at TM_O + 128 X
+
+template <uint32_t NQ>
+struct PLayout {
+  static constexpr uint32_t THREADS = 64 + NQ * 128;  // producer, issuer, NQ softmax groups of 4 warps
+  static constexpr uint32_t OFF_Q = 0, OFF_K = NQ * OPER_B, OFF_V = OFF_K + KV_SLOTS * OPER_B;
+  static constexpr uint32_t SMEM = OFF_V + KV_SLOTS * OPER_B + 1024;
+};
 
 struct PrefillParams {
   const __half* q;
   __half* out;
   uint32_t* err;
-  uint32_t row_base, m, n_head, qpg, n_qtiles;
+  uint32_t* counter;        // work-item counter, zeroed by the expand kernel of the same layer
+  uint32_t m, n_head, n_kv_head, qpg, n_groups;  // n_groups = ceil(m / (NQ * 128 / qpg))
+  unsigned long long* dbg;  // development aid: cycle counters of CTA 0, null in normal use
   float scale_log2;
 };
 
@@ -55,7 +68,7 @@ __device__ __forceinline__ uint32_t oper_off(uint32_t r, uint32_t u16) {
   return (u16 >> 3) * 16384 + r * 128 + (((u16 & 7) ^ (r & 7)) << 4);
 }
 
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
       "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
@@ -66,7 +79,7 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr)
       : "memory");
 }
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
       "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
@@ -76,271 +89,323 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-// Four int8 of one word -> four f16 scaled by `s2` (both halves the same scale), in the order
-// (b0, b2), (b1, b3): the byte x + 128 under 0x64 is the f16 1024 + x + 128; minus 1152, times scale.
-__device__ __forceinline__ void dequant4(uint32_t w, __half2 s2, uint32_t& even, uint32_t& odd) {
-  const __half2 bias = __half2half2(__ushort_as_half(0x6480));  // 1152
-  const uint32_t x = w ^ 0x80808080u;
-  uint32_t e = (x & 0x00ff00ffu) | 0x64006400u;
-  uint32_t o = ((x >> 8) & 0x00ff00ffu) | 0x64006400u;
-  __half2 eh = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&e), bias), s2);
-  __half2 oh = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&o), bias), s2);
-  even = *reinterpret_cast<uint32_t*>(&eh);
-  odd = *reinterpret_cast<uint32_t*>(&oh);
+// D (TMEM) (+)= A (TMEM: lane = row, one 32-bit column = two consecutive f16 of K) x B (smem descriptor).
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
-// One row (128 int8 + 4 block scales) of a TMA-swizzled int8 tile -> one row of an f16 operand tile.
-// `live` = false writes zeros (keys beyond the sequence: their cache rows are undefined).
-__device__ __forceinline__ void dequant_row(const uint8_t* src_tile, const uint8_t* scales, uint8_t* dst_tile, uint32_t t,
-                                            bool live) {
-  const float4 sc = *reinterpret_cast<const float4*>(scales + t * 16);
-  const float scb[4] = {sc.x, sc.y, sc.z, sc.w};
+// ---------------------------------------------------------------------------------------------
+// Expansion of rows [0, rows_pad) of one layer: rows below m get int8 * scale (product in FP32,
+// rounded once to f16, clamped to the finite range); rows m .. rows_pad - 1 get zeros, so that a
+// masked key can never feed an Inf or NaN into P V. Thread = 8 consecutive dims of one row.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) prefill_expand_kernel(const uint8_t* __restrict__ kv_k, const uint8_t* __restrict__ kv_v,
+                                                             uint64_t d_off, uint64_t qs_off, __half* __restrict__ dst,
+                                                             uint64_t dst_v_off, uint32_t kv_dim, uint32_t m, uint32_t rows_pad,
+                                                             uint32_t* counter) {
+  if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *counter = 0;
+  const uint32_t per_row = kv_dim >> 3;
+  const uint32_t idx = blockIdx.x * 256 + threadIdx.x;
+  const uint32_t row = idx / per_row, u = idx % per_row;
+  if (row >= rows_pad) return;
+  const uint8_t* src = blockIdx.y ? kv_v : kv_k;
+  __half* out = dst + (blockIdx.y ? dst_v_off : 0) + static_cast<size_t>(row) * kv_dim + 8 * u;
+  uint4 w = make_uint4(0, 0, 0, 0);
+  if (row < m) {
+    const float scale = *reinterpret_cast<const float*>(src + d_off + (static_cast<size_t>(row) * (kv_dim >> 5) + (u >> 2)) * 4);
+    const uint2 qv = *reinterpret_cast<const uint2*>(src + qs_off + static_cast<size_t>(row) * kv_dim + 8 * u);
+    const uint32_t qw[2] = {qv.x, qv.y};
+    uint32_t o[4];
 #pragma unroll
-  for (uint32_t c = 0; c < 8; c++) {  // 16-byte chunks of the int8 row: dims 16c .. 16c+15
-    uint4 w = *reinterpret_cast<const uint4*>(src_tile + t * 128 + ((c ^ (t & 7)) << 4));
-    const __half2 s2 = __float2half2_rn(live ? scb[c >> 1] : 0.f);
-    if (!live) w = make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);  // value 0: no NaN from junk
-    uint32_t a[8];
-    dequant4(w.x, s2, a[0], a[1]);
-    dequant4(w.y, s2, a[2], a[3]);
-    dequant4(w.z, s2, a[4], a[5]);
-    dequant4(w.w, s2, a[6], a[7]);
-    *reinterpret_cast<uint4*>(dst_tile + oper_off(t, 2 * c)) = make_uint4(a[0], a[1], a[2], a[3]);
-    *reinterpret_cast<uint4*>(dst_tile + oper_off(t, 2 * c + 1)) = make_uint4(a[4], a[5], a[6], a[7]);
+    for (int j = 0; j < 4; j++) {
+      const int a = static_cast<int8_t>(qw[j >> 1] >> (16 * (j & 1)));
+      const int b = static_cast<int8_t>(qw[j >> 1] >> (16 * (j & 1) + 8));
+      const float fa = fminf(fmaxf(static_cast<float>(a) * scale, -65504.f), 65504.f);
+      const float fb = fminf(fmaxf(static_cast<float>(b) * scale, -65504.f), 65504.f);
+      __half2 h = __floats2half2_rn(fa, fb);
+      o[j] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    w = make_uint4(o[0], o[1], o[2], o[3]);
   }
+  *reinterpret_cast<uint4*>(out) = w;
 }
 
-__global__ void __launch_bounds__(P_THREADS, 1)
-prefill_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_constant__ CUtensorMap map_kd,
-                    const __grid_constant__ CUtensorMap map_vq, const __grid_constant__ CUtensorMap map_vd,
-                    const PrefillParams p) {
+template <uint32_t NQ>
+__global__ void __launch_bounds__(PLayout<NQ>::THREADS, 1)
+prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const PrefillParams p) {
+  using L = PLayout<NQ>;
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t full_bar[2], empty_bar[2], s_ready[2], s_free[2];
-  __shared__ __align__(8) uint64_t kf_ready, kf_free, vf_ready, vf_free, p_ready, o_done;
-  __shared__ uint32_t tmem_base_s;
+  __shared__ __align__(8) uint64_t k_full[KV_SLOTS], k_empty[KV_SLOTS], v_full[KV_SLOTS], v_empty[KV_SLOTS];
+  __shared__ __align__(8) uint64_t s_ready[NQ], p_ready[NQ], o_done[NQ];
+  __shared__ uint32_t tmem_base_s, item_s;
   __shared__ volatile uint32_t abort_s;
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t g = blockIdx.y;
-  const uint32_t qtile = p.n_qtiles - 1 - blockIdx.x;  // long (late) tiles first
   const uint32_t tq_tokens = BM / p.qpg;               // tokens per query tile
-  const uint32_t tq0 = qtile * tq_tokens;
-  const uint32_t n_keys = min(tq0 + tq_tokens, p.m);   // keys [0, n_keys) can be attended by this tile
-  const uint32_t n_tiles = (n_keys + BN - 1) / BN;
+  const uint32_t n_items = p.n_groups * p.n_kv_head;   // work items: (group of NQ query tiles, KV head)
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 2; i++) {
-      mbar_init(smem_u32(&full_bar[i]), 1);
-      mbar_init(smem_u32(&empty_bar[i]), 4);
-      mbar_init(smem_u32(&s_ready[i]), 1);
-      mbar_init(smem_u32(&s_free[i]), 4);
+    for (uint32_t i = 0; i < KV_SLOTS; i++) {
+      mbar_init(smem_u32(&k_full[i]), 1);
+      mbar_init(smem_u32(&k_empty[i]), 1);
+      mbar_init(smem_u32(&v_full[i]), 1);
+      mbar_init(smem_u32(&v_empty[i]), 1);
     }
-    mbar_init(smem_u32(&kf_ready), 4);
-    mbar_init(smem_u32(&kf_free), 1);
-    mbar_init(smem_u32(&vf_ready), 4);
-    mbar_init(smem_u32(&vf_free), 1);
-    mbar_init(smem_u32(&p_ready), 4);
-    mbar_init(smem_u32(&o_done), 1);
+    for (uint32_t x = 0; x < NQ; x++) {
+      mbar_init(smem_u32(&s_ready[x]), 1);
+      mbar_init(smem_u32(&p_ready[x]), 4);
+      mbar_init(smem_u32(&o_done[x]), 1);
+    }
     abort_s = 0;
     fence_barrier_init();
   }
   if (warp == 1) tmem_alloc(smem_u32(&tmem_base_s), P_TMEM_COLS);
-  // Q tile: row r = (token tq0 + r / qpg, head g * qpg + r % qpg), dims in (d0, d2, d1, d3) order.
-  for (uint32_t i = threadIdx.x; i < BM * 16; i += P_THREADS) {
-    const uint32_t r = i >> 4, u = i & 15;
-    const uint32_t tok = tq0 + r / p.qpg, head = g * p.qpg + r % p.qpg;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (tok < p.m) v = *reinterpret_cast<const uint4*>(p.q + (static_cast<size_t>(tok) * p.n_head + head) * BP_HEAD_DIM + 8 * u);
-    const uint4 w = make_uint4(prmt(v.x, v.y, 0x5410), prmt(v.x, v.y, 0x7632), prmt(v.z, v.w, 0x5410), prmt(v.z, v.w, 0x7632));
-    *reinterpret_cast<uint4*>(smem_gen + OFF_Q + oper_off(r, u)) = w;
-  }
-  fence_proxy_async();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_base_s;
 
-  auto wait = [&](uint64_t* bar, uint32_t parity) {
+  const bool dbg_on = p.dbg != nullptr && blockIdx.x == 0 && lane == 0;
+  long long tw[4] = {0, 0, 0, 0};
+  const long long t_begin = clock64();
+  auto waitx = [&](uint64_t* bar, uint32_t parity, int slot) {
     if (abort_s) return;
+    const long long t0 = dbg_on ? clock64() : 0;
     if (!mbar_wait(smem_u32(bar), parity, P_WAIT_LIMIT)) {
       abort_s = 1;
       atomicExch(p.err, 5u);
     }
+    if (dbg_on) tw[slot] += clock64() - t0;
   };
 
-  if (warp == 0) {
-    // ---------------- TMA producer ----------------
-    if (lane == 0) {
-      prefetch_tensormap(&map_kq);
-      prefetch_tensormap(&map_vq);
-      prefetch_tensormap(&map_kd);
-      prefetch_tensormap(&map_vd);
-      for (uint32_t i = 0; i < n_tiles; i++) {
-        const uint32_t s = i & 1, use = i >> 1;
-        if (use > 0) wait(&empty_bar[s], (use - 1) & 1);
-        if (abort_s) break;
-        const uint32_t bar = smem_u32(&full_bar[s]);
-        const uint32_t stage = smem_base + OFF_I8 + s * I8_STAGE_B;
-        const int row = static_cast<int>(p.row_base + i * BN);
-        mbar_arrive_expect_tx(bar, I8_STAGE_B);
-        tma_load_3d(stage, &map_kq, bar, 0, static_cast<int>(g), row);
-        tma_load_2d(stage + 32768, &map_kd, bar, static_cast<int>(g * 16), row);
-        tma_load_3d(stage + 16384, &map_vq, bar, 0, static_cast<int>(g), row);
-        tma_load_2d(stage + 32768 + 2048, &map_vd, bar, static_cast<int>(g * 16), row);
-      }
-    }
-  } else if (warp == 1) {
-    // ---------------- UMMA issuer ----------------
-    if (lane == 0) {
-      constexpr uint32_t IDESC_QK = umma_idesc(1, 0, 0, 0, 0, BM, BN);  // f32 = f16 (K-major) x f16 (K-major)
-      constexpr uint32_t IDESC_PV = umma_idesc(1, 0, 0, 0, 1, BM, BN);  // f32 += f16 (K-major) x f16 (MN-major)
-      const uint64_t dk = umma_desc_sw128(0, 16, 1024);       // K-major operands
-      const uint64_t dmn = umma_desc_sw128(0, 16384, 1024);   // V: next 64 dims 16 KB away, 8 key rows 1 KB apart
-      const uint64_t qa = dk + ((smem_base + OFF_Q) >> 4), kb = dk + ((smem_base + OFF_KF) >> 4);
-      const uint64_t pa = dk + ((smem_base + OFF_P) >> 4), vb = dmn + ((smem_base + OFF_VF) >> 4);
-      auto issue_qk = [&](uint32_t i) {
-        wait(&kf_ready, i & 1);
-        if (i >= 2) wait(&s_free[i & 1], ((i >> 1) - 1) & 1);
-        tc_fence_after();
+  // Barrier phases keep counting across work items: gkv = key tiles loaded so far by this CTA,
+  // gx[X] = key tiles query tile X has gone through; nothing is re-initialised between items.
+  uint32_t gkv = 0, gx[NQ];
 #pragma unroll
-        for (uint32_t ks = 0; ks < 8; ks++) {  // 16 dims per UMMA: chunk ks / 4, 32 bytes per step inside it
-          const uint32_t o16 = (ks >> 2) * (16384 >> 4) + (ks & 3) * 2;
-          umma_f16(tmem + (i & 1) * BN, qa + o16, kb + o16, IDESC_QK, ks);
-        }
-        umma_commit(smem_u32(&s_ready[i & 1]));
-        umma_commit(smem_u32(&kf_free));
-      };
-      if (n_tiles > 0) issue_qk(0);
-      for (uint32_t i = 0; i < n_tiles; i++) {
-        if (i + 1 < n_tiles) issue_qk(i + 1);
-        wait(&p_ready, i & 1);
-        wait(&vf_ready, i & 1);
-        tc_fence_after();
+  for (uint32_t x = 0; x < NQ; x++) gx[x] = 0;
+
+  for (;;) {
+    if (threadIdx.x == 0) item_s = atomicAdd(p.counter, 1u);
+    __syncthreads();
+    const uint32_t item = item_s;
+    if (item >= n_items) break;
+    const uint32_t g = item % p.n_kv_head;
+    const uint32_t group = p.n_groups - 1 - item / p.n_kv_head;  // long (late) groups first
+    // query tile X: tokens [tq0[X], tq0[X] + tq_tokens); nx[X] key tiles (0 when it lies beyond the batch)
+    uint32_t tq0[NQ], nx[NQ], n_tiles = 0;
 #pragma unroll
-        for (uint32_t ks = 0; ks < 8; ks++) {  // 16 keys per UMMA
-          const uint32_t a16 = (ks >> 2) * (16384 >> 4) + (ks & 3) * 2;
-          umma_f16(tmem + 2 * BN, pa + a16, vb + ks * (16 * 128 >> 4), IDESC_PV, (i | ks) ? 1u : 0u);
-        }
-        umma_commit(smem_u32(&vf_free));
-        umma_commit(smem_u32(&o_done));
-      }
+    for (uint32_t x = 0; x < NQ; x++) {
+      tq0[x] = (group * NQ + x) * tq_tokens;
+      nx[x] = tq0[x] < p.m ? (min(tq0[x] + tq_tokens, p.m) + BN - 1) / BN : 0;
+      n_tiles = max(n_tiles, nx[x]);
     }
-  } else if (warp < 6) {
-    // ---------------- dequant: thread = key row of the tile ----------------
-    const uint32_t t = (warp - 2) * 32 + lane;
-    for (uint32_t i = 0; i < n_tiles; i++) {
-      const uint32_t s = i & 1;
-      const uint8_t* stage = smem_gen + OFF_I8 + s * I8_STAGE_B;
-      const bool live = i * BN + t < n_keys;
-      wait(&full_bar[s], (i >> 1) & 1);
-      if (i > 0) wait(&kf_free, (i - 1) & 1);
-      dequant_row(stage, stage + 32768, smem_gen + OFF_KF, t, live);
-      fence_proxy_async();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&kf_ready));
-      if (i > 0) wait(&vf_free, (i - 1) & 1);
-      dequant_row(stage + 16384, stage + 32768 + 2048, smem_gen + OFF_VF, t, live);
-      fence_proxy_async();
-      __syncwarp();
+    // Q tiles as K-major A operands: row r = (token tq0 + r / qpg, head g * qpg + r % qpg)
+    for (uint32_t i = threadIdx.x; i < NQ * BM * 16; i += L::THREADS) {
+      const uint32_t x = i / (BM * 16), r = (i >> 4) & (BM - 1), u = i & 15;
+      const uint32_t tok = (group * NQ + x) * tq_tokens + r / p.qpg, head = g * p.qpg + r % p.qpg;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (tok < p.m) v = *reinterpret_cast<const uint4*>(p.q + (static_cast<size_t>(tok) * p.n_head + head) * BP_HEAD_DIM + 8 * u);
+      *reinterpret_cast<uint4*>(smem_gen + L::OFF_Q + x * OPER_B + oper_off(r, u)) = v;
+    }
+    fence_proxy_async();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+
+    if (warp == 0) {
+      // ---------------- TMA producer ----------------
       if (lane == 0) {
-        mbar_arrive(smem_u32(&vf_ready));
-        mbar_arrive(smem_u32(&empty_bar[s]));
+        prefetch_tensormap(&map_k);
+        prefetch_tensormap(&map_v);
+        for (uint32_t i = 0; i < n_tiles; i++) {
+          const uint32_t s = (gkv + i) % KV_SLOTS, use = (gkv + i) / KV_SLOTS;
+          const int row = static_cast<int>(i * BN);
+          if (use > 0) waitx(&k_empty[s], (use - 1) & 1, 0);
+          if (abort_s) break;
+          mbar_arrive_expect_tx(smem_u32(&k_full[s]), OPER_B);
+          tma_load_3d(smem_base + L::OFF_K + s * OPER_B, &map_k, smem_u32(&k_full[s]), 0, row, static_cast<int>(2 * g));
+          if (use > 0) waitx(&v_empty[s], (use - 1) & 1, 1);
+          if (abort_s) break;
+          mbar_arrive_expect_tx(smem_u32(&v_full[s]), OPER_B);
+          tma_load_3d(smem_base + L::OFF_V + s * OPER_B, &map_v, smem_u32(&v_full[s]), 0, row, static_cast<int>(2 * g));
+        }
       }
-    }
-  } else {
-    // ---------------- softmax: thread = query row = TMEM lane ----------------
-    const uint32_t quad = warp & 3, r = quad * 32 + lane;
-    const uint32_t lane_addr = (quad * 32) << 16;
-    const uint32_t tok = tq0 + r / p.qpg, head = g * p.qpg + r % p.qpg;
-    float m_run = NEG_BIG, l_run = 0.f;
-    for (uint32_t i = 0; i < n_tiles; i++) {
-      const uint32_t b = i & 1;
-      wait(&s_ready[b], (i >> 1) & 1);
-      tc_fence_after();
-      float sc[128];
+    } else if (warp == 1) {
+      // ---------------- UMMA issuer ----------------
+      if (lane == 0) {
+        constexpr uint32_t IDESC_QK = umma_idesc(1, 0, 0, 0, 0, BM, BN);  // f32 = f16 (K-major) x f16 (K-major)
+        constexpr uint32_t IDESC_PV = umma_idesc(1, 0, 0, 0, 1, BM, BN);  // f32 += f16 (TMEM) x f16 (MN-major)
+        const uint64_t dk = umma_desc_sw128(0, 16, 1024);       // K-major operands
+        const uint64_t dmn = umma_desc_sw128(0, 16384, 1024);   // V: next 64 dims 16 KB away, 8 key rows 1 KB apart
+        auto issue_qk = [&](uint32_t x, uint32_t i) {
+          const uint32_t s = (gkv + i) % KV_SLOTS;
+          const uint64_t qa = dk + ((smem_base + L::OFF_Q + x * OPER_B) >> 4);
+          const uint64_t kb = dk + ((smem_base + L::OFF_K + s * OPER_B) >> 4);
 #pragma unroll
-      for (uint32_t c = 0; c < 4; c++) {
-        uint32_t raw[32];
-        tmem_ld32(tmem + lane_addr + b * BN + 32 * c, raw);
+          for (uint32_t ks = 0; ks < 8; ks++) {  // 16 dims per UMMA: chunk ks / 4, 32 bytes per step inside it
+            const uint32_t o16 = (ks >> 2) * (16384 >> 4) + (ks & 3) * 2;
+            umma_f16(tmem + TM_S + x * BN, qa + o16, kb + o16, IDESC_QK, ks);
+          }
+          umma_commit(smem_u32(&s_ready[x]));
+        };
+        if (n_tiles > 0) {
+          waitx(&k_full[gkv % KV_SLOTS], (gkv / KV_SLOTS) & 1, 0);
+          tc_fence_after();
+#pragma unroll
+          for (uint32_t x = 0; x < NQ; x++)
+            if (nx[x] > 0) issue_qk(x, 0);
+          umma_commit(smem_u32(&k_empty[gkv % KV_SLOTS]));
+        }
+        for (uint32_t i = 0; i < n_tiles; i++) {
+          const uint32_t s = (gkv + i) % KV_SLOTS, par = ((gkv + i) / KV_SLOTS) & 1;
+          const uint64_t vb = dmn + ((smem_base + L::OFF_V + s * OPER_B) >> 4);
+          bool k_next_ok = false;
+          waitx(&v_full[s], par, 1);
+#pragma unroll
+          for (uint32_t x = 0; x < NQ; x++) {
+            if (i < nx[x]) {
+              waitx(&p_ready[x], (gx[x] + i) & 1, 2);
+              tc_fence_after();
+#pragma unroll
+              for (uint32_t ks = 0; ks < 8; ks++)  // 16 keys per UMMA: 8 columns of P, 16 rows of V
+                umma_f16_ts(tmem + TM_O + x * BN, tmem + TM_S + x * BN + 8 * ks, vb + ks * (16 * 128 >> 4), IDESC_PV,
+                            (i | ks) ? 1u : 0u);
+              umma_commit(smem_u32(&o_done[x]));
+            }
+            if (x == NQ - 1) umma_commit(smem_u32(&v_empty[s]));  // the tile's V has no reader left
+            if (i + 1 < nx[x]) {
+              if (!k_next_ok) {
+                waitx(&k_full[(gkv + i + 1) % KV_SLOTS], ((gkv + i + 1) / KV_SLOTS) & 1, 3);
+                tc_fence_after();
+                k_next_ok = true;
+              }
+              issue_qk(x, i + 1);  // overwrites S_X / P_X: ordered after the P V above by the tensor pipe
+            }
+          }
+          if (i + 1 < n_tiles) umma_commit(smem_u32(&k_empty[(gkv + i + 1) % KV_SLOTS]));
+        }
+      }
+    } else {
+      // ---------------- softmax group X: thread = query row = TMEM lane ----------------
+      const uint32_t x = (warp - 2) >> 2, quad = warp & 3, r = quad * 32 + lane;
+      const uint32_t lane_addr = (quad * 32) << 16;
+      const uint32_t s_addr = tmem + lane_addr + TM_S + x * BN, o_addr = tmem + lane_addr + TM_O + x * BN;
+      const uint32_t tok = tq0[x] + r / p.qpg, head = g * p.qpg + r % p.qpg;
+      const uint32_t n_mine = nx[x], c0 = gx[x];
+      float m_run = NEG_BIG, l_run = 0.f;
+      for (uint32_t i = 0; i < n_mine; i++) {
+        waitx(&s_ready[x], (c0 + i) & 1, 0);
+        tc_fence_after();
+        uint32_t raw[128];
+#pragma unroll
+        for (uint32_t c = 0; c < 4; c++) tmem_ld32(s_addr + 32 * c, raw + 32 * c);
         tmem_ld_wait();
+        // causal mask: key i * BN + c is visible to this row iff key <= tok (only the last tile can cut)
+        if ((i + 1) * BN > tq0[x] + 1) {
+          const uint32_t k0 = i * BN;
 #pragma unroll
-        for (int j = 0; j < 32; j++) sc[32 * c + j] = __uint_as_float(raw[j]);
+          for (int c = 0; c < 128; c++)
+            if (k0 + c > tok) raw[c] = __float_as_uint(NEG_BIG);
+        }
+        float mx[4] = {__uint_as_float(raw[0]), __uint_as_float(raw[1]), __uint_as_float(raw[2]), __uint_as_float(raw[3])};
+#pragma unroll
+        for (int c = 4; c < 128; c += 4) {
+#pragma unroll
+          for (int k = 0; k < 4; k++) mx[k] = fmaxf(mx[k], __uint_as_float(raw[c + k]));
+        }
+        const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
+        const bool grow = m_tile > m_run + 8.0f;        // lazy: keep the old maximum while P stays below 2^8
+        const float m_new = grow ? m_tile : m_run;
+        const float corr = grow ? ex2(m_run - m_new) : 1.0f;
+        m_run = m_new;
+        if (i > 0 && __any_sync(FULL, grow)) {
+          // O_X += P V of the previous tile must have completed before O_X is rescaled
+          waitx(&o_done[x], (c0 + i - 1) & 1, 1);
+          tc_fence_after();
+#pragma unroll 1
+          for (uint32_t c = 0; c < 8; c++) {  // 16 columns at a time: the row's 128 S values stay live in registers
+            uint32_t o[16];
+            tmem_ld16(o_addr + 16 * c, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; j++) o[j] = __float_as_uint(__uint_as_float(o[j]) * corr);
+            tmem_st16(o_addr + 16 * c, o);
+          }
+        }
+        // P over the first 64 columns of S_X (every S value of this row is in registers by now)
+        float sum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int hf = 0; hf < 2; hf++) {
+          uint32_t ph[32];
+#pragma unroll
+          for (int c = 0; c < 32; c++) {
+            const float p0 = ex2(fmaf(__uint_as_float(raw[64 * hf + 2 * c]), p.scale_log2, -m_new));
+            const float p1 = ex2(fmaf(__uint_as_float(raw[64 * hf + 2 * c + 1]), p.scale_log2, -m_new));
+            sum[c & 3] += p0 + p1;
+            __half2 h = __floats2half2_rn(p0, p1);
+            ph[c] = *reinterpret_cast<uint32_t*>(&h);
+          }
+          tmem_st32(s_addr + 32 * hf, ph);
+        }
+        l_run = l_run * corr + ((sum[0] + sum[1]) + (sum[2] + sum[3]));
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&p_ready[x]));
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&s_free[b]));
-      // causal mask: key i*BN + c is visible to this row iff key <= tok (only the last tile can cut)
-      if ((i + 1) * BN > tq0 + 1) {
-        const uint32_t k0 = i * BN;
-#pragma unroll
-        for (int c = 0; c < 128; c++) if (k0 + c > tok) sc[c] = NEG_BIG;
-      }
-      float mx = sc[0];
-#pragma unroll
-      for (int c = 1; c < 128; c++) mx = fmaxf(mx, sc[c]);
-      const float m_new = fmaxf(m_run, mx * p.scale_log2);
-      const float corr = ex2(m_run - m_new);
-      const bool moved = m_new > m_run;
-      m_run = m_new;
-      float sum = 0.f;
-      uint32_t ph[64];
-#pragma unroll
-      for (int c = 0; c < 64; c++) {
-        const float p0 = ex2(fmaf(sc[2 * c], p.scale_log2, -m_new));
-        const float p1 = ex2(fmaf(sc[2 * c + 1], p.scale_log2, -m_new));
-        sum += p0 + p1;
-        __half2 h = __floats2half2_rn(p0, p1);
-        ph[c] = *reinterpret_cast<uint32_t*>(&h);
-      }
-      l_run = l_run * corr + sum;
-      // P and O are single-buffered: the previous tile's O += P V must have completed
-      if (i > 0) wait(&o_done, (i - 1) & 1);
-      tc_fence_after();
-      if (i > 0 && __any_sync(FULL, moved)) {
+      // ---- O / l -> f16 ----
+      if (n_mine > 0) {
+        waitx(&o_done[x], (c0 + n_mine - 1) & 1, 2);
+        tc_fence_after();
+        const float inv_l = 1.0f / l_run;
+        __half* dst = p.out + (static_cast<size_t>(tok) * p.n_head + head) * BP_HEAD_DIM;
 #pragma unroll
         for (uint32_t c = 0; c < 4; c++) {
           uint32_t o[32];
-          tmem_ld32(tmem + lane_addr + 2 * BN + 32 * c, o);
+          tmem_ld32(o_addr + 32 * c, o);
           tmem_ld_wait();
+          if (tok < p.m) {
 #pragma unroll
-          for (int j = 0; j < 32; j++) o[j] = __float_as_uint(__uint_as_float(o[j]) * corr);
-          tmem_st32(tmem + lane_addr + 2 * BN + 32 * c, o);
+            for (int q8 = 0; q8 < 4; q8++) {
+              uint32_t w[4];
+#pragma unroll
+              for (int k = 0; k < 4; k++) {
+                __half2 h = __floats2half2_rn(__uint_as_float(o[8 * q8 + 2 * k]) * inv_l, __uint_as_float(o[8 * q8 + 2 * k + 1]) * inv_l);
+                w[k] = *reinterpret_cast<uint32_t*>(&h);
+              }
+              *reinterpret_cast<uint4*>(dst + 32 * c + 8 * q8) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          }
         }
-        tmem_st_wait();
       }
-#pragma unroll
-      for (uint32_t u = 0; u < 16; u++)
-        *reinterpret_cast<uint4*>(smem_gen + OFF_P + oper_off(r, u)) = make_uint4(ph[4 * u], ph[4 * u + 1], ph[4 * u + 2], ph[4 * u + 3]);
-      fence_proxy_async();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&p_ready));
     }
-    // ---- O / l -> f16, undoing the (d0, d2, d1, d3) order ----
-    if (n_tiles > 0) wait(&o_done, (n_tiles - 1) & 1);
+    gkv += n_tiles;
+#pragma unroll
+    for (uint32_t x = 0; x < NQ; x++) gx[x] += nx[x];
+    tc_fence_before();
+    __syncthreads();  // the item is finished by every role: Q, S and O can be reused
     tc_fence_after();
-    const float inv_l = 1.0f / l_run;
-    __half* dst = p.out + (static_cast<size_t>(tok) * p.n_head + head) * BP_HEAD_DIM;
-#pragma unroll
-    for (uint32_t c = 0; c < 4; c++) {
-      uint32_t o[32];
-      tmem_ld32(tmem + lane_addr + 2 * BN + 32 * c, o);
-      tmem_ld_wait();
-      if (tok < p.m) {
-#pragma unroll
-        for (int q4 = 0; q4 < 8; q4++) {  // columns (4q4 .. 4q4+3) hold dims (d0, d2, d1, d3)
-          const float d0 = __uint_as_float(o[4 * q4]) * inv_l, d2 = __uint_as_float(o[4 * q4 + 1]) * inv_l;
-          const float d1 = __uint_as_float(o[4 * q4 + 2]) * inv_l, d3 = __uint_as_float(o[4 * q4 + 3]) * inv_l;
-          __half2 lo = __floats2half2_rn(d0, d1), hi = __floats2half2_rn(d2, d3);
-          *reinterpret_cast<uint2*>(dst + 32 * c + 4 * q4) =
-              make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
-        }
-      }
-    }
+  }
+  if (dbg_on && (warp == 0 || warp == 1 || warp == 2 || warp == 6)) {
+    const uint32_t role = warp == 0 ? 0 : warp == 1 ? 1 : warp == 2 ? 2 : 3;
+    p.dbg[role * 8] = static_cast<unsigned long long>(clock64() - t_begin);
+    for (int k = 0; k < 4; k++) p.dbg[role * 8 + 1 + k] = static_cast<unsigned long long>(tw[k]);
+    p.dbg[role * 8 + 7] = gkv;
   }
   tc_fence_before();
   __syncthreads();
@@ -351,30 +416,76 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_con
 
 uint32_t bp_prefill_stage_tokens() { return BN; }
 
+// Scratch of the expanded rows and the tensor maps over it: f16 (64 dims, rows, kv_dim / 64
+// chunks) with a (64, 128, 2) box, so one load yields [2 chunks][128 rows][128 B] with the
+// 128-byte swizzle: the K-major operand of Q K^T and, read MN-major, the B operand of P V.
 cudaError_t bp_prefill_init(bp_attn_ctx* c) {
-  c->have_pmaps = true;
-  for (int kind = 0; kind < 2 && c->have_pmaps; kind++)
-    c->have_pmaps = bp_make_kv_maps(c, kind, BN, 16, false, &c->pmap_qs[kind], &c->pmap_d[kind]);
-  return cudaFuncSetAttribute(prefill_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(P_SMEM));
+  typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  const uint32_t max_m = bp_attn_max_prefill(c);
+  c->pf_rows = (max_m + BN - 1) / BN * BN;
+  const size_t halves = static_cast<size_t>(c->pf_rows) * c->kv_dim;
+  cudaError_t e = cudaMalloc(&c->pf_kv16, 2 * halves * sizeof(__half) + 256);
+  if (e != cudaSuccess) return e;
+  e = cudaMemset(c->pf_kv16, 0, 2 * halves * sizeof(__half) + 256);
+  if (e != cudaSuccess) return e;
+  c->pf_counter = reinterpret_cast<uint32_t*>(c->pf_kv16 + 2 * halves);
+  encode_fn encode = reinterpret_cast<encode_fn>(bp_tensor_map_encoder());
+  c->have_pmaps = encode != nullptr;
+  for (int kind = 0; kind < 2 && c->have_pmaps; kind++) {
+    cuuint64_t dims[3] = {64, c->pf_rows, c->kv_dim / 64};
+    cuuint64_t strides[2] = {static_cast<cuuint64_t>(c->kv_dim) * 2, 128};
+    cuuint32_t box[3] = {64, BN, 2};
+    cuuint32_t es[3] = {1, 1, 1};
+    c->have_pmaps = encode(&c->pmap16[kind], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, c->pf_kv16 + kind * halves, dims, strides, box,
+                           es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  }
+  e = cudaFuncSetAttribute(prefill_umma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(PLayout<1>::SMEM));
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(prefill_umma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(PLayout<2>::SMEM));
 }
 
 cudaError_t bp_launch_prefill(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, const __half* q,
                               __half* out, uint32_t m, uint32_t* launches) {
-  const bool pow2 = (c->qpg & (c->qpg - 1)) == 0;
+  const bool pow2 = (c->qpg & (c->qpg - 1)) == 0 && c->qpg <= BM;
   if (c->variant == 1 || !c->have_pmaps || !pow2) return bp_launch_scalar_attention(c, s, layer, q, out, m, m, true, launches);
+  const uint32_t rows_pad = (m + BN - 1) / BN * BN;
+  {
+    const uint32_t threads = rows_pad * (c->kv_dim >> 3);
+    dim3 grid((threads + 255) / 256, 2);
+    prefill_expand_kernel<<<grid, 256, 0, s>>>(c->kv[0], c->kv[1], bp_d_off(c, layer), bp_qs_off(c, layer), c->pf_kv16,
+                                               static_cast<uint64_t>(c->pf_rows) * c->kv_dim, c->kv_dim, m, rows_pad,
+                                               c->pf_counter);
+    *launches += 1;
+  }
   PrefillParams p;
   p.q = q;
   p.out = out;
   p.err = c->err_dev;
-  p.row_base = layer * c->cfg.max_seq;
+  p.counter = c->pf_counter;
   p.m = m;
   p.n_head = c->cfg.n_head;
+  p.n_kv_head = c->cfg.n_kv_head;
+  p.dbg = c->dbg_on ? c->dbg_dev : nullptr;
   p.qpg = c->qpg;
-  const uint32_t tq_tokens = BM / c->qpg;
-  p.n_qtiles = (m + tq_tokens - 1) / tq_tokens;
   p.scale_log2 = (1.0f / sqrtf(static_cast<float>(BP_HEAD_DIM))) * 1.4426950408889634f;
-  dim3 grid(p.n_qtiles, c->cfg.n_kv_head);
-  prefill_umma_kernel<<<grid, P_THREADS, P_SMEM, s>>>(c->pmap_qs[0], c->pmap_d[0], c->pmap_qs[1], c->pmap_d[1], p);
+  const uint32_t tq_tokens = BM / c->qpg;
+  const uint32_t sms = static_cast<uint32_t>(c->sm_count);
+  // Two query tiles per item keep the tensor core busy during softmax; a batch too small to give
+  // every SM such an item is cut into single tiles instead.
+  const uint32_t groups2 = (m + 2 * tq_tokens - 1) / (2 * tq_tokens);
+  const bool pair = c->opt_pf_nq == 2 || (c->opt_pf_nq == 0 && groups2 * c->cfg.n_kv_head >= sms);
+  if (pair) {
+    p.n_groups = groups2;
+    const uint32_t n_items = p.n_groups * c->cfg.n_kv_head;
+    prefill_umma_kernel<2><<<n_items < sms ? n_items : sms, PLayout<2>::THREADS, PLayout<2>::SMEM, s>>>(c->pmap16[0], c->pmap16[1], p);
+  } else {
+    p.n_groups = (m + tq_tokens - 1) / tq_tokens;
+    const uint32_t n_items = p.n_groups * c->cfg.n_kv_head;
+    prefill_umma_kernel<1><<<n_items < sms ? n_items : sms, PLayout<1>::THREADS, PLayout<1>::SMEM, s>>>(c->pmap16[0], c->pmap16[1], p);
+  }
   *launches += 1;
   return cudaGetLastError();
 }

@@ -34,8 +34,12 @@ struct bp_attn_ctx {
   CUtensorMap umap_qs[2];  // tcgen05 decode: 128-token boxes
   CUtensorMap umap_d[2];
   bool have_umaps;
-  CUtensorMap pmap_qs[2];  // tcgen05 prefill: 128-key boxes, one head
-  CUtensorMap pmap_d[2];
+  // tcgen05 prefill: f16 expansion of the batch's cache rows [K | V][pf_rows][kv_dim], its
+  // tensor maps (128-key boxes of one head) and the work-item counter behind it
+  __half* pf_kv16;
+  uint32_t pf_rows;
+  uint32_t* pf_counter;
+  CUtensorMap pmap16[2];
   bool have_pmaps;
   // staging for the *_host entry points
   __half *stage_q, *stage_k, *stage_v, *stage_out, *stage_wq, *stage_wk;
@@ -46,6 +50,7 @@ struct bp_attn_ctx {
   uint32_t opt_nw;   // decode: compute warps per CTA (8 or 16)
   uint32_t opt_hpc;  // decode: KV heads per CTA (divides n_kv_head)
   uint32_t opt_uhpc; // tcgen05 decode: KV heads per CTA (1 or 2)
+  uint32_t opt_pf_nq; // prefill: query tiles per work item (1 or 2), 0 = by batch size
   uint32_t last_launches;
   int status;  // latched device-lost status, BP_OK otherwise
   bp_error_detail detail;

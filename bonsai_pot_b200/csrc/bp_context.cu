@@ -105,6 +105,11 @@ encode_tiled_fn get_encode() {
 
 }  // namespace
 
+void* bp_tensor_map_encoder() {
+  static encode_tiled_fn encode = get_encode();
+  return reinterpret_cast<void*>(encode);
+}
+
 // Tensor maps over one cache buffer. Quants: u8 (128 B, kv heads, rows) with a
 // (128, 1, rows_box) box; scales: u8 (row bytes, rows) with an (inner, rows_box)
 // box at byte offset `inner`-aligned. Rows run over all layers.
@@ -260,6 +265,7 @@ void bp_attn_destroy(bp_attn_ctx* c) {
   cudaFree(c->rope);
   cudaFree(c->partials);
   cudaFree(c->tickets);
+  cudaFree(c->pf_kv16);
   cudaFree(c->dbg_dev);
   if (c->err_host) cudaFreeHost(c->err_host);
   cudaFree(c->stage_q);
@@ -604,6 +610,10 @@ int bp_set_option(bp_attn_ctx* c, const char* name, uint32_t value) {
     if ((value != 1 && value != 2) || c->cfg.n_kv_head % value != 0)
       return fail_config(c, "decode_umma_heads_per_cta must be 1 or 2 and divide n_kv_head");
     c->opt_uhpc = value;
+  } else if (strcmp(name, "prefill_tiles_per_item") == 0) {
+    if (value > 2) return fail_config(c, "prefill_tiles_per_item must be 0 (by batch size), 1 or 2");
+    c->opt_pf_nq = value;
+    return BP_OK;
   } else {
     return fail_config(c, "unknown option");
   }

@@ -192,7 +192,9 @@ int bp_rope_table_copy(bp_attn_ctx* ctx, void* host_f16);      /* host copy of t
 int bp_set_variant(bp_attn_ctx* ctx, uint32_t variant);
 /* Tuning knobs of the decode kernel: "decode_warps" (8 or 16 compute warps per
  * CTA) and "decode_heads_per_cta" (KV heads streamed by one CTA; a power of two
- * dividing n_kv_head). Results do not depend on them beyond rounding. */
+ * dividing n_kv_head), "decode_umma_heads_per_cta" (1 or 2, tcgen05 decode) and
+ * "prefill_tiles_per_item" (query tiles one prefill work item owns: 1, 2, or 0 =
+ * chosen by batch size). Results do not depend on them beyond rounding. */
 int bp_set_option(bp_attn_ctx* ctx, const char* name, uint32_t value);
 /* Development aid: with the option "debug_counters" set to 1 the tcgen05 decode
  * kernel's first CTA records, per warp role (producer, UMMA issuer, softmax,
