@@ -48,7 +48,7 @@ constexpr uint32_t TM_S = 0, TM_O = 256;         // TMEM columns: S_X at TM_S + 
 
 template <uint32_t NQ>
 struct PLayout {
-  static constexpr uint32_t THREADS = 64 + NQ * 128;  // producer, issuer, NQ softmax groups of 4 warps
+  static constexpr uint32_t THREADS = 32 + NQ * 32 + NQ * 128;  // producer, NQ issuers, NQ softmax groups of 4 warps
   static constexpr uint32_t OFF_Q = 0, OFF_K = NQ * OPER_B, OFF_V = OFF_K + KV_SLOTS * OPER_B;
   static constexpr uint32_t SMEM = OFF_V + KV_SLOTS * OPER_B + 1024;
 };
@@ -60,6 +60,7 @@ struct PrefillParams {
   uint32_t* counter;        // work-item counter, zeroed by the expand kernel of the same layer
   uint32_t m, n_head, n_kv_head, qpg, n_groups;  // n_groups = ceil(m / (NQ * 128 / qpg))
   unsigned long long* dbg;  // development aid: cycle counters of CTA 0, null in normal use
+  uint32_t flags;           // bit 0: stagger the query tiles of an item
   float scale_log2;
 };
 
@@ -148,7 +149,8 @@ __global__ void __launch_bounds__(PLayout<NQ>::THREADS, 1)
 prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const PrefillParams p) {
   using L = PLayout<NQ>;
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t k_full[KV_SLOTS], k_empty[KV_SLOTS], v_full[KV_SLOTS], v_empty[KV_SLOTS];
+  __shared__ __align__(8) uint64_t k_full[KV_SLOTS], v_full[KV_SLOTS];
+  __shared__ __align__(8) uint64_t k_empty[NQ][KV_SLOTS], v_empty[NQ][KV_SLOTS];  // per query tile: it is done with the slot
   __shared__ __align__(8) uint64_t s_ready[NQ], p_ready[NQ], o_done[NQ];
   __shared__ uint32_t tmem_base_s, item_s;
   __shared__ volatile uint32_t abort_s;
@@ -162,9 +164,11 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   if (threadIdx.x == 0) {
     for (uint32_t i = 0; i < KV_SLOTS; i++) {
       mbar_init(smem_u32(&k_full[i]), 1);
-      mbar_init(smem_u32(&k_empty[i]), 1);
       mbar_init(smem_u32(&v_full[i]), 1);
-      mbar_init(smem_u32(&v_empty[i]), 1);
+      for (uint32_t x = 0; x < NQ; x++) {
+        mbar_init(smem_u32(&k_empty[x][i]), 1);
+        mbar_init(smem_u32(&v_empty[x][i]), 1);
+      }
     }
     for (uint32_t x = 0; x < NQ; x++) {
       mbar_init(smem_u32(&s_ready[x]), 1);
@@ -194,12 +198,16 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   };
 
   // Barrier phases keep counting across work items: gkv = key tiles loaded so far by this CTA,
-  // gx[X] = key tiles query tile X has gone through; nothing is re-initialised between items.
-  uint32_t gkv = 0, gx[NQ];
+  // gx[X] = key tiles query tile X has gone through, items_done for the once-per-item o_done;
+  // nothing is re-initialised between items. The producer keeps, per (query tile, slot), whether
+  // a release is outstanding and the phase it will complete (bit x * KV_SLOTS + slot).
+  uint32_t gkv = 0, gx[NQ], od[NQ];
 #pragma unroll
-  for (uint32_t x = 0; x < NQ; x++) gx[x] = 0;
+  for (uint32_t x = 0; x < NQ; x++) { gx[x] = 0; od[x] = 0; }
+  uint32_t pend_k = 0, pend_v = 0, phase_k = 0, phase_v = 0;
 
   for (;;) {
+    // An item is fetched only when the CTA is free (fetching ahead would defeat longest-first balancing).
     if (threadIdx.x == 0) item_s = atomicAdd(p.counter, 1u);
     __syncthreads();
     const uint32_t item = item_s;
@@ -215,12 +223,24 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       n_tiles = max(n_tiles, nx[x]);
     }
     // Q tiles as K-major A operands: row r = (token tq0 + r / qpg, head g * qpg + r % qpg)
-    for (uint32_t i = threadIdx.x; i < NQ * BM * 16; i += L::THREADS) {
-      const uint32_t x = i / (BM * 16), r = (i >> 4) & (BM - 1), u = i & 15;
-      const uint32_t tok = (group * NQ + x) * tq_tokens + r / p.qpg, head = g * p.qpg + r % p.qpg;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (tok < p.m) v = *reinterpret_cast<const uint4*>(p.q + (static_cast<size_t>(tok) * p.n_head + head) * BP_HEAD_DIM + 8 * u);
-      *reinterpret_cast<uint4*>(smem_gen + L::OFF_Q + x * OPER_B + oper_off(r, u)) = v;
+    {
+      constexpr uint32_t Q_UNITS = NQ * BM * 16, Q_ITERS = (Q_UNITS + L::THREADS - 1) / L::THREADS;
+      uint4 qv[Q_ITERS];
+#pragma unroll
+      for (uint32_t k = 0; k < Q_ITERS; k++) {  // every load of this thread is in flight before the first store
+        const uint32_t i = threadIdx.x + k * L::THREADS;
+        const uint32_t x = i / (BM * 16), r = (i >> 4) & (BM - 1), u = i & 15;
+        const uint32_t tok = (group * NQ + x) * tq_tokens + r / p.qpg, head = g * p.qpg + r % p.qpg;
+        qv[k] = make_uint4(0, 0, 0, 0);
+        if (i < Q_UNITS && tok < p.m)
+          qv[k] = *reinterpret_cast<const uint4*>(p.q + (static_cast<size_t>(tok) * p.n_head + head) * BP_HEAD_DIM + 8 * u);
+      }
+#pragma unroll
+      for (uint32_t k = 0; k < Q_ITERS; k++) {
+        const uint32_t i = threadIdx.x + k * L::THREADS;
+        const uint32_t x = i / (BM * 16), r = (i >> 4) & (BM - 1), u = i & 15;
+        if (i < Q_UNITS) *reinterpret_cast<uint4*>(smem_gen + L::OFF_Q + x * OPER_B + oper_off(r, u)) = qv[k];
+      }
     }
     fence_proxy_async();
     tc_fence_before();
@@ -233,76 +253,87 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         prefetch_tensormap(&map_k);
         prefetch_tensormap(&map_v);
         for (uint32_t i = 0; i < n_tiles; i++) {
-          const uint32_t s = (gkv + i) % KV_SLOTS, use = (gkv + i) / KV_SLOTS;
+          const uint32_t s = (gkv + i) % KV_SLOTS;
           const int row = static_cast<int>(i * BN);
-          if (use > 0) waitx(&k_empty[s], (use - 1) & 1, 0);
+          uint32_t users = 0, slot_bits = 0;  // query tiles that read tile i; all query tiles' bits of slot s
+#pragma unroll
+          for (uint32_t x = 0; x < NQ; x++) {
+            users |= (i < nx[x] ? 1u : 0u) << (x * KV_SLOTS + s);
+            slot_bits |= 1u << (x * KV_SLOTS + s);
+          }
+#pragma unroll
+          for (uint32_t x = 0; x < NQ; x++) {
+            const uint32_t bit = 1u << (x * KV_SLOTS + s);
+            if (pend_k & bit) {
+              waitx(&k_empty[x][s], (phase_k & bit) ? 1u : 0u, 0);
+              phase_k ^= bit;
+            }
+          }
+          pend_k = (pend_k & ~slot_bits) | users;
           if (abort_s) break;
           mbar_arrive_expect_tx(smem_u32(&k_full[s]), OPER_B);
           tma_load_3d(smem_base + L::OFF_K + s * OPER_B, &map_k, smem_u32(&k_full[s]), 0, row, static_cast<int>(2 * g));
-          if (use > 0) waitx(&v_empty[s], (use - 1) & 1, 1);
+#pragma unroll
+          for (uint32_t x = 0; x < NQ; x++) {
+            const uint32_t bit = 1u << (x * KV_SLOTS + s);
+            if (pend_v & bit) {
+              waitx(&v_empty[x][s], (phase_v & bit) ? 1u : 0u, 1);
+              phase_v ^= bit;
+            }
+          }
+          pend_v = (pend_v & ~slot_bits) | users;
           if (abort_s) break;
           mbar_arrive_expect_tx(smem_u32(&v_full[s]), OPER_B);
           tma_load_3d(smem_base + L::OFF_V + s * OPER_B, &map_v, smem_u32(&v_full[s]), 0, row, static_cast<int>(2 * g));
         }
       }
-    } else if (warp == 1) {
-      // ---------------- UMMA issuer ----------------
-      if (lane == 0) {
+    } else if (warp <= NQ) {
+      // ---------------- UMMA issuer of query tile X ----------------
+      // One issuing thread sustains about one tcgen05.mma per 100 cycles, a 128 x 128 x 16 MMA takes
+      // 64: each query tile has its own issuer so that the tensor pipe is fed from two threads.
+      const uint32_t x = warp - 1;
+      const uint32_t n_mine = nx[x], c0 = gx[x];
+      if (lane == 0 && n_mine > 0) {
         constexpr uint32_t IDESC_QK = umma_idesc(1, 0, 0, 0, 0, BM, BN);  // f32 = f16 (K-major) x f16 (K-major)
         constexpr uint32_t IDESC_PV = umma_idesc(1, 0, 0, 0, 1, BM, BN);  // f32 += f16 (TMEM) x f16 (MN-major)
         const uint64_t dk = umma_desc_sw128(0, 16, 1024);       // K-major operands
         const uint64_t dmn = umma_desc_sw128(0, 16384, 1024);   // V: next 64 dims 16 KB away, 8 key rows 1 KB apart
-        auto issue_qk = [&](uint32_t x, uint32_t i) {
+        const uint64_t qa = dk + ((smem_base + L::OFF_Q + x * OPER_B) >> 4);
+        const uint32_t s_col = tmem + TM_S + x * BN, o_col = tmem + TM_O + x * BN;
+        auto issue_qk = [&](uint32_t i) {
           const uint32_t s = (gkv + i) % KV_SLOTS;
-          const uint64_t qa = dk + ((smem_base + L::OFF_Q + x * OPER_B) >> 4);
+          waitx(&k_full[s], ((gkv + i) / KV_SLOTS) & 1, 0);
+          tc_fence_after();
           const uint64_t kb = dk + ((smem_base + L::OFF_K + s * OPER_B) >> 4);
 #pragma unroll
           for (uint32_t ks = 0; ks < 8; ks++) {  // 16 dims per UMMA: chunk ks / 4, 32 bytes per step inside it
             const uint32_t o16 = (ks >> 2) * (16384 >> 4) + (ks & 3) * 2;
-            umma_f16(tmem + TM_S + x * BN, qa + o16, kb + o16, IDESC_QK, ks);
+            umma_f16(s_col, qa + o16, kb + o16, IDESC_QK, ks);
           }
+          // also tells that every earlier MMA of this thread, the previous tile's P V included, is complete
           umma_commit(smem_u32(&s_ready[x]));
         };
-        if (n_tiles > 0) {
-          waitx(&k_full[gkv % KV_SLOTS], (gkv / KV_SLOTS) & 1, 0);
+        // Start half a period behind the previous query tile, so that one tile's softmax runs while
+        // the other one's MMAs do instead of both contending for the same unit at the same time.
+        if ((p.flags & 1u) && x > 0 && nx[x > 0 ? x - 1 : 0] > 0) waitx(&p_ready[x > 0 ? x - 1 : 0], gx[x > 0 ? x - 1 : 0] & 1, 3);
+        issue_qk(0);
+        for (uint32_t i = 0; i < n_mine; i++) {
+          const uint32_t s = (gkv + i) % KV_SLOTS;
+          const uint64_t vb = dmn + ((smem_base + L::OFF_V + s * OPER_B) >> 4);
+          waitx(&v_full[s], ((gkv + i) / KV_SLOTS) & 1, 1);
+          waitx(&p_ready[x], (c0 + i) & 1, 2);
           tc_fence_after();
 #pragma unroll
-          for (uint32_t x = 0; x < NQ; x++)
-            if (nx[x] > 0) issue_qk(x, 0);
-          umma_commit(smem_u32(&k_empty[gkv % KV_SLOTS]));
-        }
-        for (uint32_t i = 0; i < n_tiles; i++) {
-          const uint32_t s = (gkv + i) % KV_SLOTS, par = ((gkv + i) / KV_SLOTS) & 1;
-          const uint64_t vb = dmn + ((smem_base + L::OFF_V + s * OPER_B) >> 4);
-          bool k_next_ok = false;
-          waitx(&v_full[s], par, 1);
-#pragma unroll
-          for (uint32_t x = 0; x < NQ; x++) {
-            if (i < nx[x]) {
-              waitx(&p_ready[x], (gx[x] + i) & 1, 2);
-              tc_fence_after();
-#pragma unroll
-              for (uint32_t ks = 0; ks < 8; ks++)  // 16 keys per UMMA: 8 columns of P, 16 rows of V
-                umma_f16_ts(tmem + TM_O + x * BN, tmem + TM_S + x * BN + 8 * ks, vb + ks * (16 * 128 >> 4), IDESC_PV,
-                            (i | ks) ? 1u : 0u);
-              umma_commit(smem_u32(&o_done[x]));
-            }
-            if (x == NQ - 1) umma_commit(smem_u32(&v_empty[s]));  // the tile's V has no reader left
-            if (i + 1 < nx[x]) {
-              if (!k_next_ok) {
-                waitx(&k_full[(gkv + i + 1) % KV_SLOTS], ((gkv + i + 1) / KV_SLOTS) & 1, 3);
-                tc_fence_after();
-                k_next_ok = true;
-              }
-              issue_qk(x, i + 1);  // overwrites S_X / P_X: ordered after the P V above by the tensor pipe
-            }
-          }
-          if (i + 1 < n_tiles) umma_commit(smem_u32(&k_empty[(gkv + i + 1) % KV_SLOTS]));
+          for (uint32_t ks = 0; ks < 8; ks++)  // 16 keys per UMMA: 8 columns of P, 16 rows of V
+            umma_f16_ts(o_col, s_col + 8 * ks, vb + ks * (16 * 128 >> 4), IDESC_PV, (i | ks) ? 1u : 0u);
+          if (i + 1 < n_mine) issue_qk(i + 1);  // overwrites S_X / P_X: ordered after the P V above by the tensor pipe
+          else umma_commit(smem_u32(&o_done[x]));
         }
       }
     } else {
       // ---------------- softmax group X: thread = query row = TMEM lane ----------------
-      const uint32_t x = (warp - 2) >> 2, quad = warp & 3, r = quad * 32 + lane;
+      const uint32_t x = (warp - 1 - NQ) >> 2, quad = warp & 3, r = quad * 32 + lane;
+      const bool elected = ((warp - 1 - NQ) & 3) == 0 && lane == 0;  // releases the K / V slots for this query tile
       const uint32_t lane_addr = (quad * 32) << 16;
       const uint32_t s_addr = tmem + lane_addr + TM_S + x * BN, o_addr = tmem + lane_addr + TM_O + x * BN;
       const uint32_t tok = tq0[x] + r / p.qpg, head = g * p.qpg + r % p.qpg;
@@ -311,6 +342,10 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       for (uint32_t i = 0; i < n_mine; i++) {
         waitx(&s_ready[x], (c0 + i) & 1, 0);
         tc_fence_after();
+        if (elected) {  // Q K^T of tile i and P V of tile i - 1 are complete
+          mbar_arrive(smem_u32(&k_empty[x][(gkv + i) % KV_SLOTS]));
+          if (i > 0) mbar_arrive(smem_u32(&v_empty[x][(gkv + i - 1) % KV_SLOTS]));
+        }
         uint32_t raw[128];
 #pragma unroll
         for (uint32_t c = 0; c < 4; c++) tmem_ld32(s_addr + 32 * c, raw + 32 * c);
@@ -334,9 +369,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         const float corr = grow ? ex2(m_run - m_new) : 1.0f;
         m_run = m_new;
         if (i > 0 && __any_sync(FULL, grow)) {
-          // O_X += P V of the previous tile must have completed before O_X is rescaled
-          waitx(&o_done[x], (c0 + i - 1) & 1, 1);
-          tc_fence_after();
+          // O_X is idle here: the previous tile's P V completed before s_ready fired
 #pragma unroll 1
           for (uint32_t c = 0; c < 8; c++) {  // 16 columns at a time: the row's 128 S values stay live in registers
             uint32_t o[16];
@@ -370,8 +403,9 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       }
       // ---- O / l -> f16 ----
       if (n_mine > 0) {
-        waitx(&o_done[x], (c0 + n_mine - 1) & 1, 2);
+        waitx(&o_done[x], od[x] & 1, 2);
         tc_fence_after();
+        if (elected) mbar_arrive(smem_u32(&v_empty[x][(gkv + n_mine - 1) % KV_SLOTS]));
         const float inv_l = 1.0f / l_run;
         __half* dst = p.out + (static_cast<size_t>(tok) * p.n_head + head) * BP_HEAD_DIM;
 #pragma unroll
@@ -396,13 +430,16 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     }
     gkv += n_tiles;
 #pragma unroll
-    for (uint32_t x = 0; x < NQ; x++) gx[x] += nx[x];
+    for (uint32_t x = 0; x < NQ; x++) {
+      gx[x] += nx[x];
+      od[x] += nx[x] > 0 ? 1u : 0u;
+    }
     tc_fence_before();
     __syncthreads();  // the item is finished by every role: Q, S and O can be reused
     tc_fence_after();
   }
-  if (dbg_on && (warp == 0 || warp == 1 || warp == 2 || warp == 6)) {
-    const uint32_t role = warp == 0 ? 0 : warp == 1 ? 1 : warp == 2 ? 2 : 3;
+  if (dbg_on && (warp == 0 || warp == 1 || warp == 1 + NQ || warp == 5 + NQ)) {
+    const uint32_t role = warp == 0 ? 0 : warp == 1 ? 1 : warp == 1 + NQ ? 2 : 3;
     p.dbg[role * 8] = static_cast<unsigned long long>(clock64() - t_begin);
     for (int k = 0; k < 4; k++) p.dbg[role * 8 + 1 + k] = static_cast<unsigned long long>(tw[k]);
     p.dbg[role * 8 + 7] = gkv;
@@ -470,6 +507,7 @@ cudaError_t bp_launch_prefill(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, co
   p.n_kv_head = c->cfg.n_kv_head;
   p.dbg = c->dbg_on ? c->dbg_dev : nullptr;
   p.qpg = c->qpg;
+  p.flags = c->opt_pf_flags;
   p.scale_log2 = (1.0f / sqrtf(static_cast<float>(BP_HEAD_DIM))) * 1.4426950408889634f;
   const uint32_t tq_tokens = BM / c->qpg;
   const uint32_t sms = static_cast<uint32_t>(c->sm_count);

@@ -51,6 +51,7 @@ struct bp_attn_ctx {
   uint32_t opt_hpc;  // decode: KV heads per CTA (divides n_kv_head)
   uint32_t opt_uhpc; // tcgen05 decode: KV heads per CTA (1 or 2)
   uint32_t opt_pf_nq; // prefill: query tiles per work item (1 or 2), 0 = by batch size
+  uint32_t opt_pf_flags; // prefill: scheduling experiments (bit 0: stagger the query tiles of an item)
   uint32_t last_launches;
   int status;  // latched device-lost status, BP_OK otherwise
   bp_error_detail detail;

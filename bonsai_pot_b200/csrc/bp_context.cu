@@ -610,6 +610,9 @@ int bp_set_option(bp_attn_ctx* c, const char* name, uint32_t value) {
     if ((value != 1 && value != 2) || c->cfg.n_kv_head % value != 0)
       return fail_config(c, "decode_umma_heads_per_cta must be 1 or 2 and divide n_kv_head");
     c->opt_uhpc = value;
+  } else if (strcmp(name, "prefill_flags") == 0) {
+    c->opt_pf_flags = value;
+    return BP_OK;
   } else if (strcmp(name, "prefill_tiles_per_item") == 0) {
     if (value > 2) return fail_config(c, "prefill_tiles_per_item must be 0 (by batch size), 1 or 2");
     c->opt_pf_nq = value;
