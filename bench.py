@@ -269,6 +269,8 @@ def run_ours(args):
         ctx.set_option("decode_heads_per_cta", args.decode_hpc)
     if args.decode_uhpc:
         ctx.set_option("decode_umma_heads_per_cta", args.decode_uhpc)
+    if args.no_pdl:
+        ctx.set_option("dependent_launch", 0)
     gen = torch.Generator(device="cuda")
     gen.manual_seed(1234 + rank)
     fill_cache(ctx, torch, N_LAYER, kv_dim_l, ctx_len - 1, gen)
@@ -355,7 +357,7 @@ def run_ours(args):
             traffic = traffic * ctx_len / world if traffic is not None else None
         except Exception:
             traffic = None
-    roofline = {"bound": "hbm", "kernel": "decode_mma_kernel + attn_combine_kernel", "achieved": round(achieved, 1),
+    roofline = {"bound": "hbm", "kernel": "decode_umma_kernel + attn_combine_kernel", "achieved": round(achieved, 1),
                 "peak": hbm_peak, "unit": "GB/s", "frac": round(achieved / hbm_peak, 4), "peak_kind": peak_kind,
                 "us_per_launch": round(dt_k * 1e6, 3), "algorithmic_bytes_per_launch": algo_bytes_launch,
                 "traffic": traffic, "frac_of_8000_spec": round(achieved / 8000.0, 4)}
@@ -494,6 +496,7 @@ def main():
     ap.add_argument("--decode-warps", type=int, default=0, help="override the decode kernel's compute warps per CTA")
     ap.add_argument("--decode-hpc", type=int, default=0, help="override the decode kernel's KV heads per CTA")
     ap.add_argument("--decode-uhpc", type=int, default=0, help="override the tcgen05 decode kernel's KV heads per CTA")
+    ap.add_argument("--no-pdl", action="store_true", help="launch the kernels without programmatic dependent launch")
     ap.add_argument("--variant", type=int, default=0, help="decode kernel family (0 = production)")
     ap.add_argument("--prefill-only", type=int, default=0, metavar="PP",
                     help="run only the prefill pass at this prompt length and print its JSON (profiler captures)")

@@ -121,6 +121,8 @@ constexpr uint32_t COMBINE_GROUPS = 4;
 __global__ void __launch_bounds__(128 * COMBINE_GROUPS)
 attn_combine_kernel(const float* __restrict__ partials, __half* __restrict__ out, uint32_t n_head,
                     uint32_t n_splits) {
+  pdl_launch_dependents();
+  pdl_wait();  // the partials come from the kernel before this one
   __shared__ float w_sh[COMBINE_MAX_SPLITS];
   __shared__ float red[16];
   __shared__ float o_sh[COMBINE_GROUPS][BP_HEAD_DIM];
@@ -627,9 +629,9 @@ cudaError_t bp_launch_decode(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, con
     // A fused "last CTA combines" epilogue was measured slower than this second small kernel:
     // code that a CTA runs once is fetched cold, and the ticket + combine path cost more than a launch.
     if (n_splits > 1) {
-      attn_combine_kernel<<<c->cfg.n_head, 128 * COMBINE_GROUPS, 0, s>>>(c->partials, out, c->cfg.n_head, n_splits);
       *launches += 1;
-      e = cudaGetLastError();
+      e = bp_launch(c->opt_pdl != 0, attn_combine_kernel, dim3(c->cfg.n_head), dim3(128 * COMBINE_GROUPS), 0, s,
+                    static_cast<const float*>(c->partials), out, c->cfg.n_head, n_splits);
     }
     return e;
   }

@@ -108,6 +108,10 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_entry_ns));
     atomicMin(&p.dbg[32], t_entry_ns);
   }
+  // Programmatic dependent launch: the next kernel in the stream may be scheduled already (it
+  // waits for this grid's completion itself). This grid waits (pdl_wait) before it touches what
+  // the previous kernels produce (q, the newest cache row) and before its own global writes.
+  if (threadIdx.x == 0) pdl_launch_dependents();
   const uint32_t ns = p.n_stages;
   const uint32_t g0 = blockIdx.y * HPC;
   const uint32_t split = blockIdx.x, n_splits = gridDim.x;
@@ -152,6 +156,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
   // go to row hq, lo bytes to row 4 + hq of the head's Q^T tile (swizzled 128-byte rows). Done by one
   // warp while the producer already streams the first stages; the QK issuers wait on q_bar.
   auto prepare_q = [&]() {
+    pdl_wait();  // q is written by the kernel before this one
     if (lane < HPC * p.qpg * 4) {
       const uint32_t b = lane & 3, hq = (lane >> 2) % p.qpg, g = (lane >> 2) / p.qpg;
       const __half* src = p.q + (static_cast<size_t>(g0 + g) * p.qpg + hq) * BP_HEAD_DIM + 32 * b;
@@ -203,6 +208,8 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
         const uint32_t bar = smem_u32(&full_bar[s]);
         const uint32_t stage = smem_base + s * L::STAGE_B;
         const int row = static_cast<int>(p.row_base + tok_begin + it * UT);
+        // older rows were written by earlier steps; the row of the newest token by the kernel before this one
+        if (tok_begin + (it + 1) * UT >= p.cur_pos) pdl_wait();
         mbar_arrive_expect_tx(bar, L::STAGE_B);
         tma_load_2d(stage + 2 * HPC * TILE_B, &map_kd, bar, static_cast<int>(g0 * 16), row);
         tma_load_2d(stage + 2 * HPC * TILE_B + L::SCALE_B, &map_vd, bar, static_cast<int>(g0 * 16), row);
@@ -420,6 +427,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
 
   tc_fence_before();
   __syncthreads();
+  pdl_wait();  // the partials / output buffers may still be read by earlier kernels
   // ---- epilogue: partial (o, m, l) per query head, or the final output ----
   {
     const float* o_fin = reinterpret_cast<const float*>(smem_gen);
@@ -499,8 +507,8 @@ static cudaError_t launch_umma(bp_attn_ctx* c, cudaStream_t s, UmmaParams& p, ui
   p.n_stages = spp < umma_max_stages<HPC>() ? spp : umma_max_stages<HPC>();
   const size_t smem = ULayout<HPC>::total(p.n_stages);
   dim3 grid(n_splits, c->cfg.n_kv_head / HPC);
-  decode_umma_kernel<HPC><<<grid, U_THREADS, smem, s>>>(c->umap_qs[0], c->umap_d[0], c->umap_qs[1], c->umap_d[1], p);
-  return cudaGetLastError();
+  return bp_launch(c->opt_pdl != 0, decode_umma_kernel<HPC>, grid, dim3(U_THREADS), smem, s, c->umap_qs[0], c->umap_d[0],
+                   c->umap_qs[1], c->umap_d[1], p);
 }
 
 cudaError_t bp_launch_decode_umma(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, const __half* q, __half* out,

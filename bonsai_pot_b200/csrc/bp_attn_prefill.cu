@@ -117,6 +117,8 @@ __global__ void __launch_bounds__(256) prefill_expand_kernel(const uint8_t* __re
                                                              uint64_t d_off, uint64_t qs_off, __half* __restrict__ dst,
                                                              uint64_t dst_v_off, uint32_t kv_dim, uint32_t m, uint32_t rows_pad,
                                                              uint32_t* counter) {
+  pdl_launch_dependents();
+  pdl_wait();  // the cache rows were written by the kernel before this one; the scratch may still be read
   if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *counter = 0;
   const uint32_t per_row = kv_dim >> 3;
   const uint32_t idx = blockIdx.x * 256 + threadIdx.x;
@@ -183,6 +185,10 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_base_s;
+  // Set-up above overlaps the previous kernel (programmatic dependent launch); everything below reads
+  // what it wrote (the expanded rows, q, the item counter).
+  if (threadIdx.x == 0) pdl_launch_dependents();
+  pdl_wait();
 
   const bool dbg_on = p.dbg != nullptr && blockIdx.x == 0 && lane == 0;
   long long tw[4] = {0, 0, 0, 0};
@@ -492,10 +498,11 @@ cudaError_t bp_launch_prefill(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, co
   {
     const uint32_t threads = rows_pad * (c->kv_dim >> 3);
     dim3 grid((threads + 255) / 256, 2);
-    prefill_expand_kernel<<<grid, 256, 0, s>>>(c->kv[0], c->kv[1], bp_d_off(c, layer), bp_qs_off(c, layer), c->pf_kv16,
-                                               static_cast<uint64_t>(c->pf_rows) * c->kv_dim, c->kv_dim, m, rows_pad,
-                                               c->pf_counter);
+    cudaError_t e = bp_launch(c->opt_pdl != 0, prefill_expand_kernel, grid, dim3(256), 0, s, c->kv[0], c->kv[1], bp_d_off(c, layer),
+                              bp_qs_off(c, layer), c->pf_kv16, static_cast<uint64_t>(c->pf_rows) * c->kv_dim, c->kv_dim, m,
+                              rows_pad, c->pf_counter);
     *launches += 1;
+    if (e != cudaSuccess) return e;
   }
   PrefillParams p;
   p.q = q;
@@ -518,12 +525,14 @@ cudaError_t bp_launch_prefill(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, co
   if (pair) {
     p.n_groups = groups2;
     const uint32_t n_items = p.n_groups * c->cfg.n_kv_head;
-    prefill_umma_kernel<2><<<n_items < sms ? n_items : sms, PLayout<2>::THREADS, PLayout<2>::SMEM, s>>>(c->pmap16[0], c->pmap16[1], p);
+    *launches += 1;
+    return bp_launch(c->opt_pdl != 0, prefill_umma_kernel<2>, dim3(n_items < sms ? n_items : sms), dim3(PLayout<2>::THREADS),
+                     PLayout<2>::SMEM, s, c->pmap16[0], c->pmap16[1], p);
   } else {
     p.n_groups = (m + tq_tokens - 1) / tq_tokens;
     const uint32_t n_items = p.n_groups * c->cfg.n_kv_head;
-    prefill_umma_kernel<1><<<n_items < sms ? n_items : sms, PLayout<1>::THREADS, PLayout<1>::SMEM, s>>>(c->pmap16[0], c->pmap16[1], p);
+    *launches += 1;
+    return bp_launch(c->opt_pdl != 0, prefill_umma_kernel<1>, dim3(n_items < sms ? n_items : sms), dim3(PLayout<1>::THREADS),
+                     PLayout<1>::SMEM, s, c->pmap16[0], c->pmap16[1], p);
   }
-  *launches += 1;
-  return cudaGetLastError();
 }

@@ -50,6 +50,7 @@ struct bp_attn_ctx {
   uint32_t opt_nw;   // decode: compute warps per CTA (8 or 16)
   uint32_t opt_hpc;  // decode: KV heads per CTA (divides n_kv_head)
   uint32_t opt_uhpc; // tcgen05 decode: KV heads per CTA (1 or 2)
+  uint32_t opt_pdl;  // launch the kernels of a layer with programmatic stream serialization (1) or plainly (0)
   uint32_t opt_pf_nq; // prefill: query tiles per work item (1 or 2), 0 = by batch size
   uint32_t opt_pf_flags; // prefill: scheduling experiments (bit 0: stagger the query tiles of an item)
   uint32_t last_launches;
@@ -65,6 +66,24 @@ __host__ __device__ inline uint64_t bp_d_off(const bp_attn_ctx* c, uint32_t il) 
 }
 __host__ __device__ inline uint64_t bp_qs_off(const bp_attn_ctx* c, uint32_t il) {
   return c->d_total + (uint64_t)il * c->cfg.max_seq * c->kv_dim;
+}
+
+// Launches `kernel`; with `pdl` the launch carries programmatic stream serialization, so that the
+// kernel's prologue overlaps the tail of its predecessor (the kernels call pdl_wait() themselves).
+template <typename... KArgs, typename... Args>
+inline cudaError_t bp_launch(bool pdl, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                             Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 // Kernel launchers (one per kernel file). Each returns the cudaError_t of its

@@ -16,6 +16,7 @@
 // offsets 4, 2, 1, and the dim offsets 2, 1 are the in-lane sum
 // (s0 + s2) + (s1 + s3).
 #include "bp_common.cuh"
+#include "bp_ptx.cuh"
 
 namespace {
 
@@ -95,6 +96,8 @@ kv_writeback_kernel(const __half* __restrict__ k_cur, const __half* __restrict__
                     float* __restrict__ k_d, uint32_t* __restrict__ k_qs, float* __restrict__ v_d,
                     uint32_t* __restrict__ v_qs, uint32_t n_kv_head, uint32_t pos_base, uint32_t m,
                     float eps) {
+  bp::pdl_launch_dependents();
+  bp::pdl_wait();  // k_cur / v_cur come from the previous kernel; the cache rows may still be read by it
   const int lane = threadIdx.x & 31;
   const uint32_t unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (unit >= m * n_kv_head) return;  // whole warp leaves together
@@ -128,6 +131,8 @@ __global__ void __launch_bounds__(256)
 q_norm_rope_kernel(__half* __restrict__ q, const __half* __restrict__ w_q_norm,
                    const __half* __restrict__ rope, uint32_t n_head, uint32_t pos_base, uint32_t m,
                    uint32_t pos_step, float eps) {
+  bp::pdl_launch_dependents();
+  bp::pdl_wait();  // q comes from the previous kernel
   const int lane = threadIdx.x & 31;
   const uint32_t unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (unit >= m * n_head) return;
@@ -148,19 +153,17 @@ q_norm_rope_kernel(__half* __restrict__ q, const __half* __restrict__ w_q_norm,
 cudaError_t bp_launch_q_norm_rope(bp_attn_ctx* c, cudaStream_t s, __half* q, const __half* w,
                                   uint32_t pos_base, uint32_t m, uint32_t* launches) {
   const uint32_t units = m * c->cfg.n_head;
-  q_norm_rope_kernel<<<(units + 7) / 8, 256, 0, s>>>(q, w, c->rope, c->cfg.n_head, pos_base, m, 1u,
-                                                     c->cfg.rms_eps);
   *launches += 1;
-  return cudaGetLastError();
+  return bp_launch(c->opt_pdl != 0, q_norm_rope_kernel, dim3((units + 7) / 8), dim3(256), 0, s, q, w, c->rope, c->cfg.n_head,
+                   pos_base, m, 1u, c->cfg.rms_eps);
 }
 
 cudaError_t bp_launch_q_norm_rope_rows(bp_attn_ctx* c, cudaStream_t s, __half* q, const __half* w,
                                        uint32_t pos, uint32_t rows, uint32_t* launches) {
   const uint32_t units = rows * c->cfg.n_head;
-  q_norm_rope_kernel<<<(units + 7) / 8, 256, 0, s>>>(q, w, c->rope, c->cfg.n_head, pos, rows, 0u,
-                                                     c->cfg.rms_eps);
   *launches += 1;
-  return cudaGetLastError();
+  return bp_launch(c->opt_pdl != 0, q_norm_rope_kernel, dim3((units + 7) / 8), dim3(256), 0, s, q, w, c->rope, c->cfg.n_head,
+                   pos, rows, 0u, c->cfg.rms_eps);
 }
 
 cudaError_t bp_launch_kv_writeback(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, const __half* k,
@@ -171,8 +174,7 @@ cudaError_t bp_launch_kv_writeback(bp_attn_ctx* c, cudaStream_t s, uint32_t laye
   float* v_d = reinterpret_cast<float*>(c->kv[1] + bp_d_off(c, layer));
   uint32_t* k_qs = reinterpret_cast<uint32_t*>(c->kv[0] + bp_qs_off(c, layer));
   uint32_t* v_qs = reinterpret_cast<uint32_t*>(c->kv[1] + bp_qs_off(c, layer));
-  kv_writeback_kernel<<<(units + 7) / 8, 256, 0, s>>>(k, v, w, c->rope, k_d, k_qs, v_d, v_qs,
-                                                      c->cfg.n_kv_head, pos_base, m, c->cfg.rms_eps);
   *launches += 1;
-  return cudaGetLastError();
+  return bp_launch(c->opt_pdl != 0, kv_writeback_kernel, dim3((units + 7) / 8), dim3(256), 0, s, k, v, w, c->rope, k_d, k_qs, v_d,
+                   v_qs, c->cfg.n_kv_head, pos_base, m, c->cfg.rms_eps);
 }

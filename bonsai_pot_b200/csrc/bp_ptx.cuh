@@ -184,6 +184,13 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
                : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Programmatic dependent launch. A kernel launched with programmatic stream serialization may be
+// scheduled while its predecessor in the stream still runs: pdl_wait() returns once the predecessor
+// has completed and its writes are visible (a no-op for a normally launched kernel), and must come
+// before the first access to anything the predecessor produces or still reads;
+// pdl_launch_dependents() lets the successor's CTAs be scheduled early.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
