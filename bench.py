@@ -407,9 +407,18 @@ def run_ours(args):
     if rank == 0:
         line["clocks"] = clocks
         print(json.dumps(line), flush=True)
-    ctx.close()
     if world > 1:
-        dist.destroy_process_group()
+        # The captured graphs hold NCCL work; tearing the process group down with them alive has
+        # hung. Drop them, meet once more, and leave without the group's destructor.
+        del graph, decode_graph
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        ctx.close()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
+    ctx.close()
 
 
 def prefill_bench(torch, bp, stream, tflops_peak, peak_kind, pp, nl):
