@@ -124,6 +124,22 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
   const uint32_t p_tiles = q_tiles + L::Q_B;
   Misc* misc = reinterpret_cast<Misc*>(smem_gen + ns * L::STAGE_B + L::Q_B + L::P_B);
 
+  // One stage of the ring: K and V tiles of HPC heads and their scale rows, 128 tokens from `it * UT`.
+  auto issue_stage = [&](uint32_t it, uint32_t s) {
+    const uint32_t bar = smem_u32(&full_bar[s]);
+    const uint32_t stage = smem_base + s * L::STAGE_B;
+    const int row = static_cast<int>(p.row_base + tok_begin + it * UT);
+    // older rows were written by earlier steps; the row of the newest token by the kernel before this one
+    if (tok_begin + (it + 1) * UT >= p.cur_pos) pdl_wait();
+    mbar_arrive_expect_tx(bar, L::STAGE_B);
+    tma_load_2d(stage + 2 * HPC * TILE_B, &map_kd, bar, static_cast<int>(g0 * 16), row);
+    tma_load_2d(stage + 2 * HPC * TILE_B + L::SCALE_B, &map_vd, bar, static_cast<int>(g0 * 16), row);
+    for (uint32_t g = 0; g < HPC; g++) {
+      tma_load_3d(stage + g * TILE_B, &map_kq, bar, 0, static_cast<int>(g0 + g), row);
+      tma_load_3d(stage + (HPC + g) * TILE_B, &map_vq, bar, 0, static_cast<int>(g0 + g), row);
+    }
+  };
+
   // ---- set-up: barriers, TMEM, zeroed operand tiles, quantised Q ----
   if (threadIdx.x == 0) {
     for (uint32_t s = 0; s < ns; s++) {
@@ -138,9 +154,18 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
       mbar_init(smem_u32(&o_ready[b]), 1);
       mbar_init(smem_u32(&o_free[b]), 4);
     }
-    mbar_init(smem_u32(&q_bar), 1);
+    mbar_init(smem_u32(&q_bar), 4);  // the four accumulate warps prepare Q
     abort_s = 0;
     fence_barrier_init();
+    // The first round of the ring is requested here, before the CTA-wide set-up barrier: the loads
+    // need nothing but the full barriers of their stages, and their latency (descriptor fetch + DRAM)
+    // is the longest item on the critical path of a short launch.
+    prefetch_tensormap(&map_kq);
+    prefetch_tensormap(&map_vq);
+    prefetch_tensormap(&map_kd);
+    prefetch_tensormap(&map_vd);
+    const uint32_t n_pre = n_iter < ns ? n_iter : ns;
+    for (uint32_t it = 0; it < n_pre; it++) issue_stage(it, it);
   }
   {
     uint4* z = reinterpret_cast<uint4*>(smem_gen + ns * L::STAGE_B);
@@ -153,34 +178,34 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
   tc_fence_after();
   const uint32_t tmem = tmem_base_s;
   // Q of head (g, hq), block b: 15-bit integers = 128 * hi + lo against the block's absmax; hi bytes
-  // go to row hq, lo bytes to row 4 + hq of the head's Q^T tile (swizzled 128-byte rows). Done by one
-  // warp while the producer already streams the first stages; the QK issuers wait on q_bar.
-  auto prepare_q = [&]() {
+  // go to row hq, lo bytes to row 4 + hq of the head's Q^T tile (swizzled 128-byte rows). Done by the
+  // accumulate warps while the producer already streams the first stages; the QK issuers wait on q_bar.
+  auto prepare_q = [&](uint32_t aw) {  // aw = 0..3: the calling accumulate warp; warp aw takes heads aw, aw + 4, ...
     pdl_wait();  // q is written by the kernel before this one
-    if (lane < HPC * p.qpg * 4) {
-      const uint32_t b = lane & 3, hq = (lane >> 2) % p.qpg, g = (lane >> 2) / p.qpg;
-      const __half* src = p.q + (static_cast<size_t>(g0 + g) * p.qpg + hq) * BP_HEAD_DIM + 32 * b;
-      // two passes over the 32 values, kept as rolled loops: this runs once per CTA and its
-      // instructions are fetched cold, so code size is what it costs
-      float amax = 0.f;
-#pragma unroll 1
-      for (int i = 0; i < 16; i++) {
-        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(src + 2 * i));
-        amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
-      }
+    // lane l holds dims 4l .. 4l+3 of one head: a Q8_0 block is 8 lanes. One 8-byte load, three
+    // shuffles for the block maximum, two 4-byte stores: short straight-line code, because this sits
+    // on the critical path of every launch (the first Q K^T waits for it) and runs cold.
+    for (uint32_t hl = aw; hl < HPC * p.qpg; hl += 4) {
+      const uint32_t g = hl / p.qpg, hq = hl % p.qpg, b = lane >> 3;
+      const uint2 raw = *reinterpret_cast<const uint2*>(p.q + (static_cast<size_t>(g0 + g) * p.qpg + hq) * BP_HEAD_DIM + 4 * lane);
+      const float2 f01 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+      const float2 f23 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+      const float f[4] = {f01.x, f01.y, f23.x, f23.y};
+      float amax = fmaxf(fmaxf(fabsf(f[0]), fabsf(f[1])), fmaxf(fabsf(f[2]), fabsf(f[3])));
+#pragma unroll
+      for (int off = 1; off <= 4; off <<= 1) amax = fmaxf(amax, __shfl_xor_sync(FULL, amax, off));
       const float sq = amax / 16383.0f, inv = amax > 0.f ? 16383.0f / amax : 0.f;
-      uint8_t* tile = smem_gen + ns * L::STAGE_B + g * 2048;
-#pragma unroll 1
-      for (int i = 0; i < 16; i++) {
-        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(src + 2 * i));
-        const int q0 = __float2int_rn(f.x * inv), q1 = __float2int_rn(f.y * inv);
-        const uint32_t col = 32 * b + 2 * i;
-        const uint16_t hi = static_cast<uint16_t>((static_cast<uint32_t>(q0 >> 7) & 0xffu) | ((static_cast<uint32_t>(q1 >> 7) & 0xffu) << 8));
-        const uint16_t lo = static_cast<uint16_t>((static_cast<uint32_t>(q0) & 0x7fu) | ((static_cast<uint32_t>(q1) & 0x7fu) << 8));
-        *reinterpret_cast<uint16_t*>(tile + swz128(hq * 128 + col)) = hi;
-        *reinterpret_cast<uint16_t*>(tile + swz128((4 + hq) * 128 + col)) = lo;
+      uint32_t hi = 0, lo = 0;
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        const int q = __float2int_rn(f[i] * inv);
+        hi |= (static_cast<uint32_t>(q >> 7) & 0xffu) << (8 * i);
+        lo |= (static_cast<uint32_t>(q) & 0x7fu) << (8 * i);
       }
-      misc->sq[g][hq][b] = sq * p.sm_scale_log2;
+      uint8_t* tile = smem_gen + ns * L::STAGE_B + g * 2048;
+      *reinterpret_cast<uint32_t*>(tile + swz128(hq * 128 + 4 * lane)) = hi;
+      *reinterpret_cast<uint32_t*>(tile + swz128((4 + hq) * 128 + 4 * lane)) = lo;
+      if ((lane & 7) == 0) misc->sq[g][hq][b] = sq * p.sm_scale_log2;
     }
     fence_proxy_async();
     __syncwarp();
@@ -195,28 +220,13 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
   auto wait = [&](uint64_t* bar, uint32_t parity) { cta_wait(bar, parity, &abort_s, p.err); };
 
   if (warp == 0) {
-    // ---------------- TMA producer ----------------
+    // ---------------- TMA producer: the rounds of the ring after the first (requested during set-up) ----------------
     if (lane == 0) {
-      prefetch_tensormap(&map_kq);
-      prefetch_tensormap(&map_vq);
-      prefetch_tensormap(&map_kd);
-      prefetch_tensormap(&map_vd);
-      uint32_t s = 0, use = 0;
-      for (uint32_t it = 0; it < n_iter; it++) {
-        if (use > 0) wait(&empty_bar[s], (use - 1) & 1);
+      uint32_t s = 0, use = 1;
+      for (uint32_t it = ns; it < n_iter; it++) {
+        wait(&empty_bar[s], (use - 1) & 1);
         if (abort_s) break;
-        const uint32_t bar = smem_u32(&full_bar[s]);
-        const uint32_t stage = smem_base + s * L::STAGE_B;
-        const int row = static_cast<int>(p.row_base + tok_begin + it * UT);
-        // older rows were written by earlier steps; the row of the newest token by the kernel before this one
-        if (tok_begin + (it + 1) * UT >= p.cur_pos) pdl_wait();
-        mbar_arrive_expect_tx(bar, L::STAGE_B);
-        tma_load_2d(stage + 2 * HPC * TILE_B, &map_kd, bar, static_cast<int>(g0 * 16), row);
-        tma_load_2d(stage + 2 * HPC * TILE_B + L::SCALE_B, &map_vd, bar, static_cast<int>(g0 * 16), row);
-        for (uint32_t g = 0; g < HPC; g++) {
-          tma_load_3d(stage + g * TILE_B, &map_kq, bar, 0, static_cast<int>(g0 + g), row);
-          tma_load_3d(stage + (HPC + g) * TILE_B, &map_vq, bar, 0, static_cast<int>(g0 + g), row);
-        }
+        issue_stage(it, s);
         if (++s == ns) { s = 0; use++; }
       }
     }
@@ -383,7 +393,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
     }
   } else {
     // ---------------- accumulate: thread = head dim ----------------
-    if (warp == U_FIRST_SM_WARP + 4 * NGRP) prepare_q();
+    prepare_q(warp - (U_FIRST_SM_WARP + 4 * NGRP));
     const uint32_t quad = warp & 3, dim = quad * 32 + lane;
     const uint32_t lane_addr = (quad * 32) << 16;
     float o[NGRP][4];
