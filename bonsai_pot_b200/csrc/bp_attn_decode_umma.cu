@@ -31,7 +31,8 @@ constexpr float NEG_BIG = -1e30f;
 constexpr uint32_t UT = 128;                 // tokens per stage = UMMA M
 constexpr uint32_t TILE_B = UT * 128;        // int8 tile of one head and stage: 16 KB
 constexpr uint32_t U_MAX_STAGES = 6;
-constexpr uint32_t NGRP = 4;                     // softmax groups working on different jobs in parallel
+constexpr uint32_t NGRP = 4;
+constexpr uint32_t FIN_BAR = 6;                   // named barrier: softmax warps arrive, accumulate warps wait                     // softmax groups working on different jobs in parallel
 constexpr uint32_t NISS = 2;                     // UMMA issuer warps per kind (QK, PV)
 constexpr uint32_t U_FIRST_SM_WARP = 1 + 2 * NISS;  // warp 0 producer, then the issuers
 constexpr uint32_t U_THREADS = (U_FIRST_SM_WARP + 4 * NGRP + 4) * 32;
@@ -142,30 +143,35 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
 
   // ---- set-up: barriers, TMEM, zeroed operand tiles, quantised Q ----
   if (threadIdx.x == 0) {
-    for (uint32_t s = 0; s < ns; s++) {
-      mbar_init(smem_u32(&full_bar[s]), 1);
-      mbar_init(smem_u32(&empty_bar[s]), HPC);  // one tcgen05.commit per job of the stage
-    }
-    for (int b = 0; b < 4; b++) {
-      mbar_init(smem_u32(&s_ready[b]), 1);
-      mbar_init(smem_u32(&s_free[b]), 4);
-      mbar_init(smem_u32(&p_ready[b]), 4);
-      mbar_init(smem_u32(&p_free[b]), 1);
-      mbar_init(smem_u32(&o_ready[b]), 1);
-      mbar_init(smem_u32(&o_free[b]), 4);
-    }
-    mbar_init(smem_u32(&q_bar), 4);  // the four accumulate warps prepare Q
+    // Thread 0 initialises only what the first loads need and requests the first round of the ring
+    // at once, before the CTA-wide set-up barrier: their latency (descriptor fetch + DRAM) is the
+    // longest item on the critical path of a short launch. The other barriers are initialised by
+    // the lanes of warp 2 in parallel.
     abort_s = 0;
+    for (uint32_t s = 0; s < ns; s++) mbar_init(smem_u32(&full_bar[s]), 1);
     fence_barrier_init();
-    // The first round of the ring is requested here, before the CTA-wide set-up barrier: the loads
-    // need nothing but the full barriers of their stages, and their latency (descriptor fetch + DRAM)
-    // is the longest item on the critical path of a short launch.
     prefetch_tensormap(&map_kq);
     prefetch_tensormap(&map_vq);
     prefetch_tensormap(&map_kd);
     prefetch_tensormap(&map_vd);
     const uint32_t n_pre = n_iter < ns ? n_iter : ns;
     for (uint32_t it = 0; it < n_pre; it++) issue_stage(it, it);
+  } else if (warp == 2) {
+    if (lane < 4) {
+      mbar_init(smem_u32(&s_ready[lane]), 1);
+      mbar_init(smem_u32(&p_free[lane]), 1);
+    } else if (lane < 8) {
+      mbar_init(smem_u32(&s_free[lane - 4]), 4);
+      mbar_init(smem_u32(&o_ready[lane - 4]), 1);
+    } else if (lane < 12) {
+      mbar_init(smem_u32(&p_ready[lane - 8]), 4);
+      mbar_init(smem_u32(&o_free[lane - 8]), 4);
+    } else if (lane == 12) {
+      mbar_init(smem_u32(&q_bar), 4);  // the four accumulate warps prepare Q
+    } else if (lane - 13 < ns) {
+      mbar_init(smem_u32(&empty_bar[lane - 13]), HPC);  // one tcgen05.commit per job of the stage
+    }
+    fence_barrier_init();
   }
   {
     uint4* z = reinterpret_cast<uint4*>(smem_gen + ns * L::STAGE_B);
@@ -391,6 +397,8 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
       if (lane == 0) misc->lsum[w][h][quad] = l;
       if (t == 0) misc->mfin[w][h] = m_run[h];
     }
+    __threadfence_block();
+    named_bar_arrive(FIN_BAR, 128 * NGRP + 128);  // the accumulate warps merge the groups
   } else {
     // ---------------- accumulate: thread = head dim ----------------
     prepare_q(warp - (U_FIRST_SM_WARP + 4 * NGRP));
@@ -426,44 +434,39 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
         }
       }
     }
-    // stash O for the epilogue: o_fin[group][h][dim]; the stage ring is idle by now
-    float* o_fin = reinterpret_cast<float*>(smem_gen);
-    __syncwarp();
+    // ---- epilogue: partial (o, m, l) per query head, or the final output ----
+    // Every group's O is in this thread's registers; the groups' maxima and sums arrive through
+    // shared memory once the softmax warps are done. The groups w with w % HPC == g hold disjoint
+    // token subsets of head g and are merged here.
+    named_bar_sync(FIN_BAR, 128 * NGRP + 128);
+    pdl_wait();  // the partials / output buffers may still be read by earlier kernels
 #pragma unroll
-    for (uint32_t w = 0; w < NGRP; w++)
+    for (uint32_t g = 0; g < HPC; g++) {
 #pragma unroll
-      for (int h = 0; h < 4; h++) o_fin[(w * 4 + h) * BP_HEAD_DIM + dim] = o[w][h];
-  }
-
-  tc_fence_before();
-  __syncthreads();
-  pdl_wait();  // the partials / output buffers may still be read by earlier kernels
-  // ---- epilogue: partial (o, m, l) per query head, or the final output ----
-  {
-    const float* o_fin = reinterpret_cast<const float*>(smem_gen);
-    const uint32_t total = HPC * p.qpg * BP_HEAD_DIM;
-    for (uint32_t idx = threadIdx.x; idx < total; idx += U_THREADS) {
-      const uint32_t hl = idx >> 7, d = idx & 127;
-      const uint32_t g = hl / p.qpg, hq = hl % p.qpg;
-      // the groups w with w % HPC == g hold disjoint token subsets of head g: merge them
-      float m = NEG_BIG;
-      for (uint32_t w = g; w < NGRP; w += HPC) m = fmaxf(m, misc->mfin[w][hq]);
-      float o = 0.f, l = 0.f;
-      for (uint32_t w = g; w < NGRP; w += HPC) {
-        const float e = ex2(misc->mfin[w][hq] - m);
-        l += ((misc->lsum[w][hq][0] + misc->lsum[w][hq][1]) + (misc->lsum[w][hq][2] + misc->lsum[w][hq][3])) * e;
-        o += o_fin[(w * 4 + hq) * BP_HEAD_DIM + d] * e;
-      }
-      const uint32_t h = (g0 + g) * p.qpg + hq;
-      if (n_splits == 1) {
-        p.out[static_cast<size_t>(h) * BP_HEAD_DIM + d] = __float2half_rn(o * (1.0f / l));
-      } else {
-        float* dst = p.partials + (static_cast<size_t>(split) * p.n_head + h) * BP_PART_STRIDE;
-        dst[d] = o;
-        if (d == 0) { dst[128] = m; dst[129] = l; }
+      for (uint32_t hq = 0; hq < 4; hq++) {
+        float m = NEG_BIG;
+#pragma unroll
+        for (uint32_t w = g; w < NGRP; w += HPC) m = fmaxf(m, misc->mfin[w][hq]);
+        float acc = 0.f, l = 0.f;
+#pragma unroll
+        for (uint32_t w = g; w < NGRP; w += HPC) {
+          const float e = ex2(misc->mfin[w][hq] - m);
+          l += ((misc->lsum[w][hq][0] + misc->lsum[w][hq][1]) + (misc->lsum[w][hq][2] + misc->lsum[w][hq][3])) * e;
+          acc += o[w][hq] * e;
+        }
+        const uint32_t h = (g0 + g) * p.qpg + hq;
+        if (n_splits == 1) {
+          p.out[static_cast<size_t>(h) * BP_HEAD_DIM + dim] = __float2half_rn(acc * (1.0f / l));
+        } else {
+          float* dst = p.partials + (static_cast<size_t>(split) * p.n_head + h) * BP_PART_STRIDE;
+          dst[dim] = acc;
+          if (dim == 0) { dst[128] = m; dst[129] = l; }
+        }
       }
     }
   }
+
+  tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem, TMEM_COLS);
   if (p.dbg != nullptr && threadIdx.x == 0) {  // development aid: span of the launch in ns
