@@ -280,7 +280,7 @@ def run_ours(args):
     q_raw = torch.randn(N_LAYER, q_dim_l, generator=gen, device="cuda").half()
     k_new = torch.randn(N_LAYER, kv_dim_l, generator=gen, device="cuda").half()
     v_new = torch.randn(N_LAYER, kv_dim_l, generator=gen, device="cuda").half()
-    q_work = torch.empty_like(q_raw)
+    q_work = q_raw.clone()
     out_local = torch.zeros(N_LAYER, q_dim_l, dtype=torch.float16, device="cuda")
     out_full = torch.zeros(N_LAYER, Q_DIM, dtype=torch.float16, device="cuda") if world > 1 else out_local
     pos = ctx_len - 1
@@ -290,14 +290,19 @@ def run_ours(args):
     def one_token():
         nonlocal launches_per_step
         n = 0
-        q_work.copy_(q_raw)  # q_norm_rope works in place; restore the raw activations (1 torch copy kernel)
+        if args.separate:
+            q_work.copy_(q_raw)  # q_norm_rope works in place; restore the raw activations (1 torch copy kernel)
         for il in range(N_LAYER):
-            ctx.dispatch_q_norm_rope_fused(q_work[il], w, pos, 1, stream=stream)
-            n += ctx.last_launch_count()
-            ctx.dispatch_kv_writeback_fused(il, k_new[il], v_new[il], w, pos, 1, stream=stream)
-            n += ctx.last_launch_count()
-            ctx.dispatch_attention_decode(il, q_work[il], out_local[il], pos + 1, stream=stream)
-            n += ctx.last_launch_count()
+            if args.separate:
+                ctx.dispatch_q_norm_rope_fused(q_work[il], w, pos, 1, stream=stream)
+                n += ctx.last_launch_count()
+                ctx.dispatch_kv_writeback_fused(il, k_new[il], v_new[il], w, pos, 1, stream=stream)
+                n += ctx.last_launch_count()
+                ctx.dispatch_attention_decode(il, q_work[il], out_local[il], pos + 1, stream=stream)
+                n += ctx.last_launch_count()
+            else:  # the same layer step as one call (bp_attn_decode_layer)
+                ctx.decode_layer(il, q_raw[il], w, k_new[il], v_new[il], w, pos, out_local[il], stream=stream)
+                n += ctx.last_launch_count()
             if world > 1:
                 dist.all_gather_into_tensor(out_full[il], out_local[il])
         launches_per_step = n
@@ -365,7 +370,7 @@ def run_ours(args):
         "config": {"workload": f"decode_ctx{ctx_len}_{N_LAYER}layers", "n_head": N_HEAD, "n_kv_head": N_KV_HEAD,
                    "head_dim": HEAD_DIM, "kv_cache": "Q8_0 (int8 + f32 block scales)", "bytes_per_token_layer": BYTES_PER_TOKEN_LAYER,
                    "parallelism": f"kv_head_shard{world}" if world > 1 else "single",
-                   "launch": "36 dependent layers in one CUDA graph", "l2": "working set 340 MB per step > 126 MB L2",
+                   "launch": "36 dependent layers in one CUDA graph, " + ("three dispatches per layer" if args.separate else "one bp_attn_decode_layer call per layer"), "l2": "working set 340 MB per step > 126 MB L2",
                    "us_per_layer": round(sec_per_step * 1e6 / N_LAYER, 3)},
         "roofline": roofline, "gpu_launches": launches_per_step * args.steps,
     }
@@ -500,6 +505,8 @@ def main():
     ap.add_argument("--decode-warps", type=int, default=0, help="override the decode kernel's compute warps per CTA")
     ap.add_argument("--decode-hpc", type=int, default=0, help="override the decode kernel's KV heads per CTA")
     ap.add_argument("--decode-uhpc", type=int, default=0, help="override the tcgen05 decode kernel's KV heads per CTA")
+    ap.add_argument("--separate", action="store_true",
+                    help="drive a layer with the reference's three dispatches instead of the one-call layer step")
     ap.add_argument("--no-pdl", action="store_true", help="launch the kernels without programmatic dependent launch")
     ap.add_argument("--variant", type=int, default=0, help="decode kernel family (0 = production)")
     ap.add_argument("--prefill-only", type=int, default=0, metavar="PP",

@@ -97,6 +97,7 @@ SIGNATURES = {
     "bp_debug_counters": (_int, [_vp, C.POINTER(C.c_uint64)]),
     "bp_last_launch_count": (_u32, [_vp]),
     "bp_decode_num_splits": (_u32, [_vp, _u32]),
+    "bp_attn_decode_layer": (_int, [_vp, _vp, _u32, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _vp]),
     "bp_attn_decode_static_scratch": (_int, [_vp, _vp, _vp, _vp, _vp] + [_u32] * 6),
 }
 

@@ -103,6 +103,14 @@ class AttnContext:
         """attention_split + attention_merge: q, out f16 [n_head*128]; keys [0, cur_pos)."""
         self._check(self._lib.bp_attn_decode(self._h, _stream(stream), layer_il, _ptr(q), _ptr(out), cur_pos))
 
+    def decode_layer(self, layer_il, q_raw, w_q_norm, k_cur, v_cur, w_k_norm, pos, out, q_roped=None, stream=None):
+        """One decode step of one layer as one call (q_norm_rope_fused + kv_writeback_fused at row
+        `pos` + decode attention over pos + 1 keys). q_raw is not modified; q_roped (optional)
+        receives the normalised, rotated q."""
+        self._check(self._lib.bp_attn_decode_layer(self._h, _stream(stream), layer_il, _ptr(q_raw),
+                                                   _ptr(q_roped) if q_roped is not None else None, _ptr(w_q_norm),
+                                                   _ptr(k_cur), _ptr(v_cur), _ptr(w_k_norm), pos, _ptr(out)))
+
     def dispatch_attention(self, layer_il, q, out, m_tokens, stream=None):
         """Batched prefill (pos = 0, is_prefill = true): q, out f16 [m][n_head*128]."""
         self._check(self._lib.bp_attn_prefill(self._h, _stream(stream), layer_il, _ptr(q), _ptr(out), m_tokens))

@@ -618,6 +618,39 @@ static cudaError_t launch_mma(bp_attn_ctx* c, cudaStream_t s, DecodeParams& p, u
   return cudaGetLastError();
 }
 
+// Fused layer step. With the tcgen05 kernel: one launch does the Q norm + RoPE, the new token's
+// cache write and the split attention, a second one merges the splits. Otherwise: the separate kernels.
+cudaError_t bp_launch_decode_fused(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, const __half* q_raw, __half* q_roped,
+                                   const __half* w_q, const __half* k_cur, const __half* v_cur, const __half* w_k,
+                                   uint32_t pos, __half* out, uint32_t* launches) {
+  if (c->variant == 0 && bp_use_umma(c)) {
+    bp_fused_step fs;
+    fs.q_roped = q_roped;
+    fs.w_q = w_q;
+    fs.w_k = w_k;
+    fs.k_cur = k_cur;
+    fs.v_cur = v_cur;
+    uint32_t n_splits = 1;
+    cudaError_t e = bp_launch_decode_umma(c, s, layer, q_raw, out, pos + 1, &n_splits, &fs);
+    *launches += 1;
+    if (e != cudaSuccess) return e;
+    if (n_splits > 1) {
+      *launches += 1;
+      e = bp_launch(c->opt_pdl != 0, attn_combine_kernel, dim3(c->cfg.n_head), dim3(128 * COMBINE_GROUPS), 0, s,
+                    static_cast<const float*>(c->partials), out, c->cfg.n_head, n_splits);
+    }
+    return e;
+  }
+  if (q_roped == nullptr) return cudaErrorInvalidValue;  // the separate kernels rotate q in a caller's buffer
+  cudaError_t e = cudaMemcpyAsync(q_roped, q_raw, static_cast<size_t>(c->q_dim) * sizeof(__half), cudaMemcpyDeviceToDevice, s);
+  if (e != cudaSuccess) return e;
+  e = bp_launch_q_norm_rope(c, s, q_roped, w_q, pos, 1, launches);
+  if (e != cudaSuccess) return e;
+  e = bp_launch_kv_writeback(c, s, layer, k_cur, v_cur, w_k, pos, 1, launches);
+  if (e != cudaSuccess) return e;
+  return bp_launch_decode(c, s, layer, q_roped, out, pos + 1, launches);
+}
+
 cudaError_t bp_launch_decode(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, const __half* q,
                              __half* out, uint32_t cur_pos, uint32_t* launches) {
   if (c->variant == 1) return bp_launch_scalar_attention(c, s, layer, q, out, cur_pos, 1, false, launches);

@@ -21,6 +21,7 @@
 // error word.
 #include "bp_common.cuh"
 #include "bp_ptx.cuh"
+#include "bp_norm_quant.cuh"
 
 namespace {
 
@@ -47,6 +48,16 @@ struct UmmaParams {
   uint32_t* err;
   uint32_t row_base, cur_pos, tps, n_stages, n_head, qpg;
   float sm_scale_log2;
+  // Fused layer step (fused = 1): q is the RAW query; the kernel normalises and rotates it itself
+  // (optionally storing the result to q_roped), and the CTAs of the last split quantise the new
+  // token's K / V rows (k_cur, v_cur), write them to the cache and patch them into their last stage.
+  uint32_t fused;
+  float eps;
+  __half* q_roped;
+  const __half *w_q, *w_k, *k_cur, *v_cur, *rope_row;
+  float *k_d, *v_d;        // the layer's scale sections
+  uint32_t *k_qs, *v_qs;   // the layer's quant sections (as words)
+  uint32_t n_kv_head;
   unsigned long long* dbg;  // optional cycle counters of CTA (0, 0); null in normal use
 };
 
@@ -97,7 +108,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[U_MAX_STAGES], empty_bar[U_MAX_STAGES];
   __shared__ __align__(8) uint64_t s_ready[4], s_free[4], p_ready[4], p_free[4], o_ready[4], o_free[4];
-  __shared__ __align__(8) uint64_t q_bar;
+  __shared__ __align__(8) uint64_t q_bar, patched_bar;
   __shared__ uint32_t tmem_base_s;
   __shared__ volatile uint32_t abort_s;
 
@@ -130,8 +141,9 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
     const uint32_t bar = smem_u32(&full_bar[s]);
     const uint32_t stage = smem_base + s * L::STAGE_B;
     const int row = static_cast<int>(p.row_base + tok_begin + it * UT);
-    // older rows were written by earlier steps; the row of the newest token by the kernel before this one
-    if (tok_begin + (it + 1) * UT >= p.cur_pos) pdl_wait();
+    // older rows were written by earlier steps; the row of the newest token by the kernel before this
+    // one (fused step: by this CTA, which patches it into the stage after the load)
+    if (!p.fused && tok_begin + (it + 1) * UT >= p.cur_pos) pdl_wait();
     mbar_arrive_expect_tx(bar, L::STAGE_B);
     tma_load_2d(stage + 2 * HPC * TILE_B, &map_kd, bar, static_cast<int>(g0 * 16), row);
     tma_load_2d(stage + 2 * HPC * TILE_B + L::SCALE_B, &map_vd, bar, static_cast<int>(g0 * 16), row);
@@ -168,6 +180,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
       mbar_init(smem_u32(&o_free[lane - 8]), 4);
     } else if (lane == 12) {
       mbar_init(smem_u32(&q_bar), 4);  // the four accumulate warps prepare Q
+      mbar_init(smem_u32(&patched_bar), 1);
     } else if (lane - 13 < ns) {
       mbar_init(smem_u32(&empty_bar[lane - 13]), HPC);  // one tcgen05.commit per job of the stage
     }
@@ -193,7 +206,18 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
     // on the critical path of every launch (the first Q K^T waits for it) and runs cold.
     for (uint32_t hl = aw; hl < HPC * p.qpg; hl += 4) {
       const uint32_t g = hl / p.qpg, hq = hl % p.qpg, b = lane >> 3;
-      const uint2 raw = *reinterpret_cast<const uint2*>(p.q + (static_cast<size_t>(g0 + g) * p.qpg + hq) * BP_HEAD_DIM + 4 * lane);
+      const size_t q_off = (static_cast<size_t>(g0 + g) * p.qpg + hq) * BP_HEAD_DIM;
+      uint2 raw;
+      if (p.fused) {
+        // q_norm_rope of this head, rounded to f16 exactly as the stand-alone kernel stores it
+        const Rot4 r = norm_rope(p.q + q_off, p.w_q, p.rope_row, p.eps, static_cast<int>(lane));
+        const __half2 lo2 = __floats2half2_rn(r.v[0], r.v[1]), hi2 = __floats2half2_rn(r.v[2], r.v[3]);
+        raw.x = *reinterpret_cast<const uint32_t*>(&lo2);
+        raw.y = *reinterpret_cast<const uint32_t*>(&hi2);
+        if (p.q_roped != nullptr && split == 0) *reinterpret_cast<uint2*>(p.q_roped + q_off + 4 * lane) = raw;
+      } else {
+        raw = *reinterpret_cast<const uint2*>(p.q + q_off + 4 * lane);
+      }
       const float2 f01 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
       const float2 f23 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
       const float f[4] = {f01.x, f01.y, f23.x, f23.y};
@@ -227,6 +251,34 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
 
   if (warp == 0) {
     // ---------------- TMA producer: the rounds of the ring after the first (requested during set-up) ----------------
+    // Fused step, last split: the whole warp first quantises the new token's K / V rows of this
+    // CTA's heads (the arithmetic of kv_writeback_kernel) and stores them to the cache.
+    const bool new_row = p.fused && tok_end == p.cur_pos;
+    uint32_t pk[HPC], pv[HPC];
+    float dk[HPC], dv[HPC];
+    if (new_row) {
+      pdl_wait();  // k_cur / v_cur come from the kernel before this one
+      const uint32_t pos = p.cur_pos - 1, kv_dim = p.n_kv_head * BP_HEAD_DIM;
+#pragma unroll
+      for (uint32_t g = 0; g < HPC; g++) {
+        const size_t src = static_cast<size_t>(g0 + g) * BP_HEAD_DIM;
+        const Rot4 kp = norm_rope(p.k_cur + src, p.w_k, p.rope_row, p.eps, static_cast<int>(lane));
+        const uint2 vr = *reinterpret_cast<const uint2*>(p.v_cur + src + 4 * lane);
+        const float2 v01 = __half22float2(*reinterpret_cast<const __half2*>(&vr.x));
+        const float2 v23 = __half22float2(*reinterpret_cast<const __half2*>(&vr.y));
+        const float vraw[4] = {v01.x, v01.y, v23.x, v23.y};
+        pk[g] = quant4(kp.v, &dk[g]);
+        pv[g] = quant4(vraw, &dv[g]);
+        const size_t word = (static_cast<size_t>(pos) * kv_dim + src) / 4 + lane;
+        p.k_qs[word] = pk[g];
+        p.v_qs[word] = pv[g];
+        if ((lane & 7) == 0) {
+          const size_t blk = static_cast<size_t>(pos) * (kv_dim / BP_QK8) + (g0 + g) * 4 + (lane >> 3);
+          p.k_d[blk] = dk[g];
+          p.v_d[blk] = dv[g];
+        }
+      }
+    }
     if (lane == 0) {
       uint32_t s = 0, use = 1;
       for (uint32_t it = ns; it < n_iter; it++) {
@@ -235,6 +287,27 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
         issue_stage(it, s);
         if (++s == ns) { s = 0; use++; }
       }
+    }
+    __syncwarp();
+    if (new_row) {
+      // The last stage was loaded with whatever the cache row held before: once it has landed,
+      // the fresh row replaces it in shared memory (swizzled tile rows and scale rows).
+      const uint32_t it_last = n_iter - 1, s_last = it_last % ns;
+      wait(&full_bar[s_last], (it_last / ns) & 1);
+      const uint32_t r = p.cur_pos - 1 - (tok_begin + it_last * UT);
+      uint8_t* stage = smem_gen + s_last * L::STAGE_B;
+#pragma unroll
+      for (uint32_t g = 0; g < HPC; g++) {
+        *reinterpret_cast<uint32_t*>(stage + g * TILE_B + swz128(r * 128 + 4 * lane)) = pk[g];
+        *reinterpret_cast<uint32_t*>(stage + (HPC + g) * TILE_B + swz128(r * 128 + 4 * lane)) = pv[g];
+        if ((lane & 7) == 0) {
+          *reinterpret_cast<float*>(stage + 2 * HPC * TILE_B + (r * HPC + g) * 16 + 4 * (lane >> 3)) = dk[g];
+          *reinterpret_cast<float*>(stage + 2 * HPC * TILE_B + L::SCALE_B + (r * HPC + g) * 16 + 4 * (lane >> 3)) = dv[g];
+        }
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&patched_bar));
     }
   } else if (warp < 1 + NISS) {
     // ---------------- QK issuers: S^T[token][(block, byte row, head)] = K tile x Q^T ----------------
@@ -248,6 +321,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
       for (uint32_t j = q; j < n_jobs; j += NISS) {
         const uint32_t it = j / HPC, g = j % HPC, bi = j % NGRP, k = j / NGRP, s = it % ns, use = it / ns;
         wait(&full_bar[s], use & 1);
+        if (p.fused && tok_end == p.cur_pos && it == n_iter - 1) wait(&patched_bar, 0);  // the new row is in place
         if (k > 0) wait(&s_free[bi], (k - 1) & 1);
         tc_fence_after();
         const uint64_t ka = dbase + ((smem_base + s * L::STAGE_B + g * TILE_B) >> 4);
@@ -525,7 +599,7 @@ static cudaError_t launch_umma(bp_attn_ctx* c, cudaStream_t s, UmmaParams& p, ui
 }
 
 cudaError_t bp_launch_decode_umma(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, const __half* q, __half* out,
-                                  uint32_t cur_pos, uint32_t* n_splits_out) {
+                                  uint32_t cur_pos, uint32_t* n_splits_out, const bp_fused_step* fs) {
   const uint32_t spp = umma_spp(c, cur_pos);
   const uint32_t n_splits = bp_decode_umma_splits(c, cur_pos);
   UmmaParams p;
@@ -541,6 +615,25 @@ cudaError_t bp_launch_decode_umma(bp_attn_ctx* c, cudaStream_t s, uint32_t layer
   p.qpg = c->qpg;
   p.sm_scale_log2 = (1.0f / sqrtf(static_cast<float>(BP_HEAD_DIM))) * 1.4426950408889634f;
   p.dbg = c->dbg_on ? c->dbg_dev : nullptr;
+  p.fused = fs != nullptr ? 1u : 0u;
+  p.eps = c->cfg.rms_eps;
+  p.n_kv_head = c->cfg.n_kv_head;
+  p.q_roped = nullptr;
+  p.w_q = p.w_k = p.k_cur = p.v_cur = p.rope_row = nullptr;
+  p.k_d = p.v_d = nullptr;
+  p.k_qs = p.v_qs = nullptr;
+  if (fs != nullptr) {
+    p.q_roped = fs->q_roped;
+    p.w_q = fs->w_q;
+    p.w_k = fs->w_k;
+    p.k_cur = fs->k_cur;
+    p.v_cur = fs->v_cur;
+    p.rope_row = c->rope + static_cast<size_t>(cur_pos - 1) * BP_HEAD_DIM;
+    p.k_d = reinterpret_cast<float*>(c->kv[0] + bp_d_off(c, layer));
+    p.v_d = reinterpret_cast<float*>(c->kv[1] + bp_d_off(c, layer));
+    p.k_qs = reinterpret_cast<uint32_t*>(c->kv[0] + bp_qs_off(c, layer));
+    p.v_qs = reinterpret_cast<uint32_t*>(c->kv[1] + bp_qs_off(c, layer));
+  }
   *n_splits_out = n_splits;
   return c->opt_uhpc == 2 ? launch_umma<2>(c, s, p, spp, n_splits) : launch_umma<1>(c, s, p, spp, n_splits);
 }

@@ -107,6 +107,16 @@ uint32_t bp_decode_max_splits(const bp_attn_ctx* c);
 cudaError_t bp_decode_umma_init(bp_attn_ctx* c);
 uint32_t bp_decode_umma_stage_tokens();
 uint32_t bp_decode_umma_splits(const bp_attn_ctx* c, uint32_t cur_pos);
+// Extra inputs of the fused layer step: raw q goes in as `q`, the kernel normalises / rotates it and
+// quantises the new token's K / V rows itself (q_roped may be null).
+struct bp_fused_step {
+  __half* q_roped;
+  const __half *w_q, *w_k, *k_cur, *v_cur;
+};
 cudaError_t bp_launch_decode_umma(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, const __half* q, __half* out,
-                                  uint32_t cur_pos, uint32_t* n_splits_out);
+                                  uint32_t cur_pos, uint32_t* n_splits_out, const bp_fused_step* fs = nullptr);
+// q_norm_rope + kv_writeback at row `pos` + decode attention over pos + 1 keys as one step.
+cudaError_t bp_launch_decode_fused(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, const __half* q_raw, __half* q_roped,
+                                   const __half* w_q, const __half* k_cur, const __half* v_cur, const __half* w_k,
+                                   uint32_t pos, __half* out, uint32_t* launches);
 inline bool bp_use_umma(const bp_attn_ctx* c) { return c->variant == 0 && c->qpg == 4 && c->have_umaps; }

@@ -316,6 +316,30 @@ int bp_attn_decode(bp_attn_ctx* c, void* stream, uint32_t layer, const void* q, 
   return BP_OK;
 }
 
+static int ensure_stage(bp_attn_ctx* c, uint32_t rows);
+
+int bp_attn_decode_layer(bp_attn_ctx* c, void* stream, uint32_t layer, const void* q_raw, void* q_roped,
+                         const void* w_q_norm, const void* k_cur, const void* v_cur, const void* w_k_norm,
+                         uint32_t pos, void* out) {
+  if (int s = enter(c)) return s;
+  if (!q_raw || !w_q_norm || !k_cur || !v_cur || !w_k_norm || !out) return fail(c, BP_ERR_NULL, "null pointer argument");
+  if (layer >= c->cfg.n_layer) return fail_config(c, "layer index out of range");
+  if (static_cast<uint64_t>(pos) + 1 > c->cfg.max_seq) return fail_overflow(c, pos, 1, c->cfg.max_seq);
+  __half* qr = static_cast<__half*>(q_roped);
+  if (qr == nullptr && !(c->variant == 0 && bp_use_umma(c))) {
+    // the separate kernels rotate q in place: give them the context's staging row
+    if (int s = bind_device(c)) return s;
+    if (int s = ensure_stage(c, 1)) return s;
+    qr = c->stage_q;
+  }
+  c->last_launches = 0;
+  BP_CUDA(c, bp_launch_decode_fused(c, static_cast<cudaStream_t>(stream), layer, static_cast<const __half*>(q_raw), qr,
+                                    static_cast<const __half*>(w_q_norm), static_cast<const __half*>(k_cur),
+                                    static_cast<const __half*>(v_cur), static_cast<const __half*>(w_k_norm), pos,
+                                    static_cast<__half*>(out), &c->last_launches));
+  return BP_OK;
+}
+
 uint32_t bp_attn_max_prefill(const bp_attn_ctx* c) {
   if (!c) return 0;
   return c->cfg.max_prefill ? (c->cfg.max_prefill < c->cfg.max_seq ? c->cfg.max_prefill : c->cfg.max_seq) : c->cfg.max_seq;
@@ -380,11 +404,16 @@ static int layer_host(bp_attn_ctx* c, uint32_t layer, const void* q, const void*
   BP_CUDA(c, cudaMemcpyAsync(c->stage_wq, wq, BP_HEAD_DIM * 2, cudaMemcpyHostToDevice, st));
   BP_CUDA(c, cudaMemcpyAsync(c->stage_wk, wk, BP_HEAD_DIM * 2, cudaMemcpyHostToDevice, st));
   uint32_t launches = 0;
-  BP_CUDA(c, bp_launch_q_norm_rope(c, st, c->stage_q, c->stage_wq, pos_base, m, &launches));
-  BP_CUDA(c, bp_launch_kv_writeback(c, st, layer, c->stage_k, c->stage_v, c->stage_wk, pos_base, m, &launches));
   if (prefill) {
+    BP_CUDA(c, bp_launch_q_norm_rope(c, st, c->stage_q, c->stage_wq, pos_base, m, &launches));
+    BP_CUDA(c, bp_launch_kv_writeback(c, st, layer, c->stage_k, c->stage_v, c->stage_wk, pos_base, m, &launches));
     BP_CUDA(c, bp_launch_prefill(c, st, layer, c->stage_q, c->stage_out, m, &launches));
+  } else if (c->variant == 0 && bp_use_umma(c)) {
+    BP_CUDA(c, bp_launch_decode_fused(c, st, layer, c->stage_q, nullptr, c->stage_wq, c->stage_k, c->stage_v, c->stage_wk,
+                                      pos_base, c->stage_out, &launches));
   } else {
+    BP_CUDA(c, bp_launch_q_norm_rope(c, st, c->stage_q, c->stage_wq, pos_base, m, &launches));
+    BP_CUDA(c, bp_launch_kv_writeback(c, st, layer, c->stage_k, c->stage_v, c->stage_wk, pos_base, m, &launches));
     BP_CUDA(c, bp_launch_decode(c, st, layer, c->stage_q, c->stage_out, pos_base + 1, &launches));
   }
   BP_CUDA(c, cudaMemcpyAsync(out, c->stage_out, qb, cudaMemcpyDeviceToHost, st));
@@ -415,13 +444,23 @@ int bp_decode_token_host(bp_attn_ctx* c, const void* q, const void* k, const voi
   BP_CUDA(c, cudaMemcpyAsync(c->stage_wq, wq, BP_HEAD_DIM * 2, cudaMemcpyHostToDevice, st));
   BP_CUDA(c, cudaMemcpyAsync(c->stage_wk, wk, BP_HEAD_DIM * 2, cudaMemcpyHostToDevice, st));
   uint32_t launches = 0;
-  // Q norm + RoPE of all layers' queries is one launch: every layer's row sits at the same position.
-  BP_CUDA(c, bp_launch_q_norm_rope_rows(c, st, c->stage_q, c->stage_wq, pos, nl, &launches));
-  for (uint32_t il = 0; il < nl; il++) {
-    BP_CUDA(c, bp_launch_kv_writeback(c, st, il, c->stage_k + static_cast<size_t>(il) * c->kv_dim,
-                                      c->stage_v + static_cast<size_t>(il) * c->kv_dim, c->stage_wk, pos, 1, &launches));
-    BP_CUDA(c, bp_launch_decode(c, st, il, c->stage_q + static_cast<size_t>(il) * c->q_dim,
-                                c->stage_out + static_cast<size_t>(il) * c->q_dim, pos + 1, &launches));
+  if (c->variant == 0 && bp_use_umma(c)) {
+    // fused layer steps: the decode kernel normalises q and writes the new cache row itself
+    for (uint32_t il = 0; il < nl; il++) {
+      BP_CUDA(c, bp_launch_decode_fused(c, st, il, c->stage_q + static_cast<size_t>(il) * c->q_dim, nullptr, c->stage_wq,
+                                        c->stage_k + static_cast<size_t>(il) * c->kv_dim,
+                                        c->stage_v + static_cast<size_t>(il) * c->kv_dim, c->stage_wk, pos,
+                                        c->stage_out + static_cast<size_t>(il) * c->q_dim, &launches));
+    }
+  } else {
+    // Q norm + RoPE of all layers' queries is one launch: every layer's row sits at the same position.
+    BP_CUDA(c, bp_launch_q_norm_rope_rows(c, st, c->stage_q, c->stage_wq, pos, nl, &launches));
+    for (uint32_t il = 0; il < nl; il++) {
+      BP_CUDA(c, bp_launch_kv_writeback(c, st, il, c->stage_k + static_cast<size_t>(il) * c->kv_dim,
+                                        c->stage_v + static_cast<size_t>(il) * c->kv_dim, c->stage_wk, pos, 1, &launches));
+      BP_CUDA(c, bp_launch_decode(c, st, il, c->stage_q + static_cast<size_t>(il) * c->q_dim,
+                                  c->stage_out + static_cast<size_t>(il) * c->q_dim, pos + 1, &launches));
+    }
   }
   BP_CUDA(c, cudaMemcpyAsync(out, c->stage_out, qb, cudaMemcpyDeviceToHost, st));
   BP_CUDA(c, cudaStreamSynchronize(st));

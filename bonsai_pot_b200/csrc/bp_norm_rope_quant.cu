@@ -17,78 +17,13 @@
 // (s0 + s2) + (s1 + s3).
 #include "bp_common.cuh"
 #include "bp_ptx.cuh"
+#include "bp_norm_quant.cuh"
 
 namespace {
 
-constexpr unsigned FULL = 0xffffffffu;
-
-struct Rot4 {
-  float v[4];
-};
-
-// Steps shared by both kernels: f16 load, RMS-norm, weight, NEOX rotation.
-// x: the head's 128 f16 values; w: norm weight [128]; rope_row: [64][2] f16.
-__device__ __forceinline__ Rot4 norm_rope(const __half* x, const __half* w, const __half* rope_row,
-                                          float eps, int lane) {
-  const uint2 xr = *reinterpret_cast<const uint2*>(x + 4 * lane);
-  const uint2 wr = *reinterpret_cast<const uint2*>(w + 4 * lane);
-  const uint4 rr = *reinterpret_cast<const uint4*>(rope_row + 8 * (lane & 15));
-  const __half2* xh = reinterpret_cast<const __half2*>(&xr);
-  const __half2* wh = reinterpret_cast<const __half2*>(&wr);
-  const __half2* rh = reinterpret_cast<const __half2*>(&rr);
-  float raw[4], wt[4], sq[4];
-  {
-    float2 a = __half22float2(xh[0]), b = __half22float2(xh[1]);
-    raw[0] = a.x; raw[1] = a.y; raw[2] = b.x; raw[3] = b.y;
-    float2 c = __half22float2(wh[0]), d = __half22float2(wh[1]);
-    wt[0] = c.x; wt[1] = c.y; wt[2] = d.x; wt[3] = d.y;
-  }
-#pragma unroll
-  for (int c = 0; c < 4; c++) sq[c] = __fmul_rn(raw[c], raw[c]);
-#pragma unroll
-  for (int off = 4; off >= 1; off >>= 1) {
-#pragma unroll
-    for (int c = 0; c < 4; c++) sq[c] = __fadd_rn(sq[c], __shfl_xor_sync(FULL, sq[c], off));
-  }
-  float w32 = __fadd_rn(__fadd_rn(sq[0], sq[2]), __fadd_rn(sq[1], sq[3]));
-  w32 = __fadd_rn(w32, __shfl_xor_sync(FULL, w32, 8));
-  const float total = __fadd_rn(w32, __shfl_xor_sync(FULL, w32, 16));
-  const float inv_h = __frsqrt_rn(__fadd_rn(__fdiv_rn(total, 128.0f), eps));
-
-  Rot4 out;
-#pragma unroll
-  for (int c = 0; c < 4; c++) {
-    const float xn = __fmul_rn(__fmul_rn(raw[c], inv_h), wt[c]);
-    const float partner = __shfl_xor_sync(FULL, xn, 16);
-    const float2 cs = __half22float2(rh[c]);  // (cos, sin) of j = dim mod 64
-    if (lane < 16) {
-      out.v[c] = __fsub_rn(__fmul_rn(xn, cs.x), __fmul_rn(partner, cs.y));
-    } else {
-      out.v[c] = __fadd_rn(__fmul_rn(partner, cs.y), __fmul_rn(xn, cs.x));
-    }
-  }
-  return out;
-}
-
-// Block-32 absmax quantiser over 8 lanes x 4 values. Returns the packed int8
-// word of this lane; *d_out is the block scale (same in all 8 lanes).
-__device__ __forceinline__ uint32_t quant4(const float* x, float* d_out) {
-  float a = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
-  a = fmaxf(a, __shfl_xor_sync(FULL, a, 1));
-  a = fmaxf(a, __shfl_xor_sync(FULL, a, 2));
-  a = fmaxf(a, __shfl_xor_sync(FULL, a, 4));
-  const float d = __fdiv_rn(a, 127.0f);
-  const float inv = d > 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
-  uint32_t packed = 0;
-#pragma unroll
-  for (int c = 0; c < 4; c++) {
-    float r = rintf(__fmul_rn(x[c], inv));
-    r = fminf(fmaxf(r, -127.0f), 127.0f);
-    packed |= (static_cast<uint32_t>(static_cast<int>(r)) & 0xffu) << (8 * c);
-  }
-  *d_out = d;
-  return packed;
-}
+using bp::Rot4;
+using bp::norm_rope;
+using bp::quant4;
 
 __global__ void __launch_bounds__(256)
 kv_writeback_kernel(const __half* __restrict__ k_cur, const __half* __restrict__ v_cur,

@@ -103,6 +103,20 @@ int bp_kv_writeback(bp_attn_ctx* ctx, void* stream, uint32_t layer, const void* 
 int bp_attn_decode(bp_attn_ctx* ctx, void* stream, uint32_t layer, const void* q, void* out,
                    uint32_t cur_pos);
 
+/* One decode step of one layer as ONE call: what `encode_step_matvec` does
+ * with three dispatches (src/forward.rs:612-631: q_norm_rope_fused,
+ * kv_writeback_fused at row `pos`, attention_split + attention_merge over
+ * pos + 1 keys). Same arithmetic and the same cache bytes as the three
+ * separate calls; on the tcgen05 decode path the decode kernel does the Q
+ * norm + RoPE and the new row's quantisation itself, which removes two kernel
+ * boundaries per layer. q_raw: device f16 [n_head*128], NOT modified;
+ * q_roped: device f16 [n_head*128] receiving the normalised, rotated q, or
+ * NULL when the caller has no use for it; k_cur, v_cur: device f16
+ * [n_kv_head*128]; out: device f16 [n_head*128]. Asynchronous on `stream`. */
+int bp_attn_decode_layer(bp_attn_ctx* ctx, void* stream, uint32_t layer, const void* q_raw, void* q_roped,
+                         const void* w_q_norm, const void* k_cur, const void* v_cur, const void* w_k_norm,
+                         uint32_t pos, void* out);
+
 /* `dispatch_attention(.., pos = 0, m_tokens = m, is_prefill = true)`
  * (src/forward.rs:501-532, params src/model.rs:195-210, kernel
  * src/shaders/attention.wgsl). q, out: device f16 [m][n_head*128]; token i

@@ -168,6 +168,49 @@ def test_decode_config0_end_to_end(seed):
     assert within_tolerance(got, ref_order)[0]
 
 
+@pytest.mark.parametrize("variant", [0, 3])
+@pytest.mark.parametrize("n_past", [0, 1, 126, 127, 128, 129, 511, 700, 4095])
+def test_decode_layer_fused_equals_the_three_dispatches(n_past, variant):
+    """bp_attn_decode_layer = q_norm_rope_fused + kv_writeback_fused + decode attention in one call
+    (src/forward.rs:612-631): the cache rows and the rotated q are bit-exact against the oracle, the raw q
+    is left alone, and the output equals the separate calls' output bit for bit."""
+    sh = O.Shape(n_layer=2, max_seq=4096)
+    layer = 1
+    rng = np.random.default_rng(31)
+    w_q = (1 + 0.1 * rng.standard_normal(128)).astype(np.float16)
+    w_k = (1 + 0.1 * rng.standard_normal(128)).astype(np.float16)
+    case = build_decode_case(sh, seed=3, cfg_id=0, layer=layer, n_past=n_past, w_q=w_q, w_k=w_k)
+    with make_ctx(sh) as ctx:
+        ctx.set_variant(variant)
+        if n_past:
+            load_cache(ctx, sh, case["kv_k"], case["kv_v"], layer, n_past)  # past rows only
+        q_raw = dev(case["q"])
+        q_roped = torch.zeros(sh.q_dim, dtype=torch.float16, device="cuda")
+        out = torch.zeros(sh.q_dim, dtype=torch.float16, device="cuda")
+        ctx.decode_layer(layer, q_raw, dev(w_q), dev(case["k_new"]), dev(case["v_new"]), dev(w_k), n_past, out,
+                         q_roped=q_roped)
+        torch.cuda.synchronize()
+        assert np.array_equal(host(q_raw).view(np.uint16).reshape(-1), case["q"].view(np.uint16).reshape(-1))
+        assert np.array_equal(host(q_roped).view(np.uint16).reshape(-1), case["qn"].view(np.uint16).reshape(-1))
+        (kd, kq), (vd, vq) = read_cache(ctx, sh, layer, n_past + 1)
+        assert np.array_equal(kq, sh.qs_section(case["kv_k"], layer)[:n_past + 1])
+        assert np.array_equal(kd.view(np.uint32), sh.d_section(case["kv_k"], layer)[:n_past + 1].view(np.uint32))
+        assert np.array_equal(vq, sh.qs_section(case["kv_v"], layer)[:n_past + 1])
+        assert np.array_equal(vd.view(np.uint32), sh.d_section(case["kv_v"], layer)[:n_past + 1].view(np.uint32))
+        fused = host(out).copy()
+        # the same step through the three dispatches, and once more fused without a q_roped buffer
+        out2 = torch.zeros_like(out)
+        ctx.dispatch_attention_decode(layer, q_roped, out2, n_past + 1)
+        out3 = torch.zeros_like(out)
+        ctx.decode_layer(layer, q_raw, dev(w_q), dev(case["k_new"]), dev(case["v_new"]), dev(w_k), n_past, out3)
+        torch.cuda.synchronize()
+        assert np.array_equal(fused.view(np.uint16), host(out2).view(np.uint16))
+        assert np.array_equal(fused.view(np.uint16), host(out3).view(np.uint16))
+    exact = O.attn_exact(sh, case["qn"], case["kv_k"], case["kv_v"], layer, 1, n_past)[0]
+    ok, max_abs, max_rel = within_tolerance(fused, exact)
+    assert ok, (max_abs, max_rel)
+
+
 @pytest.mark.parametrize("ctx_len,layer", [(4096, 1), (32768, 1)])
 def test_decode_long_context(ctx_len, layer):
     """BASELINE configs 1 and 3 at full context length (two layers allocated,
@@ -400,7 +443,7 @@ def test_host_entry_points_equal_the_device_path():
         load_cache(ctx, sh, case["kv_k"], case["kv_v"], 1, 700)
         out_h = np.zeros(sh.q_dim, dtype=np.float16)
         ctx.decode_step_host(1, case["q"], case["k_new"], case["v_new"], case["w_q"], case["w_k"], 700, out_h)
-        assert ctx.last_launch_count() >= 3
+        assert ctx.last_launch_count() >= 2  # the fused layer step + the merge of its splits
         got_dev = run_decode(ctx, sh, case, 1)
         assert np.array_equal(out_h.view(np.uint16), got_dev.view(np.uint16))
         m = 48
