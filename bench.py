@@ -271,6 +271,8 @@ def run_ours(args):
         ctx.set_option("decode_umma_heads_per_cta", args.decode_uhpc)
     if args.no_pdl:
         ctx.set_option("dependent_launch", 0)
+    if args.separate_merge:
+        ctx.set_option("decode_in_kernel_merge", 0)
     gen = torch.Generator(device="cuda")
     gen.manual_seed(1234 + rank)
     fill_cache(ctx, torch, N_LAYER, kv_dim_l, ctx_len - 1, gen)
@@ -507,6 +509,7 @@ def main():
     ap.add_argument("--decode-uhpc", type=int, default=0, help="override the tcgen05 decode kernel's KV heads per CTA")
     ap.add_argument("--separate", action="store_true",
                     help="drive a layer with the reference's three dispatches instead of the one-call layer step")
+    ap.add_argument("--separate-merge", action="store_true", help="merge the decode splits with a second kernel")
     ap.add_argument("--no-pdl", action="store_true", help="launch the kernels without programmatic dependent launch")
     ap.add_argument("--variant", type=int, default=0, help="decode kernel family (0 = production)")
     ap.add_argument("--prefill-only", type=int, default=0, metavar="PP",

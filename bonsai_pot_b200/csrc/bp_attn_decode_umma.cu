@@ -33,6 +33,7 @@ constexpr uint32_t UT = 128;                 // tokens per stage = UMMA M
 constexpr uint32_t TILE_B = UT * 128;        // int8 tile of one head and stage: 16 KB
 constexpr uint32_t U_MAX_STAGES = 6;
 constexpr uint32_t NGRP = 4;
+constexpr uint32_t EPI_BAR = 7, MERGE_BAR = 8;    // named barriers of the in-kernel merge of the splits
 constexpr uint32_t FIN_BAR = 6;                   // named barrier: softmax warps arrive, accumulate warps wait                     // softmax groups working on different jobs in parallel
 constexpr uint32_t NISS = 2;                     // UMMA issuer warps per kind (QK, PV)
 constexpr uint32_t U_FIRST_SM_WARP = 1 + 2 * NISS;  // warp 0 producer, then the issuers
@@ -51,6 +52,8 @@ struct UmmaParams {
   // Fused layer step (fused = 1): q is the RAW query; the kernel normalises and rotates it itself
   // (optionally storing the result to q_roped), and the CTAs of the last split quantise the new
   // token's K / V rows (k_cur, v_cur), write them to the cache and patch them into their last stage.
+  uint32_t merge;       // 1: the CTA of a head group that finishes last merges the splits itself
+  uint32_t* tickets;    // one arrival counter per head group (grid y), zero between launches
   uint32_t fused;
   float eps;
   __half* q_roped;
@@ -78,6 +81,7 @@ struct Misc {            // small shared state, lives in the MISC_B region
   float info[NGRP][8];      // per group: corr[4], dequantisation factor of P' per block [4]
   float lsum[NGRP][4][4];   // final l per (softmax group, query head, warp)
   float mfin[NGRP][4];
+  uint32_t is_last;         // this CTA took the last ticket of its head group
 };
 
 __device__ __forceinline__ float s32_to_f32(uint32_t x) {  // exact for |x| < 2^22
@@ -248,6 +252,44 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
   // buffer; its k-th job (k = j / NGRP) completes phase k of its barriers.
   // A wait that degrades to a no-op once any warp of the CTA has timed out.
   auto wait = [&](uint64_t* bar, uint32_t parity) { cta_wait(bar, parity, &abort_s, p.err); };
+  // Log-sum-exp merge over the splits (attention_merge.wgsl:70-130) by the softmax and accumulate
+  // warps (640 threads) of the CTA that took the last ticket: thread = one output element.
+  auto merge_splits = [&]() {
+    pdl_wait();
+    __threadfence();
+    const uint32_t tid = threadIdx.x - U_FIRST_SM_WARP * 32, n_thr = 128 * NGRP + 128;
+    const size_t stride = static_cast<size_t>(p.n_head) * BP_PART_STRIDE;
+    for (uint32_t idx = tid; idx < HPC * p.qpg * BP_HEAD_DIM; idx += n_thr) {
+      const uint32_t hl = idx >> 7, d = idx & 127;
+      const uint32_t h = g0 * p.qpg + hl;
+      const float* base = p.partials + static_cast<size_t>(h) * BP_PART_STRIDE;
+      float m_all = NEG_BIG, o = 0.f, l = 0.f;
+      for (uint32_t s0 = 0; s0 < n_splits; s0 += 6) {
+        float2 ml[6];
+        float v[6];
+#pragma unroll
+        for (uint32_t k = 0; k < 6; k++) {
+          const bool in = s0 + k < n_splits;
+          ml[k] = in ? __ldcg(reinterpret_cast<const float2*>(base + (s0 + k) * stride + 128)) : make_float2(NEG_BIG, 0.f);
+          v[k] = in ? __ldcg(base + (s0 + k) * stride + d) : 0.f;
+        }
+        float m_new = m_all;
+#pragma unroll
+        for (uint32_t k = 0; k < 6; k++) m_new = fmaxf(m_new, ml[k].x);
+        const float c = ex2(m_all - m_new);
+        o *= c;
+        l *= c;
+        m_all = m_new;
+#pragma unroll
+        for (uint32_t k = 0; k < 6; k++) {
+          const float e = ex2(ml[k].x - m_all);
+          o = fmaf(v[k], e, o);
+          l = fmaf(ml[k].y, e, l);
+        }
+      }
+      p.out[static_cast<size_t>(h) * BP_HEAD_DIM + d] = __float2half_rn(o * (1.0f / l));
+    }
+  };
 
   if (warp == 0) {
     // ---------------- TMA producer: the rounds of the ring after the first (requested during set-up) ----------------
@@ -473,6 +515,10 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
     }
     __threadfence_block();
     named_bar_arrive(FIN_BAR, 128 * NGRP + 128);  // the accumulate warps merge the groups
+    if (n_splits > 1 && p.merge) {
+      named_bar_sync(MERGE_BAR, 128 * NGRP + 128);  // the ticket has been drawn
+      if (misc->is_last) merge_splits();
+    }
   } else {
     // ---------------- accumulate: thread = head dim ----------------
     prepare_q(warp - (U_FIRST_SM_WARP + 4 * NGRP));
@@ -537,6 +583,20 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
           if (dim == 0) { dst[128] = m; dst[129] = l; }
         }
       }
+    }
+    if (n_splits > 1 && p.merge) {
+      // Publish the partial, draw a ticket; the CTA of this head group that arrives last merges.
+      __threadfence();
+      named_bar_sync(EPI_BAR, 128);
+      if (warp == U_FIRST_SM_WARP + 4 * NGRP && lane == 0) {
+        const uint32_t t = atomicAdd(&p.tickets[blockIdx.y], 1u);
+        const uint32_t last = t == n_splits - 1 ? 1u : 0u;
+        if (last) p.tickets[blockIdx.y] = 0;  // every other CTA has arrived: the next launch starts from zero
+        misc->is_last = last;
+        __threadfence_block();
+      }
+      named_bar_sync(MERGE_BAR, 128 * NGRP + 128);
+      if (misc->is_last) merge_splits();
     }
   }
 
@@ -615,6 +675,8 @@ cudaError_t bp_launch_decode_umma(bp_attn_ctx* c, cudaStream_t s, uint32_t layer
   p.qpg = c->qpg;
   p.sm_scale_log2 = (1.0f / sqrtf(static_cast<float>(BP_HEAD_DIM))) * 1.4426950408889634f;
   p.dbg = c->dbg_on ? c->dbg_dev : nullptr;
+  p.merge = c->opt_umerge;
+  p.tickets = c->tickets;
   p.fused = fs != nullptr ? 1u : 0u;
   p.eps = c->cfg.rms_eps;
   p.n_kv_head = c->cfg.n_kv_head;
@@ -634,6 +696,6 @@ cudaError_t bp_launch_decode_umma(bp_attn_ctx* c, cudaStream_t s, uint32_t layer
     p.k_qs = reinterpret_cast<uint32_t*>(c->kv[0] + bp_qs_off(c, layer));
     p.v_qs = reinterpret_cast<uint32_t*>(c->kv[1] + bp_qs_off(c, layer));
   }
-  *n_splits_out = n_splits;
+  *n_splits_out = p.merge ? 1 : n_splits;  // nothing left to merge for the caller
   return c->opt_uhpc == 2 ? launch_umma<2>(c, s, p, spp, n_splits) : launch_umma<1>(c, s, p, spp, n_splits);
 }

@@ -39,18 +39,20 @@ using namespace bp;
 
 constexpr unsigned FULL = 0xffffffffu;
 constexpr float NEG_BIG = -1e30f;
-constexpr uint32_t BM = 128, BN = 128;
+constexpr uint32_t BM = 128, BN = 64;             // query rows per tile, keys per tile
 constexpr uint32_t P_TMEM_COLS = 512;            // S_A, S_B, O_A, O_B: 128 columns each
 constexpr uint32_t P_WAIT_LIMIT = 1u << 22;
 constexpr uint32_t OPER_B = 2 * 16384;           // one f16 operand tile: 2 chunks of [128 rows][128 B]
-constexpr uint32_t KV_SLOTS = 2;
+constexpr uint32_t KV_SLOTS = 4;
+constexpr uint32_t KV_TILE_B = 2 * 8192;          // one f16 K or V tile: 2 chunks of [64 keys][128 B]
+constexpr uint32_t SW = 128;                      // TMEM columns of one query tile's S region (two 64-column buffers) and of O
 constexpr uint32_t TM_S = 0, TM_O = 256;         // TMEM columns: S_X at TM_S + 128 X, O_X at TM_O + 128 X
 
 template <uint32_t NQ>
 struct PLayout {
   static constexpr uint32_t THREADS = 32 + NQ * 32 + NQ * 128;  // producer, NQ issuers, NQ softmax groups of 4 warps
-  static constexpr uint32_t OFF_Q = 0, OFF_K = NQ * OPER_B, OFF_V = OFF_K + KV_SLOTS * OPER_B;
-  static constexpr uint32_t SMEM = OFF_V + KV_SLOTS * OPER_B + 1024;
+  static constexpr uint32_t OFF_Q = 0, OFF_K = NQ * OPER_B, OFF_V = OFF_K + KV_SLOTS * KV_TILE_B;
+  static constexpr uint32_t SMEM = OFF_V + KV_SLOTS * KV_TILE_B + 1024;
 };
 
 struct PrefillParams {
@@ -153,7 +155,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t k_full[KV_SLOTS], v_full[KV_SLOTS];
   __shared__ __align__(8) uint64_t k_empty[NQ][KV_SLOTS], v_empty[NQ][KV_SLOTS];  // per query tile: it is done with the slot
-  __shared__ __align__(8) uint64_t s_ready[NQ], p_ready[NQ], o_done[NQ];
+  __shared__ __align__(8) uint64_t s_ready[NQ][2], p_ready[NQ], o_done[NQ];
   __shared__ uint32_t tmem_base_s, item_s;
   __shared__ volatile uint32_t abort_s;
 
@@ -173,7 +175,8 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       }
     }
     for (uint32_t x = 0; x < NQ; x++) {
-      mbar_init(smem_u32(&s_ready[x]), 1);
+      mbar_init(smem_u32(&s_ready[x][0]), 1);
+      mbar_init(smem_u32(&s_ready[x][1]), 1);
       mbar_init(smem_u32(&p_ready[x]), 4);
       mbar_init(smem_u32(&o_done[x]), 1);
     }
@@ -211,6 +214,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
 #pragma unroll
   for (uint32_t x = 0; x < NQ; x++) { gx[x] = 0; od[x] = 0; }
   uint32_t pend_k = 0, pend_v = 0, phase_k = 0, phase_v = 0;
+  uint32_t vph = 0;  // softmax threads: next phase of "P V complete" per K/V slot, for their own query tile
 
   for (;;) {
     // An item is fetched only when the CTA is free (fetching ahead would defeat longest-first balancing).
@@ -277,8 +281,8 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
           }
           pend_k = (pend_k & ~slot_bits) | users;
           if (abort_s) break;
-          mbar_arrive_expect_tx(smem_u32(&k_full[s]), OPER_B);
-          tma_load_3d(smem_base + L::OFF_K + s * OPER_B, &map_k, smem_u32(&k_full[s]), 0, row, static_cast<int>(2 * g));
+          mbar_arrive_expect_tx(smem_u32(&k_full[s]), KV_TILE_B);
+          tma_load_3d(smem_base + L::OFF_K + s * KV_TILE_B, &map_k, smem_u32(&k_full[s]), 0, row, static_cast<int>(2 * g));
 #pragma unroll
           for (uint32_t x = 0; x < NQ; x++) {
             const uint32_t bit = 1u << (x * KV_SLOTS + s);
@@ -289,8 +293,8 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
           }
           pend_v = (pend_v & ~slot_bits) | users;
           if (abort_s) break;
-          mbar_arrive_expect_tx(smem_u32(&v_full[s]), OPER_B);
-          tma_load_3d(smem_base + L::OFF_V + s * OPER_B, &map_v, smem_u32(&v_full[s]), 0, row, static_cast<int>(2 * g));
+          mbar_arrive_expect_tx(smem_u32(&v_full[s]), KV_TILE_B);
+          tma_load_3d(smem_base + L::OFF_V + s * KV_TILE_B, &map_v, smem_u32(&v_full[s]), 0, row, static_cast<int>(2 * g));
         }
       }
     } else if (warp <= NQ) {
@@ -300,72 +304,72 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       const uint32_t x = warp - 1;
       const uint32_t n_mine = nx[x], c0 = gx[x];
       if (lane == 0 && n_mine > 0) {
-        constexpr uint32_t IDESC_QK = umma_idesc(1, 0, 0, 0, 0, BM, BN);  // f32 = f16 (K-major) x f16 (K-major)
-        constexpr uint32_t IDESC_PV = umma_idesc(1, 0, 0, 0, 1, BM, BN);  // f32 += f16 (TMEM) x f16 (MN-major)
+        constexpr uint32_t IDESC_QK = umma_idesc(1, 0, 0, 0, 0, BM, BN);   // f32 = f16 (K-major) x f16 (K-major), N = 64 keys
+        constexpr uint32_t IDESC_PV = umma_idesc(1, 0, 0, 0, 1, BM, 128);  // f32 += f16 (TMEM) x f16 (MN-major), N = 128 dims
         const uint64_t dk = umma_desc_sw128(0, 16, 1024);       // K-major operands
-        const uint64_t dmn = umma_desc_sw128(0, 16384, 1024);   // V: next 64 dims 16 KB away, 8 key rows 1 KB apart
+        const uint64_t dmn = umma_desc_sw128(0, 8192, 1024);    // V: next 64 dims 8 KB away, 8 key rows 1 KB apart
         const uint64_t qa = dk + ((smem_base + L::OFF_Q + x * OPER_B) >> 4);
-        const uint32_t s_col = tmem + TM_S + x * BN, o_col = tmem + TM_O + x * BN;
+        const uint32_t s_col = tmem + TM_S + x * SW, o_col = tmem + TM_O + x * SW;
+        // S of tile i goes to buffer (c0 + i) & 1 of the query tile's S region; P of the tile is
+        // written over it and read from there by P V. Q K^T runs two tiles ahead of P V, so a
+        // tile's softmax overlaps the MMAs of its neighbours.
         auto issue_qk = [&](uint32_t i) {
-          const uint32_t s = (gkv + i) % KV_SLOTS;
+          const uint32_t s = (gkv + i) % KV_SLOTS, b = (c0 + i) & 1;
           waitx(&k_full[s], ((gkv + i) / KV_SLOTS) & 1, 0);
           tc_fence_after();
-          const uint64_t kb = dk + ((smem_base + L::OFF_K + s * OPER_B) >> 4);
+          const uint64_t kb = dk + ((smem_base + L::OFF_K + s * KV_TILE_B) >> 4);
 #pragma unroll
           for (uint32_t ks = 0; ks < 8; ks++) {  // 16 dims per UMMA: chunk ks / 4, 32 bytes per step inside it
-            const uint32_t o16 = (ks >> 2) * (16384 >> 4) + (ks & 3) * 2;
-            umma_f16(s_col, qa + o16, kb + o16, IDESC_QK, ks);
+            const uint32_t qo = (ks >> 2) * (16384 >> 4) + (ks & 3) * 2, ko = (ks >> 2) * (8192 >> 4) + (ks & 3) * 2;
+            umma_f16(s_col + 64 * b, qa + qo, kb + ko, IDESC_QK, ks);
           }
-          // also tells that every earlier MMA of this thread, the previous tile's P V included, is complete
-          umma_commit(smem_u32(&s_ready[x]));
+          umma_commit(smem_u32(&s_ready[x][b]));
         };
-        // Start half a period behind the previous query tile, so that one tile's softmax runs while
-        // the other one's MMAs do instead of both contending for the same unit at the same time.
-        if ((p.flags & 1u) && x > 0 && nx[x > 0 ? x - 1 : 0] > 0) waitx(&p_ready[x > 0 ? x - 1 : 0], gx[x > 0 ? x - 1 : 0] & 1, 3);
         issue_qk(0);
+        if (n_mine > 1) issue_qk(1);
         for (uint32_t i = 0; i < n_mine; i++) {
-          const uint32_t s = (gkv + i) % KV_SLOTS;
-          const uint64_t vb = dmn + ((smem_base + L::OFF_V + s * OPER_B) >> 4);
+          const uint32_t s = (gkv + i) % KV_SLOTS, b = (c0 + i) & 1;
+          const uint64_t vb = dmn + ((smem_base + L::OFF_V + s * KV_TILE_B) >> 4);
           waitx(&v_full[s], ((gkv + i) / KV_SLOTS) & 1, 1);
           waitx(&p_ready[x], (c0 + i) & 1, 2);
           tc_fence_after();
 #pragma unroll
-          for (uint32_t ks = 0; ks < 8; ks++)  // 16 keys per UMMA: 8 columns of P, 16 rows of V
-            umma_f16_ts(o_col, s_col + 8 * ks, vb + ks * (16 * 128 >> 4), IDESC_PV, (i | ks) ? 1u : 0u);
-          if (i + 1 < n_mine) issue_qk(i + 1);  // overwrites S_X / P_X: ordered after the P V above by the tensor pipe
-          else umma_commit(smem_u32(&o_done[x]));
+          for (uint32_t ks = 0; ks < 4; ks++)  // 16 keys per UMMA: 8 columns of P, 16 rows of V
+            umma_f16_ts(o_col, s_col + 64 * b + 8 * ks, vb + ks * (16 * 128 >> 4), IDESC_PV, (i | ks) ? 1u : 0u);
+          umma_commit(smem_u32(&v_empty[x][s]));  // P V of tile i complete: V slot free, O_X consistent
+          if (i + 2 < n_mine) issue_qk(i + 2);    // into the buffer P V just read: ordered behind it by the tensor pipe
         }
+        umma_commit(smem_u32(&o_done[x]));
       }
     } else {
       // ---------------- softmax group X: thread = query row = TMEM lane ----------------
       const uint32_t x = (warp - 1 - NQ) >> 2, quad = warp & 3, r = quad * 32 + lane;
       const bool elected = ((warp - 1 - NQ) & 3) == 0 && lane == 0;  // releases the K / V slots for this query tile
       const uint32_t lane_addr = (quad * 32) << 16;
-      const uint32_t s_addr = tmem + lane_addr + TM_S + x * BN, o_addr = tmem + lane_addr + TM_O + x * BN;
+      const uint32_t s_addr = tmem + lane_addr + TM_S + x * SW, o_addr = tmem + lane_addr + TM_O + x * SW;
       const uint32_t tok = tq0[x] + r / p.qpg, head = g * p.qpg + r % p.qpg;
       const uint32_t n_mine = nx[x], c0 = gx[x];
       float m_run = NEG_BIG, l_run = 0.f;
+      uint32_t prev_par = 0, prev_slot = 0;  // phase and slot of the previous tile's "P V complete" barrier
       for (uint32_t i = 0; i < n_mine; i++) {
-        waitx(&s_ready[x], (c0 + i) & 1, 0);
+        const uint32_t b = (c0 + i) & 1, slot = (gkv + i) % KV_SLOTS;
+        waitx(&s_ready[x][b], ((c0 + i) >> 1) & 1, 0);
         tc_fence_after();
-        if (elected) {  // Q K^T of tile i and P V of tile i - 1 are complete
-          mbar_arrive(smem_u32(&k_empty[x][(gkv + i) % KV_SLOTS]));
-          if (i > 0) mbar_arrive(smem_u32(&v_empty[x][(gkv + i - 1) % KV_SLOTS]));
-        }
-        uint32_t raw[128];
-#pragma unroll
-        for (uint32_t c = 0; c < 4; c++) tmem_ld32(s_addr + 32 * c, raw + 32 * c);
+        if (elected) mbar_arrive(smem_u32(&k_empty[x][slot]));  // Q K^T of tile i is complete
+        uint32_t raw[64];
+        tmem_ld32(s_addr + 64 * b, raw);
+        tmem_ld32(s_addr + 64 * b + 32, raw + 32);
         tmem_ld_wait();
         // causal mask: key i * BN + c is visible to this row iff key <= tok (only the last tile can cut)
         if ((i + 1) * BN > tq0[x] + 1) {
           const uint32_t k0 = i * BN;
 #pragma unroll
-          for (int c = 0; c < 128; c++)
+          for (int c = 0; c < 64; c++)
             if (k0 + c > tok) raw[c] = __float_as_uint(NEG_BIG);
         }
         float mx[4] = {__uint_as_float(raw[0]), __uint_as_float(raw[1]), __uint_as_float(raw[2]), __uint_as_float(raw[3])};
 #pragma unroll
-        for (int c = 4; c < 128; c += 4) {
+        for (int c = 4; c < 64; c += 4) {
 #pragma unroll
           for (int k = 0; k < 4; k++) mx[k] = fmaxf(mx[k], __uint_as_float(raw[c + k]));
         }
@@ -375,9 +379,12 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         const float corr = grow ? ex2(m_run - m_new) : 1.0f;
         m_run = m_new;
         if (i > 0 && __any_sync(FULL, grow)) {
-          // O_X is idle here: the previous tile's P V completed before s_ready fired
+          // O_X may be rescaled only between two P V: the previous tile's must have completed (this
+          // tile's is not issued before this thread hands over P)
+          waitx(&v_empty[x][prev_slot], prev_par, 1);
+          tc_fence_after();
 #pragma unroll 1
-          for (uint32_t c = 0; c < 8; c++) {  // 16 columns at a time: the row's 128 S values stay live in registers
+          for (uint32_t c = 0; c < 8; c++) {
             uint32_t o[16];
             tmem_ld16(o_addr + 16 * c, o);
             tmem_ld_wait();
@@ -386,21 +393,22 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             tmem_st16(o_addr + 16 * c, o);
           }
         }
-        // P over the first 64 columns of S_X (every S value of this row is in registers by now)
+        // the completion of this tile's P V will be phase `vph bit slot` of its slot's barrier
+        prev_par = (vph >> slot) & 1u;
+        prev_slot = slot;
+        vph ^= 1u << slot;
+        // P over the first 32 columns of the buffer (every S value of this row is in registers by now)
         float sum[4] = {0.f, 0.f, 0.f, 0.f};
+        uint32_t ph[32];
 #pragma unroll
-        for (int hf = 0; hf < 2; hf++) {
-          uint32_t ph[32];
-#pragma unroll
-          for (int c = 0; c < 32; c++) {
-            const float p0 = ex2(fmaf(__uint_as_float(raw[64 * hf + 2 * c]), p.scale_log2, -m_new));
-            const float p1 = ex2(fmaf(__uint_as_float(raw[64 * hf + 2 * c + 1]), p.scale_log2, -m_new));
-            sum[c & 3] += p0 + p1;
-            __half2 h = __floats2half2_rn(p0, p1);
-            ph[c] = *reinterpret_cast<uint32_t*>(&h);
-          }
-          tmem_st32(s_addr + 32 * hf, ph);
+        for (int c = 0; c < 32; c++) {
+          const float p0 = ex2(fmaf(__uint_as_float(raw[2 * c]), p.scale_log2, -m_new));
+          const float p1 = ex2(fmaf(__uint_as_float(raw[2 * c + 1]), p.scale_log2, -m_new));
+          sum[c & 3] += p0 + p1;
+          __half2 h = __floats2half2_rn(p0, p1);
+          ph[c] = *reinterpret_cast<uint32_t*>(&h);
         }
+        tmem_st32(s_addr + 64 * b, ph);
         l_run = l_run * corr + ((sum[0] + sum[1]) + (sum[2] + sum[3]));
         tmem_st_wait();
         tc_fence_before();
@@ -411,7 +419,6 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       if (n_mine > 0) {
         waitx(&o_done[x], od[x] & 1, 2);
         tc_fence_after();
-        if (elected) mbar_arrive(smem_u32(&v_empty[x][(gkv + n_mine - 1) % KV_SLOTS]));
         const float inv_l = 1.0f / l_run;
         __half* dst = p.out + (static_cast<size_t>(tok) * p.n_head + head) * BP_HEAD_DIM;
 #pragma unroll

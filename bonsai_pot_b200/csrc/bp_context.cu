@@ -249,6 +249,7 @@ int bp_attn_create(const bp_attn_config* cfg, bp_attn_ctx** out) {
   c->opt_nw = 8;
   c->opt_hpc = cfg->n_kv_head;
   c->opt_pdl = 1;
+  c->opt_umerge = 1;
   c->opt_uhpc = 1;  // one KV head per CTA measured faster than two at every context length tried
   if (!rebuild_decode_maps(c)) return fail(c, BP_ERR_CUDA, "cuTensorMapEncodeTiled failed for the KV cache");
   BP_CUDA(c, bp_decode_init(c));
@@ -650,6 +651,9 @@ int bp_set_option(bp_attn_ctx* c, const char* name, uint32_t value) {
     if ((value != 1 && value != 2) || c->cfg.n_kv_head % value != 0)
       return fail_config(c, "decode_umma_heads_per_cta must be 1 or 2 and divide n_kv_head");
     c->opt_uhpc = value;
+  } else if (strcmp(name, "decode_in_kernel_merge") == 0) {
+    c->opt_umerge = value != 0;
+    return BP_OK;
   } else if (strcmp(name, "dependent_launch") == 0) {
     c->opt_pdl = value != 0;
     return BP_OK;

@@ -443,7 +443,7 @@ def test_host_entry_points_equal_the_device_path():
         load_cache(ctx, sh, case["kv_k"], case["kv_v"], 1, 700)
         out_h = np.zeros(sh.q_dim, dtype=np.float16)
         ctx.decode_step_host(1, case["q"], case["k_new"], case["v_new"], case["w_q"], case["w_k"], 700, out_h)
-        assert ctx.last_launch_count() >= 2  # the fused layer step + the merge of its splits
+        assert ctx.last_launch_count() >= 1  # one fused layer step (the last CTA of a head merges the splits)
         got_dev = run_decode(ctx, sh, case, 1)
         assert np.array_equal(out_h.view(np.uint16), got_dev.view(np.uint16))
         m = 48
