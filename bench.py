@@ -354,12 +354,13 @@ def run_ours(args):
         dt_k = time_region(torch, decode_graph, reps, stream) / (reps * N_LAYER)
     algo_bytes_launch = ctx_len * BYTES_PER_TOKEN_LAYER // world
     achieved = algo_bytes_launch / dt_k / 1e9
-    # DRAM traffic per launch: one ncu capture of the decode kernel at ctx 32768 read 75.57 MB and wrote
-    # 1.8 MB (the split partials) against 75.50 MB of algorithmic bytes (profiles/decode_umma_kernel_ctx32768.md);
-    # reads grow in proportion to the tokens streamed, the partials do not, so the capture is scaled by
-    # tokens for the reads and taken as is for the writes.
-    traffic = int(75.57e6 * ctx_len / 32768 / world + 1.8e6 / world) if args.variant == 0 else None
-    roofline = {"bound": "hbm", "kernel": "decode_umma_kernel + attn_combine_kernel", "achieved": round(achieved, 1),
+    # DRAM traffic per launch: one ncu capture of the decode kernel at ctx 32768 read 75.57 MB against
+    # 75.50 MB of algorithmic bytes (profiles/decode_umma_kernel_ctx32768.md); reads grow in proportion to
+    # the tokens streamed, so the capture is scaled by tokens. The split partials (written once, read back
+    # from L2 by the merging CTA) are added as written bytes.
+    n_splits = ctx.decode_num_splits(pos + 1) if hasattr(ctx, "decode_num_splits") else 18
+    traffic = int(75.57e6 * ctx_len / 32768 / world + n_splits * nh_l * 132 * 4) if args.variant == 0 else None
+    roofline = {"bound": "hbm", "kernel": "decode_umma_kernel (splits merged by the last CTA of each head group)", "achieved": round(achieved, 1),
                 "peak": hbm_peak, "unit": "GB/s", "frac": round(achieved / hbm_peak, 4), "peak_kind": peak_kind,
                 "us_per_launch": round(dt_k * 1e6, 3), "algorithmic_bytes_per_launch": algo_bytes_launch,
                 "traffic": traffic, "frac_of_8000_spec": round(achieved / 8000.0, 4)}

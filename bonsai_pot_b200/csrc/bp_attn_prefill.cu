@@ -13,16 +13,18 @@
 //    (tcgen05.mma kind::f16, accumulators in TMEM). A work item is one KV head
 //    and NQ query tiles of 128 rows each; a tile's rows are 128 / qpg
 //    consecutive tokens times the qpg query heads of the group. Persistent
-//    CTAs fetch items, longest first, from a global counter. Per tile of 128
-//    keys and per query tile X:
+//    CTAs fetch items, longest first, from a global counter. Keys come in
+//    tiles of 64. Per key tile and per query tile X:
 //      producer warp   TMA: f16 K and V tiles (128-byte swizzle) straight into UMMA operand layout
-//      issuer warp     S_X = Q_X K^T (8 UMMAs M 128, N 128, K 16) into TMEM;
-//                      O_X += P_X V with P_X read from TMEM as the A operand
+//      issuer warp X   S_X = Q_X K^T (8 UMMAs M 128, N 64, K 16) into one of the two 64-column
+//                      buffers of X's S region in TMEM, two tiles ahead of
+//                      O_X += P_X V (4 UMMAs M 128, N 128, K 16, P_X read from TMEM as the A operand)
 //      softmax group X thread = query row = TMEM lane: scale, causal mask, online max / sum,
-//                      P as f16 written over S_X in TMEM; O_X is rescaled in TMEM only when
-//                      a row maximum grew by more than 2^8 (P stays below 2^8 meanwhile)
-//    With NQ = 2 the tensor core works on one query tile while the other one's
-//    softmax runs.
+//                      P as f16 written over the tile's S buffer; O_X is rescaled in TMEM only
+//                      when a row maximum grew by more than 2^8 (P stays below 2^8 meanwhile)
+//    S is double-buffered so that a tile's softmax overlaps the MMAs of its neighbours; with
+//    NQ = 2 the two query tiles share every K / V tile and fill each other's gaps.
+//    TMEM: S_A, S_B, O_A, O_B, 128 columns each.
 // Every wait is bounded; a timeout sets the context's error word and the CTA
 // winds down and frees its TMEM.
 #include "bp_common.cuh"
@@ -62,7 +64,6 @@ struct PrefillParams {
   uint32_t* counter;        // work-item counter, zeroed by the expand kernel of the same layer
   uint32_t m, n_head, n_kv_head, qpg, n_groups;  // n_groups = ceil(m / (NQ * 128 / qpg))
   unsigned long long* dbg;  // development aid: cycle counters of CTA 0, null in normal use
-  uint32_t flags;           // bit 0: stagger the query tiles of an item
   float scale_log2;
 };
 
@@ -521,7 +522,6 @@ cudaError_t bp_launch_prefill(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, co
   p.n_kv_head = c->cfg.n_kv_head;
   p.dbg = c->dbg_on ? c->dbg_dev : nullptr;
   p.qpg = c->qpg;
-  p.flags = c->opt_pf_flags;
   p.scale_log2 = (1.0f / sqrtf(static_cast<float>(BP_HEAD_DIM))) * 1.4426950408889634f;
   const uint32_t tq_tokens = BM / c->qpg;
   const uint32_t sms = static_cast<uint32_t>(c->sm_count);

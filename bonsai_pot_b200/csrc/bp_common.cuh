@@ -53,7 +53,6 @@ struct bp_attn_ctx {
   uint32_t opt_umerge; // tcgen05 decode: merge the splits in the decode kernel (1) or with a second kernel (0)
   uint32_t opt_pdl;  // launch the kernels of a layer with programmatic stream serialization (1) or plainly (0)
   uint32_t opt_pf_nq; // prefill: query tiles per work item (1 or 2), 0 = by batch size
-  uint32_t opt_pf_flags; // prefill: scheduling experiments (bit 0: stagger the query tiles of an item)
   uint32_t last_launches;
   int status;  // latched device-lost status, BP_OK otherwise
   bp_error_detail detail;

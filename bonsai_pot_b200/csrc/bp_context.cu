@@ -657,9 +657,6 @@ int bp_set_option(bp_attn_ctx* c, const char* name, uint32_t value) {
   } else if (strcmp(name, "dependent_launch") == 0) {
     c->opt_pdl = value != 0;
     return BP_OK;
-  } else if (strcmp(name, "prefill_flags") == 0) {
-    c->opt_pf_flags = value;
-    return BP_OK;
   } else if (strcmp(name, "prefill_tiles_per_item") == 0) {
     if (value > 2) return fail_config(c, "prefill_tiles_per_item must be 0 (by batch size), 1 or 2");
     c->opt_pf_nq = value;
