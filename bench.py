@@ -285,6 +285,28 @@ def run_ours(args):
     q_work = q_raw.clone()
     out_local = torch.zeros(N_LAYER, q_dim_l, dtype=torch.float16, device="cuda")
     out_full = torch.zeros(N_LAYER, Q_DIM, dtype=torch.float16, device="cuda") if world > 1 else out_local
+    # N > 1: the decode kernel's epilogue stores its heads straight into every rank's gathered buffer (peer
+    # stores over NVLink, buffers from torch's symmetric-memory allocator) and one small kernel per token
+    # waits for all ranks' arrivals. --nccl-gather keeps the plain NCCL all-gather after every layer instead.
+    exchange = "none"
+    if world > 1:
+        exchange = "nccl all-gather per layer"
+        if not args.nccl_gather and not args.separate and args.variant == 0:
+            try:
+                import torch.distributed._symmetric_memory as symm_mem
+                out_full = symm_mem.empty((N_LAYER, Q_DIM), dtype=torch.float16, device=torch.device("cuda", local_rank))
+                px_flags = symm_mem.empty((64,), dtype=torch.int32, device=torch.device("cuda", local_rank))
+                out_full.zero_()
+                px_flags.zero_()
+                h_out = symm_mem.rendezvous(out_full, dist.group.WORLD)
+                h_flag = symm_mem.rendezvous(px_flags, dist.group.WORLD)
+                torch.cuda.synchronize()
+                dist.barrier()
+                ctx.set_peer_exchange(list(h_out.buffer_ptrs), list(h_flag.buffer_ptrs))
+                exchange = "peer stores in the decode epilogue + one wait kernel per token"
+            except Exception as e:  # no peer mapping on this box: fall back to NCCL
+                print(f"[bench] symmetric memory unavailable ({type(e).__name__}: {e}); using NCCL all-gather", file=sys.stderr)
+    use_px = exchange.startswith("peer")
     pos = ctx_len - 1
     stream = torch.cuda.Stream()
     launches_per_step = 0
@@ -305,14 +327,27 @@ def run_ours(args):
             else:  # the same layer step as one call (bp_attn_decode_layer)
                 ctx.decode_layer(il, q_raw[il], w, k_new[il], v_new[il], w, pos, out_local[il], stream=stream)
                 n += ctx.last_launch_count()
-            if world > 1:
+            if world > 1 and not use_px:
                 dist.all_gather_into_tensor(out_full[il], out_local[il])
+        if use_px:
+            ctx.peer_wait(stream=stream)
+            n += 1
         launches_per_step = n
 
     # Capture one token (36 dependent layers) in a CUDA graph: launch-bound otherwise.
     with torch.cuda.stream(stream):
         one_token()
         stream.synchronize()
+        if use_px:
+            # the gathered buffer must equal an NCCL all-gather of the ranks' local outputs
+            dist.barrier()
+            check = torch.zeros(N_LAYER, world, q_dim_l, dtype=torch.float16, device="cuda")
+            for il in range(N_LAYER):
+                dist.all_gather_into_tensor(check[il].reshape(-1), out_local[il])
+            torch.cuda.synchronize()
+            if not torch.equal(check.reshape(N_LAYER, Q_DIM), out_full):
+                raise SystemExit("peer exchange: the gathered buffer differs from the NCCL all-gather")
+            dist.barrier()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
             one_token()
@@ -372,7 +407,7 @@ def run_ours(args):
         "data": "synthetic",
         "config": {"workload": f"decode_ctx{ctx_len}_{N_LAYER}layers", "n_head": N_HEAD, "n_kv_head": N_KV_HEAD,
                    "head_dim": HEAD_DIM, "kv_cache": "Q8_0 (int8 + f32 block scales)", "bytes_per_token_layer": BYTES_PER_TOKEN_LAYER,
-                   "parallelism": f"kv_head_shard{world}" if world > 1 else "single",
+                   "parallelism": f"kv_head_shard{world}" if world > 1 else "single", "exchange": exchange,
                    "launch": "36 dependent layers in one CUDA graph, " + ("three dispatches per layer" if args.separate else "one bp_attn_decode_layer call per layer"), "l2": "working set 340 MB per step > 126 MB L2",
                    "us_per_layer": round(sec_per_step * 1e6 / N_LAYER, 3)},
         "roofline": roofline, "gpu_launches": launches_per_step * args.steps,
@@ -511,6 +546,7 @@ def main():
     ap.add_argument("--separate", action="store_true",
                     help="drive a layer with the reference's three dispatches instead of the one-call layer step")
     ap.add_argument("--separate-merge", action="store_true", help="merge the decode splits with a second kernel")
+    ap.add_argument("--nccl-gather", action="store_true", help="N > 1: all-gather the head outputs with NCCL after every layer")
     ap.add_argument("--no-pdl", action="store_true", help="launch the kernels without programmatic dependent launch")
     ap.add_argument("--variant", type=int, default=0, help="decode kernel family (0 = production)")
     ap.add_argument("--prefill-only", type=int, default=0, metavar="PP",

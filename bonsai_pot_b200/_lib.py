@@ -98,6 +98,8 @@ SIGNATURES = {
     "bp_last_launch_count": (_u32, [_vp]),
     "bp_decode_num_splits": (_u32, [_vp, _u32]),
     "bp_attn_decode_layer": (_int, [_vp, _vp, _u32, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _vp]),
+    "bp_set_peer_exchange": (_int, [_vp, _u32, _vp, _vp]),
+    "bp_peer_wait": (_int, [_vp, _vp]),
     "bp_attn_decode_static_scratch": (_int, [_vp, _vp, _vp, _vp, _vp] + [_u32] * 6),
 }
 

@@ -618,6 +618,32 @@ static cudaError_t launch_mma(bp_attn_ctx* c, cudaStream_t s, DecodeParams& p, u
   return cudaGetLastError();
 }
 
+// Consumer side of the peer exchange: one thread per layer spins (bounded, system-scope acquire loads)
+// until the layer's arrival counter has reached (tokens so far + 1) * arrivals per token, then the
+// token count is advanced. Counters only grow, so a rank that runs ahead cannot confuse a slower one.
+__global__ void __launch_bounds__(64)
+peer_wait_kernel(uint32_t* flags, uint32_t n_layer, uint32_t per_token, uint32_t* epoch, uint32_t* err) {
+  const uint32_t target = (*epoch + 1u) * per_token;
+  for (uint32_t l = threadIdx.x; l < n_layer; l += blockDim.x) {
+    bool ok = false;
+    for (uint32_t i = 0; i < (1u << 22) && !ok; i++) {
+      uint32_t v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + l) : "memory");
+      ok = static_cast<int32_t>(v - target) >= 0;
+      if (!ok) __nanosleep(64);
+    }
+    if (!ok) atomicExch(err, 6u);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) *epoch += 1u;
+}
+
+cudaError_t bp_launch_peer_wait(bp_attn_ctx* c, cudaStream_t s) {
+  const uint32_t per_token = c->cfg.n_shards * (c->cfg.n_kv_head / c->opt_uhpc);
+  peer_wait_kernel<<<1, 64, 0, s>>>(c->px_flag[c->cfg.shard], c->cfg.n_layer, per_token, c->px_epoch, c->err_dev);
+  return cudaGetLastError();
+}
+
 // Fused layer step. With the tcgen05 kernel: one launch does the Q norm + RoPE, the new token's
 // cache write and the split attention, a second one merges the splits. Otherwise: the separate kernels.
 cudaError_t bp_launch_decode_fused(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, const __half* q_raw, __half* q_roped,

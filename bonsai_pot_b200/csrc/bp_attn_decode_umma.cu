@@ -52,6 +52,13 @@ struct UmmaParams {
   // Fused layer step (fused = 1): q is the RAW query; the kernel normalises and rotates it itself
   // (optionally storing the result to q_roped), and the CTAs of the last split quantise the new
   // token's K / V rows (k_cur, v_cur), write them to the cache and patch them into their last stage.
+  // Peer exchange (n_px > 0): every final output element is also stored into each rank's gathered
+  // buffer (this rank's included) at px_off + head * 128 + dim, and once a head group's outputs are
+  // out, each rank's arrival counter of this layer is incremented (system scope). An all-gather
+  // by peer stores in the epilogue instead of a collective after the kernel.
+  uint32_t n_px, px_off, px_flag_idx;
+  __half* px_out[BP_MAX_PEERS];
+  uint32_t* px_flag[BP_MAX_PEERS];
   uint32_t merge;       // 1: the CTA of a head group that finishes last merges the splits itself
   uint32_t* tickets;    // one arrival counter per head group (grid y), zero between launches
   uint32_t fused;
@@ -254,6 +261,19 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
   auto wait = [&](uint64_t* bar, uint32_t parity) { cta_wait(bar, parity, &abort_s, p.err); };
   // Log-sum-exp merge over the splits (attention_merge.wgsl:70-130) by the softmax and accumulate
   // warps (640 threads) of the CTA that took the last ticket: thread = one output element.
+  auto put = [&](uint32_t h, uint32_t d, float v) {  // one final output element: local, and to the peers
+    const __half hv = __float2half_rn(v);
+    p.out[static_cast<size_t>(h) * BP_HEAD_DIM + d] = hv;
+    for (uint32_t r = 0; r < p.n_px; r++) p.px_out[r][p.px_off + static_cast<size_t>(h) * BP_HEAD_DIM + d] = hv;
+  };
+  // After the writers' stores: fence to system scope, meet, then one thread tells every rank.
+  auto signal_peers = [&](uint32_t bar_id, uint32_t n_thr, bool leader) {
+    if (p.n_px == 0) return;
+    __threadfence_system();
+    named_bar_sync(bar_id, n_thr);
+    if (leader)
+      for (uint32_t r = 0; r < p.n_px; r++) atomicAdd_system(p.px_flag[r] + p.px_flag_idx, 1u);
+  };
   auto merge_splits = [&]() {
     pdl_wait();
     __threadfence();
@@ -287,8 +307,9 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
           l = fmaf(ml[k].y, e, l);
         }
       }
-      p.out[static_cast<size_t>(h) * BP_HEAD_DIM + d] = __float2half_rn(o * (1.0f / l));
+      put(h, d, o * (1.0f / l));
     }
+    signal_peers(MERGE_BAR, 128 * NGRP + 128, tid == 0);
   };
 
   if (warp == 0) {
@@ -576,7 +597,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
         }
         const uint32_t h = (g0 + g) * p.qpg + hq;
         if (n_splits == 1) {
-          p.out[static_cast<size_t>(h) * BP_HEAD_DIM + dim] = __float2half_rn(acc * (1.0f / l));
+          put(h, dim, acc * (1.0f / l));
         } else {
           float* dst = p.partials + (static_cast<size_t>(split) * p.n_head + h) * BP_PART_STRIDE;
           dst[dim] = acc;
@@ -584,6 +605,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
         }
       }
     }
+    if (n_splits == 1) signal_peers(EPI_BAR, 128, warp == U_FIRST_SM_WARP + 4 * NGRP && lane == 0);
     if (n_splits > 1 && p.merge) {
       // Publish the partial, draw a ticket; the CTA of this head group that arrives last merges.
       __threadfence();
@@ -675,7 +697,14 @@ cudaError_t bp_launch_decode_umma(bp_attn_ctx* c, cudaStream_t s, uint32_t layer
   p.qpg = c->qpg;
   p.sm_scale_log2 = (1.0f / sqrtf(static_cast<float>(BP_HEAD_DIM))) * 1.4426950408889634f;
   p.dbg = c->dbg_on ? c->dbg_dev : nullptr;
-  p.merge = c->opt_umerge;
+  p.n_px = c->n_px;
+  p.px_off = layer * c->cfg.n_shards * c->q_dim + c->cfg.shard * c->q_dim;
+  p.px_flag_idx = layer;
+  for (uint32_t r = 0; r < BP_MAX_PEERS; r++) {
+    p.px_out[r] = r < c->n_px ? c->px_out[r] : nullptr;
+    p.px_flag[r] = r < c->n_px ? c->px_flag[r] : nullptr;
+  }
+  p.merge = c->opt_umerge || c->n_px > 0;  // the exchange lives in the in-kernel merge
   p.tickets = c->tickets;
   p.fused = fs != nullptr ? 1u : 0u;
   p.eps = c->cfg.rms_eps;

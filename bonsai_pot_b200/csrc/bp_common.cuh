@@ -12,6 +12,7 @@
 constexpr uint32_t BP_HEAD_DIM = 128;
 constexpr uint32_t BP_QK8 = 32;          // Q8_0 block size
 constexpr uint32_t BP_PART_STRIDE = 132; // floats per (split, head) partial: o[128], m, l, pad
+constexpr uint32_t BP_MAX_PEERS = 8;     // ranks of a peer exchange
 
 struct bp_attn_ctx {
   bp_attn_config cfg;
@@ -50,6 +51,12 @@ struct bp_attn_ctx {
   uint32_t opt_nw;   // decode: compute warps per CTA (8 or 16)
   uint32_t opt_hpc;  // decode: KV heads per CTA (divides n_kv_head)
   uint32_t opt_uhpc; // tcgen05 decode: KV heads per CTA (1 or 2)
+  // peer exchange of the decode outputs (bp_set_peer_exchange): each rank's gathered buffer
+  // [n_layer][n_shards * q_dim] f16 and arrival counters [n_layer], mapped into this process
+  uint32_t n_px;
+  __half* px_out[BP_MAX_PEERS];
+  uint32_t* px_flag[BP_MAX_PEERS];
+  uint32_t* px_epoch;  // device: tokens waited for so far
   uint32_t opt_umerge; // tcgen05 decode: merge the splits in the decode kernel (1) or with a second kernel (0)
   uint32_t opt_pdl;  // launch the kernels of a layer with programmatic stream serialization (1) or plainly (0)
   uint32_t opt_pf_nq; // prefill: query tiles per work item (1 or 2), 0 = by batch size
@@ -100,6 +107,8 @@ cudaError_t bp_launch_decode(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, con
                              __half* out, uint32_t cur_pos, uint32_t* launches);
 cudaError_t bp_launch_prefill(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, const __half* q,
                               __half* out, uint32_t m, uint32_t* launches);
+// Waits (bounded) until every head group of every rank has delivered the token's outputs of all layers.
+cudaError_t bp_launch_peer_wait(bp_attn_ctx* c, cudaStream_t s);
 uint32_t bp_decode_splits(const bp_attn_ctx* c, uint32_t cur_pos);
 uint32_t bp_decode_max_splits(const bp_attn_ctx* c);
 

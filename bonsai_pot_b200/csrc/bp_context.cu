@@ -267,6 +267,7 @@ void bp_attn_destroy(bp_attn_ctx* c) {
   cudaFree(c->rope);
   cudaFree(c->partials);
   cudaFree(c->tickets);
+  cudaFree(c->px_epoch);
   cudaFree(c->pf_kv16);
   cudaFree(c->dbg_dev);
   if (c->err_host) cudaFreeHost(c->err_host);
@@ -338,6 +339,36 @@ int bp_attn_decode_layer(bp_attn_ctx* c, void* stream, uint32_t layer, const voi
                                     static_cast<const __half*>(w_q_norm), static_cast<const __half*>(k_cur),
                                     static_cast<const __half*>(v_cur), static_cast<const __half*>(w_k_norm), pos,
                                     static_cast<__half*>(out), &c->last_launches));
+  return BP_OK;
+}
+
+int bp_set_peer_exchange(bp_attn_ctx* c, uint32_t n_ranks, const uint64_t* out_ptrs, const uint64_t* flag_ptrs) {
+  if (int s = enter(c)) return s;
+  if (n_ranks == 0) {
+    c->n_px = 0;
+    return BP_OK;
+  }
+  if (!out_ptrs || !flag_ptrs) return fail(c, BP_ERR_NULL, "null pointer argument");
+  if (n_ranks != c->cfg.n_shards || n_ranks > BP_MAX_PEERS)
+    return fail_config(c, "the peer exchange needs one buffer per shard (n_ranks == n_shards <= 8)");
+  if (!bp_use_umma(c)) return fail_config(c, "the peer exchange is part of the tcgen05 decode kernel (4 query heads per KV head)");
+  if (int s = bind_device(c)) return s;
+  if (!c->px_epoch) {
+    BP_CUDA(c, cudaMalloc(&c->px_epoch, sizeof(uint32_t)));
+    BP_CUDA(c, cudaMemset(c->px_epoch, 0, sizeof(uint32_t)));
+  }
+  for (uint32_t r = 0; r < n_ranks; r++) {
+    c->px_out[r] = reinterpret_cast<__half*>(static_cast<uintptr_t>(out_ptrs[r]));
+    c->px_flag[r] = reinterpret_cast<uint32_t*>(static_cast<uintptr_t>(flag_ptrs[r]));
+  }
+  c->n_px = n_ranks;
+  return BP_OK;
+}
+
+int bp_peer_wait(bp_attn_ctx* c, void* stream) {
+  if (int s = enter(c)) return s;
+  if (c->n_px == 0) return fail_config(c, "no peer exchange is set");
+  BP_CUDA(c, bp_launch_peer_wait(c, static_cast<cudaStream_t>(stream)));
   return BP_OK;
 }
 

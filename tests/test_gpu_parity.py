@@ -211,6 +211,40 @@ def test_decode_layer_fused_equals_the_three_dispatches(n_past, variant):
     assert ok, (max_abs, max_rel)
 
 
+def test_peer_exchange_epilogue_on_one_rank():
+    """The decode kernel's peer-store epilogue with a single rank acting as its own peer: the gathered
+    buffer receives every layer's outputs, each layer's arrival counter grows by one per KV head and
+    token, and the bounded wait passes once per token."""
+    sh = O.Shape(n_layer=3, max_seq=2048)
+    case = build_decode_case(sh, seed=4, cfg_id=0, layer=0, n_past=1500)
+    with make_ctx(sh) as ctx:
+        gathered = torch.zeros(sh.n_layer, sh.q_dim, dtype=torch.float16, device="cuda")
+        flags = torch.zeros(64, dtype=torch.int32, device="cuda")
+        ctx.set_peer_exchange([gathered.data_ptr()], [flags.data_ptr()])
+        outs = []
+        for token in range(2):
+            for layer in range(sh.n_layer):
+                load_cache(ctx, sh, case["kv_k"], case["kv_v"], 0, 1500) if layer == 0 and token == 0 else None
+                out = torch.zeros(sh.q_dim, dtype=torch.float16, device="cuda")
+                n_keys = 1501 if layer == 0 else 1
+                if layer > 0:  # other layers: a single key written by the fused step itself
+                    ctx.decode_layer(layer, dev(case["q"]), dev(case["w_q"]), dev(case["k_new"]), dev(case["v_new"]),
+                                     dev(case["w_k"]), 0, out)
+                else:
+                    ctx.decode_layer(0, dev(case["q"]), dev(case["w_q"]), dev(case["k_new"]), dev(case["v_new"]),
+                                     dev(case["w_k"]), 1500, out)
+                outs.append(out)
+            ctx.peer_wait()
+            torch.cuda.synchronize()
+            assert ctx.status() == 0
+            for layer in range(sh.n_layer):
+                assert torch.equal(gathered[layer], outs[token * sh.n_layer + layer])
+            assert flags[:sh.n_layer].tolist() == [sh.n_kv_head * (token + 1)] * sh.n_layer
+        ctx.set_peer_exchange([], [])
+    ref = O.attn_decode(sh, case["qn"], case["kv_k"], case["kv_v"], 0, 1501).astype(np.float32)
+    assert within_tolerance(host(outs[0]), ref)[0]
+
+
 @pytest.mark.parametrize("ctx_len,layer", [(4096, 1), (32768, 1)])
 def test_decode_long_context(ctx_len, layer):
     """BASELINE configs 1 and 3 at full context length (two layers allocated,
