@@ -303,7 +303,7 @@ def run_ours(args):
                 torch.cuda.synchronize()
                 dist.barrier()
                 ctx.set_peer_exchange(list(h_out.buffer_ptrs), list(h_flag.buffer_ptrs))
-                exchange = "peer stores in the decode epilogue + one wait kernel per token"
+                exchange = "peer stores in the decode epilogue, ranks meet " + ("once per token" if args.sync_per_token else "after every layer")
             except Exception as e:  # no peer mapping on this box: fall back to NCCL
                 print(f"[bench] symmetric memory unavailable ({type(e).__name__}: {e}); using NCCL all-gather", file=sys.stderr)
     use_px = exchange.startswith("peer")
@@ -329,8 +329,11 @@ def run_ours(args):
                 n += ctx.last_launch_count()
             if world > 1 and not use_px:
                 dist.all_gather_into_tensor(out_full[il], out_local[il])
-        if use_px:
-            ctx.peer_wait(stream=stream)
+            if use_px and not args.sync_per_token:
+                ctx.peer_sync(slot=il, stream=stream)  # the next operation of a decoder consumes this layer's gathered row
+                n += 1
+        if use_px and args.sync_per_token:
+            ctx.peer_sync(slot=0, stream=stream)
             n += 1
         launches_per_step = n
 
@@ -546,6 +549,8 @@ def main():
     ap.add_argument("--separate", action="store_true",
                     help="drive a layer with the reference's three dispatches instead of the one-call layer step")
     ap.add_argument("--separate-merge", action="store_true", help="merge the decode splits with a second kernel")
+    ap.add_argument("--sync-per-token", action="store_true",
+                    help="N > 1: the ranks meet once per token instead of after every layer")
     ap.add_argument("--nccl-gather", action="store_true", help="N > 1: all-gather the head outputs with NCCL after every layer")
     ap.add_argument("--no-pdl", action="store_true", help="launch the kernels without programmatic dependent launch")
     ap.add_argument("--variant", type=int, default=0, help="decode kernel family (0 = production)")

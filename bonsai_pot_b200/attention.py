@@ -113,15 +113,16 @@ class AttnContext:
 
     def set_peer_exchange(self, out_ptrs, flag_ptrs):
         """Peer exchange of decode outputs: device addresses (valid in this process) of every rank's
-        gathered buffer [n_layer][n_shards*n_head*128] f16 and arrival counters [n_layer] uint32."""
+        gathered buffer [n_layer][n_shards*n_head*128] f16 and meeting counters [64] uint32."""
         n = len(out_ptrs)
         arr_o = (C.c_uint64 * max(n, 1))(*[int(p) for p in out_ptrs])
         arr_f = (C.c_uint64 * max(n, 1))(*[int(p) for p in flag_ptrs])
         self._check(self._lib.bp_set_peer_exchange(self._h, n, arr_o, arr_f))
 
-    def peer_wait(self, stream=None):
-        """Wait (on the stream) for one more token's outputs of all layers from all ranks."""
-        self._check(self._lib.bp_peer_wait(self._h, _stream(stream)))
+    def peer_sync(self, slot=0, stream=None):
+        """Meeting of the ranks on the stream: this rank's kernels so far are complete (peer stores
+        included), and so are every other rank's up to their matching call."""
+        self._check(self._lib.bp_peer_sync(self._h, _stream(stream), slot))
 
     def dispatch_attention(self, layer_il, q, out, m_tokens, stream=None):
         """Batched prefill (pos = 0, is_prefill = true): q, out f16 [m][n_head*128]."""

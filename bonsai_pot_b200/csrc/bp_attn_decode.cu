@@ -618,30 +618,40 @@ static cudaError_t launch_mma(bp_attn_ctx* c, cudaStream_t s, DecodeParams& p, u
   return cudaGetLastError();
 }
 
-// Consumer side of the peer exchange: one thread per layer spins (bounded, system-scope acquire loads)
-// until the layer's arrival counter has reached (tokens so far + 1) * arrivals per token, then the
-// token count is advanced. Counters only grow, so a rank that runs ahead cannot confuse a slower one.
-__global__ void __launch_bounds__(64)
-peer_wait_kernel(uint32_t* flags, uint32_t n_layer, uint32_t per_token, uint32_t* epoch, uint32_t* err) {
-  const uint32_t target = (*epoch + 1u) * per_token;
-  for (uint32_t l = threadIdx.x; l < n_layer; l += blockDim.x) {
+// Meeting point of the ranks of a peer exchange, counter `slot`: every rank adds one to every
+// rank's counter (system-scope release, after a system fence: the peer stores of the kernels
+// before this one in the stream are complete by then), then waits (bounded, system-scope acquire
+// loads) until its own counter has reached (meetings so far + 1) * ranks. Counters only grow, so a
+// rank that runs ahead cannot confuse a slower one.
+struct PeerFlags {
+  uint32_t* f[BP_MAX_PEERS];
+};
+__global__ void __launch_bounds__(32)
+peer_sync_kernel(PeerFlags flags, uint32_t n_ranks, uint32_t rank, uint32_t slot, uint32_t* epochs, uint32_t* err) {
+  bp::pdl_wait();
+  if (threadIdx.x < n_ranks) {
+    __threadfence_system();
+    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(flags.f[threadIdx.x] + slot), "r"(1u) : "memory");
+  }
+  if (threadIdx.x == 0) {
+    const uint32_t target = (epochs[slot] + 1u) * n_ranks;
     bool ok = false;
     for (uint32_t i = 0; i < (1u << 22) && !ok; i++) {
       uint32_t v;
-      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + l) : "memory");
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags.f[rank] + slot) : "memory");
       ok = static_cast<int32_t>(v - target) >= 0;
-      if (!ok) __nanosleep(64);
+      if (!ok) __nanosleep(32);
     }
     if (!ok) atomicExch(err, 6u);
+    epochs[slot] += 1u;
   }
-  __syncthreads();
-  if (threadIdx.x == 0) *epoch += 1u;
 }
 
-cudaError_t bp_launch_peer_wait(bp_attn_ctx* c, cudaStream_t s) {
-  const uint32_t per_token = c->cfg.n_shards * (c->cfg.n_kv_head / c->opt_uhpc);
-  peer_wait_kernel<<<1, 64, 0, s>>>(c->px_flag[c->cfg.shard], c->cfg.n_layer, per_token, c->px_epoch, c->err_dev);
-  return cudaGetLastError();
+cudaError_t bp_launch_peer_sync(bp_attn_ctx* c, cudaStream_t s, uint32_t slot) {
+  PeerFlags f;
+  for (uint32_t r = 0; r < BP_MAX_PEERS; r++) f.f[r] = r < c->n_px ? c->px_flag[r] : nullptr;
+  return bp_launch(c->opt_pdl != 0, peer_sync_kernel, dim3(1), dim3(32), 0, s, f, c->n_px, c->cfg.shard, slot, c->px_epoch,
+                   c->err_dev);
 }
 
 // Fused layer step. With the tcgen05 kernel: one launch does the Q norm + RoPE, the new token's

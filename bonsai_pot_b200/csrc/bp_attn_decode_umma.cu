@@ -53,12 +53,11 @@ struct UmmaParams {
   // (optionally storing the result to q_roped), and the CTAs of the last split quantise the new
   // token's K / V rows (k_cur, v_cur), write them to the cache and patch them into their last stage.
   // Peer exchange (n_px > 0): every final output element is also stored into each rank's gathered
-  // buffer (this rank's included) at px_off + head * 128 + dim, and once a head group's outputs are
-  // out, each rank's arrival counter of this layer is incremented (system scope). An all-gather
-  // by peer stores in the epilogue instead of a collective after the kernel.
-  uint32_t n_px, px_off, px_flag_idx;
+  // buffer (this rank's included) at px_off + head * 128 + dim: an all-gather by peer stores in the
+  // epilogue instead of a collective after the kernel. The stores are complete when the grid is;
+  // ranks meet afterwards with bp_peer_sync.
+  uint32_t n_px, px_off;
   __half* px_out[BP_MAX_PEERS];
-  uint32_t* px_flag[BP_MAX_PEERS];
   uint32_t merge;       // 1: the CTA of a head group that finishes last merges the splits itself
   uint32_t* tickets;    // one arrival counter per head group (grid y), zero between launches
   uint32_t fused;
@@ -266,14 +265,6 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
     p.out[static_cast<size_t>(h) * BP_HEAD_DIM + d] = hv;
     for (uint32_t r = 0; r < p.n_px; r++) p.px_out[r][p.px_off + static_cast<size_t>(h) * BP_HEAD_DIM + d] = hv;
   };
-  // After the writers' stores: fence to system scope, meet, then one thread tells every rank.
-  auto signal_peers = [&](uint32_t bar_id, uint32_t n_thr, bool leader) {
-    if (p.n_px == 0) return;
-    __threadfence_system();
-    named_bar_sync(bar_id, n_thr);
-    if (leader)
-      for (uint32_t r = 0; r < p.n_px; r++) atomicAdd_system(p.px_flag[r] + p.px_flag_idx, 1u);
-  };
   auto merge_splits = [&]() {
     pdl_wait();
     __threadfence();
@@ -309,7 +300,6 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
       }
       put(h, d, o * (1.0f / l));
     }
-    signal_peers(MERGE_BAR, 128 * NGRP + 128, tid == 0);
   };
 
   if (warp == 0) {
@@ -605,7 +595,6 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
         }
       }
     }
-    if (n_splits == 1) signal_peers(EPI_BAR, 128, warp == U_FIRST_SM_WARP + 4 * NGRP && lane == 0);
     if (n_splits > 1 && p.merge) {
       // Publish the partial, draw a ticket; the CTA of this head group that arrives last merges.
       __threadfence();
@@ -662,6 +651,11 @@ static uint32_t umma_spp(const bp_attn_ctx* c, uint32_t cur_pos) {
   const uint32_t groups = c->cfg.n_kv_head / c->opt_uhpc;
   uint32_t ctas = bp_decode_max_splits(c) / groups;
   if (ctas == 0) ctas = 1;
+  // With few KV heads per device (a shard of a multi-GPU run) there are many more SMs than a head
+  // can use well: a job costs about 1 us of streaming, merging a split about 0.07 us in the CTA
+  // that finishes last, so beyond sqrt(15 * stages) splits the merge outgrows what it saves.
+  const uint32_t cap = static_cast<uint32_t>(sqrtf(15.0f * static_cast<float>(n_st))) + 1;
+  if (ctas > cap) ctas = cap < 8 ? 8 : cap;
   return (n_st + ctas - 1) / ctas;
 }
 
@@ -699,11 +693,7 @@ cudaError_t bp_launch_decode_umma(bp_attn_ctx* c, cudaStream_t s, uint32_t layer
   p.dbg = c->dbg_on ? c->dbg_dev : nullptr;
   p.n_px = c->n_px;
   p.px_off = layer * c->cfg.n_shards * c->q_dim + c->cfg.shard * c->q_dim;
-  p.px_flag_idx = layer;
-  for (uint32_t r = 0; r < BP_MAX_PEERS; r++) {
-    p.px_out[r] = r < c->n_px ? c->px_out[r] : nullptr;
-    p.px_flag[r] = r < c->n_px ? c->px_flag[r] : nullptr;
-  }
+  for (uint32_t r = 0; r < BP_MAX_PEERS; r++) p.px_out[r] = r < c->n_px ? c->px_out[r] : nullptr;
   p.merge = c->opt_umerge || c->n_px > 0;  // the exchange lives in the in-kernel merge
   p.tickets = c->tickets;
   p.fused = fs != nullptr ? 1u : 0u;

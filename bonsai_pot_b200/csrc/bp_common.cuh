@@ -52,11 +52,11 @@ struct bp_attn_ctx {
   uint32_t opt_hpc;  // decode: KV heads per CTA (divides n_kv_head)
   uint32_t opt_uhpc; // tcgen05 decode: KV heads per CTA (1 or 2)
   // peer exchange of the decode outputs (bp_set_peer_exchange): each rank's gathered buffer
-  // [n_layer][n_shards * q_dim] f16 and arrival counters [n_layer], mapped into this process
+  // [n_layer][n_shards * q_dim] f16 and meeting counters [64], mapped into this process
   uint32_t n_px;
   __half* px_out[BP_MAX_PEERS];
   uint32_t* px_flag[BP_MAX_PEERS];
-  uint32_t* px_epoch;  // device: tokens waited for so far
+  uint32_t* px_epoch;  // device: meetings so far, per counter slot [64]
   uint32_t opt_umerge; // tcgen05 decode: merge the splits in the decode kernel (1) or with a second kernel (0)
   uint32_t opt_pdl;  // launch the kernels of a layer with programmatic stream serialization (1) or plainly (0)
   uint32_t opt_pf_nq; // prefill: query tiles per work item (1 or 2), 0 = by batch size
@@ -107,8 +107,8 @@ cudaError_t bp_launch_decode(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, con
                              __half* out, uint32_t cur_pos, uint32_t* launches);
 cudaError_t bp_launch_prefill(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, const __half* q,
                               __half* out, uint32_t m, uint32_t* launches);
-// Waits (bounded) until every head group of every rank has delivered the token's outputs of all layers.
-cudaError_t bp_launch_peer_wait(bp_attn_ctx* c, cudaStream_t s);
+// Meeting of the ranks of the peer exchange on counter `slot` (< 64): signal all, wait (bounded) for all.
+cudaError_t bp_launch_peer_sync(bp_attn_ctx* c, cudaStream_t s, uint32_t slot);
 uint32_t bp_decode_splits(const bp_attn_ctx* c, uint32_t cur_pos);
 uint32_t bp_decode_max_splits(const bp_attn_ctx* c);
 

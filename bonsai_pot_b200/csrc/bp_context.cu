@@ -354,8 +354,8 @@ int bp_set_peer_exchange(bp_attn_ctx* c, uint32_t n_ranks, const uint64_t* out_p
   if (!bp_use_umma(c)) return fail_config(c, "the peer exchange is part of the tcgen05 decode kernel (4 query heads per KV head)");
   if (int s = bind_device(c)) return s;
   if (!c->px_epoch) {
-    BP_CUDA(c, cudaMalloc(&c->px_epoch, sizeof(uint32_t)));
-    BP_CUDA(c, cudaMemset(c->px_epoch, 0, sizeof(uint32_t)));
+    BP_CUDA(c, cudaMalloc(&c->px_epoch, 64 * sizeof(uint32_t)));
+    BP_CUDA(c, cudaMemset(c->px_epoch, 0, 64 * sizeof(uint32_t)));
   }
   for (uint32_t r = 0; r < n_ranks; r++) {
     c->px_out[r] = reinterpret_cast<__half*>(static_cast<uintptr_t>(out_ptrs[r]));
@@ -365,10 +365,11 @@ int bp_set_peer_exchange(bp_attn_ctx* c, uint32_t n_ranks, const uint64_t* out_p
   return BP_OK;
 }
 
-int bp_peer_wait(bp_attn_ctx* c, void* stream) {
+int bp_peer_sync(bp_attn_ctx* c, void* stream, uint32_t slot) {
   if (int s = enter(c)) return s;
   if (c->n_px == 0) return fail_config(c, "no peer exchange is set");
-  BP_CUDA(c, bp_launch_peer_wait(c, static_cast<cudaStream_t>(stream)));
+  if (slot >= 64) return fail_config(c, "peer sync slot must be below 64");
+  BP_CUDA(c, bp_launch_peer_sync(c, static_cast<cudaStream_t>(stream), slot));
   return BP_OK;
 }
 

@@ -120,22 +120,25 @@ int bp_attn_decode_layer(bp_attn_ctx* ctx, void* stream, uint32_t layer, const v
 /* Peer exchange of the decode outputs between KV-head shards (no counterpart
  * in the reference, which runs on one device). out_ptrs[r] / flag_ptrs[r] are
  * device addresses, valid IN THIS PROCESS, of rank r's gathered output buffer
- * (f16 [n_layer][n_shards * n_head * 128]) and of its arrival counters
- * (uint32 [n_layer], zero at the start); r = 0 .. n_ranks-1 with n_ranks ==
+ * (f16 [n_layer][n_shards * n_head * 128]) and of its meeting counters
+ * (uint32 [64], zero at the start); r = 0 .. n_ranks-1 with n_ranks ==
  * n_shards, this rank's own buffers included (peer-mapped memory: CUDA IPC,
  * VMM or a symmetric-memory allocator). From then on the tcgen05 decode kernel
  * stores every output element of its heads into all ranks' gathered buffers
- * (row = layer, columns of this shard) as it produces them, and increments
- * every rank's counter of the layer once per head group: the all-gather of
+ * (row = layer, columns of this shard) as it produces them: the all-gather of
  * head outputs happens inside the kernel's epilogue, by peer stores over
- * NVLink. n_ranks = 0 switches the exchange off. */
+ * NVLink. The stores are complete when the kernel is. n_ranks = 0 switches the
+ * exchange off. */
 int bp_set_peer_exchange(bp_attn_ctx* ctx, uint32_t n_ranks, const uint64_t* out_ptrs,
                          const uint64_t* flag_ptrs);
-/* Enqueues a small kernel that waits (bounded; a timeout latches
- * BP_ERR_TIMEOUT) until the outputs of ONE more token have arrived from every
- * rank for every layer. Counters only grow. Call once per token, after the
- * token's last decode call, before the gathered buffer is read. */
-int bp_peer_wait(bp_attn_ctx* ctx, void* stream);
+/* Meeting point of the ranks, enqueued on `stream`: tells every rank that this
+ * rank's kernels up to here have completed (their peer stores included) and
+ * waits (bounded; a timeout latches BP_ERR_TIMEOUT) until every rank has said
+ * so on counter `slot` (< 64; each slot counts its own meetings). Call it
+ * where the gathered outputs are needed: after a layer's decode call with slot
+ * = layer mod 64 when the next operation consumes that layer's gathered row,
+ * or once per token when nothing in between does. */
+int bp_peer_sync(bp_attn_ctx* ctx, void* stream, uint32_t slot);
 
 /* `dispatch_attention(.., pos = 0, m_tokens = m, is_prefill = true)`
  * (src/forward.rs:501-532, params src/model.rs:195-210, kernel

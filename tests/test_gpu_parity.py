@@ -213,8 +213,7 @@ def test_decode_layer_fused_equals_the_three_dispatches(n_past, variant):
 
 def test_peer_exchange_epilogue_on_one_rank():
     """The decode kernel's peer-store epilogue with a single rank acting as its own peer: the gathered
-    buffer receives every layer's outputs, each layer's arrival counter grows by one per KV head and
-    token, and the bounded wait passes once per token."""
+    buffer receives every layer's outputs, and the meeting kernel counts one arrival per call on its slot."""
     sh = O.Shape(n_layer=3, max_seq=2048)
     case = build_decode_case(sh, seed=4, cfg_id=0, layer=0, n_past=1500)
     with make_ctx(sh) as ctx:
@@ -234,12 +233,12 @@ def test_peer_exchange_epilogue_on_one_rank():
                     ctx.decode_layer(0, dev(case["q"]), dev(case["w_q"]), dev(case["k_new"]), dev(case["v_new"]),
                                      dev(case["w_k"]), 1500, out)
                 outs.append(out)
-            ctx.peer_wait()
+            ctx.peer_sync(slot=5)
             torch.cuda.synchronize()
             assert ctx.status() == 0
             for layer in range(sh.n_layer):
                 assert torch.equal(gathered[layer], outs[token * sh.n_layer + layer])
-            assert flags[:sh.n_layer].tolist() == [sh.n_kv_head * (token + 1)] * sh.n_layer
+            assert flags[5].item() == token + 1 and flags[:5].abs().sum().item() == 0
         ctx.set_peer_exchange([], [])
     ref = O.attn_decode(sh, case["qn"], case["kv_k"], case["kv_v"], 0, 1501).astype(np.float32)
     assert within_tolerance(host(outs[0]), ref)[0]
