@@ -393,7 +393,7 @@ def run_ours(args):
     algo_bytes_launch = ctx_len * BYTES_PER_TOKEN_LAYER // world
     achieved = algo_bytes_launch / dt_k / 1e9
     # DRAM traffic per launch: one ncu capture of the decode kernel at ctx 32768 read 75.57 MB against
-    # 75.50 MB of algorithmic bytes (profiles/decode_umma_kernel_ctx32768.md); reads grow in proportion to
+    # 75.50 MB of algorithmic bytes; reads grow in proportion to
     # the tokens streamed, so the capture is scaled by tokens. The split partials (written once, read back
     # from L2 by the merging CTA) are added as written bytes.
     n_splits = ctx.decode_num_splits(pos + 1) if hasattr(ctx, "decode_num_splits") else 18
