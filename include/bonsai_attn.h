@@ -46,7 +46,10 @@ enum {
   BP_ERR_PREFILL_TOO_LARGE = 3, /* PotError::PrefillTooLarge { n, max } */
   BP_ERR_DEVICE_LOST = 4,       /* PotError::DeviceLost */
   BP_ERR_CUDA = 5,              /* a CUDA runtime/driver call failed (no reference counterpart) */
-  BP_ERR_TIMEOUT = 6,           /* a bounded device-side wait gave up (multi-GPU exchange) */
+  BP_ERR_TIMEOUT = 6,           /* a bounded device-side wait gave up (a TMA / MMA barrier inside a kernel, or the
+                                   meeting of the ranks): the kernel wound down instead of hanging; its results and
+                                   the context's device-side counters are undefined. Sticky, like DeviceLost: take a
+                                   snapshot if the cache is still wanted, destroy the context, create a new one. */
   BP_ERR_NULL = 7               /* a required pointer argument was NULL */
 };
 
