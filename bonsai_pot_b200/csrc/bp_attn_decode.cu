@@ -695,8 +695,8 @@ cudaError_t bp_launch_decode(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, con
     cudaError_t e = bp_launch_decode_umma(c, s, layer, q, out, cur_pos, &n_splits);
     *launches += 1;
     if (e != cudaSuccess) return e;
-    // A fused "last CTA combines" epilogue was measured slower than this second small kernel:
-    // code that a CTA runs once is fetched cold, and the ticket + combine path cost more than a launch.
+    // The kernel reports one split when it merged the splits itself (the default); the separate
+    // merge kernel runs only with the option decode_in_kernel_merge = 0.
     if (n_splits > 1) {
       *launches += 1;
       e = bp_launch(c->opt_pdl != 0, attn_combine_kernel, dim3(c->cfg.n_head), dim3(128 * COMBINE_GROUPS), 0, s,

@@ -528,3 +528,22 @@ def test_decode_tuning_options_do_not_change_results(warps, hpc):
             assert ok, (warps, hpc, cur_pos, max_abs, max_rel)
         with pytest.raises(bp.ConfigError):
             ctx.set_option("decode_warps", 12)
+
+
+@pytest.mark.parametrize("merge,pdl", [(0, 1), (1, 0), (0, 0)])
+def test_decode_launch_structure_options_do_not_change_results(merge, pdl):
+    """Separate merge kernel vs in-kernel merge, plain vs programmatic dependent launches: results stay
+    within tolerance of the exact softmax and within 1e-3 of the default structure (the partials are
+    the same; the two merges sum the splits in different groupings)."""
+    sh = O.Shape(n_layer=1, max_seq=4096)
+    case = build_decode_case(sh, seed=12, cfg_id=1, layer=0, n_past=4000)
+    with make_ctx(sh) as ctx:
+        load_cache(ctx, sh, case["kv_k"], case["kv_v"], 0, 4001)
+        base = run_decode(ctx, sh, case, 0)
+        ctx.set_option("decode_in_kernel_merge", merge)
+        ctx.set_option("dependent_launch", pdl)
+        got = run_decode(ctx, sh, case, 0)
+        exact = O.attn_exact(sh, case["qn"], case["kv_k"], case["kv_v"], 0, 1, 4000)[0]
+        ok, max_abs, max_rel = within_tolerance(got, exact)
+        assert ok, (merge, pdl, max_abs, max_rel)
+        assert np.abs(got.astype(np.float32) - base.astype(np.float32)).max() <= 1e-3
