@@ -156,7 +156,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t k_full[KV_SLOTS], v_full[KV_SLOTS];
   __shared__ __align__(8) uint64_t k_empty[NQ][KV_SLOTS], v_empty[NQ][KV_SLOTS];  // per query tile: it is done with the slot
-  __shared__ __align__(8) uint64_t s_ready[NQ][2], p_ready[NQ], o_done[NQ];
+  __shared__ __align__(8) uint64_t s_ready[NQ][2], p_ready[NQ][2], o_done[NQ];
   __shared__ uint32_t tmem_base_s, item_s;
   __shared__ volatile uint32_t abort_s;
 
@@ -178,7 +178,8 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     for (uint32_t x = 0; x < NQ; x++) {
       mbar_init(smem_u32(&s_ready[x][0]), 1);
       mbar_init(smem_u32(&s_ready[x][1]), 1);
-      mbar_init(smem_u32(&p_ready[x]), 4);
+      mbar_init(smem_u32(&p_ready[x][0]), 4);
+      mbar_init(smem_u32(&p_ready[x][1]), 4);
       mbar_init(smem_u32(&o_done[x]), 1);
     }
     abort_s = 0;
@@ -332,7 +333,9 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
           const uint32_t s = (gkv + i) % KV_SLOTS, b = (c0 + i) & 1;
           const uint64_t vb = dmn + ((smem_base + L::OFF_V + s * KV_TILE_B) >> 4);
           waitx(&v_full[s], ((gkv + i) / KV_SLOTS) & 1, 1);
-          waitx(&p_ready[x], (c0 + i) & 1, 2);
+          // one barrier per S buffer: the softmax group may run two tiles ahead of this wait, and two
+          // completions on one barrier would be indistinguishable from none
+          waitx(&p_ready[x][b], ((c0 + i) >> 1) & 1, 2);
           tc_fence_after();
 #pragma unroll
           for (uint32_t ks = 0; ks < 4; ks++)  // 16 keys per UMMA: 8 columns of P, 16 rows of V
@@ -414,7 +417,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&p_ready[x]));
+        if (lane == 0) mbar_arrive(smem_u32(&p_ready[x][b]));
       }
       // ---- O / l -> f16 ----
       if (n_mine > 0) {
