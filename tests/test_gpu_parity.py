@@ -547,3 +547,33 @@ def test_decode_launch_structure_options_do_not_change_results(merge, pdl):
         ok, max_abs, max_rel = within_tolerance(got, exact)
         assert ok, (merge, pdl, max_abs, max_rel)
         assert np.abs(got.astype(np.float32) - base.astype(np.float32)).max() <= 1e-3
+
+
+@pytest.mark.parametrize("tiles_per_item", [1, 2])
+@pytest.mark.parametrize("m", [65, 129, 512, 700, 2048])
+def test_prefill_tile_modes_against_the_scalar_kernel(m, tiles_per_item):
+    """Both work-item shapes of the tensor-core prefill kernel (one or two query tiles per item), on sizes
+    that give every SM an item and some SMs several, against the plain CUDA-core kernel on the same cache.
+    Repeated launches: a hand-over between the kernel's roles that only fails under some timing shows here."""
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(100 + m)
+    with bp.AttnContext(n_layer=1, max_seq=2048) as ctx:
+        w = torch.ones(128, dtype=torch.float16, device="cuda")
+        q = torch.randn(m, 4096, generator=gen, device="cuda").half()
+        k = torch.randn(m, 1024, generator=gen, device="cuda").half()
+        v = torch.randn(m, 1024, generator=gen, device="cuda").half()
+        ctx.dispatch_q_norm_rope_fused(q, w, 0, m)
+        ctx.dispatch_kv_writeback_fused(0, k, v, w, 0, m)
+        ref = torch.zeros(m, 4096, dtype=torch.float16, device="cuda")
+        ctx.set_variant(1)
+        ctx.dispatch_attention(0, q, ref, m)
+        torch.cuda.synchronize()
+        ctx.set_variant(0)
+        ctx.set_option("prefill_tiles_per_item", tiles_per_item)
+        for _ in range(3):
+            out = torch.full((m, 4096), float("nan"), dtype=torch.float16, device="cuda")
+            ctx.dispatch_attention(0, q, out, m)
+            torch.cuda.synchronize()
+            assert ctx.status() == 0
+            ok, max_abs, max_rel = within_tolerance(host(out), host(ref).astype(np.float32))
+            assert ok, (m, tiles_per_item, max_abs, max_rel)
