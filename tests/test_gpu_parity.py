@@ -577,3 +577,30 @@ def test_prefill_tile_modes_against_the_scalar_kernel(m, tiles_per_item):
             assert ctx.status() == 0
             ok, max_abs, max_rel = within_tolerance(host(out), host(ref).astype(np.float32))
             assert ok, (m, tiles_per_item, max_abs, max_rel)
+
+
+@pytest.mark.parametrize("n_head,n_kv_head", [(2, 1), (6, 2), (8, 2)])
+def test_norm_rope_quant_bit_exact_for_other_head_counts(n_head, n_kv_head):
+    """The batched kernels take 4, 2 or 1 heads per warp depending on what divides the head count: every
+    grouping must give the oracle's bits."""
+    m = 2048
+    sh = O.Shape(n_layer=1, n_head=n_head, n_kv_head=n_kv_head, max_seq=m)
+    rope = O.rope_table_f16(sh)
+    rng = np.random.default_rng(17)
+    w = (1 + 0.1 * rng.standard_normal(128)).astype(np.float16)
+    q = synth.tensor(5, 2, 0, synth.T_Q, (m, sh.q_dim))
+    k = synth.tensor(5, 2, 0, synth.T_K_NEW, (m, sh.kv_dim))
+    v = synth.tensor(5, 2, 0, synth.T_V_NEW, (m, sh.kv_dim))
+    ref_k, ref_v = sh.new_cache(), sh.new_cache()
+    O.kv_writeback(sh, k, v, w, rope, ref_k, ref_v, 0, 0, m)
+    ref_q = O.q_norm_rope(sh, q, w, rope, 0, m)
+    with make_ctx(sh) as ctx:
+        qd = dev(q)
+        ctx.dispatch_q_norm_rope_fused(qd, dev(w), 0, m)
+        ctx.dispatch_kv_writeback_fused(0, dev(k), dev(v), dev(w), 0, m)
+        torch.cuda.synchronize()
+        (kd, kq), (vd, vq) = read_cache(ctx, sh, 0, m)
+        assert np.array_equal(host(qd).view(np.uint16).reshape(-1), ref_q.view(np.uint16).reshape(-1))
+    assert np.array_equal(kq, sh.qs_section(ref_k, 0)[:m]) and np.array_equal(vq, sh.qs_section(ref_v, 0)[:m])
+    assert np.array_equal(kd.view(np.uint32), sh.d_section(ref_k, 0)[:m].view(np.uint32))
+    assert np.array_equal(vd.view(np.uint32), sh.d_section(ref_v, 0)[:m].view(np.uint32))
