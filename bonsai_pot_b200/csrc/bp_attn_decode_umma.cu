@@ -16,9 +16,16 @@
 //
 // Roles (800 threads): warp 0 TMA producer, warps 1-2 QK issuers (warp 1 owns TMEM), warps 3-4 PV
 // issuers, warps 5-20 four softmax groups (thread = token row = TMEM lane), warps 21-24 accumulate
-// (thread = head dim = TMEM lane). Every mbarrier wait is bounded; after a
-// timeout the CTA stops waiting, drains and frees TMEM, and reports through the
-// error word.
+// (thread = head dim = TMEM lane; they also quantise Q at the start and write the
+// partials at the end). Every mbarrier wait is bounded; after a timeout the CTA
+// stops waiting, drains and frees TMEM, and reports through the error word.
+//
+// Around that core the same launch can do the rest of a layer's decode step:
+//   fused step   the Q preparation normalises and rotates the raw q first, and the CTAs of
+//                the last split quantise the new token's K / V rows, store them to the cache
+//                and patch them into their last stage (bp_attn_decode_layer);
+//   merge        the CTA of a head group that draws the last ticket merges the splits;
+//   exchange     final outputs are also stored into every rank's gathered buffer (peer stores).
 #include "bp_common.cuh"
 #include "bp_ptx.cuh"
 #include "bp_norm_quant.cuh"
@@ -32,9 +39,9 @@ constexpr float NEG_BIG = -1e30f;
 constexpr uint32_t UT = 128;                 // tokens per stage = UMMA M
 constexpr uint32_t TILE_B = UT * 128;        // int8 tile of one head and stage: 16 KB
 constexpr uint32_t U_MAX_STAGES = 6;
-constexpr uint32_t NGRP = 4;
+constexpr uint32_t NGRP = 4;                      // softmax groups working on different jobs in parallel
 constexpr uint32_t EPI_BAR = 7, MERGE_BAR = 8;    // named barriers of the in-kernel merge of the splits
-constexpr uint32_t FIN_BAR = 6;                   // named barrier: softmax warps arrive, accumulate warps wait                     // softmax groups working on different jobs in parallel
+constexpr uint32_t FIN_BAR = 6;                   // named barrier: softmax warps arrive, accumulate warps wait
 constexpr uint32_t NISS = 2;                     // UMMA issuer warps per kind (QK, PV)
 constexpr uint32_t U_FIRST_SM_WARP = 1 + 2 * NISS;  // warp 0 producer, then the issuers
 constexpr uint32_t U_THREADS = (U_FIRST_SM_WARP + 4 * NGRP + 4) * 32;
