@@ -271,6 +271,8 @@ def run_ours(args):
         ctx.set_option("decode_umma_heads_per_cta", args.decode_uhpc)
     if args.no_pdl:
         ctx.set_option("dependent_launch", 0)
+    if args.decode_ring:
+        ctx.set_option("decode_ring", args.decode_ring)
     if args.separate_merge:
         ctx.set_option("decode_in_kernel_merge", 0)
     gen = torch.Generator(device="cuda")
@@ -552,6 +554,7 @@ def main():
     ap.add_argument("--sync-per-token", action="store_true",
                     help="N > 1: the ranks meet once per token instead of after every layer")
     ap.add_argument("--nccl-gather", action="store_true", help="N > 1: all-gather the head outputs with NCCL after every layer")
+    ap.add_argument("--decode-ring", type=int, default=0, help="override the decode kernel's ring: K stages * 16 + V slots")
     ap.add_argument("--no-pdl", action="store_true", help="launch the kernels without programmatic dependent launch")
     ap.add_argument("--variant", type=int, default=0, help="decode kernel family (0 = production)")
     ap.add_argument("--prefill-only", type=int, default=0, metavar="PP",

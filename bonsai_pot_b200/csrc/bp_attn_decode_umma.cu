@@ -38,7 +38,7 @@ constexpr unsigned FULL = 0xffffffffu;
 constexpr float NEG_BIG = -1e30f;
 constexpr uint32_t UT = 128;                 // tokens per stage = UMMA M
 constexpr uint32_t TILE_B = UT * 128;        // int8 tile of one head and stage: 16 KB
-constexpr uint32_t U_MAX_STAGES = 6;
+constexpr uint32_t U_MAX_STAGES = 8;             // upper bound of K stages and of V slots
 constexpr uint32_t NGRP = 4;                      // softmax groups working on different jobs in parallel
 constexpr uint32_t EPI_BAR = 7, MERGE_BAR = 8;    // named barriers of the in-kernel merge of the splits
 constexpr uint32_t FIN_BAR = 6;                   // named barrier: softmax warps arrive, accumulate warps wait
@@ -54,7 +54,7 @@ struct UmmaParams {
   __half* out;
   float* partials;
   uint32_t* err;
-  uint32_t row_base, cur_pos, tps, n_stages, n_head, qpg;
+  uint32_t row_base, cur_pos, tps, nk, nv, n_head, qpg;  // nk K stages, nv V slots in shared memory
   float sm_scale_log2;
   // Fused layer step (fused = 1): q is the RAW query; the kernel normalises and rotates it itself
   // (optionally storing the result to q_roped), and the CTAs of the last split quantise the new
@@ -79,13 +79,20 @@ struct UmmaParams {
 
 template <uint32_t HPC>
 struct ULayout {
+  // Two rings. A K stage holds what a job needs first and only briefly: the K tiles of the HPC heads
+  // and BOTH scale rows of its 128 tokens; it is released as soon as the softmax group has read S and
+  // the scales. A V slot holds one head's V tile, requested when that job's Q K^T is issued and held
+  // until its P V has run. A stage that carried K and V together sat in shared memory for the load
+  // latency plus the whole job, which is what bounded the stream.
   static constexpr uint32_t SCALE_B = UT * HPC * 16;                   // scale rows of one stage (K or V)
-  static constexpr uint32_t STAGE_B = 2 * HPC * TILE_B + 2 * SCALE_B;  // 73,728 B for HPC = 2
+  static constexpr uint32_t KSTAGE_B = HPC * TILE_B + 2 * SCALE_B;     // 20,480 B for HPC = 1
+  static constexpr uint32_t VSLOT_B = TILE_B;
   static constexpr uint32_t Q_B = HPC * 2048;                          // Q^T tiles: 16 rows x 128 B per head
   static constexpr uint32_t P_B = NGRP * 4 * 2048;                     // P'^T tiles: one per group x 4 blocks
   static constexpr uint32_t MISC_B = 4096;
   static constexpr uint32_t tail() { return Q_B + P_B + MISC_B; }
-  static constexpr uint32_t total(uint32_t stages) { return stages * STAGE_B + tail() + 1024; }
+  static constexpr uint32_t ring(uint32_t nk, uint32_t nv) { return nk * KSTAGE_B + nv * VSLOT_B; }
+  static constexpr uint32_t total(uint32_t nk, uint32_t nv) { return ring(nk, nv) + tail() + 1024; }
 };
 
 struct Misc {            // small shared state, lives in the MISC_B region
@@ -123,9 +130,9 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
                    const UmmaParams p) {
   using L = ULayout<HPC>;
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t full_bar[U_MAX_STAGES], empty_bar[U_MAX_STAGES];
+  __shared__ __align__(8) uint64_t full_bar[U_MAX_STAGES], k_empty[U_MAX_STAGES], v_full[U_MAX_STAGES], v_empty[U_MAX_STAGES];
   __shared__ __align__(8) uint64_t s_ready[4], s_free[4], p_ready[4], p_free[4], o_ready[4], o_free[4];
-  __shared__ __align__(8) uint64_t q_bar, patched_bar;
+  __shared__ __align__(8) uint64_t q_bar, patched_bar, patched_v;
   __shared__ uint32_t tmem_base_s;
   __shared__ volatile uint32_t abort_s;
 
@@ -141,33 +148,40 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
   // waits for this grid's completion itself). This grid waits (pdl_wait) before it touches what
   // the previous kernels produce (q, the newest cache row) and before its own global writes.
   if (threadIdx.x == 0) pdl_launch_dependents();
-  const uint32_t ns = p.n_stages;
+  const uint32_t ns = p.nk, nv = p.nv;  // ns: K stages
   const uint32_t g0 = blockIdx.y * HPC;
   const uint32_t split = blockIdx.x, n_splits = gridDim.x;
   const uint32_t tok_begin = split * p.tps;
   const uint32_t tok_end = min(tok_begin + p.tps, p.cur_pos);
   const uint32_t n_iter = (tok_end - tok_begin + UT - 1) / UT;
   const uint32_t n_jobs = n_iter * HPC;
+  const uint32_t v_pre = n_jobs <= p.nv ? n_jobs : 0;  // V tiles requested during set-up
 
-  const uint32_t q_tiles = smem_base + ns * L::STAGE_B;   // 1024-aligned (STAGE_B is a multiple of 1024)
+  const uint32_t ring_b = ns * L::KSTAGE_B + nv * L::VSLOT_B;  // K ring, then V ring: both multiples of 1024
+  const uint32_t v_ring = smem_base + ns * L::KSTAGE_B;
+  const uint32_t q_tiles = smem_base + ring_b;
   const uint32_t p_tiles = q_tiles + L::Q_B;
-  Misc* misc = reinterpret_cast<Misc*>(smem_gen + ns * L::STAGE_B + L::Q_B + L::P_B);
+  Misc* misc = reinterpret_cast<Misc*>(smem_gen + ring_b + L::Q_B + L::P_B);
 
-  // One stage of the ring: K and V tiles of HPC heads and their scale rows, 128 tokens from `it * UT`.
+  // One K stage: K tiles of the HPC heads and both scale rows, 128 tokens from `it * UT`.
   auto issue_stage = [&](uint32_t it, uint32_t s) {
     const uint32_t bar = smem_u32(&full_bar[s]);
-    const uint32_t stage = smem_base + s * L::STAGE_B;
+    const uint32_t stage = smem_base + s * L::KSTAGE_B;
     const int row = static_cast<int>(p.row_base + tok_begin + it * UT);
     // older rows were written by earlier steps; the row of the newest token by the kernel before this
     // one (fused step: by this CTA, which patches it into the stage after the load)
     if (!p.fused && tok_begin + (it + 1) * UT >= p.cur_pos) pdl_wait();
-    mbar_arrive_expect_tx(bar, L::STAGE_B);
-    tma_load_2d(stage + 2 * HPC * TILE_B, &map_kd, bar, static_cast<int>(g0 * 16), row);
-    tma_load_2d(stage + 2 * HPC * TILE_B + L::SCALE_B, &map_vd, bar, static_cast<int>(g0 * 16), row);
-    for (uint32_t g = 0; g < HPC; g++) {
-      tma_load_3d(stage + g * TILE_B, &map_kq, bar, 0, static_cast<int>(g0 + g), row);
-      tma_load_3d(stage + (HPC + g) * TILE_B, &map_vq, bar, 0, static_cast<int>(g0 + g), row);
-    }
+    mbar_arrive_expect_tx(bar, L::KSTAGE_B);
+    tma_load_2d(stage + HPC * TILE_B, &map_kd, bar, static_cast<int>(g0 * 16), row);
+    tma_load_2d(stage + HPC * TILE_B + L::SCALE_B, &map_vd, bar, static_cast<int>(g0 * 16), row);
+    for (uint32_t g = 0; g < HPC; g++) tma_load_3d(stage + g * TILE_B, &map_kq, bar, 0, static_cast<int>(g0 + g), row);
+  };
+  // The V tile of job j (stage j / HPC, head j % HPC) into V slot j % nv.
+  auto issue_v = [&](uint32_t j) {
+    const uint32_t v = j % nv, bar = smem_u32(&v_full[v]);
+    const int row = static_cast<int>(p.row_base + tok_begin + (j / HPC) * UT);
+    mbar_arrive_expect_tx(bar, L::VSLOT_B);
+    tma_load_3d(v_ring + v * L::VSLOT_B, &map_vq, bar, 0, static_cast<int>(g0 + j % HPC), row);
   };
 
   // ---- set-up: barriers, TMEM, zeroed operand tiles, quantised Q ----
@@ -178,6 +192,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
     // the lanes of warp 2 in parallel.
     abort_s = 0;
     for (uint32_t s = 0; s < ns; s++) mbar_init(smem_u32(&full_bar[s]), 1);
+    for (uint32_t v = 0; v < nv; v++) mbar_init(smem_u32(&v_full[v]), 1);
     fence_barrier_init();
     prefetch_tensormap(&map_kq);
     prefetch_tensormap(&map_vq);
@@ -185,6 +200,9 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
     prefetch_tensormap(&map_vd);
     const uint32_t n_pre = n_iter < ns ? n_iter : ns;
     for (uint32_t it = 0; it < n_pre; it++) issue_stage(it, it);
+    // a launch whose V tiles all fit at once requests them here too (it should not wait for them);
+    // otherwise the Q K^T issuers request every V tile when its job starts
+    for (uint32_t j = 0; j < v_pre; j++) issue_v(j);
   } else if (warp == 2) {
     if (lane < 4) {
       mbar_init(smem_u32(&s_ready[lane]), 1);
@@ -198,13 +216,16 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
     } else if (lane == 12) {
       mbar_init(smem_u32(&q_bar), 4);  // the four accumulate warps prepare Q
       mbar_init(smem_u32(&patched_bar), 1);
-    } else if (lane - 13 < ns) {
-      mbar_init(smem_u32(&empty_bar[lane - 13]), HPC);  // one tcgen05.commit per job of the stage
+      mbar_init(smem_u32(&patched_v), 1);
+    } else if (lane < 21) {
+      if (lane - 13 < ns) mbar_init(smem_u32(&k_empty[lane - 13]), HPC * 4);  // the 4 warps of each job's softmax group
+    } else if (lane < 29) {
+      if (lane - 21 < nv) mbar_init(smem_u32(&v_empty[lane - 21]), 1);  // the tcgen05.commit behind the job's P V
     }
     fence_barrier_init();
   }
   {
-    uint4* z = reinterpret_cast<uint4*>(smem_gen + ns * L::STAGE_B);
+    uint4* z = reinterpret_cast<uint4*>(smem_gen + ring_b);
     for (uint32_t i = threadIdx.x; i < (L::Q_B + L::P_B) / 16; i += U_THREADS) z[i] = make_uint4(0, 0, 0, 0);
   }
   if (warp == 1) tmem_alloc(smem_u32(&tmem_base_s), TMEM_COLS);
@@ -249,7 +270,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
         hi |= (static_cast<uint32_t>(q >> 7) & 0xffu) << (8 * i);
         lo |= (static_cast<uint32_t>(q) & 0x7fu) << (8 * i);
       }
-      uint8_t* tile = smem_gen + ns * L::STAGE_B + g * 2048;
+      uint8_t* tile = smem_gen + ring_b + g * 2048;
       *reinterpret_cast<uint32_t*>(tile + swz128(hq * 128 + 4 * lane)) = hi;
       *reinterpret_cast<uint32_t*>(tile + swz128((4 + hq) * 128 + 4 * lane)) = lo;
       if ((lane & 7) == 0) misc->sq[g][hq][b] = sq * p.sm_scale_log2;
@@ -342,7 +363,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
     if (lane == 0) {
       uint32_t s = 0, use = 1;
       for (uint32_t it = ns; it < n_iter; it++) {
-        wait(&empty_bar[s], (use - 1) & 1);
+        wait(&k_empty[s], (use - 1) & 1);
         if (abort_s) break;
         issue_stage(it, s);
         if (++s == ns) { s = 0; use++; }
@@ -350,24 +371,34 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
     }
     __syncwarp();
     if (new_row) {
-      // The last stage was loaded with whatever the cache row held before: once it has landed,
-      // the fresh row replaces it in shared memory (swizzled tile rows and scale rows).
+      // The last K stage and the last jobs' V slots were loaded with whatever the cache row held
+      // before: once they have landed, the fresh row replaces it in shared memory (swizzled tile
+      // rows, scale rows). K side first (the last Q K^T waits for it and only then requests its V
+      // tile), V side when that tile is there (the last P V waits for it).
       const uint32_t it_last = n_iter - 1, s_last = it_last % ns;
       wait(&full_bar[s_last], (it_last / ns) & 1);
       const uint32_t r = p.cur_pos - 1 - (tok_begin + it_last * UT);
-      uint8_t* stage = smem_gen + s_last * L::STAGE_B;
+      uint8_t* stage = smem_gen + s_last * L::KSTAGE_B;
 #pragma unroll
       for (uint32_t g = 0; g < HPC; g++) {
         *reinterpret_cast<uint32_t*>(stage + g * TILE_B + swz128(r * 128 + 4 * lane)) = pk[g];
-        *reinterpret_cast<uint32_t*>(stage + (HPC + g) * TILE_B + swz128(r * 128 + 4 * lane)) = pv[g];
         if ((lane & 7) == 0) {
-          *reinterpret_cast<float*>(stage + 2 * HPC * TILE_B + (r * HPC + g) * 16 + 4 * (lane >> 3)) = dk[g];
-          *reinterpret_cast<float*>(stage + 2 * HPC * TILE_B + L::SCALE_B + (r * HPC + g) * 16 + 4 * (lane >> 3)) = dv[g];
+          *reinterpret_cast<float*>(stage + HPC * TILE_B + (r * HPC + g) * 16 + 4 * (lane >> 3)) = dk[g];
+          *reinterpret_cast<float*>(stage + HPC * TILE_B + L::SCALE_B + (r * HPC + g) * 16 + 4 * (lane >> 3)) = dv[g];
         }
       }
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&patched_bar));
+#pragma unroll
+      for (uint32_t g = 0; g < HPC; g++) {
+        const uint32_t j = it_last * HPC + g, v = j % nv;
+        wait(&v_full[v], (j / nv) & 1);
+        *reinterpret_cast<uint32_t*>(smem_gen + ns * L::KSTAGE_B + v * L::VSLOT_B + swz128(r * 128 + 4 * lane)) = pv[g];
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&patched_v));
     }
   } else if (warp < 1 + NISS) {
     // ---------------- QK issuers: S^T[token][(block, byte row, head)] = K tile x Q^T ----------------
@@ -384,11 +415,17 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
         if (p.fused && tok_end == p.cur_pos && it == n_iter - 1) wait(&patched_bar, 0);  // the new row is in place
         if (k > 0) wait(&s_free[bi], (k - 1) & 1);
         tc_fence_after();
-        const uint64_t ka = dbase + ((smem_base + s * L::STAGE_B + g * TILE_B) >> 4);
+        const uint64_t ka = dbase + ((smem_base + s * L::KSTAGE_B + g * TILE_B) >> 4);
         const uint64_t qb = dbase + ((q_tiles + g * 2048) >> 4);
 #pragma unroll
         for (uint32_t b = 0; b < 4; b++) umma_i8(tmem + bi * 64 + 16 * b, ka + 2 * b, qb + 2 * b, IDESC_QK, 0u);
         umma_commit(smem_u32(&s_ready[bi]));
+        // Now request the job's V tile (unless set-up did): it arrives while the softmax group works,
+        // and its slot is occupied for one load latency instead of the load latency plus the whole job.
+        if (j >= v_pre) {
+          if (j >= nv) wait(&v_empty[j % nv], (j / nv - 1) & 1);
+          if (!abort_s) issue_v(j);
+        }
       }
     }
   } else if (warp < 1 + 2 * NISS) {
@@ -401,18 +438,21 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
       const uint64_t dbase = umma_desc_sw128(0, 16, 1024);
       const uint32_t q = warp - 1 - NISS;
       for (uint32_t j = q; j < n_jobs; j += NISS) {
-        const uint32_t it = j / HPC, g = j % HPC, bi = j % NGRP, k = j / NGRP, s = it % ns;
+        const uint32_t it = j / HPC, bi = j % NGRP, k = j / NGRP;
+        const uint32_t v = j % nv;
+        wait(&v_full[v], (j / nv) & 1);
+        if (p.fused && tok_end == p.cur_pos && it == n_iter - 1) wait(&patched_v, 0);  // the new row is in place
         wait(&p_ready[bi], k & 1);
         if (k > 0) wait(&o_free[bi], (k - 1) & 1);
         tc_fence_after();
-        const uint64_t va = dbase + ((smem_base + s * L::STAGE_B + (HPC + g) * TILE_B) >> 4);
+        const uint64_t va = dbase + ((v_ring + v * L::VSLOT_B) >> 4);
         const uint64_t pb = dbase + ((p_tiles + bi * 4 * 2048) >> 4);
 #pragma unroll
         for (uint32_t kk = 0; kk < 4; kk++)
           umma_i8(tmem + NGRP * 64 + bi * 64, va + kk * (32 * 128 >> 4), pb + 2 * kk, IDESC_PV, kk);
         umma_commit(smem_u32(&o_ready[bi]));
         umma_commit(smem_u32(&p_free[bi]));
-        umma_commit(smem_u32(&empty_bar[s]));  // one arrival per job of the stage
+        umma_commit(smem_u32(&v_empty[v]));  // the V slot is free once this P V has run
       }
     }
   }
@@ -428,7 +468,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
 
     for (uint32_t j = w; j < n_jobs; j += NGRP) {
       const uint32_t it = j / HPC, g = j % HPC, bi = w, k = j / NGRP;
-      const uint8_t* stage = smem_gen + (it % ns) * L::STAGE_B;
+      const uint8_t* stage = smem_gen + (it % ns) * L::KSTAGE_B;
       const bool valid = tok_begin + it * UT + t < tok_end;
       wait(&s_ready[bi], k & 1);
       tc_fence_after();
@@ -436,12 +476,15 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
 #pragma unroll
       for (uint32_t b = 0; b < 4; b++) tmem_ld8(tmem + lane_addr + bi * 64 + 16 * b, d[b]);
       tmem_ld_wait();
+      const float4 sk = *reinterpret_cast<const float4*>(stage + HPC * TILE_B + (t * HPC + g) * 16);
+      float4 sv = *reinterpret_cast<const float4*>(stage + HPC * TILE_B + L::SCALE_B + (t * HPC + g) * 16);
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&s_free[bi]));
+      if (lane == 0) {
+        mbar_arrive(smem_u32(&s_free[bi]));
+        mbar_arrive(smem_u32(&k_empty[it % ns]));  // S and the scale rows are in registers: the K stage is done with
+      }
 
-      const float4 sk = *reinterpret_cast<const float4*>(stage + 2 * HPC * TILE_B + (t * HPC + g) * 16);
-      float4 sv = *reinterpret_cast<const float4*>(stage + 2 * HPC * TILE_B + L::SCALE_B + (t * HPC + g) * 16);
       const float skb[4] = {sk.x, sk.y, sk.z, sk.w};
       float sc[4];
 #pragma unroll
@@ -506,7 +549,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
       // P'[h][b] = p[h] * sV[b] as a 23-bit integer: the low three bytes of (x * qscale + 2^23).
       // Byte rows of block b's tile: hi -> row h, mid -> row 4 + h, lo -> row 8 + h; this token's
       // column inside a swizzled row n is t ^ ((n & 7) << 4).
-      uint8_t* pt = smem_gen + ns * L::STAGE_B + L::Q_B + bi * 4 * 2048;
+      uint8_t* pt = smem_gen + ring_b + L::Q_B + bi * 4 * 2048;
 #pragma unroll
       for (int b = 0; b < 4; b++) {
         uint8_t* tile = pt + b * 2048;
@@ -645,9 +688,11 @@ cudaError_t bp_decode_umma_init(bp_attn_ctx*) {
   return umma_attr<2>();
 }
 
+// K stages and V slots that fit: equal numbers (a K stage is busy for a load latency plus the short
+// wait for its softmax group, a V slot for a load latency plus the P V issue), at most U_MAX_STAGES.
 template <uint32_t HPC>
 static uint32_t umma_max_stages() {
-  uint32_t n = (U_SMEM_BUDGET - ULayout<HPC>::tail() - 1024) / ULayout<HPC>::STAGE_B;
+  uint32_t n = (U_SMEM_BUDGET - ULayout<HPC>::tail() - 1024) / (ULayout<HPC>::KSTAGE_B + HPC * ULayout<HPC>::VSLOT_B);
   return n > U_MAX_STAGES ? U_MAX_STAGES : n;
 }
 
@@ -674,8 +719,18 @@ uint32_t bp_decode_umma_splits(const bp_attn_ctx* c, uint32_t cur_pos) {
 
 template <uint32_t HPC>
 static cudaError_t launch_umma(bp_attn_ctx* c, cudaStream_t s, UmmaParams& p, uint32_t spp, uint32_t n_splits) {
-  p.n_stages = spp < umma_max_stages<HPC>() ? spp : umma_max_stages<HPC>();
-  const size_t smem = ULayout<HPC>::total(p.n_stages);
+  uint32_t cap = umma_max_stages<HPC>();
+  uint32_t v_cap = cap * HPC > U_MAX_STAGES ? U_MAX_STAGES : cap * HPC;
+  if (c->opt_uring != 0) {  // tuning override: K stages * 16 + V slots, accepted when it fits
+    const uint32_t k = c->opt_uring >> 4, v = c->opt_uring & 15;
+    if (k >= 1 && v >= 1 && k <= U_MAX_STAGES && v <= U_MAX_STAGES && ULayout<HPC>::total(k, v) <= U_SMEM_BUDGET) {
+      cap = k;
+      v_cap = v;
+    }
+  }
+  p.nk = spp < cap ? spp : cap;
+  p.nv = spp * HPC < v_cap ? spp * HPC : v_cap;
+  const size_t smem = ULayout<HPC>::total(p.nk, p.nv);
   dim3 grid(n_splits, c->cfg.n_kv_head / HPC);
   return bp_launch(c->opt_pdl != 0, decode_umma_kernel<HPC>, grid, dim3(U_THREADS), smem, s, c->umap_qs[0], c->umap_d[0],
                    c->umap_qs[1], c->umap_d[1], p);
@@ -693,7 +748,7 @@ cudaError_t bp_launch_decode_umma(bp_attn_ctx* c, cudaStream_t s, uint32_t layer
   p.row_base = layer * c->cfg.max_seq;
   p.cur_pos = cur_pos;
   p.tps = spp * UT;
-  p.n_stages = 1;
+  p.nk = p.nv = 1;
   p.n_head = c->cfg.n_head;
   p.qpg = c->qpg;
   p.sm_scale_log2 = (1.0f / sqrtf(static_cast<float>(BP_HEAD_DIM))) * 1.4426950408889634f;

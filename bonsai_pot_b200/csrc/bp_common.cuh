@@ -57,6 +57,7 @@ struct bp_attn_ctx {
   __half* px_out[BP_MAX_PEERS];
   uint32_t* px_flag[BP_MAX_PEERS];
   uint32_t* px_epoch;  // device: meetings so far, per counter slot [64]
+  uint32_t opt_uring;  // tcgen05 decode: 0 = default ring sizes, else K stages * 16 + V slots
   uint32_t opt_umerge; // tcgen05 decode: merge the splits in the decode kernel (1) or with a second kernel (0)
   uint32_t opt_pdl;  // launch the kernels of a layer with programmatic stream serialization (1) or plainly (0)
   uint32_t opt_pf_nq; // prefill: query tiles per work item (1 or 2), 0 = by batch size

@@ -683,6 +683,9 @@ int bp_set_option(bp_attn_ctx* c, const char* name, uint32_t value) {
     if ((value != 1 && value != 2) || c->cfg.n_kv_head % value != 0)
       return fail_config(c, "decode_umma_heads_per_cta must be 1 or 2 and divide n_kv_head");
     c->opt_uhpc = value;
+  } else if (strcmp(name, "decode_ring") == 0) {
+    c->opt_uring = value;
+    return BP_OK;
   } else if (strcmp(name, "decode_in_kernel_merge") == 0) {
     c->opt_umerge = value != 0;
     return BP_OK;
