@@ -604,3 +604,33 @@ def test_norm_rope_quant_bit_exact_for_other_head_counts(n_head, n_kv_head):
     assert np.array_equal(kq, sh.qs_section(ref_k, 0)[:m]) and np.array_equal(vq, sh.qs_section(ref_v, 0)[:m])
     assert np.array_equal(kd.view(np.uint32), sh.d_section(ref_k, 0)[:m].view(np.uint32))
     assert np.array_equal(vd.view(np.uint32), sh.d_section(ref_v, 0)[:m].view(np.uint32))
+
+
+@pytest.mark.parametrize("n_head,n_kv_head", [(4, 1), (8, 2), (16, 4)])
+def test_prefill_on_a_kv_head_shard(n_head, n_kv_head):
+    """A context that holds the heads of one of N shards (n_head / N, n_kv_head / N): the tensor-core
+    prefill kernel against the plain CUDA-core kernel on the same cache, 700 tokens."""
+    m = 700
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(7 * n_head)
+    with bp.AttnContext(n_layer=1, n_head=n_head, n_kv_head=n_kv_head, max_seq=1024, n_shards=8 // n_kv_head,
+                        shard=0) as ctx:
+        w = torch.ones(128, dtype=torch.float16, device="cuda")
+        q = torch.randn(m, n_head * 128, generator=gen, device="cuda").half()
+        k = torch.randn(m, n_kv_head * 128, generator=gen, device="cuda").half()
+        v = torch.randn(m, n_kv_head * 128, generator=gen, device="cuda").half()
+        ctx.dispatch_q_norm_rope_fused(q, w, 0, m)
+        ctx.dispatch_kv_writeback_fused(0, k, v, w, 0, m)
+        ref = torch.zeros(m, n_head * 128, dtype=torch.float16, device="cuda")
+        ctx.set_variant(1)
+        ctx.dispatch_attention(0, q, ref, m)
+        torch.cuda.synchronize()
+        ctx.set_variant(0)
+        for tiles in (0, 1, 2):
+            ctx.set_option("prefill_tiles_per_item", tiles)
+            out = torch.full((m, n_head * 128), float("nan"), dtype=torch.float16, device="cuda")
+            ctx.dispatch_attention(0, q, out, m)
+            torch.cuda.synchronize()
+            assert ctx.status() == 0
+            ok, max_abs, max_rel = within_tolerance(host(out), host(ref).astype(np.float32))
+            assert ok, (n_head, n_kv_head, tiles, max_abs, max_rel)
