@@ -40,7 +40,8 @@ constexpr uint32_t UT = 128;                 // tokens per stage = UMMA M
 constexpr uint32_t TILE_B = UT * 128;        // int8 tile of one head and stage: 16 KB
 constexpr uint32_t U_MAX_STAGES = 8;             // upper bound of K stages and of V slots
 constexpr uint32_t NGRP = 4;                      // softmax groups working on different jobs in parallel
-constexpr uint32_t EPI_BAR = 7, MERGE_BAR = 8;    // named barriers of the in-kernel merge of the splits
+constexpr uint32_t POLL_LIMIT = 1u << 18;         // polling rounds (about 0.2 us each) before the merge gives up
+constexpr uint32_t MERGE_BAR = 8;                 // named barrier: the merger's accumulate and softmax warps
 constexpr uint32_t FIN_BAR = 6;                   // named barrier: softmax warps arrive, accumulate warps wait
 constexpr uint32_t NISS = 2;                     // UMMA issuer warps per kind (QK, PV)
 constexpr uint32_t U_FIRST_SM_WARP = 1 + 2 * NISS;  // warp 0 producer, then the issuers
@@ -65,8 +66,9 @@ struct UmmaParams {
   // ranks meet afterwards with bp_peer_sync.
   uint32_t n_px, px_off;
   __half* px_out[BP_MAX_PEERS];
-  uint32_t merge;       // 1: the CTA of a head group that finishes last merges the splits itself
-  uint32_t* tickets;    // one arrival counter per head group (grid y), zero between launches
+  uint32_t merge;       // 1: the CTAs of a head group merge its splits themselves (merge_unit)
+  uint2* ll;            // tagged partials [split][head][BP_LL_STRIDE]: (value bits, tag of the launch)
+  uint32_t* epochs;     // per head group (grid y): the tag of the last merged launch
   uint32_t fused;
   float eps;
   __half* q_roped;
@@ -101,7 +103,7 @@ struct Misc {            // small shared state, lives in the MISC_B region
   float info[NGRP][8];      // per group: corr[4], dequantisation factor of P' per block [4]
   float lsum[NGRP][4][4];   // final l per (softmax group, query head, warp)
   float mfin[NGRP][4];
-  uint32_t is_last;         // this CTA took the last ticket of its head group
+  uint32_t tag;             // the launch's tag, for the softmax warps of a merging CTA
 };
 
 __device__ __forceinline__ float s32_to_f32(uint32_t x) {  // exact for |x| < 2^22
@@ -123,11 +125,104 @@ __device__ __noinline__ void cta_wait(uint64_t* bar, uint32_t parity, volatile u
   }
 }
 
+// One final output element: to this rank's output and, with a peer exchange, to every rank's gathered buffer.
+__device__ __forceinline__ void put_out(const UmmaParams& p, uint32_t h, uint32_t d, float v) {
+  const __half hv = __float2half_rn(v);
+  p.out[static_cast<size_t>(h) * BP_HEAD_DIM + d] = hv;
+  for (uint32_t r = 0; r < p.n_px; r++) p.px_out[r][p.px_off + static_cast<size_t>(h) * BP_HEAD_DIM + d] = hv;
+}
+
+// Merge of the splits (attention_merge.wgsl:70-130) inside the launch. CTAs publish their partial
+// (o[128], m, l) per query head as (value, tag) pairs, the tag naming this launch (the head group's
+// epoch + 1): one 8-byte store per value and no fence, because a reader that sees the tag sees the
+// value stored with it. The output of a head group is cut into units of 32 elements (one query head
+// x one quarter of the dims), and a unit is merged by one warp that has its own CTA's part at hand
+// and polls the other splits' parts: lane k reads (m, l) of the k-th other split, the weights travel
+// by shuffle, and the loads of a round are all in flight together. Who merges which unit:
+//   mode 2 (up to 16 splits of up to 4 stages: launches bound by latency)  one CTA per head group, a full-length split, merges all units with its
+//           softmax warps; its own partial stays in shared memory, so when it is the last to finish
+//           the merge ends one L2 round trip later. One SM can only keep so many loads in flight:
+//           with 16 units x 17 splits this took 2.5 us per polling round.
+//   mode 1 (more splits)      unit u belongs to split u mod n_splits, whose accumulate warp of that
+//           quarter holds the CTA's part in registers: one more hop (the slowest split's stores must
+//           reach the others), but no SM is a bottleneck.
+// One warp; `split` is the caller's, (a_own, m_own, l_own) its partial of head h at dim d.
+template <uint32_t MERGE_W>  // partials of one element in flight per polling round
+__device__ __forceinline__ void merge_unit(const UmmaParams& p, uint32_t lane, uint32_t n_splits, uint32_t split, uint32_t h,
+                                           uint32_t d, float a_own, float m_own, float l_own, uint32_t tag,
+                                           volatile uint32_t* abort_flag) {
+  const uint32_t n_oth = n_splits - 1;  // the i-th other split is i for i < split, else i + 1
+  const uint32_t sstride = p.n_head * BP_LL_STRIDE;  // 32-bit index arithmetic: the scratch has < 2^20 pairs
+  const uint2* base = p.ll + h * BP_LL_STRIDE;
+  float m_run = m_own, l_run = l_own, o_run = a_own;
+  for (uint32_t c0 = 0; c0 < n_oth; c0 += 32) {
+    const uint32_t nc = min(32u, n_oth - c0);
+    float e_k = 0.f;
+    for (uint32_t v0 = 0; v0 < nc; v0 += MERGE_W) {
+      uint2 v[MERGE_W];
+      uint2 mm, ls;
+      for (uint32_t spin = 0;; spin++) {
+        // Straight-line loads (indices clamped to the chunk's last split instead of branching around
+        // a load): every load of the round is issued before the first is used. `first` is made opaque
+        // so that the addresses are formed here, next to their loads: hoisted out of the polling loop
+        // they would take two registers each and spill the loaded values, and a load whose result is
+        // spilled is waited for at once.
+        uint32_t first = c0;
+        asm volatile("" : "+r"(first));
+        const uint32_t i_ml = first + min(lane, nc - 1);
+        const uint2* ml = base + (i_ml + (i_ml >= split ? 1u : 0u)) * sstride;
+        mm = ld_tagged(ml + 128);
+        ls = ld_tagged(ml + 129);
+        const uint32_t k_max = nc - 1 - v0;
+#pragma unroll
+        for (uint32_t k = 0; k < MERGE_W; k++) {
+          const uint32_t i = first + v0 + min(k, k_max);
+          v[k] = ld_tagged(base + (i + (i >= split ? 1u : 0u)) * sstride + d);
+        }
+        bool ok = mm.y == tag && ls.y == tag;
+#pragma unroll
+        for (uint32_t k = 0; k < MERGE_W; k++) ok = ok && v[k].y == tag;
+        if (__all_sync(FULL, ok)) break;
+        const bool give_up = *abort_flag != 0 || spin >= POLL_LIMIT;
+        if (__any_sync(FULL, give_up)) {  // warp-uniform exit: the shuffles below need every lane
+          if (*abort_flag == 0) {
+            *abort_flag = 1;
+            atomicExch(p.err, 3u);
+          }
+          break;
+        }
+        __nanosleep(spin < 4 ? 64u : 256u);
+      }
+      if (v0 == 0) {
+        const float m_k = lane < nc ? __uint_as_float(mm.x) : NEG_BIG;
+        float m_c = m_k;
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) m_c = fmaxf(m_c, __shfl_xor_sync(FULL, m_c, off));
+        const float m_new = fmaxf(m_run, m_c);
+        e_k = lane < nc ? ex2(m_k - m_new) : 0.f;
+        float l_c = lane < nc ? __uint_as_float(ls.x) * e_k : 0.f;
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) l_c += __shfl_xor_sync(FULL, l_c, off);
+        const float scale = ex2(m_run - m_new);
+        o_run *= scale;
+        l_run = fmaf(l_run, scale, l_c);
+        m_run = m_new;
+      }
+#pragma unroll
+      for (uint32_t k = 0; k < MERGE_W; k++) {
+        const float e = __shfl_sync(FULL, e_k, (v0 + k) & 31u);
+        o_run = fmaf(__uint_as_float(v[k].x), v0 + k < nc ? e : 0.f, o_run);
+      }
+    }
+  }
+  put_out(p, h, d, o_run * (1.0f / l_run));
+}
+
 template <uint32_t HPC>
 __global__ void __launch_bounds__(U_THREADS, 1)
 decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_constant__ CUtensorMap map_kd,
                    const __grid_constant__ CUtensorMap map_vq, const __grid_constant__ CUtensorMap map_vd,
-                   const UmmaParams p) {
+                   const __grid_constant__ UmmaParams p) {
   using L = ULayout<HPC>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[U_MAX_STAGES], k_empty[U_MAX_STAGES], v_full[U_MAX_STAGES], v_empty[U_MAX_STAGES];
@@ -237,8 +332,34 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
   // Q of head (g, hq), block b: 15-bit integers = 128 * hi + lo against the block's absmax; hi bytes
   // go to row hq, lo bytes to row 4 + hq of the head's Q^T tile (swizzled 128-byte rows). Done by the
   // accumulate warps while the producer already streams the first stages; the QK issuers wait on q_bar.
+  uint32_t epoch = 0;  // accumulate warps: the head group's epoch, read once the previous launch is complete
+  // In-kernel merge of the splits (merge_unit): 0 none, 1 spread over the CTAs, 2 by one CTA of the head
+  // group: the last split when it is as long as the others (with the fused step it has the new row's
+  // work on top, finishes last, and its partial never leaves the SM), else the first.
+  // (Evaluated where it is used, in the epilogues: kept in registers from here on, these few values
+  // changed the register allocation of the main loops and cost 3 % at long contexts.)
+  auto merge_plan = [&](uint32_t& mode, bool& is_merger) {
+    mode = p.merge && n_splits > 1 ? (n_splits <= 16 && p.tps <= 4 * UT ? 2u : 1u) : 0u;
+    const uint32_t last_stages = (p.cur_pos - (n_splits - 1) * p.tps + UT - 1) / UT;
+    const uint32_t merger_split = last_stages == p.tps / UT ? n_splits - 1 : 0;
+    is_merger = mode == 2 && split == merger_split;
+  };
+  auto own_part = [&]() {  // the merger's own o: over the dead P' tiles
+    return reinterpret_cast<float*>(smem_gen + ring_b + L::Q_B);
+  };
+  // (m, l) of query head hq of head g over this CTA's tokens: the softmax groups' values, merged
+  auto head_ml = [&](uint32_t g, uint32_t hq, float& m, float& l) {
+    m = NEG_BIG;
+    for (uint32_t w = g; w < NGRP; w += HPC) m = fmaxf(m, misc->mfin[w][hq]);
+    l = 0.f;
+    for (uint32_t w = g; w < NGRP; w += HPC) {
+      const float4 ls = *reinterpret_cast<const float4*>(misc->lsum[w][hq]);
+      l += ((ls.x + ls.y) + (ls.z + ls.w)) * ex2(misc->mfin[w][hq] - m);
+    }
+  };
   auto prepare_q = [&](uint32_t aw) {  // aw = 0..3: the calling accumulate warp; warp aw takes heads aw, aw + 4, ...
     pdl_wait();  // q is written by the kernel before this one
+    if (p.merge && n_splits > 1) epoch = ld_relaxed_u32(p.epochs + blockIdx.y);  // used in the epilogue
     // lane l holds dims 4l .. 4l+3 of one head: a Q8_0 block is 8 lanes. One 8-byte load, three
     // shuffles for the block maximum, two 4-byte stores: short straight-line code, because this sits
     // on the critical path of every launch (the first Q K^T waits for it) and runs cold.
@@ -286,50 +407,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
   // buffer; its k-th job (k = j / NGRP) completes phase k of its barriers.
   // A wait that degrades to a no-op once any warp of the CTA has timed out.
   auto wait = [&](uint64_t* bar, uint32_t parity) { cta_wait(bar, parity, &abort_s, p.err); };
-  // Log-sum-exp merge over the splits (attention_merge.wgsl:70-130) by the softmax and accumulate
-  // warps (640 threads) of the CTA that took the last ticket: thread = one output element.
-  auto put = [&](uint32_t h, uint32_t d, float v) {  // one final output element: local, and to the peers
-    const __half hv = __float2half_rn(v);
-    p.out[static_cast<size_t>(h) * BP_HEAD_DIM + d] = hv;
-    for (uint32_t r = 0; r < p.n_px; r++) p.px_out[r][p.px_off + static_cast<size_t>(h) * BP_HEAD_DIM + d] = hv;
-  };
-  auto merge_splits = [&]() {
-    pdl_wait();
-    __threadfence();
-    const uint32_t tid = threadIdx.x - U_FIRST_SM_WARP * 32, n_thr = 128 * NGRP + 128;
-    const size_t stride = static_cast<size_t>(p.n_head) * BP_PART_STRIDE;
-    for (uint32_t idx = tid; idx < HPC * p.qpg * BP_HEAD_DIM; idx += n_thr) {
-      const uint32_t hl = idx >> 7, d = idx & 127;
-      const uint32_t h = g0 * p.qpg + hl;
-      const float* base = p.partials + static_cast<size_t>(h) * BP_PART_STRIDE;
-      float m_all = NEG_BIG, o = 0.f, l = 0.f;
-      for (uint32_t s0 = 0; s0 < n_splits; s0 += 6) {
-        float2 ml[6];
-        float v[6];
-#pragma unroll
-        for (uint32_t k = 0; k < 6; k++) {
-          const bool in = s0 + k < n_splits;
-          ml[k] = in ? __ldcg(reinterpret_cast<const float2*>(base + (s0 + k) * stride + 128)) : make_float2(NEG_BIG, 0.f);
-          v[k] = in ? __ldcg(base + (s0 + k) * stride + d) : 0.f;
-        }
-        float m_new = m_all;
-#pragma unroll
-        for (uint32_t k = 0; k < 6; k++) m_new = fmaxf(m_new, ml[k].x);
-        const float c = ex2(m_all - m_new);
-        o *= c;
-        l *= c;
-        m_all = m_new;
-#pragma unroll
-        for (uint32_t k = 0; k < 6; k++) {
-          const float e = ex2(ml[k].x - m_all);
-          o = fmaf(v[k], e, o);
-          l = fmaf(ml[k].y, e, l);
-        }
-      }
-      put(h, d, o * (1.0f / l));
-    }
-  };
-
+  auto put = [&](uint32_t h, uint32_t d, float v) { put_out(p, h, d, v); };
   if (warp == 0) {
     // ---------------- TMA producer: the rounds of the ring after the first (requested during set-up) ----------------
     // Fused step, last split: the whole warp first quantises the new token's K / V rows of this
@@ -576,10 +654,6 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
     }
     __threadfence_block();
     named_bar_arrive(FIN_BAR, 128 * NGRP + 128);  // the accumulate warps merge the groups
-    if (n_splits > 1 && p.merge) {
-      named_bar_sync(MERGE_BAR, 128 * NGRP + 128);  // the ticket has been drawn
-      if (misc->is_last) merge_splits();
-    }
   } else {
     // ---------------- accumulate: thread = head dim ----------------
     prepare_q(warp - (U_FIRST_SM_WARP + 4 * NGRP));
@@ -621,43 +695,74 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
     // token subsets of head g and are merged here.
     named_bar_sync(FIN_BAR, 128 * NGRP + 128);
     pdl_wait();  // the partials / output buffers may still be read by earlier kernels
+    const uint32_t tag = epoch + 1 != 0 ? epoch + 1 : 1u;  // never 0: untouched scratch reads as tag 0
+    uint32_t merge_mode;
+    bool merger;
+    merge_plan(merge_mode, merger);
+    float acc_h[HPC * 4];  // this CTA's partial o per query head, at this thread's dim
 #pragma unroll
     for (uint32_t g = 0; g < HPC; g++) {
 #pragma unroll
       for (uint32_t hq = 0; hq < 4; hq++) {
-        float m = NEG_BIG;
+        float m, l, acc = 0.f;
+        head_ml(g, hq, m, l);
 #pragma unroll
-        for (uint32_t w = g; w < NGRP; w += HPC) m = fmaxf(m, misc->mfin[w][hq]);
-        float acc = 0.f, l = 0.f;
-#pragma unroll
-        for (uint32_t w = g; w < NGRP; w += HPC) {
-          const float e = ex2(misc->mfin[w][hq] - m);
-          l += ((misc->lsum[w][hq][0] + misc->lsum[w][hq][1]) + (misc->lsum[w][hq][2] + misc->lsum[w][hq][3])) * e;
-          acc += o[w][hq] * e;
-        }
+        for (uint32_t w = g; w < NGRP; w += HPC) acc += o[w][hq] * ex2(misc->mfin[w][hq] - m);
+        acc_h[g * 4 + hq] = acc;
         const uint32_t h = (g0 + g) * p.qpg + hq;
         if (n_splits == 1) {
           put(h, dim, acc * (1.0f / l));
-        } else {
+        } else if (merger) {  // stays in the CTA
+          own_part()[(g * 4 + hq) * BP_HEAD_DIM + dim] = acc;
+        } else if (merge_mode != 0) {  // tagged, for the CTAs that merge this head's units
+          uint2* dst = p.ll + (split * p.n_head + h) * BP_LL_STRIDE;
+          st_tagged(dst + dim, __float_as_uint(acc), tag);
+          if (dim == 0) {
+            st_tagged(dst + 128, __float_as_uint(m), tag);
+            st_tagged(dst + 129, __float_as_uint(l), tag);
+          }
+        } else {  // plain, for attn_combine_kernel
           float* dst = p.partials + (static_cast<size_t>(split) * p.n_head + h) * BP_PART_STRIDE;
           dst[dim] = acc;
           if (dim == 0) { dst[128] = m; dst[129] = l; }
         }
       }
     }
-    if (n_splits > 1 && p.merge) {
-      // Publish the partial, draw a ticket; the CTA of this head group that arrives last merges.
-      __threadfence();
-      named_bar_sync(EPI_BAR, 128);
-      if (warp == U_FIRST_SM_WARP + 4 * NGRP && lane == 0) {
-        const uint32_t t = atomicAdd(&p.tickets[blockIdx.y], 1u);
-        const uint32_t last = t == n_splits - 1 ? 1u : 0u;
-        if (last) p.tickets[blockIdx.y] = 0;  // every other CTA has arrived: the next launch starts from zero
-        misc->is_last = last;
-        __threadfence_block();
+    if (merger && dim == 0) misc->tag = tag;
+    if (merge_mode == 1) {
+      // This warp's units: (query head hl, dim quarter `quad`) with (hl * 4 + quad) mod n_splits == split.
+#pragma unroll 1
+      for (uint32_t hl = 0; hl < HPC * 4; hl++) {
+        if ((hl * 4 + quad) % n_splits != split) continue;
+        float a = acc_h[0], m, l;
+#pragma unroll
+        for (uint32_t i = 1; i < HPC * 4; i++) a = hl == i ? acc_h[i] : a;
+        head_ml(hl / 4, hl % 4, m, l);
+        merge_unit<10>(p, lane, n_splits, split, g0 * p.qpg + hl, dim, a, m, l, tag, &abort_s);
+        // The next launch's tag. Safe to advance once unit 0 is merged: its warp has seen every split's
+        // tag, so every CTA of the group has read the epoch.
+        if (hl == 0 && quad == 0 && lane == 0) *reinterpret_cast<volatile uint32_t*>(p.epochs + blockIdx.y) = tag;
       }
-      named_bar_sync(MERGE_BAR, 128 * NGRP + 128);
-      if (misc->is_last) merge_splits();
+    }
+  }
+
+  // Mode 2: the merger's softmax warps take the units (one call site, after the roles: their registers
+  // are dead here and a round's loads all fit).
+  uint32_t merge_mode_end;
+  bool merger_end;
+  merge_plan(merge_mode_end, merger_end);
+  if (merger_end && warp >= U_FIRST_SM_WARP) {
+    __threadfence_block();
+    named_bar_sync(MERGE_BAR, 128 * NGRP + 128);  // this CTA's own partial and the tag are in shared memory
+    const uint32_t tag = misc->tag;
+    pdl_wait();  // the output buffer may still be read by earlier kernels
+#pragma unroll 1
+    for (uint32_t u = warp - U_FIRST_SM_WARP; u < HPC * 16; u += 4 * NGRP + 4) {
+      const uint32_t hl = u >> 2, d = (u & 3) * 32 + lane;
+      float m, l;
+      head_ml(hl / 4, hl % 4, m, l);
+      merge_unit<15>(p, lane, n_splits, split, g0 * p.qpg + hl, d, own_part()[hl * BP_HEAD_DIM + d], m, l, tag, &abort_s);
+      if (u == 0 && lane == 0) *reinterpret_cast<volatile uint32_t*>(p.epochs + blockIdx.y) = tag;  // as in mode 1
     }
   }
 
@@ -757,7 +862,8 @@ cudaError_t bp_launch_decode_umma(bp_attn_ctx* c, cudaStream_t s, uint32_t layer
   p.px_off = layer * c->cfg.n_shards * c->q_dim + c->cfg.shard * c->q_dim;
   for (uint32_t r = 0; r < BP_MAX_PEERS; r++) p.px_out[r] = r < c->n_px ? c->px_out[r] : nullptr;
   p.merge = c->opt_umerge || c->n_px > 0;  // the exchange lives in the in-kernel merge
-  p.tickets = c->tickets;
+  p.ll = c->ll;
+  p.epochs = c->epochs;
   p.fused = fs != nullptr ? 1u : 0u;
   p.eps = c->cfg.rms_eps;
   p.n_kv_head = c->cfg.n_kv_head;

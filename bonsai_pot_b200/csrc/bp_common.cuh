@@ -12,6 +12,7 @@
 constexpr uint32_t BP_HEAD_DIM = 128;
 constexpr uint32_t BP_QK8 = 32;          // Q8_0 block size
 constexpr uint32_t BP_PART_STRIDE = 132; // floats per (split, head) partial: o[128], m, l, pad
+constexpr uint32_t BP_LL_STRIDE = 132;   // (value, tag) pairs per (split, head) partial of the in-kernel merge: same order
 constexpr uint32_t BP_MAX_PEERS = 8;     // ranks of a peer exchange
 
 struct bp_attn_ctx {
@@ -21,7 +22,8 @@ struct bp_attn_ctx {
   uint8_t* kv[2];    // device: kv_k, kv_v (d-section then qs-section)
   __half* rope;      // device: [max_seq][64][2] (cos, sin)
   float* partials;   // device: split-KV scratch [max_splits][n_head][BP_PART_STRIDE]
-  uint32_t* tickets; // device: arrival counters of the in-kernel split combine (self-resetting)
+  uint2* ll;         // device: tagged split partials of the in-kernel merge [max_splits][n_head][BP_LL_STRIDE] (value, tag)
+  uint32_t* epochs;  // device: per head group, the tag of the last merged launch (64 words)
   uint32_t* err_host; // pinned, mapped: kernels store a non-zero code here when a bounded wait gives up
   uint32_t* err_dev;  // device alias of err_host
   uint32_t max_splits;

@@ -143,6 +143,10 @@ bool bp_make_kv_maps(bp_attn_ctx* c, int kind, uint32_t rows_box, uint32_t d_inn
 }
 
 // (Re)builds the decode tensor maps for the current nw / hpc options.
+static size_t ll_bytes(const bp_attn_ctx* c) {
+  return static_cast<size_t>(c->max_splits) * c->cfg.n_head * BP_LL_STRIDE * sizeof(uint2);
+}
+
 static bool rebuild_decode_maps(bp_attn_ctx* c) {
   c->have_maps = true;
   const uint32_t inner = 16 * c->opt_hpc;
@@ -238,8 +242,10 @@ int bp_attn_create(const bp_attn_config* cfg, bp_attn_ctx** out) {
 
   c->max_splits = bp_decode_max_splits(c);
   BP_CUDA(c, cudaMalloc(&c->partials, static_cast<size_t>(c->max_splits) * cfg->n_head * BP_PART_STRIDE * sizeof(float)));
-  BP_CUDA(c, cudaMalloc(&c->tickets, 64 * sizeof(uint32_t)));
-  BP_CUDA(c, cudaMemset(c->tickets, 0, 64 * sizeof(uint32_t)));
+  BP_CUDA(c, cudaMalloc(&c->ll, ll_bytes(c)));
+  BP_CUDA(c, cudaMalloc(&c->epochs, 64 * sizeof(uint32_t)));
+  BP_CUDA(c, cudaMemset(c->ll, 0, ll_bytes(c)));
+  BP_CUDA(c, cudaMemset(c->epochs, 0, 64 * sizeof(uint32_t)));
   BP_CUDA(c, cudaMalloc(&c->dbg_dev, 64 * sizeof(unsigned long long)));
   BP_CUDA(c, cudaMemset(c->dbg_dev, 0, 64 * sizeof(unsigned long long)));
   BP_CUDA(c, cudaHostAlloc(&c->err_host, sizeof(uint32_t), cudaHostAllocMapped));
@@ -266,7 +272,8 @@ void bp_attn_destroy(bp_attn_ctx* c) {
   cudaFree(c->kv[1]);
   cudaFree(c->rope);
   cudaFree(c->partials);
-  cudaFree(c->tickets);
+  cudaFree(c->ll);
+  cudaFree(c->epochs);
   cudaFree(c->px_epoch);
   cudaFree(c->pf_kv16);
   cudaFree(c->dbg_dev);
@@ -683,6 +690,11 @@ int bp_set_option(bp_attn_ctx* c, const char* name, uint32_t value) {
     if ((value != 1 && value != 2) || c->cfg.n_kv_head % value != 0)
       return fail_config(c, "decode_umma_heads_per_cta must be 1 or 2 and divide n_kv_head");
     c->opt_uhpc = value;
+    // the tags of the in-kernel merge advance per head group: a new grouping starts from a clean slate
+    if (bind_device(c) != BP_OK) return BP_ERR_CUDA;
+    BP_CUDA(c, cudaDeviceSynchronize());
+    BP_CUDA(c, cudaMemset(c->ll, 0, ll_bytes(c)));
+    BP_CUDA(c, cudaMemset(c->epochs, 0, 64 * sizeof(uint32_t)));
   } else if (strcmp(name, "decode_ring") == 0) {
     c->opt_uring = value;
     return BP_OK;
