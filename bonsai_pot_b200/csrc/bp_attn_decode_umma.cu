@@ -24,7 +24,7 @@
 //   fused step   the Q preparation normalises and rotates the raw q first, and the CTAs of
 //                the last split quantise the new token's K / V rows, store them to the cache
 //                and patch them into their last stage (bp_attn_decode_layer);
-//   merge        the CTA of a head group that draws the last ticket merges the splits;
+//   merge        the CTAs of a head group merge its splits themselves, through tagged partials;
 //   exchange     final outputs are also stored into every rank's gathered buffer (peer stores).
 #include "bp_common.cuh"
 #include "bp_ptx.cuh"
@@ -358,6 +358,13 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
     }
   };
   auto prepare_q = [&](uint32_t aw) {  // aw = 0..3: the calling accumulate warp; warp aw takes heads aw, aw + 4, ...
+    // The norm weight and this position's RoPE row are constants: bring them in while the previous
+    // kernel still runs (the RoPE row of a new position is not in L2 yet).
+    if (p.fused && aw == 0) {
+      prefetch_l2(p.w_q + 4 * lane);
+      prefetch_l2(p.rope_row + 4 * lane);
+      prefetch_l2(p.w_k + 4 * lane);
+    }
     pdl_wait();  // q is written by the kernel before this one
     if (p.merge && n_splits > 1) epoch = ld_relaxed_u32(p.epochs + blockIdx.y);  // used in the epilogue
     // lane l holds dims 4l .. 4l+3 of one head: a Q8_0 block is 8 lanes. One 8-byte load, three

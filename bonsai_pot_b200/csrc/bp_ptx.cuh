@@ -73,6 +73,9 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
       ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -199,20 +202,14 @@ __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t nthreads) {
 }
 // A value and its tag as one aligned 8-byte access: a reader that sees the tag sees the value that
 // was stored with it, without a fence on either side. Relaxed gpu-scope accesses are served by L2
-// (never a stale L1 line) and, unlike volatile ones, a thread may have many in flight at once (18
-// volatile loads in a row took 3.9 us on B200, one round trip each).
+// (never a stale L1 line). A thread may have many such loads in flight, as long as their results
+// stay in registers: a load whose result the compiler spills is waited for at once.
 __device__ __forceinline__ void st_tagged(uint2* p, uint32_t value, uint32_t tag) {
   asm volatile("st.relaxed.gpu.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(value), "r"(tag) : "memory");
 }
 __device__ __forceinline__ uint2 ld_tagged(const uint2* p) {
   uint2 r;
-#ifdef BP_LL_WEAK
-  asm volatile("ld.global.cg.v2.u32 {%0, %1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p) : "memory");
-#elif defined(BP_LL_NOCLOB)
-  asm volatile("ld.relaxed.gpu.global.v2.u32 {%0, %1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p));
-#else
   asm volatile("ld.relaxed.gpu.global.v2.u32 {%0, %1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p) : "memory");
-#endif
   return r;
 }
 __device__ __forceinline__ uint32_t ld_relaxed_u32(const uint32_t* p) {

@@ -234,7 +234,13 @@ int bp_set_variant(bp_attn_ctx* ctx, uint32_t variant);
  * CTA) and "decode_heads_per_cta" (KV heads streamed by one CTA; a power of two
  * dividing n_kv_head), "decode_umma_heads_per_cta" (1 or 2, tcgen05 decode) and
  * "prefill_tiles_per_item" (query tiles one prefill work item owns: 1, 2, or 0 =
- * chosen by batch size). Results do not depend on them beyond rounding. */
+ * chosen by batch size). Launch structure: "dependent_launch" (1 = kernels are
+ * launched with programmatic stream serialization, the default), "decode_in_kernel_merge"
+ * (1 = the tcgen05 decode kernel merges its splits itself, the default; 0 = a
+ * second kernel does), "decode_ring" (K stages * 16 + V slots of the tcgen05
+ * decode kernel, 0 = as many as fit). Results do not depend on any of them beyond
+ * rounding. The in-kernel merge keeps per-context state on the device (a tag per
+ * launch): compute calls on one context must not overlap on different streams. */
 int bp_set_option(bp_attn_ctx* ctx, const char* name, uint32_t value);
 /* Development aid: with the option "debug_counters" set to 1 the tcgen05 decode
  * kernel's first CTA records, per warp role (producer, UMMA issuer, softmax,

@@ -476,7 +476,7 @@ def test_host_entry_points_equal_the_device_path():
         load_cache(ctx, sh, case["kv_k"], case["kv_v"], 1, 700)
         out_h = np.zeros(sh.q_dim, dtype=np.float16)
         ctx.decode_step_host(1, case["q"], case["k_new"], case["v_new"], case["w_q"], case["w_k"], 700, out_h)
-        assert ctx.last_launch_count() >= 1  # one fused layer step (the last CTA of a head merges the splits)
+        assert ctx.last_launch_count() >= 1  # one fused layer step (the splits are merged inside the launch)
         got_dev = run_decode(ctx, sh, case, 1)
         assert np.array_equal(out_h.view(np.uint16), got_dev.view(np.uint16))
         m = 48
@@ -634,3 +634,36 @@ def test_prefill_on_a_kv_head_shard(n_head, n_kv_head):
             assert ctx.status() == 0
             ok, max_abs, max_rel = within_tolerance(host(out), host(ref).astype(np.float32))
             assert ok, (n_head, n_kv_head, tiles, max_abs, max_rel)
+
+
+@pytest.mark.parametrize("n_kv_head,ctx_len", [(1, 32768), (2, 20000), (8, 4096), (8, 4100), (8, 16384)])
+def test_decode_merge_of_many_splits(n_kv_head, ctx_len):
+    """The in-kernel merge of the splits (one merging CTA for short launches, all CTAs of a head group for
+    long ones, more than 32 splits on a one-head shard) against the separate combine kernel and the
+    warp-MMA family on the same cache, twice in a row (the second launch must see fresh tags)."""
+    n_head = 4 * n_kv_head
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(ctx_len + n_kv_head)
+    with bp.AttnContext(n_layer=1, n_head=n_head, n_kv_head=n_kv_head, max_seq=ctx_len, n_shards=8 // n_kv_head,
+                        shard=0) as ctx:
+        w = torch.ones(128, dtype=torch.float16, device="cuda")
+        for r0 in range(0, ctx_len, 4096):
+            rows = min(4096, ctx_len - r0)
+            k = torch.randn(rows, n_kv_head * 128, generator=gen, device="cuda").half()
+            v = torch.randn(rows, n_kv_head * 128, generator=gen, device="cuda").half()
+            ctx.dispatch_kv_writeback_fused(0, k, v, w, r0, rows)
+        q = torch.randn(n_head * 128, generator=gen, device="cuda").half()
+        ctx.dispatch_q_norm_rope_fused(q, w, ctx_len - 1, 1)
+        outs = {}
+        for name, variant, merge in (("mma", 3, 1), ("combine", 0, 0), ("in_kernel", 0, 1), ("in_kernel_again", 0, 1)):
+            ctx.set_variant(variant)
+            ctx.set_option("decode_in_kernel_merge", merge)
+            out = torch.full((n_head * 128,), float("nan"), dtype=torch.float16, device="cuda")
+            ctx.dispatch_attention_decode(0, q, out, ctx_len)
+            torch.cuda.synchronize()
+            assert ctx.status() == 0
+            outs[name] = host(out).astype(np.float32)
+        assert np.array_equal(outs["in_kernel"], outs["in_kernel_again"])
+        for name in ("combine", "in_kernel"):
+            ok, max_abs, max_rel = within_tolerance(outs[name], outs["mma"])
+            assert ok, (name, max_abs, max_rel)
