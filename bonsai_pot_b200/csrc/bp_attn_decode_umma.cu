@@ -820,7 +820,11 @@ static uint32_t umma_spp(const bp_attn_ctx* c, uint32_t cur_pos) {
   // that finishes last, so beyond sqrt(15 * stages) splits the merge outgrows what it saves.
   const uint32_t cap = static_cast<uint32_t>(sqrtf(15.0f * static_cast<float>(n_st))) + 1;
   if (ctas > cap) ctas = cap < 8 ? 8 : cap;
-  return (n_st + ctas - 1) / ctas;
+  uint32_t spp = (n_st + ctas - 1) / ctas;
+  // Short launches are merged by one CTA per head group, whose merge polls up to 15 other splits in
+  // one round: 17 or 18 splits of up to 4 stages become at most 16 slightly longer ones.
+  if (spp <= 4 && (n_st + spp - 1) / spp > 16 && (n_st + 15) / 16 <= 4) spp = (n_st + 15) / 16;
+  return spp;
 }
 
 uint32_t bp_decode_umma_splits(const bp_attn_ctx* c, uint32_t cur_pos) {
