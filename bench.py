@@ -394,12 +394,12 @@ def run_ours(args):
         dt_k = time_region(torch, decode_graph, reps, stream) / (reps * N_LAYER)
     algo_bytes_launch = ctx_len * BYTES_PER_TOKEN_LAYER // world
     achieved = algo_bytes_launch / dt_k / 1e9
-    # DRAM traffic per launch: one ncu capture of the decode kernel at ctx 32768 read 75.57 MB against
-    # 75.50 MB of algorithmic bytes; reads grow in proportion to
-    # the tokens streamed, so the capture is scaled by tokens. The split partials (written once, read back
-    # from L2 by the merging CTA) are added as written bytes.
+    # DRAM traffic per launch: one ncu capture of the decode kernel at ctx 32768 read 75.62 MB against
+    # 75.50 MB of algorithmic bytes; reads grow in proportion to the tokens streamed, so the capture is
+    # scaled by tokens. The split partials (tagged pairs, 8 bytes per value, written once and read back
+    # from L2 by the merging warps) are added as written bytes.
     n_splits = ctx.decode_num_splits(pos + 1) if hasattr(ctx, "decode_num_splits") else 18
-    traffic = int(75.57e6 * ctx_len / 32768 / world + n_splits * nh_l * 132 * 4) if args.variant == 0 else None
+    traffic = int(75.62e6 * ctx_len / 32768 / world + n_splits * nh_l * 132 * 8) if args.variant == 0 else None
     roofline = {"bound": "hbm", "kernel": "decode_umma_kernel (splits merged in the kernel through tagged partials)", "achieved": round(achieved, 1),
                 "peak": hbm_peak, "unit": "GB/s", "frac": round(achieved / hbm_peak, 4), "peak_kind": peak_kind,
                 "us_per_launch": round(dt_k * 1e6, 3), "algorithmic_bytes_per_launch": algo_bytes_launch,
