@@ -281,23 +281,23 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
 
   // ---- set-up: barriers, TMEM, zeroed operand tiles, quantised Q ----
   if (threadIdx.x == 0) {
-    // Thread 0 initialises only what the first loads need and requests the first round of the ring
-    // at once, before the CTA-wide set-up barrier: their latency (descriptor fetch + DRAM) is the
-    // longest item on the critical path of a short launch. The other barriers are initialised by
-    // the lanes of warp 2 in parallel.
+    // Thread 0 initialises the first stage's barrier and requests that stage at once: its latency
+    // (descriptor fetch + DRAM) is the longest item on the critical path of a CTA that starts late.
+    // It requests the rest of the first round after the CTA-wide set-up barrier (measured: initialising
+    // all of the ring's barriers and issuing the whole round first held every other warp at that
+    // barrier for 0.9 us). The other barriers are initialised by the lanes of warps 2 and 3.
     abort_s = 0;
-    for (uint32_t s = 0; s < ns; s++) mbar_init(smem_u32(&full_bar[s]), 1);
-    for (uint32_t v = 0; v < nv; v++) mbar_init(smem_u32(&v_full[v]), 1);
+    mbar_init(smem_u32(&full_bar[0]), 1);
     fence_barrier_init();
     prefetch_tensormap(&map_kq);
-    prefetch_tensormap(&map_vq);
     prefetch_tensormap(&map_kd);
     prefetch_tensormap(&map_vd);
-    const uint32_t n_pre = n_iter < ns ? n_iter : ns;
-    for (uint32_t it = 0; it < n_pre; it++) issue_stage(it, it);
-    // a launch whose V tiles all fit at once requests them here too (it should not wait for them);
-    // otherwise the Q K^T issuers request every V tile when its job starts
-    for (uint32_t j = 0; j < v_pre; j++) issue_v(j);
+    issue_stage(0, 0);
+    prefetch_tensormap(&map_vq);
+  } else if (warp == 3) {
+    if (lane >= 1 && lane < ns) mbar_init(smem_u32(&full_bar[lane]), 1);
+    if (lane >= 8 && lane - 8 < nv) mbar_init(smem_u32(&v_full[lane - 8]), 1);
+    fence_barrier_init();
   } else if (warp == 2) {
     if (lane < 4) {
       mbar_init(smem_u32(&s_ready[lane]), 1);
@@ -416,7 +416,16 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
   auto wait = [&](uint64_t* bar, uint32_t parity) { cta_wait(bar, parity, &abort_s, p.err); };
   auto put = [&](uint32_t h, uint32_t d, float v) { put_out(p, h, d, v); };
   if (warp == 0) {
-    // ---------------- TMA producer: the rounds of the ring after the first (requested during set-up) ----------------
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      // the rest of the first round (stage 0 was requested during set-up)
+      const uint32_t n_pre = n_iter < ns ? n_iter : ns;
+      for (uint32_t it = 1; it < n_pre; it++) issue_stage(it, it);
+      // a launch whose V tiles all fit at once requests them here too (it should not wait for them);
+      // otherwise the Q K^T issuers request every V tile when its job starts
+      for (uint32_t j = 0; j < v_pre; j++) issue_v(j);
+    }
+    __syncwarp();
     // Fused step, last split: the whole warp first quantises the new token's K / V rows of this
     // CTA's heads (the arithmetic of kv_writeback_kernel) and stores them to the cache.
     const bool new_row = p.fused && tok_end == p.cur_pos;
