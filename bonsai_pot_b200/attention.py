@@ -119,6 +119,13 @@ class AttnContext:
         arr_f = (C.c_uint64 * max(n, 1))(*[int(p) for p in flag_ptrs])
         self._check(self._lib.bp_set_peer_exchange(self._h, n, arr_o, arr_f))
 
+    def set_prefill_exchange(self, out_ptrs):
+        """Peer exchange of prefill outputs: device addresses (valid in this process) of every rank's
+        gathered buffer [rows][n_shards*n_head*128] f16; an empty list switches it off."""
+        n = len(out_ptrs)
+        arr_o = (C.c_uint64 * max(n, 1))(*[int(p) for p in out_ptrs])
+        self._check(self._lib.bp_set_prefill_exchange(self._h, n, arr_o))
+
     def peer_sync(self, slot=0, stream=None):
         """Meeting of the ranks on the stream: this rank's kernels so far are complete (peer stores
         included), and so are every other rank's up to their matching call."""

@@ -65,7 +65,7 @@ struct UmmaParams {
   // epilogue instead of a collective after the kernel. The stores are complete when the grid is;
   // ranks meet afterwards with bp_peer_sync.
   uint32_t n_px, px_off;
-  __half* px_out[BP_MAX_PEERS];
+  __half* const* px_out;  // in device memory: the parameter block stays small (a larger one costs about 1 % per launch)
   uint32_t merge;       // 1: the CTAs of a head group merge its splits themselves (merge_unit)
   uint2* ll;            // tagged partials [split][head][BP_LL_STRIDE]: (value bits, tag of the launch)
   uint32_t* epochs;     // per head group (grid y): the tag of the last merged launch
@@ -880,7 +880,7 @@ cudaError_t bp_launch_decode_umma(bp_attn_ctx* c, cudaStream_t s, uint32_t layer
   p.dbg = c->dbg_on ? c->dbg_dev : nullptr;
   p.n_px = c->n_px;
   p.px_off = layer * c->cfg.n_shards * c->q_dim + c->cfg.shard * c->q_dim;
-  for (uint32_t r = 0; r < BP_MAX_PEERS; r++) p.px_out[r] = r < c->n_px ? c->px_out[r] : nullptr;
+  p.px_out = c->px_dev;
   p.merge = c->opt_umerge || c->n_px > 0;  // the exchange lives in the in-kernel merge
   p.ll = c->ll;
   p.epochs = c->epochs;

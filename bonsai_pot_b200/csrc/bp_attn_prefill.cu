@@ -65,6 +65,13 @@ struct PrefillParams {
   uint32_t m, n_head, n_kv_head, qpg, n_groups;  // n_groups = ceil(m / (NQ * 128 / qpg))
   unsigned long long* dbg;  // development aid: cycle counters of CTA 0, null in normal use
   float scale_log2;
+  // Peer exchange (n_px > 0): every output vector is also stored into each rank's gathered buffer
+  // (this rank's included), row = token, at column px_col0 + head * 128 of rows px_row_stride wide:
+  // the all-gather of the KV-head shards' outputs by peer stores in the epilogue.
+  // The addresses sit in device memory, not here: a parameter block 64 bytes larger made the kernel
+  // 2 % slower (58.8 against 57.4 us per layer at 2048 tokens), with or without the exchange.
+  uint32_t n_px, px_col0, px_row_stride;
+  __half* const* px_out;
 };
 
 // Physical byte offset of 16-byte unit `u16` (0..15) of row `r` in an operand tile.
@@ -149,7 +156,7 @@ __global__ void __launch_bounds__(256) prefill_expand_kernel(const uint8_t* __re
   *reinterpret_cast<uint4*>(out) = w;
 }
 
-template <uint32_t NQ>
+template <uint32_t NQ, bool PX>  // PX: with the peer exchange in the epilogue (an instance of its own: the plain one pays nothing)
 __global__ void __launch_bounds__(PLayout<NQ>::THREADS, 1)
 prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const PrefillParams p) {
   using L = PLayout<NQ>;
@@ -439,7 +446,12 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                 __half2 h = __floats2half2_rn(__uint_as_float(o[8 * q8 + 2 * k]) * inv_l, __uint_as_float(o[8 * q8 + 2 * k + 1]) * inv_l);
                 w[k] = *reinterpret_cast<uint32_t*>(&h);
               }
-              *reinterpret_cast<uint4*>(dst + 32 * c + 8 * q8) = make_uint4(w[0], w[1], w[2], w[3]);
+              const uint4 w4 = make_uint4(w[0], w[1], w[2], w[3]);
+              *reinterpret_cast<uint4*>(dst + 32 * c + 8 * q8) = w4;
+              if constexpr (PX)
+                for (uint32_t r = 0; r < p.n_px; r++)
+                  *reinterpret_cast<uint4*>(p.px_out[r] + static_cast<size_t>(tok) * p.px_row_stride + p.px_col0 +
+                                          head * BP_HEAD_DIM + 32 * c + 8 * q8) = w4;
             }
           }
         }
@@ -496,15 +508,22 @@ cudaError_t bp_prefill_init(bp_attn_ctx* c) {
                            es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
   }
-  e = cudaFuncSetAttribute(prefill_umma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(PLayout<1>::SMEM));
+  e = cudaFuncSetAttribute(prefill_umma_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(PLayout<1>::SMEM));
   if (e != cudaSuccess) return e;
-  return cudaFuncSetAttribute(prefill_umma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(PLayout<2>::SMEM));
+  e = cudaFuncSetAttribute(prefill_umma_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(PLayout<1>::SMEM));
+  if (e != cudaSuccess) return e;
+  e = cudaFuncSetAttribute(prefill_umma_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(PLayout<2>::SMEM));
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(prefill_umma_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(PLayout<2>::SMEM));
 }
 
 cudaError_t bp_launch_prefill(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, const __half* q,
                               __half* out, uint32_t m, uint32_t* launches) {
   const bool pow2 = (c->qpg & (c->qpg - 1)) == 0 && c->qpg <= BM;
-  if (c->variant == 1 || !c->have_pmaps || !pow2) return bp_launch_scalar_attention(c, s, layer, q, out, m, m, true, launches);
+  if (c->variant == 1 || !c->have_pmaps || !pow2) {
+    if (c->n_ppx != 0) return cudaErrorNotSupported;  // the exchange lives in the tensor-core kernel's epilogue
+    return bp_launch_scalar_attention(c, s, layer, q, out, m, m, true, launches);
+  }
   const uint32_t rows_pad = (m + BN - 1) / BN * BN;
   {
     const uint32_t threads = rows_pad * (c->kv_dim >> 3);
@@ -526,6 +545,10 @@ cudaError_t bp_launch_prefill(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, co
   p.dbg = c->dbg_on ? c->dbg_dev : nullptr;
   p.qpg = c->qpg;
   p.scale_log2 = (1.0f / sqrtf(static_cast<float>(BP_HEAD_DIM))) * 1.4426950408889634f;
+  p.n_px = c->n_ppx;
+  p.px_col0 = c->cfg.shard * c->q_dim;
+  p.px_row_stride = c->cfg.n_shards * c->q_dim;
+  p.px_out = c->ppx_dev;
   const uint32_t tq_tokens = BM / c->qpg;
   const uint32_t sms = static_cast<uint32_t>(c->sm_count);
   // Two query tiles per item keep the tensor core busy during softmax; a batch too small to give
@@ -536,13 +559,19 @@ cudaError_t bp_launch_prefill(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, co
     p.n_groups = groups2;
     const uint32_t n_items = p.n_groups * c->cfg.n_kv_head;
     *launches += 1;
-    return bp_launch(c->opt_pdl != 0, prefill_umma_kernel<2>, dim3(n_items < sms ? n_items : sms), dim3(PLayout<2>::THREADS),
+    if (p.n_px != 0)
+      return bp_launch(c->opt_pdl != 0, prefill_umma_kernel<2, true>, dim3(n_items < sms ? n_items : sms), dim3(PLayout<2>::THREADS),
+                       PLayout<2>::SMEM, s, c->pmap16[0], c->pmap16[1], p);
+    return bp_launch(c->opt_pdl != 0, prefill_umma_kernel<2, false>, dim3(n_items < sms ? n_items : sms), dim3(PLayout<2>::THREADS),
                      PLayout<2>::SMEM, s, c->pmap16[0], c->pmap16[1], p);
   } else {
     p.n_groups = (m + tq_tokens - 1) / tq_tokens;
     const uint32_t n_items = p.n_groups * c->cfg.n_kv_head;
     *launches += 1;
-    return bp_launch(c->opt_pdl != 0, prefill_umma_kernel<1>, dim3(n_items < sms ? n_items : sms), dim3(PLayout<1>::THREADS),
+    if (p.n_px != 0)
+      return bp_launch(c->opt_pdl != 0, prefill_umma_kernel<1, true>, dim3(n_items < sms ? n_items : sms), dim3(PLayout<1>::THREADS),
+                       PLayout<1>::SMEM, s, c->pmap16[0], c->pmap16[1], p);
+    return bp_launch(c->opt_pdl != 0, prefill_umma_kernel<1, false>, dim3(n_items < sms ? n_items : sms), dim3(PLayout<1>::THREADS),
                      PLayout<1>::SMEM, s, c->pmap16[0], c->pmap16[1], p);
   }
 }

@@ -57,8 +57,11 @@ struct bp_attn_ctx {
   // [n_layer][n_shards * q_dim] f16 and meeting counters [64], mapped into this process
   uint32_t n_px;
   __half* px_out[BP_MAX_PEERS];
+  __half** px_dev;     // device copy of px_out, read by the decode kernel
   uint32_t* px_flag[BP_MAX_PEERS];
   uint32_t* px_epoch;  // device: meetings so far, per counter slot [64]
+  uint32_t n_ppx;      // prefill exchange: every rank's gathered prefill buffer [rows][n_shards * q_dim]
+  __half** ppx_dev;    // device: the n_ppx addresses
   uint32_t opt_uring;  // tcgen05 decode: 0 = default ring sizes, else K stages * 16 + V slots
   uint32_t opt_umerge; // tcgen05 decode: merge the splits in the decode kernel (1) or with a second kernel (0)
   uint32_t opt_pdl;  // launch the kernels of a layer with programmatic stream serialization (1) or plainly (0)

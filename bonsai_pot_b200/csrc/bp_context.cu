@@ -272,6 +272,8 @@ void bp_attn_destroy(bp_attn_ctx* c) {
   cudaFree(c->kv[1]);
   cudaFree(c->rope);
   cudaFree(c->partials);
+  cudaFree(c->ppx_dev);
+  cudaFree(c->px_dev);
   cudaFree(c->ll);
   cudaFree(c->epochs);
   cudaFree(c->px_epoch);
@@ -368,7 +370,30 @@ int bp_set_peer_exchange(bp_attn_ctx* c, uint32_t n_ranks, const uint64_t* out_p
     c->px_out[r] = reinterpret_cast<__half*>(static_cast<uintptr_t>(out_ptrs[r]));
     c->px_flag[r] = reinterpret_cast<uint32_t*>(static_cast<uintptr_t>(flag_ptrs[r]));
   }
+  if (!c->px_dev) BP_CUDA(c, cudaMalloc(&c->px_dev, BP_MAX_PEERS * sizeof(__half*)));
+  BP_CUDA(c, cudaDeviceSynchronize());  // no kernel may still read the old addresses
+  BP_CUDA(c, cudaMemcpy(c->px_dev, c->px_out, n_ranks * sizeof(__half*), cudaMemcpyHostToDevice));
   c->n_px = n_ranks;
+  return BP_OK;
+}
+
+int bp_set_prefill_exchange(bp_attn_ctx* c, uint32_t n_ranks, const uint64_t* out_ptrs) {
+  if (int s = enter(c)) return s;
+  if (n_ranks == 0) {
+    c->n_ppx = 0;
+    return BP_OK;
+  }
+  if (!out_ptrs) return fail(c, BP_ERR_NULL, "null pointer argument");
+  if (n_ranks != c->cfg.n_shards || n_ranks > BP_MAX_PEERS)
+    return fail_config(c, "the prefill exchange needs one buffer per shard (n_ranks == n_shards <= 8)");
+  if (!c->have_pmaps || (c->qpg & (c->qpg - 1)) != 0 || c->qpg > 128)
+    return fail_config(c, "the prefill exchange is part of the tensor-core prefill kernel");
+  if (int s = bind_device(c)) return s;
+  if (!c->ppx_dev) BP_CUDA(c, cudaMalloc(&c->ppx_dev, BP_MAX_PEERS * sizeof(__half*)));
+  static_assert(sizeof(__half*) == sizeof(uint64_t), "device addresses are 64-bit");
+  BP_CUDA(c, cudaDeviceSynchronize());  // no kernel may still read the old addresses
+  BP_CUDA(c, cudaMemcpy(c->ppx_dev, out_ptrs, n_ranks * sizeof(uint64_t), cudaMemcpyHostToDevice));
+  c->n_ppx = n_ranks;
   return BP_OK;
 }
 
@@ -397,6 +422,8 @@ int bp_attn_prefill(bp_attn_ctx* c, void* stream, uint32_t layer, const void* q,
   }
   if (m > c->cfg.max_seq) return fail_overflow(c, 0, m, c->cfg.max_seq);
   c->last_launches = 0;
+  if (c->n_ppx != 0 && c->variant == 1)
+    return fail_config(c, "the prefill exchange is part of the tensor-core prefill kernel (variant 0)");
   BP_CUDA(c, bp_launch_prefill(c, static_cast<cudaStream_t>(stream), layer, static_cast<const __half*>(q),
                                static_cast<__half*>(out), m, &c->last_launches));
   return BP_OK;

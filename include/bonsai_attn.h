@@ -134,6 +134,14 @@ int bp_attn_decode_layer(bp_attn_ctx* ctx, void* stream, uint32_t layer, const v
  * exchange off. */
 int bp_set_peer_exchange(bp_attn_ctx* ctx, uint32_t n_ranks, const uint64_t* out_ptrs,
                          const uint64_t* flag_ptrs);
+/* The same for batched prefill: out_ptrs[r] is the device address, valid in
+ * this process, of rank r's gathered prefill output (f16 [rows][n_shards *
+ * n_head * 128], rows >= the largest m passed to bp_attn_prefill). From then
+ * on the tensor-core prefill kernel stores every output vector of its heads
+ * into all ranks' gathered buffers as well (row = token, columns of this
+ * shard). The ranks meet with bp_peer_sync (whose counters come from
+ * bp_set_peer_exchange). n_ranks = 0 switches it off. */
+int bp_set_prefill_exchange(bp_attn_ctx* ctx, uint32_t n_ranks, const uint64_t* out_ptrs);
 /* Meeting point of the ranks, enqueued on `stream`: tells every rank that this
  * rank's kernels up to here have completed (their peer stores included) and
  * waits (bounded; a timeout latches BP_ERR_TIMEOUT) until every rank has said

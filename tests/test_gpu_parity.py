@@ -667,3 +667,45 @@ def test_decode_merge_of_many_splits(n_kv_head, ctx_len):
         for name in ("combine", "in_kernel"):
             ok, max_abs, max_rel = within_tolerance(outs[name], outs["mma"])
             assert ok, (name, max_abs, max_rel)
+
+
+def test_prefill_peer_exchange_of_two_shards_on_one_device():
+    """Two KV-head shards (as two contexts on this device) run batched prefill with the peer exchange
+    on: each 'rank' owns a gathered buffer [m][2 * q_dim], both kernels store their heads' outputs into
+    both buffers, and both buffers must end up as the two local outputs side by side."""
+    m, n_head, n_kv_head = 300, 16, 4
+    q_dim = n_head * 128
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(11)
+    gathered = [torch.full((m, 2 * q_dim), float("nan"), dtype=torch.float16, device="cuda") for _ in range(2)]
+    w = torch.ones(128, dtype=torch.float16, device="cuda")
+    local = []
+    ctxs = [bp.AttnContext(n_layer=1, n_head=n_head, n_kv_head=n_kv_head, max_seq=512, n_shards=2, shard=s)
+            for s in range(2)]
+    try:
+        for s, ctx in enumerate(ctxs):
+            q = torch.randn(m, q_dim, generator=gen, device="cuda").half()
+            k = torch.randn(m, n_kv_head * 128, generator=gen, device="cuda").half()
+            v = torch.randn(m, n_kv_head * 128, generator=gen, device="cuda").half()
+            ctx.dispatch_q_norm_rope_fused(q, w, 0, m)
+            ctx.dispatch_kv_writeback_fused(0, k, v, w, 0, m)
+            ref = torch.zeros(m, q_dim, dtype=torch.float16, device="cuda")
+            ctx.dispatch_attention(0, q, ref, m)  # exchange off: the plain result
+            ctx.set_prefill_exchange([g.data_ptr() for g in gathered])
+            out = torch.zeros(m, q_dim, dtype=torch.float16, device="cuda")
+            ctx.dispatch_attention(0, q, out, m)
+            torch.cuda.synchronize()
+            assert ctx.status() == 0
+            assert torch.equal(out, ref)
+            local.append(out)
+            ctx.set_variant(1)  # the CUDA-core kernel has no exchange: a configuration error, not a silent skip
+            with pytest.raises(bp.errors.ConfigError):
+                ctx.dispatch_attention(0, q, out, m)
+            ctx.set_variant(0)
+            ctx.set_prefill_exchange([])
+        want = torch.cat(local, dim=1)
+        for g in gathered:
+            assert torch.equal(g, want)
+    finally:
+        for ctx in ctxs:
+            ctx.close()
