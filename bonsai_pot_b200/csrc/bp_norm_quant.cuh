@@ -62,15 +62,14 @@ __device__ __forceinline__ void norm_rope_rows(const __half* x, size_t row_strid
 #pragma unroll
   for (int c = 0; c < 4; c++) {
     const float2 cs = __half22float2(rh[c]);  // (cos, sin) of j = dim mod 64
+    // Lower half: x cos - partner sin; upper half: partner sin + x cos. One code path for both:
+    // a - b == a + (-b) and (-p) s == -(p s) hold exactly in IEEE arithmetic, and + commutes.
+    const float sn = lane < 16 ? -cs.y : cs.y;
 #pragma unroll
     for (int r = 0; r < R; r++) {
       const float xn = __fmul_rn(__fmul_rn(raw[r][c], inv_h[r]), wt[c]);
       const float partner = __shfl_xor_sync(NRQ_FULL, xn, 16);
-      if (lane < 16) {
-        out[r].v[c] = __fsub_rn(__fmul_rn(xn, cs.x), __fmul_rn(partner, cs.y));
-      } else {
-        out[r].v[c] = __fadd_rn(__fmul_rn(partner, cs.y), __fmul_rn(xn, cs.x));
-      }
+      out[r].v[c] = __fadd_rn(__fmul_rn(xn, cs.x), __fmul_rn(partner, sn));
     }
   }
 }
