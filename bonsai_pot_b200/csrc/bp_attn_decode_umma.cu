@@ -336,8 +336,8 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
   // In-kernel merge of the splits (merge_unit): 0 none, 1 spread over the CTAs, 2 by one CTA of the head
   // group: the last split when it is as long as the others (with the fused step it has the new row's
   // work on top, finishes last, and its partial never leaves the SM), else the first.
-  // (Evaluated where it is used, in the epilogues: kept in registers from here on, these few values
-  // changed the register allocation of the main loops and cost 3 % at long contexts.)
+  // Evaluated where it is used, in the epilogues, so that nothing of it is held in registers through
+  // the main loops.
   auto merge_plan = [&](uint32_t& mode, bool& is_merger) {
     mode = p.merge && n_splits > 1 ? (n_splits <= 16 && p.tps <= 4 * UT ? 2u : 1u) : 0u;
     const uint32_t last_stages = (p.cur_pos - (n_splits - 1) * p.tps + UT - 1) / UT;
@@ -825,8 +825,8 @@ static uint32_t umma_spp(const bp_attn_ctx* c, uint32_t cur_pos) {
   uint32_t ctas = bp_decode_max_splits(c) / groups;
   if (ctas == 0) ctas = 1;
   // With few KV heads per device (a shard of a multi-GPU run) there are many more SMs than a head
-  // can use well: a job costs about 1 us of streaming, merging a split about 0.07 us in the CTA
-  // that finishes last, so beyond sqrt(15 * stages) splits the merge outgrows what it saves.
+  // can use well: a job costs about 1 us of streaming, merging one more split about 0.07 us at the
+  // end of the launch, so beyond sqrt(15 * stages) splits the merge outgrows what it saves.
   const uint32_t cap = static_cast<uint32_t>(sqrtf(15.0f * static_cast<float>(n_st))) + 1;
   if (ctas > cap) ctas = cap < 8 ? 8 : cap;
   uint32_t spp = (n_st + ctas - 1) / ctas;
