@@ -138,7 +138,8 @@ __device__ __forceinline__ void put_out(const UmmaParams& p, uint32_t h, uint32_
 // value stored with it. The output of a head group is cut into units of 32 elements (one query head
 // x one quarter of the dims), and a unit is merged by one warp that has its own CTA's part at hand
 // and polls the other splits' parts: lane k reads (m, l) of the k-th other split, the weights travel
-// by shuffle, and the loads of a round are all in flight together. Who merges which unit:
+// by shuffle, and the loads of a round are all in flight together. Who merges which unit (the mode is
+// chosen per launch: up to 16 splits of up to 4 stages take mode 2):
 //   mode 2 (up to 16 splits of up to 4 stages: launches bound by latency)  one CTA per head group, a full-length split, merges all units with its
 //           softmax warps; its own partial stays in shared memory, so when it is the last to finish
 //           the merge ends one L2 round trip later. One SM can only keep so many loads in flight:
@@ -218,7 +219,12 @@ __device__ __forceinline__ void merge_unit(const UmmaParams& p, uint32_t lane, u
   put_out(p, h, d, o_run * (1.0f / l_run));
 }
 
-template <uint32_t HPC>
+// MODE: which merge code (see merge_unit) the instance carries. 1: mode 1 only, launched for long
+// launches; 3: both, the mode chosen at run time, launched for short ones. These kernels move by a
+// few percent with the sheer amount of code around their loops; measured on one GPU, per call at
+// ctx 4096 / 32768: both codes in one kernel 8.09 / 20.45 us, one instance per mode 8.29 / 19.90 us.
+// Hence this pairing.
+template <uint32_t HPC, uint32_t MODE>
 __global__ void __launch_bounds__(U_THREADS, 1)
 decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_constant__ CUtensorMap map_kd,
                    const __grid_constant__ CUtensorMap map_vq, const __grid_constant__ CUtensorMap map_vd,
@@ -339,7 +345,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
   // Evaluated where it is used, in the epilogues, so that nothing of it is held in registers through
   // the main loops.
   auto merge_plan = [&](uint32_t& mode, bool& is_merger) {
-    mode = p.merge && n_splits > 1 ? (n_splits <= 16 && p.tps <= 4 * UT ? 2u : 1u) : 0u;
+    mode = p.merge && n_splits > 1 ? (MODE == 1 ? 1u : (n_splits <= 16 && p.tps <= 4 * UT ? 2u : 1u)) : 0u;
     const uint32_t last_stages = (p.cur_pos - (n_splits - 1) * p.tps + UT - 1) / UT;
     const uint32_t merger_split = last_stages == p.tps / UT ? n_splits - 1 : 0;
     is_merger = mode == 2 && split == merger_split;
@@ -728,7 +734,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
         const uint32_t h = (g0 + g) * p.qpg + hq;
         if (n_splits == 1) {
           put(h, dim, acc * (1.0f / l));
-        } else if (merger) {  // stays in the CTA
+        } else if (MODE != 1 && merger) {  // stays in the CTA
           own_part()[(g * 4 + hq) * BP_HEAD_DIM + dim] = acc;
         } else if (merge_mode != 0) {  // tagged, for the CTAs that merge this head's units
           uint2* dst = p.ll + (split * p.n_head + h) * BP_LL_STRIDE;
@@ -744,7 +750,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
         }
       }
     }
-    if (merger && dim == 0) misc->tag = tag;
+    if (MODE != 1 && merger && dim == 0) misc->tag = tag;
     if (merge_mode == 1) {
       // This warp's units: (query head hl, dim quarter `quad`) with (hl * 4 + quad) mod n_splits == split.
 #pragma unroll 1
@@ -767,7 +773,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
   uint32_t merge_mode_end;
   bool merger_end;
   merge_plan(merge_mode_end, merger_end);
-  if (merger_end && warp >= U_FIRST_SM_WARP) {
+  if constexpr (MODE != 1) if (merger_end && warp >= U_FIRST_SM_WARP) {
     __threadfence_block();
     named_bar_sync(MERGE_BAR, 128 * NGRP + 128);  // this CTA's own partial and the tag are in shared memory
     const uint32_t tag = misc->tag;
@@ -799,7 +805,10 @@ uint32_t bp_decode_umma_stage_tokens() { return UT; }
 
 template <uint32_t HPC>
 static cudaError_t umma_attr() {
-  return cudaFuncSetAttribute(decode_umma_kernel<HPC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  cudaError_t e = cudaFuncSetAttribute(decode_umma_kernel<HPC, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(U_SMEM_BUDGET));
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(decode_umma_kernel<HPC, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                               static_cast<int>(U_SMEM_BUDGET));
 }
 
@@ -857,7 +866,12 @@ static cudaError_t launch_umma(bp_attn_ctx* c, cudaStream_t s, UmmaParams& p, ui
   p.nv = spp * HPC < v_cap ? spp * HPC : v_cap;
   const size_t smem = ULayout<HPC>::total(p.nk, p.nv);
   dim3 grid(n_splits, c->cfg.n_kv_head / HPC);
-  return bp_launch(c->opt_pdl != 0, decode_umma_kernel<HPC>, grid, dim3(U_THREADS), smem, s, c->umap_qs[0], c->umap_d[0],
+  // Short launches (up to 16 splits of up to 4 stages) are merged by one CTA per head group, longer
+  // ones by all CTAs of the group.
+  if (n_splits <= 16 && spp <= 4)
+    return bp_launch(c->opt_pdl != 0, decode_umma_kernel<HPC, 3>, grid, dim3(U_THREADS), smem, s, c->umap_qs[0], c->umap_d[0],
+                     c->umap_qs[1], c->umap_d[1], p);
+  return bp_launch(c->opt_pdl != 0, decode_umma_kernel<HPC, 1>, grid, dim3(U_THREADS), smem, s, c->umap_qs[0], c->umap_d[0],
                    c->umap_qs[1], c->umap_d[1], p);
 }
 
