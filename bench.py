@@ -1,18 +1,25 @@
 #!/usr/bin/env python
 """Benchmark of the attention hot path on B200.
 
-Headline workload (`decode_ctx4096_36layers`): one decode token through the
-36-layer decode-attention stack at context 4096 with Qwen3-8B attention shapes
-(32 query heads, 8 KV heads, head_dim 128, Q8_0 KV cache). One step = for each
-layer: Q norm+RoPE, KV write-back of the new token at row 4095, split-KV decode
-attention over 4096 keys. The metric is achieved HBM GB/s = algorithmic cache
-bytes read (2304 B per token per layer) / time.
+Headline workload (`decode_ctx32768_36layers`): one decode token through the
+36-layer decode-attention stack at context 32768 with Qwen3-8B attention shapes
+(32 query heads, 8 KV heads, head_dim 128, Q8_0 KV cache; 2.7 GB of cache). One
+step = for each layer: Q norm+RoPE, KV write-back of the new token at row 32767,
+split-KV decode attention over 32768 keys (one bp_attn_decode_layer call). The
+metric is achieved HBM GB/s = algorithmic cache bytes read (2304 B per token per
+layer) / time.
 
   python bench.py --gpus 1 --steps 50 --warmup 5          # this implementation
   python bench.py --impl reference --steps 3 --warmup 1   # CPU restatement of the reference
 
-With N > 1 ranks (torchrun) the KV heads are sharded over the ranks and the
-per-head outputs are all-gathered with NCCL after every layer (strong scaling).
+With N > 1 ranks (torchrun) the KV heads are sharded over the ranks (strong
+scaling: the same stack, 1/N of the heads per GPU). The all-gather of the head
+outputs happens inside the decode kernel: its epilogue stores every output
+element into every rank's gathered buffer (peer stores over NVLink), its last
+CTA signals the layer's meeting counter on every rank, and the next layer's
+kernel waits for that counter before it ends. `--exchange` selects the other
+forms (a meeting kernel after every layer, one per token, or an NCCL all-gather
+after every layer).
 
 Prints ONE JSON line on rank 0.
 """
@@ -35,6 +42,11 @@ N_LAYER, N_HEAD, N_KV_HEAD, HEAD_DIM = 36, 32, 8, 128
 Q_DIM, KV_DIM = N_HEAD * HEAD_DIM, N_KV_HEAD * HEAD_DIM
 BYTES_PER_TOKEN_LAYER = 2 * (KV_DIM + KV_DIM // 32 * 4)  # 2304: K and V, int8 + f32 block scales
 FALLBACK_HBM_GBS, FALLBACK_TFLOPS = 6650.0, 1590.0
+CPU_SAMPLE_LAYERS = 4
+MIN_TIMED_SECONDS = 0.5
+# DRAM bytes one decode launch at ctx 32768 read under ncu (profiles/decode_umma_kernel_ctx32768.md)
+# against 75.50 MB of algorithmic bytes; reads grow in proportion to the tokens streamed.
+CAPTURED_DRAM_BYTES_CTX32768 = 75.62e6
 
 
 def measured_peaks():
@@ -45,6 +57,10 @@ def measured_peaks():
         return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
     except Exception:
         return FALLBACK_HBM_GBS, FALLBACK_TFLOPS, "fallback"
+
+
+def workload_name(ctx_len):
+    return f"decode_ctx{ctx_len}_{N_LAYER}layers"
 
 
 class ClockSampler:
@@ -97,107 +113,85 @@ class ClockSampler:
 
 
 # ----------------------------------------------------------------------------
-# CPU side: the oracle timed as the baseline / the reference arm.
+# CPU side: the oracle timed as the baseline AND as the reference arm. One
+# function, one set of inputs: both report the same measurement.
 # ----------------------------------------------------------------------------
-def cpu_decode_gbs(ctx_len, n_layers_sample, reps, seed=0):
-    """Times the CPU restatement of attention_split + attention_merge (plus the
-    two small kernels) on `n_layers_sample` layers of the workload, all host
-    threads. Returns (GB/s, seconds per sample, threads)."""
+_CPU = {}
+
+
+def cpu_sample(ctx_len):
+    """One pass of the CPU restatement over CPU_SAMPLE_LAYERS layers of the workload: per layer
+    q_norm_rope, kv_writeback at the last row, attention_split + attention_merge over ctx_len keys.
+    All host cores (the thread count is set explicitly: a launcher's OMP_NUM_THREADS=1 does not apply).
+    Returns (seconds, threads)."""
     import numpy as np
     from bonsai_pot_b200 import synth
     from oracle import oracle as O
-    try:
-        O.lib(native=True)
-        native = True
-    except Exception:
-        native = False
-    sh = O.Shape(n_layer=n_layers_sample, n_head=N_HEAD, n_kv_head=N_KV_HEAD, max_seq=ctx_len)
-    rope = O.rope_table_f16(sh)
-    w = synth.ones_weight()
-    kv_k, kv_v = sh.new_cache(), sh.new_cache()
-    qs, ks, vs = [], [], []
-    for il in range(n_layers_sample):
-        O.quantize_rows(sh, synth.tensor(seed, 1, il, synth.T_K_PAST, (ctx_len - 1, sh.kv_dim)), kv_k, il, 0, ctx_len - 1)
-        O.quantize_rows(sh, synth.tensor(seed, 1, il, synth.T_V_PAST, (ctx_len - 1, sh.kv_dim)), kv_v, il, 0, ctx_len - 1)
-        qs.append(synth.tensor(seed, 1, il, synth.T_Q, (1, sh.q_dim)))
-        ks.append(synth.tensor(seed, 1, il, synth.T_K_NEW, (1, sh.kv_dim)))
-        vs.append(synth.tensor(seed, 1, il, synth.T_V_NEW, (1, sh.kv_dim)))
-    best = None
-    for _ in range(reps):
-        t0 = time.perf_counter()
-        for il in range(n_layers_sample):
-            qn = O.q_norm_rope(sh, qs[il], w, rope, ctx_len - 1, 1, native=native)
-            O.kv_writeback(sh, ks[il], vs[il], w, rope, kv_k, kv_v, il, ctx_len - 1, 1, native=native)
-            O.attn_decode(sh, qn, kv_k, kv_v, il, ctx_len, native=native)
-        dt = time.perf_counter() - t0
-        best = dt if best is None else min(best, dt)
-    gbs = n_layers_sample * ctx_len * BYTES_PER_TOKEN_LAYER / best / 1e9
-    return gbs, best, O.num_threads(native)
+    if "native" not in _CPU:
+        try:
+            O.lib(native=True)
+            _CPU["native"] = True
+        except Exception:
+            _CPU["native"] = False
+        O.set_threads(os.cpu_count() or 1, native=_CPU["native"])
+    native = _CPU["native"]
+    if ctx_len not in _CPU:
+        nl = CPU_SAMPLE_LAYERS
+        sh = O.Shape(n_layer=nl, n_head=N_HEAD, n_kv_head=N_KV_HEAD, max_seq=ctx_len)
+        kv_k, kv_v = sh.new_cache(), sh.new_cache()
+        rng = np.random.default_rng(0)
+        # cache content does not change the CPU time: plain random quants and small positive scales
+        for kv in (kv_k, kv_v):
+            kv[:sh.d_total].view(np.float32)[:] = rng.random(sh.d_total // 4, dtype=np.float32) * 0.03
+            kv[sh.d_total:] = rng.integers(0, 256, size=kv.size - sh.d_total, dtype=np.uint8)
+        q = [synth.tensor(0, 3, il, synth.T_Q, (1, sh.q_dim)) for il in range(nl)]
+        k = [synth.tensor(0, 3, il, synth.T_K_NEW, (1, sh.kv_dim)) for il in range(nl)]
+        v = [synth.tensor(0, 3, il, synth.T_V_NEW, (1, sh.kv_dim)) for il in range(nl)]
+        _CPU[ctx_len] = (sh, kv_k, kv_v, q, k, v, O.rope_table_f16(sh), synth.ones_weight())
+    sh, kv_k, kv_v, q, k, v, rope, w = _CPU[ctx_len]
+    t0 = time.perf_counter()
+    for il in range(sh.n_layer):
+        qn = O.q_norm_rope(sh, q[il], w, rope, ctx_len - 1, 1, native=native)
+        O.kv_writeback(sh, k[il], v[il], w, rope, kv_k, kv_v, il, ctx_len - 1, 1, native=native)
+        O.attn_decode(sh, qn, kv_k, kv_v, il, ctx_len, native=native)
+    return time.perf_counter() - t0, O.num_threads(native)
+
+
+def cpu_gbs(ctx_len, seconds):
+    return CPU_SAMPLE_LAYERS * ctx_len * BYTES_PER_TOKEN_LAYER / seconds / 1e9
+
+
+def cpu_sample_text(ctx_len):
+    return (f"{CPU_SAMPLE_LAYERS} of {N_LAYER} layers of the decode stack at ctx {ctx_len} per step "
+            "(q_norm_rope + kv_writeback + attention_split/merge per layer)")
 
 
 def run_reference(args):
-    """Reference arm: the reference's own engine (Rust + wgpu/Vulkan) cannot be
-    built or run on this machine, so its CPU restatement (the oracle) is timed
-    on the host cores with all threads, on the same workload and metric."""
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    """Reference arm: the reference's own engine (Rust + wgpu/Vulkan) cannot be built or run on this
+    machine, so its CPU restatement (the oracle) is timed on the host cores with all threads, on the
+    same workload and metric. Each step is a bounded sample (CPU_SAMPLE_LAYERS layers)."""
+    if int(os.environ.get("RANK", "0")) != 0:
         return
-    n_sample = 4
-    times = []
-    gbs = 0.0
-    threads = 1
+    times, threads = [], 1
     for i in range(args.warmup + args.steps):
-        g, dt, threads = cpu_decode_gbs(args.ctx, n_sample, 1, seed=0) if i == 0 else cpu_decode_gbs_cached(args.ctx, n_sample)
+        dt, threads = cpu_sample(args.ctx)
         if i >= args.warmup:
             times.append(dt)
     dt = statistics.mean(times)
-    gbs = n_sample * args.ctx * BYTES_PER_TOKEN_LAYER / dt / 1e9
-    sample = f"{n_sample} of {N_LAYER} layers of the decode stack at ctx {args.ctx} per step"
+    gbs = cpu_gbs(args.ctx, dt)
     line = {
         "impl": "reference", "metric": "decode_attn_hbm_gbs", "value": round(gbs, 4), "unit": "GB/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt * 1e3, 3),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"decode_ctx{args.ctx}_{N_LAYER}layers", "n_head": N_HEAD, "n_kv_head": N_KV_HEAD,
+        "config": {"workload": workload_name(args.ctx), "n_head": N_HEAD, "n_kv_head": N_KV_HEAD,
                    "head_dim": HEAD_DIM, "kv_cache": "Q8_0 (int8 + f32 block scales)"},
-        "cpu_baseline": {"value": round(gbs, 4), "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": round(gbs, 4), "unit": "GB/s", "cores": threads, "kind": "port",
+                         "sample": cpu_sample_text(args.ctx)},
         "e2e": {"value": round(gbs, 4), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
         "note": "CPU restatement of the reference's WGSL math (the Rust/wgpu reference itself is unavailable on this box)",
     }
     print(json.dumps(line), flush=True)
-
-
-_CPU_CACHE = {}
-
-
-def cpu_decode_gbs_cached(ctx_len, n_layers_sample):
-    """Same measurement as cpu_decode_gbs without regenerating the inputs."""
-    import numpy as np
-    from bonsai_pot_b200 import synth
-    from oracle import oracle as O
-    key = (ctx_len, n_layers_sample)
-    if key not in _CPU_CACHE:
-        sh = O.Shape(n_layer=n_layers_sample, n_head=N_HEAD, n_kv_head=N_KV_HEAD, max_seq=ctx_len)
-        kv_k, kv_v = sh.new_cache(), sh.new_cache()
-        rng = np.random.default_rng(0)
-        # cache content does not change the CPU time: fill with plain random quants and scales
-        for kv in (kv_k, kv_v):
-            kv[:sh.d_total].view(np.float32)[:] = rng.random(sh.d_total // 4, dtype=np.float32) * 0.03
-            kv[sh.d_total:] = rng.integers(0, 256, size=kv.size - sh.d_total, dtype=np.uint8)
-        q = [O.q_norm_rope(sh, synth.tensor(0, 1, il, synth.T_Q, (1, sh.q_dim)), synth.ones_weight(),
-                           O.rope_table_f16(sh), ctx_len - 1, 1) for il in range(n_layers_sample)]
-        _CPU_CACHE[key] = (sh, kv_k, kv_v, q)
-    sh, kv_k, kv_v, q = _CPU_CACHE[key]
-    try:
-        O.lib(native=True)
-        native = True
-    except Exception:
-        native = False
-    t0 = time.perf_counter()
-    for il in range(n_layers_sample):
-        O.attn_decode(sh, q[il], kv_k, kv_v, il, ctx_len, native=native)
-    dt = time.perf_counter() - t0
-    return n_layers_sample * ctx_len * BYTES_PER_TOKEN_LAYER / dt / 1e9, dt, O.num_threads(native)
 
 
 # ----------------------------------------------------------------------------
@@ -230,15 +224,45 @@ def graphed(torch, fn, stream):
     return g.replay
 
 
-def time_region(torch, fn, steps, stream):
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+def time_blocks(torch, fn, steps, stream, min_seconds=MIN_TIMED_SECONDS, max_blocks=400, n_blocks=None):
+    """Times blocks of exactly `steps` calls of fn each with CUDA events on `stream`, back to back, until
+    the region is at least min_seconds long (the block count comes from a first block, or from
+    n_blocks). Returns (median seconds per block, blocks, seconds of the whole region)."""
+    def block():
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(steps):
+            fn()
+        b.record(stream)
+        return a, b
     torch.cuda.synchronize()
-    start.record(stream)
-    for _ in range(steps):
-        fn()
-    end.record(stream)
+    if n_blocks is None:
+        a, b = block()
+        torch.cuda.synchronize()
+        first = max(a.elapsed_time(b) / 1e3, 1e-6)
+        n_blocks = int(min(max_blocks, max(3, -(-min_seconds // first))))
+    evs = [block() for _ in range(n_blocks)]
     torch.cuda.synchronize()
-    return start.elapsed_time(end) / 1e3  # seconds
+    times = [a.elapsed_time(b) / 1e3 for a, b in evs]
+    return statistics.median(times), n_blocks, sum(times)
+
+
+def make_context(bp, args, n_layer, nh_l, nkv_l, ctx_len, world, rank, device):
+    ctx = bp.AttnContext(n_layer=n_layer, n_head=nh_l, n_kv_head=nkv_l, max_seq=ctx_len, n_shards=world, shard=rank,
+                         device=device, max_prefill=min(ctx_len, 2048))
+    for name, value in (("decode_warps", args.decode_warps), ("decode_heads_per_cta", args.decode_hpc),
+                        ("decode_umma_heads_per_cta", args.decode_uhpc), ("decode_ring", args.decode_ring)):
+        if value:
+            ctx.set_option(name, value)
+    if args.no_pdl:
+        ctx.set_option("dependent_launch", 0)
+    if args.separate_merge:
+        ctx.set_option("decode_in_kernel_merge", 0)
+    if args.l2_promotion:
+        ctx.set_option("tma_l2_promotion", args.l2_promotion)
+    if args.no_v_preload:
+        ctx.set_option("decode_v_preload", 0)
+    return ctx
 
 
 def run_ours(args):
@@ -261,20 +285,7 @@ def run_ours(args):
     ctx_len = args.ctx
     hbm_peak, tflops_peak, peak_kind = measured_peaks()
 
-    ctx = bp.AttnContext(n_layer=N_LAYER, n_head=nh_l, n_kv_head=nkv_l, max_seq=ctx_len, n_shards=world, shard=rank,
-                         device=local_rank)
-    if args.decode_warps:
-        ctx.set_option("decode_warps", args.decode_warps)
-    if args.decode_hpc:
-        ctx.set_option("decode_heads_per_cta", args.decode_hpc)
-    if args.decode_uhpc:
-        ctx.set_option("decode_umma_heads_per_cta", args.decode_uhpc)
-    if args.no_pdl:
-        ctx.set_option("dependent_launch", 0)
-    if args.decode_ring:
-        ctx.set_option("decode_ring", args.decode_ring)
-    if args.separate_merge:
-        ctx.set_option("decode_in_kernel_merge", 0)
+    ctx = make_context(bp, args, N_LAYER, nh_l, nkv_l, ctx_len, world, rank, local_rank)
     gen = torch.Generator(device="cuda")
     gen.manual_seed(1234 + rank)
     fill_cache(ctx, torch, N_LAYER, kv_dim_l, ctx_len - 1, gen)
@@ -287,33 +298,51 @@ def run_ours(args):
     q_work = q_raw.clone()
     out_local = torch.zeros(N_LAYER, q_dim_l, dtype=torch.float16, device="cuda")
     out_full = torch.zeros(N_LAYER, Q_DIM, dtype=torch.float16, device="cuda") if world > 1 else out_local
-    # N > 1: the decode kernel's epilogue stores its heads straight into every rank's gathered buffer (peer
-    # stores over NVLink, buffers from torch's symmetric-memory allocator) and one small kernel per token
-    # waits for all ranks' arrivals. --nccl-gather keeps the plain NCCL all-gather after every layer instead.
-    exchange = "none"
-    if world > 1:
-        exchange = "nccl all-gather per layer"
-        if not args.nccl_gather and not args.separate and args.variant == 0:
-            try:
-                import torch.distributed._symmetric_memory as symm_mem
-                out_full = symm_mem.empty((N_LAYER, Q_DIM), dtype=torch.float16, device=torch.device("cuda", local_rank))
-                px_flags = symm_mem.empty((64,), dtype=torch.int32, device=torch.device("cuda", local_rank))
-                out_full.zero_()
-                px_flags.zero_()
-                h_out = symm_mem.rendezvous(out_full, dist.group.WORLD)
-                h_flag = symm_mem.rendezvous(px_flags, dist.group.WORLD)
-                torch.cuda.synchronize()
-                dist.barrier()
-                ctx.set_peer_exchange(list(h_out.buffer_ptrs), list(h_flag.buffer_ptrs))
-                exchange = "peer stores in the decode epilogue, ranks meet " + ("once per token" if args.sync_per_token else "after every layer")
-            except Exception as e:  # no peer mapping on this box: fall back to NCCL
-                print(f"[bench] symmetric memory unavailable ({type(e).__name__}: {e}); using NCCL all-gather", file=sys.stderr)
-    use_px = exchange.startswith("peer")
+    # N > 1: the gathered buffers and the meeting counters come from torch's symmetric-memory allocator
+    # (peer-mapped over NVLink); the decode kernel stores into every rank's buffer itself.
+    mode = args.exchange if world > 1 else "none"
+    if world > 1 and (args.separate or args.variant != 0) and mode != "nccl":
+        mode = "nccl"  # the exchange lives in the tcgen05 decode kernel
+    if world > 1 and mode != "nccl":
+        try:
+            import torch.distributed._symmetric_memory as symm_mem
+            out_full = symm_mem.empty((N_LAYER, Q_DIM), dtype=torch.float16, device=torch.device("cuda", local_rank))
+            px_flags = symm_mem.empty((64,), dtype=torch.int32, device=torch.device("cuda", local_rank))
+            out_full.zero_()
+            px_flags.zero_()
+            h_out = symm_mem.rendezvous(out_full, dist.group.WORLD)
+            h_flag = symm_mem.rendezvous(px_flags, dist.group.WORLD)
+            torch.cuda.synchronize()
+            dist.barrier()
+            out_ptrs, flag_ptrs = list(h_out.buffer_ptrs), list(h_flag.buffer_ptrs)
+        except Exception as e:  # no peer mapping on this box: fall back to NCCL
+            print(f"[bench] symmetric memory unavailable ({type(e).__name__}: {e}); using NCCL all-gather", file=sys.stderr)
+            mode = "nccl"
+    exchange_text = {
+        "none": "none",
+        "kernel": "peer stores in the decode epilogue; the kernel's last CTA signals, the next layer's kernel waits",
+        "sync-kernel": "peer stores in the decode epilogue; a meeting kernel after every layer",
+        "per-token": "peer stores in the decode epilogue; one meeting kernel per token",
+        "nccl": "nccl all-gather per layer",
+    }[mode]
+    use_px = mode in ("kernel", "sync-kernel", "per-token")
+
+    def exchange_on(on):
+        if not use_px:
+            return
+        if on:
+            ctx.set_peer_exchange(out_ptrs, flag_ptrs)
+            ctx.set_option("peer_signal_in_kernel", 1 if mode == "kernel" else 0)
+            ctx.set_option("peer_wait_in_kernel", 1 if mode == "kernel" else 0)
+        else:
+            ctx.set_peer_exchange([], [])
+    exchange_on(True)
     pos = ctx_len - 1
     stream = torch.cuda.Stream()
     launches_per_step = 0
+    last_slot = (N_LAYER - 1) % 64
 
-    def one_token():
+    def one_token(exchange=True):
         nonlocal launches_per_step
         n = 0
         if args.separate:
@@ -329,13 +358,18 @@ def run_ours(args):
             else:  # the same layer step as one call (bp_attn_decode_layer)
                 ctx.decode_layer(il, q_raw[il], w, k_new[il], v_new[il], w, pos, out_local[il], stream=stream)
                 n += ctx.last_launch_count()
-            if world > 1 and not use_px:
+            if not exchange:
+                continue
+            if mode == "nccl":
                 dist.all_gather_into_tensor(out_full[il], out_local[il])
-            if use_px and not args.sync_per_token:
-                ctx.peer_sync(slot=il, stream=stream)  # the next operation of a decoder consumes this layer's gathered row
+            elif mode == "sync-kernel":
+                ctx.peer_sync(slot=il % 64, stream=stream)  # the next operation of a decoder consumes this layer's gathered row
                 n += 1
-        if use_px and args.sync_per_token:
+        if exchange and mode == "per-token":
             ctx.peer_sync(slot=0, stream=stream)
+            n += 1
+        if exchange and mode == "kernel":
+            ctx.peer_wait(slot=last_slot, stream=stream)  # the last layer's row has no next layer to wait in
             n += 1
         launches_per_step = n
 
@@ -363,26 +397,70 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    def agree(value, op):  # one number for all ranks
+        if world == 1:
+            return value
+        t = torch.tensor([float(value)], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=op)
+        return float(t.item())
+
     with torch.cuda.stream(stream):
         for _ in range(args.warmup):
             graph.replay()
         barrier()
+        # every rank must run the same number of blocks: the ranks wait for one another in every layer
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(args.steps):
+            graph.replay()
+        b.record(stream)
+        torch.cuda.synchronize()
+        first = agree(a.elapsed_time(b) / 1e3, dist.ReduceOp.MAX if world > 1 else None)
+        n_blocks = int(min(400, max(3, -(-MIN_TIMED_SECONDS // max(first, 1e-6)))))
+        barrier()
         sampler = ClockSampler(local_rank)
         if rank == 0:
             sampler.start()
-        dt = time_region(torch, graph.replay, args.steps, stream)
+        dt, n_blocks, region = time_blocks(torch, graph.replay, args.steps, stream, n_blocks=n_blocks)
         barrier()
         clocks = sampler.stop() if rank == 0 else None
-    if world > 1:
-        t = torch.tensor([dt], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dt = float(t.item())
+    dt = agree(dt, dist.ReduceOp.MAX if world > 1 else None)
     sec_per_step = dt / args.steps
     bytes_per_step = N_LAYER * ctx_len * BYTES_PER_TOKEN_LAYER  # whole job, all ranks
     value = bytes_per_step / sec_per_step / 1e9
 
-    # Roofline of the dominant kernel pair (split-KV pass + combine), timed alone
-    # back to back over the 36 layers (340 MB of cache per sweep, larger than L2).
+    # Multi-GPU: what the exchange costs. Compute only = the same stack with the exchange switched off
+    # (no peer stores, no meeting); meeting only = 36 meeting kernels (signal + wait) and nothing else.
+    scaling_detail = None
+    if world > 1 and use_px:
+        exchange_on(False)
+        compute_g = graphed(torch, lambda: one_token(exchange=False), stream)
+        exchange_on(True)
+
+        def meetings():
+            for il in range(N_LAYER):
+                ctx.peer_sync(slot=il % 64, stream=stream)
+        meet_g = graphed(torch, meetings, stream)
+        with torch.cuda.stream(stream):
+            barrier()
+            for _ in range(3):
+                compute_g()
+            t_c, _, _ = time_blocks(torch, compute_g, args.steps, stream, n_blocks=5)
+            barrier()
+            for _ in range(3):
+                meet_g()
+            t_m, _, _ = time_blocks(torch, meet_g, args.steps, stream, n_blocks=5)
+            barrier()
+        t_c, t_m = agree(t_c, dist.ReduceOp.MAX), agree(t_m, dist.ReduceOp.MAX)
+        scaling_detail = {"us_per_layer_with_exchange": round(sec_per_step * 1e6 / N_LAYER, 3),
+                          "us_per_layer_compute_only": round(t_c / args.steps * 1e6 / N_LAYER, 3),
+                          "us_per_meeting_kernel_alone": round(t_m / args.steps * 1e6 / N_LAYER, 3)}
+        del compute_g, meet_g
+
+    # Roofline of the dominant kernel (the decode kernel, splits merged inside it), timed alone back to
+    # back over the 36 layers (each layer's cache is larger than what L2 keeps of it between sweeps).
+    exchange_on(False)
+
     def decode_only():
         for il in range(N_LAYER):
             ctx.dispatch_attention_decode(il, q_work[il], out_local[il], pos + 1, stream=stream)
@@ -390,63 +468,95 @@ def run_ours(args):
     with torch.cuda.stream(stream):
         for _ in range(3):
             decode_graph()
-        reps = max(3, min(args.steps, 20))
-        dt_k = time_region(torch, decode_graph, reps, stream) / (reps * N_LAYER)
+        dt_k, _, _ = time_blocks(torch, decode_graph, 5, stream, n_blocks=5)
+        dt_k /= 5 * N_LAYER
+    exchange_on(True)
     algo_bytes_launch = ctx_len * BYTES_PER_TOKEN_LAYER // world
     achieved = algo_bytes_launch / dt_k / 1e9
-    # DRAM traffic per launch: one ncu capture of the decode kernel at ctx 32768 read 75.62 MB against
-    # 75.50 MB of algorithmic bytes; reads grow in proportion to the tokens streamed, so the capture is
-    # scaled by tokens. The split partials (tagged pairs, 8 bytes per value, written once and read back
-    # from L2 by the merging warps) are added as written bytes.
-    n_splits = ctx.decode_num_splits(pos + 1) if hasattr(ctx, "decode_num_splits") else 18
-    traffic = int(75.62e6 * ctx_len / 32768 / world + n_splits * nh_l * 132 * 8) if args.variant == 0 else None
-    roofline = {"bound": "hbm", "kernel": "decode_umma_kernel (splits merged in the kernel through tagged partials)", "achieved": round(achieved, 1),
-                "peak": hbm_peak, "unit": "GB/s", "frac": round(achieved / hbm_peak, 4), "peak_kind": peak_kind,
-                "us_per_launch": round(dt_k * 1e6, 3), "algorithmic_bytes_per_launch": algo_bytes_launch,
-                "traffic": traffic, "frac_of_8000_spec": round(achieved / 8000.0, 4)}
+    n_splits = ctx.decode_num_splits(pos + 1)
+    # the tagged split partials (8 bytes per value, written once, read back from L2) are added as written bytes
+    traffic = int(CAPTURED_DRAM_BYTES_CTX32768 * ctx_len / 32768 / world + n_splits * nh_l * 132 * 8) if args.variant == 0 else None
+    roofline = {"bound": "hbm", "kernel": "decode_umma_kernel (splits merged in the kernel through tagged partials)",
+                "achieved": round(achieved, 1), "peak": hbm_peak, "unit": "GB/s", "frac": round(achieved / hbm_peak, 4),
+                "peak_kind": peak_kind, "us_per_launch": round(dt_k * 1e6, 3),
+                "algorithmic_bytes_per_launch": algo_bytes_launch, "traffic": traffic,
+                "traffic_source": "dram__bytes_read+write of one ncu capture of this kernel at ctx 32768 "
+                                  "(profiles/decode_umma_kernel_ctx32768.md), scaled by the tokens of a launch",
+                "frac_of_8000_spec": round(achieved / 8000.0, 4), "splits": n_splits}
 
+    mb_step = bytes_per_step / 1e6
     line = {
         "metric": "decode_attn_hbm_gbs", "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(sec_per_step * 1e3, 5), "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "f32 accumulate (int8 cache, f16 tensor-core operands)",
-        "data": "synthetic",
-        "config": {"workload": f"decode_ctx{ctx_len}_{N_LAYER}layers", "n_head": N_HEAD, "n_kv_head": N_KV_HEAD,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(ctx_len), "n_head": N_HEAD, "n_kv_head": N_KV_HEAD,
                    "head_dim": HEAD_DIM, "kv_cache": "Q8_0 (int8 + f32 block scales)", "bytes_per_token_layer": BYTES_PER_TOKEN_LAYER,
-                   "parallelism": f"kv_head_shard{world}" if world > 1 else "single", "exchange": exchange,
-                   "launch": "36 dependent layers in one CUDA graph, " + ("three dispatches per layer" if args.separate else "one bp_attn_decode_layer call per layer"), "l2": "working set 340 MB per step > 126 MB L2",
+                   "arithmetic": "int8 tensor-core products (exact), f32 scales / softmax / accumulation, f16 in and out",
+                   "parallelism": f"kv_head_shard{world}" if world > 1 else "single", "exchange": exchange_text,
+                   "launch": f"{N_LAYER} dependent layers in one CUDA graph, " +
+                             ("three dispatches per layer" if args.separate else "one bp_attn_decode_layer call per layer"),
+                   "l2": f"working set {mb_step:.0f} MB per step > 126 MB L2",
+                   "timing": f"median of {n_blocks} blocks of {args.steps} steps, {region:.2f} s timed",
                    "us_per_layer": round(sec_per_step * 1e6 / N_LAYER, 3)},
-        "roofline": roofline, "gpu_launches": launches_per_step * args.steps,
+        "roofline": roofline, "gpu_launches": launches_per_step * args.steps * n_blocks,
     }
+    if scaling_detail:
+        line["exchange_cost"] = scaling_detail
 
-    if rank == 0 and world == 1:
-        # ---- e2e: host buffers through the C ABI, one call per token ----
-        qh = q_raw.cpu().pin_memory(); kh = k_new.cpu().pin_memory(); vh = v_new.cpu().pin_memory()
-        wh = w.cpu().pin_memory()
-        oh = torch.zeros(N_LAYER, Q_DIM, dtype=torch.float16).pin_memory()
-        def host_token():
-            ctx.decode_token_host(qh.numpy(), kh.numpy(), vh.numpy(), wh.numpy(), wh.numpy(), pos, oh.numpy())
+    # ---- e2e: host buffers through the C ABI, one bp_decode_token_host call per token ----
+    qh = q_raw.cpu().pin_memory(); kh = k_new.cpu().pin_memory(); vh = v_new.cpu().pin_memory()
+    wh = w.cpu().pin_memory()
+    oh = torch.zeros(N_LAYER, q_dim_l, dtype=torch.float16).pin_memory()
+    gh = torch.zeros(N_LAYER, Q_DIM, dtype=torch.float16).pin_memory() if use_px else None
+
+    def host_token():
+        ctx.decode_token_host(qh.numpy(), kh.numpy(), vh.numpy(), wh.numpy(), wh.numpy(), pos, oh.numpy())
+        if use_px:
+            # the gathered rows of all ranks, once every rank's stores have landed
+            with torch.cuda.stream(stream):
+                if mode == "kernel":
+                    ctx.peer_wait(slot=last_slot, stream=stream)
+                else:
+                    ctx.peer_sync(slot=0, stream=stream)
+                gh.copy_(out_full, non_blocking=True)
+            stream.synchronize()
+    if mode != "nccl":  # (the host entry point has no per-layer meeting kernel: the ranks meet once per token)
+        barrier()
         for _ in range(3):
             host_token()
         e_steps = max(5, args.steps)
+        barrier()
         t0 = time.perf_counter()
         for _ in range(e_steps):
             host_token()
-        e_dt = (time.perf_counter() - t0) / e_steps
+        e_dt = agree((time.perf_counter() - t0) / e_steps, dist.ReduceOp.MAX if world > 1 else None)
         line["e2e"] = {"value": round(bytes_per_step / e_dt / 1e9, 2), "unit": "GB/s",
-                       "h2d_bytes_per_step": int(qh.numel() * 2 + kh.numel() * 2 + vh.numel() * 2 + 512),
-                       "d2h_bytes_per_step": int(oh.numel() * 2), "ms_per_step": round(e_dt * 1e3, 4),
-                       "call": "bp_decode_token_host (pinned host activations in, f16 outputs back, one sync per token)"}
+                       "h2d_bytes_per_step": int(qh.numel() * 2 + kh.numel() * 2 + vh.numel() * 2 + 512) * world,
+                       "d2h_bytes_per_step": int(oh.numel() * 2 + (gh.numel() * 2 if gh is not None else 0)) * world,
+                       "ms_per_step": round(e_dt * 1e3, 4),
+                       "call": "bp_decode_token_host (pinned host activations in, f16 outputs back, one sync per token)" +
+                               ("; then the meeting and the gathered rows back to the host, on every rank" if use_px else "")}
+    if rank == 0 and world == 1:
         # ---- the other configurations, briefly ----
         if not args.no_extras:
             line["also"] = extras(torch, bp, stream, hbm_peak, tflops_peak, peak_kind, args)
-        # ---- CPU baseline on this box's cores (bounded sample) ----
+        # ---- CPU baseline on this box's cores (bounded sample; the reference arm runs the same function) ----
         if not args.no_cpu:
             try:
-                g, t, th = cpu_decode_gbs(ctx_len, 4, 3)
-                line["cpu_baseline"] = {"value": round(g, 4), "unit": "GB/s", "cores": th, "kind": "port",
-                                        "sample": f"4 of {N_LAYER} layers at ctx {ctx_len}, best of 3 ({t*1e3:.1f} ms)"}
+                cpu_sample(ctx_len)  # builds the inputs, warms the cores
+                times = []
+                for _ in range(3):
+                    t, th = cpu_sample(ctx_len)
+                    times.append(t)
+                t = statistics.mean(times)
+                line["cpu_baseline"] = {"value": round(cpu_gbs(ctx_len, t), 4), "unit": "GB/s", "cores": th, "kind": "port",
+                                        "sample": cpu_sample_text(ctx_len) + f", mean of 3 ({t*1e3:.1f} ms)"}
             except Exception as e:  # the oracle is optional for the bench
                 line["cpu_baseline"] = {"value": None, "unit": "GB/s", "cores": 0, "kind": "port", "sample": f"failed: {e}"}
+    if world > 1 and not args.no_extras and use_px:
+        pf = prefill_exchange_bench(torch, dist, bp, stream, args, world, rank, local_rank, tflops_peak, peak_kind)
+        if rank == 0:
+            line["also"] = {"prefill_pp2048_sharded": pf}
     if rank == 0:
         line["clocks"] = clocks
         print(json.dumps(line), flush=True)
@@ -490,9 +600,10 @@ def prefill_bench(torch, bp, stream, tflops_peak, peak_kind, pp, nl):
         with torch.cuda.stream(stream):
             for _ in range(3):
                 full_g()
-            reps = 10
-            dt_full = time_region(torch, full_g, reps, stream) / (reps * nl)
-            dt_attn = time_region(torch, attn_g, reps, stream) / (reps * nl)
+            dt_full, _, _ = time_blocks(torch, full_g, 10, stream, n_blocks=5)
+            dt_attn, _, _ = time_blocks(torch, attn_g, 10, stream, n_blocks=5)
+        dt_full /= 10 * nl
+        dt_attn /= 10 * nl
         flops = 8192 * pp * (pp + 1)
         return {"us_per_layer_pass": round(dt_full * 1e6, 2), "us_per_layer_attention": round(dt_attn * 1e6, 2),
                 "tflops_pass": round(flops / dt_full / 1e12, 2), "tflops_attention": round(flops / dt_attn / 1e12, 2),
@@ -500,39 +611,105 @@ def prefill_bench(torch, bp, stream, tflops_peak, peak_kind, pp, nl):
                 "frac_of_2250_spec": round(flops / dt_attn / 1e12 / 2250.0, 4)}
 
 
+def prefill_exchange_bench(torch, dist, bp, stream, args, world, rank, local_rank, tflops_peak, peak_kind):
+    """Batched prefill at pp 2048 on KV-head shards: every rank's kernel stores its heads' outputs into
+    every rank's gathered buffer (bp_set_prefill_exchange), the ranks meet once per layer."""
+    import torch.distributed._symmetric_memory as symm_mem
+    pp, nl = 2048, 4
+    nkv_l, nh_l = N_KV_HEAD // world, N_HEAD // world
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(70 + rank)
+    w = torch.ones(128, dtype=torch.float16, device="cuda")
+    gathered = symm_mem.empty((pp, Q_DIM), dtype=torch.float16, device=torch.device("cuda", local_rank))
+    flags = symm_mem.empty((64,), dtype=torch.int32, device=torch.device("cuda", local_rank))
+    gathered.zero_()
+    flags.zero_()
+    h_g, h_f = symm_mem.rendezvous(gathered, dist.group.WORLD), symm_mem.rendezvous(flags, dist.group.WORLD)
+    torch.cuda.synchronize()
+    dist.barrier()
+    with bp.AttnContext(n_layer=nl, n_head=nh_l, n_kv_head=nkv_l, max_seq=pp, n_shards=world, shard=rank,
+                        device=local_rank) as c:
+        q = torch.randn(nl, pp, nh_l * HEAD_DIM, generator=gen, device="cuda").half()
+        k = torch.randn(nl, pp, nkv_l * HEAD_DIM, generator=gen, device="cuda").half()
+        v = torch.randn(nl, pp, nkv_l * HEAD_DIM, generator=gen, device="cuda").half()
+        o = torch.zeros(nl, pp, nh_l * HEAD_DIM, dtype=torch.float16, device="cuda")
+        for il in range(nl):
+            c.dispatch_q_norm_rope_fused(q[il], w, 0, pp, stream=stream)
+            c.dispatch_kv_writeback_fused(il, k[il], v[il], w, 0, pp, stream=stream)
+        torch.cuda.synchronize()
+
+        def attn(exchange):
+            for il in range(nl):
+                c.dispatch_attention(il, q[il], o[il], pp, stream=stream)
+                if exchange:
+                    c.peer_sync(slot=il, stream=stream)
+        res = {}
+        for name, exchange in (("compute_only", False), ("with_exchange", True)):
+            if exchange:
+                c.set_peer_exchange([0] * world, list(h_f.buffer_ptrs))  # meeting counters only: decode is not run here
+                c.set_prefill_exchange(list(h_g.buffer_ptrs))
+            g = graphed(torch, lambda: attn(exchange), stream)
+            with torch.cuda.stream(stream):
+                dist.barrier()
+                torch.cuda.synchronize()
+                for _ in range(3):
+                    g()
+                dt, _, _ = time_blocks(torch, g, 5, stream, n_blocks=5)
+                dist.barrier()
+                torch.cuda.synchronize()
+            t = torch.tensor([dt / (5 * nl)], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            res[name] = float(t.item())
+            del g
+        if not torch.equal(gathered[:, rank * nh_l * HEAD_DIM:(rank + 1) * nh_l * HEAD_DIM], o[nl - 1]):
+            raise SystemExit("prefill exchange: this rank's columns of the gathered buffer differ from its local output")
+        c.set_prefill_exchange([])
+        c.set_peer_exchange([], [])
+    flops = 8192 * pp * (pp + 1)  # whole job, all ranks
+    return {"us_per_layer_compute_only": round(res["compute_only"] * 1e6, 2),
+            "us_per_layer_with_exchange": round(res["with_exchange"] * 1e6, 2),
+            "tflops_whole_job": round(flops / res["with_exchange"] / 1e12, 2),
+            "frac_of_peak_per_gpu": round(flops / res["with_exchange"] / 1e12 / world / tflops_peak, 4), "peak_kind": peak_kind,
+            "exchange": "peer stores in the prefill epilogue, one meeting kernel per layer"}
+
+
 def extras(torch, bp, stream, hbm_peak, tflops_peak, peak_kind, args):
-    """Long-context decode (ctx 32768) and the prefill pass (pp 512 / 2048) on one GPU."""
+    """The 36-layer decode stack at ctx 4096 (BASELINE config 1) and the prefill pass (pp 512 / 2048) on one GPU."""
     out = {}
     gen = torch.Generator(device="cuda")
     gen.manual_seed(99)
     w = torch.ones(128, dtype=torch.float16, device="cuda")
-    # decode at 32K: 4 layers allocated and swept (302 MB > L2)
-    nl, ctx_len = 4, 32768
-    with bp.AttnContext(n_layer=nl, max_seq=ctx_len) as c:
-        if args.decode_warps:
-            c.set_option("decode_warps", args.decode_warps)
-        if args.decode_hpc:
-            c.set_option("decode_heads_per_cta", args.decode_hpc)
-        if args.decode_uhpc:
-            c.set_option("decode_umma_heads_per_cta", args.decode_uhpc)
-        fill_cache(c, torch, nl, KV_DIM, ctx_len, gen)
-        c.set_variant(args.variant)
-        q = torch.randn(nl, Q_DIM, generator=gen, device="cuda").half()
-        o = torch.zeros(nl, Q_DIM, dtype=torch.float16, device="cuda")
-        sweeps = 9  # one graph = 36 decode calls back to back, like a token of the 36-layer stack
-        def sweep():
-            for _ in range(sweeps):
+    nl, ctx_len = N_LAYER, 4096
+    if args.ctx != ctx_len:
+        with make_context(bp, args, nl, N_HEAD, N_KV_HEAD, ctx_len, 1, 0, torch.cuda.current_device()) as c:
+            fill_cache(c, torch, nl, KV_DIM, ctx_len - 1, gen)
+            c.set_variant(args.variant)
+            q = torch.randn(nl, Q_DIM, generator=gen, device="cuda").half()
+            k = torch.randn(nl, KV_DIM, generator=gen, device="cuda").half()
+            v = torch.randn(nl, KV_DIM, generator=gen, device="cuda").half()
+            o = torch.zeros(nl, Q_DIM, dtype=torch.float16, device="cuda")
+
+            def token():
+                for il in range(nl):
+                    c.decode_layer(il, q[il], w, k[il], v[il], w, ctx_len - 1, o[il], stream=stream)
+
+            def kernel_only():
                 for il in range(nl):
                     c.dispatch_attention_decode(il, q[il], o[il], ctx_len, stream=stream)
-        sweep_g = graphed(torch, sweep, stream)
-        with torch.cuda.stream(stream):
-            for _ in range(3):
-                sweep_g()
-            dt = time_region(torch, sweep_g, 5, stream) / (5 * sweeps * nl)
-        gbs = ctx_len * BYTES_PER_TOKEN_LAYER / dt / 1e9
-        out["decode_ctx32768"] = {"us_per_layer": round(dt * 1e6, 2), "gbs": round(gbs, 1),
-                                  "frac_of_peak": round(gbs / hbm_peak, 4), "peak_kind": peak_kind,
-                                  "frac_of_8000_spec": round(gbs / 8000.0, 4), "splits": c.decode_num_splits(ctx_len)}
+            token_g, kernel_g = graphed(torch, token, stream), graphed(torch, kernel_only, stream)
+            with torch.cuda.stream(stream):
+                for _ in range(3):
+                    token_g()
+                dt, _, _ = time_blocks(torch, token_g, 20, stream, n_blocks=5)
+                dt_k, _, _ = time_blocks(torch, kernel_g, 20, stream, n_blocks=5)
+            dt /= 20 * nl
+            dt_k /= 20 * nl
+            gbs = ctx_len * BYTES_PER_TOKEN_LAYER / dt / 1e9
+            out[workload_name(ctx_len)] = {
+                "us_per_layer": round(dt * 1e6, 3), "gbs": round(gbs, 1), "frac_of_peak": round(gbs / hbm_peak, 4),
+                "peak_kind": peak_kind, "us_per_decode_kernel": round(dt_k * 1e6, 3),
+                "kernel_frac_of_peak": round(ctx_len * BYTES_PER_TOKEN_LAYER / dt_k / 1e9 / hbm_peak, 4),
+                "splits": c.decode_num_splits(ctx_len)}
     for pp in (512, 2048):
         out[f"prefill_pp{pp}"] = prefill_bench(torch, bp, stream, tflops_peak, peak_kind, pp, 4)
     return out
@@ -542,10 +719,10 @@ def main():
     global N_LAYER
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--ctx", type=int, default=4096, help="context length of the decode stack")
+    ap.add_argument("--ctx", type=int, default=32768, help="context length of the decode stack")
     ap.add_argument("--layers", type=int, default=N_LAYER, help="layers of the stack (smaller only for profiler captures)")
     ap.add_argument("--decode-warps", type=int, default=0, help="override the decode kernel's compute warps per CTA")
     ap.add_argument("--decode-hpc", type=int, default=0, help="override the decode kernel's KV heads per CTA")
@@ -553,15 +730,16 @@ def main():
     ap.add_argument("--separate", action="store_true",
                     help="drive a layer with the reference's three dispatches instead of the one-call layer step")
     ap.add_argument("--separate-merge", action="store_true", help="merge the decode splits with a second kernel")
-    ap.add_argument("--sync-per-token", action="store_true",
-                    help="N > 1: the ranks meet once per token instead of after every layer")
-    ap.add_argument("--nccl-gather", action="store_true", help="N > 1: all-gather the head outputs with NCCL after every layer")
+    ap.add_argument("--exchange", default="kernel", choices=["kernel", "sync-kernel", "per-token", "nccl"],
+                    help="N > 1: how the ranks' head outputs are gathered (see the module docstring)")
     ap.add_argument("--decode-ring", type=int, default=0, help="override the decode kernel's ring: K stages * 16 + V slots")
+    ap.add_argument("--l2-promotion", type=int, default=0, help="L2 promotion of the cache tensor maps: 0 = 256 B, 1 = 128 B, 2 = 64 B, 3 = none")
+    ap.add_argument("--no-v-preload", action="store_true", help="request V tiles only when their job starts")
     ap.add_argument("--no-pdl", action="store_true", help="launch the kernels without programmatic dependent launch")
     ap.add_argument("--variant", type=int, default=0, help="decode kernel family (0 = production)")
     ap.add_argument("--prefill-only", type=int, default=0, metavar="PP",
                     help="run only the prefill pass at this prompt length and print its JSON (profiler captures)")
-    ap.add_argument("--no-extras", action="store_true", help="skip the ctx-32768 and prefill side measurements")
+    ap.add_argument("--no-extras", action="store_true", help="skip the ctx-4096 and prefill side measurements")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     N_LAYER = args.layers

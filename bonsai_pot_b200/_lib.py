@@ -95,12 +95,14 @@ SIGNATURES = {
     "bp_set_variant": (_int, [_vp, _u32]),
     "bp_set_option": (_int, [_vp, C.c_char_p, _u32]),
     "bp_debug_counters": (_int, [_vp, C.POINTER(C.c_uint64)]),
+    "bp_debug_hold_sms": (_int, [_vp, _u32, _u32]),
     "bp_last_launch_count": (_u32, [_vp]),
     "bp_decode_num_splits": (_u32, [_vp, _u32]),
     "bp_attn_decode_layer": (_int, [_vp, _vp, _u32, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _vp]),
     "bp_set_peer_exchange": (_int, [_vp, _u32, _vp, _vp]),
     "bp_set_prefill_exchange": (_int, [_vp, _u32, _vp]),
     "bp_peer_sync": (_int, [_vp, _vp, _u32]),
+    "bp_peer_wait": (_int, [_vp, _vp, _u32]),
     "bp_attn_decode_static_scratch": (_int, [_vp, _vp, _vp, _vp, _vp] + [_u32] * 6),
 }
 

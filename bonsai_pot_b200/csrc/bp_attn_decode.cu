@@ -622,21 +622,23 @@ static cudaError_t launch_mma(bp_attn_ctx* c, cudaStream_t s, DecodeParams& p, u
 // rank's counter (system-scope release, after a system fence: the peer stores of the kernels
 // before this one in the stream are complete by then), then waits (bounded, system-scope acquire
 // loads) until its own counter has reached (meetings so far + 1) * ranks. Counters only grow, so a
-// rank that runs ahead cannot confuse a slower one.
+// rank that runs ahead cannot confuse a slower one. With `signal` = 0 the kernel only waits: the
+// decode kernel's last CTA has signalled already (option peer_signal_in_kernel).
 struct PeerFlags {
   uint32_t* f[BP_MAX_PEERS];
 };
 __global__ void __launch_bounds__(32)
-peer_sync_kernel(PeerFlags flags, uint32_t n_ranks, uint32_t rank, uint32_t slot, uint32_t* epochs, uint32_t* err) {
+peer_sync_kernel(PeerFlags flags, uint32_t n_ranks, uint32_t rank, uint32_t slot, uint32_t signal, uint32_t limit,
+                 uint32_t* epochs, uint32_t* err) {
   bp::pdl_wait();
-  if (threadIdx.x < n_ranks) {
+  if (signal && threadIdx.x < n_ranks) {
     __threadfence_system();
     asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(flags.f[threadIdx.x] + slot), "r"(1u) : "memory");
   }
   if (threadIdx.x == 0) {
     const uint32_t target = (epochs[slot] + 1u) * n_ranks;
     bool ok = false;
-    for (uint32_t i = 0; i < (1u << 22) && !ok; i++) {
+    for (uint32_t i = 0; i < limit && !ok; i++) {
       uint32_t v;
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags.f[rank] + slot) : "memory");
       ok = static_cast<int32_t>(v - target) >= 0;
@@ -647,11 +649,11 @@ peer_sync_kernel(PeerFlags flags, uint32_t n_ranks, uint32_t rank, uint32_t slot
   }
 }
 
-cudaError_t bp_launch_peer_sync(bp_attn_ctx* c, cudaStream_t s, uint32_t slot) {
+cudaError_t bp_launch_peer_sync(bp_attn_ctx* c, cudaStream_t s, uint32_t slot, bool signal) {
   PeerFlags f;
   for (uint32_t r = 0; r < BP_MAX_PEERS; r++) f.f[r] = r < c->n_px ? c->px_flag[r] : nullptr;
-  return bp_launch(c->opt_pdl != 0, peer_sync_kernel, dim3(1), dim3(32), 0, s, f, c->n_px, c->cfg.shard, slot, c->px_epoch,
-                   c->err_dev);
+  return bp_launch(c->opt_pdl != 0, peer_sync_kernel, dim3(1), dim3(32), 0, s, f, c->n_px, c->cfg.shard, slot, signal ? 1u : 0u,
+                   c->opt_wait_limit, c->px_epoch, c->err_dev);
 }
 
 // Fused layer step. With the tcgen05 kernel: one launch does the Q norm + RoPE, the new token's
@@ -750,7 +752,13 @@ cudaError_t bp_launch_decode(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, con
 // one array, so two calls that overlap on the GPU (different streams, or
 // different host threads) race on it. Nothing in the array has to be zero on
 // entry: each call overwrites every partial it later reads, and what the
-// previous call left behind is never read.
+// previous call left behind is never read. The arithmetic runs on the plain
+// CUDA-core kernels (attn_scalar_kernel + attn_combine_kernel), not on the
+// tcgen05 kernel of bp_attn_decode, whose scratch protocol needs a context: the
+// results agree within the attention tolerance, not bit for bit, and a call
+// takes several times longer. The per-device address slot below is written
+// without a lock; concurrent first calls from several host threads store the
+// same value.
 // ---------------------------------------------------------------------------
 namespace {
 constexpr uint32_t NOALLOC_MAX_HEADS = 64;
@@ -775,6 +783,13 @@ extern "C" int bp_attn_decode_static_scratch(void* stream, const void* q, const 
   if (cur_pos > max_seq) return BP_ERR_CONTEXT_OVERFLOW;
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) return BP_ERR_CUDA;
+  {
+    // The scratch address belongs to the CURRENT device, so the cache (and with it the stream and
+    // the other buffers) must live there too; a cache on another GPU is refused, not guessed at.
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, kv_k) != cudaSuccess) return BP_ERR_CUDA;
+    if (attr.type == cudaMemoryTypeDevice && attr.device != dev) return BP_ERR_CONFIG;
+  }
   if (!g_noalloc_ptr[dev]) {
     // First call on this device: resolve the array's device address (this does
     // not allocate). Make this first call outside any stream capture.

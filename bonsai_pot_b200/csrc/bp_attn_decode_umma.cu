@@ -40,14 +40,13 @@ constexpr uint32_t UT = 128;                 // tokens per stage = UMMA M
 constexpr uint32_t TILE_B = UT * 128;        // int8 tile of one head and stage: 16 KB
 constexpr uint32_t U_MAX_STAGES = 8;             // upper bound of K stages and of V slots
 constexpr uint32_t NGRP = 4;                      // softmax groups working on different jobs in parallel
-constexpr uint32_t POLL_LIMIT = 1u << 18;         // polling rounds (about 0.2 us each) before the merge gives up
 constexpr uint32_t MERGE_BAR = 8;                 // named barrier: the merger's accumulate and softmax warps
 constexpr uint32_t FIN_BAR = 6;                   // named barrier: softmax warps arrive, accumulate warps wait
 constexpr uint32_t NISS = 2;                     // UMMA issuer warps per kind (QK, PV)
 constexpr uint32_t U_FIRST_SM_WARP = 1 + 2 * NISS;  // warp 0 producer, then the issuers
 constexpr uint32_t U_THREADS = (U_FIRST_SM_WARP + 4 * NGRP + 4) * 32;
 constexpr uint32_t TMEM_COLS = 512;          // per softmax group: D1 (64 columns) and D2 (64 columns)
-constexpr uint32_t WAIT_LIMIT = 1u << 22;
+constexpr uint32_t NO_SLOT = 0xffu;           // px_sig / px_wait: no meeting counter
 constexpr uint32_t U_SMEM_BUDGET = 226 * 1024;  // dynamic shared memory; the static part needs the rest of 227 KB
 
 struct UmmaParams {
@@ -76,6 +75,23 @@ struct UmmaParams {
   float *k_d, *v_d;        // the layer's scale sections
   uint32_t *k_qs, *v_qs;   // the layer's quant sections (as words)
   uint32_t n_kv_head;
+  // Bounds of the waits: polls of an mbarrier (and of a meeting counter), polling rounds of the merge
+  // (about 0.2 us each). When one runs out the CTA stores a code in *err, stops waiting and winds down.
+  uint32_t wait_limit, poll_limit;
+  // Rows from fresh_from on may have been written by a launch that is not certainly complete when
+  // this kernel's prologue runs (dependent launches): stages that hold such rows are requested
+  // only after the dependency wait. UINT32_MAX: every row older than the new token is settled.
+  uint32_t fresh_from;
+  uint32_t v_pre_all;   // 1: the first round of V tiles is requested during set-up, like the K stages
+  // Meeting of the ranks without a kernel of its own. px_sig: the last CTA of this grid to finish
+  // adds one to every rank's counter of that slot (its peer stores are complete by then).
+  // px_wait: CTA (0, 0) waits, bounded, until every rank has signalled that slot (the previous
+  // layer's, whose gathered row a consumer of this kernel's position in the stream would read).
+  // (Slots and rank are bytes of one word and the counters sit behind one pointer: the parameter
+  // block stays small.)
+  uint32_t px_meet;           // px_sig | px_wait << 8 | this rank << 16; slot 0xff = none
+  uint32_t* const* px_tab;    // in device memory: [r] rank r's meeting counters [64], [8] this rank's count of
+                              // finished CTAs per slot, [9] this rank's count of meetings per slot
   unsigned long long* dbg;  // optional cycle counters of CTA (0, 0); null in normal use
 };
 
@@ -117,9 +133,10 @@ __device__ __forceinline__ float f32_unorder(int k) { return __int_as_float(k >=
 
 // Bounded mbarrier wait shared by every role (one copy of the code: the kernel's instruction
 // footprint matters, cold instruction fetches cost more than the waits themselves).
-__device__ __noinline__ void cta_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* err) {
+__device__ __noinline__ void cta_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* err,
+                                     uint32_t limit) {
   if (*abort_flag) return;
-  if (!mbar_wait(smem_u32(bar), parity, WAIT_LIMIT)) {
+  if (!mbar_wait(smem_u32(bar), parity, limit)) {
     *abort_flag = 1;
     atomicExch(err, 3u);
   }
@@ -184,7 +201,7 @@ __device__ __forceinline__ void merge_unit(const UmmaParams& p, uint32_t lane, u
 #pragma unroll
         for (uint32_t k = 0; k < MERGE_W; k++) ok = ok && v[k].y == tag;
         if (__all_sync(FULL, ok)) break;
-        const bool give_up = *abort_flag != 0 || spin >= POLL_LIMIT;
+        const bool give_up = *abort_flag != 0 || spin >= p.poll_limit;
         if (__any_sync(FULL, give_up)) {  // warp-uniform exit: the shuffles below need every lane
           if (*abort_flag == 0) {
             *abort_flag = 1;
@@ -256,7 +273,9 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
   const uint32_t tok_end = min(tok_begin + p.tps, p.cur_pos);
   const uint32_t n_iter = (tok_end - tok_begin + UT - 1) / UT;
   const uint32_t n_jobs = n_iter * HPC;
-  const uint32_t v_pre = n_jobs <= p.nv ? n_jobs : 0;  // V tiles requested during set-up
+  // V tiles requested during set-up: the first round (their slots are empty anyway, and the first
+  // jobs' P V should not wait for a load that starts only when their Q K^T is issued)
+  const uint32_t v_pre = p.v_pre_all ? (n_jobs < p.nv ? n_jobs : p.nv) : (n_jobs <= p.nv ? n_jobs : 0);
 
   const uint32_t ring_b = ns * L::KSTAGE_B + nv * L::VSLOT_B;  // K ring, then V ring: both multiples of 1024
   const uint32_t v_ring = smem_base + ns * L::KSTAGE_B;
@@ -269,9 +288,11 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
     const uint32_t bar = smem_u32(&full_bar[s]);
     const uint32_t stage = smem_base + s * L::KSTAGE_B;
     const int row = static_cast<int>(p.row_base + tok_begin + it * UT);
-    // older rows were written by earlier steps; the row of the newest token by the kernel before this
-    // one (fused step: by this CTA, which patches it into the stage after the load)
-    if (!p.fused && tok_begin + (it + 1) * UT >= p.cur_pos) pdl_wait();
+    // Older rows were written by launches that have long completed; rows from fresh_from on (the
+    // newest token's, when a separate kernel wrote it just before this one) only by the time the
+    // dependency wait returns. In the fused step this CTA writes the newest row itself and patches
+    // it into the stage after the load.
+    if (tok_begin + (it + 1) * UT > p.fresh_from) pdl_wait();
     mbar_arrive_expect_tx(bar, L::KSTAGE_B);
     tma_load_2d(stage + HPC * TILE_B, &map_kd, bar, static_cast<int>(g0 * 16), row);
     tma_load_2d(stage + HPC * TILE_B + L::SCALE_B, &map_vd, bar, static_cast<int>(g0 * 16), row);
@@ -419,7 +440,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
   // sees the same head (w % HPC). Each group owns one D1, one D2 and one P'
   // buffer; its k-th job (k = j / NGRP) completes phase k of its barriers.
   // A wait that degrades to a no-op once any warp of the CTA has timed out.
-  auto wait = [&](uint64_t* bar, uint32_t parity) { cta_wait(bar, parity, &abort_s, p.err); };
+  auto wait = [&](uint64_t* bar, uint32_t parity) { cta_wait(bar, parity, &abort_s, p.err, p.wait_limit); };
   auto put = [&](uint32_t h, uint32_t d, float v) { put_out(p, h, d, v); };
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -499,6 +520,24 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&patched_v));
+    }
+    // Consumer side of the previous layer's meeting: one thread of the grid, idle by now, waits until
+    // every rank has signalled that slot (all ranks' stores into this rank's gathered row have landed).
+    const uint32_t px_wait = (p.px_meet >> 8) & 0xffu;
+    if (px_wait != NO_SLOT && blockIdx.x == 0 && blockIdx.y == 0 && lane == 0) {
+      pdl_wait();  // the meeting count was advanced by an earlier kernel
+      uint32_t* epoch = p.px_tab[9] + px_wait;
+      const uint32_t* flag = p.px_tab[(p.px_meet >> 16) & 0xffu] + px_wait;
+      const uint32_t target = (*epoch + 1u) * p.n_px;
+      bool ok = false;
+      for (uint32_t i = 0; i < p.wait_limit && !ok; i++) {
+        uint32_t v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        ok = static_cast<int32_t>(v - target) >= 0;
+        if (!ok) __nanosleep(64);
+      }
+      if (!ok) atomicExch(p.err, 6u);
+      *epoch += 1u;
     }
   } else if (warp < 1 + NISS) {
     // ---------------- QK issuers: S^T[token][(block, byte row, head)] = K tile x Q^T ----------------
@@ -791,6 +830,18 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem, TMEM_COLS);
+  // Producer side of this layer's meeting: every CTA's stores (peer stores included) are ordered
+  // before its count by a system fence; the CTA that counts last tells every rank.
+  const uint32_t px_sig = p.px_meet & 0xffu;
+  if (px_sig != NO_SLOT && threadIdx.x == 0) {
+    __threadfence_system();
+    uint32_t* done = p.px_tab[8] + px_sig;
+    if (atomicAdd(done, 1u) == gridDim.x * gridDim.y - 1) {
+      *done = 0;  // for the next launch on this slot, which starts after this grid
+      for (uint32_t r = 0; r < p.n_px; r++)
+        asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.px_tab[r] + px_sig), "r"(1u) : "memory");
+    }
+  }
   if (p.dbg != nullptr && threadIdx.x == 0) {  // development aid: span of the launch in ns
     unsigned long long t_exit_ns;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_exit_ns));
@@ -812,10 +863,20 @@ static cudaError_t umma_attr() {
                               static_cast<int>(U_SMEM_BUDGET));
 }
 
-cudaError_t bp_decode_umma_init(bp_attn_ctx*) {
+cudaError_t bp_decode_umma_init(bp_attn_ctx* c) {
   cudaError_t e = umma_attr<1>();
   if (e != cudaSuccess) return e;
-  return umma_attr<2>();
+  e = umma_attr<2>();
+  if (e != cudaSuccess) return e;
+  // The in-kernel merge makes the CTAs of a head group wait for one another, so a launch may never
+  // have more CTAs than the device holds at once: ask the runtime instead of assuming one per SM.
+  int per_sm = 0;
+  e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_umma_kernel<1, 1>, static_cast<int>(U_THREADS),
+                                                    static_cast<size_t>(U_SMEM_BUDGET));
+  if (e != cudaSuccess) return e;
+  if (per_sm < 1) return cudaErrorLaunchOutOfResources;
+  c->umma_resident = static_cast<uint32_t>(per_sm) * static_cast<uint32_t>(c->sm_count);
+  return cudaSuccess;
 }
 
 // K stages and V slots that fit: equal numbers (a K stage is busy for a load latency plus the short
@@ -831,7 +892,8 @@ static uint32_t umma_max_stages() {
 static uint32_t umma_spp(const bp_attn_ctx* c, uint32_t cur_pos) {
   const uint32_t n_st = (cur_pos + UT - 1) / UT;
   const uint32_t groups = c->cfg.n_kv_head / c->opt_uhpc;
-  uint32_t ctas = bp_decode_max_splits(c) / groups;
+  const uint32_t budget = c->umma_resident < bp_decode_max_splits(c) ? c->umma_resident : bp_decode_max_splits(c);
+  uint32_t ctas = budget / groups;
   if (ctas == 0) ctas = 1;
   // With few KV heads per device (a shard of a multi-GPU run) there are many more SMs than a head
   // can use well: a job costs about 1 us of streaming, merging one more split about 0.07 us at the
@@ -895,7 +957,18 @@ cudaError_t bp_launch_decode_umma(bp_attn_ctx* c, cudaStream_t s, uint32_t layer
   p.n_px = c->n_px;
   p.px_off = layer * c->cfg.n_shards * c->q_dim + c->cfg.shard * c->q_dim;
   p.px_out = c->px_dev;
-  p.merge = c->opt_umerge || c->n_px > 0;  // the exchange lives in the in-kernel merge
+  // The in-kernel merge makes CTAs wait for one another: all of them must be resident at once,
+  // which only a caller with the device to itself can promise (option exclusive_device). The
+  // exchange lives in the in-kernel merge.
+  p.merge = (c->opt_umerge && c->opt_exclusive) || c->n_px > 0;
+  p.wait_limit = c->opt_wait_limit;
+  p.poll_limit = c->opt_poll_limit;
+  p.v_pre_all = c->opt_vpre;
+  p.fresh_from = bp_fresh_from(c, layer);
+  const uint32_t px_sig = c->n_px > 0 && c->opt_px_signal ? layer % 64 : NO_SLOT;
+  const uint32_t px_wait = c->n_px > 0 && c->opt_px_wait && layer > 0 ? (layer - 1) % 64 : NO_SLOT;
+  p.px_meet = px_sig | px_wait << 8 | c->cfg.shard << 16;
+  p.px_tab = c->pxf_dev;
   p.ll = c->ll;
   p.epochs = c->epochs;
   p.fused = fs != nullptr ? 1u : 0u;
@@ -918,5 +991,7 @@ cudaError_t bp_launch_decode_umma(bp_attn_ctx* c, cudaStream_t s, uint32_t layer
     p.v_qs = reinterpret_cast<uint32_t*>(c->kv[1] + bp_qs_off(c, layer));
   }
   *n_splits_out = p.merge ? 1 : n_splits;  // nothing left to merge for the caller
+  if (fs != nullptr) bp_note_row_write(c, layer, cur_pos - 1);
+  bp_note_sm_launch(c, n_splits * (c->cfg.n_kv_head / c->opt_uhpc));
   return c->opt_uhpc == 2 ? launch_umma<2>(c, s, p, spp, n_splits) : launch_umma<1>(c, s, p, spp, n_splits);
 }

@@ -43,7 +43,6 @@ constexpr unsigned FULL = 0xffffffffu;
 constexpr float NEG_BIG = -1e30f;
 constexpr uint32_t BM = 128, BN = 64;             // query rows per tile, keys per tile
 constexpr uint32_t P_TMEM_COLS = 512;            // S_A, S_B, O_A, O_B: 128 columns each
-constexpr uint32_t P_WAIT_LIMIT = 1u << 22;
 constexpr uint32_t OPER_B = 2 * 16384;           // one f16 operand tile: 2 chunks of [128 rows][128 B]
 constexpr uint32_t KV_SLOTS = 4;
 constexpr uint32_t KV_TILE_B = 2 * 8192;          // one f16 K or V tile: 2 chunks of [64 keys][128 B]
@@ -65,6 +64,7 @@ struct PrefillParams {
   uint32_t m, n_head, n_kv_head, qpg, n_groups;  // n_groups = ceil(m / (NQ * 128 / qpg))
   unsigned long long* dbg;  // development aid: cycle counters of CTA 0, null in normal use
   float scale_log2;
+  uint32_t wait_limit;      // polls of an mbarrier before the CTA gives up and winds down
   // Peer exchange (n_px > 0): every output vector is also stored into each rank's gathered buffer
   // (this rank's included), row = token, at column px_col0 + head * 128 of rows px_row_stride wide:
   // the all-gather of the KV-head shards' outputs by peer stores in the epilogue.
@@ -208,7 +208,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   auto waitx = [&](uint64_t* bar, uint32_t parity, int slot) {
     if (abort_s) return;
     const long long t0 = dbg_on ? clock64() : 0;
-    if (!mbar_wait(smem_u32(bar), parity, P_WAIT_LIMIT)) {
+    if (!mbar_wait(smem_u32(bar), parity, p.wait_limit)) {
       abort_s = 1;
       atomicExch(p.err, 5u);
     }
@@ -545,6 +545,7 @@ cudaError_t bp_launch_prefill(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, co
   p.dbg = c->dbg_on ? c->dbg_dev : nullptr;
   p.qpg = c->qpg;
   p.scale_log2 = (1.0f / sqrtf(static_cast<float>(BP_HEAD_DIM))) * 1.4426950408889634f;
+  p.wait_limit = c->opt_wait_limit;
   p.n_px = c->n_ppx;
   p.px_col0 = c->cfg.shard * c->q_dim;
   p.px_row_stride = c->cfg.n_shards * c->q_dim;
@@ -559,6 +560,7 @@ cudaError_t bp_launch_prefill(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, co
     p.n_groups = groups2;
     const uint32_t n_items = p.n_groups * c->cfg.n_kv_head;
     *launches += 1;
+    bp_note_sm_launch(c, n_items < sms ? n_items : sms);
     if (p.n_px != 0)
       return bp_launch(c->opt_pdl != 0, prefill_umma_kernel<2, true>, dim3(n_items < sms ? n_items : sms), dim3(PLayout<2>::THREADS),
                        PLayout<2>::SMEM, s, c->pmap16[0], c->pmap16[1], p);
@@ -568,6 +570,7 @@ cudaError_t bp_launch_prefill(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, co
     p.n_groups = (m + tq_tokens - 1) / tq_tokens;
     const uint32_t n_items = p.n_groups * c->cfg.n_kv_head;
     *launches += 1;
+    bp_note_sm_launch(c, n_items < sms ? n_items : sms);
     if (p.n_px != 0)
       return bp_launch(c->opt_pdl != 0, prefill_umma_kernel<1, true>, dim3(n_items < sms ? n_items : sms), dim3(PLayout<1>::THREADS),
                        PLayout<1>::SMEM, s, c->pmap16[0], c->pmap16[1], p);

@@ -66,6 +66,24 @@ struct bp_attn_ctx {
   uint32_t opt_umerge; // tcgen05 decode: merge the splits in the decode kernel (1) or with a second kernel (0)
   uint32_t opt_pdl;  // launch the kernels of a layer with programmatic stream serialization (1) or plainly (0)
   uint32_t opt_pf_nq; // prefill: query tiles per work item (1 or 2), 0 = by batch size
+  uint32_t opt_wait_limit;  // polls of an mbarrier / a meeting counter before a kernel gives up (BP_ERR_TIMEOUT)
+  uint32_t opt_poll_limit;  // polling rounds of the in-kernel merge before it gives up
+  uint32_t opt_exclusive;   // 1: the caller's kernels have the device to themselves (all CTAs of a launch are co-resident)
+  uint32_t umma_resident;   // tcgen05 decode: CTAs the device holds at once (occupancy query), the bound of a launch whose CTAs wait for one another
+  uint32_t opt_vpre;        // tcgen05 decode: request the first round of V tiles during set-up
+  uint32_t opt_l2promo;     // L2 promotion of the cache tensor maps: 0 = 256 B, 1 = 128 B, 2 = 64 B, 3 = none
+  uint32_t opt_px_signal;   // peer exchange: the decode kernel's last CTA signals the meeting counter of its layer itself
+  uint32_t opt_px_wait;     // peer exchange: the decode kernel of layer L waits for the meeting of layer L - 1
+  uint32_t** pxf_dev;       // device copy of px_flag, read by the decode kernel
+  uint32_t* px_done;        // device: CTAs of the current launch that have finished, per counter slot [64]
+  // Dependent launches let a kernel's prologue run before earlier kernels have completed. A decode
+  // kernel may request cache rows that early only when the launch that wrote them is certainly
+  // complete: sm_seq counts the CTAs of kernels that hold a whole SM each; row_mark[layer] is its
+  // value after the last launch that wrote rows of that layer, row_from[layer] the first row such
+  // a recent launch wrote.
+  uint64_t sm_seq;
+  uint64_t* row_mark;
+  uint32_t* row_from;
   uint32_t last_launches;
   int status;  // latched device-lost status, BP_OK otherwise
   bp_error_detail detail;
@@ -113,8 +131,15 @@ cudaError_t bp_launch_decode(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, con
                              __half* out, uint32_t cur_pos, uint32_t* launches);
 cudaError_t bp_launch_prefill(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, const __half* q,
                               __half* out, uint32_t m, uint32_t* launches);
-// Meeting of the ranks of the peer exchange on counter `slot` (< 64): signal all, wait (bounded) for all.
-cudaError_t bp_launch_peer_sync(bp_attn_ctx* c, cudaStream_t s, uint32_t slot);
+// Meeting of the ranks of the peer exchange on counter `slot` (< 64): signal all (unless the decode
+// kernel did), wait (bounded) for all.
+cudaError_t bp_launch_peer_sync(bp_attn_ctx* c, cudaStream_t s, uint32_t slot, bool signal);
+// Book-keeping of the rule above. A launch that wrote rows [row0, ...) of `layer`; a launch of
+// `ctas` CTAs that hold one SM each; the first row of `layer` a reader must not request before
+// its dependency wait (UINT32_MAX: none).
+void bp_note_row_write(bp_attn_ctx* c, uint32_t layer, uint32_t row0);
+void bp_note_sm_launch(bp_attn_ctx* c, uint32_t ctas);
+uint32_t bp_fresh_from(const bp_attn_ctx* c, uint32_t layer);
 uint32_t bp_decode_splits(const bp_attn_ctx* c, uint32_t cur_pos);
 uint32_t bp_decode_max_splits(const bp_attn_ctx* c);
 

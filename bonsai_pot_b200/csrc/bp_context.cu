@@ -69,11 +69,24 @@ int fail_cuda(bp_attn_ctx* c, cudaError_t e, const char* where) {
     if (e_ != cudaSuccess) return fail_cuda(c, e_, #call); \
   } while (0)
 
-// Every entry point starts here (check_device, src/model.rs:1733-1741).
+// Every compute entry point starts here (check_device, src/model.rs:1733-1741). A kernel whose
+// bounded wait gave up has stored a code in the context's error word (mapped host memory): that
+// latches BP_ERR_TIMEOUT, sticky like a lost device, because the merge tags and meeting counters on
+// the device are undefined from then on.
 int enter(bp_attn_ctx* c) {
   if (!c) return BP_ERR_NULL;
+  if (c->status == BP_OK && c->err_host && *static_cast<volatile uint32_t*>(c->err_host) != 0) c->status = BP_ERR_TIMEOUT;
+  if (c->status == BP_ERR_TIMEOUT)
+    return fail(c, BP_ERR_TIMEOUT, "a bounded device-side wait gave up: context is unusable, snapshot it if needed and create a new one");
   if (c->status != BP_OK) return fail(c, c->status, "device lost: context is unusable, create a new one");
   return BP_OK;
+}
+
+// Entry of the calls that only copy the cache out (export, snapshot capture, introspection): they
+// still work after a timeout, whose damage is confined to the scratch state of the kernels.
+int enter_io(bp_attn_ctx* c) {
+  const int s = enter(c);
+  return s == BP_ERR_TIMEOUT ? BP_OK : s;
 }
 
 int bind_device(bp_attn_ctx* c) {
@@ -105,6 +118,25 @@ encode_tiled_fn get_encode() {
 
 }  // namespace
 
+void bp_note_sm_launch(bp_attn_ctx* c, uint32_t ctas) { c->sm_seq += ctas; }
+
+// Launches that hold an SM each and lie between a write and a read bound how far the reader's
+// prologue can run ahead of the writer: with more than two devices' worth of such CTAs in between,
+// the writer's grid has retired before the reader's first CTA finds a free SM.
+static bool recent_write(const bp_attn_ctx* c, uint32_t layer) {
+  return c->opt_pdl != 0 && c->sm_seq - c->row_mark[layer] < 2ull * static_cast<uint64_t>(c->sm_count);
+}
+
+void bp_note_row_write(bp_attn_ctx* c, uint32_t layer, uint32_t row0) {
+  if (recent_write(c, layer) && c->row_from[layer] < row0) row0 = c->row_from[layer];
+  c->row_from[layer] = row0;
+  c->row_mark[layer] = c->sm_seq;
+}
+
+uint32_t bp_fresh_from(const bp_attn_ctx* c, uint32_t layer) {
+  return recent_write(c, layer) ? c->row_from[layer] : UINT32_MAX;
+}
+
 void* bp_tensor_map_encoder() {
   static encode_tiled_fn encode = get_encode();
   return reinterpret_cast<void*>(encode);
@@ -117,6 +149,10 @@ bool bp_make_kv_maps(bp_attn_ctx* c, int kind, uint32_t rows_box, uint32_t d_inn
                      CUtensorMap* map_qs, CUtensorMap* map_d) {
   static encode_tiled_fn encode = get_encode();
   if (!encode) return false;
+  const CUtensorMapL2promotion promo = c->opt_l2promo == 1   ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B
+                                       : c->opt_l2promo == 2 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
+                                       : c->opt_l2promo == 3 ? CU_TENSOR_MAP_L2_PROMOTION_NONE
+                                                             : CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
   const cuuint64_t rows = static_cast<cuuint64_t>(c->cfg.n_layer) * c->cfg.max_seq;
   {
     cuuint64_t dims[3] = {128, c->cfg.n_kv_head, rows};
@@ -124,7 +160,7 @@ bool bp_make_kv_maps(bp_attn_ctx* c, int kind, uint32_t rows_box, uint32_t d_inn
     cuuint32_t box[3] = {128, 1, rows_box};
     cuuint32_t es[3] = {1, 1, 1};
     if (encode(map_qs, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, c->kv[kind] + c->d_total, dims, strides, box, es,
-               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promo,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return false;
   }
@@ -136,7 +172,7 @@ bool bp_make_kv_maps(bp_attn_ctx* c, int kind, uint32_t rows_box, uint32_t d_inn
     cuuint32_t es[2] = {1, 1};
     if (encode(map_d, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, c->kv[kind], dims, strides, box, es,
                CU_TENSOR_MAP_INTERLEAVE_NONE, d_swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
-               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+               promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return false;
   }
   return true;
@@ -158,6 +194,22 @@ static bool rebuild_decode_maps(bp_attn_ctx* c) {
     c->have_umaps = bp_make_kv_maps(c, kind, bp_decode_umma_stage_tokens(), 16 * c->opt_uhpc, false,
                                     &c->umap_qs[kind], &c->umap_d[kind]);
   return c->have_maps;
+}
+
+// Test aid: a CTA that asks for nearly all of an SM's shared memory, so that no tcgen05 decode or
+// prefill CTA fits beside it, and leaves after a fixed time (bounded: at most 0.1 s).
+constexpr int HOLD_SMEM = 200 * 1024;
+__global__ void __launch_bounds__(32) hold_sm_kernel(unsigned long long ns) {
+  extern __shared__ uint8_t hold_smem[];
+  if (threadIdx.x == 0) {
+    unsigned long long t0, t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    hold_smem[0] = 1;
+    do {
+      __nanosleep(1000);
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    } while (t - t0 < ns && t - t0 < 100000000ull);
+  }
 }
 
 extern "C" {
@@ -257,6 +309,14 @@ int bp_attn_create(const bp_attn_config* cfg, bp_attn_ctx** out) {
   c->opt_pdl = 1;
   c->opt_umerge = 1;
   c->opt_uhpc = 1;  // one KV head per CTA measured faster than two at every context length tried
+  c->opt_wait_limit = 1u << 22;
+  c->opt_poll_limit = 1u << 18;
+  c->opt_exclusive = 1;
+  c->opt_vpre = 1;
+  c->sm_seq = 1ull << 32;  // nothing written yet counts as written long ago
+  c->row_mark = static_cast<uint64_t*>(calloc(cfg->n_layer, sizeof(uint64_t)));
+  c->row_from = static_cast<uint32_t*>(calloc(cfg->n_layer, sizeof(uint32_t)));
+  if (!c->row_mark || !c->row_from) return fail(c, BP_ERR_CUDA, "out of host memory");
   if (!rebuild_decode_maps(c)) return fail(c, BP_ERR_CUDA, "cuTensorMapEncodeTiled failed for the KV cache");
   BP_CUDA(c, bp_decode_init(c));
   BP_CUDA(c, bp_decode_umma_init(c));
@@ -277,6 +337,10 @@ void bp_attn_destroy(bp_attn_ctx* c) {
   cudaFree(c->ll);
   cudaFree(c->epochs);
   cudaFree(c->px_epoch);
+  cudaFree(c->pxf_dev);
+  cudaFree(c->px_done);
+  free(c->row_mark);
+  free(c->row_from);
   cudaFree(c->pf_kv16);
   cudaFree(c->dbg_dev);
   if (c->err_host) cudaFreeHost(c->err_host);
@@ -321,6 +385,8 @@ int bp_attn_decode(bp_attn_ctx* c, void* stream, uint32_t layer, const void* q, 
   if (layer >= c->cfg.n_layer) return fail_config(c, "layer index out of range");
   if (cur_pos == 0) return fail_config(c, "decode attention needs at least one key (cur_pos >= 1)");
   if (cur_pos > c->cfg.max_seq) return fail_overflow(c, cur_pos - 1, 1, c->cfg.max_seq);
+  if (c->n_px != 0 && !bp_use_umma(c))
+    return fail_config(c, "the peer exchange is part of the tcgen05 decode kernel (variant 0)");
   c->last_launches = 0;
   BP_CUDA(c, bp_launch_decode(c, static_cast<cudaStream_t>(stream), layer, static_cast<const __half*>(q),
                               static_cast<__half*>(out), cur_pos, &c->last_launches));
@@ -336,6 +402,8 @@ int bp_attn_decode_layer(bp_attn_ctx* c, void* stream, uint32_t layer, const voi
   if (!q_raw || !w_q_norm || !k_cur || !v_cur || !w_k_norm || !out) return fail(c, BP_ERR_NULL, "null pointer argument");
   if (layer >= c->cfg.n_layer) return fail_config(c, "layer index out of range");
   if (static_cast<uint64_t>(pos) + 1 > c->cfg.max_seq) return fail_overflow(c, pos, 1, c->cfg.max_seq);
+  if (c->n_px != 0 && !bp_use_umma(c))
+    return fail_config(c, "the peer exchange is part of the tcgen05 decode kernel (variant 0)");
   __half* qr = static_cast<__half*>(q_roped);
   if (qr == nullptr && !(c->variant == 0 && bp_use_umma(c))) {
     // the separate kernels rotate q in place: give them the context's staging row
@@ -371,8 +439,20 @@ int bp_set_peer_exchange(bp_attn_ctx* c, uint32_t n_ranks, const uint64_t* out_p
     c->px_flag[r] = reinterpret_cast<uint32_t*>(static_cast<uintptr_t>(flag_ptrs[r]));
   }
   if (!c->px_dev) BP_CUDA(c, cudaMalloc(&c->px_dev, BP_MAX_PEERS * sizeof(__half*)));
+  if (!c->pxf_dev) BP_CUDA(c, cudaMalloc(&c->pxf_dev, (BP_MAX_PEERS + 2) * sizeof(uint32_t*)));
+  if (!c->px_done) {
+    BP_CUDA(c, cudaMalloc(&c->px_done, 64 * sizeof(uint32_t)));
+    BP_CUDA(c, cudaMemset(c->px_done, 0, 64 * sizeof(uint32_t)));
+  }
   BP_CUDA(c, cudaDeviceSynchronize());  // no kernel may still read the old addresses
   BP_CUDA(c, cudaMemcpy(c->px_dev, c->px_out, n_ranks * sizeof(__half*), cudaMemcpyHostToDevice));
+  {  // the decode kernel's table: every rank's counters, then this rank's two book-keeping arrays
+    uint32_t* tab[BP_MAX_PEERS + 2] = {};
+    for (uint32_t r = 0; r < n_ranks; r++) tab[r] = c->px_flag[r];
+    tab[BP_MAX_PEERS] = c->px_done;
+    tab[BP_MAX_PEERS + 1] = c->px_epoch;
+    BP_CUDA(c, cudaMemcpy(c->pxf_dev, tab, sizeof tab, cudaMemcpyHostToDevice));
+  }
   c->n_px = n_ranks;
   return BP_OK;
 }
@@ -397,13 +477,16 @@ int bp_set_prefill_exchange(bp_attn_ctx* c, uint32_t n_ranks, const uint64_t* ou
   return BP_OK;
 }
 
-int bp_peer_sync(bp_attn_ctx* c, void* stream, uint32_t slot) {
+static int peer_meet(bp_attn_ctx* c, void* stream, uint32_t slot, bool signal) {
   if (int s = enter(c)) return s;
   if (c->n_px == 0) return fail_config(c, "no peer exchange is set");
   if (slot >= 64) return fail_config(c, "peer sync slot must be below 64");
-  BP_CUDA(c, bp_launch_peer_sync(c, static_cast<cudaStream_t>(stream), slot));
+  BP_CUDA(c, bp_launch_peer_sync(c, static_cast<cudaStream_t>(stream), slot, signal));
   return BP_OK;
 }
+
+int bp_peer_sync(bp_attn_ctx* c, void* stream, uint32_t slot) { return peer_meet(c, stream, slot, true); }
+int bp_peer_wait(bp_attn_ctx* c, void* stream, uint32_t slot) { return peer_meet(c, stream, slot, false); }
 
 uint32_t bp_attn_max_prefill(const bp_attn_ctx* c) {
   if (!c) return 0;
@@ -486,7 +569,7 @@ static int layer_host(bp_attn_ctx* c, uint32_t layer, const void* q, const void*
   BP_CUDA(c, cudaMemcpyAsync(out, c->stage_out, qb, cudaMemcpyDeviceToHost, st));
   BP_CUDA(c, cudaStreamSynchronize(st));
   c->last_launches = launches;
-  if (*c->err_host) return fail(c, BP_ERR_TIMEOUT, "a bounded device-side wait gave up");
+  if (*c->err_host) return enter(c);  // latches BP_ERR_TIMEOUT
   return BP_OK;
 }
 
@@ -532,7 +615,7 @@ int bp_decode_token_host(bp_attn_ctx* c, const void* q, const void* k, const voi
   BP_CUDA(c, cudaMemcpyAsync(out, c->stage_out, qb, cudaMemcpyDeviceToHost, st));
   BP_CUDA(c, cudaStreamSynchronize(st));
   c->last_launches = launches;
-  if (*c->err_host) return fail(c, BP_ERR_TIMEOUT, "a bounded device-side wait gave up");
+  if (*c->err_host) return enter(c);  // latches BP_ERR_TIMEOUT
   return BP_OK;
 }
 
@@ -545,7 +628,7 @@ int bp_prefill_layer_host(bp_attn_ctx* c, uint32_t layer, const void* q, const v
 // Cache sections and snapshots.
 // ---------------------------------------------------------------------------
 static int kv_copy(bp_attn_ctx* c, uint32_t kind, uint32_t layer, uint32_t sect, uint32_t pos, void* host, bool to_host) {
-  if (int s = enter(c)) return s;
+  if (int s = to_host ? enter_io(c) : enter(c)) return s;
   if (!host && pos) return fail(c, BP_ERR_NULL, "null pointer argument");
   if (kind > 1 || sect > 1) return fail_config(c, "kind and sect must be 0 or 1");
   if (layer >= c->cfg.n_layer) return fail_config(c, "layer index out of range");
@@ -599,7 +682,7 @@ static cudaError_t shard_copy(void* host_row0, size_t pitch, size_t col, uint8_t
 }
 
 int bp_snapshot_capture(bp_attn_ctx* c, uint32_t pos, void* blob, uint64_t blob_bytes) {
-  if (int s = enter(c)) return s;
+  if (int s = enter_io(c)) return s;
   if (!blob) return fail(c, BP_ERR_NULL, "null pointer argument");
   if (pos > c->cfg.max_seq) return fail_overflow(c, 0, pos, c->cfg.max_seq);
   if (blob_bytes < bp_snapshot_size(c, pos)) return fail_config(c, "snapshot buffer is too small");
@@ -663,7 +746,7 @@ int bp_ctx_status(const bp_attn_ctx* c) {
   if (!c) return BP_ERR_NULL;
   if (c->status != BP_OK) return c->status;
   // Meaningful once the stream that ran the kernels has been synchronised.
-  if (c->err_host && *c->err_host) return BP_ERR_TIMEOUT;
+  if (c->err_host && *static_cast<volatile uint32_t*>(c->err_host)) return BP_ERR_TIMEOUT;
   return BP_OK;
 }
 
@@ -683,7 +766,7 @@ uint64_t bp_kv_buffer_bytes(const bp_attn_ctx* c) { return c ? c->kv_bytes : 0; 
 const void* bp_rope_device_ptr(const bp_attn_ctx* c) { return c ? c->rope : nullptr; }
 
 int bp_rope_table_copy(bp_attn_ctx* c, void* host_f16) {
-  if (int s = enter(c)) return s;
+  if (int s = enter_io(c)) return s;
   if (!host_f16) return fail(c, BP_ERR_NULL, "null pointer argument");
   if (int s = bind_device(c)) return s;
   BP_CUDA(c, cudaMemcpy(host_f16, c->rope, static_cast<size_t>(c->cfg.max_seq) * BP_HEAD_DIM * 2, cudaMemcpyDeviceToHost));
@@ -731,6 +814,31 @@ int bp_set_option(bp_attn_ctx* c, const char* name, uint32_t value) {
   } else if (strcmp(name, "dependent_launch") == 0) {
     c->opt_pdl = value != 0;
     return BP_OK;
+  } else if (strcmp(name, "wait_limit") == 0) {
+    if (value == 0) return fail_config(c, "wait_limit must be > 0");
+    c->opt_wait_limit = value;
+    return BP_OK;
+  } else if (strcmp(name, "merge_poll_limit") == 0) {
+    if (value == 0) return fail_config(c, "merge_poll_limit must be > 0");
+    c->opt_poll_limit = value;
+    return BP_OK;
+  } else if (strcmp(name, "exclusive_device") == 0) {
+    if (value == 0 && c->n_px != 0)
+      return fail_config(c, "the peer exchange lives in the in-kernel merge, which needs the device to itself");
+    c->opt_exclusive = value != 0;
+    return BP_OK;
+  } else if (strcmp(name, "decode_v_preload") == 0) {
+    c->opt_vpre = value != 0;
+    return BP_OK;
+  } else if (strcmp(name, "peer_signal_in_kernel") == 0) {
+    c->opt_px_signal = value != 0;
+    return BP_OK;
+  } else if (strcmp(name, "peer_wait_in_kernel") == 0) {
+    c->opt_px_wait = value != 0;
+    return BP_OK;
+  } else if (strcmp(name, "tma_l2_promotion") == 0) {
+    if (value > 3) return fail_config(c, "tma_l2_promotion must be 0 (256 B), 1 (128 B), 2 (64 B) or 3 (none)");
+    c->opt_l2promo = value;
   } else if (strcmp(name, "prefill_tiles_per_item") == 0) {
     if (value > 2) return fail_config(c, "prefill_tiles_per_item must be 0 (by batch size), 1 or 2");
     c->opt_pf_nq = value;
@@ -745,11 +853,25 @@ int bp_set_option(bp_attn_ctx* c, const char* name, uint32_t value) {
 }
 
 int bp_debug_counters(bp_attn_ctx* c, uint64_t* out64) {
-  if (int s = enter(c)) return s;
+  if (int s = enter_io(c)) return s;
   if (!out64) return fail(c, BP_ERR_NULL, "null pointer argument");
   if (int s = bind_device(c)) return s;
   BP_CUDA(c, cudaMemcpy(out64, c->dbg_dev, 64 * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
   return BP_OK;
+}
+
+int bp_debug_hold_sms(void* stream, uint32_t n_ctas, uint32_t microseconds) {
+  if (n_ctas == 0 || n_ctas > 1024 || microseconds > 100000) return BP_ERR_CONFIG;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return BP_ERR_CUDA;
+  if (!attr_set[dev]) {
+    if (cudaFuncSetAttribute(hold_sm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, HOLD_SMEM) != cudaSuccess)
+      return BP_ERR_CUDA;
+    attr_set[dev] = true;
+  }
+  hold_sm_kernel<<<n_ctas, 32, HOLD_SMEM, static_cast<cudaStream_t>(stream)>>>(static_cast<unsigned long long>(microseconds) * 1000ull);
+  return cudaGetLastError() == cudaSuccess ? BP_OK : BP_ERR_CUDA;
 }
 
 uint32_t bp_last_launch_count(const bp_attn_ctx* c) { return c ? c->last_launches : 0; }

@@ -143,6 +143,7 @@ cudaError_t bp_launch_kv_writeback(bp_attn_ctx* c, cudaStream_t s, uint32_t laye
                                    const __half* v, const __half* w, uint32_t pos_base, uint32_t m,
                                    uint32_t* launches) {
   *launches += 1;
+  bp_note_row_write(c, layer, pos_base);
   if (static_cast<uint64_t>(m) * c->cfg.n_kv_head >= 4096 && c->cfg.n_kv_head % 2 == 0)
     return launch_kv<2>(c, s, layer, k, v, w, pos_base, m);
   return launch_kv<1>(c, s, layer, k, v, w, pos_base, m);

@@ -150,6 +150,18 @@ int bp_set_prefill_exchange(bp_attn_ctx* ctx, uint32_t n_ranks, const uint64_t* 
  * = layer mod 64 when the next operation consumes that layer's gathered row,
  * or once per token when nothing in between does. */
 int bp_peer_sync(bp_attn_ctx* ctx, void* stream, uint32_t slot);
+/* The waiting half of bp_peer_sync alone, for use with the option
+ * "peer_signal_in_kernel" = 1: then the last CTA of every tcgen05 decode launch
+ * signals slot (layer mod 64) to all ranks itself, right after its peer stores,
+ * and no kernel of its own is needed on the producer side. The consumer of a
+ * gathered row waits for its slot before reading it: with bp_peer_wait on the
+ * stream, or, with the option "peer_wait_in_kernel" = 1, inside the decode
+ * kernel of the next layer (layer L waits for slot (L - 1) mod 64 before it
+ * ends, standing in for the operation that would consume that row; the last
+ * layer's slot is left to bp_peer_wait). Every signalled slot must be waited
+ * for exactly once, by either means, before it is signalled again. Bounded; a
+ * timeout latches BP_ERR_TIMEOUT. No counterpart in the reference. */
+int bp_peer_wait(bp_attn_ctx* ctx, void* stream, uint32_t slot);
 
 /* `dispatch_attention(.., pos = 0, m_tokens = m, is_prefill = true)`
  * (src/forward.rs:501-532, params src/model.rs:195-210, kernel
@@ -246,33 +258,60 @@ int bp_set_variant(bp_attn_ctx* ctx, uint32_t variant);
  * launched with programmatic stream serialization, the default), "decode_in_kernel_merge"
  * (1 = the tcgen05 decode kernel merges its splits itself, the default; 0 = a
  * second kernel does), "decode_ring" (K stages * 16 + V slots of the tcgen05
- * decode kernel, 0 = as many as fit). Results do not depend on any of them beyond
- * rounding. The in-kernel merge keeps per-context state on the device (a tag per
- * launch): compute calls on one context must not overlap on different streams. */
+ * decode kernel, 0 = as many as fit), "decode_v_preload" (1 = the first round of
+ * V tiles is requested during set-up, the default), "tma_l2_promotion" (0 = 256 B,
+ * the default, 1 = 128 B, 2 = 64 B, 3 = none). Results do not depend on any of
+ * them beyond rounding. The in-kernel merge keeps per-context state on the device
+ * (a tag per launch): compute calls on one context must not overlap on different
+ * streams.
+ * Co-residency: with the in-kernel merge the CTAs of a head group wait (bounded)
+ * for one another's partials, which is only correct when every CTA of the launch
+ * is resident at once. The grid is sized from the runtime's occupancy figure for
+ * an otherwise idle device; a caller whose other work (another stream, another
+ * process through MPS, a green context) may hold SMs while decode runs must set
+ * "exclusive_device" = 0: the splits are then merged by a second kernel that
+ * waits for nobody. Left at 1 on a shared device, a launch whose CTAs cannot all
+ * start ends in BP_ERR_TIMEOUT after "merge_poll_limit" polling rounds (default
+ * 2^18, about 0.2 us each). The peer exchange needs "exclusive_device" = 1.
+ * Bounds of the device-side waits: "wait_limit" (polls of an mbarrier or of a
+ * meeting counter before a kernel gives up, default 2^22) and "merge_poll_limit".
+ * Peer exchange: "peer_signal_in_kernel", "peer_wait_in_kernel" (see bp_peer_wait). */
 int bp_set_option(bp_attn_ctx* ctx, const char* name, uint32_t value);
 /* Development aid: with the option "debug_counters" set to 1 the tcgen05 decode
  * kernel's first CTA records, per warp role (producer, UMMA issuer, softmax,
  * accumulate), its cycles in the main loop and in each kind of wait; this call
  * synchronises and copies the 64 counters (8 per role) to the host. */
 int bp_debug_counters(bp_attn_ctx* ctx, uint64_t* out64);
+/* Test aid: occupies `n_ctas` SMs (one CTA each, holding nearly all of the SM's
+ * shared memory so that no tcgen05 CTA fits beside it) for `microseconds`
+ * (at most 100000) on `stream`, then leaves. Used to test decode under
+ * co-tenancy ("exclusive_device" = 0) without a second process. */
+int bp_debug_hold_sms(void* stream, uint32_t n_ctas, uint32_t microseconds);
 /* Number of kernels the last compute call launched. */
 uint32_t bp_last_launch_count(const bp_attn_ctx* ctx);
 /* Number of split-KV partitions `bp_attn_decode` uses at `cur_pos`. */
 uint32_t bp_decode_num_splits(const bp_attn_ctx* ctx, uint32_t cur_pos);
 
-/* No counterpart in the reference. Decode attention (the same result as
- * bp_attn_decode) for callers that cannot allocate device memory where they
- * call it - a host whose allocator owns all of the GPU, a plugin inside someone
- * else's process, a no-allocation region of a serving loop. It takes no
- * context: the caller passes the query, the two whole cache buffers in the
- * reference layout (d-section then qs-section, see bp_kv_device_ptr) and the
- * output, and the split-KV scratch is a fixed array inside the library image
- * (about 1.1 MB on every GPU that loads the library, held until exit). The call
- * itself allocates nothing. Limits: n_head <= 64 (BP_ERR_CONFIG beyond that;
- * use bp_attn_decode), head_dim 128. The first call on a device looks up the
- * array's device address; make that call before any stream capture. All calls
- * share the one array: calls that overlap on the GPU race, so keep them on one
- * stream. Nothing has to be cleared between calls. Asynchronous on `stream`. */
+/* No counterpart in the reference. Decode attention for callers that cannot
+ * allocate device memory where they call it - a host whose allocator owns all
+ * of the GPU, a plugin inside someone else's process, a no-allocation region of
+ * a serving loop. It takes no context: the caller passes the query, the two
+ * whole cache buffers in the reference layout (d-section then qs-section, see
+ * bp_kv_device_ptr) and the output, and the split-KV scratch is a fixed array
+ * inside the library image (about 1.1 MB on every GPU that loads the library,
+ * held until exit). After the first call on a device the call allocates
+ * nothing (the first one makes the CUDA runtime load the library's device code
+ * and looks up the array's device address; make it before any stream capture).
+ * It runs the plain CUDA-core kernels, not the tcgen05 kernel of
+ * bp_attn_decode: its result agrees with bp_attn_decode's within the attention
+ * tolerance (|x - ref| <= 2e-3 + 1e-2 |ref|), not bit for bit, and a call is
+ * several times slower (DESIGN.md gives the measured times). Limits: n_head <=
+ * 64 (BP_ERR_CONFIG beyond that; use bp_attn_decode), head_dim 128, at most 32
+ * splits (longer contexts get longer splits). The CURRENT device must be the one
+ * that holds the cache, the other buffers and the stream (a cache on another
+ * device gives BP_ERR_CONFIG). All calls share the one array: calls that overlap
+ * on the GPU race, so keep them on one stream. Nothing has to be cleared
+ * between calls. Asynchronous on `stream`. */
 int bp_attn_decode_static_scratch(void* stream, const void* q, const void* kv_k, const void* kv_v, void* out,
                                   uint32_t n_layer, uint32_t max_seq, uint32_t n_head, uint32_t n_kv_head,
                                   uint32_t layer, uint32_t cur_pos);

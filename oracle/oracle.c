@@ -518,6 +518,18 @@ void orc_attn_exact(const uint16_t* q, const uint8_t* kv_k, const uint8_t* kv_v,
   }
 }
 
+/* Number of OpenMP threads the parallel loops above use from now on (n >= 1). A
+ * launcher may export OMP_NUM_THREADS=1 for its children; the timed CPU baseline
+ * sets the count it wants explicitly. No-op in a build without OpenMP. */
+void orc_set_threads(int n) {
+#ifdef _OPENMP
+  extern void omp_set_num_threads(int);
+  if (n >= 1) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 int orc_num_threads(void) {
 #ifdef _OPENMP
   extern int omp_get_max_threads(void);

@@ -65,6 +65,7 @@ def _load(native: bool = False) -> C.CDLL:
         "orc_attn_prefill": (None, [_u16p, _u8p, _u8p, _u16p] + [_u32] * 6),
         "orc_attn_exact": (None, [_u16p, _u8p, _u8p, _f32p] + [_u32] * 7),
         "orc_num_threads": (_int, []),
+        "orc_set_threads": (None, [_int]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)
@@ -193,6 +194,11 @@ def attn_exact(sh, q, kv_k, kv_v, layer, m, key_base):
 
 def num_threads(native=False):
     return lib(native).orc_num_threads()
+
+
+def set_threads(n, native=False):
+    """Thread count of the OpenMP loops from now on (a launcher's OMP_NUM_THREADS=1 does not bind the baseline)."""
+    lib(native).orc_set_threads(int(n))
 
 
 # ------------------------------------------------------------- numpy twin ----

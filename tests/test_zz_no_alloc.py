@@ -7,7 +7,11 @@ library image. The test calls it through the C ABI twice in a row, with
 different key counts so that the second call finds the first call's leftovers in
 the shared scratch, and checks each result against the context-based
 bp_attn_decode on the same cache, within the tolerance the other attention tests
-use. It also checks the size limit. This file sorts last on purpose."""
+use. A second test walks the split-count edges (a single split, which writes
+the output directly; the step to two splits; the cap of 32 splits beyond 8192
+keys) and a model with 8 query heads per KV head and 64 query heads, the
+largest the fixed scratch holds. Both check the size limits. This file sorts
+last on purpose."""
 import numpy as np
 import pytest
 
@@ -51,3 +55,32 @@ def test_static_scratch_decode_matches_context_decode_twice_in_a_row():
         assert lib.bp_attn_decode_static_scratch(stream, q.data_ptr(), ctx.kv_device_ptr(0), ctx.kv_device_ptr(1),
                                                  got.data_ptr(), 2, 4096, 32, 8, 0, 4097) == 2
         assert lib.bp_attn_decode_static_scratch(stream, None, None, None, None, 2, 4096, 32, 8, 0, 1) == 7
+
+
+def test_static_scratch_split_edges_and_other_head_ratio():
+    """cur_pos 1, 256 (one split: no scratch at all), 257 (two), 8193 and 12000 (the 32-split cap:
+    splits grow instead) on 64 query heads over 8 KV heads, against bp_attn_decode and the exact softmax."""
+    lib = _lib.load()
+    sh = O.Shape(n_layer=1, n_head=64, n_kv_head=8, max_seq=12288)
+    case = build_decode_case(sh, seed=3, cfg_id=1, layer=0, n_past=11999)
+    with bp.AttnContext(n_layer=1, n_head=64, n_kv_head=8, max_seq=12288) as ctx:
+        for kind, kv in enumerate((case["kv_k"], case["kv_v"])):
+            ctx.kv_import(kind, 0, 0, 12000, np.ascontiguousarray(sh.d_section(kv, 0)[:12000]))
+            ctx.kv_import(kind, 0, 1, 12000, np.ascontiguousarray(sh.qs_section(kv, 0)[:12000]))
+        q = torch.from_numpy(np.ascontiguousarray(case["qn"])).cuda()
+        stream = torch.cuda.current_stream().cuda_stream
+        for cur_pos in (12000, 1, 8193, 256, 257):
+            ref = torch.zeros(sh.q_dim, dtype=torch.float16, device="cuda")
+            got = torch.full((sh.q_dim,), float("nan"), dtype=torch.float16, device="cuda")
+            ctx.dispatch_attention_decode(0, q, ref, cur_pos)
+            st = lib.bp_attn_decode_static_scratch(stream, q.data_ptr(), ctx.kv_device_ptr(0), ctx.kv_device_ptr(1),
+                                                   got.data_ptr(), 1, 12288, 64, 8, 0, cur_pos)
+            assert st == 0
+            torch.cuda.synchronize()
+            ok, max_abs, max_rel = within_tolerance(got.cpu().numpy(), ref.cpu().numpy().astype(np.float32))
+            assert ok, (cur_pos, max_abs, max_rel)
+            exact = O.attn_exact(sh, case["qn"], case["kv_k"], case["kv_v"], 0, 1, cur_pos - 1)[0]
+            assert within_tolerance(got.cpu().numpy(), exact)[0], cur_pos
+        # one head more than the scratch holds
+        assert lib.bp_attn_decode_static_scratch(stream, q.data_ptr(), ctx.kv_device_ptr(0), ctx.kv_device_ptr(1),
+                                                 got.data_ptr(), 1, 12288, 72, 8, 0, 10) == 1
