@@ -161,9 +161,59 @@ void orc_build_rope_table_f16(uint32_t head_dim, float freq_base, uint32_t max_s
 
 /* --------------------------------------------- norm + RoPE + quantise ---- */
 
-/* Correctly rounded 1/sqrt(x): evaluated in 64-bit-mantissa long double and
- * rounded once to binary32. */
-static float rsqrt_rn(float x) { return (float)(1.0L / sqrtl((long double)x)); }
+/* Sign of mid^2 * x - 1, exactly, for a positive `mid` with at most 26 significant bits (a float
+ * or the midpoint of two adjacent floats) and a positive normal float x: integer mantissas, one
+ * 128-bit product, a power-of-two comparison. mid^2 * x > 1 is the same as 1/sqrt(x) < mid. */
+static int mid2x_vs_one(double mid, float x) {
+  int e1, e2;
+  const double fm = frexp(mid, &e1);       /* mid = fm * 2^e1, fm in [0.5, 1) */
+  const float fx = frexpf(x, &e2);
+  const uint64_t m = (uint64_t)ldexp(fm, 26); /* exact: at most 26 bits */
+  const uint64_t xm = (uint64_t)ldexpf(fx, 24);
+  const unsigned __int128 p = (unsigned __int128)(m * m) * xm; /* < 2^76 */
+  const int s = -(2 * (e1 - 26) + (e2 - 24));                  /* compare p with 2^s */
+  if (s < 0) return 1;
+  if (s > 126) return -1;
+  const unsigned __int128 one = (unsigned __int128)1 << s;
+  return p > one ? 1 : (p < one ? -1 : 0);
+}
+
+/* Correctly rounded 1/sqrt(x) for positive normal x (CUDA's __frsqrt_rn, WGSL's inverseSqrt taken
+ * at its best): a binary64 estimate picks the candidate, and the exact comparison above moves it to
+ * a neighbour when 1/sqrt(x) lies on the other side of the midpoint. No tie exists: a midpoint of
+ * two floats has an odd 25-bit mantissa, and 1/mid^2 is then not a dyadic number, so it cannot be x. */
+static float rsqrt_rn(float x) {
+  float c = (float)(1.0 / sqrt((double)x));
+  for (int iter = 0; iter < 2; iter++) {
+    const float lo = nextafterf(c, 0.0f), hi = nextafterf(c, INFINITY);
+    if (mid2x_vs_one(((double)lo + (double)c) * 0.5, x) > 0) c = lo;       /* 1/sqrt(x) below the lower midpoint */
+    else if (mid2x_vs_one(((double)c + (double)hi) * 0.5, x) < 0) c = hi;  /* above the upper midpoint */
+    else break;
+  }
+  return c;
+}
+
+/* For the tests: the function above; the earlier evaluation through an 80-bit long double (two
+ * roundings); and a sweep over `count` inputs from bit pattern `first` in steps of `stride` that
+ * returns how many of them the two evaluate differently (and checks on each that the exact result
+ * has 1/sqrt(x) between its two midpoints: a violation returns UINT64_MAX). */
+float orc_rsqrt_rn(float x) { return rsqrt_rn(x); }
+float orc_rsqrt_long_double(float x) { return (float)(1.0L / sqrtl((long double)x)); }
+uint64_t orc_rsqrt_sweep(uint32_t first, uint64_t count, uint32_t stride) {
+  uint64_t differ = 0, bad = 0;
+#pragma omp parallel for schedule(static) reduction(+ : differ, bad)
+  for (uint64_t i = 0; i < count; i++) {
+    const uint32_t bits = first + (uint32_t)(i * stride);
+    float x;
+    memcpy(&x, &bits, 4);
+    if (!(x >= 1.17549435e-38f) || !(x <= 3.0e38f)) continue; /* positive normal inputs only */
+    const float r = rsqrt_rn(x);
+    const float lo = nextafterf(r, 0.0f), hi = nextafterf(r, INFINITY);
+    if (mid2x_vs_one(((double)lo + (double)r) * 0.5, x) > 0 || mid2x_vs_one(((double)r + (double)hi) * 0.5, x) < 0) bad++;
+    if (r != orc_rsqrt_long_double(x)) differ++;
+  }
+  return bad ? UINT64_MAX : differ;
+}
 
 /* Sum of 128 squares. tree 0: the canonical order (see the file header).
  * tree 1: one 64-lane butterfly per half, then h0 + h1 (a wave64 device).

@@ -65,6 +65,9 @@ def _load(native: bool = False) -> C.CDLL:
         "orc_attn_prefill": (None, [_u16p, _u8p, _u8p, _u16p] + [_u32] * 6),
         "orc_attn_exact": (None, [_u16p, _u8p, _u8p, _f32p] + [_u32] * 7),
         "orc_num_threads": (_int, []),
+        "orc_rsqrt_rn": (C.c_float, [C.c_float]),
+        "orc_rsqrt_long_double": (C.c_float, [C.c_float]),
+        "orc_rsqrt_sweep": (_u64, [_u32, _u64, _u32]),
         "orc_set_threads": (None, [_int]),
     }
     for name, (res, args) in sig.items():

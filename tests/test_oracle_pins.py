@@ -205,3 +205,30 @@ def test_oracle_is_deterministic():
     a = O.attn_decode(sh, c["qn"], c["kv_k"], c["kv_v"], 0, c["cur_pos"])
     b = O.attn_decode(sh, c["qn"], c["kv_k"], c["kv_v"], 0, c["cur_pos"])
     assert np.array_equal(a.view(np.uint16), b.view(np.uint16))
+
+
+def test_rsqrt_is_correctly_rounded():
+    """The oracle's 1/sqrt (step 2 of kv_writeback_fused.wgsl / q_norm_rope_fused.wgsl, fixed here as
+    the correctly rounded value) against an independent exact check in Python integers, on random and
+    hand-picked inputs; then every float of [2^-20, 16) (201 million, the range `total / 128 + eps` can
+    take for f16 inputs is inside it) through the C sweep, which re-checks the defining property and
+    counts disagreements with the former long-double evaluation."""
+    from fractions import Fraction
+    lib = O.lib()
+    rng = np.random.default_rng(11)
+    xs = np.concatenate([
+        np.exp(rng.uniform(np.log(1e-6), np.log(7e4), 4000)).astype(np.float32),
+        np.array([1e-6, 1.0, 2.0, 4.0, 0.25, 3.0, 1.0 + 2.0 ** -23, 2.0 - 2.0 ** -23, 65504.0 ** 2 / 128], dtype=np.float32),
+    ])
+    for x in xs:
+        r = np.float32(lib.orc_rsqrt_rn(float(x)))
+        lo, hi = np.nextafter(r, np.float32(0)), np.nextafter(r, np.float32(np.inf))
+        fx = Fraction(float(x))
+        m_lo = (Fraction(float(lo)) + Fraction(float(r))) / 2
+        m_hi = (Fraction(float(r)) + Fraction(float(hi))) / 2
+        # m_lo < 1/sqrt(x) < m_hi  <=>  m_lo^2 x < 1 < m_hi^2 x
+        assert m_lo * m_lo * fx < 1 < m_hi * m_hi * fx, float(x)
+    first, last = 0x35800000, 0x41800000  # bit patterns of 2^-20 and 16.0
+    differ = lib.orc_rsqrt_sweep(first, last - first, 1)
+    assert differ != 2 ** 64 - 1, "the exact 1/sqrt violated its own rounding property"
+    assert differ == 0, f"{differ} inputs where the long-double evaluation was not correctly rounded"
