@@ -16,9 +16,12 @@
 //    CTAs fetch items, longest first, from a global counter. Keys come in
 //    tiles of 64. Per key tile and per query tile X:
 //      producer warp   TMA: f16 K and V tiles (128-byte swizzle) straight into UMMA operand layout
-//      issuer warp X   S_X = Q_X K^T (8 UMMAs M 128, N 64, K 16) into one of the two 64-column
-//                      buffers of X's S region in TMEM, two tiles ahead of
-//                      O_X += P_X V (4 UMMAs M 128, N 128, K 16, P_X read from TMEM as the A operand)
+//      Q K^T issuer X  S_X = Q_X K^T (8 UMMAs M 128, N 64, K 16) into one of the two 64-column
+//                      buffers of X's S region in TMEM, up to two tiles ahead of
+//      P V issuer      O_X += P_X V (4 UMMAs M 128, N 128, K 16, P_X read from TMEM as the A operand)
+//                      for whichever query tile has its P ready (one thread issues a tcgen05.mma
+//                      only every ~115 cycles, the tensor pipe takes one every 70 to 80 from
+//                      several threads: hence three issuing threads for two query tiles)
 //      softmax group X thread = query row = TMEM lane: scale, causal mask, online max / sum,
 //                      P as f16 written over the tile's S buffer; O_X is rescaled in TMEM only
 //                      when a row maximum grew by more than 2^8 (P stays below 2^8 meanwhile)
@@ -51,7 +54,9 @@ constexpr uint32_t TM_S = 0, TM_O = 256;         // TMEM columns: S_X at TM_S + 
 
 template <uint32_t NQ>
 struct PLayout {
-  static constexpr uint32_t THREADS = 32 + NQ * 32 + NQ * 128;  // producer, NQ issuers, NQ softmax groups of 4 warps
+  // producer, NQ Q K^T issuers, one P V issuer, NQ softmax groups of 4 warps
+  static constexpr uint32_t FIRST_SM_WARP = NQ + 2;
+  static constexpr uint32_t THREADS = 32 * FIRST_SM_WARP + NQ * 128;
   static constexpr uint32_t OFF_Q = 0, OFF_K = NQ * OPER_B, OFF_V = OFF_K + KV_SLOTS * KV_TILE_B;
   static constexpr uint32_t SMEM = OFF_V + KV_SLOTS * KV_TILE_B + 1024;
 };
@@ -163,7 +168,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t k_full[KV_SLOTS], v_full[KV_SLOTS];
   __shared__ __align__(8) uint64_t k_empty[NQ][KV_SLOTS], v_empty[NQ][KV_SLOTS];  // per query tile: it is done with the slot
-  __shared__ __align__(8) uint64_t s_ready[NQ][2], p_ready[NQ][2], o_done[NQ];
+  __shared__ __align__(8) uint64_t s_ready[NQ][2], p_ready[NQ][2], p_free[NQ][2], o_done[NQ];
   __shared__ uint32_t tmem_base_s, item_s;
   __shared__ volatile uint32_t abort_s;
 
@@ -187,6 +192,8 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       mbar_init(smem_u32(&s_ready[x][1]), 1);
       mbar_init(smem_u32(&p_ready[x][0]), 4);
       mbar_init(smem_u32(&p_ready[x][1]), 4);
+      mbar_init(smem_u32(&p_free[x][0]), 1);
+      mbar_init(smem_u32(&p_free[x][1]), 1);
       mbar_init(smem_u32(&o_done[x]), 1);
     }
     abort_s = 0;
@@ -204,6 +211,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
 
   const bool dbg_on = p.dbg != nullptr && blockIdx.x == 0 && lane == 0;
   long long tw[4] = {0, 0, 0, 0};
+  long long tph[4] = {0, 0, 0, 0};  // softmax phases: S load, maximum (+ rescale), exponentials, P store
   const long long t_begin = clock64();
   auto waitx = [&](uint64_t* bar, uint32_t parity, int slot) {
     if (abort_s) return;
@@ -307,24 +315,25 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         }
       }
     } else if (warp <= NQ) {
-      // ---------------- UMMA issuer of query tile X ----------------
-      // One issuing thread sustains about one tcgen05.mma per 100 cycles, a 128 x 128 x 16 MMA takes
-      // 64: each query tile has its own issuer so that the tensor pipe is fed from two threads.
+      // ---------------- Q K^T issuer of query tile X ----------------
+      // One issuing thread sustains about one tcgen05.mma per 115 cycles whatever its size; the tensor
+      // pipe takes one 128 x 128 x 16 MMA per 70 to 80 cycles from several threads (measured). So the
+      // issue work is spread: one thread per query tile for S = Q K^T (8 MMAs per key tile), one more
+      // for all P V (4 per key tile and query tile).
       const uint32_t x = warp - 1;
       const uint32_t n_mine = nx[x], c0 = gx[x];
       if (lane == 0 && n_mine > 0) {
         constexpr uint32_t IDESC_QK = umma_idesc(1, 0, 0, 0, 0, BM, BN);   // f32 = f16 (K-major) x f16 (K-major), N = 64 keys
-        constexpr uint32_t IDESC_PV = umma_idesc(1, 0, 0, 0, 1, BM, 128);  // f32 += f16 (TMEM) x f16 (MN-major), N = 128 dims
         const uint64_t dk = umma_desc_sw128(0, 16, 1024);       // K-major operands
-        const uint64_t dmn = umma_desc_sw128(0, 8192, 1024);    // V: next 64 dims 8 KB away, 8 key rows 1 KB apart
         const uint64_t qa = dk + ((smem_base + L::OFF_Q + x * OPER_B) >> 4);
-        const uint32_t s_col = tmem + TM_S + x * SW, o_col = tmem + TM_O + x * SW;
+        const uint32_t s_col = tmem + TM_S + x * SW;
         // S of tile i goes to buffer (c0 + i) & 1 of the query tile's S region; P of the tile is
-        // written over it and read from there by P V. Q K^T runs two tiles ahead of P V, so a
-        // tile's softmax overlaps the MMAs of its neighbours.
-        auto issue_qk = [&](uint32_t i) {
-          const uint32_t s = (gkv + i) % KV_SLOTS, b = (c0 + i) & 1;
+        // written over it and read from there by P V. Q K^T runs up to two tiles ahead of P V: a
+        // buffer is free again when the P V of its previous tile has completed (p_free).
+        for (uint32_t i = 0; i < n_mine; i++) {
+          const uint32_t s = (gkv + i) % KV_SLOTS, c = c0 + i, b = c & 1;
           waitx(&k_full[s], ((gkv + i) / KV_SLOTS) & 1, 0);
+          if (c >= 2) waitx(&p_free[x][b], ((c >> 1) - 1) & 1, 2);
           tc_fence_after();
           const uint64_t kb = dk + ((smem_base + L::OFF_K + s * KV_TILE_B) >> 4);
 #pragma unroll
@@ -333,29 +342,54 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             umma_f16(s_col + 64 * b, qa + qo, kb + ko, IDESC_QK, ks);
           }
           umma_commit(smem_u32(&s_ready[x][b]));
-        };
-        issue_qk(0);
-        if (n_mine > 1) issue_qk(1);
-        for (uint32_t i = 0; i < n_mine; i++) {
-          const uint32_t s = (gkv + i) % KV_SLOTS, b = (c0 + i) & 1;
-          const uint64_t vb = dmn + ((smem_base + L::OFF_V + s * KV_TILE_B) >> 4);
-          waitx(&v_full[s], ((gkv + i) / KV_SLOTS) & 1, 1);
-          // one barrier per S buffer: the softmax group may run two tiles ahead of this wait, and two
-          // completions on one barrier would be indistinguishable from none
-          waitx(&p_ready[x][b], ((c0 + i) >> 1) & 1, 2);
-          tc_fence_after();
-#pragma unroll
-          for (uint32_t ks = 0; ks < 4; ks++)  // 16 keys per UMMA: 8 columns of P, 16 rows of V
-            umma_f16_ts(o_col, s_col + 64 * b + 8 * ks, vb + ks * (16 * 128 >> 4), IDESC_PV, (i | ks) ? 1u : 0u);
-          umma_commit(smem_u32(&v_empty[x][s]));  // P V of tile i complete: V slot free, O_X consistent
-          if (i + 2 < n_mine) issue_qk(i + 2);    // into the buffer P V just read: ordered behind it by the tensor pipe
         }
-        umma_commit(smem_u32(&o_done[x]));
+      }
+    } else if (warp == NQ + 1) {
+      // ---------------- P V issuer (all query tiles) ----------------
+      // O_X += P_X V for whichever query tile has its P ready: the tiles of one query tile in order,
+      // the query tiles in the order their softmax groups finish.
+      if (lane == 0) {
+        constexpr uint32_t IDESC_PV = umma_idesc(1, 0, 0, 0, 1, BM, 128);  // f32 += f16 (TMEM) x f16 (MN-major), N = 128 dims
+        const uint64_t dmn = umma_desc_sw128(0, 8192, 1024);    // V: next 64 dims 8 KB away, 8 key rows 1 KB apart
+        uint32_t ix[NQ], spins = 0;
+#pragma unroll
+        for (uint32_t x = 0; x < NQ; x++) ix[x] = 0;
+        for (;;) {
+          bool all_done = true, progressed = false;
+#pragma unroll
+          for (uint32_t x = 0; x < NQ; x++) {
+            if (ix[x] >= nx[x]) continue;
+            all_done = false;
+            const uint32_t i = ix[x], s = (gkv + i) % KV_SLOTS, c = gx[x] + i, b = c & 1;
+            // one barrier per S buffer: the softmax group may run two tiles ahead of this test, and two
+            // completions on one barrier would be indistinguishable from none
+            if (!mbar_test(smem_u32(&p_ready[x][b]), (c >> 1) & 1)) continue;
+            waitx(&v_full[s], ((gkv + i) / KV_SLOTS) & 1, 1);
+            tc_fence_after();
+            const uint64_t vb = dmn + ((smem_base + L::OFF_V + s * KV_TILE_B) >> 4);
+            const uint32_t s_col = tmem + TM_S + x * SW, o_col = tmem + TM_O + x * SW;
+#pragma unroll
+            for (uint32_t ks = 0; ks < 4; ks++)  // 16 keys per UMMA: 8 columns of P, 16 rows of V
+              umma_f16_ts(o_col, s_col + 64 * b + 8 * ks, vb + ks * (16 * 128 >> 4), IDESC_PV, (i | ks) ? 1u : 0u);
+            umma_commit(smem_u32(&v_empty[x][s]));  // P V of tile i complete: V slot free, O_X consistent
+            umma_commit(smem_u32(&p_free[x][b]));   // ... and the S buffer may take the next Q K^T
+            if (++ix[x] == nx[x]) umma_commit(smem_u32(&o_done[x]));
+            progressed = true;
+          }
+          if (all_done || abort_s) break;
+          if (progressed) {
+            spins = 0;
+          } else if (++spins > p.wait_limit) {  // bounded like every other wait (a round is a few dozen cycles)
+            abort_s = 1;
+            atomicExch(p.err, 5u);
+            break;
+          }
+        }
       }
     } else {
       // ---------------- softmax group X: thread = query row = TMEM lane ----------------
-      const uint32_t x = (warp - 1 - NQ) >> 2, quad = warp & 3, r = quad * 32 + lane;
-      const bool elected = ((warp - 1 - NQ) & 3) == 0 && lane == 0;  // releases the K / V slots for this query tile
+      const uint32_t x = (warp - L::FIRST_SM_WARP) >> 2, quad = warp & 3, r = quad * 32 + lane;
+      const bool elected = ((warp - L::FIRST_SM_WARP) & 3) == 0 && lane == 0;  // releases the K slots for this query tile
       const uint32_t lane_addr = (quad * 32) << 16;
       const uint32_t s_addr = tmem + lane_addr + TM_S + x * SW, o_addr = tmem + lane_addr + TM_O + x * SW;
       const uint32_t tok = tq0[x] + r / p.qpg, head = g * p.qpg + r % p.qpg;
@@ -366,11 +400,13 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         const uint32_t b = (c0 + i) & 1, slot = (gkv + i) % KV_SLOTS;
         waitx(&s_ready[x][b], ((c0 + i) >> 1) & 1, 0);
         tc_fence_after();
+        const long long tp0 = dbg_on ? clock64() : 0;
         if (elected) mbar_arrive(smem_u32(&k_empty[x][slot]));  // Q K^T of tile i is complete
         uint32_t raw[64];
         tmem_ld32(s_addr + 64 * b, raw);
         tmem_ld32(s_addr + 64 * b + 32, raw + 32);
         tmem_ld_wait();
+        const long long tp1 = dbg_on ? clock64() : 0;
         // causal mask: key i * BN + c is visible to this row iff key <= tok (only the last tile can cut)
         if ((i + 1) * BN > tq0[x] + 1) {
           const uint32_t k0 = i * BN;
@@ -404,6 +440,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             tmem_st16(o_addr + 16 * c, o);
           }
         }
+        const long long tp2 = dbg_on ? clock64() : 0;
         // the completion of this tile's P V will be phase `vph bit slot` of its slot's barrier
         prev_par = (vph >> slot) & 1u;
         prev_slot = slot;
@@ -419,12 +456,17 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
           __half2 h = __floats2half2_rn(p0, p1);
           ph[c] = *reinterpret_cast<uint32_t*>(&h);
         }
+        const long long tp3 = dbg_on ? clock64() : 0;
         tmem_st32(s_addr + 64 * b, ph);
         l_run = l_run * corr + ((sum[0] + sum[1]) + (sum[2] + sum[3]));
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&p_ready[x][b]));
+        if (dbg_on) {
+          const long long tp4 = clock64();
+          tph[0] += tp1 - tp0; tph[1] += tp2 - tp1; tph[2] += tp3 - tp2; tph[3] += tp4 - tp3;
+        }
       }
       // ---- O / l -> f16 ----
       if (n_mine > 0) {
@@ -467,11 +509,12 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     __syncthreads();  // the item is finished by every role: Q, S and O can be reused
     tc_fence_after();
   }
-  if (dbg_on && (warp == 0 || warp == 1 || warp == 1 + NQ || warp == 5 + NQ)) {
-    const uint32_t role = warp == 0 ? 0 : warp == 1 ? 1 : warp == 1 + NQ ? 2 : 3;
+  if (dbg_on && (warp == 0 || warp == 1 || warp == L::FIRST_SM_WARP || warp == L::FIRST_SM_WARP + 4 || warp == NQ + 1)) {
+    const uint32_t role = warp == 0 ? 0 : warp == 1 ? 1 : warp == L::FIRST_SM_WARP ? 2 : warp == NQ + 1 ? 6 : 3;
     p.dbg[role * 8] = static_cast<unsigned long long>(clock64() - t_begin);
     for (int k = 0; k < 4; k++) p.dbg[role * 8 + 1 + k] = static_cast<unsigned long long>(tw[k]);
     p.dbg[role * 8 + 7] = gkv;
+    if (role == 2) for (int k = 0; k < 4; k++) p.dbg[40 + k] = static_cast<unsigned long long>(tph[k]);
   }
   tc_fence_before();
   __syncthreads();
