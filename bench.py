@@ -15,9 +15,9 @@ layer) / time.
 With N > 1 ranks (torchrun) the KV heads are sharded over the ranks (strong
 scaling: the same stack, 1/N of the heads per GPU). The all-gather of the head
 outputs happens inside the decode kernel: its epilogue stores every output
-element into every rank's gathered buffer (peer stores over NVLink), its last
-CTA signals the layer's meeting counter on every rank, and the next layer's
-kernel waits for that counter before it ends. `--exchange` selects the other
+element into every rank's gathered buffer (peer stores over NVLink), and the
+next layer's decode kernel holds the ranks' meeting for that row (it signals
+once its predecessors are complete and waits before it ends). `--exchange` selects the other
 forms (a meeting kernel after every layer, one per token, or an NCCL all-gather
 after every layer).
 
@@ -320,7 +320,7 @@ def run_ours(args):
             mode = "nccl"
     exchange_text = {
         "none": "none",
-        "kernel": "peer stores in the decode epilogue; the kernel's last CTA signals, the next layer's kernel waits",
+        "kernel": "peer stores in the decode epilogue; the next layer's decode kernel holds the meeting (signal at its start, wait before its end), one meeting kernel per token for the last layer",
         "sync-kernel": "peer stores in the decode epilogue; a meeting kernel after every layer",
         "per-token": "peer stores in the decode epilogue; one meeting kernel per token",
         "nccl": "nccl all-gather per layer",
@@ -332,8 +332,7 @@ def run_ours(args):
             return
         if on:
             ctx.set_peer_exchange(out_ptrs, flag_ptrs)
-            ctx.set_option("peer_signal_in_kernel", 1 if mode == "kernel" else 0)
-            ctx.set_option("peer_wait_in_kernel", 1 if mode == "kernel" else 0)
+            ctx.set_option("peer_meet_in_kernel", 1 if mode == "kernel" else 0)
         else:
             ctx.set_peer_exchange([], [])
     exchange_on(True)
@@ -369,7 +368,7 @@ def run_ours(args):
             ctx.peer_sync(slot=0, stream=stream)
             n += 1
         if exchange and mode == "kernel":
-            ctx.peer_wait(slot=last_slot, stream=stream)  # the last layer's row has no next layer to wait in
+            ctx.peer_sync(slot=last_slot, stream=stream)  # the last layer's row has no next layer to meet in
             n += 1
         launches_per_step = n
 
@@ -514,10 +513,7 @@ def run_ours(args):
         if use_px:
             # the gathered rows of all ranks, once every rank's stores have landed
             with torch.cuda.stream(stream):
-                if mode == "kernel":
-                    ctx.peer_wait(slot=last_slot, stream=stream)
-                else:
-                    ctx.peer_sync(slot=0, stream=stream)
+                ctx.peer_sync(slot=last_slot if mode == "kernel" else 0, stream=stream)
                 gh.copy_(out_full, non_blocking=True)
             stream.synchronize()
     if mode != "nccl":  # (the host entry point has no per-layer meeting kernel: the ranks meet once per token)

@@ -102,7 +102,6 @@ SIGNATURES = {
     "bp_set_peer_exchange": (_int, [_vp, _u32, _vp, _vp]),
     "bp_set_prefill_exchange": (_int, [_vp, _u32, _vp]),
     "bp_peer_sync": (_int, [_vp, _vp, _u32]),
-    "bp_peer_wait": (_int, [_vp, _vp, _u32]),
     "bp_attn_decode_static_scratch": (_int, [_vp, _vp, _vp, _vp, _vp] + [_u32] * 6),
 }
 

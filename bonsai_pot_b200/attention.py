@@ -131,10 +131,6 @@ class AttnContext:
         included), and so are every other rank's up to their matching call."""
         self._check(self._lib.bp_peer_sync(self._h, _stream(stream), slot))
 
-    def peer_wait(self, slot=0, stream=None):
-        """The waiting half of peer_sync alone (the decode kernel signalled: option peer_signal_in_kernel)."""
-        self._check(self._lib.bp_peer_wait(self._h, _stream(stream), slot))
-
     def dispatch_attention(self, layer_il, q, out, m_tokens, stream=None):
         """Batched prefill (pos = 0, is_prefill = true): q, out f16 [m][n_head*128]."""
         self._check(self._lib.bp_attn_prefill(self._h, _stream(stream), layer_il, _ptr(q), _ptr(out), m_tokens))

@@ -622,16 +622,15 @@ static cudaError_t launch_mma(bp_attn_ctx* c, cudaStream_t s, DecodeParams& p, u
 // rank's counter (system-scope release, after a system fence: the peer stores of the kernels
 // before this one in the stream are complete by then), then waits (bounded, system-scope acquire
 // loads) until its own counter has reached (meetings so far + 1) * ranks. Counters only grow, so a
-// rank that runs ahead cannot confuse a slower one. With `signal` = 0 the kernel only waits: the
-// decode kernel's last CTA has signalled already (option peer_signal_in_kernel).
+// rank that runs ahead cannot confuse a slower one.
 struct PeerFlags {
   uint32_t* f[BP_MAX_PEERS];
 };
 __global__ void __launch_bounds__(32)
-peer_sync_kernel(PeerFlags flags, uint32_t n_ranks, uint32_t rank, uint32_t slot, uint32_t signal, uint32_t limit,
-                 uint32_t* epochs, uint32_t* err) {
+peer_sync_kernel(PeerFlags flags, uint32_t n_ranks, uint32_t rank, uint32_t slot, uint32_t limit, uint32_t* epochs,
+                 uint32_t* err) {
   bp::pdl_wait();
-  if (signal && threadIdx.x < n_ranks) {
+  if (threadIdx.x < n_ranks) {
     __threadfence_system();
     asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(flags.f[threadIdx.x] + slot), "r"(1u) : "memory");
   }
@@ -649,11 +648,11 @@ peer_sync_kernel(PeerFlags flags, uint32_t n_ranks, uint32_t rank, uint32_t slot
   }
 }
 
-cudaError_t bp_launch_peer_sync(bp_attn_ctx* c, cudaStream_t s, uint32_t slot, bool signal) {
+cudaError_t bp_launch_peer_sync(bp_attn_ctx* c, cudaStream_t s, uint32_t slot) {
   PeerFlags f;
   for (uint32_t r = 0; r < BP_MAX_PEERS; r++) f.f[r] = r < c->n_px ? c->px_flag[r] : nullptr;
-  return bp_launch(c->opt_pdl != 0, peer_sync_kernel, dim3(1), dim3(32), 0, s, f, c->n_px, c->cfg.shard, slot, signal ? 1u : 0u,
-                   c->opt_wait_limit, c->px_epoch, c->err_dev);
+  return bp_launch(c->opt_pdl != 0, peer_sync_kernel, dim3(1), dim3(32), 0, s, f, c->n_px, c->cfg.shard, slot, c->opt_wait_limit,
+                   c->px_epoch, c->err_dev);
 }
 
 // Fused layer step. With the tcgen05 kernel: one launch does the Q norm + RoPE, the new token's

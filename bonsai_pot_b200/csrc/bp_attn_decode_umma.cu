@@ -41,12 +41,13 @@ constexpr uint32_t TILE_B = UT * 128;        // int8 tile of one head and stage:
 constexpr uint32_t U_MAX_STAGES = 8;             // upper bound of K stages and of V slots
 constexpr uint32_t NGRP = 4;                      // softmax groups working on different jobs in parallel
 constexpr uint32_t MERGE_BAR = 8;                 // named barrier: the merger's accumulate and softmax warps
+constexpr uint32_t SHARE_BAR = 9;                 // named barrier: the four accumulate warps combining their shares
 constexpr uint32_t FIN_BAR = 6;                   // named barrier: softmax warps arrive, accumulate warps wait
 constexpr uint32_t NISS = 2;                     // UMMA issuer warps per kind (QK, PV)
 constexpr uint32_t U_FIRST_SM_WARP = 1 + 2 * NISS;  // warp 0 producer, then the issuers
 constexpr uint32_t U_THREADS = (U_FIRST_SM_WARP + 4 * NGRP + 4) * 32;
 constexpr uint32_t TMEM_COLS = 512;          // per softmax group: D1 (64 columns) and D2 (64 columns)
-constexpr uint32_t NO_SLOT = 0xffu;           // px_sig / px_wait: no meeting counter
+constexpr uint32_t NO_SLOT = 0xffu;           // px_meet: no meeting in this launch
 constexpr uint32_t U_SMEM_BUDGET = 226 * 1024;  // dynamic shared memory; the static part needs the rest of 227 KB
 
 struct UmmaParams {
@@ -83,15 +84,15 @@ struct UmmaParams {
   // only after the dependency wait. UINT32_MAX: every row older than the new token is settled.
   uint32_t fresh_from;
   uint32_t v_pre_all;   // 1: the first round of V tiles is requested during set-up, like the K stages
-  // Meeting of the ranks without a kernel of its own. px_sig: the last CTA of this grid to finish
-  // adds one to every rank's counter of that slot (its peer stores are complete by then).
-  // px_wait: CTA (0, 0) waits, bounded, until every rank has signalled that slot (the previous
-  // layer's, whose gathered row a consumer of this kernel's position in the stream would read).
-  // (Slots and rank are bytes of one word and the counters sit behind one pointer: the parameter
+  // Meeting of the ranks without a kernel of its own (px_meet slot != none; set for layer L >= 1,
+  // slot of layer L - 1): once the kernels before this one in the stream are complete (their peer
+  // stores have landed by then), one thread of CTA (0, 0) adds one to every rank's counter of that
+  // slot; before the grid ends, one thread waits, bounded, until every rank has done so: the
+  // consumer's side of layer L - 1's gathered row. Nothing of it lies on this kernel's own path.
+  // (Slot and rank are bytes of one word and the counters sit behind one pointer: the parameter
   // block stays small.)
-  uint32_t px_meet;           // px_sig | px_wait << 8 | this rank << 16; slot 0xff = none
-  uint32_t* const* px_tab;    // in device memory: [r] rank r's meeting counters [64], [8] this rank's count of
-                              // finished CTAs per slot, [9] this rank's count of meetings per slot
+  uint32_t px_meet;           // slot | this rank << 8; slot 0xff = none
+  uint32_t* const* px_tab;    // in device memory: [r] rank r's meeting counters [64], [9] this rank's count of meetings per slot
   unsigned long long* dbg;  // optional cycle counters of CTA (0, 0); null in normal use
 };
 
@@ -120,6 +121,7 @@ struct Misc {            // small shared state, lives in the MISC_B region
   float lsum[NGRP][4][4];   // final l per (softmax group, query head, warp)
   float mfin[NGRP][4];
   uint32_t tag;             // the launch's tag, for the softmax warps of a merging CTA
+  float xm[4], xl[4], xo[4][32];  // mode-1 merge: the four accumulate warps' shares of a unit
 };
 
 __device__ __forceinline__ float s32_to_f32(uint32_t x) {  // exact for |x| < 2^22
@@ -234,6 +236,75 @@ __device__ __forceinline__ void merge_unit(const UmmaParams& p, uint32_t lane, u
     }
   }
   put_out(p, h, d, o_run * (1.0f / l_run));
+}
+
+// A share of a unit's merge, for mode 1: the other splits first, first + stride, ... (`count` of
+// them, numbered like merge_unit's: the i-th other split is i for i < split, else i + 1) are folded
+// into the running (m, l, o) of this warp; no output. The four accumulate warps of a CTA take a
+// quarter of the other splits each, so that a unit's merge is ONE polling round of at most MERGE_W
+// partials per lane for up to 4 * MERGE_W + 1 splits (two rounds by one warp took 0.6 us longer at
+// 18 splits, five rounds 2.5 us longer at 37), and combine their shares through shared memory.
+template <uint32_t MERGE_W>
+__device__ __forceinline__ void merge_part(const UmmaParams& p, uint32_t lane, uint32_t first, uint32_t stride, uint32_t count,
+                                           uint32_t split, uint32_t h, uint32_t d, uint32_t tag, volatile uint32_t* abort_flag,
+                                           float& m_run, float& l_run, float& o_run) {
+  const uint32_t sstride = p.n_head * BP_LL_STRIDE;
+  const uint2* base = p.ll + h * BP_LL_STRIDE;
+  for (uint32_t c0 = 0; c0 < count; c0 += 32) {
+    const uint32_t nc = min(32u, count - c0);
+    float e_k = 0.f;
+    for (uint32_t v0 = 0; v0 < nc; v0 += MERGE_W) {
+      uint2 v[MERGE_W];
+      uint2 mm, ls;
+      for (uint32_t spin = 0;; spin++) {
+        uint32_t c00 = c0;
+        asm volatile("" : "+r"(c00));  // addresses are formed next to their loads (see merge_unit)
+        const uint32_t i_ml = first + (c00 + min(lane, nc - 1)) * stride;
+        const uint2* ml = base + (i_ml + (i_ml >= split ? 1u : 0u)) * sstride;
+        mm = ld_tagged(ml + 128);
+        ls = ld_tagged(ml + 129);
+        const uint32_t k_max = nc - 1 - v0;
+#pragma unroll
+        for (uint32_t k = 0; k < MERGE_W; k++) {
+          const uint32_t i = first + (c00 + v0 + min(k, k_max)) * stride;
+          v[k] = ld_tagged(base + (i + (i >= split ? 1u : 0u)) * sstride + d);
+        }
+        bool ok = mm.y == tag && ls.y == tag;
+#pragma unroll
+        for (uint32_t k = 0; k < MERGE_W; k++) ok = ok && v[k].y == tag;
+        if (__all_sync(FULL, ok)) break;
+        const bool give_up = *abort_flag != 0 || spin >= p.poll_limit;
+        if (__any_sync(FULL, give_up)) {
+          if (*abort_flag == 0) {
+            *abort_flag = 1;
+            atomicExch(p.err, 3u);
+          }
+          break;
+        }
+        __nanosleep(spin < 4 ? 64u : 256u);
+      }
+      if (v0 == 0) {
+        const float m_k = lane < nc ? __uint_as_float(mm.x) : NEG_BIG;
+        float m_c = m_k;
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) m_c = fmaxf(m_c, __shfl_xor_sync(FULL, m_c, off));
+        const float m_new = fmaxf(m_run, m_c);
+        e_k = lane < nc ? ex2(m_k - m_new) : 0.f;
+        float l_c = lane < nc ? __uint_as_float(ls.x) * e_k : 0.f;
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) l_c += __shfl_xor_sync(FULL, l_c, off);
+        const float scale = ex2(m_run - m_new);
+        o_run *= scale;
+        l_run = fmaf(l_run, scale, l_c);
+        m_run = m_new;
+      }
+#pragma unroll
+      for (uint32_t k = 0; k < MERGE_W; k++) {
+        const float e = __shfl_sync(FULL, e_k, (v0 + k) & 31u);
+        o_run = fmaf(__uint_as_float(v[k].x), v0 + k < nc ? e : 0.f, o_run);
+      }
+    }
+  }
 }
 
 // MODE: which merge code (see merge_unit) the instance carries. 1: mode 1 only, launched for long
@@ -394,6 +465,9 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
     }
     pdl_wait();  // q is written by the kernel before this one
     if (p.merge && n_splits > 1) epoch = ld_relaxed_u32(p.epochs + blockIdx.y);  // used in the epilogue
+    if ((p.px_meet & 0xffu) != NO_SLOT && blockIdx.x == 0 && blockIdx.y == 0 && aw == 0 && lane < p.n_px)
+      // everything before this kernel in the stream is complete, the previous layer's peer stores included
+      asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.px_tab[lane] + (p.px_meet & 0xffu)), "r"(1u) : "memory");
     // lane l holds dims 4l .. 4l+3 of one head: a Q8_0 block is 8 lanes. One 8-byte load, three
     // shuffles for the block maximum, two 4-byte stores: short straight-line code, because this sits
     // on the critical path of every launch (the first Q K^T waits for it) and runs cold.
@@ -523,11 +597,11 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
     }
     // Consumer side of the previous layer's meeting: one thread of the grid, idle by now, waits until
     // every rank has signalled that slot (all ranks' stores into this rank's gathered row have landed).
-    const uint32_t px_wait = (p.px_meet >> 8) & 0xffu;
-    if (px_wait != NO_SLOT && blockIdx.x == 0 && blockIdx.y == 0 && lane == 0) {
+    const uint32_t px_slot = p.px_meet & 0xffu;
+    if (px_slot != NO_SLOT && blockIdx.x == 0 && blockIdx.y == 0 && lane == 0) {
       pdl_wait();  // the meeting count was advanced by an earlier kernel
-      uint32_t* epoch = p.px_tab[9] + px_wait;
-      const uint32_t* flag = p.px_tab[(p.px_meet >> 16) & 0xffu] + px_wait;
+      uint32_t* epoch = p.px_tab[9] + px_slot;
+      const uint32_t* flag = p.px_tab[(p.px_meet >> 8) & 0xffu] + px_slot;
       const uint32_t target = (*epoch + 1u) * p.n_px;
       bool ok = false;
       for (uint32_t i = 0; i < p.wait_limit && !ok; i++) {
@@ -791,18 +865,44 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
     }
     if (MODE != 1 && merger && dim == 0) misc->tag = tag;
     if (merge_mode == 1) {
-      // This warp's units: (query head hl, dim quarter `quad`) with (hl * 4 + quad) mod n_splits == split.
+      // This CTA's units: u = (query head hl, dim quarter qd) with u mod n_splits == split. All four
+      // accumulate warps work on a unit: each folds a quarter of the other splits (warp `qd` starts from
+      // the CTA's own part, which it holds in registers), then warp `qd` combines the four shares.
 #pragma unroll 1
-      for (uint32_t hl = 0; hl < HPC * 4; hl++) {
-        if ((hl * 4 + quad) % n_splits != split) continue;
-        float a = acc_h[0], m, l;
+      for (uint32_t u = split; u < HPC * 16; u += n_splits) {
+        const uint32_t hl = u >> 2, qd = u & 3;
+        float m_r = NEG_BIG, l_r = 0.f, o_r = 0.f;
+        if (quad == qd) {
+          o_r = acc_h[0];
 #pragma unroll
-        for (uint32_t i = 1; i < HPC * 4; i++) a = hl == i ? acc_h[i] : a;
-        head_ml(hl / 4, hl % 4, m, l);
-        merge_unit<10>(p, lane, n_splits, split, g0 * p.qpg + hl, dim, a, m, l, tag, &abort_s);
-        // The next launch's tag. Safe to advance once unit 0 is merged: its warp has seen every split's
-        // tag, so every CTA of the group has read the epoch.
-        if (hl == 0 && quad == 0 && lane == 0) *reinterpret_cast<volatile uint32_t*>(p.epochs + blockIdx.y) = tag;
+          for (uint32_t i = 1; i < HPC * 4; i++) o_r = hl == i ? acc_h[i] : o_r;
+          head_ml(hl / 4, hl % 4, m_r, l_r);
+        }
+        const uint32_t n_oth = n_splits - 1;
+        const uint32_t mine = quad < n_oth ? (n_oth - quad + 3) / 4 : 0;  // other splits quad, quad + 4, ...
+        merge_part<10>(p, lane, quad, 4, mine, split, g0 * p.qpg + hl, qd * 32 + lane, tag, &abort_s, m_r, l_r, o_r);
+        misc->xo[quad][lane] = o_r;
+        if (lane == 0) {
+          misc->xm[quad] = m_r;
+          misc->xl[quad] = l_r;
+        }
+        __threadfence_block();
+        named_bar_sync(SHARE_BAR, 128);
+        if (quad == qd) {
+          const float m_all = fmaxf(fmaxf(misc->xm[0], misc->xm[1]), fmaxf(misc->xm[2], misc->xm[3]));
+          float o_all = 0.f, l_all = 0.f;
+#pragma unroll
+          for (uint32_t w = 0; w < 4; w++) {
+            const float e = ex2(misc->xm[w] - m_all);
+            o_all = fmaf(misc->xo[w][lane], e, o_all);
+            l_all = fmaf(misc->xl[w], e, l_all);
+          }
+          put(g0 * p.qpg + hl, qd * 32 + lane, o_all * (1.0f / l_all));
+          // The next launch's tag. Safe to advance once unit 0 is merged: its warps have seen every split's
+          // tag, so every CTA of the group has read the epoch.
+          if (u == 0 && lane == 0) *reinterpret_cast<volatile uint32_t*>(p.epochs + blockIdx.y) = tag;
+        }
+        if (u + n_splits < HPC * 16) named_bar_sync(SHARE_BAR, 128);  // the exchange area is reused
       }
     }
   }
@@ -830,18 +930,6 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem, TMEM_COLS);
-  // Producer side of this layer's meeting: every CTA's stores (peer stores included) are ordered
-  // before its count by a system fence; the CTA that counts last tells every rank.
-  const uint32_t px_sig = p.px_meet & 0xffu;
-  if (px_sig != NO_SLOT && threadIdx.x == 0) {
-    __threadfence_system();
-    uint32_t* done = p.px_tab[8] + px_sig;
-    if (atomicAdd(done, 1u) == gridDim.x * gridDim.y - 1) {
-      *done = 0;  // for the next launch on this slot, which starts after this grid
-      for (uint32_t r = 0; r < p.n_px; r++)
-        asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.px_tab[r] + px_sig), "r"(1u) : "memory");
-    }
-  }
   if (p.dbg != nullptr && threadIdx.x == 0) {  // development aid: span of the launch in ns
     unsigned long long t_exit_ns;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_exit_ns));
@@ -965,9 +1053,8 @@ cudaError_t bp_launch_decode_umma(bp_attn_ctx* c, cudaStream_t s, uint32_t layer
   p.poll_limit = c->opt_poll_limit;
   p.v_pre_all = c->opt_vpre;
   p.fresh_from = bp_fresh_from(c, layer);
-  const uint32_t px_sig = c->n_px > 0 && c->opt_px_signal ? layer % 64 : NO_SLOT;
-  const uint32_t px_wait = c->n_px > 0 && c->opt_px_wait && layer > 0 ? (layer - 1) % 64 : NO_SLOT;
-  p.px_meet = px_sig | px_wait << 8 | c->cfg.shard << 16;
+  const uint32_t px_slot = c->n_px > 0 && c->opt_px_meet && layer > 0 ? (layer - 1) % 64 : NO_SLOT;
+  p.px_meet = px_slot | c->cfg.shard << 8;
   p.px_tab = c->pxf_dev;
   p.ll = c->ll;
   p.epochs = c->epochs;

@@ -72,10 +72,8 @@ struct bp_attn_ctx {
   uint32_t umma_resident;   // tcgen05 decode: CTAs the device holds at once (occupancy query), the bound of a launch whose CTAs wait for one another
   uint32_t opt_vpre;        // tcgen05 decode: request the first round of V tiles during set-up
   uint32_t opt_l2promo;     // L2 promotion of the cache tensor maps: 0 = 256 B, 1 = 128 B, 2 = 64 B, 3 = none
-  uint32_t opt_px_signal;   // peer exchange: the decode kernel's last CTA signals the meeting counter of its layer itself
-  uint32_t opt_px_wait;     // peer exchange: the decode kernel of layer L waits for the meeting of layer L - 1
-  uint32_t** pxf_dev;       // device copy of px_flag, read by the decode kernel
-  uint32_t* px_done;        // device: CTAs of the current launch that have finished, per counter slot [64]
+  uint32_t opt_px_meet;     // peer exchange: the decode kernel of layer L >= 1 holds the meeting of layer L - 1 itself
+  uint32_t** pxf_dev;       // device table read by the decode kernel: px_flag[0..7], -, px_epoch
   // Dependent launches let a kernel's prologue run before earlier kernels have completed. A decode
   // kernel may request cache rows that early only when the launch that wrote them is certainly
   // complete: sm_seq counts the CTAs of kernels that hold a whole SM each; row_mark[layer] is its
@@ -131,9 +129,8 @@ cudaError_t bp_launch_decode(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, con
                              __half* out, uint32_t cur_pos, uint32_t* launches);
 cudaError_t bp_launch_prefill(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, const __half* q,
                               __half* out, uint32_t m, uint32_t* launches);
-// Meeting of the ranks of the peer exchange on counter `slot` (< 64): signal all (unless the decode
-// kernel did), wait (bounded) for all.
-cudaError_t bp_launch_peer_sync(bp_attn_ctx* c, cudaStream_t s, uint32_t slot, bool signal);
+// Meeting of the ranks of the peer exchange on counter `slot` (< 64): signal all, wait (bounded) for all.
+cudaError_t bp_launch_peer_sync(bp_attn_ctx* c, cudaStream_t s, uint32_t slot);
 // Book-keeping of the rule above. A launch that wrote rows [row0, ...) of `layer`; a launch of
 // `ctas` CTAs that hold one SM each; the first row of `layer` a reader must not request before
 // its dependency wait (UINT32_MAX: none).

@@ -338,7 +338,6 @@ void bp_attn_destroy(bp_attn_ctx* c) {
   cudaFree(c->epochs);
   cudaFree(c->px_epoch);
   cudaFree(c->pxf_dev);
-  cudaFree(c->px_done);
   free(c->row_mark);
   free(c->row_from);
   cudaFree(c->pf_kv16);
@@ -440,16 +439,11 @@ int bp_set_peer_exchange(bp_attn_ctx* c, uint32_t n_ranks, const uint64_t* out_p
   }
   if (!c->px_dev) BP_CUDA(c, cudaMalloc(&c->px_dev, BP_MAX_PEERS * sizeof(__half*)));
   if (!c->pxf_dev) BP_CUDA(c, cudaMalloc(&c->pxf_dev, (BP_MAX_PEERS + 2) * sizeof(uint32_t*)));
-  if (!c->px_done) {
-    BP_CUDA(c, cudaMalloc(&c->px_done, 64 * sizeof(uint32_t)));
-    BP_CUDA(c, cudaMemset(c->px_done, 0, 64 * sizeof(uint32_t)));
-  }
   BP_CUDA(c, cudaDeviceSynchronize());  // no kernel may still read the old addresses
   BP_CUDA(c, cudaMemcpy(c->px_dev, c->px_out, n_ranks * sizeof(__half*), cudaMemcpyHostToDevice));
   {  // the decode kernel's table: every rank's counters, then this rank's two book-keeping arrays
     uint32_t* tab[BP_MAX_PEERS + 2] = {};
     for (uint32_t r = 0; r < n_ranks; r++) tab[r] = c->px_flag[r];
-    tab[BP_MAX_PEERS] = c->px_done;
     tab[BP_MAX_PEERS + 1] = c->px_epoch;
     BP_CUDA(c, cudaMemcpy(c->pxf_dev, tab, sizeof tab, cudaMemcpyHostToDevice));
   }
@@ -477,16 +471,13 @@ int bp_set_prefill_exchange(bp_attn_ctx* c, uint32_t n_ranks, const uint64_t* ou
   return BP_OK;
 }
 
-static int peer_meet(bp_attn_ctx* c, void* stream, uint32_t slot, bool signal) {
+int bp_peer_sync(bp_attn_ctx* c, void* stream, uint32_t slot) {
   if (int s = enter(c)) return s;
   if (c->n_px == 0) return fail_config(c, "no peer exchange is set");
   if (slot >= 64) return fail_config(c, "peer sync slot must be below 64");
-  BP_CUDA(c, bp_launch_peer_sync(c, static_cast<cudaStream_t>(stream), slot, signal));
+  BP_CUDA(c, bp_launch_peer_sync(c, static_cast<cudaStream_t>(stream), slot));
   return BP_OK;
 }
-
-int bp_peer_sync(bp_attn_ctx* c, void* stream, uint32_t slot) { return peer_meet(c, stream, slot, true); }
-int bp_peer_wait(bp_attn_ctx* c, void* stream, uint32_t slot) { return peer_meet(c, stream, slot, false); }
 
 uint32_t bp_attn_max_prefill(const bp_attn_ctx* c) {
   if (!c) return 0;
@@ -830,11 +821,8 @@ int bp_set_option(bp_attn_ctx* c, const char* name, uint32_t value) {
   } else if (strcmp(name, "decode_v_preload") == 0) {
     c->opt_vpre = value != 0;
     return BP_OK;
-  } else if (strcmp(name, "peer_signal_in_kernel") == 0) {
-    c->opt_px_signal = value != 0;
-    return BP_OK;
-  } else if (strcmp(name, "peer_wait_in_kernel") == 0) {
-    c->opt_px_wait = value != 0;
+  } else if (strcmp(name, "peer_meet_in_kernel") == 0) {
+    c->opt_px_meet = value != 0;
     return BP_OK;
   } else if (strcmp(name, "tma_l2_promotion") == 0) {
     if (value > 3) return fail_config(c, "tma_l2_promotion must be 0 (256 B), 1 (128 B), 2 (64 B) or 3 (none)");

@@ -80,7 +80,6 @@ extern "C" {
     ) -> c_int;
     pub fn bp_set_prefill_exchange(ctx: *mut bp_attn_ctx, n_ranks: u32, out_ptrs: *const u64) -> c_int;
     pub fn bp_peer_sync(ctx: *mut bp_attn_ctx, stream: *mut c_void, slot: u32) -> c_int;
-    pub fn bp_peer_wait(ctx: *mut bp_attn_ctx, stream: *mut c_void, slot: u32) -> c_int;
     pub fn bp_attn_prefill(
         ctx: *mut bp_attn_ctx, stream: *mut c_void, layer: u32, q: *const c_void, out: *mut c_void, m: u32
     ) -> c_int;

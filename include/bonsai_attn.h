@@ -150,18 +150,17 @@ int bp_set_prefill_exchange(bp_attn_ctx* ctx, uint32_t n_ranks, const uint64_t* 
  * = layer mod 64 when the next operation consumes that layer's gathered row,
  * or once per token when nothing in between does. */
 int bp_peer_sync(bp_attn_ctx* ctx, void* stream, uint32_t slot);
-/* The waiting half of bp_peer_sync alone, for use with the option
- * "peer_signal_in_kernel" = 1: then the last CTA of every tcgen05 decode launch
- * signals slot (layer mod 64) to all ranks itself, right after its peer stores,
- * and no kernel of its own is needed on the producer side. The consumer of a
- * gathered row waits for its slot before reading it: with bp_peer_wait on the
- * stream, or, with the option "peer_wait_in_kernel" = 1, inside the decode
- * kernel of the next layer (layer L waits for slot (L - 1) mod 64 before it
- * ends, standing in for the operation that would consume that row; the last
- * layer's slot is left to bp_peer_wait). Every signalled slot must be waited
- * for exactly once, by either means, before it is signalled again. Bounded; a
- * timeout latches BP_ERR_TIMEOUT. No counterpart in the reference. */
-int bp_peer_wait(bp_attn_ctx* ctx, void* stream, uint32_t slot);
+/* Meeting without a kernel of its own: with the option "peer_meet_in_kernel" = 1
+ * the tcgen05 decode kernel of every layer L >= 1 holds the meeting of layer
+ * L - 1 on slot (L - 1) mod 64 itself. Once the kernels before it on the stream
+ * are complete (layer L - 1's peer stores have landed by then) one of its
+ * threads tells every rank, and before the grid ends one thread waits (bounded;
+ * a timeout latches BP_ERR_TIMEOUT) until every rank has said so: the decode
+ * kernel stands in for the consumer of layer L - 1's gathered row, and the
+ * meeting costs no launch and lies off the kernel's own critical path. The
+ * caller must then NOT call bp_peer_sync for those slots; the LAST layer's row
+ * has no next layer and is met with bp_peer_sync(ctx, stream, (n_layer - 1) mod
+ * 64) once per token. All ranks must make the same calls in the same order. */
 
 /* `dispatch_attention(.., pos = 0, m_tokens = m, is_prefill = true)`
  * (src/forward.rs:501-532, params src/model.rs:195-210, kernel
@@ -275,7 +274,7 @@ int bp_set_variant(bp_attn_ctx* ctx, uint32_t variant);
  * 2^18, about 0.2 us each). The peer exchange needs "exclusive_device" = 1.
  * Bounds of the device-side waits: "wait_limit" (polls of an mbarrier or of a
  * meeting counter before a kernel gives up, default 2^22) and "merge_poll_limit".
- * Peer exchange: "peer_signal_in_kernel", "peer_wait_in_kernel" (see bp_peer_wait). */
+ * Peer exchange: "peer_meet_in_kernel" (see above, after bp_peer_sync). */
 int bp_set_option(bp_attn_ctx* ctx, const char* name, uint32_t value);
 /* Development aid: with the option "debug_counters" set to 1 the tcgen05 decode
  * kernel's first CTA records, per warp role (producer, UMMA issuer, softmax,

@@ -96,9 +96,9 @@ def test_meeting_that_never_completes_times_out_and_latches():
         fresh.close()
 
 
-def test_in_kernel_wait_that_never_completes_times_out():
-    """The same with the consumer-side wait inside the decode kernel (option peer_wait_in_kernel): layer
-    1's kernel waits for layer 0's meeting, which the absent second rank never joins."""
+def test_in_kernel_meeting_that_never_completes_times_out():
+    """The same with the meeting inside the decode kernel (option peer_meet_in_kernel): layer 1's kernel
+    signals layer 0's slot to both ranks and waits for both; the absent second rank never signals."""
     sh = O.Shape(n_layer=2, n_head=16, n_kv_head=4, max_seq=512)
     gen = torch.Generator(device="cuda")
     gen.manual_seed(5)
@@ -112,73 +112,55 @@ def test_in_kernel_wait_that_never_completes_times_out():
         gathered = [torch.zeros(sh.n_layer, 2 * sh.q_dim, dtype=torch.float16, device="cuda") for _ in range(2)]
         flags = [torch.zeros(64, dtype=torch.int32, device="cuda") for _ in range(2)]
         ctx.set_peer_exchange([g.data_ptr() for g in gathered], [f.data_ptr() for f in flags])
-        ctx.set_option("peer_signal_in_kernel", 1)
-        ctx.set_option("peer_wait_in_kernel", 1)
+        ctx.set_option("peer_meet_in_kernel", 1)
         ctx.set_option("wait_limit", 20000)
         out = torch.zeros(2, sh.q_dim, dtype=torch.float16, device="cuda")
         ctx.dispatch_attention_decode(0, q, out[0], 400)
+        torch.cuda.synchronize()
+        assert ctx.status() == 0 and flags[0][0].item() == 0  # layer 0 holds no meeting
         ctx.dispatch_attention_decode(1, q, out[1], 400)
         torch.cuda.synchronize()
-        assert flags[0][0].item() == 1 and flags[1][0].item() == 1 and flags[0][1].item() == 1
+        assert flags[0][0].item() == 1 and flags[1][0].item() == 1 and flags[0][1].item() == 0
         assert torch.equal(gathered[0][:, :sh.q_dim], out)  # the outputs themselves arrived
         assert ctx.status() == bp.errors.BP_ERR_TIMEOUT
         with pytest.raises(bp.DeviceTimeout):
             ctx.dispatch_attention_decode(0, q, out[0], 400)
 
 
-def test_two_shards_meet_through_the_decode_kernel_itself():
-    """Two KV-head shards as two contexts on this device, launched in an order in which every signal
-    precedes the wait for it (kernels that wait for one another never run concurrently here): each
-    decode launch signals its layer's slot to both ranks from its last CTA, the next layer's launch
-    waits for the previous slot inside the kernel, and bp_peer_wait covers the last layer. Both
-    gathered buffers end up as the two ranks' outputs side by side, token after token."""
-    n_layer, n_head, n_kv_head, ctx_len = 3, 16, 4, 3000
-    q_dim = n_head * 128
+def test_meeting_held_by_the_decode_kernel_itself():
+    """One rank acting as its own peer (kernels that wait for one another cannot run as separate
+    launches on one GPU, so a second rank's kernels are left to the multi-GPU benchmark): every decode
+    launch of layer L >= 1 signals layer L - 1's slot and waits for it, bp_peer_sync meets the last
+    layer, token after token; outputs land in the gathered buffer and every slot counts one meeting
+    per token."""
+    n_layer, ctx_len = 3, 3000
+    sh = O.Shape(n_layer=n_layer, max_seq=ctx_len)
     gen = torch.Generator(device="cuda")
     gen.manual_seed(23)
     w = torch.ones(128, dtype=torch.float16, device="cuda")
-    gathered = [torch.zeros(n_layer, 2 * q_dim, dtype=torch.float16, device="cuda") for _ in range(2)]
-    flags = [torch.zeros(64, dtype=torch.int32, device="cuda") for _ in range(2)]
-    ctxs = [bp.AttnContext(n_layer=n_layer, n_head=n_head, n_kv_head=n_kv_head, max_seq=ctx_len, n_shards=2, shard=s)
-            for s in range(2)]
-    try:
-        qs, plain = [], []
-        for s, ctx in enumerate(ctxs):
-            for layer in range(n_layer):
-                k = torch.randn(ctx_len, n_kv_head * 128, generator=gen, device="cuda").half()
-                v = torch.randn(ctx_len, n_kv_head * 128, generator=gen, device="cuda").half()
-                ctx.dispatch_kv_writeback_fused(layer, k, v, w, 0, ctx_len)
-            q = torch.randn(n_layer, q_dim, generator=gen, device="cuda").half()
-            ref = torch.zeros(n_layer, q_dim, dtype=torch.float16, device="cuda")
-            for layer in range(n_layer):
-                ctx.dispatch_attention_decode(layer, q[layer], ref[layer], ctx_len)
-            qs.append(q)
-            plain.append(ref)
-            ctx.set_peer_exchange([g.data_ptr() for g in gathered], [f.data_ptr() for f in flags])
-            ctx.set_option("peer_signal_in_kernel", 1)
-            ctx.set_option("peer_wait_in_kernel", 1)
-        torch.cuda.synchronize()
-        want = torch.cat(plain, dim=1)
+    with make_ctx(sh) as ctx:
+        for layer in range(n_layer):
+            k = torch.randn(ctx_len, sh.kv_dim, generator=gen, device="cuda").half()
+            v = torch.randn(ctx_len, sh.kv_dim, generator=gen, device="cuda").half()
+            ctx.dispatch_kv_writeback_fused(layer, k, v, w, 0, ctx_len)
+        q = torch.randn(n_layer, sh.q_dim, generator=gen, device="cuda").half()
+        plain = torch.zeros(n_layer, sh.q_dim, dtype=torch.float16, device="cuda")
+        for layer in range(n_layer):
+            ctx.dispatch_attention_decode(layer, q[layer], plain[layer], ctx_len)
+        gathered = torch.zeros(n_layer, sh.q_dim, dtype=torch.float16, device="cuda")
+        flags = torch.zeros(64, dtype=torch.int32, device="cuda")
+        ctx.set_peer_exchange([gathered.data_ptr()], [flags.data_ptr()])
+        ctx.set_option("peer_meet_in_kernel", 1)
         for token in range(3):
-            for g in gathered:
-                g.zero_()
-            out = [torch.zeros(n_layer, q_dim, dtype=torch.float16, device="cuda") for _ in range(2)]
+            gathered.zero_()
+            out = torch.zeros(n_layer, sh.q_dim, dtype=torch.float16, device="cuda")
             for layer in range(n_layer):
-                for s, ctx in enumerate(ctxs):  # both ranks' layer L before anybody's layer L + 1
-                    ctx.dispatch_attention_decode(layer, qs[s][layer], out[s][layer], ctx_len)
-            for ctx in ctxs:
-                ctx.peer_wait(slot=n_layer - 1)
+                ctx.dispatch_attention_decode(layer, q[layer], out[layer], ctx_len)
+            ctx.peer_sync(slot=n_layer - 1)
             torch.cuda.synchronize()
-            for s, ctx in enumerate(ctxs):
-                assert ctx.status() == 0
-                assert torch.equal(out[s], plain[s])
-            for g in gathered:
-                assert torch.equal(g, want)
-            for f in flags:
-                assert f[:n_layer].tolist() == [2 * (token + 1)] * n_layer  # one signal per rank per token
-    finally:
-        for ctx in ctxs:
-            ctx.close()
+            assert ctx.status() == 0
+            assert torch.equal(out, plain) and torch.equal(gathered, plain)
+            assert flags[:n_layer].tolist() == [token + 1] * n_layer
 
 
 def test_decode_is_correct_while_other_work_holds_sms():
