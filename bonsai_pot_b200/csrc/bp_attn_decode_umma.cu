@@ -465,9 +465,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
     }
     pdl_wait();  // q is written by the kernel before this one
     if (p.merge && n_splits > 1) epoch = ld_relaxed_u32(p.epochs + blockIdx.y);  // used in the epilogue
-    if ((p.px_meet & 0xffu) != NO_SLOT && blockIdx.x == 0 && blockIdx.y == 0 && aw == 0 && lane < p.n_px)
-      // everything before this kernel in the stream is complete, the previous layer's peer stores included
-      asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.px_tab[lane] + (p.px_meet & 0xffu)), "r"(1u) : "memory");
+
     // lane l holds dims 4l .. 4l+3 of one head: a Q8_0 block is 8 lanes. One 8-byte load, three
     // shuffles for the block maximum, two 4-byte stores: short straight-line code, because this sits
     // on the critical path of every launch (the first Q K^T waits for it) and runs cold.
@@ -677,6 +675,13 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_cons
     float m_run[4], l_part[4];
 #pragma unroll
     for (int h = 0; h < 4; h++) { m_run[h] = NEG_BIG; l_part[h] = 0.f; }
+    // Producer side of the previous layer's meeting, by a warp that has nothing to do until Q is ready:
+    // once everything before this kernel in the stream is complete (the previous layer's peer stores
+    // included), tell every rank.
+    if ((p.px_meet & 0xffu) != NO_SLOT && blockIdx.x == 0 && blockIdx.y == 0 && warp == U_FIRST_SM_WARP && lane < p.n_px) {
+      pdl_wait();
+      asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.px_tab[lane] + (p.px_meet & 0xffu)), "r"(1u) : "memory");
+    }
     wait(&q_bar, 0);  // the Q block scales in misc->sq are written by prepare_q
 
     for (uint32_t j = w; j < n_jobs; j += NGRP) {
