@@ -6,6 +6,8 @@ from .errors import (ConfigError, ContextOverflow, CudaError, DeviceLost, Device
                      PrefillTooLarge)
 from .attention import AttnContext  # noqa: F401
 from .kv_snapshot import KvSnapshot  # noqa: F401
+from .errors import IoError  # noqa: F401
+from .model import GenerateOptions, Model, Sampler, Session, StopReason  # noqa: F401
 
 __all__ = ["AttnContext", "KvSnapshot", "PotError", "ConfigError", "ContextOverflow", "PrefillTooLarge",
-           "DeviceLost", "CudaError", "DeviceTimeout"]
+           "DeviceLost", "CudaError", "DeviceTimeout", "IoError", "Model", "Session", "Sampler", "GenerateOptions", "StopReason"]

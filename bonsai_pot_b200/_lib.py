@@ -15,6 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "libbonsai_attn.so")
 HEADER = os.path.join(os.path.dirname(HERE), "include", "bonsai_attn.h")
+MODEL_HEADER = os.path.join(os.path.dirname(HERE), "include", "bonsai_model.h")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -30,7 +31,7 @@ def needs_build() -> bool:
     if not os.path.exists(LIB_PATH):
         return True
     built = os.path.getmtime(LIB_PATH)
-    deps = sources() + glob.glob(os.path.join(CSRC, "*.cuh")) + [HEADER]
+    deps = sources() + glob.glob(os.path.join(CSRC, "*.cuh")) + [HEADER, MODEL_HEADER]
     return any(os.path.getmtime(p) > built for p in deps)
 
 
@@ -105,6 +106,68 @@ SIGNATURES = {
     "bp_attn_decode_static_scratch": (_int, [_vp, _vp, _vp, _vp, _vp] + [_u32] * 6),
 }
 
+
+
+class ModelConfig(C.Structure):
+    """`bp_model_config` of include/bonsai_model.h."""
+    _fields_ = [(k, C.c_uint32) for k in ("n_layer", "n_embd", "n_ff", "n_head", "n_kv_head", "head_dim", "n_vocab",
+                                           "eos_token_id", "q_dim", "kv_dim")] + \
+               [("rope_freq_base", C.c_float), ("rms_eps", C.c_float), ("tied_embeddings", C.c_uint32),
+                ("max_seq", C.c_uint32), ("m_max", C.c_uint32)]
+
+
+class SamplerStruct(C.Structure):
+    """`bp_sampler` of include/bonsai_model.h."""
+    _fields_ = [("temperature", C.c_float), ("top_k", C.c_uint32), ("top_p", C.c_float), ("seed", C.c_uint64)]
+
+
+STOP_FN = C.CFUNCTYPE(C.c_int, C.c_uint32, C.c_void_p)
+TOKEN_FN = C.CFUNCTYPE(None, C.c_uint32, C.c_void_p)
+_f32p, _u32p, _pp = C.POINTER(C.c_float), C.POINTER(C.c_uint32), C.POINTER(C.c_void_p)
+_smp = C.POINTER(SamplerStruct)
+
+# name -> (restype, argtypes); must list every symbol include/bonsai_model.h declares.
+MODEL_SIGNATURES = {
+    "bp_op_q1_relayout": (_int, [_vp, _vp, _vp, _u64]),
+    "bp_op_matvec_q1_0": (_int, [_vp, _vp, _vp, _u32, _u32, _vp, _vp, _u32]),
+    "bp_op_matvec_q1_0_fused_normed": (_int, [_vp, _u32, _vp, _vp, C.c_float, _u32, _pp, _pp, _u32p, _pp]),
+    "bp_op_matvec_q1_0_silu": (_int, [_vp, _vp, _vp, _u32, _u32, _vp, _vp, _vp, _u32]),
+    "bp_op_rms_norm": (_int, [_vp, _vp, _vp, _vp, _u32, _u32, C.c_float]),
+    "bp_op_silu_mul": (_int, [_vp, _vp, _vp, _vp, _u64]),
+    "bp_op_embed": (_int, [_vp, _vp, _vp, _u32, _vp, _u32, _vp]),
+    "bp_op_quantize_q8_0": (_int, [_vp, _vp, _u32, _u32, _vp, _vp]),
+    "bp_op_matmul_q1_0_q8_0": (_int, [_vp, _vp, _vp, _u32, _u32, _u32, _vp, _vp, _vp, _u32]),
+    "bp_op_topk_reduce": (_int, [_vp, _vp, _u32, _u32, _vp, _vp]),
+    "bp_model_check_dir": (_int, [C.c_char_p, C.c_char_p, C.c_size_t]),
+    "bp_model_load": (_int, [C.c_char_p, _u32, C.c_int32, _pp]),
+    "bp_model_free": (None, [_vp]),
+    "bp_model_get_config": (_int, [_vp, C.POINTER(ModelConfig)]),
+    "bp_model_last_error": (C.c_char_p, [_vp]),
+    "bp_model_error_detail": (None, [_vp, C.POINTER(ErrorDetail)]),
+    "bp_model_attn": (_vp, [_vp]),
+    "bp_model_step_topk": (_int, [_vp, _u32, _u32, _u32, _f32p, _u32p]),
+    "bp_model_prefill_topk": (_int, [_vp, _u32p, _u32, _u32, _f32p, _u32p]),
+    "bp_model_prefill_loop_topk": (_int, [_vp, _u32p, _u32, _u32, _u32, _f32p, _u32p]),
+    "bp_model_read_hidden": (_int, [_vp, _u32, _vp]),
+    "bp_model_read_logits": (_int, [_vp, _vp]),
+    "bp_model_attn_tap": (_int, [_vp, _u32, _vp]),
+    "bp_sampler_default": (None, [_smp]),
+    "bp_effective_k": (_u32, [_smp]),
+    "bp_uniform_f32": (C.c_float, [_u64]),
+    "bp_sample_from_topk": (_u32, [_f32p, _u32p, _u32, _smp, _u32]),
+    "bp_session_create": (_int, [_vp, _pp]),
+    "bp_session_free": (None, [_vp]),
+    "bp_session_pos": (_u32, [_vp]),
+    "bp_session_reset": (None, [_vp]),
+    "bp_session_prefill": (_int, [_vp, _u32p, _u32, _smp, _u32p]),
+    "bp_session_prefill_one_at_a_time": (_int, [_vp, _u32p, _u32, _smp, _u32p]),
+    "bp_session_step": (_int, [_vp, _u32, _smp, _u32p]),
+    "bp_session_generate": (_int, [_vp, _u32, _u32, _smp, STOP_FN, TOKEN_FN, _vp, _u32p, _u32p, C.POINTER(C.c_int32)]),
+    "bp_session_snapshot_size": (_u64, [_vp]),
+    "bp_session_snapshot": (_int, [_vp, _vp, _u64]),
+    "bp_session_restore": (_int, [_vp, _vp, _u64]),
+}
+
 _LIB = None
 
 
@@ -121,7 +184,7 @@ def load() -> C.CDLL:
             if not os.path.exists(LIB_PATH):
                 raise ImportError(f"libbonsai_attn.so is missing and could not be built: {e}") from e
     lib = C.CDLL(path)
-    for name, (res, args) in SIGNATURES.items():
+    for name, (res, args) in list(SIGNATURES.items()) + list(MODEL_SIGNATURES.items()):
         fn = getattr(lib, name)  # AttributeError here = the header and the library disagree
         fn.restype = res
         fn.argtypes = args

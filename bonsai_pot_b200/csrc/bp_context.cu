@@ -224,6 +224,7 @@ const char* bp_strerror(int status) {
     case BP_ERR_CUDA: return "CUDA error";
     case BP_ERR_TIMEOUT: return "device-side wait timed out";
     case BP_ERR_NULL: return "null pointer argument";
+    case BP_ERR_IO: return "io error";
     default: return "unknown status";
   }
 }

@@ -1,0 +1,557 @@
+// The non-attention operators of one decode / prefill layer on Q1_0 weights: what the reference's
+// matvec_q1_0*.wgsl, rms_norm.wgsl, silu_mul.wgsl, embed.wgsl, quantize_q8_0.wgsl,
+// matmul_q1_0_q8_0.wgsl and topk_reduce.wgsl compute, with the same operation ORDER, so that the
+// f16 / f32 results are the reference's bit for bit under the evaluation rules the CPU restatement
+// states (f16 operations rounded one by one, no FMA contraction, correctly rounded division and
+// reciprocal square root, a fixed exp): every rounded operation below is an explicit intrinsic.
+//
+// Matvec family (one token): a row is reduced by 8 lanes, lane tx taking the 128-weight blocks
+// b = tx (mod 8) in order, as the shaders do (matvec_q1_0.wgsl:84-133). Inside a block the four f16
+// accumulators of the shader's vec4<f16> are two half2 registers; a weight's sign is applied by
+// flipping the activation's sign bit. The sign bits are re-laid out once at load (bp_q1_relayout)
+// so that the xor mask of a half2 is ONE shift and ONE and: word 0 / 1 of a block hold, for the
+// groups g = 0..15 / 16..31, the flip bit of element 4 g at bit 15 - g and of element 4 g + 1 at
+// bit 31 - g; words 2 / 3 the same for elements 4 g + 2, 4 g + 3. A lane works on four rows at
+// once (the activations it reads from shared memory serve all four).
+#include <cuda_fp16.h>
+#include <math.h>
+
+#include "bp_common.cuh"
+#include "bp_ptx.cuh"
+#include "bp_q1_ops.cuh"
+
+namespace {
+
+using namespace bp;
+constexpr unsigned FULL = 0xffffffffu;
+constexpr uint32_t MV_THREADS = 128;          // the invocation count of the fused shader: its sum of squares is per invocation
+constexpr uint32_t MV_ROWS_PER_LANE = 4;
+constexpr uint32_t MV_ROWS_PER_CTA = (MV_THREADS / 8) * MV_ROWS_PER_LANE;  // 64
+constexpr uint32_t XB_STRIDE = 128 + 8;       // halves per staged block: 16 bytes of padding keep the 8 lanes of a row off each other's banks
+
+__device__ __forceinline__ float exp_det(float x) {  // the restatement's orc_exp_det, operation for operation
+  x = fminf(fmaxf(x, -87.3f), 88.7f);
+  const float n = rintf(__fmul_rn(x, 1.44269504088896341f));
+  float r = __fmaf_rn(n, -0.693359375f, x);
+  r = __fmaf_rn(n, 2.12194440e-4f, r);
+  float p = __fmaf_rn(r, 1.0f / 720.0f, 1.0f / 120.0f);
+  p = __fmaf_rn(r, p, 1.0f / 24.0f);
+  p = __fmaf_rn(r, p, 1.0f / 6.0f);
+  p = __fmaf_rn(r, p, 0.5f);
+  p = __fmaf_rn(r, p, 1.0f);
+  p = __fmaf_rn(r, p, 1.0f);
+  return ldexpf(p, static_cast<int>(n));
+}
+
+// f16(g / (1 + exp(-g))) * up, in f16 (silu_mul.wgsl:22-26)
+__device__ __forceinline__ __half silu_times_up(__half gate, __half up) {
+  const float g = __half2float(gate);
+  const float s = __fdiv_rn(g, __fadd_rn(1.0f, exp_det(-g)));
+  return __hmul(__float2half_rn(s), up);
+}
+
+// subgroupAdd of a 32-lane subgroup: xor butterfly 16, 8, 4, 2, 1
+__device__ __forceinline__ float butterfly32(float v) {
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) v = __fadd_rn(v, __shfl_xor_sync(FULL, v, off));
+  return v;
+}
+
+// Workgroup sum of rms_norm.wgsl:62-78 / matvec_q1_0_fused_normed.wgsl:131-146 for a CTA of NW warps:
+// per-warp butterfly, partial of warp s into lane s of warp 0 (zero elsewhere), butterfly again.
+template <uint32_t NW>
+__device__ __forceinline__ float workgroup_sum(float v, float* part /* shared, 32 floats */) {
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const float s = butterfly32(v);
+  if (lane == 0) part[warp] = s;
+  __syncthreads();
+  if (warp == 0) {
+    const float c = lane < NW ? part[lane] : 0.0f;
+    const float f = butterfly32(c);
+    if (lane == 0) part[0] = f;
+  }
+  __syncthreads();
+  const float total = part[0];
+  __syncthreads();
+  return total;
+}
+
+struct MvRange {
+  const __half* d;        // block scales [n][nb]
+  const uint4* bits;      // re-laid-out sign words [n][nb]
+  __half* out;
+  uint32_t n;
+};
+struct MvParams {
+  MvRange r[3];
+  uint32_t n_ranges, n_total, k;
+  const __half* x;        // input activations (MODE 0, 1) or gate (MODE 2)
+  const __half* aux;      // norm weight (MODE 1) or up (MODE 2)
+  float eps;
+  uint32_t accumulate;
+};
+
+// MODE 0: y (+)= W x (matvec_q1_0.wgsl); 1: W (rms_norm(x) * w), scales times inv_rms
+// (matvec_q1_0_fused_normed.wgsl); 2: y (+)= W (silu(gate) * up) (matvec_q1_0_silu.wgsl).
+template <int MODE>
+__global__ void __launch_bounds__(MV_THREADS) matvec_q1_kernel(const MvParams p) {
+  extern __shared__ __align__(16) uint8_t mv_smem[];
+  __shared__ float part[32];
+  __half* xs = reinterpret_cast<__half*>(mv_smem);
+  pdl_launch_dependents();
+  pdl_wait();  // the activations come from the kernel before this one
+  const uint32_t tid = threadIdx.x, nb = p.k / 128u;
+  float inv_rms = 1.0f;
+  // ---- stage the activations: block b at xs + b * XB_STRIDE ----
+  if (MODE == 1) {
+    float ssq = 0.0f;
+    for (uint32_t v = tid; v < p.k / 4u; v += MV_THREADS) {
+      const uint2 raw = *reinterpret_cast<const uint2*>(p.x + 4u * v);
+      const uint2 wr = *reinterpret_cast<const uint2*>(p.aux + 4u * v);
+      const __half2 x01 = *reinterpret_cast<const __half2*>(&raw.x), x23 = *reinterpret_cast<const __half2*>(&raw.y);
+      const float2 f01 = __half22float2(x01), f23 = __half22float2(x23);
+      ssq = __fadd_rn(ssq, __fmul_rn(f01.x, f01.x));
+      ssq = __fadd_rn(ssq, __fmul_rn(f01.y, f01.y));
+      ssq = __fadd_rn(ssq, __fmul_rn(f23.x, f23.x));
+      ssq = __fadd_rn(ssq, __fmul_rn(f23.y, f23.y));
+      const __half2 y01 = __hmul2(x01, *reinterpret_cast<const __half2*>(&wr.x));
+      const __half2 y23 = __hmul2(x23, *reinterpret_cast<const __half2*>(&wr.y));
+      uint2 o;
+      o.x = *reinterpret_cast<const uint32_t*>(&y01);
+      o.y = *reinterpret_cast<const uint32_t*>(&y23);
+      *reinterpret_cast<uint2*>(xs + (v >> 5) * XB_STRIDE + 4u * (v & 31u)) = o;
+    }
+    const float total = workgroup_sum<MV_THREADS / 32>(ssq, part);
+    inv_rms = __frsqrt_rn(__fadd_rn(__fdiv_rn(total, static_cast<float>(p.k)), p.eps));
+  } else {
+    for (uint32_t v = tid; v < p.k / 4u; v += MV_THREADS) {
+      uint2 o = *reinterpret_cast<const uint2*>(p.x + 4u * v);
+      if (MODE == 2) {
+        const uint2 u = *reinterpret_cast<const uint2*>(p.aux + 4u * v);
+        const __half* g4 = reinterpret_cast<const __half*>(&o);
+        const __half* u4 = reinterpret_cast<const __half*>(&u);
+        __half y[4];
+#pragma unroll
+        for (int c = 0; c < 4; c++) y[c] = silu_times_up(g4[c], u4[c]);
+        o = *reinterpret_cast<const uint2*>(y);
+      }
+      *reinterpret_cast<uint2*>(xs + (v >> 5) * XB_STRIDE + 4u * (v & 31u)) = o;
+    }
+    __syncthreads();
+  }
+
+  // ---- rows: lane = (row slot rs = lane / 8, tx = lane % 8); a lane owns rows base + rs + 4 j ----
+  const uint32_t warp = tid >> 5, lane = tid & 31, tx = lane & 7, rs = lane >> 3;
+  const uint32_t row0 = blockIdx.x * MV_ROWS_PER_CTA + warp * (4 * MV_ROWS_PER_LANE) + rs;
+  const __half* d_row[MV_ROWS_PER_LANE];
+  const uint4* b_row[MV_ROWS_PER_LANE];
+  __half* out_ptr[MV_ROWS_PER_LANE];
+  bool valid[MV_ROWS_PER_LANE];
+#pragma unroll
+  for (uint32_t j = 0; j < MV_ROWS_PER_LANE; j++) {
+    uint32_t row = row0 + 4u * j;
+    valid[j] = row < p.n_total;
+    if (!valid[j]) row = 0;
+    uint32_t ri = 0;
+    if (p.n_ranges > 1 && row >= p.r[0].n) {
+      row -= p.r[0].n;
+      ri = 1;
+      if (p.n_ranges > 2 && row >= p.r[1].n) {
+        row -= p.r[1].n;
+        ri = 2;
+      }
+    }
+    d_row[j] = p.r[ri].d + static_cast<size_t>(row) * nb;
+    b_row[j] = p.r[ri].bits + static_cast<size_t>(row) * nb;
+    out_ptr[j] = p.r[ri].out + row;
+  }
+  float acc[MV_ROWS_PER_LANE];
+#pragma unroll
+  for (uint32_t j = 0; j < MV_ROWS_PER_LANE; j++) acc[j] = 0.0f;
+  const __half2 zero2 = __float2half2_rn(0.0f);
+  for (uint32_t b = tx; b < nb; b += 8) {
+    uint4 w[MV_ROWS_PER_LANE];
+    __half dh[MV_ROWS_PER_LANE];
+#pragma unroll
+    for (uint32_t j = 0; j < MV_ROWS_PER_LANE; j++) {
+      w[j] = __ldg(b_row[j] + b);
+      dh[j] = __ldg(d_row[j] + b);
+    }
+    __half2 a01[MV_ROWS_PER_LANE], a23[MV_ROWS_PER_LANE];
+#pragma unroll
+    for (uint32_t j = 0; j < MV_ROWS_PER_LANE; j++) a01[j] = a23[j] = zero2;
+    const uint4* xb = reinterpret_cast<const uint4*>(xs + b * XB_STRIDE);
+#pragma unroll
+    for (uint32_t half = 0; half < 2; half++) {  // groups 0..15, then 16..31
+#pragma unroll
+      for (uint32_t g2 = 0; g2 < 8; g2++) {      // two groups per 16-byte read
+        const uint4 xv = xb[half * 8 + g2];
+#pragma unroll
+        for (uint32_t gg = 0; gg < 2; gg++) {
+          const uint32_t g = 2 * g2 + gg;
+          const uint32_t x01 = gg ? xv.z : xv.x, x23 = gg ? xv.w : xv.y;
+#pragma unroll
+          for (uint32_t j = 0; j < MV_ROWS_PER_LANE; j++) {
+            const uint32_t w01 = half ? w[j].y : w[j].x, w23 = half ? w[j].w : w[j].z;
+            const uint32_t s01 = x01 ^ ((w01 << g) & 0x80008000u);
+            const uint32_t s23 = x23 ^ ((w23 << g) & 0x80008000u);
+            a01[j] = __hadd2(a01[j], *reinterpret_cast<const __half2*>(&s01));
+            a23[j] = __hadd2(a23[j], *reinterpret_cast<const __half2*>(&s23));
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (uint32_t j = 0; j < MV_ROWS_PER_LANE; j++) {
+      const __half ls = __hadd(__hadd(__hadd(__low2half(a01[j]), __high2half(a01[j])), __low2half(a23[j])), __high2half(a23[j]));
+      float d = __half2float(dh[j]);
+      if (MODE == 1) d = __fmul_rn(d, inv_rms);
+      acc[j] = __fadd_rn(acc[j], __fmul_rn(d, __half2float(ls)));
+    }
+  }
+#pragma unroll
+  for (uint32_t j = 0; j < MV_ROWS_PER_LANE; j++) {
+    float a = acc[j];
+    a = __fadd_rn(a, __shfl_xor_sync(FULL, a, 1));
+    a = __fadd_rn(a, __shfl_xor_sync(FULL, a, 2));
+    a = __fadd_rn(a, __shfl_xor_sync(FULL, a, 4));
+    if (tx == 0 && valid[j]) {
+      if (MODE != 1 && p.accumulate) a = __fadd_rn(__half2float(*out_ptr[j]), a);
+      *out_ptr[j] = __float2half_rn(a);
+    }
+  }
+}
+
+// rms_norm.wgsl:41-85: one CTA of 512 threads per group.
+__global__ void __launch_bounds__(512) rms_norm_kernel(const __half* in, __half* out, const __half* w, uint32_t n, float eps) {
+  __shared__ float part[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const __half* src = in + static_cast<size_t>(blockIdx.x) * n;
+  __half* dst = out + static_cast<size_t>(blockIdx.x) * n;
+  float s = 0.0f;
+  for (uint32_t i = threadIdx.x; i < n; i += 512) {
+    const float v = __half2float(src[i]);
+    s = __fadd_rn(s, __fmul_rn(v, v));
+  }
+  const float total = workgroup_sum<16>(s, part);
+  const __half inv_h = __float2half_rn(__frsqrt_rn(__fadd_rn(__fdiv_rn(total, static_cast<float>(n)), eps)));
+  for (uint32_t i = threadIdx.x; i < n; i += 512) dst[i] = __hmul(__hmul(src[i], inv_h), w[i]);
+}
+
+// silu_mul.wgsl:18-27
+__global__ void __launch_bounds__(256) silu_mul_kernel(const __half* gate, const __half* up, __half* out, uint64_t n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const uint64_t i = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x;
+  if (i < n) out[i] = silu_times_up(gate[i], up[i]);
+}
+
+// embed.wgsl:37-52: thread = one 16-byte unit (8 weights) of an output row
+__global__ void __launch_bounds__(256) embed_kernel(const __half* d, const uint8_t* qs, uint32_t k, const uint32_t* tokens,
+                                                    uint32_t m, __half* x) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const uint32_t units = k / 8u;
+  const uint64_t idx = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x;
+  if (idx >= static_cast<uint64_t>(m) * units) return;
+  const uint32_t t = static_cast<uint32_t>(idx / units), u = static_cast<uint32_t>(idx % units);
+  const uint64_t row = tokens[t];
+  const uint32_t nb = k / 128u, b = u / 16u;
+  const __half dp = d[row * nb + b], dn = __hneg(dp);
+  const uint32_t byte = qs[(row * nb + b) * 16u + (u & 15u)];
+  __half o[8];
+#pragma unroll
+  for (int bit = 0; bit < 8; bit++) o[bit] = (byte >> bit) & 1u ? dp : dn;
+  *reinterpret_cast<uint4*>(x + static_cast<size_t>(t) * k + 8u * u) = *reinterpret_cast<const uint4*>(o);
+}
+
+// quantize_q8_0.wgsl:49-106: one warp per block of 32 values
+__global__ void __launch_bounds__(256) quantize_q8_kernel(const __half* x, uint64_t n_blocks, float* d_out, int8_t* qs_out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const uint64_t blk = static_cast<uint64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (blk >= n_blocks) return;
+  const uint32_t lane = threadIdx.x & 31;
+  const float v = __half2float(x[blk * 32u + lane]);
+  float amax = fabsf(v);
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(FULL, amax, off));
+  const float d = __fdiv_rn(amax, 127.0f);
+  const float id = d > 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+  const float r = fminf(fmaxf(rintf(__fmul_rn(v, id)), -127.0f), 127.0f);
+  qs_out[blk * 32u + lane] = static_cast<int8_t>(static_cast<int>(r));
+  if (lane == 0) d_out[blk] = d;
+}
+
+// matmul_q1_0_q8_0.wgsl:57-293: y[m][n] (+)= sum_b sum_s (a_d[m][4 b + s] * w_d[n][b]) * f32(sumi), in that
+// order. A CTA owns 64 x 64 outputs, a thread 4 (m) x 4 (n); the integer dot of 32 signs with 32 int8 values
+// is 2 * dot(a, bit) - sum(a), eight dp4a each.
+constexpr uint32_t MM_T = 64;
+__global__ void __launch_bounds__(256) matmul_q1_q8_kernel(const __half* w_d, const uint8_t* w_qs, uint32_t k, uint32_t n, uint32_t m,
+                                                           const float* a_d, const int8_t* a_qs, __half* y, uint32_t accumulate) {
+  __shared__ float s_wd[MM_T];
+  __shared__ uint32_t s_wb[MM_T][4 + 1];     // sign words of the block, one row per weight row
+  __shared__ float s_ad[MM_T][4];
+  __shared__ uint32_t s_aq[MM_T][32 + 1];    // 128 int8 of the block per token
+  __shared__ int s_asum[MM_T][4];
+  pdl_launch_dependents();
+  pdl_wait();
+  const uint32_t tid = threadIdx.x, lx = tid & 15, ly = tid >> 4;
+  const uint32_t n_base = blockIdx.x * MM_T, m_base = blockIdx.y * MM_T;
+  const uint32_t nb1 = k / 128u, nb8 = k / 32u;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; i++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) acc[i][j] = 0.0f;
+  for (uint32_t b = 0; b < nb1; b++) {
+    if (tid < MM_T) {
+      const uint32_t ni = n_base + tid;
+      s_wd[tid] = ni < n ? __half2float(w_d[static_cast<size_t>(ni) * nb1 + b]) : 0.0f;
+    }
+    {
+      const uint32_t nl = tid >> 2, s = tid & 3, ni = n_base + nl;
+      s_wb[nl][s] = ni < n ? *reinterpret_cast<const uint32_t*>(w_qs + (static_cast<size_t>(ni) * nb1 + b) * 16u + 4u * s) : 0u;
+      const uint32_t ml = tid >> 2, mi = m_base + ml;
+      s_ad[ml][s] = mi < m ? a_d[static_cast<size_t>(mi) * nb8 + 4u * b + s] : 0.0f;
+    }
+    for (uint32_t li = 0; li < 8; li++) {
+      const uint32_t idx = li * 256 + tid, ml = idx >> 5, su = idx & 31, mi = m_base + ml;
+      s_aq[ml][su] = mi < m ? *reinterpret_cast<const uint32_t*>(a_qs + static_cast<size_t>(mi) * k + 128u * b + 4u * su) : 0u;
+    }
+    __syncthreads();
+    {
+      const uint32_t ml = tid >> 2, s = tid & 3;
+      int t = 0;
+#pragma unroll
+      for (int u = 0; u < 8; u++) t = __dp4a(static_cast<int>(s_aq[ml][8 * s + u]), 0x01010101, t);
+      s_asum[ml][s] = t;
+    }
+    __syncthreads();
+#pragma unroll
+    for (uint32_t s = 0; s < 4; s++) {
+      uint32_t spread[4][8];  // per weight row: 8 words whose bytes are 1 where the sign bit is set
+#pragma unroll
+      for (int tn = 0; tn < 4; tn++) {
+        const uint32_t bw = s_wb[lx * 4 + tn][s];
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+          const uint32_t bits = (bw >> (4 * u)) & 0xFu;
+          spread[tn][u] = (bits & 1u) | ((bits & 2u) << 7) | ((bits & 4u) << 14) | ((bits & 8u) << 21);
+        }
+      }
+#pragma unroll
+      for (int tm = 0; tm < 4; tm++) {
+        const uint32_t ml = ly * 4 + tm;
+        const float ad = s_ad[ml][s];
+        const int asum = s_asum[ml][s];
+        int pos[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+          const int a = static_cast<int>(s_aq[ml][8 * s + u]);
+#pragma unroll
+          for (int tn = 0; tn < 4; tn++) pos[tn] = __dp4a(a, static_cast<int>(spread[tn][u]), pos[tn]);
+        }
+#pragma unroll
+        for (int tn = 0; tn < 4; tn++) {
+          const float scale = __fmul_rn(ad, s_wd[lx * 4 + tn]);
+          acc[tm][tn] = __fadd_rn(acc[tm][tn], __fmul_rn(scale, static_cast<float>(2 * pos[tn] - asum)));
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int tm = 0; tm < 4; tm++) {
+    const uint32_t mi = m_base + ly * 4 + tm;
+    if (mi >= m) continue;
+#pragma unroll
+    for (int tn = 0; tn < 4; tn++) {
+      const uint32_t ni = n_base + lx * 4 + tn;
+      if (ni >= n) continue;
+      __half* dst = y + static_cast<size_t>(mi) * n + ni;
+      const float v = accumulate ? __fadd_rn(__half2float(*dst), acc[tm][tn]) : acc[tm][tn];
+      *dst = __float2half_rn(v);
+    }
+  }
+}
+
+// topk_reduce.wgsl:59-196, the same steps on the same lists (256 per-thread heaps of 32, heapsort, then
+// log2(256) bitonic merge rounds), so that ties fall exactly where the shader's comparisons put them.
+// List j's element i sits at [i][j] in shared memory (bank = j) instead of [j][i]: same lists, no conflicts.
+constexpr uint32_t TK_WG = 256, TK_K = 32;
+__device__ __forceinline__ void tk_sift(float* val, uint32_t* idx, uint32_t j, uint32_t limit) {
+  uint32_t i = 0;
+  for (;;) {
+    const uint32_t l = 2 * i + 1, r = l + 1;
+    uint32_t smallest = i;
+    if (l < limit && val[l * TK_WG + j] < val[smallest * TK_WG + j]) smallest = l;
+    if (r < limit && val[r * TK_WG + j] < val[smallest * TK_WG + j]) smallest = r;
+    if (smallest == i) break;
+    const float tv = val[i * TK_WG + j]; val[i * TK_WG + j] = val[smallest * TK_WG + j]; val[smallest * TK_WG + j] = tv;
+    const uint32_t ti = idx[i * TK_WG + j]; idx[i * TK_WG + j] = idx[smallest * TK_WG + j]; idx[smallest * TK_WG + j] = ti;
+    i = smallest;
+  }
+}
+__global__ void __launch_bounds__(TK_WG) topk_kernel(const __half* logits, uint32_t n, uint32_t k, float* out_val, uint32_t* out_idx) {
+  extern __shared__ __align__(16) uint8_t tk_smem[];
+  float* val = reinterpret_cast<float*>(tk_smem);
+  uint32_t* idx = reinterpret_cast<uint32_t*>(tk_smem + TK_WG * TK_K * 4);
+  pdl_launch_dependents();
+  pdl_wait();
+  const uint32_t tid = threadIdx.x;
+  for (uint32_t i = 0; i < TK_K; i++) { val[i * TK_WG + tid] = -1e30f; idx[i * TK_WG + tid] = 0; }
+  const uint32_t n_words = (n + 1) >> 1;
+  float cur_min = -1e30f;  // mirrors val[0] of this thread's heap
+  for (uint32_t w = tid; w < n_words; w += TK_WG) {
+    const __half2 pair = *reinterpret_cast<const __half2*>(logits + 2 * w);
+    const float v0 = __low2float(pair), v1 = __high2float(pair);
+    if (v0 > cur_min) { val[tid] = v0; idx[tid] = 2 * w; tk_sift(val, idx, tid, TK_K); cur_min = val[tid]; }
+    if (2 * w + 1 < n && v1 > cur_min) { val[tid] = v1; idx[tid] = 2 * w + 1; tk_sift(val, idx, tid, TK_K); cur_min = val[tid]; }
+  }
+  for (uint32_t active = TK_K - 1; active > 0; active--) {
+    const float tv = val[tid]; val[tid] = val[active * TK_WG + tid]; val[active * TK_WG + tid] = tv;
+    const uint32_t ti = idx[tid]; idx[tid] = idx[active * TK_WG + tid]; idx[active * TK_WG + tid] = ti;
+    tk_sift(val, idx, tid, active);
+  }
+  __syncthreads();
+  for (uint32_t s = TK_WG / 2; s > 0; s >>= 1) {
+    for (uint32_t kk = tid; kk < s * TK_K; kk += TK_WG) {
+      const uint32_t pair = kk / TK_K, i = kk % TK_K, bi = TK_K - 1 - i;
+      const float av = val[i * TK_WG + pair], bv = val[bi * TK_WG + pair + s];
+      if (bv > av) { val[i * TK_WG + pair] = bv; idx[i * TK_WG + pair] = idx[bi * TK_WG + pair + s]; }
+    }
+    __syncthreads();
+    for (uint32_t stride = TK_K / 2; stride > 0; stride >>= 1) {
+      for (uint32_t kk = tid; kk < s * (TK_K / 2); kk += TK_WG) {
+        const uint32_t pair = kk / (TK_K / 2), local = kk % (TK_K / 2);
+        const uint32_t lo = ((local & ~(stride - 1)) << 1) | (local & (stride - 1)), hi = lo | stride;
+        const float vlo = val[lo * TK_WG + pair], vhi = val[hi * TK_WG + pair];
+        if (vhi > vlo) {
+          const uint32_t ilo = idx[lo * TK_WG + pair];
+          val[lo * TK_WG + pair] = vhi; val[hi * TK_WG + pair] = vlo;
+          idx[lo * TK_WG + pair] = idx[hi * TK_WG + pair]; idx[hi * TK_WG + pair] = ilo;
+        }
+      }
+      __syncthreads();
+    }
+  }
+  const uint32_t kk = k < TK_K ? k : TK_K;
+  if (tid < kk) { out_val[tid] = val[tid * TK_WG]; out_idx[tid] = idx[tid * TK_WG]; }
+}
+
+// Sign bits of one Q1_0 tensor -> the matvec kernels' layout (see the file header). Thread = block.
+__global__ void __launch_bounds__(256) relayout_kernel(const uint8_t* qs, uint4* out, uint64_t n_blocks) {
+  const uint64_t blk = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x;
+  if (blk >= n_blocks) return;
+  const uint4 src = *reinterpret_cast<const uint4*>(qs + blk * 16u);
+  const uint32_t sw[4] = {src.x, src.y, src.z, src.w};
+  uint32_t o[4] = {0, 0, 0, 0};
+  for (uint32_t g = 0; g < 32; g++) {
+    const uint32_t nib = (~(sw[g >> 3] >> (4 * (g & 7)))) & 0xFu;  // flip bits of elements 4 g .. 4 g + 3
+    const uint32_t sh = 15 - (g & 15), hi = g >> 4;
+    o[hi] |= ((nib & 1u) << sh) | (((nib >> 1) & 1u) << (sh + 16));
+    o[2 + hi] |= (((nib >> 2) & 1u) << sh) | (((nib >> 3) & 1u) << (sh + 16));
+  }
+  out[blk] = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+size_t mv_smem_bytes(uint32_t k) { return static_cast<size_t>(k / 128u) * XB_STRIDE * sizeof(__half); }
+
+template <int MODE>
+cudaError_t launch_mv(bool pdl, cudaStream_t s, const MvParams& p) {
+  const size_t smem = mv_smem_bytes(p.k);
+  static size_t configured[3] = {0, 0, 0};
+  if (smem > 48 * 1024 && smem > configured[MODE]) {
+    cudaError_t e = cudaFuncSetAttribute(matvec_q1_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+    configured[MODE] = smem;
+  }
+  const uint32_t ctas = (p.n_total + MV_ROWS_PER_CTA - 1) / MV_ROWS_PER_CTA;
+  return bp_launch(pdl, matvec_q1_kernel<MODE>, dim3(ctas), dim3(MV_THREADS), smem, s, p);
+}
+
+}  // namespace
+
+cudaError_t bp_q1_relayout(cudaStream_t s, const uint8_t* qs, void* out, uint64_t n_blocks) {
+  relayout_kernel<<<static_cast<unsigned>((n_blocks + 255) / 256), 256, 0, s>>>(qs, static_cast<uint4*>(out), n_blocks);
+  return cudaGetLastError();
+}
+
+cudaError_t bp_q1_matvec(bool pdl, cudaStream_t s, const bp_q1_tensor& w, const __half* x, __half* y, bool accumulate) {
+  MvParams p = {};
+  p.r[0] = {w.d, static_cast<const uint4*>(w.bits), y, w.n};
+  p.n_ranges = 1;
+  p.n_total = w.n;
+  p.k = w.k;
+  p.x = x;
+  p.accumulate = accumulate ? 1u : 0u;
+  return launch_mv<0>(pdl, s, p);
+}
+
+cudaError_t bp_q1_matvec_normed(bool pdl, cudaStream_t s, const bp_q1_tensor* w, __half* const* out, uint32_t n_ranges,
+                                const __half* x, const __half* w_norm, float eps) {
+  if (n_ranges == 0 || n_ranges > 3) return cudaErrorInvalidValue;
+  MvParams p = {};
+  p.n_ranges = n_ranges;
+  for (uint32_t r = 0; r < n_ranges; r++) {
+    if (w[r].k != w[0].k || w[r].n % 16u != 0) return cudaErrorInvalidValue;  // the shader's range rule (ROWS_PER_WG = 16)
+    p.r[r] = {w[r].d, static_cast<const uint4*>(w[r].bits), out[r], w[r].n};
+    p.n_total += w[r].n;
+  }
+  p.k = w[0].k;
+  p.x = x;
+  p.aux = w_norm;
+  p.eps = eps;
+  return launch_mv<1>(pdl, s, p);
+}
+
+cudaError_t bp_q1_matvec_silu(bool pdl, cudaStream_t s, const bp_q1_tensor& w, const __half* gate, const __half* up, __half* y,
+                              bool accumulate) {
+  MvParams p = {};
+  p.r[0] = {w.d, static_cast<const uint4*>(w.bits), y, w.n};
+  p.n_ranges = 1;
+  p.n_total = w.n;
+  p.k = w.k;
+  p.x = gate;
+  p.aux = up;
+  p.accumulate = accumulate ? 1u : 0u;
+  return launch_mv<2>(pdl, s, p);
+}
+
+cudaError_t bp_q1_rms_norm(bool pdl, cudaStream_t s, const __half* in, __half* out, const __half* w, uint32_t group_size,
+                           uint32_t n_groups, float eps) {
+  return bp_launch(pdl, rms_norm_kernel, dim3(n_groups), dim3(512), 0, s, in, out, w, group_size, eps);
+}
+
+cudaError_t bp_q1_silu_mul(bool pdl, cudaStream_t s, const __half* gate, const __half* up, __half* out, uint64_t n) {
+  return bp_launch(pdl, silu_mul_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, s, gate, up, out, n);
+}
+
+cudaError_t bp_q1_embed(bool pdl, cudaStream_t s, const bp_q1_tensor& w, const uint32_t* tokens, uint32_t m, __half* x) {
+  const uint64_t units = static_cast<uint64_t>(m) * (w.k / 8u);
+  return bp_launch(pdl, embed_kernel, dim3(static_cast<unsigned>((units + 255) / 256)), dim3(256), 0, s, w.d, w.qs, w.k, tokens, m, x);
+}
+
+cudaError_t bp_q1_quantize_q8(bool pdl, cudaStream_t s, const __half* x, uint32_t k, uint32_t m, float* d_out, int8_t* qs_out) {
+  const uint64_t n_blocks = static_cast<uint64_t>(m) * (k / 32u);
+  return bp_launch(pdl, quantize_q8_kernel, dim3(static_cast<unsigned>((n_blocks + 7) / 8)), dim3(256), 0, s, x, n_blocks, d_out, qs_out);
+}
+
+cudaError_t bp_q1_matmul(bool pdl, cudaStream_t s, const bp_q1_tensor& w, uint32_t m, const float* a_d, const int8_t* a_qs, __half* y,
+                         bool accumulate) {
+  dim3 grid((w.n + MM_T - 1) / MM_T, (m + MM_T - 1) / MM_T);
+  return bp_launch(pdl, matmul_q1_q8_kernel, grid, dim3(256), 0, s, w.d, w.qs, w.k, w.n, m, a_d, a_qs, y, accumulate ? 1u : 0u);
+}
+
+cudaError_t bp_q1_topk(bool pdl, cudaStream_t s, const __half* logits, uint32_t n, uint32_t k, float* out_val, uint32_t* out_idx) {
+  static bool configured = false;
+  const size_t smem = TK_WG * TK_K * 8;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  return bp_launch(pdl, topk_kernel, dim3(1), dim3(TK_WG), smem, s, logits, n, k, out_val, out_idx);
+}

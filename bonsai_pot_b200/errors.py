@@ -10,6 +10,7 @@ BP_ERR_DEVICE_LOST = 4
 BP_ERR_CUDA = 5
 BP_ERR_TIMEOUT = 6
 BP_ERR_NULL = 7
+BP_ERR_IO = 8
 
 
 class PotError(Exception):
@@ -49,12 +50,17 @@ class CudaError(PotError):
     status = BP_ERR_CUDA
 
 
+class IoError(PotError):
+    """`PotError::Io { path, source }`: a file of the model directory could not be read."""
+    status = BP_ERR_IO
+
+
 class DeviceTimeout(PotError):
     """A bounded device-side wait gave up."""
     status = BP_ERR_TIMEOUT
 
 
-_BY_STATUS = {cls.status: cls for cls in (ConfigError, ContextOverflow, PrefillTooLarge, DeviceLost, CudaError, DeviceTimeout)}
+_BY_STATUS = {cls.status: cls for cls in (ConfigError, ContextOverflow, PrefillTooLarge, DeviceLost, CudaError, DeviceTimeout, IoError)}
 
 
 def raise_for_status(status: int, message: str, **fields):

@@ -54,6 +54,7 @@ pub const BP_ERR_DEVICE_LOST: c_int = 4;
 pub const BP_ERR_CUDA: c_int = 5;
 pub const BP_ERR_TIMEOUT: c_int = 6;
 pub const BP_ERR_NULL: c_int = 7;
+pub const BP_ERR_IO: c_int = 8;
 
 #[link(name = "bonsai_attn")]
 extern "C" {
@@ -169,7 +170,7 @@ pub unsafe fn check(ctx: *const bp_attn_ctx, st: c_int) -> Result<(), AttnError>
         BP_ERR_CONTEXT_OVERFLOW => AttnError::ContextOverflow { pos: d.pos, n: d.n, max: d.max },
         BP_ERR_PREFILL_TOO_LARGE => AttnError::PrefillTooLarge { n: d.n, max: d.max },
         BP_ERR_DEVICE_LOST | BP_ERR_TIMEOUT | BP_ERR_CUDA => AttnError::DeviceLost { status: st, message },
-        BP_ERR_CONFIG | BP_ERR_NULL => AttnError::Config(message),
+        BP_ERR_CONFIG | BP_ERR_NULL | BP_ERR_IO => AttnError::Config(message),
         _ => AttnError::Config(message),
     })
 }

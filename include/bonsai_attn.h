@@ -50,7 +50,8 @@ enum {
                                    meeting of the ranks): the kernel wound down instead of hanging; its results and
                                    the context's device-side counters are undefined. Sticky, like DeviceLost: take a
                                    snapshot if the cache is still wanted, destroy the context, create a new one. */
-  BP_ERR_NULL = 7               /* a required pointer argument was NULL */
+  BP_ERR_NULL = 7,              /* a required pointer argument was NULL */
+  BP_ERR_IO = 8                 /* PotError::Io { path, source }: a model file could not be read (bonsai_model.h) */
 };
 
 /* The fields of the reference's `Config` + `LoadOptions` that this path reads

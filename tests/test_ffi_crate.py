@@ -44,7 +44,7 @@ def test_extern_block_matches_the_header():
 def test_status_constants_match_the_header_enum():
     enum = dict((k, int(v)) for k, v in re.findall(r"\b(BP_[A-Z_]+)\s*=\s*(\d+)", header_text()))
     rust = dict((k, int(v)) for k, v in re.findall(r"pub const (BP_[A-Z_]+): c_int = (\d+);", open(LIB_RS).read()))
-    assert enum == rust and len(enum) == 8
+    assert enum == rust and len(enum) == 9
     # a timed-out device-side wait is sticky like a lost device: check() must not map it to Config
     check = re.search(r"pub unsafe fn check\(.*?\n\}", open(LIB_RS).read(), flags=re.S).group(0)
     arm = re.search(r"([A-Z_| ]+)=> AttnError::DeviceLost", check).group(1)
