@@ -132,6 +132,7 @@ MODEL_SIGNATURES = {
     "bp_op_matvec_q1_0": (_int, [_vp, _vp, _vp, _u32, _u32, _vp, _vp, _u32]),
     "bp_op_matvec_q1_0_fused_normed": (_int, [_vp, _u32, _vp, _vp, C.c_float, _u32, _pp, _pp, _u32p, _pp]),
     "bp_op_matvec_q1_0_silu": (_int, [_vp, _vp, _vp, _u32, _u32, _vp, _vp, _vp, _u32]),
+    "bp_op_set_matvec_rows": (None, [_u32]),
     "bp_op_rms_norm": (_int, [_vp, _vp, _vp, _vp, _u32, _u32, C.c_float]),
     "bp_op_silu_mul": (_int, [_vp, _vp, _vp, _vp, _u64]),
     "bp_op_embed": (_int, [_vp, _vp, _vp, _u32, _vp, _u32, _vp]),

@@ -379,7 +379,10 @@ int decode_layer(bp_model* m, uint32_t il, uint32_t pos) {
     __half* const out[2] = {m->gate, m->up};
     M_CUDA(m, bp_q1_matvec_normed(pdl, s, w, out, 2, m->x, lt.ffn_norm, c.rms_eps));
   }
-  M_CUDA(m, bp_q1_matvec_silu(pdl, s, lt.wd, m->gate, m->up, m->x, true));
+  // dispatch_matvec_q1_0_silu as two launches: silu(gate) * up once (the same f16 values the fused kernel stages;
+  // fused, each of the 256 CTAs of this 4096-row tensor recomputed all 12288 of them: 27.6 us against 3 + 8), then the matvec
+  M_CUDA(m, bp_q1_silu_mul(pdl, s, m->gate, m->up, m->ffn_in, c.n_ff));
+  M_CUDA(m, bp_q1_matvec(pdl, s, lt.wd, m->ffn_in, m->x, true));
   return BP_OK;
 }
 
@@ -464,6 +467,9 @@ int bp_op_matvec_q1_0_silu(void* stream, const void* d, const void* bits, uint32
   if (bad_k(k) || n == 0) return BP_ERR_CONFIG;
   return OP_CUDA(bp_q1_matvec_silu(false, static_cast<cudaStream_t>(stream), op_tensor(d, nullptr, bits, k, n),
                                    static_cast<const __half*>(gate), static_cast<const __half*>(up), static_cast<__half*>(y), accumulate != 0));
+}
+void bp_op_set_matvec_rows(uint32_t rows_per_lane) {
+  bp_q1_set_matvec_rows(rows_per_lane == 1 || rows_per_lane == 2 || rows_per_lane == 4 ? rows_per_lane : 0);
 }
 int bp_op_rms_norm(void* stream, const void* in, void* out, const void* w, uint32_t group_size, uint32_t n_groups, float eps) {
   if (!in || !out || !w) return BP_ERR_NULL;

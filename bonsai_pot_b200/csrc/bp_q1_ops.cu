@@ -25,8 +25,8 @@ namespace {
 using namespace bp;
 constexpr unsigned FULL = 0xffffffffu;
 constexpr uint32_t MV_THREADS = 128;          // the invocation count of the fused shader: its sum of squares is per invocation
-constexpr uint32_t MV_ROWS_PER_LANE = 4;
-constexpr uint32_t MV_ROWS_PER_CTA = (MV_THREADS / 8) * MV_ROWS_PER_LANE;  // 64
+// rows per lane (R): 4 for tall tensors (the activations a lane reads serve all of them), fewer for the
+// 4096-row ones, which would otherwise give the device only 64 CTAs
 constexpr uint32_t XB_STRIDE = 128 + 8;       // halves per staged block: 16 bytes of padding keep the 8 lanes of a row off each other's banks
 
 __device__ __forceinline__ float exp_det(float x) {  // the restatement's orc_exp_det, operation for operation
@@ -93,8 +93,9 @@ struct MvParams {
 
 // MODE 0: y (+)= W x (matvec_q1_0.wgsl); 1: W (rms_norm(x) * w), scales times inv_rms
 // (matvec_q1_0_fused_normed.wgsl); 2: y (+)= W (silu(gate) * up) (matvec_q1_0_silu.wgsl).
-template <int MODE>
+template <int MODE, uint32_t MV_ROWS_PER_LANE>
 __global__ void __launch_bounds__(MV_THREADS) matvec_q1_kernel(const MvParams p) {
+  constexpr uint32_t MV_ROWS_PER_CTA = (MV_THREADS / 8) * MV_ROWS_PER_LANE;
   extern __shared__ __align__(16) uint8_t mv_smem[];
   __shared__ float part[32];
   __half* xs = reinterpret_cast<__half*>(mv_smem);
@@ -169,13 +170,30 @@ __global__ void __launch_bounds__(MV_THREADS) matvec_q1_kernel(const MvParams p)
 #pragma unroll
   for (uint32_t j = 0; j < MV_ROWS_PER_LANE; j++) acc[j] = 0.0f;
   const __half2 zero2 = __float2half2_rn(0.0f);
+  // the next block's sign words and scales are requested before the current block is worked on
+  uint4 w_nxt[MV_ROWS_PER_LANE];
+  __half d_nxt[MV_ROWS_PER_LANE];
+  if (tx < nb) {
+#pragma unroll
+    for (uint32_t j = 0; j < MV_ROWS_PER_LANE; j++) {
+      w_nxt[j] = __ldg(b_row[j] + tx);
+      d_nxt[j] = __ldg(d_row[j] + tx);
+    }
+  }
   for (uint32_t b = tx; b < nb; b += 8) {
     uint4 w[MV_ROWS_PER_LANE];
     __half dh[MV_ROWS_PER_LANE];
 #pragma unroll
     for (uint32_t j = 0; j < MV_ROWS_PER_LANE; j++) {
-      w[j] = __ldg(b_row[j] + b);
-      dh[j] = __ldg(d_row[j] + b);
+      w[j] = w_nxt[j];
+      dh[j] = d_nxt[j];
+    }
+    if (b + 8 < nb) {
+#pragma unroll
+      for (uint32_t j = 0; j < MV_ROWS_PER_LANE; j++) {
+        w_nxt[j] = __ldg(b_row[j] + b + 8);
+        d_nxt[j] = __ldg(d_row[j] + b + 8);
+      }
     }
     __half2 a01[MV_ROWS_PER_LANE], a23[MV_ROWS_PER_LANE];
 #pragma unroll
@@ -377,68 +395,141 @@ __global__ void __launch_bounds__(256) matmul_q1_q8_kernel(const __half* w_d, co
   }
 }
 
-// topk_reduce.wgsl:59-196, the same steps on the same lists (256 per-thread heaps of 32, heapsort, then
-// log2(256) bitonic merge rounds), so that ties fall exactly where the shader's comparisons put them.
-// List j's element i sits at [i][j] in shared memory (bank = j) instead of [j][i]: same lists, no conflicts.
-constexpr uint32_t TK_WG = 256, TK_K = 32;
-__device__ __forceinline__ void tk_sift(float* val, uint32_t* idx, uint32_t j, uint32_t limit) {
+// topk_reduce.wgsl:59-196, the same steps on the same lists (256 per-thread min-heaps of 32, heapsort, then
+// log2(256) bitonic merge rounds), so that ties fall exactly where the shader's comparisons put them. What
+// differs is only how the steps are scheduled on a warp:
+//   - list j's element i sits at [i][j] in shared memory (bank = j) as one 8-byte (value, index) pair;
+//   - a sift moves the inserted element down a chain of holes instead of swapping at every level (the same
+//     comparisons, hence the same final array);
+//   - a lane's list is scanned from a chunk of logits staged in shared memory, and the lanes of a warp are
+//     not held in step: per chunk a lane first marks, in one straight-line pass, the elements above its
+//     heap's root (only those can enter, the root only rises), then the lanes walk their marks: every lane
+//     skips to its next mark that still beats the root, and the lanes that have one sift together. In step,
+//     nearly every one of the 594 iterations made the whole warp wait for some lane's insertion (375 us per
+//     call at 151936 logits);
+//   - for the merge rounds each list is moved to a row of its own (33 entries apart: consecutive lanes then
+//     read consecutive entries of ONE list, as the shader's layout has it).
+constexpr uint32_t TK_WG = 256, TK_K = 32, TK_CHUNK = 32;  // chunk: words (two logits) per list and stage
+constexpr uint32_t TK_ROW = TK_K + 1;                      // entries between the rows of the merge rounds
+struct __align__(8) TkEntry { float v; uint32_t i; };
+__device__ __forceinline__ void tk_sift_hole(TkEntry* heap, uint32_t j, uint32_t limit, TkEntry e) {
+  // heap[0] of list j is being replaced by e: walk down while a child is smaller (topk_reduce.wgsl:35-50)
   uint32_t i = 0;
   for (;;) {
     const uint32_t l = 2 * i + 1, r = l + 1;
+    if (l >= limit) break;
+    const TkEntry cl = heap[l * TK_WG + j];
     uint32_t smallest = i;
-    if (l < limit && val[l * TK_WG + j] < val[smallest * TK_WG + j]) smallest = l;
-    if (r < limit && val[r * TK_WG + j] < val[smallest * TK_WG + j]) smallest = r;
+    float sv = e.v;
+    TkEntry cs = e;
+    if (cl.v < sv) { smallest = l; sv = cl.v; cs = cl; }
+    if (r < limit) {
+      const TkEntry cr = heap[r * TK_WG + j];
+      if (cr.v < sv) { smallest = r; cs = cr; }
+    }
     if (smallest == i) break;
-    const float tv = val[i * TK_WG + j]; val[i * TK_WG + j] = val[smallest * TK_WG + j]; val[smallest * TK_WG + j] = tv;
-    const uint32_t ti = idx[i * TK_WG + j]; idx[i * TK_WG + j] = idx[smallest * TK_WG + j]; idx[smallest * TK_WG + j] = ti;
+    heap[i * TK_WG + j] = cs;
     i = smallest;
   }
+  heap[i * TK_WG + j] = e;
 }
 __global__ void __launch_bounds__(TK_WG) topk_kernel(const __half* logits, uint32_t n, uint32_t k, float* out_val, uint32_t* out_idx) {
   extern __shared__ __align__(16) uint8_t tk_smem[];
-  float* val = reinterpret_cast<float*>(tk_smem);
-  uint32_t* idx = reinterpret_cast<uint32_t*>(tk_smem + TK_WG * TK_K * 4);
+  TkEntry* heap = reinterpret_cast<TkEntry*>(tk_smem);                                    // [TK_K][TK_WG]
+  __half2* stage = reinterpret_cast<__half2*>(tk_smem + TK_WG * TK_K * sizeof(TkEntry));  // [TK_CHUNK][TK_WG]
   pdl_launch_dependents();
   pdl_wait();
   const uint32_t tid = threadIdx.x;
-  for (uint32_t i = 0; i < TK_K; i++) { val[i * TK_WG + tid] = -1e30f; idx[i * TK_WG + tid] = 0; }
+  for (uint32_t i = 0; i < TK_K; i++) heap[i * TK_WG + tid] = TkEntry{-1e30f, 0u};
   const uint32_t n_words = (n + 1) >> 1;
-  float cur_min = -1e30f;  // mirrors val[0] of this thread's heap
-  for (uint32_t w = tid; w < n_words; w += TK_WG) {
-    const __half2 pair = *reinterpret_cast<const __half2*>(logits + 2 * w);
-    const float v0 = __low2float(pair), v1 = __high2float(pair);
-    if (v0 > cur_min) { val[tid] = v0; idx[tid] = 2 * w; tk_sift(val, idx, tid, TK_K); cur_min = val[tid]; }
-    if (2 * w + 1 < n && v1 > cur_min) { val[tid] = v1; idx[tid] = 2 * w + 1; tk_sift(val, idx, tid, TK_K); cur_min = val[tid]; }
+  float cur_min = -1e30f;  // mirrors the root of this thread's heap
+  for (uint32_t w_base = 0; w_base < n_words; w_base += TK_CHUNK * TK_WG) {
+    __syncthreads();  // the previous chunk has been consumed
+    {
+      __half2 tmp[TK_CHUNK];  // every load of the chunk in flight before the first store
+#pragma unroll
+      for (uint32_t c = 0; c < TK_CHUNK; c++) {
+        const uint32_t w = w_base + c * TK_WG + tid;
+        tmp[c] = w < n_words ? __ldg(reinterpret_cast<const __half2*>(logits + 2 * w)) : __half2();
+      }
+#pragma unroll
+      for (uint32_t c = 0; c < TK_CHUNK; c++) stage[c * TK_WG + tid] = tmp[c];
+    }
+    __syncthreads();
+    // this thread's elements of the chunk, in the shader's order: word c (low half, then high half) = bit 2 c, 2 c + 1
+    const uint32_t words_here = w_base + tid < n_words ? min(TK_CHUNK, (n_words - w_base - tid + TK_WG - 1) / TK_WG) : 0;
+    unsigned long long marks = 0;
+#pragma unroll
+    for (uint32_t c = 0; c < TK_CHUNK; c++) {
+      const __half2 pair = stage[c * TK_WG + tid];
+      const uint32_t i0 = 2 * (w_base + c * TK_WG + tid);
+      const bool m0 = c < words_here && __low2float(pair) > cur_min;
+      const bool m1 = c < words_here && i0 + 1 < n && __high2float(pair) > cur_min;
+      marks |= (static_cast<unsigned long long>(m0) << (2 * c)) | (static_cast<unsigned long long>(m1) << (2 * c + 1));
+    }
+    for (;;) {
+      float v = 0.f;
+      uint32_t idx = 0;
+      bool have = false;
+      while (marks != 0) {  // skip to the next mark that still beats the root
+        const uint32_t pos = __ffsll(static_cast<long long>(marks)) - 1;
+        marks &= marks - 1;
+        const __half2 pair = stage[(pos >> 1) * TK_WG + tid];
+        v = (pos & 1) ? __high2float(pair) : __low2float(pair);
+        idx = 2 * (w_base + (pos >> 1) * TK_WG + tid) + (pos & 1);
+        if (v > cur_min) {
+          have = true;
+          break;
+        }
+      }
+      if (!__any_sync(FULL, have)) break;
+      if (have) {
+        tk_sift_hole(heap, tid, TK_K, TkEntry{v, idx});
+        cur_min = heap[tid].v;
+      }
+    }
   }
+  // heapsort to descending order (topk_reduce.wgsl:106-126): swap the root with the last active slot, sift
   for (uint32_t active = TK_K - 1; active > 0; active--) {
-    const float tv = val[tid]; val[tid] = val[active * TK_WG + tid]; val[active * TK_WG + tid] = tv;
-    const uint32_t ti = idx[tid]; idx[tid] = idx[active * TK_WG + tid]; idx[active * TK_WG + tid] = ti;
-    tk_sift(val, idx, tid, active);
+    const TkEntry root = heap[tid], last = heap[active * TK_WG + tid];
+    heap[active * TK_WG + tid] = root;
+    tk_sift_hole(heap, tid, active, last);
   }
-  __syncthreads();
+  {  // every list to a row of its own: rows[j * TK_ROW + i], over the heap and stage areas
+    TkEntry mine[TK_K];
+#pragma unroll
+    for (uint32_t i = 0; i < TK_K; i++) mine[i] = heap[i * TK_WG + tid];
+    __syncthreads();
+#pragma unroll
+    for (uint32_t i = 0; i < TK_K; i++) heap[tid * TK_ROW + i] = mine[i];
+    __syncthreads();
+  }
+  TkEntry* rows = heap;
   for (uint32_t s = TK_WG / 2; s > 0; s >>= 1) {
     for (uint32_t kk = tid; kk < s * TK_K; kk += TK_WG) {
       const uint32_t pair = kk / TK_K, i = kk % TK_K, bi = TK_K - 1 - i;
-      const float av = val[i * TK_WG + pair], bv = val[bi * TK_WG + pair + s];
-      if (bv > av) { val[i * TK_WG + pair] = bv; idx[i * TK_WG + pair] = idx[bi * TK_WG + pair + s]; }
+      const TkEntry a = rows[pair * TK_ROW + i], b = rows[(pair + s) * TK_ROW + bi];
+      if (b.v > a.v) rows[pair * TK_ROW + i] = b;
     }
     __syncthreads();
     for (uint32_t stride = TK_K / 2; stride > 0; stride >>= 1) {
       for (uint32_t kk = tid; kk < s * (TK_K / 2); kk += TK_WG) {
         const uint32_t pair = kk / (TK_K / 2), local = kk % (TK_K / 2);
         const uint32_t lo = ((local & ~(stride - 1)) << 1) | (local & (stride - 1)), hi = lo | stride;
-        const float vlo = val[lo * TK_WG + pair], vhi = val[hi * TK_WG + pair];
-        if (vhi > vlo) {
-          const uint32_t ilo = idx[lo * TK_WG + pair];
-          val[lo * TK_WG + pair] = vhi; val[hi * TK_WG + pair] = vlo;
-          idx[lo * TK_WG + pair] = idx[hi * TK_WG + pair]; idx[hi * TK_WG + pair] = ilo;
+        const TkEntry a = rows[pair * TK_ROW + lo], b = rows[pair * TK_ROW + hi];
+        if (b.v > a.v) {
+          rows[pair * TK_ROW + lo] = b;
+          rows[pair * TK_ROW + hi] = a;
         }
       }
       __syncthreads();
     }
   }
   const uint32_t kk = k < TK_K ? k : TK_K;
-  if (tid < kk) { out_val[tid] = val[tid * TK_WG]; out_idx[tid] = idx[tid * TK_WG]; }
+  if (tid < kk) {
+    out_val[tid] = rows[tid].v;
+    out_idx[tid] = rows[tid].i;
+  }
 }
 
 // Sign bits of one Q1_0 tensor -> the matvec kernels' layout (see the file header). Thread = block.
@@ -459,20 +550,36 @@ __global__ void __launch_bounds__(256) relayout_kernel(const uint8_t* qs, uint4*
 
 size_t mv_smem_bytes(uint32_t k) { return static_cast<size_t>(k / 128u) * XB_STRIDE * sizeof(__half); }
 
+template <int MODE, uint32_t R>
+cudaError_t launch_mv_r(bool pdl, cudaStream_t s, const MvParams& p) {
+  const size_t smem = mv_smem_bytes(p.k);
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(matvec_q1_kernel<MODE, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+    configured = smem;
+  }
+  const uint32_t rows_per_cta = (MV_THREADS / 8) * R;
+  const uint32_t ctas = (p.n_total + rows_per_cta - 1) / rows_per_cta;
+  return bp_launch(pdl, matvec_q1_kernel<MODE, R>, dim3(ctas), dim3(MV_THREADS), smem, s, p);
+}
+
+uint32_t g_mv_rows_override = 0;  // tuning aid (bp_op_set_matvec_rows): 0 = by tensor height
+
 template <int MODE>
 cudaError_t launch_mv(bool pdl, cudaStream_t s, const MvParams& p) {
-  const size_t smem = mv_smem_bytes(p.k);
-  static size_t configured[3] = {0, 0, 0};
-  if (smem > 48 * 1024 && smem > configured[MODE]) {
-    cudaError_t e = cudaFuncSetAttribute(matvec_q1_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (e != cudaSuccess) return e;
-    configured[MODE] = smem;
-  }
-  const uint32_t ctas = (p.n_total + MV_ROWS_PER_CTA - 1) / MV_ROWS_PER_CTA;
-  return bp_launch(pdl, matvec_q1_kernel<MODE>, dim3(ctas), dim3(MV_THREADS), smem, s, p);
+  uint32_t r = g_mv_rows_override;
+  // measured at Bonsai-8B shapes (us per call, R = 1 / 2 / 4): 4096 rows 4.9 / 5.9 / 9.2, 6144 rows 5.8 / 6.9 / 7.6,
+  // 24576 rows 12.9 / 10.6 / 10.9, 151936 rows 50 / 45 / 54
+  if (r == 0) r = p.n_total >= 16384 ? 2 : 1;
+  if (r >= 4) return launch_mv_r<MODE, 4>(pdl, s, p);
+  if (r == 2) return launch_mv_r<MODE, 2>(pdl, s, p);
+  return launch_mv_r<MODE, 1>(pdl, s, p);
 }
 
 }  // namespace
+
+void bp_q1_set_matvec_rows(uint32_t rows_per_lane) { g_mv_rows_override = rows_per_lane; }
 
 cudaError_t bp_q1_relayout(cudaStream_t s, const uint8_t* qs, void* out, uint64_t n_blocks) {
   relayout_kernel<<<static_cast<unsigned>((n_blocks + 255) / 256), 256, 0, s>>>(qs, static_cast<uint4*>(out), n_blocks);
@@ -547,7 +654,7 @@ cudaError_t bp_q1_matmul(bool pdl, cudaStream_t s, const bp_q1_tensor& w, uint32
 
 cudaError_t bp_q1_topk(bool pdl, cudaStream_t s, const __half* logits, uint32_t n, uint32_t k, float* out_val, uint32_t* out_idx) {
   static bool configured = false;
-  const size_t smem = TK_WG * TK_K * 8;
+  const size_t smem = TK_WG * TK_K * sizeof(TkEntry) + TK_CHUNK * TK_WG * sizeof(__half2);
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return e;

@@ -14,6 +14,7 @@ struct bp_q1_tensor {
   uint32_t k, n;
 };
 
+void bp_q1_set_matvec_rows(uint32_t rows_per_lane);  // tuning aid: 0 = by tensor height, else 1, 2 or 4
 cudaError_t bp_q1_relayout(cudaStream_t s, const uint8_t* qs, void* out, uint64_t n_blocks);
 cudaError_t bp_q1_matvec(bool pdl, cudaStream_t s, const bp_q1_tensor& w, const __half* x, __half* y, bool accumulate);
 cudaError_t bp_q1_matvec_normed(bool pdl, cudaStream_t s, const bp_q1_tensor* w, __half* const* out, uint32_t n_ranges,
