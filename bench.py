@@ -708,7 +708,49 @@ def extras(torch, bp, stream, hbm_peak, tflops_peak, peak_kind, args):
                 "splits": c.decode_num_splits(ctx_len)}
     for pp in (512, 2048):
         out[f"prefill_pp{pp}"] = prefill_bench(torch, bp, stream, tflops_peak, peak_kind, pp, 4)
+    try:
+        out["e2e_bonsai8b_pp512_tg128"] = engine_bench(torch, bp)
+    except Exception as e:  # a side measurement: it must not take the headline down
+        out["e2e_bonsai8b_pp512_tg128"] = {"failed": f"{type(e).__name__}: {e}"}
     return out
+
+
+def engine_bench(torch, bp):
+    """BASELINE config 4: a Bonsai-8B-shaped random-init model (Q1_0 signs Bernoulli(0.5), f16 block scales
+    |N(0, 0.02)|, norms 1.0) written to a temporary model directory, loaded, prefilled with 512 tokens through
+    the batched path and decoded greedily for 128 tokens through Session::generate, this library's attention
+    inside. Tokens per second, whole engine (the CPU restatement of this size is hours of CPU time: the
+    bit-for-bit comparison with it runs in the tests, at these widths on two layers and end to end on a small model)."""
+    import shutil
+    import tempfile
+    import numpy as np
+    from bonsai_pot_b200 import model_dir
+    d = tempfile.mkdtemp(prefix="bonsai8b_synth_")
+    try:
+        model_dir.write_synthetic_model(d, shape=model_dir.BONSAI_8B, seed=1)
+        with bp.Model(d, max_seq=1024) as m:
+            prompt = np.random.default_rng(0).integers(0, model_dir.BONSAI_8B["n_vocab"], 512).tolist()
+            greedy = bp.Sampler(temperature=0.0)
+            sess = m.new_session()
+            best_pp, best_tg, toks = None, None, None
+            for _ in range(3):
+                sess.reset()
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                first = sess.prefill(prompt, greedy)
+                t_pp = time.perf_counter() - t0
+                t0 = time.perf_counter()
+                toks, _reason = sess.generate(first, bp.GenerateOptions(max_new_tokens=128, stop_pred=lambda _t: False, sampler=greedy))
+                t_tg = time.perf_counter() - t0
+                best_pp = t_pp if best_pp is None else min(best_pp, t_pp)
+                best_tg = t_tg if best_tg is None else min(best_tg, t_tg)
+            weights_mb = sum(os.path.getsize(os.path.join(d, f)) for f in os.listdir(d) if f.endswith(".bin")) / 1e6
+        return {"pp512_tok_s": round(512 / best_pp, 1), "tg128_tok_s": round(128 / best_tg, 1), "pp512_ms": round(best_pp * 1e3, 2),
+                "tg128_ms_per_token": round(best_tg * 1e3 / 128, 3), "weights_mb": round(weights_mb, 1), "tokens_emitted": len(toks),
+                "weight_stream_gbs_decode": round(weights_mb / 1e3 / (best_tg / 128), 1),
+                "note": "whole engine through Session::prefill + Session::generate, host loop and sampling included"}
+    finally:
+        shutil.rmtree(d, ignore_errors=True)
 
 
 def main():

@@ -37,8 +37,10 @@ def build(native: bool = False) -> str:
     """Compile the oracle if its shared object is missing; return its path."""
     name = "liboracle_native.so" if native else "liboracle.so"
     path = os.path.join(HERE, name)
-    if native or not os.path.exists(path):
-        args = ["make", "-C", HERE] + (["-B", "native"] if native else [])
+    srcs = [os.path.join(HERE, f) for f in ("oracle.c", "engine.c", "Makefile")]
+    stale = not os.path.exists(path) or any(os.path.getmtime(f) > os.path.getmtime(path) for f in srcs)
+    if native or stale:
+        args = ["make", "-C", HERE] + (["-B", "native"] if native else ["-B"])
         subprocess.run(args, check=True, capture_output=True)
     return path
 
