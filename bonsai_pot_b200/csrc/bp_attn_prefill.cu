@@ -15,13 +15,14 @@
 //    consecutive tokens times the qpg query heads of the group. Persistent
 //    CTAs fetch items, longest first, from a global counter. Keys come in
 //    tiles of 64. Per key tile and per query tile X:
-//      producer warp   TMA: f16 K and V tiles (128-byte swizzle) straight into UMMA operand layout
+//      warp 0          requests the V tiles (TMA, 128-byte swizzle, straight into UMMA operand layout)
+//                      and issues O_0 += P_0 V (4 UMMAs M 128, N 128, K 16, P read from TMEM as the
+//                      A operand); never blocks: it polls its barriers
+//      warp NQ + 1     the same for the K tiles and O_1 += P_1 V
 //      Q K^T issuer X  S_X = Q_X K^T (8 UMMAs M 128, N 64, K 16) into one of the two 64-column
-//                      buffers of X's S region in TMEM, up to two tiles ahead of
-//      P V issuer      O_X += P_X V (4 UMMAs M 128, N 128, K 16, P_X read from TMEM as the A operand)
-//                      for whichever query tile has its P ready (one thread issues a tcgen05.mma
-//                      only every ~115 cycles, the tensor pipe takes one every 70 to 80 from
-//                      several threads: hence three issuing threads for two query tiles)
+//                      buffers of X's S region in TMEM, up to two tiles ahead of P V
+//                      (one thread issues a tcgen05.mma only every ~115 cycles, the tensor pipe takes
+//                      one every 70 to 80 from several threads: hence four issuing threads)
 //      softmax group X thread = query row = TMEM lane: scale, causal mask, online max / sum,
 //                      P as f16 written over the tile's S buffer; O_X is rescaled in TMEM only
 //                      when a row maximum grew by more than 2^8 (P stays below 2^8 meanwhile)
@@ -274,45 +275,80 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     __syncthreads();
     tc_fence_after();
 
-    if (warp == 0) {
-      // ---------------- TMA producer ----------------
+    if (warp == 0 || warp == NQ + 1) {
+      // ---------------- loaders and P V issuers ----------------
+      // Two threads, neither of which ever blocks: warp 0 requests the V tiles and issues O_0 += P_0 V,
+      // warp NQ + 1 requests the K tiles and issues O_1 += P_1 V. A single thread issuing the P V of both
+      // query tiles was the bottleneck of this kernel: it needs about 1100 cycles per key tile and query
+      // tile (polls, four MMAs at 115 cycles each, three commits), so with two query tiles a P tile waited
+      // some 1400 cycles for its turn and the softmax groups then waited as long for the next S.
       if (lane == 0) {
-        prefetch_tensormap(&map_k);
-        prefetch_tensormap(&map_v);
-        for (uint32_t i = 0; i < n_tiles; i++) {
-          const uint32_t s = (gkv + i) % KV_SLOTS;
-          const int row = static_cast<int>(i * BN);
-          uint32_t users = 0, slot_bits = 0;  // query tiles that read tile i; all query tiles' bits of slot s
+        constexpr uint32_t IDESC_PV = umma_idesc(1, 0, 0, 0, 1, BM, 128);  // f32 += f16 (TMEM) x f16 (MN-major), N = 128 dims
+        const uint64_t dmn = umma_desc_sw128(0, 8192, 1024);    // V: next 64 dims 8 KB away, 8 key rows 1 KB apart
+        const bool loads_k = warp != 0;
+        const uint32_t x = loads_k ? 1u : 0u;                   // the query tile whose P V this thread issues
+        const uint32_t n_pv = x < NQ ? nx[x < NQ ? x : 0] : 0u;
+        const CUtensorMap* map = loads_k ? &map_k : &map_v;
+        uint64_t* full = loads_k ? k_full : v_full;
+        const uint32_t dst0 = smem_base + (loads_k ? L::OFF_K : L::OFF_V);
+        uint32_t pend = loads_k ? pend_k : pend_v, phase = loads_k ? phase_k : phase_v;
+        uint32_t li = 0, ip = 0, spins = 0;  // tiles requested, P V issued
+        prefetch_tensormap(map);
+        while ((li < n_tiles || ip < n_pv) && !abort_s) {
+          bool progressed = false;
+          if (li < n_tiles) {
+            // the next tile, once every query tile that used the slot's last tile has released it
+            const uint32_t s = (gkv + li) % KV_SLOTS;
+            bool slot_free = true;
+            uint32_t users = 0;
 #pragma unroll
-          for (uint32_t x = 0; x < NQ; x++) {
-            users |= (i < nx[x] ? 1u : 0u) << (x * KV_SLOTS + s);
-            slot_bits |= 1u << (x * KV_SLOTS + s);
-          }
-#pragma unroll
-          for (uint32_t x = 0; x < NQ; x++) {
-            const uint32_t bit = 1u << (x * KV_SLOTS + s);
-            if (pend_k & bit) {
-              waitx(&k_empty[x][s], (phase_k & bit) ? 1u : 0u, 0);
-              phase_k ^= bit;
+            for (uint32_t y = 0; y < NQ; y++) {
+              const uint32_t bit = 1u << (y * KV_SLOTS + s);
+              users |= li < nx[y] ? bit : 0u;
+              if (pend & bit) {
+                if (mbar_test(smem_u32(loads_k ? &k_empty[y][s] : &v_empty[y][s]), (phase & bit) ? 1u : 0u)) {
+                  pend &= ~bit;
+                  phase ^= bit;
+                } else {
+                  slot_free = false;
+                }
+              }
+            }
+            if (slot_free) {
+              pend |= users;
+              mbar_arrive_expect_tx(smem_u32(&full[s]), KV_TILE_B);
+              tma_load_3d(dst0 + s * KV_TILE_B, map, smem_u32(&full[s]), 0, static_cast<int>(li * BN), static_cast<int>(2 * g));
+              li++;
+              progressed = true;
             }
           }
-          pend_k = (pend_k & ~slot_bits) | users;
-          if (abort_s) break;
-          mbar_arrive_expect_tx(smem_u32(&k_full[s]), KV_TILE_B);
-          tma_load_3d(smem_base + L::OFF_K + s * KV_TILE_B, &map_k, smem_u32(&k_full[s]), 0, row, static_cast<int>(2 * g));
+          if (ip < n_pv) {
+            const uint32_t xq = x < NQ ? x : 0;  // (x < NQ whenever n_pv > 0)
+            const uint32_t i = ip, s = (gkv + i) % KV_SLOTS, c = gx[xq] + i, b = c & 1;
+            // one barrier per S buffer: the softmax group may run two tiles ahead of this test, and two
+            // completions on one barrier would be indistinguishable from none
+            if (mbar_test(smem_u32(&p_ready[xq][b]), (c >> 1) & 1) &&
+                mbar_test(smem_u32(&v_full[s]), ((gkv + i) / KV_SLOTS) & 1)) {
+              tc_fence_after();
+              const uint64_t vb = dmn + ((smem_base + L::OFF_V + s * KV_TILE_B) >> 4);
+              const uint32_t s_col = tmem + TM_S + xq * SW, o_col = tmem + TM_O + xq * SW;
 #pragma unroll
-          for (uint32_t x = 0; x < NQ; x++) {
-            const uint32_t bit = 1u << (x * KV_SLOTS + s);
-            if (pend_v & bit) {
-              waitx(&v_empty[x][s], (phase_v & bit) ? 1u : 0u, 1);
-              phase_v ^= bit;
+              for (uint32_t ks = 0; ks < 4; ks++)  // 16 keys per UMMA: 8 columns of P, 16 rows of V
+                umma_f16_ts(o_col, s_col + 64 * b + 8 * ks, vb + ks * (16 * 128 >> 4), IDESC_PV, (i | ks) ? 1u : 0u);
+              umma_commit(smem_u32(&p_free[xq][b]));   // P V of tile i complete: the S buffer may take the next Q K^T,
+              umma_commit(smem_u32(&v_empty[xq][s]));  // the V slot is free and O_X is consistent
+              if (++ip == n_pv) umma_commit(smem_u32(&o_done[xq]));
+              progressed = true;
             }
           }
-          pend_v = (pend_v & ~slot_bits) | users;
-          if (abort_s) break;
-          mbar_arrive_expect_tx(smem_u32(&v_full[s]), KV_TILE_B);
-          tma_load_3d(smem_base + L::OFF_V + s * KV_TILE_B, &map_v, smem_u32(&v_full[s]), 0, row, static_cast<int>(2 * g));
+          if (progressed) {
+            spins = 0;
+          } else if (++spins > p.wait_limit) {  // bounded like every other wait (a round is a few dozen cycles)
+            abort_s = 1;
+            atomicExch(p.err, 5u);
+          }
         }
+        if (loads_k) { pend_k = pend; phase_k = phase; } else { pend_v = pend; phase_v = phase; }
       }
     } else if (warp <= NQ) {
       // ---------------- Q K^T issuer of query tile X ----------------
@@ -342,48 +378,6 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             umma_f16(s_col + 64 * b, qa + qo, kb + ko, IDESC_QK, ks);
           }
           umma_commit(smem_u32(&s_ready[x][b]));
-        }
-      }
-    } else if (warp == NQ + 1) {
-      // ---------------- P V issuer (all query tiles) ----------------
-      // O_X += P_X V for whichever query tile has its P ready: the tiles of one query tile in order,
-      // the query tiles in the order their softmax groups finish.
-      if (lane == 0) {
-        constexpr uint32_t IDESC_PV = umma_idesc(1, 0, 0, 0, 1, BM, 128);  // f32 += f16 (TMEM) x f16 (MN-major), N = 128 dims
-        const uint64_t dmn = umma_desc_sw128(0, 8192, 1024);    // V: next 64 dims 8 KB away, 8 key rows 1 KB apart
-        uint32_t ix[NQ], spins = 0;
-#pragma unroll
-        for (uint32_t x = 0; x < NQ; x++) ix[x] = 0;
-        for (;;) {
-          bool all_done = true, progressed = false;
-#pragma unroll
-          for (uint32_t x = 0; x < NQ; x++) {
-            if (ix[x] >= nx[x]) continue;
-            all_done = false;
-            const uint32_t i = ix[x], s = (gkv + i) % KV_SLOTS, c = gx[x] + i, b = c & 1;
-            // one barrier per S buffer: the softmax group may run two tiles ahead of this test, and two
-            // completions on one barrier would be indistinguishable from none
-            if (!mbar_test(smem_u32(&p_ready[x][b]), (c >> 1) & 1)) continue;
-            waitx(&v_full[s], ((gkv + i) / KV_SLOTS) & 1, 1);
-            tc_fence_after();
-            const uint64_t vb = dmn + ((smem_base + L::OFF_V + s * KV_TILE_B) >> 4);
-            const uint32_t s_col = tmem + TM_S + x * SW, o_col = tmem + TM_O + x * SW;
-#pragma unroll
-            for (uint32_t ks = 0; ks < 4; ks++)  // 16 keys per UMMA: 8 columns of P, 16 rows of V
-              umma_f16_ts(o_col, s_col + 64 * b + 8 * ks, vb + ks * (16 * 128 >> 4), IDESC_PV, (i | ks) ? 1u : 0u);
-            umma_commit(smem_u32(&v_empty[x][s]));  // P V of tile i complete: V slot free, O_X consistent
-            umma_commit(smem_u32(&p_free[x][b]));   // ... and the S buffer may take the next Q K^T
-            if (++ix[x] == nx[x]) umma_commit(smem_u32(&o_done[x]));
-            progressed = true;
-          }
-          if (all_done || abort_s) break;
-          if (progressed) {
-            spins = 0;
-          } else if (++spins > p.wait_limit) {  // bounded like every other wait (a round is a few dozen cycles)
-            abort_s = 1;
-            atomicExch(p.err, 5u);
-            break;
-          }
         }
       }
     } else {
@@ -469,18 +463,16 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         }
       }
       // ---- O / l -> f16 ----
-      // A thread holds one output row (256 B of f16). Without the peer exchange it stores the row itself,
-      // 16 bytes at a time (a warp's store touches 32 rows; the local L2 merges them). Over NVLink that
-      // pattern took 48 us per layer at 2048 tokens on two GPUs, so with the exchange the rows go to the dead Q
-      // tile of this query tile first (16-byte chunks xor-swizzled by the row) and every warp then writes
-      // its 32 rows as 256 contiguous bytes each (10 us; the detour costs the local path 1 to 3 us,
-      // hence two code paths).
+      // A thread holds one output row (256 B of f16). Stored from here, 16 bytes at a time, a warp's store
+      // instruction touches 32 different lines, and the load/store unit takes a cycle per line: 3800 cycles
+      // per work item at 2048 tokens (48 us per layer when the rows went over NVLink). So the rows go to the
+      // dead Q tile of this query tile first (16-byte chunks xor-swizzled by the row) and every warp then
+      // writes the 32 rows its own lanes staged as whole 256-byte rows.
       if (n_mine > 0) {
         waitx(&o_done[x], od[x] & 1, 2);
         tc_fence_after();
         const float inv_l = 1.0f / l_run;
         uint8_t* stage = smem_gen + L::OFF_Q + x * OPER_B;
-        __half* dst = p.out + (static_cast<size_t>(tok) * p.n_head + g * p.qpg + r % p.qpg) * BP_HEAD_DIM;
 #pragma unroll
         for (uint32_t c = 0; c < 4; c++) {
           uint32_t o[32];
@@ -495,15 +487,21 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
               w[k] = *reinterpret_cast<uint32_t*>(&h);
             }
             const uint4 w4 = make_uint4(w[0], w[1], w[2], w[3]);
-            if constexpr (PX) {
-              *reinterpret_cast<uint4*>(stage + r * 256 + (((4 * c + q8) ^ (r & 15)) << 4)) = w4;
-            } else {
-              if (tok < p.m) *reinterpret_cast<uint4*>(dst + 32 * c + 8 * q8) = w4;
-            }
+            *reinterpret_cast<uint4*>(stage + r * 256 + (((4 * c + q8) ^ (r & 15)) << 4)) = w4;
           }
         }
-        if constexpr (PX) {
-          named_bar_sync(1 + x, 128);
+        __syncwarp();  // a warp reads back only the 32 rows its own lanes wrote
+        if constexpr (!PX) {
+          // two rows per store instruction: lanes 0-15 one row of 256 bytes, lanes 16-31 the next
+#pragma unroll 4
+          for (uint32_t rr = 0; rr < 32; rr += 2) {
+            const uint32_t row = quad * 32 + rr + (lane >> 4), u = lane & 15;
+            const uint32_t tok_r = tq0[x] + row / p.qpg, head_r = g * p.qpg + row % p.qpg;
+            if (tok_r >= p.m) continue;
+            const uint4 v = *reinterpret_cast<const uint4*>(stage + row * 256 + ((u ^ (row & 15)) << 4));
+            *reinterpret_cast<uint4*>(p.out + (static_cast<size_t>(tok_r) * p.n_head + head_r) * BP_HEAD_DIM + 8 * u) = v;
+          }
+        } else {
 #pragma unroll 4
           for (uint32_t rr = 0; rr < 32; rr++) {
             const uint32_t row = quad * 32 + rr;
