@@ -106,6 +106,24 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
         "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
+// Packed FP32 pairs (sm_100): one instruction for two lanes of a 64-bit register pair.
+__device__ __forceinline__ void fma2(float& d0, float& d1, float a0, float a1, float b, float c) {
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %4};\n\tmov.b64 rc, {%5, %5};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b), "f"(c));
+}
+__device__ __forceinline__ void add2(float& d0, float& d1, float a0, float a1) {
+  asm("{\n\t.reg .b64 ra, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rd, {%0, %1};\n\t"
+      "add.rn.f32x2 rd, rd, ra;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "+f"(d0), "+f"(d1) : "f"(a0), "f"(a1));
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
@@ -410,10 +428,12 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         }
         float mx[4] = {__uint_as_float(raw[0]), __uint_as_float(raw[1]), __uint_as_float(raw[2]), __uint_as_float(raw[3])};
 #pragma unroll
-        for (int c = 4; c < 64; c += 4) {
+        for (int c = 4; c < 60; c += 8) {
 #pragma unroll
-          for (int k = 0; k < 4; k++) mx[k] = fmaxf(mx[k], __uint_as_float(raw[c + k]));
+          for (int k = 0; k < 4; k++) mx[k] = max3(mx[k], __uint_as_float(raw[c + k]), __uint_as_float(raw[c + 4 + k]));
         }
+#pragma unroll
+        for (int k = 0; k < 4; k++) mx[k] = fmaxf(mx[k], __uint_as_float(raw[60 + k]));
         const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
         const bool grow = m_tile > m_run + 8.0f;        // lazy: keep the old maximum while P stays below 2^8
         const float m_new = grow ? m_tile : m_run;
@@ -442,11 +462,13 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         // P over the first 32 columns of the buffer (every S value of this row is in registers by now)
         float sum[4] = {0.f, 0.f, 0.f, 0.f};
         uint32_t ph[32];
+        const float neg_m = -m_new;
 #pragma unroll
         for (int c = 0; c < 32; c++) {
-          const float p0 = ex2(fmaf(__uint_as_float(raw[2 * c]), p.scale_log2, -m_new));
-          const float p1 = ex2(fmaf(__uint_as_float(raw[2 * c + 1]), p.scale_log2, -m_new));
-          sum[c & 3] += p0 + p1;
+          float a0, a1;
+          fma2(a0, a1, __uint_as_float(raw[2 * c]), __uint_as_float(raw[2 * c + 1]), p.scale_log2, neg_m);
+          const float p0 = ex2(a0), p1 = ex2(a1);
+          add2(sum[2 * (c & 1)], sum[2 * (c & 1) + 1], p0, p1);
           __half2 h = __floats2half2_rn(p0, p1);
           ph[c] = *reinterpret_cast<uint32_t*>(&h);
         }
