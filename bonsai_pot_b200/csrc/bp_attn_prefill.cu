@@ -14,21 +14,26 @@
 //    and NQ query tiles of 128 rows each; a tile's rows are 128 / qpg
 //    consecutive tokens times the qpg query heads of the group. Persistent
 //    CTAs fetch items, longest first, from a global counter. Keys come in
-//    tiles of 64. Per key tile and per query tile X:
-//      warp 0          requests the V tiles (TMA, 128-byte swizzle, straight into UMMA operand layout)
-//                      and issues O_0 += P_0 V (4 UMMAs M 128, N 128, K 16, P read from TMEM as the
-//                      A operand); never blocks: it polls its barriers
-//      warp NQ + 1     the same for the K tiles and O_1 += P_1 V
+//    tiles of 64. Three layouts (PLayout): one query tile per item and two CTAs
+//    per SM (the default when there are more items than SMs: while one CTA is
+//    between two items, 7 us of item fetch, Q load, pipeline fill and epilogue,
+//    the other computes), one query tile and one CTA per SM (small batches), two
+//    query tiles on one CTA per SM (every K / V tile loaded once for both).
+//    Per key tile and per query tile X:
+//      warps 0 .. NQ-1 request the K and V tiles (TMA, 128-byte swizzle, straight into UMMA operand
+//                      layout) and issue O_X += P_X V (4 UMMAs M 128, N 128, K 16, P read from TMEM
+//                      as the A operand); they poll their barriers and never block. With two query
+//                      tiles warp 0 loads V and warp 1 loads K
 //      Q K^T issuer X  S_X = Q_X K^T (8 UMMAs M 128, N 64, K 16) into one of the two 64-column
 //                      buffers of X's S region in TMEM, up to two tiles ahead of P V
-//                      (one thread issues a tcgen05.mma only every ~115 cycles, the tensor pipe takes
-//                      one every 70 to 80 from several threads: hence four issuing threads)
+//                      (one thread issues a tcgen05.mma only every ~85 to 115 cycles, the tensor pipe
+//                      takes one every 70 to 80 from several threads: hence an issuing thread per role
+//                      and query tile)
 //      softmax group X thread = query row = TMEM lane: scale, causal mask, online max / sum,
 //                      P as f16 written over the tile's S buffer; O_X is rescaled in TMEM only
 //                      when a row maximum grew by more than 2^8 (P stays below 2^8 meanwhile)
-//    S is double-buffered so that a tile's softmax overlaps the MMAs of its neighbours; with
-//    NQ = 2 the two query tiles share every K / V tile and fill each other's gaps.
-//    TMEM: S_A, S_B, O_A, O_B, 128 columns each.
+//    S is double-buffered so that a tile's softmax overlaps the MMAs of its neighbours.
+//    TMEM per query tile: S (two buffers of 64 columns) and O, 128 columns each.
 // Every wait is bounded; a timeout sets the context's error word and the CTA
 // winds down and frees its TMEM.
 #include "bp_common.cuh"
@@ -46,17 +51,22 @@ using namespace bp;
 constexpr unsigned FULL = 0xffffffffu;
 constexpr float NEG_BIG = -1e30f;
 constexpr uint32_t BM = 128, BN = 64;             // query rows per tile, keys per tile
-constexpr uint32_t P_TMEM_COLS = 512;            // S_A, S_B, O_A, O_B: 128 columns each
 constexpr uint32_t OPER_B = 2 * 16384;           // one f16 operand tile: 2 chunks of [128 rows][128 B]
-constexpr uint32_t KV_SLOTS = 4;
 constexpr uint32_t KV_TILE_B = 2 * 8192;          // one f16 K or V tile: 2 chunks of [64 keys][128 B]
 constexpr uint32_t SW = 128;                      // TMEM columns of one query tile's S region (two 64-column buffers) and of O
-constexpr uint32_t TM_S = 0, TM_O = 256;         // TMEM columns: S_X at TM_S + 128 X, O_X at TM_O + 128 X
 
-template <uint32_t NQ>
+template <uint32_t NQ, uint32_t CPS>  // query tiles per CTA (work item), CTAs per SM
 struct PLayout {
   // producer, NQ Q K^T issuers, one P V issuer, NQ softmax groups of 4 warps
-  static constexpr uint32_t FIRST_SM_WARP = NQ + 2;
+  // One CTA per SM: four K and four V slots. Two CTAs per SM (one query tile and 256 TMEM columns each):
+  // two slots each; while one CTA is between two work items (7 us of item fetch, Q load, pipeline fill
+  // and epilogue per item) the other one computes.
+  static_assert(CPS == 1 || (CPS == 2 && NQ == 1), "two CTAs per SM only with one query tile each");
+  static constexpr uint32_t KV_SLOTS = CPS == 2 ? 2 : 4;
+  static constexpr uint32_t TMEM_COLS = 256 * NQ;   // S_X at 128 X, O_X at 128 (NQ + X): 128 columns each
+  static constexpr uint32_t TM_S = 0, TM_O = 128 * NQ;
+  static constexpr uint32_t N_LOADERS = NQ;         // warps 0 .. NQ - 1 load tiles and issue P V, the next NQ warps issue Q K^T
+  static constexpr uint32_t FIRST_SM_WARP = 2 * NQ;
   static constexpr uint32_t THREADS = 32 * FIRST_SM_WARP + NQ * 128;
   static constexpr uint32_t OFF_Q = 0, OFF_K = NQ * OPER_B, OFF_V = OFF_K + KV_SLOTS * KV_TILE_B;
   static constexpr uint32_t SMEM = OFF_V + KV_SLOTS * KV_TILE_B + 1024;
@@ -180,13 +190,13 @@ __global__ void __launch_bounds__(256) prefill_expand_kernel(const uint8_t* __re
   *reinterpret_cast<uint4*>(out) = w;
 }
 
-template <uint32_t NQ, bool PX>  // PX: with the peer exchange in the epilogue (an instance of its own: the plain one pays nothing)
-__global__ void __launch_bounds__(PLayout<NQ>::THREADS, 1)
+template <uint32_t NQ, uint32_t CPS, bool PX>  // PX: with the peer exchange in the epilogue (an instance of its own: the plain one pays nothing)
+__global__ void __launch_bounds__(PLayout<NQ, CPS>::THREADS, CPS)
 prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const PrefillParams p) {
-  using L = PLayout<NQ>;
+  using L = PLayout<NQ, CPS>;
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t k_full[KV_SLOTS], v_full[KV_SLOTS];
-  __shared__ __align__(8) uint64_t k_empty[NQ][KV_SLOTS], v_empty[NQ][KV_SLOTS];  // per query tile: it is done with the slot
+  __shared__ __align__(8) uint64_t k_full[L::KV_SLOTS], v_full[L::KV_SLOTS];
+  __shared__ __align__(8) uint64_t k_empty[NQ][L::KV_SLOTS], v_empty[NQ][L::KV_SLOTS];  // per query tile: it is done with the slot
   __shared__ __align__(8) uint64_t s_ready[NQ][2], p_ready[NQ][2], p_free[NQ][2], o_done[NQ];
   __shared__ uint32_t tmem_base_s, item_s;
   __shared__ volatile uint32_t abort_s;
@@ -198,7 +208,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   const uint32_t n_items = p.n_groups * p.n_kv_head;   // work items: (group of NQ query tiles, KV head)
 
   if (threadIdx.x == 0) {
-    for (uint32_t i = 0; i < KV_SLOTS; i++) {
+    for (uint32_t i = 0; i < L::KV_SLOTS; i++) {
       mbar_init(smem_u32(&k_full[i]), 1);
       mbar_init(smem_u32(&v_full[i]), 1);
       for (uint32_t x = 0; x < NQ; x++) {
@@ -218,7 +228,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     abort_s = 0;
     fence_barrier_init();
   }
-  if (warp == 1) tmem_alloc(smem_u32(&tmem_base_s), P_TMEM_COLS);
+  if (warp == 1) tmem_alloc(smem_u32(&tmem_base_s), L::TMEM_COLS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -245,7 +255,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   // Barrier phases keep counting across work items: gkv = key tiles loaded so far by this CTA,
   // gx[X] = key tiles query tile X has gone through, items_done for the once-per-item o_done;
   // nothing is re-initialised between items. The producer keeps, per (query tile, slot), whether
-  // a release is outstanding and the phase it will complete (bit x * KV_SLOTS + slot).
+  // a release is outstanding and the phase it will complete (bit x * L::KV_SLOTS + slot).
   uint32_t gkv = 0, gx[NQ], od[NQ];
 #pragma unroll
   for (uint32_t x = 0; x < NQ; x++) { gx[x] = 0; od[x] = 0; }
@@ -293,69 +303,67 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     __syncthreads();
     tc_fence_after();
 
-    if (warp == 0 || warp == NQ + 1) {
+    if (warp < L::N_LOADERS) {
       // ---------------- loaders and P V issuers ----------------
-      // Two threads, neither of which ever blocks: warp 0 requests the V tiles and issues O_0 += P_0 V,
-      // warp NQ + 1 requests the K tiles and issues O_1 += P_1 V. A single thread issuing the P V of both
-      // query tiles was the bottleneck of this kernel: it needs about 1100 cycles per key tile and query
-      // tile (polls, four MMAs at 115 cycles each, three commits), so with two query tiles a P tile waited
-      // some 1400 cycles for its turn and the softmax groups then waited as long for the next S.
+      // Threads that never block. With two query tiles per CTA: warp 0 requests the V tiles and issues
+      // O_0 += P_0 V, warp 1 requests the K tiles and issues O_1 += P_1 V. A single thread issuing the
+      // P V of both query tiles was the bottleneck of this kernel: it needs about 1100 cycles per key tile
+      // and query tile (polls, four MMAs at 115 cycles each, three commits), so a P tile waited some 1400
+      // cycles for its turn and the softmax groups then waited as long for the next S. With one query
+      // tile per CTA warp 0 does all of it.
       if (lane == 0) {
         constexpr uint32_t IDESC_PV = umma_idesc(1, 0, 0, 0, 1, BM, 128);  // f32 += f16 (TMEM) x f16 (MN-major), N = 128 dims
         const uint64_t dmn = umma_desc_sw128(0, 8192, 1024);    // V: next 64 dims 8 KB away, 8 key rows 1 KB apart
-        const bool loads_k = warp != 0;
-        const uint32_t x = loads_k ? 1u : 0u;                   // the query tile whose P V this thread issues
-        const uint32_t n_pv = x < NQ ? nx[x < NQ ? x : 0] : 0u;
-        const CUtensorMap* map = loads_k ? &map_k : &map_v;
-        uint64_t* full = loads_k ? k_full : v_full;
-        const uint32_t dst0 = smem_base + (loads_k ? L::OFF_K : L::OFF_V);
-        uint32_t pend = loads_k ? pend_k : pend_v, phase = loads_k ? phase_k : phase_v;
-        uint32_t li = 0, ip = 0, spins = 0;  // tiles requested, P V issued
-        prefetch_tensormap(map);
-        while ((li < n_tiles || ip < n_pv) && !abort_s) {
-          bool progressed = false;
-          if (li < n_tiles) {
-            // the next tile, once every query tile that used the slot's last tile has released it
-            const uint32_t s = (gkv + li) % KV_SLOTS;
-            bool slot_free = true;
-            uint32_t users = 0;
+        const bool do_k = L::N_LOADERS == 1 || warp == 1, do_v = warp == 0;
+        const uint32_t x = warp;                                // the query tile whose P V this thread issues
+        const uint32_t n_pv = nx[x];
+        uint32_t lk = do_k ? 0u : n_tiles, lv = do_v ? 0u : n_tiles, ip = 0, spins = 0;  // tiles requested, P V issued
+        // the next tile of a stream, once every query tile that used the slot's last tile has released it
+        auto try_load = [&](bool is_k, uint32_t& li, uint32_t& pend, uint32_t& phase) {
+          const uint32_t s = (gkv + li) % L::KV_SLOTS;
+          bool slot_free = true;
+          uint32_t users = 0;
 #pragma unroll
-            for (uint32_t y = 0; y < NQ; y++) {
-              const uint32_t bit = 1u << (y * KV_SLOTS + s);
-              users |= li < nx[y] ? bit : 0u;
-              if (pend & bit) {
-                if (mbar_test(smem_u32(loads_k ? &k_empty[y][s] : &v_empty[y][s]), (phase & bit) ? 1u : 0u)) {
-                  pend &= ~bit;
-                  phase ^= bit;
-                } else {
-                  slot_free = false;
-                }
+          for (uint32_t y = 0; y < NQ; y++) {
+            const uint32_t bit = 1u << (y * L::KV_SLOTS + s);
+            users |= li < nx[y] ? bit : 0u;
+            if (pend & bit) {
+              if (mbar_test(smem_u32(is_k ? &k_empty[y][s] : &v_empty[y][s]), (phase & bit) ? 1u : 0u)) {
+                pend &= ~bit;
+                phase ^= bit;
+              } else {
+                slot_free = false;
               }
             }
-            if (slot_free) {
-              pend |= users;
-              mbar_arrive_expect_tx(smem_u32(&full[s]), KV_TILE_B);
-              tma_load_3d(dst0 + s * KV_TILE_B, map, smem_u32(&full[s]), 0, static_cast<int>(li * BN), static_cast<int>(2 * g));
-              li++;
-              progressed = true;
-            }
           }
+          if (!slot_free) return false;
+          pend |= users;
+          uint64_t* full = is_k ? &k_full[s] : &v_full[s];
+          mbar_arrive_expect_tx(smem_u32(full), KV_TILE_B);
+          tma_load_3d(smem_base + (is_k ? L::OFF_K : L::OFF_V) + s * KV_TILE_B, is_k ? &map_k : &map_v, smem_u32(full), 0,
+                      static_cast<int>(li * BN), static_cast<int>(2 * g));
+          li++;
+          return true;
+        };
+        while ((lk < n_tiles || lv < n_tiles || ip < n_pv) && !abort_s) {
+          bool progressed = false;
+          if (lk < n_tiles) progressed |= try_load(true, lk, pend_k, phase_k);
+          if (lv < n_tiles) progressed |= try_load(false, lv, pend_v, phase_v);
           if (ip < n_pv) {
-            const uint32_t xq = x < NQ ? x : 0;  // (x < NQ whenever n_pv > 0)
-            const uint32_t i = ip, s = (gkv + i) % KV_SLOTS, c = gx[xq] + i, b = c & 1;
+            const uint32_t i = ip, s = (gkv + i) % L::KV_SLOTS, c = gx[x] + i, b = c & 1;
             // one barrier per S buffer: the softmax group may run two tiles ahead of this test, and two
             // completions on one barrier would be indistinguishable from none
-            if (mbar_test(smem_u32(&p_ready[xq][b]), (c >> 1) & 1) &&
-                mbar_test(smem_u32(&v_full[s]), ((gkv + i) / KV_SLOTS) & 1)) {
+            if (mbar_test(smem_u32(&p_ready[x][b]), (c >> 1) & 1) &&
+                mbar_test(smem_u32(&v_full[s]), ((gkv + i) / L::KV_SLOTS) & 1)) {
               tc_fence_after();
               const uint64_t vb = dmn + ((smem_base + L::OFF_V + s * KV_TILE_B) >> 4);
-              const uint32_t s_col = tmem + TM_S + xq * SW, o_col = tmem + TM_O + xq * SW;
+              const uint32_t s_col = tmem + L::TM_S + x * SW, o_col = tmem + L::TM_O + x * SW;
 #pragma unroll
               for (uint32_t ks = 0; ks < 4; ks++)  // 16 keys per UMMA: 8 columns of P, 16 rows of V
                 umma_f16_ts(o_col, s_col + 64 * b + 8 * ks, vb + ks * (16 * 128 >> 4), IDESC_PV, (i | ks) ? 1u : 0u);
-              umma_commit(smem_u32(&p_free[xq][b]));   // P V of tile i complete: the S buffer may take the next Q K^T,
-              umma_commit(smem_u32(&v_empty[xq][s]));  // the V slot is free and O_X is consistent
-              if (++ip == n_pv) umma_commit(smem_u32(&o_done[xq]));
+              umma_commit(smem_u32(&p_free[x][b]));   // P V of tile i complete: the S buffer may take the next Q K^T,
+              umma_commit(smem_u32(&v_empty[x][s]));  // the V slot is free and O_X is consistent
+              if (++ip == n_pv) umma_commit(smem_u32(&o_done[x]));
               progressed = true;
             }
           }
@@ -366,27 +374,26 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             atomicExch(p.err, 5u);
           }
         }
-        if (loads_k) { pend_k = pend; phase_k = phase; } else { pend_v = pend; phase_v = phase; }
       }
-    } else if (warp <= NQ) {
+    } else if (warp < L::FIRST_SM_WARP) {
       // ---------------- Q K^T issuer of query tile X ----------------
       // One issuing thread sustains about one tcgen05.mma per 115 cycles whatever its size; the tensor
       // pipe takes one 128 x 128 x 16 MMA per 70 to 80 cycles from several threads (measured). So the
       // issue work is spread: one thread per query tile for S = Q K^T (8 MMAs per key tile), one more
       // for all P V (4 per key tile and query tile).
-      const uint32_t x = warp - 1;
+      const uint32_t x = warp - L::N_LOADERS;
       const uint32_t n_mine = nx[x], c0 = gx[x];
       if (lane == 0 && n_mine > 0) {
         constexpr uint32_t IDESC_QK = umma_idesc(1, 0, 0, 0, 0, BM, BN);   // f32 = f16 (K-major) x f16 (K-major), N = 64 keys
         const uint64_t dk = umma_desc_sw128(0, 16, 1024);       // K-major operands
         const uint64_t qa = dk + ((smem_base + L::OFF_Q + x * OPER_B) >> 4);
-        const uint32_t s_col = tmem + TM_S + x * SW;
+        const uint32_t s_col = tmem + L::TM_S + x * SW;
         // S of tile i goes to buffer (c0 + i) & 1 of the query tile's S region; P of the tile is
         // written over it and read from there by P V. Q K^T runs up to two tiles ahead of P V: a
         // buffer is free again when the P V of its previous tile has completed (p_free).
         for (uint32_t i = 0; i < n_mine; i++) {
-          const uint32_t s = (gkv + i) % KV_SLOTS, c = c0 + i, b = c & 1;
-          waitx(&k_full[s], ((gkv + i) / KV_SLOTS) & 1, 0);
+          const uint32_t s = (gkv + i) % L::KV_SLOTS, c = c0 + i, b = c & 1;
+          waitx(&k_full[s], ((gkv + i) / L::KV_SLOTS) & 1, 0);
           if (c >= 2) waitx(&p_free[x][b], ((c >> 1) - 1) & 1, 2);
           tc_fence_after();
           const uint64_t kb = dk + ((smem_base + L::OFF_K + s * KV_TILE_B) >> 4);
@@ -403,13 +410,13 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       const uint32_t x = (warp - L::FIRST_SM_WARP) >> 2, quad = warp & 3, r = quad * 32 + lane;
       const bool elected = ((warp - L::FIRST_SM_WARP) & 3) == 0 && lane == 0;  // releases the K slots for this query tile
       const uint32_t lane_addr = (quad * 32) << 16;
-      const uint32_t s_addr = tmem + lane_addr + TM_S + x * SW, o_addr = tmem + lane_addr + TM_O + x * SW;
+      const uint32_t s_addr = tmem + lane_addr + L::TM_S + x * SW, o_addr = tmem + lane_addr + L::TM_O + x * SW;
       const uint32_t tok = tq0[x] + r / p.qpg;
       const uint32_t n_mine = nx[x], c0 = gx[x];
       float m_run = NEG_BIG, l_run = 0.f;
       uint32_t prev_par = 0, prev_slot = 0;  // phase and slot of the previous tile's "P V complete" barrier
       for (uint32_t i = 0; i < n_mine; i++) {
-        const uint32_t b = (c0 + i) & 1, slot = (gkv + i) % KV_SLOTS;
+        const uint32_t b = (c0 + i) & 1, slot = (gkv + i) % L::KV_SLOTS;
         waitx(&s_ready[x][b], ((c0 + i) >> 1) & 1, 0);
         tc_fence_after();
         const long long tp0 = dbg_on ? clock64() : 0;
@@ -548,8 +555,8 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     __syncthreads();  // the item is finished by every role: Q, S and O can be reused
     tc_fence_after();
   }
-  if (dbg_on && (warp == 0 || warp == 1 || warp == L::FIRST_SM_WARP || warp == L::FIRST_SM_WARP + 4 || warp == NQ + 1)) {
-    const uint32_t role = warp == 0 ? 0 : warp == 1 ? 1 : warp == L::FIRST_SM_WARP ? 2 : warp == NQ + 1 ? 6 : 3;
+  if (dbg_on && (warp == 0 || warp == L::N_LOADERS || warp == L::FIRST_SM_WARP || warp == L::FIRST_SM_WARP + 4)) {
+    const uint32_t role = warp == 0 ? 0 : warp == L::N_LOADERS ? 1 : warp == L::FIRST_SM_WARP ? 2 : 3;
     p.dbg[role * 8] = static_cast<unsigned long long>(clock64() - t_begin);
     for (int k = 0; k < 4; k++) p.dbg[role * 8 + 1 + k] = static_cast<unsigned long long>(tw[k]);
     p.dbg[role * 8 + 7] = gkv;
@@ -557,7 +564,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem, P_TMEM_COLS);
+  if (warp == 1) tmem_dealloc(tmem, L::TMEM_COLS);
 }
 
 }  // namespace
@@ -590,13 +597,15 @@ cudaError_t bp_prefill_init(bp_attn_ctx* c) {
                            es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
   }
-  e = cudaFuncSetAttribute(prefill_umma_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(PLayout<1>::SMEM));
-  if (e != cudaSuccess) return e;
-  e = cudaFuncSetAttribute(prefill_umma_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(PLayout<1>::SMEM));
-  if (e != cudaSuccess) return e;
-  e = cudaFuncSetAttribute(prefill_umma_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(PLayout<2>::SMEM));
-  if (e != cudaSuccess) return e;
-  return cudaFuncSetAttribute(prefill_umma_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(PLayout<2>::SMEM));
+  auto allow = [](auto kernel, uint32_t bytes) {
+    return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+  };
+  if ((e = allow(prefill_umma_kernel<1, 1, false>, PLayout<1, 1>::SMEM)) != cudaSuccess) return e;
+  if ((e = allow(prefill_umma_kernel<1, 1, true>, PLayout<1, 1>::SMEM)) != cudaSuccess) return e;
+  if ((e = allow(prefill_umma_kernel<1, 2, false>, PLayout<1, 2>::SMEM)) != cudaSuccess) return e;
+  if ((e = allow(prefill_umma_kernel<1, 2, true>, PLayout<1, 2>::SMEM)) != cudaSuccess) return e;
+  if ((e = allow(prefill_umma_kernel<2, 1, false>, PLayout<2, 1>::SMEM)) != cudaSuccess) return e;
+  return allow(prefill_umma_kernel<2, 1, true>, PLayout<2, 1>::SMEM);
 }
 
 cudaError_t bp_launch_prefill(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, const __half* q,
@@ -634,29 +643,26 @@ cudaError_t bp_launch_prefill(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, co
   p.px_out = c->ppx_dev;
   const uint32_t tq_tokens = BM / c->qpg;
   const uint32_t sms = static_cast<uint32_t>(c->sm_count);
-  // Two query tiles per item keep the tensor core busy during softmax; a batch too small to give
-  // every SM such an item is cut into single tiles instead.
-  const uint32_t groups2 = (m + 2 * tq_tokens - 1) / (2 * tq_tokens);
-  const bool pair = c->opt_pf_nq == 2 || (c->opt_pf_nq == 0 && groups2 * c->cfg.n_kv_head >= sms);
-  if (pair) {
-    p.n_groups = groups2;
-    const uint32_t n_items = p.n_groups * c->cfg.n_kv_head;
+  // Work items of ONE query tile, two CTAs per SM, whenever there are more items than SMs: measured
+  // 49.0 against 50.9 us per layer at 2048 tokens and 25.3 against 28.3 at 1024 for items of two query
+  // tiles on one CTA per SM (which load every K / V tile once for both). A batch with at most one item
+  // per SM runs one CTA per SM with four slots. Option prefill_tiles_per_item: 0 = that choice, 1 = one
+  // tile and one CTA per SM, 2 = two tiles (one CTA per SM), 3 = one tile and two CTAs per SM.
+  auto launch = [&](auto kernel, uint32_t nq, uint32_t cps, uint32_t threads, uint32_t smem) {
+    p.n_groups = (m + nq * tq_tokens - 1) / (nq * tq_tokens);
+    const uint32_t n_items = p.n_groups * c->cfg.n_kv_head, slots = sms * cps, grid = n_items < slots ? n_items : slots;
     *launches += 1;
-    bp_note_sm_launch(c, n_items < sms ? n_items : sms);
-    if (p.n_px != 0)
-      return bp_launch(c->opt_pdl != 0, prefill_umma_kernel<2, true>, dim3(n_items < sms ? n_items : sms), dim3(PLayout<2>::THREADS),
-                       PLayout<2>::SMEM, s, c->pmap16[0], c->pmap16[1], p);
-    return bp_launch(c->opt_pdl != 0, prefill_umma_kernel<2, false>, dim3(n_items < sms ? n_items : sms), dim3(PLayout<2>::THREADS),
-                     PLayout<2>::SMEM, s, c->pmap16[0], c->pmap16[1], p);
-  } else {
-    p.n_groups = (m + tq_tokens - 1) / tq_tokens;
-    const uint32_t n_items = p.n_groups * c->cfg.n_kv_head;
-    *launches += 1;
-    bp_note_sm_launch(c, n_items < sms ? n_items : sms);
-    if (p.n_px != 0)
-      return bp_launch(c->opt_pdl != 0, prefill_umma_kernel<1, true>, dim3(n_items < sms ? n_items : sms), dim3(PLayout<1>::THREADS),
-                       PLayout<1>::SMEM, s, c->pmap16[0], c->pmap16[1], p);
-    return bp_launch(c->opt_pdl != 0, prefill_umma_kernel<1, false>, dim3(n_items < sms ? n_items : sms), dim3(PLayout<1>::THREADS),
-                     PLayout<1>::SMEM, s, c->pmap16[0], c->pmap16[1], p);
-  }
+    bp_note_sm_launch(c, grid < sms ? grid : sms);
+    return bp_launch(c->opt_pdl != 0, kernel, dim3(grid), dim3(threads), smem, s, c->pmap16[0], c->pmap16[1], p);
+  };
+  const bool px = p.n_px != 0;
+  if (c->opt_pf_nq == 2)
+    return px ? launch(prefill_umma_kernel<2, 1, true>, 2, 1, PLayout<2, 1>::THREADS, PLayout<2, 1>::SMEM)
+              : launch(prefill_umma_kernel<2, 1, false>, 2, 1, PLayout<2, 1>::THREADS, PLayout<2, 1>::SMEM);
+  const uint32_t items1 = (m + tq_tokens - 1) / tq_tokens * c->cfg.n_kv_head;
+  if (c->opt_pf_nq == 3 || (c->opt_pf_nq == 0 && items1 > sms))
+    return px ? launch(prefill_umma_kernel<1, 2, true>, 1, 2, PLayout<1, 2>::THREADS, PLayout<1, 2>::SMEM)
+              : launch(prefill_umma_kernel<1, 2, false>, 1, 2, PLayout<1, 2>::THREADS, PLayout<1, 2>::SMEM);
+  return px ? launch(prefill_umma_kernel<1, 1, true>, 1, 1, PLayout<1, 1>::THREADS, PLayout<1, 1>::SMEM)
+            : launch(prefill_umma_kernel<1, 1, false>, 1, 1, PLayout<1, 1>::THREADS, PLayout<1, 1>::SMEM);
 }

@@ -829,7 +829,7 @@ int bp_set_option(bp_attn_ctx* c, const char* name, uint32_t value) {
     if (value > 3) return fail_config(c, "tma_l2_promotion must be 0 (256 B), 1 (128 B), 2 (64 B) or 3 (none)");
     c->opt_l2promo = value;
   } else if (strcmp(name, "prefill_tiles_per_item") == 0) {
-    if (value > 2) return fail_config(c, "prefill_tiles_per_item must be 0 (by batch size), 1 or 2");
+    if (value > 3) return fail_config(c, "prefill_tiles_per_item must be 0 (by batch size), 1, 2 or 3");
     c->opt_pf_nq = value;
     return BP_OK;
   } else {

@@ -253,8 +253,10 @@ int bp_set_variant(bp_attn_ctx* ctx, uint32_t variant);
 /* Tuning knobs of the decode kernel: "decode_warps" (8 or 16 compute warps per
  * CTA) and "decode_heads_per_cta" (KV heads streamed by one CTA; a power of two
  * dividing n_kv_head), "decode_umma_heads_per_cta" (1 or 2, tcgen05 decode) and
- * "prefill_tiles_per_item" (query tiles one prefill work item owns: 1, 2, or 0 =
- * chosen by batch size). Launch structure: "dependent_launch" (1 = kernels are
+ * "prefill_tiles_per_item" (layout of the prefill kernel: 1 = work items of one
+ * query tile, one CTA per SM; 2 = two query tiles, one CTA per SM; 3 = one query
+ * tile, two CTAs per SM; 0 = chosen by batch size: 3 when there are more work
+ * items than SMs, else 1). Launch structure: "dependent_launch" (1 = kernels are
  * launched with programmatic stream serialization, the default), "decode_in_kernel_merge"
  * (1 = the tcgen05 decode kernel merges its splits itself, the default; 0 = a
  * second kernel does), "decode_ring" (K stages * 16 + V slots of the tcgen05

@@ -549,7 +549,7 @@ def test_decode_launch_structure_options_do_not_change_results(merge, pdl):
         assert np.abs(got.astype(np.float32) - base.astype(np.float32)).max() <= 1e-3
 
 
-@pytest.mark.parametrize("tiles_per_item", [1, 2])
+@pytest.mark.parametrize("tiles_per_item", [1, 2, 3])
 @pytest.mark.parametrize("m", [65, 129, 512, 700, 2048])
 def test_prefill_tile_modes_against_the_scalar_kernel(m, tiles_per_item):
     """Both work-item shapes of the tensor-core prefill kernel (one or two query tiles per item), on sizes
@@ -626,7 +626,7 @@ def test_prefill_on_a_kv_head_shard(n_head, n_kv_head):
         ctx.dispatch_attention(0, q, ref, m)
         torch.cuda.synchronize()
         ctx.set_variant(0)
-        for tiles in (0, 1, 2):
+        for tiles in (0, 1, 2, 3):
             ctx.set_option("prefill_tiles_per_item", tiles)
             out = torch.full((m, n_head * 128), float("nan"), dtype=torch.float16, device="cuda")
             ctx.dispatch_attention(0, q, out, m)
