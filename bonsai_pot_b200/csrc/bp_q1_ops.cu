@@ -395,6 +395,182 @@ __global__ void __launch_bounds__(256) matmul_q1_q8_kernel(const __half* w_d, co
   }
 }
 
+// The same product on the tensor cores, for batches of more than MMA_MIN_M tokens. The integer dot of a
+// sub-block of 32 (int8 activations with weights of +1 / -1) is computed as an f16 MMA with FP32
+// accumulation: every operand is an integer below 2^11 and every partial sum an integer below 2^13, so the
+// result is the exact integer whatever the order of the additions, already in FP32. What the reference
+// does in floating point, y += (a_d * w_d) * f32(sumi) per sub-block in ascending order, is done here
+// in the same order by the thread that holds the MMA's accumulator, so the result has the same bits.
+// A CTA owns 128 tokens x 128 weight rows, a warp 64 x 32 (4 x 4 MMA tiles of m16 n8). Per block of 128
+// inputs the CTA stages the activations as f16 [128][128] and the weights as +-1 f16 [128][128] in shared
+// memory (16-byte chunks xor-swizzled by the row, read back with ldmatrix); the next block's global loads
+// are in flight while the current one is multiplied.
+constexpr uint32_t MMA_MIN_M = 32;
+constexpr uint32_t MT = 128;                        // tile edge, tokens and weight rows
+constexpr uint32_t MMA_TILE_B = MT * 128 * 2;       // one operand tile: 128 rows of 128 halves
+constexpr uint32_t MMA_SMEM = 4 * MMA_TILE_B + 2 * (MT * 4 + MT) * 4 + 128;  // A, B double-buffered, scales, sign table
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_f16_f32(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1, const float (&c)[4]) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %11, %12, %13};"
+               : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
+}
+// four int8 -> four f16, exactly: bias to unsigned, 0x6400 | byte = 1024 + byte, minus 1152
+__device__ __forceinline__ uint2 s8x4_to_f16x4(uint32_t x) {
+  x ^= 0x80808080u;
+  uint32_t lo = __byte_perm(x, 0x64646464u, 0x4140), hi = __byte_perm(x, 0x64646464u, 0x4342);
+  const __half2 bias = __halves2half2(__ushort_as_half(0x6480), __ushort_as_half(0x6480));
+  __half2 l = __hsub2(*reinterpret_cast<__half2*>(&lo), bias), h = __hsub2(*reinterpret_cast<__half2*>(&hi), bias);
+  return make_uint2(*reinterpret_cast<uint32_t*>(&l), *reinterpret_cast<uint32_t*>(&h));
+}
+
+__global__ void __launch_bounds__(256, 1) matmul_q1_q8_mma_kernel(const __half* __restrict__ w_d, const uint8_t* __restrict__ w_qs,
+                                                                  uint32_t k, uint32_t n, uint32_t m, const float* __restrict__ a_d,
+                                                                  const int8_t* __restrict__ a_qs, __half* y, uint32_t accumulate) {
+  extern __shared__ __align__(1024) uint8_t mm_smem[];
+  uint8_t* sA = mm_smem;                                   // [2][128 tokens][128 halves]
+  uint8_t* sB = mm_smem + 2 * MMA_TILE_B;                  // [2][128 weight rows][128 halves]
+  float* s_ad = reinterpret_cast<float*>(mm_smem + 4 * MMA_TILE_B);      // [2][128][4]
+  float* s_wd = s_ad + 2 * MT * 4;                                        // [2][128]
+  uint2* s_sign = reinterpret_cast<uint2*>(s_wd + 2 * MT);               // nibble of sign bits -> four halves of +-1
+  pdl_launch_dependents();
+  pdl_wait();
+  const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t n_base = blockIdx.x * MT, m_base = blockIdx.y * MT;
+  const uint32_t nb1 = k / 128u, nb8 = k / 32u;
+  if (tid < 16) {
+    uint32_t h[4];
+#pragma unroll
+    for (int e = 0; e < 4; e++) h[e] = (tid >> e) & 1u ? 0x3C00u : 0xBC00u;  // bit set: +1, clear: -1
+    s_sign[tid] = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
+  }
+  // staging: thread -> (row, half of the row's 128 inputs)
+  const uint32_t srow = tid >> 1, shalf = tid & 1;
+  const bool a_ok = m_base + srow < m, b_ok = n_base + srow < n;
+  const int8_t* a_src = a_qs + static_cast<size_t>(m_base + srow) * k + 64u * shalf;
+  const uint8_t* b_src = w_qs + static_cast<size_t>(n_base + srow) * nb1 * 16u + 8u * shalf;
+  uint4 ra[4];
+  uint2 rb;
+  float4 rad;
+  float rwd;
+  auto fetch = [&](uint32_t b) {
+#pragma unroll
+    for (int c = 0; c < 4; c++) ra[c] = a_ok ? *reinterpret_cast<const uint4*>(a_src + 128u * b + 16u * c) : make_uint4(0, 0, 0, 0);
+    rb = b_ok ? *reinterpret_cast<const uint2*>(b_src + 16u * b) : make_uint2(0, 0);
+    if (tid < MT) {
+      rad = m_base + tid < m ? *reinterpret_cast<const float4*>(a_d + static_cast<size_t>(m_base + tid) * nb8 + 4u * b)
+                             : make_float4(0.f, 0.f, 0.f, 0.f);
+    } else {
+      const uint32_t ni = n_base + tid - MT;
+      rwd = ni < n ? __half2float(w_d[static_cast<size_t>(ni) * nb1 + b]) : 0.0f;
+    }
+  };
+  auto stage = [&](uint32_t buf) {
+    uint8_t* arow = sA + buf * MMA_TILE_B + srow * 256u;
+    uint8_t* brow = sB + buf * MMA_TILE_B + srow * 256u;
+#pragma unroll
+    for (int c = 0; c < 4; c++) {  // 16 int8 -> two chunks of 8 halves
+      const uint2 h0 = s8x4_to_f16x4(ra[c].x), h1 = s8x4_to_f16x4(ra[c].y), h2 = s8x4_to_f16x4(ra[c].z), h3 = s8x4_to_f16x4(ra[c].w);
+      const uint32_t ch = shalf * 8u + 2u * c;
+      *reinterpret_cast<uint4*>(arow + (((ch) ^ (srow & 7u)) << 4)) = make_uint4(h0.x, h0.y, h1.x, h1.y);
+      *reinterpret_cast<uint4*>(arow + (((ch + 1u) ^ (srow & 7u)) << 4)) = make_uint4(h2.x, h2.y, h3.x, h3.y);
+    }
+    const uint32_t wq[2] = {rb.x, rb.y};
+#pragma unroll
+    for (int j = 0; j < 8; j++) {  // one byte of signs -> one chunk of 8 halves
+      const uint32_t byte = (wq[j >> 2] >> (8 * (j & 3))) & 0xFFu;
+      const uint2 lo = s_sign[byte & 15u], hi = s_sign[byte >> 4];
+      *reinterpret_cast<uint4*>(brow + (((shalf * 8u + j) ^ (srow & 7u)) << 4)) = make_uint4(lo.x, lo.y, hi.x, hi.y);
+    }
+    if (tid < MT) {
+      *reinterpret_cast<float4*>(s_ad + buf * MT * 4 + tid * 4) = rad;
+    } else {
+      s_wd[buf * MT + tid - MT] = rwd;
+    }
+  };
+  const uint32_t wm = warp >> 2, wn = warp & 3, g = lane >> 2, t = lane & 3;
+  float acc[4][4][4];
+#pragma unroll
+  for (int i = 0; i < 4; i++)
+#pragma unroll
+    for (int j = 0; j < 4; j++)
+#pragma unroll
+      for (int e = 0; e < 4; e++) acc[i][j][e] = 0.0f;
+  const float zero4[4] = {0.f, 0.f, 0.f, 0.f};
+  // ldmatrix row addresses of this lane: matrix lane >> 3, row lane & 7
+  const uint32_t lm = lane >> 3, lr = lane & 7;
+  const uint32_t a_row0 = wm * 64u + (lm & 1u) * 8u + lr, a_chunk0 = lm >> 1;        // + 16 per m tile; chunk + 2 per k16 step
+  const uint32_t b_row0 = wn * 32u + (lm >> 1) * 8u + lr, b_chunk0 = lm & 1u;        // + 16 per pair of n tiles
+  const uint32_t sA_u = static_cast<uint32_t>(__cvta_generic_to_shared(sA)), sB_u = static_cast<uint32_t>(__cvta_generic_to_shared(sB));
+
+  __syncthreads();  // the sign table
+  fetch(0);
+  stage(0);
+  __syncthreads();
+  for (uint32_t b = 0; b < nb1; b++) {
+    const uint32_t buf = b & 1u;
+    if (b + 1 < nb1) fetch(b + 1);
+    const float* ad = s_ad + buf * MT * 4;
+    const float* wd = s_wd + buf * MT;
+    float wdv[4][2];
+#pragma unroll
+    for (int nt = 0; nt < 4; nt++) {
+      wdv[nt][0] = wd[wn * 32u + nt * 8u + 2u * t];
+      wdv[nt][1] = wd[wn * 32u + nt * 8u + 2u * t + 1u];
+    }
+#pragma unroll 1
+    for (uint32_t s = 0; s < 4; s++) {
+      uint32_t bf[2][4][2];  // [k16 step][n tile][register]
+#pragma unroll
+      for (uint32_t ks = 0; ks < 2; ks++)
+#pragma unroll
+        for (uint32_t jp = 0; jp < 2; jp++) {
+          const uint32_t row = b_row0 + jp * 16u, chunk = s * 4u + ks * 2u + b_chunk0;
+          ldmatrix_x4(sB_u + buf * MMA_TILE_B + row * 256u + ((chunk ^ (row & 7u)) << 4), bf[ks][2 * jp][0], bf[ks][2 * jp][1],
+                      bf[ks][2 * jp + 1][0], bf[ks][2 * jp + 1][1]);
+        }
+#pragma unroll
+      for (uint32_t mt = 0; mt < 4; mt++) {
+        uint32_t af[2][4];
+#pragma unroll
+        for (uint32_t ks = 0; ks < 2; ks++) {
+          const uint32_t row = a_row0 + mt * 16u, chunk = s * 4u + ks * 2u + a_chunk0;
+          ldmatrix_x4(sA_u + buf * MMA_TILE_B + row * 256u + ((chunk ^ (row & 7u)) << 4), af[ks][0], af[ks][1], af[ks][2], af[ks][3]);
+        }
+        const float ad_lo = ad[(wm * 64u + mt * 16u + g) * 4u + s], ad_hi = ad[(wm * 64u + mt * 16u + g + 8u) * 4u + s];
+#pragma unroll
+        for (uint32_t nt = 0; nt < 4; nt++) {
+          float d[4];
+          mma_f16_f32(d, af[0], bf[0][nt][0], bf[0][nt][1], zero4);
+          mma_f16_f32(d, af[1], bf[1][nt][0], bf[1][nt][1], d);
+          acc[mt][nt][0] = __fadd_rn(acc[mt][nt][0], __fmul_rn(__fmul_rn(ad_lo, wdv[nt][0]), d[0]));
+          acc[mt][nt][1] = __fadd_rn(acc[mt][nt][1], __fmul_rn(__fmul_rn(ad_lo, wdv[nt][1]), d[1]));
+          acc[mt][nt][2] = __fadd_rn(acc[mt][nt][2], __fmul_rn(__fmul_rn(ad_hi, wdv[nt][0]), d[2]));
+          acc[mt][nt][3] = __fadd_rn(acc[mt][nt][3], __fmul_rn(__fmul_rn(ad_hi, wdv[nt][1]), d[3]));
+        }
+      }
+    }
+    if (b + 1 < nb1) stage(buf ^ 1u);
+    __syncthreads();
+  }
+#pragma unroll
+  for (uint32_t mt = 0; mt < 4; mt++)
+#pragma unroll
+    for (uint32_t nt = 0; nt < 4; nt++)
+#pragma unroll
+      for (uint32_t e = 0; e < 4; e++) {
+        const uint32_t mi = m_base + wm * 64u + mt * 16u + g + (e >> 1) * 8u, ni = n_base + wn * 32u + nt * 8u + 2u * t + (e & 1u);
+        if (mi >= m || ni >= n) continue;
+        __half* dst = y + static_cast<size_t>(mi) * n + ni;
+        const float v = accumulate ? __fadd_rn(__half2float(*dst), acc[mt][nt][e]) : acc[mt][nt][e];
+        *dst = __float2half_rn(v);
+      }
+}
+
 // topk_reduce.wgsl:59-196, the same steps on the same lists (256 per-thread min-heaps of 32, heapsort, then
 // log2(256) bitonic merge rounds), so that ties fall exactly where the shader's comparisons put them. What
 // differs is only how the steps are scheduled on a warp:
@@ -648,6 +824,16 @@ cudaError_t bp_q1_quantize_q8(bool pdl, cudaStream_t s, const __half* x, uint32_
 
 cudaError_t bp_q1_matmul(bool pdl, cudaStream_t s, const bp_q1_tensor& w, uint32_t m, const float* a_d, const int8_t* a_qs, __half* y,
                          bool accumulate) {
+  if (m > MMA_MIN_M) {
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(matmul_q1_q8_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(MMA_SMEM));
+      if (e != cudaSuccess) return e;
+      configured = true;
+    }
+    dim3 grid((w.n + MT - 1) / MT, (m + MT - 1) / MT);
+    return bp_launch(pdl, matmul_q1_q8_mma_kernel, grid, dim3(256), MMA_SMEM, s, w.d, w.qs, w.k, w.n, m, a_d, a_qs, y, accumulate ? 1u : 0u);
+  }
   dim3 grid((w.n + MM_T - 1) / MM_T, (m + MM_T - 1) / MM_T);
   return bp_launch(pdl, matmul_q1_q8_kernel, grid, dim3(256), 0, s, w.d, w.qs, w.k, w.n, m, a_d, a_qs, y, accumulate ? 1u : 0u);
 }

@@ -135,7 +135,8 @@ def test_rms_norm_silu_mul_embed_quantize_bit_exact():
     assert np.array_equal(q_out.cpu().numpy(), want_q)
 
 
-@pytest.mark.parametrize("k,n,m,accumulate", [(512, 256, 1, False), (512, 200, 7, True), (1536, 512, 130, True), (4096, 1024, 64, False)])
+@pytest.mark.parametrize("k,n,m,accumulate", [(512, 256, 1, False), (512, 200, 7, True), (1536, 512, 130, True), (4096, 1024, 64, False),
+                                              (512, 200, 40, True), (1024, 300, 257, False), (256, 128, 33, False)])
 def test_matmul_q1_0_q8_0_bit_exact(k, n, m, accumulate):
     lib = _lib.load()
     rng = np.random.default_rng(k + m)
