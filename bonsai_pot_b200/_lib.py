@@ -138,6 +138,8 @@ MODEL_SIGNATURES = {
     "bp_op_embed": (_int, [_vp, _vp, _vp, _u32, _vp, _u32, _vp]),
     "bp_op_quantize_q8_0": (_int, [_vp, _vp, _u32, _u32, _vp, _vp]),
     "bp_op_matmul_q1_0_q8_0": (_int, [_vp, _vp, _vp, _u32, _u32, _u32, _vp, _vp, _vp, _u32]),
+    "bp_op_set_matmul_variant": (None, [_u32]),
+    "bp_op_device_status": (_int, []),
     "bp_op_topk_reduce": (_int, [_vp, _vp, _u32, _u32, _vp, _vp]),
     "bp_model_check_dir": (_int, [C.c_char_p, C.c_char_p, C.c_size_t]),
     "bp_model_load": (_int, [C.c_char_p, _u32, C.c_int32, _pp]),

@@ -414,7 +414,7 @@ int quantize_and_matmul(bp_model* m, const __half* act, uint32_t k, uint32_t mt,
                         bool accumulate) {
   cudaStream_t s = m->stream;
   M_CUDA(m, bp_q1_quantize_q8(true, s, act, k, mt, m->a_d, m->a_qs));
-  for (uint32_t i = 0; i < n_w; i++) M_CUDA(m, bp_q1_matmul(true, s, w[i], mt, m->a_d, m->a_qs, out[i], accumulate));
+  M_CUDA(m, bp_q1_matmul_multi(true, s, w, out, n_w, mt, m->a_d, m->a_qs, accumulate, m->attn->err_dev, m->attn->opt_wait_limit));
   return BP_OK;
 }
 
@@ -504,6 +504,13 @@ int bp_op_matmul_q1_0_q8_0(void* stream, const void* d, const void* qs, uint32_t
   if (m == 0) return BP_OK;
   return OP_CUDA(bp_q1_matmul(false, static_cast<cudaStream_t>(stream), op_tensor(d, qs, nullptr, k, n), m, static_cast<const float*>(a_d),
                               static_cast<const int8_t*>(a_qs), static_cast<__half*>(y), accumulate != 0));
+}
+void bp_op_set_matmul_variant(uint32_t variant) { bp_q1_set_matmul_variant(variant); }
+int bp_op_device_status(void) {
+  if (cudaDeviceSynchronize() != cudaSuccess) return BP_ERR_CUDA;
+  uint32_t code = 0;
+  if (bp_q1_take_error(&code) != cudaSuccess) return BP_ERR_CUDA;
+  return code != 0 ? BP_ERR_TIMEOUT : BP_OK;
 }
 int bp_op_topk_reduce(void* stream, const void* logits, uint32_t n, uint32_t k, void* out_val, void* out_idx) {
   if (!logits || !out_val || !out_idx) return BP_ERR_NULL;

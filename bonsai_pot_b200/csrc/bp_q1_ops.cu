@@ -395,29 +395,30 @@ __global__ void __launch_bounds__(256) matmul_q1_q8_kernel(const __half* w_d, co
   }
 }
 
-// The same product on the tensor cores, for batches of more than MMA_MIN_M tokens. The integer dot of a
-// sub-block of 32 (int8 activations with weights of +1 / -1) is computed as an f16 MMA with FP32
-// accumulation: every operand is an integer below 2^11 and every partial sum an integer below 2^13, so the
-// result is the exact integer whatever the order of the additions, already in FP32. What the reference
-// does in floating point, y += (a_d * w_d) * f32(sumi) per sub-block in ascending order, is done here
-// in the same order by the thread that holds the MMA's accumulator, so the result has the same bits.
-// A CTA owns 128 tokens x 128 weight rows, a warp 64 x 32 (4 x 4 MMA tiles of m16 n8). Per block of 128
-// inputs the CTA stages the activations as f16 [128][128] and the weights as +-1 f16 [128][128] in shared
-// memory (16-byte chunks xor-swizzled by the row, read back with ldmatrix); the next block's global loads
-// are in flight while the current one is multiplied.
+// The same product with warp-level MMAs (mma.sync m16n8k32, int8 x int8 -> int32), for batches of more than
+// MMA_MIN_M tokens: the integer dot of a sub-block of 32 is one MMA of the int8 activations with the weights
+// as +1 / -1 bytes. What the reference does in floating point, y += (a_d * w_d) * f32(sumi) per sub-block
+// in ascending order, is done in the same order by the thread that holds the MMA's accumulator, so the result
+// has the same bits. A CTA of 16 warps owns 128 tokens x 128 weight rows, a warp 32 x 32 (2 x 4 MMA tiles
+// of m16 n8). Per block of 128 inputs the CTA stages the activations [128][128] and the weights as +-1
+// bytes [128][128] in shared memory (16-byte chunks xor-swizzled by the row, read back with ldmatrix); the
+// next block's global loads are in flight while the current one is multiplied.
 constexpr uint32_t MMA_MIN_M = 32;
 constexpr uint32_t MT = 128;                        // tile edge, tokens and weight rows
-constexpr uint32_t MMA_TILE_B = MT * 128 * 2;       // one operand tile: 128 rows of 128 halves
-constexpr uint32_t MMA_SMEM = 4 * MMA_TILE_B + 2 * (MT * 4 + MT) * 4 + 128;  // A, B double-buffered, scales, sign table
+constexpr uint32_t MMA_TILE_B = MT * 128;           // one operand tile: 128 rows of 128 int8
+constexpr uint32_t MMA_SMEM = 4 * MMA_TILE_B + 2 * (MT * 4 + MT) * 4 + 64;  // A, B double-buffered, scales, sign table
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
                : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
 }
-__device__ __forceinline__ void mma_f16_f32(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1, const float (&c)[4]) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %11, %12, %13};"
-               : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
+__device__ __forceinline__ void mma_s8_s32(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
+               : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0));
+}
+__device__ __forceinline__ float q1_s32_to_f32(int x) {  // exact for |x| < 2^22
+  return __int_as_float(x + 0x4B400000) - 12582912.0f;
 }
 // four int8 -> four f16, exactly: bias to unsigned, 0x6400 | byte = 1024 + byte, minus 1152
 __device__ __forceinline__ uint2 s8x4_to_f16x4(uint32_t x) {
@@ -428,82 +429,97 @@ __device__ __forceinline__ uint2 s8x4_to_f16x4(uint32_t x) {
   return make_uint2(*reinterpret_cast<uint32_t*>(&l), *reinterpret_cast<uint32_t*>(&h));
 }
 
-__global__ void __launch_bounds__(256, 1) matmul_q1_q8_mma_kernel(const __half* __restrict__ w_d, const uint8_t* __restrict__ w_qs,
-                                                                  uint32_t k, uint32_t n, uint32_t m, const float* __restrict__ a_d,
-                                                                  const int8_t* __restrict__ a_qs, __half* y, uint32_t accumulate) {
+constexpr uint32_t MMA_THREADS = 512, MMA_MT_W = 2;   // m16 tiles per warp (warps: 4 along the tokens x 4 along the weight rows)
+constexpr uint32_t MMA_SEG = MT * 128 / MMA_THREADS;  // inputs of one row that a thread stages: 32
+
+// Up to three weight tensors over the same activations in one launch (Q, K and V of a layer: the K and V
+// projections alone would fill a fifth of the device each): tile blockIdx.x belongs to the tensor whose
+// range of tiles contains it.
+struct MmaTensors {
+  const __half* w_d[3];
+  const uint8_t* w_qs[3];
+  __half* y[3];
+  uint32_t n[3];
+  uint32_t tile_end[3];  // running total of 128-row tiles
+};
+
+__global__ void __launch_bounds__(MMA_THREADS, 1) matmul_q1_q8_mma_kernel(const MmaTensors tensors, uint32_t k, uint32_t m,
+                                                                  const float* __restrict__ a_d, const int8_t* __restrict__ a_qs,
+                                                                  uint32_t accumulate) {
+  const uint32_t which = blockIdx.x < tensors.tile_end[0] ? 0u : blockIdx.x < tensors.tile_end[1] ? 1u : 2u;
+  const __half* __restrict__ w_d = tensors.w_d[which];
+  const uint8_t* __restrict__ w_qs = tensors.w_qs[which];
+  __half* y = tensors.y[which];
+  const uint32_t n = tensors.n[which];
   extern __shared__ __align__(1024) uint8_t mm_smem[];
-  uint8_t* sA = mm_smem;                                   // [2][128 tokens][128 halves]
-  uint8_t* sB = mm_smem + 2 * MMA_TILE_B;                  // [2][128 weight rows][128 halves]
+  uint8_t* sA = mm_smem;                                   // [2][128 tokens][128 int8]
+  uint8_t* sB = mm_smem + 2 * MMA_TILE_B;                  // [2][128 weight rows][128 bytes of +1 / -1]
   float* s_ad = reinterpret_cast<float*>(mm_smem + 4 * MMA_TILE_B);      // [2][128][4]
   float* s_wd = s_ad + 2 * MT * 4;                                        // [2][128]
-  uint2* s_sign = reinterpret_cast<uint2*>(s_wd + 2 * MT);               // nibble of sign bits -> four halves of +-1
+  uint32_t* s_sign = reinterpret_cast<uint32_t*>(s_wd + 2 * MT);         // nibble of sign bits -> four bytes of +-1
   pdl_launch_dependents();
   pdl_wait();
   const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const uint32_t n_base = blockIdx.x * MT, m_base = blockIdx.y * MT;
+  const uint32_t n_base = (blockIdx.x - (which == 0 ? 0u : tensors.tile_end[which - 1])) * MT, m_base = blockIdx.y * MT;
   const uint32_t nb1 = k / 128u, nb8 = k / 32u;
   if (tid < 16) {
-    uint32_t h[4];
+    uint32_t v = 0;
 #pragma unroll
-    for (int e = 0; e < 4; e++) h[e] = (tid >> e) & 1u ? 0x3C00u : 0xBC00u;  // bit set: +1, clear: -1
-    s_sign[tid] = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
+    for (int e = 0; e < 4; e++) v |= ((tid >> e) & 1u ? 0x01u : 0xFFu) << (8 * e);  // bit set: +1, clear: -1
+    s_sign[tid] = v;
   }
-  // staging: thread -> (row, half of the row's 128 inputs)
-  const uint32_t srow = tid >> 1, shalf = tid & 1;
+  // staging: thread -> (row, a segment of MMA_SEG of the row's 128 inputs)
+  constexpr uint32_t SEGS = 128 / MMA_SEG, A_LD = MMA_SEG / 16, B_BYTES = MMA_SEG / 8;
+  static_assert(B_BYTES == 4, "a thread stages one 32-bit word of sign bits");
+  const uint32_t srow = tid / SEGS, sseg = tid % SEGS;
   const bool a_ok = m_base + srow < m, b_ok = n_base + srow < n;
-  const int8_t* a_src = a_qs + static_cast<size_t>(m_base + srow) * k + 64u * shalf;
-  const uint8_t* b_src = w_qs + static_cast<size_t>(n_base + srow) * nb1 * 16u + 8u * shalf;
-  uint4 ra[4];
-  uint2 rb;
+  const int8_t* a_src = a_qs + static_cast<size_t>(m_base + srow) * k + MMA_SEG * sseg;
+  const uint8_t* b_src = w_qs + static_cast<size_t>(n_base + srow) * nb1 * 16u + B_BYTES * sseg;
+  uint4 ra[A_LD];
+  uint32_t rb;
   float4 rad;
   float rwd;
   auto fetch = [&](uint32_t b) {
 #pragma unroll
-    for (int c = 0; c < 4; c++) ra[c] = a_ok ? *reinterpret_cast<const uint4*>(a_src + 128u * b + 16u * c) : make_uint4(0, 0, 0, 0);
-    rb = b_ok ? *reinterpret_cast<const uint2*>(b_src + 16u * b) : make_uint2(0, 0);
+    for (uint32_t c = 0; c < A_LD; c++) ra[c] = a_ok ? *reinterpret_cast<const uint4*>(a_src + 128u * b + 16u * c) : make_uint4(0, 0, 0, 0);
+    rb = b_ok ? *reinterpret_cast<const uint32_t*>(b_src + 16u * b) : 0u;
     if (tid < MT) {
       rad = m_base + tid < m ? *reinterpret_cast<const float4*>(a_d + static_cast<size_t>(m_base + tid) * nb8 + 4u * b)
                              : make_float4(0.f, 0.f, 0.f, 0.f);
-    } else {
+    } else if (tid < 2 * MT) {
       const uint32_t ni = n_base + tid - MT;
       rwd = ni < n ? __half2float(w_d[static_cast<size_t>(ni) * nb1 + b]) : 0.0f;
     }
   };
   auto stage = [&](uint32_t buf) {
-    uint8_t* arow = sA + buf * MMA_TILE_B + srow * 256u;
-    uint8_t* brow = sB + buf * MMA_TILE_B + srow * 256u;
+    uint8_t* arow = sA + buf * MMA_TILE_B + srow * 128u;
+    uint8_t* brow = sB + buf * MMA_TILE_B + srow * 128u;
 #pragma unroll
-    for (int c = 0; c < 4; c++) {  // 16 int8 -> two chunks of 8 halves
-      const uint2 h0 = s8x4_to_f16x4(ra[c].x), h1 = s8x4_to_f16x4(ra[c].y), h2 = s8x4_to_f16x4(ra[c].z), h3 = s8x4_to_f16x4(ra[c].w);
-      const uint32_t ch = shalf * 8u + 2u * c;
-      *reinterpret_cast<uint4*>(arow + (((ch) ^ (srow & 7u)) << 4)) = make_uint4(h0.x, h0.y, h1.x, h1.y);
-      *reinterpret_cast<uint4*>(arow + (((ch + 1u) ^ (srow & 7u)) << 4)) = make_uint4(h2.x, h2.y, h3.x, h3.y);
-    }
-    const uint32_t wq[2] = {rb.x, rb.y};
+    for (uint32_t c = 0; c < A_LD; c++)  // a chunk of 16 int8 as it is
+      *reinterpret_cast<uint4*>(arow + (((sseg * A_LD + c) ^ (srow & 7u)) << 4)) = ra[c];
 #pragma unroll
-    for (int j = 0; j < 8; j++) {  // one byte of signs -> one chunk of 8 halves
-      const uint32_t byte = (wq[j >> 2] >> (8 * (j & 3))) & 0xFFu;
-      const uint2 lo = s_sign[byte & 15u], hi = s_sign[byte >> 4];
-      *reinterpret_cast<uint4*>(brow + (((shalf * 8u + j) ^ (srow & 7u)) << 4)) = make_uint4(lo.x, lo.y, hi.x, hi.y);
+    for (uint32_t j = 0; j < B_BYTES; j += 2) {  // two bytes of signs -> one chunk of 16 bytes
+      const uint32_t b0 = (rb >> (8 * j)) & 0xFFu, b1 = (rb >> (8 * j + 8)) & 0xFFu;
+      *reinterpret_cast<uint4*>(brow + (((sseg * (B_BYTES / 2) + (j >> 1)) ^ (srow & 7u)) << 4)) =
+          make_uint4(s_sign[b0 & 15u], s_sign[b0 >> 4], s_sign[b1 & 15u], s_sign[b1 >> 4]);
     }
     if (tid < MT) {
       *reinterpret_cast<float4*>(s_ad + buf * MT * 4 + tid * 4) = rad;
-    } else {
+    } else if (tid < 2 * MT) {
       s_wd[buf * MT + tid - MT] = rwd;
     }
   };
   const uint32_t wm = warp >> 2, wn = warp & 3, g = lane >> 2, t = lane & 3;
-  float acc[4][4][4];
+  float acc[MMA_MT_W][4][4];
 #pragma unroll
-  for (int i = 0; i < 4; i++)
+  for (uint32_t i = 0; i < MMA_MT_W; i++)
 #pragma unroll
     for (int j = 0; j < 4; j++)
 #pragma unroll
       for (int e = 0; e < 4; e++) acc[i][j][e] = 0.0f;
-  const float zero4[4] = {0.f, 0.f, 0.f, 0.f};
   // ldmatrix row addresses of this lane: matrix lane >> 3, row lane & 7
   const uint32_t lm = lane >> 3, lr = lane & 7;
-  const uint32_t a_row0 = wm * 64u + (lm & 1u) * 8u + lr, a_chunk0 = lm >> 1;        // + 16 per m tile; chunk + 2 per k16 step
+  const uint32_t a_row0 = wm * (16u * MMA_MT_W) + (lm & 1u) * 8u + lr, a_chunk0 = lm >> 1;  // + 16 per m tile; chunk + 2 per sub-block
   const uint32_t b_row0 = wn * 32u + (lm >> 1) * 8u + lr, b_chunk0 = lm & 1u;        // + 16 per pair of n tiles
   const uint32_t sA_u = static_cast<uint32_t>(__cvta_generic_to_shared(sA)), sB_u = static_cast<uint32_t>(__cvta_generic_to_shared(sB));
 
@@ -524,33 +540,29 @@ __global__ void __launch_bounds__(256, 1) matmul_q1_q8_mma_kernel(const __half* 
     }
 #pragma unroll 1
     for (uint32_t s = 0; s < 4; s++) {
-      uint32_t bf[2][4][2];  // [k16 step][n tile][register]
+      uint32_t bf[4][2];  // [n tile][register]
 #pragma unroll
-      for (uint32_t ks = 0; ks < 2; ks++)
+      for (uint32_t jp = 0; jp < 2; jp++) {
+        const uint32_t row = b_row0 + jp * 16u, chunk = s * 2u + b_chunk0;
+        ldmatrix_x4(sB_u + buf * MMA_TILE_B + row * 128u + ((chunk ^ (row & 7u)) << 4), bf[2 * jp][0], bf[2 * jp][1], bf[2 * jp + 1][0],
+                    bf[2 * jp + 1][1]);
+      }
 #pragma unroll
-        for (uint32_t jp = 0; jp < 2; jp++) {
-          const uint32_t row = b_row0 + jp * 16u, chunk = s * 4u + ks * 2u + b_chunk0;
-          ldmatrix_x4(sB_u + buf * MMA_TILE_B + row * 256u + ((chunk ^ (row & 7u)) << 4), bf[ks][2 * jp][0], bf[ks][2 * jp][1],
-                      bf[ks][2 * jp + 1][0], bf[ks][2 * jp + 1][1]);
+      for (uint32_t mt = 0; mt < MMA_MT_W; mt++) {
+        uint32_t af[4];
+        {
+          const uint32_t row = a_row0 + mt * 16u, chunk = s * 2u + a_chunk0;
+          ldmatrix_x4(sA_u + buf * MMA_TILE_B + row * 128u + ((chunk ^ (row & 7u)) << 4), af[0], af[1], af[2], af[3]);
         }
-#pragma unroll
-      for (uint32_t mt = 0; mt < 4; mt++) {
-        uint32_t af[2][4];
-#pragma unroll
-        for (uint32_t ks = 0; ks < 2; ks++) {
-          const uint32_t row = a_row0 + mt * 16u, chunk = s * 4u + ks * 2u + a_chunk0;
-          ldmatrix_x4(sA_u + buf * MMA_TILE_B + row * 256u + ((chunk ^ (row & 7u)) << 4), af[ks][0], af[ks][1], af[ks][2], af[ks][3]);
-        }
-        const float ad_lo = ad[(wm * 64u + mt * 16u + g) * 4u + s], ad_hi = ad[(wm * 64u + mt * 16u + g + 8u) * 4u + s];
+        const float ad_lo = ad[(wm * (16u * MMA_MT_W) + mt * 16u + g) * 4u + s], ad_hi = ad[(wm * (16u * MMA_MT_W) + mt * 16u + g + 8u) * 4u + s];
 #pragma unroll
         for (uint32_t nt = 0; nt < 4; nt++) {
-          float d[4];
-          mma_f16_f32(d, af[0], bf[0][nt][0], bf[0][nt][1], zero4);
-          mma_f16_f32(d, af[1], bf[1][nt][0], bf[1][nt][1], d);
-          acc[mt][nt][0] = __fadd_rn(acc[mt][nt][0], __fmul_rn(__fmul_rn(ad_lo, wdv[nt][0]), d[0]));
-          acc[mt][nt][1] = __fadd_rn(acc[mt][nt][1], __fmul_rn(__fmul_rn(ad_lo, wdv[nt][1]), d[1]));
-          acc[mt][nt][2] = __fadd_rn(acc[mt][nt][2], __fmul_rn(__fmul_rn(ad_hi, wdv[nt][0]), d[2]));
-          acc[mt][nt][3] = __fadd_rn(acc[mt][nt][3], __fmul_rn(__fmul_rn(ad_hi, wdv[nt][1]), d[3]));
+          int d[4];
+          mma_s8_s32(d, af, bf[nt][0], bf[nt][1]);
+          acc[mt][nt][0] = __fadd_rn(acc[mt][nt][0], __fmul_rn(__fmul_rn(ad_lo, wdv[nt][0]), q1_s32_to_f32(d[0])));
+          acc[mt][nt][1] = __fadd_rn(acc[mt][nt][1], __fmul_rn(__fmul_rn(ad_lo, wdv[nt][1]), q1_s32_to_f32(d[1])));
+          acc[mt][nt][2] = __fadd_rn(acc[mt][nt][2], __fmul_rn(__fmul_rn(ad_hi, wdv[nt][0]), q1_s32_to_f32(d[2])));
+          acc[mt][nt][3] = __fadd_rn(acc[mt][nt][3], __fmul_rn(__fmul_rn(ad_hi, wdv[nt][1]), q1_s32_to_f32(d[3])));
         }
       }
     }
@@ -558,17 +570,235 @@ __global__ void __launch_bounds__(256, 1) matmul_q1_q8_mma_kernel(const __half* 
     __syncthreads();
   }
 #pragma unroll
-  for (uint32_t mt = 0; mt < 4; mt++)
+  for (uint32_t mt = 0; mt < MMA_MT_W; mt++)
 #pragma unroll
     for (uint32_t nt = 0; nt < 4; nt++)
 #pragma unroll
       for (uint32_t e = 0; e < 4; e++) {
-        const uint32_t mi = m_base + wm * 64u + mt * 16u + g + (e >> 1) * 8u, ni = n_base + wn * 32u + nt * 8u + 2u * t + (e & 1u);
+        const uint32_t mi = m_base + wm * (16u * MMA_MT_W) + mt * 16u + g + (e >> 1) * 8u, ni = n_base + wn * 32u + nt * 8u + 2u * t + (e & 1u);
         if (mi >= m || ni >= n) continue;
         __half* dst = y + static_cast<size_t>(mi) * n + ni;
         const float v = accumulate ? __fadd_rn(__half2float(*dst), acc[mt][nt][e]) : acc[mt][nt][e];
         *dst = __float2half_rn(v);
       }
+}
+
+// The same product on the 5th-generation tensor cores (tcgen05); selectable (variant 3), not the default.
+// The arithmetic that has to stay on the CUDA cores, three roundings per output and sub-block, is what
+// bounds it; the integer dots cost nothing on the tensor pipe. They are computed as f16 MMAs with FP32
+// accumulation: every operand is an integer below 2^11 and every partial sum an integer below 2^13, so
+// the result is the exact integer whatever the order of the additions, already in FP32 (no conversion).
+// A CTA owns 128 tokens x 128 weight rows. Per half block (64 inputs = two sub-blocks):
+//   16 worker warps   stage the half block two steps ahead (thread = 16 inputs of a row: int8 -> f16 for
+//                     the activations, sign bits -> f16 +-1 for the weights) into a ring of K-major
+//                     128-byte-swizzled operand tiles, then take the finished half block out of TMEM:
+//                     thread = token = TMEM lane, 32 weight rows: y += (a_d * w_d) * sumi in the
+//                     reference's order, accumulated in registers over all blocks
+//   warp 0, lane 0    per sub-block two tcgen05.mma kind::f16 (M 128, N 128, K 16) into one of two TMEM
+//                     buffers of 2 x 128 columns, one step ahead of the workers
+// Every wait is bounded; a wait that gives up stores a code in the error word and the CTA winds down.
+constexpr uint32_t UM_STAGES = 4, UM_TILE_B = 16384, UM_STAGE_B = 2 * UM_TILE_B;
+constexpr uint32_t UM_EPI_WARPS = 16;
+constexpr uint32_t UM_THREADS = (1 + UM_EPI_WARPS) * 32;
+constexpr uint32_t UM_SMEM = UM_STAGES * UM_STAGE_B + 1024;
+static __device__ uint32_t g_q1_err;  // error word of launches that were given none
+
+__global__ void __launch_bounds__(UM_THREADS, 1) matmul_q1_q8_umma_kernel(const __half* __restrict__ w_d, const uint8_t* __restrict__ w_qs,
+                                                                          uint32_t k, uint32_t n, uint32_t m, const float* __restrict__ a_d,
+                                                                          const int8_t* __restrict__ a_qs, __half* y, uint32_t accumulate,
+                                                                          uint32_t* err, uint32_t wait_limit) {
+  extern __shared__ uint8_t um_raw[];
+  __shared__ __align__(8) uint64_t full[UM_STAGES], empty[UM_STAGES], d_full[2], d_empty[2];
+  __shared__ uint2 s_sign[16];
+  __shared__ __align__(16) float s_wd[UM_EPI_WARPS][32];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ volatile uint32_t abort_s;
+  const uint32_t smem_base = (smem_u32(um_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = um_raw + (smem_base - smem_u32(um_raw));
+  const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t n_base = blockIdx.x * MT, m_base = blockIdx.y * MT;
+  const uint32_t nb1 = k / 128u, nb8 = k / 32u, n_stages = 2u * nb1;
+  if (err == nullptr) err = &g_q1_err;
+  if (tid == 0) {
+    for (uint32_t i = 0; i < UM_STAGES; i++) {
+      mbar_init(smem_u32(&full[i]), UM_EPI_WARPS);
+      mbar_init(smem_u32(&empty[i]), 1);
+    }
+    for (uint32_t i = 0; i < 2; i++) {
+      mbar_init(smem_u32(&d_full[i]), 1);
+      mbar_init(smem_u32(&d_empty[i]), UM_EPI_WARPS);
+    }
+    abort_s = 0;
+    fence_barrier_init();
+  }
+  if (tid < 16) {
+    uint32_t h[4];
+#pragma unroll
+    for (int e = 0; e < 4; e++) h[e] = (tid >> e) & 1u ? 0x3C00u : 0xBC00u;  // bit set: +1, clear: -1
+    s_sign[tid] = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
+  }
+  if (warp == 0) tmem_alloc(smem_u32(&tmem_base_s), 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_s;
+  if (tid == 0) pdl_launch_dependents();
+  pdl_wait();
+  // try_wait with a suspend-time hint: sixteen warps polling at full rate would take issue slots from
+  // the warps that are computing
+  auto waitb = [&](uint64_t* bar, uint32_t parity) {
+    if (abort_s) return;
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t i = 0; i < wait_limit; i++) {
+      uint32_t ok;
+      asm volatile(
+          "{\n\t.reg .pred p;\n\t"
+          "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+          "selp.u32 %0, 1, 0, p;\n\t}"
+          : "=r"(ok)
+          : "r"(addr), "r"(parity), "r"(2000u)
+          : "memory");
+      if (ok) return;
+    }
+    abort_s = 1;
+    atomicExch(err, 6u);
+  };
+
+  if (warp == 0) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t IDESC = umma_idesc(1, 0, 0, 0, 0, 128, 128);  // f32 = f16 (K-major) x f16 (K-major)
+      const uint64_t dk = umma_desc_sw128(0, 16, 1024);
+      for (uint32_t j = 0; j < n_stages && !abort_s; j++) {
+        const uint32_t slot = j % UM_STAGES, pb = j & 1u;
+        waitb(&full[slot], (j / UM_STAGES) & 1u);
+        if (j >= 2) waitb(&d_empty[pb], ((j >> 1) - 1u) & 1u);
+        tc_fence_after();
+        const uint64_t ad = dk + ((smem_base + slot * UM_STAGE_B) >> 4), bd = ad + (UM_TILE_B >> 4);
+#pragma unroll
+        for (uint32_t sb = 0; sb < 2; sb++)      // sub-block: 32 inputs = 64 bytes along the row
+#pragma unroll
+          for (uint32_t ks = 0; ks < 2; ks++)    // 16 inputs per MMA
+            umma_f16(tmem + pb * 256u + sb * 128u, ad + sb * 4u + ks * 2u, bd + sb * 4u + ks * 2u, IDESC, ks);
+        umma_commit(smem_u32(&empty[slot]));
+        umma_commit(smem_u32(&d_full[pb]));
+      }
+    }
+  } else {
+    // ---------------- workers ----------------
+    // staging: thread = 16 inputs (quarter q of the half block) of row srow, of A and of B
+    const uint32_t wt = tid - 32u, srow = wt >> 2, sq = wt & 3u;
+    const bool a_ok = m_base + srow < m, b_ok = n_base + srow < n;
+    const int8_t* a_src = a_qs + static_cast<size_t>(m_base + srow) * k + 16u * sq;
+    const uint8_t* b_src = w_qs + static_cast<size_t>(n_base + srow) * nb1 * 16u + 2u * sq;
+    uint4 ra, ra2 = make_uint4(0, 0, 0, 0);   // the data of the step after next, and of the one after that
+    uint32_t rb, rb2 = 0;
+    auto fetch = [&](uint32_t h) {
+      ra = ra2;
+      rb = rb2;
+      ra2 = a_ok ? *reinterpret_cast<const uint4*>(a_src + 64u * h) : make_uint4(0, 0, 0, 0);
+      rb2 = b_ok ? *reinterpret_cast<const uint16_t*>(b_src + 8u * h) : 0u;
+    };
+    auto store = [&](uint32_t h) {
+      const uint32_t slot = h % UM_STAGES;
+      if (h >= UM_STAGES) waitb(&empty[slot], ((h / UM_STAGES) - 1u) & 1u);
+      uint8_t* arow = smem_gen + slot * UM_STAGE_B + srow * 128u;
+      uint8_t* brow = arow + UM_TILE_B;
+      const uint2 h0 = s8x4_to_f16x4(ra.x), h1 = s8x4_to_f16x4(ra.y), h2 = s8x4_to_f16x4(ra.z), h3 = s8x4_to_f16x4(ra.w);
+      *reinterpret_cast<uint4*>(arow + (((2u * sq) ^ (srow & 7u)) << 4)) = make_uint4(h0.x, h0.y, h1.x, h1.y);
+      *reinterpret_cast<uint4*>(arow + (((2u * sq + 1u) ^ (srow & 7u)) << 4)) = make_uint4(h2.x, h2.y, h3.x, h3.y);
+#pragma unroll
+      for (uint32_t jb = 0; jb < 2; jb++) {  // one byte of signs -> one chunk of 8 halves; zeros beyond the last weight row
+        const uint32_t byte = (rb >> (8u * jb)) & 0xFFu;
+        const uint2 lo = s_sign[byte & 15u], hi = s_sign[byte >> 4];
+        *reinterpret_cast<uint4*>(brow + (((2u * sq + jb) ^ (srow & 7u)) << 4)) = b_ok ? make_uint4(lo.x, lo.y, hi.x, hi.y) : make_uint4(0, 0, 0, 0);
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&full[slot]));
+    };
+    // epilogue: thread = token (TMEM lane), 32 weight rows
+    const uint32_t quad = warp & 3u, ew = warp - 1u, cg = ew >> 2;  // TMEM lane quarter; columns 32 cg ..
+    const uint32_t row = quad * 32u + lane, mi = m_base + row;
+    const uint32_t t_addr = tmem + ((quad * 32u) << 16) + cg * 32u;
+    const bool row_ok = mi < m;
+    const uint32_t my_col = n_base + cg * 32u + lane;  // the weight row whose scale this lane fetches for its warp
+    const float* ad_src = a_d + static_cast<size_t>(mi) * nb8;
+    const __half* wd_src = w_d + static_cast<size_t>(my_col) * nb1;
+    float acc[32];
+#pragma unroll
+    for (int c = 0; c < 32; c++) acc[c] = 0.0f;
+    float4 ad_next = row_ok ? *reinterpret_cast<const float4*>(ad_src) : make_float4(0.f, 0.f, 0.f, 0.f);
+    float wd_next = my_col < n ? __half2float(wd_src[0]) : 0.0f;
+    float adv[4] = {0.f, 0.f, 0.f, 0.f};
+    // the first two steps, and the third one's data on its way
+    // fetch(h) requests step h and makes step h - 1, requested one call earlier, the one that store() writes
+    fetch(0);
+    fetch(1);
+    store(0);
+    fetch(n_stages > 2 ? 2 : 1);
+    store(1);
+    fetch(n_stages > 3 ? 3 : 1);  // now: step 2 ready to be stored, step 3 on its way
+    for (uint32_t j = 0; j < n_stages && !abort_s; j++) {
+      const uint32_t pb = j & 1u, b = j >> 1;
+      if (j + 2 < n_stages) {
+        store(j + 2);
+        fetch(j + 4 < n_stages ? j + 4 : j + 2);  // (past the end: any valid step, never stored)
+      }
+      if (pb == 0) {  // a new block: its scales, and the next block's on their way
+        adv[0] = ad_next.x; adv[1] = ad_next.y; adv[2] = ad_next.z; adv[3] = ad_next.w;
+        __syncwarp();
+        s_wd[ew][lane] = wd_next;
+        __syncwarp();
+        if (b + 1 < nb1) {
+          if (row_ok) ad_next = *reinterpret_cast<const float4*>(ad_src + 4u * (b + 1u));
+          if (my_col < n) wd_next = __half2float(wd_src[b + 1u]);
+        }
+      }
+      waitb(&d_full[pb], (j >> 1) & 1u);
+      tc_fence_after();
+      // The half block's 2 x 32 columns in four loads of 16, each in flight while the previous one's
+      // sixteen outputs are scaled and added (all workers reach this point together: without the overlap
+      // every load's latency would be exposed on all of them at once).
+      uint32_t d[2][16];
+      tmem_ld16(t_addr + pb * 256u, d[0]);
+#pragma unroll
+      for (uint32_t q = 0; q < 4; q++) {  // quarter q: sub-block q / 2, columns 16 (q % 2) ..
+        tmem_ld_wait();
+        if (q < 3) {
+          tmem_ld16(t_addr + pb * 256u + ((q + 1u) >> 1) * 128u + ((q + 1u) & 1u) * 16u, d[(q + 1u) & 1u]);
+        } else {  // the whole half block is in registers: the buffer may take the MMAs of the step after next
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&d_empty[pb]));
+        }
+        const float ad_s = adv[2u * pb + (q >> 1)];
+        const uint32_t c0 = (q & 1u) * 16u;
+#pragma unroll
+        for (int c4 = 0; c4 < 4; c4++) {
+          const float4 w4 = *reinterpret_cast<const float4*>(&s_wd[ew][c0 + 4 * c4]);
+          const uint32_t* dq = d[q & 1u] + 4 * c4;
+          float* a4 = acc + c0 + 4 * c4;
+          a4[0] = __fadd_rn(a4[0], __fmul_rn(__fmul_rn(ad_s, w4.x), __uint_as_float(dq[0])));
+          a4[1] = __fadd_rn(a4[1], __fmul_rn(__fmul_rn(ad_s, w4.y), __uint_as_float(dq[1])));
+          a4[2] = __fadd_rn(a4[2], __fmul_rn(__fmul_rn(ad_s, w4.z), __uint_as_float(dq[2])));
+          a4[3] = __fadd_rn(a4[3], __fmul_rn(__fmul_rn(ad_s, w4.w), __uint_as_float(dq[3])));
+        }
+      }
+    }
+    if (row_ok && !abort_s) {
+      __half* dst = y + static_cast<size_t>(mi) * n + n_base + cg * 32u;
+#pragma unroll
+      for (int c = 0; c < 32; c++) {
+        if (n_base + cg * 32u + c >= n) break;
+        const float v = accumulate ? __fadd_rn(__half2float(dst[c]), acc[c]) : acc[c];
+        dst[c] = __float2half_rn(v);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 512);
 }
 
 // topk_reduce.wgsl:59-196, the same steps on the same lists (256 per-thread min-heaps of 32, heapsort, then
@@ -822,20 +1052,82 @@ cudaError_t bp_q1_quantize_q8(bool pdl, cudaStream_t s, const __half* x, uint32_
   return bp_launch(pdl, quantize_q8_kernel, dim3(static_cast<unsigned>((n_blocks + 7) / 8)), dim3(256), 0, s, x, n_blocks, d_out, qs_out);
 }
 
+static cudaError_t launch_mma(bool pdl, cudaStream_t s, const bp_q1_tensor* w, __half* const* y, uint32_t n_w, uint32_t m, const float* a_d,
+                              const int8_t* a_qs, uint32_t acc) {
+  MmaTensors t;
+  uint32_t tiles = 0;
+  for (uint32_t i = 0; i < 3; i++) {
+    const uint32_t j = i < n_w ? i : n_w - 1;  // unused entries repeat the last tensor; their tile range is empty
+    t.w_d[i] = w[j].d;
+    t.w_qs[i] = w[j].qs;
+    t.y[i] = y[j];
+    t.n[i] = w[j].n;
+    if (i < n_w) tiles += (w[i].n + MT - 1) / MT;
+    t.tile_end[i] = tiles;
+  }
+  dim3 grid(tiles, (m + MT - 1) / MT);
+  return bp_launch(pdl, matmul_q1_q8_mma_kernel, grid, dim3(MMA_THREADS), MMA_SMEM, s, t, w[0].k, m, a_d, a_qs, acc);
+}
+
+static uint32_t g_matmul_variant = 0;
+void bp_q1_set_matmul_variant(uint32_t v) { g_matmul_variant = v <= 3 ? v : 0; }
+
+cudaError_t bp_q1_take_error(uint32_t* code) {
+  cudaError_t e = cudaMemcpyFromSymbol(code, g_q1_err, sizeof(uint32_t));
+  if (e != cudaSuccess || *code == 0) return e;
+  const uint32_t zero = 0;
+  return cudaMemcpyToSymbol(g_q1_err, &zero, sizeof zero);
+}
+
+// Batches of up to MMA_MIN_M tokens: CUDA cores (64 x 64 tiles fit them better than a 128-row MMA tile);
+// larger ones: the mma.sync kernel, which measured faster than the tcgen05 one (254 against 323 us for
+// 512 tokens x 4096 rows x 12288 inputs: both are bound by instruction issue, and what the tcgen05 kernel
+// saves on the arithmetic, 3 instead of 5 instructions per output and sub-block, it spends on staging f16
+// operands and on its barriers). Variant 1, 2, 3 forces dp4a, mma.sync, tcgen05 (tuning and tests: all
+// three give the same bits).
 cudaError_t bp_q1_matmul(bool pdl, cudaStream_t s, const bp_q1_tensor& w, uint32_t m, const float* a_d, const int8_t* a_qs, __half* y,
-                         bool accumulate) {
-  if (m > MMA_MIN_M) {
-    static bool configured = false;
-    if (!configured) {
-      cudaError_t e = cudaFuncSetAttribute(matmul_q1_q8_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(MMA_SMEM));
-      if (e != cudaSuccess) return e;
-      configured = true;
-    }
+                         bool accumulate, uint32_t* err, uint32_t wait_limit) {
+  const uint32_t variant = g_matmul_variant != 0 ? g_matmul_variant : (m > MMA_MIN_M ? 2u : 1u);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(matmul_q1_q8_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(MMA_SMEM));
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(matmul_q1_q8_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(UM_SMEM));
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  if (m == 0) return cudaSuccess;
+  const uint32_t acc = accumulate ? 1u : 0u;
+  if (variant == 3) {
     dim3 grid((w.n + MT - 1) / MT, (m + MT - 1) / MT);
-    return bp_launch(pdl, matmul_q1_q8_mma_kernel, grid, dim3(256), MMA_SMEM, s, w.d, w.qs, w.k, w.n, m, a_d, a_qs, y, accumulate ? 1u : 0u);
+    return bp_launch(pdl, matmul_q1_q8_umma_kernel, grid, dim3(UM_THREADS), UM_SMEM, s, w.d, w.qs, w.k, w.n, m, a_d, a_qs, y, acc, err,
+                     wait_limit != 0 ? wait_limit : (1u << 22));
+  }
+  if (variant == 2) {
+    const bp_q1_tensor* one = &w;
+    __half* out = y;
+    return launch_mma(pdl, s, one, &out, 1, m, a_d, a_qs, acc);
   }
   dim3 grid((w.n + MM_T - 1) / MM_T, (m + MM_T - 1) / MM_T);
-  return bp_launch(pdl, matmul_q1_q8_kernel, grid, dim3(256), 0, s, w.d, w.qs, w.k, w.n, m, a_d, a_qs, y, accumulate ? 1u : 0u);
+  return bp_launch(pdl, matmul_q1_q8_kernel, grid, dim3(256), 0, s, w.d, w.qs, w.k, w.n, m, a_d, a_qs, y, acc);
+}
+
+// The same activations through up to three weight tensors of equal k: one launch where the kernel allows.
+cudaError_t bp_q1_matmul_multi(bool pdl, cudaStream_t s, const bp_q1_tensor* w, __half* const* y, uint32_t n_w, uint32_t m, const float* a_d,
+                               const int8_t* a_qs, bool accumulate, uint32_t* err, uint32_t wait_limit) {
+  const uint32_t variant = g_matmul_variant != 0 ? g_matmul_variant : (m > MMA_MIN_M ? 2u : 1u);
+  bool same_k = n_w >= 1 && n_w <= 3;
+  for (uint32_t i = 1; i < n_w && same_k; i++) same_k = w[i].k == w[0].k;
+  if (variant == 2 && same_k && n_w > 1) {
+    cudaError_t e = bp_q1_matmul(pdl, s, w[0], 0, a_d, a_qs, y[0], accumulate, err, wait_limit);  // (m = 0: configures the kernels only)
+    if (e != cudaSuccess) return e;
+    return launch_mma(pdl, s, w, y, n_w, m, a_d, a_qs, accumulate ? 1u : 0u);
+  }
+  for (uint32_t i = 0; i < n_w; i++) {
+    cudaError_t e = bp_q1_matmul(pdl, s, w[i], m, a_d, a_qs, y[i], accumulate, err, wait_limit);
+    if (e != cudaSuccess) return e;
+  }
+  return cudaSuccess;
 }
 
 cudaError_t bp_q1_topk(bool pdl, cudaStream_t s, const __half* logits, uint32_t n, uint32_t k, float* out_val, uint32_t* out_idx) {

@@ -26,6 +26,12 @@ cudaError_t bp_q1_rms_norm(bool pdl, cudaStream_t s, const __half* in, __half* o
 cudaError_t bp_q1_silu_mul(bool pdl, cudaStream_t s, const __half* gate, const __half* up, __half* out, uint64_t n);
 cudaError_t bp_q1_embed(bool pdl, cudaStream_t s, const bp_q1_tensor& w, const uint32_t* tokens, uint32_t m, __half* x);
 cudaError_t bp_q1_quantize_q8(bool pdl, cudaStream_t s, const __half* x, uint32_t k, uint32_t m, float* d_out, int8_t* qs_out);
+// err: device-visible error word that a bounded wait of the tensor-core kernel stores a code in when it gives
+// up (null: a word of the library's own, read and cleared by bp_q1_take_error); wait_limit 0 = default.
 cudaError_t bp_q1_matmul(bool pdl, cudaStream_t s, const bp_q1_tensor& w, uint32_t m, const float* a_d, const int8_t* a_qs, __half* y,
-                         bool accumulate);
+                         bool accumulate, uint32_t* err = nullptr, uint32_t wait_limit = 0);
+cudaError_t bp_q1_matmul_multi(bool pdl, cudaStream_t s, const bp_q1_tensor* w, __half* const* y, uint32_t n_w, uint32_t m, const float* a_d,
+                               const int8_t* a_qs, bool accumulate, uint32_t* err = nullptr, uint32_t wait_limit = 0);
+void bp_q1_set_matmul_variant(uint32_t variant);  // tuning aid: 0 = by batch size (1 or 2), 1 = dp4a, 2 = mma.sync, 3 = tcgen05
+cudaError_t bp_q1_take_error(uint32_t* code);     // synchronous; 0 = no wait gave up since the last call
 cudaError_t bp_q1_topk(bool pdl, cudaStream_t s, const __half* logits, uint32_t n, uint32_t k, float* out_val, uint32_t* out_idx);

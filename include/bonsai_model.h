@@ -53,6 +53,15 @@ int bp_op_quantize_q8_0(void* stream, const void* x, uint32_t k, uint32_t m, voi
 /* dispatch_matmul_q1_0 (src/forward.rs:443-472, matmul_q1_0_q8_0.wgsl): y[m][n] (+)= A W^T */
 int bp_op_matmul_q1_0_q8_0(void* stream, const void* d, const void* qs, uint32_t k, uint32_t n, uint32_t m, const void* a_d,
                            const void* a_qs, void* y, uint32_t accumulate);
+/* Tuning aid of the matmul: 0 = chosen by the batch (CUDA cores up to 32 tokens, mma.sync above, the
+ * default), 1 = CUDA cores (dp4a), 2 = mma.sync (int8), 3 = tcgen05 (f16 operands). Results do not depend
+ * on it. Process-wide. */
+void bp_op_set_matmul_variant(uint32_t variant);
+/* The tcgen05 matmul waits on barriers, with a bound. Synchronizes the device and returns BP_ERR_TIMEOUT
+ * if such a wait of a bp_op_matmul_q1_0_q8_0 launch gave up since the last call (its output is then
+ * unspecified), BP_ERR_CUDA if the device reports an error, else BP_OK. A model reports the same through
+ * its own status. */
+int bp_op_device_status(void);
 /* dispatch_topk_reduce (src/forward.rs:336-357, topk_reduce.wgsl): the min(k, 32) largest logits, descending,
  * with their indices; out_val f32, out_idx uint32 (device) */
 int bp_op_topk_reduce(void* stream, const void* logits, uint32_t n, uint32_t k, void* out_val, void* out_idx);

@@ -145,11 +145,17 @@ def test_matmul_q1_0_q8_0_bit_exact(k, n, m, accumulate):
     a_d, a_qs = E.quantize_q8_0(act, k, m)
     y0 = rng.standard_normal((m, n)).astype(np.float16)
     want = E.matmul(blob, d_off, qs_off, k, n, m, a_d, a_qs, y=y0 if accumulate else None)
-    y, add, aqd = dev(y0.copy()), dev(a_d), dev(a_qs)
-    assert lib.bp_op_matmul_q1_0_q8_0(None, d_dev.data_ptr(), qs_dev.data_ptr(), k, n, m, add.data_ptr(), aqd.data_ptr(),
-                                      y.data_ptr(), int(accumulate)) == 0
-    torch.cuda.synchronize()
-    assert bits_equal(y, want)
+    add, aqd = dev(a_d), dev(a_qs)
+    try:
+        for variant in (0, 1, 2, 3):  # by batch size, CUDA cores, mma.sync, tcgen05: the same bits
+            lib.bp_op_set_matmul_variant(variant)
+            y = dev(y0.copy())
+            assert lib.bp_op_matmul_q1_0_q8_0(None, d_dev.data_ptr(), qs_dev.data_ptr(), k, n, m, add.data_ptr(), aqd.data_ptr(),
+                                              y.data_ptr(), int(accumulate)) == 0
+            assert lib.bp_op_device_status() == 0
+            assert bits_equal(y, want), variant
+    finally:
+        lib.bp_op_set_matmul_variant(0)
 
 
 @pytest.mark.parametrize("n,k,ties", [(151936, 32, False), (5001, 32, True), (2048, 5, True), (7, 32, False)])
@@ -230,6 +236,27 @@ def test_free_running_passes_agree_on_the_top_candidates(tmp_path):
         for i, t in enumerate(prompt):
             out = cpu2.step(t, i, suffix=i == len(prompt) - 1)
         assert out[1][0] == ix_mv[0] and np.max(np.abs(out[0] - lg_mv)) < 0.05
+
+
+def test_batched_prefill_is_identical_across_matmul_kernels(tmp_path):
+    """A 40-token prefill takes the tensor-core matmul (one launch for Q, K and V, one for gate and up); the
+    CUDA-core kernel and the tcgen05 kernel must give the same bits all the way to the logits."""
+    d = str(tmp_path / "m")
+    model_dir.write_synthetic_model(d, seed=5)
+    prompt = [(7 * i + 3) % 200 for i in range(40)]
+    lib = _lib.load()
+    got = {}
+    try:
+        for variant in (1, 0, 3):
+            lib.bp_op_set_matmul_variant(variant)
+            with bp.Model(d, max_seq=64) as gm:
+                lg, ix = gm.prefill_topk(prompt)
+                got[variant] = (lg.copy(), ix.copy(), gm.hidden(len(prompt) - 1).copy(), gm.logits().copy())
+    finally:
+        lib.bp_op_set_matmul_variant(0)
+    for variant in (0, 3):
+        for a, b in zip(got[1], got[variant]):
+            assert np.array_equal(a.view(np.uint8), b.view(np.uint8)), variant
 
 
 # ---------------------------------------------------------------------- session ----
