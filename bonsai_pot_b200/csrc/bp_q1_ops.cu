@@ -93,6 +93,7 @@ struct MvParams {
 
 // MODE 0: y (+)= W x (matvec_q1_0.wgsl); 1: W (rms_norm(x) * w), scales times inv_rms
 // (matvec_q1_0_fused_normed.wgsl); 2: y (+)= W (silu(gate) * up) (matvec_q1_0_silu.wgsl).
+constexpr uint32_t MV_PF = 4;  // blocks of a lane in flight
 template <int MODE, uint32_t MV_ROWS_PER_LANE>
 __global__ void __launch_bounds__(MV_THREADS) matvec_q1_kernel(const MvParams p) {
   constexpr uint32_t MV_ROWS_PER_CTA = (MV_THREADS / 8) * MV_ROWS_PER_LANE;
@@ -100,8 +101,63 @@ __global__ void __launch_bounds__(MV_THREADS) matvec_q1_kernel(const MvParams p)
   __shared__ float part[32];
   __half* xs = reinterpret_cast<__half*>(mv_smem);
   pdl_launch_dependents();
-  pdl_wait();  // the activations come from the kernel before this one
   const uint32_t tid = threadIdx.x, nb = p.k / 128u;
+  // ---- rows: lane = (row slot rs = lane / 8, tx = lane % 8); a lane owns rows base + rs + 4 j ----
+  const uint32_t warp = tid >> 5, lane = tid & 31, tx = lane & 7, rs = lane >> 3;
+  const uint32_t row0 = blockIdx.x * MV_ROWS_PER_CTA + warp * (4 * MV_ROWS_PER_LANE) + rs;
+  const __half* d_row[MV_ROWS_PER_LANE];
+  const uint4* b_row[MV_ROWS_PER_LANE];
+  __half* out_ptr[MV_ROWS_PER_LANE];
+  bool valid[MV_ROWS_PER_LANE];
+#pragma unroll
+  for (uint32_t j = 0; j < MV_ROWS_PER_LANE; j++) {
+    uint32_t row = row0 + 4u * j;
+    valid[j] = row < p.n_total;
+    if (!valid[j]) row = 0;
+    uint32_t ri = 0;
+    if (p.n_ranges > 1 && row >= p.r[0].n) {
+      row -= p.r[0].n;
+      ri = 1;
+      if (p.n_ranges > 2 && row >= p.r[1].n) {
+        row -= p.r[1].n;
+        ri = 2;
+      }
+    }
+    d_row[j] = p.r[ri].d + static_cast<size_t>(row) * nb;
+    b_row[j] = p.r[ri].bits + static_cast<size_t>(row) * nb;
+    out_ptr[j] = p.r[ri].out + row;
+  }
+  float acc[MV_ROWS_PER_LANE];
+#pragma unroll
+  for (uint32_t j = 0; j < MV_ROWS_PER_LANE; j++) acc[j] = 0.0f;
+  const __half2 zero2 = __float2half2_rn(0.0f);
+  // A lane works through its blocks tx, tx + 8, ... in order, and a block's sign words and scale are
+  // requested MV_PF blocks ahead: with one block ahead a call was a chain of k / 1024 memory latencies
+  // (8.9 us for 4096 x 12288 weights). The weights are constants: the first MV_PF blocks are on their way to
+  // registers, and the others to L2, while the kernel before this one, which produces the activations, is
+  // still running.
+  uint4 w_q[MV_PF][MV_ROWS_PER_LANE];
+  __half d_q[MV_PF][MV_ROWS_PER_LANE];
+#pragma unroll
+  for (uint32_t u = 0; u < MV_PF; u++) {
+    if (tx + 8 * u < nb) {
+#pragma unroll
+      for (uint32_t j = 0; j < MV_ROWS_PER_LANE; j++) {
+        w_q[u][j] = __ldg(b_row[j] + tx + 8 * u);
+        d_q[u][j] = __ldg(d_row[j] + tx + 8 * u);
+      }
+    }
+  }
+  for (uint32_t b = tx + 8 * MV_PF; b < nb; b += 8) {
+#pragma unroll
+    for (uint32_t j = 0; j < MV_ROWS_PER_LANE; j++) prefetch_l2(b_row[j] + b);
+  }
+  if (tx == 0) {
+#pragma unroll
+    for (uint32_t j = 0; j < MV_ROWS_PER_LANE; j++)
+      for (uint32_t b = 64; b < nb; b += 64) prefetch_l2(d_row[j] + b);  // scales: 64 per 128-byte line
+  }
+  pdl_wait();  // the activations come from the kernel before this one
   float inv_rms = 1.0f;
   // ---- stage the activations: block b at xs + b * XB_STRIDE ----
   if (MODE == 1) {
@@ -141,58 +197,23 @@ __global__ void __launch_bounds__(MV_THREADS) matvec_q1_kernel(const MvParams p)
     __syncthreads();
   }
 
-  // ---- rows: lane = (row slot rs = lane / 8, tx = lane % 8); a lane owns rows base + rs + 4 j ----
-  const uint32_t warp = tid >> 5, lane = tid & 31, tx = lane & 7, rs = lane >> 3;
-  const uint32_t row0 = blockIdx.x * MV_ROWS_PER_CTA + warp * (4 * MV_ROWS_PER_LANE) + rs;
-  const __half* d_row[MV_ROWS_PER_LANE];
-  const uint4* b_row[MV_ROWS_PER_LANE];
-  __half* out_ptr[MV_ROWS_PER_LANE];
-  bool valid[MV_ROWS_PER_LANE];
+  for (uint32_t b0 = tx; b0 < nb; b0 += 8 * MV_PF) {
 #pragma unroll
-  for (uint32_t j = 0; j < MV_ROWS_PER_LANE; j++) {
-    uint32_t row = row0 + 4u * j;
-    valid[j] = row < p.n_total;
-    if (!valid[j]) row = 0;
-    uint32_t ri = 0;
-    if (p.n_ranges > 1 && row >= p.r[0].n) {
-      row -= p.r[0].n;
-      ri = 1;
-      if (p.n_ranges > 2 && row >= p.r[1].n) {
-        row -= p.r[1].n;
-        ri = 2;
-      }
-    }
-    d_row[j] = p.r[ri].d + static_cast<size_t>(row) * nb;
-    b_row[j] = p.r[ri].bits + static_cast<size_t>(row) * nb;
-    out_ptr[j] = p.r[ri].out + row;
-  }
-  float acc[MV_ROWS_PER_LANE];
-#pragma unroll
-  for (uint32_t j = 0; j < MV_ROWS_PER_LANE; j++) acc[j] = 0.0f;
-  const __half2 zero2 = __float2half2_rn(0.0f);
-  // the next block's sign words and scales are requested before the current block is worked on
-  uint4 w_nxt[MV_ROWS_PER_LANE];
-  __half d_nxt[MV_ROWS_PER_LANE];
-  if (tx < nb) {
-#pragma unroll
-    for (uint32_t j = 0; j < MV_ROWS_PER_LANE; j++) {
-      w_nxt[j] = __ldg(b_row[j] + tx);
-      d_nxt[j] = __ldg(d_row[j] + tx);
-    }
-  }
-  for (uint32_t b = tx; b < nb; b += 8) {
+  for (uint32_t u = 0; u < MV_PF; u++) {
+    const uint32_t b = b0 + 8 * u;
+    if (b >= nb) break;
     uint4 w[MV_ROWS_PER_LANE];
     __half dh[MV_ROWS_PER_LANE];
 #pragma unroll
     for (uint32_t j = 0; j < MV_ROWS_PER_LANE; j++) {
-      w[j] = w_nxt[j];
-      dh[j] = d_nxt[j];
+      w[j] = w_q[u][j];
+      dh[j] = d_q[u][j];
     }
-    if (b + 8 < nb) {
+    if (b + 8 * MV_PF < nb) {
 #pragma unroll
       for (uint32_t j = 0; j < MV_ROWS_PER_LANE; j++) {
-        w_nxt[j] = __ldg(b_row[j] + b + 8);
-        d_nxt[j] = __ldg(d_row[j] + b + 8);
+        w_q[u][j] = __ldg(b_row[j] + b + 8 * MV_PF);
+        d_q[u][j] = __ldg(d_row[j] + b + 8 * MV_PF);
       }
     }
     __half2 a01[MV_ROWS_PER_LANE], a23[MV_ROWS_PER_LANE];
@@ -226,6 +247,7 @@ __global__ void __launch_bounds__(MV_THREADS) matvec_q1_kernel(const MvParams p)
       if (MODE == 1) d = __fmul_rn(d, inv_rms);
       acc[j] = __fadd_rn(acc[j], __fmul_rn(d, __half2float(ls)));
     }
+  }
   }
 #pragma unroll
   for (uint32_t j = 0; j < MV_ROWS_PER_LANE; j++) {
