@@ -57,7 +57,7 @@ constexpr uint32_t SW = 128;                      // TMEM columns of one query t
 
 template <uint32_t NQ, uint32_t CPS>  // query tiles per CTA (work item), CTAs per SM
 struct PLayout {
-  // producer, NQ Q K^T issuers, one P V issuer, NQ softmax groups of 4 warps
+  // NQ loader / P V issuer warps, NQ Q K^T issuer warps, NQ softmax groups of 4 warps.
   // One CTA per SM: four K and four V slots. Two CTAs per SM (one query tile and 256 TMEM columns each):
   // two slots each; while one CTA is between two work items (7 us of item fetch, Q load, pipeline fill
   // and epilogue per item) the other one computes.
@@ -253,8 +253,8 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   };
 
   // Barrier phases keep counting across work items: gkv = key tiles loaded so far by this CTA,
-  // gx[X] = key tiles query tile X has gone through, items_done for the once-per-item o_done;
-  // nothing is re-initialised between items. The producer keeps, per (query tile, slot), whether
+  // gx[X] = key tiles query tile X has gone through, od[X] for the once-per-item o_done;
+  // nothing is re-initialised between items. A loader keeps, per (query tile, slot), whether
   // a release is outstanding and the phase it will complete (bit x * L::KV_SLOTS + slot).
   uint32_t gkv = 0, gx[NQ], od[NQ];
 #pragma unroll
@@ -262,11 +262,16 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   uint32_t pend_k = 0, pend_v = 0, phase_k = 0, phase_v = 0;
   uint32_t vph = 0;  // softmax threads: next phase of "P V complete" per K/V slot, for their own query tile
 
-  for (;;) {
-    // An item is fetched only when the CTA is free (fetching ahead would defeat longest-first balancing).
-    if (threadIdx.x == 0) item_s = atomicAdd(p.counter, 1u);
-    __syncthreads();
-    const uint32_t item = item_s;
+  for (uint32_t round = 0;; round++) {
+    // The first item of a CTA is its own index (the grid never has more CTAs than there are items); further
+    // items come from the counter, fetched only when the CTA is free (fetching ahead would defeat
+    // longest-first balancing).
+    uint32_t item = blockIdx.x;
+    if (round != 0) {
+      if (threadIdx.x == 0) item_s = gridDim.x + atomicAdd(p.counter, 1u);
+      __syncthreads();
+      item = item_s;
+    }
     if (item >= n_items) break;
     const uint32_t g = item % p.n_kv_head;
     const uint32_t group = p.n_groups - 1 - item / p.n_kv_head;  // long (late) groups first
