@@ -374,14 +374,11 @@ int decode_layer(bp_model* m, uint32_t il, uint32_t pos) {
     }
   }
   M_CUDA(m, bp_q1_matvec(pdl, s, lt.wo, m->attn_out, m->x, true));
-  {
-    const bp_q1_tensor w[2] = {lt.wg, lt.wu};
-    __half* const out[2] = {m->gate, m->up};
-    M_CUDA(m, bp_q1_matvec_normed(pdl, s, w, out, 2, m->x, lt.ffn_norm, c.rms_eps));
-  }
-  // dispatch_matvec_q1_0_silu as two launches: silu(gate) * up once (the same f16 values the fused kernel stages;
-  // fused, each of the 256 CTAs of this 4096-row tensor recomputed all 12288 of them: 27.6 us against 3 + 8), then the matvec
-  M_CUDA(m, bp_q1_silu_mul(pdl, s, m->gate, m->up, m->ffn_in, c.n_ff));
+  // matvec_q1_0_fused_normed over (gate, up) and silu(gate) * up in one launch: a lane computes row i of both
+  // tensors and writes the f16 value that feeds the down projection (the same values dispatch_matvec_q1_0_silu
+  // stages; that shader as one kernel had each of the 256 CTAs of the 4096-row down tensor recompute all 12288
+  // of them: 27.6 us against 8 for the plain matvec).
+  M_CUDA(m, bp_q1_matvec_normed_silu(pdl, s, lt.wg, lt.wu, m->ffn_in, m->x, lt.ffn_norm, c.rms_eps));
   M_CUDA(m, bp_q1_matvec(pdl, s, lt.wd, m->ffn_in, m->x, true));
   return BP_OK;
 }

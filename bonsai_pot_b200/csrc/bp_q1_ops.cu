@@ -92,11 +92,16 @@ struct MvParams {
 };
 
 // MODE 0: y (+)= W x (matvec_q1_0.wgsl); 1: W (rms_norm(x) * w), scales times inv_rms
-// (matvec_q1_0_fused_normed.wgsl); 2: y (+)= W (silu(gate) * up) (matvec_q1_0_silu.wgsl).
+// (matvec_q1_0_fused_normed.wgsl); 2: y (+)= W (silu(gate) * up) (matvec_q1_0_silu.wgsl);
+// 3: MODE 1 over two tensors of equal height (gate, up) with silu_mul.wgsl applied to the pair of results:
+// a lane computes row i of both (MV_ROWS_PER_LANE = 2 is the tensor index) and writes
+// silu(f16(gate_i)) * f16(up_i), what the two dispatches of the reference leave in the buffer that feeds
+// the down projection.
 constexpr uint32_t MV_PF = 4;  // blocks of a lane in flight
 template <int MODE, uint32_t MV_ROWS_PER_LANE>
 __global__ void __launch_bounds__(MV_THREADS) matvec_q1_kernel(const MvParams p) {
-  constexpr uint32_t MV_ROWS_PER_CTA = (MV_THREADS / 8) * MV_ROWS_PER_LANE;
+  static_assert(MODE != 3 || MV_ROWS_PER_LANE == 2, "the paired mode computes one row of each of two tensors per lane");
+  constexpr uint32_t MV_ROWS_PER_CTA = (MV_THREADS / 8) * (MODE == 3 ? 1 : MV_ROWS_PER_LANE);
   extern __shared__ __align__(16) uint8_t mv_smem[];
   __shared__ float part[32];
   __half* xs = reinterpret_cast<__half*>(mv_smem);
@@ -104,18 +109,18 @@ __global__ void __launch_bounds__(MV_THREADS) matvec_q1_kernel(const MvParams p)
   const uint32_t tid = threadIdx.x, nb = p.k / 128u;
   // ---- rows: lane = (row slot rs = lane / 8, tx = lane % 8); a lane owns rows base + rs + 4 j ----
   const uint32_t warp = tid >> 5, lane = tid & 31, tx = lane & 7, rs = lane >> 3;
-  const uint32_t row0 = blockIdx.x * MV_ROWS_PER_CTA + warp * (4 * MV_ROWS_PER_LANE) + rs;
+  const uint32_t row0 = blockIdx.x * MV_ROWS_PER_CTA + warp * (4 * (MODE == 3 ? 1 : MV_ROWS_PER_LANE)) + rs;
   const __half* d_row[MV_ROWS_PER_LANE];
   const uint4* b_row[MV_ROWS_PER_LANE];
   __half* out_ptr[MV_ROWS_PER_LANE];
   bool valid[MV_ROWS_PER_LANE];
 #pragma unroll
   for (uint32_t j = 0; j < MV_ROWS_PER_LANE; j++) {
-    uint32_t row = row0 + 4u * j;
-    valid[j] = row < p.n_total;
+    uint32_t row = MODE == 3 ? row0 : row0 + 4u * j;
+    valid[j] = row < (MODE == 3 ? p.r[0].n : p.n_total);
     if (!valid[j]) row = 0;
-    uint32_t ri = 0;
-    if (p.n_ranges > 1 && row >= p.r[0].n) {
+    uint32_t ri = MODE == 3 ? j : 0;
+    if (MODE != 3 && p.n_ranges > 1 && row >= p.r[0].n) {
       row -= p.r[0].n;
       ri = 1;
       if (p.n_ranges > 2 && row >= p.r[1].n) {
@@ -160,7 +165,7 @@ __global__ void __launch_bounds__(MV_THREADS) matvec_q1_kernel(const MvParams p)
   pdl_wait();  // the activations come from the kernel before this one
   float inv_rms = 1.0f;
   // ---- stage the activations: block b at xs + b * XB_STRIDE ----
-  if (MODE == 1) {
+  if (MODE == 1 || MODE == 3) {
     float ssq = 0.0f;
     for (uint32_t v = tid; v < p.k / 4u; v += MV_THREADS) {
       const uint2 raw = *reinterpret_cast<const uint2*>(p.x + 4u * v);
@@ -244,22 +249,26 @@ __global__ void __launch_bounds__(MV_THREADS) matvec_q1_kernel(const MvParams p)
     for (uint32_t j = 0; j < MV_ROWS_PER_LANE; j++) {
       const __half ls = __hadd(__hadd(__hadd(__low2half(a01[j]), __high2half(a01[j])), __low2half(a23[j])), __high2half(a23[j]));
       float d = __half2float(dh[j]);
-      if (MODE == 1) d = __fmul_rn(d, inv_rms);
+      if (MODE == 1 || MODE == 3) d = __fmul_rn(d, inv_rms);
       acc[j] = __fadd_rn(acc[j], __fmul_rn(d, __half2float(ls)));
     }
   }
   }
+  float total[MV_ROWS_PER_LANE];
 #pragma unroll
   for (uint32_t j = 0; j < MV_ROWS_PER_LANE; j++) {
     float a = acc[j];
     a = __fadd_rn(a, __shfl_xor_sync(FULL, a, 1));
     a = __fadd_rn(a, __shfl_xor_sync(FULL, a, 2));
     a = __fadd_rn(a, __shfl_xor_sync(FULL, a, 4));
-    if (tx == 0 && valid[j]) {
+    total[j] = a;
+    if (MODE != 3 && tx == 0 && valid[j]) {
       if (MODE != 1 && p.accumulate) a = __fadd_rn(__half2float(*out_ptr[j]), a);
       *out_ptr[j] = __float2half_rn(a);
     }
   }
+  if (MODE == 3 && tx == 0 && valid[0])
+    *out_ptr[0] = silu_times_up(__float2half_rn(total[0]), __float2half_rn(total[MV_ROWS_PER_LANE - 1]));
 }
 
 // rms_norm.wgsl:41-85: one CTA of 512 threads per group.
@@ -1040,6 +1049,31 @@ cudaError_t bp_q1_matvec_normed(bool pdl, cudaStream_t s, const bp_q1_tensor* w,
   p.aux = w_norm;
   p.eps = eps;
   return launch_mv<1>(pdl, s, p);
+}
+
+// out[i] = silu(f16(W_gate rms_norm(x))_i) * f16(W_up rms_norm(x))_i: matvec_q1_0_fused_normed over (gate, up)
+// followed by silu_mul, in one launch.
+cudaError_t bp_q1_matvec_normed_silu(bool pdl, cudaStream_t s, const bp_q1_tensor& w_gate, const bp_q1_tensor& w_up, __half* out,
+                                     const __half* x, const __half* w_norm, float eps) {
+  if (w_gate.k != w_up.k || w_gate.n != w_up.n) return cudaErrorInvalidValue;
+  MvParams p = {};
+  p.n_ranges = 2;
+  p.r[0] = {w_gate.d, static_cast<const uint4*>(w_gate.bits), out, w_gate.n};
+  p.r[1] = {w_up.d, static_cast<const uint4*>(w_up.bits), out, w_up.n};
+  p.n_total = w_gate.n;
+  p.k = w_gate.k;
+  p.x = x;
+  p.aux = w_norm;
+  p.eps = eps;
+  const size_t smem = mv_smem_bytes(p.k);
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(matvec_q1_kernel<3, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+    configured = smem;
+  }
+  const uint32_t rows_per_cta = MV_THREADS / 8;
+  return bp_launch(pdl, matvec_q1_kernel<3, 2>, dim3((p.n_total + rows_per_cta - 1) / rows_per_cta), dim3(MV_THREADS), smem, s, p);
 }
 
 cudaError_t bp_q1_matvec_silu(bool pdl, cudaStream_t s, const bp_q1_tensor& w, const __half* gate, const __half* up, __half* y,

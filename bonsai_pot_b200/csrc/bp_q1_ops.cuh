@@ -19,6 +19,8 @@ cudaError_t bp_q1_relayout(cudaStream_t s, const uint8_t* qs, void* out, uint64_
 cudaError_t bp_q1_matvec(bool pdl, cudaStream_t s, const bp_q1_tensor& w, const __half* x, __half* y, bool accumulate);
 cudaError_t bp_q1_matvec_normed(bool pdl, cudaStream_t s, const bp_q1_tensor* w, __half* const* out, uint32_t n_ranges,
                                 const __half* x, const __half* w_norm, float eps);
+cudaError_t bp_q1_matvec_normed_silu(bool pdl, cudaStream_t s, const bp_q1_tensor& w_gate, const bp_q1_tensor& w_up, __half* out,
+                                     const __half* x, const __half* w_norm, float eps);
 cudaError_t bp_q1_matvec_silu(bool pdl, cudaStream_t s, const bp_q1_tensor& w, const __half* gate, const __half* up, __half* y,
                               bool accumulate);
 cudaError_t bp_q1_rms_norm(bool pdl, cudaStream_t s, const __half* in, __half* out, const __half* w, uint32_t group_size,
