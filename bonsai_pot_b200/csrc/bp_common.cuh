@@ -48,6 +48,8 @@ struct bp_attn_ctx {
   __half *stage_q, *stage_k, *stage_v, *stage_out, *stage_wq, *stage_wk;
   uint32_t stage_rows;
   cudaStream_t host_stream;
+  uint8_t stage_w_host[2][BP_HEAD_DIM * 2];  // the norm weights last uploaded by a host-buffer call (they rarely change)
+  bool stage_w_valid;
   int sm_count;
   uint32_t variant;
   uint32_t opt_nw;   // decode: compute warps per CTA (8 or 16)
