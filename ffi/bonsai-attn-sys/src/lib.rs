@@ -9,6 +9,9 @@
 #![allow(non_camel_case_types)]
 use std::os::raw::{c_char, c_int, c_void};
 
+/// `include/bonsai_model.h`: operators, model directory, forward passes, sampler, session.
+pub mod model;
+
 /// Opaque context: owns `kv_k`, `kv_v`, the RoPE table and the split-KV scratch
 /// (what `Model` owns for this path, src/model.rs:1148-1248).
 #[repr(C)]

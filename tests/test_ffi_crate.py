@@ -11,20 +11,24 @@ HEADER = os.path.join(ROOT, "include", "bonsai_attn.h")
 LIB_RS = os.path.join(ROOT, "ffi", "bonsai-attn-sys", "src", "lib.rs")
 
 
-def header_text():
-    return re.sub(r"/\*.*?\*/", "", open(HEADER).read(), flags=re.S)
+def header_text(path=HEADER):
+    return re.sub(r"/\*.*?\*/", "", open(path).read(), flags=re.S)
 
 
-def header_functions():
+def header_functions(path=HEADER):
     out = {}
-    for m in re.finditer(r"([a-zA-Z_][\w \*]*?)\b(bp_[a-z0-9_]+)\s*\(([^)]*)\)\s*;", header_text()):
+    for m in re.finditer(r"([a-zA-Z_][\w \*]*?)\b(bp_[a-z0-9_]+)\s*\(([^)]*)\)\s*;", header_text(path)):
         ret, name, args = m.group(1).strip(), m.group(2), m.group(3)
-        out[name] = (len([a for a in args.split(",") if a.strip()]), ret == "void")
+        out[name] = (len([a for a in args.split(",") if a.strip() and a.strip() != "void"]), ret == "void")
     return out
 
 
-def rust_functions():
-    text = re.sub(r"//.*", "", open(LIB_RS).read())
+MODEL_HEADER = os.path.join(ROOT, "include", "bonsai_model.h")
+MODEL_RS = os.path.join(ROOT, "ffi", "bonsai-attn-sys", "src", "model.rs")
+
+
+def rust_functions(path=LIB_RS):
+    text = re.sub(r"//.*", "", open(path).read())
     block = re.search(r'extern "C" \{(.*?)\n\}', text, flags=re.S).group(1)
     out = {}
     for m in re.finditer(r"pub fn (bp_[a-z0-9_]+)\s*\((.*?)\)\s*(->\s*[^;]+)?;", block, flags=re.S):
@@ -74,3 +78,26 @@ def test_repr_c_structs_match_the_header():
         c, r = c_struct_fields(name), rust_struct_fields(name)
         assert [n for n, _ in c] == [n for n, _ in r], name
         assert [t for _, t in c] == [ctype[t] for _, t in r], name
+
+
+def test_model_module_matches_the_model_header():
+    """src/model.rs declares exactly the functions of include/bonsai_model.h, with the same number of
+    arguments and the same kind of return value, and its two repr(C) structs list the header's fields."""
+    h, r = header_functions(MODEL_HEADER), rust_functions(MODEL_RS)
+    assert len(h) >= 40
+    assert sorted(h) == sorted(r)
+    for name in h:
+        assert h[name] == r[name], (name, h[name], r[name])
+    text = re.sub(r"//.*", "", open(MODEL_RS).read())
+    cfg = re.search(r"pub struct bp_model_config \{(.*?)\n\}", text, flags=re.S).group(1)
+    fields = [n for n, _ in re.findall(r"pub (\w+):\s*([^,\n]+)", cfg)]
+    body = re.search(r"typedef struct bp_model_config \{(.*?)\}", header_text(MODEL_HEADER), flags=re.S).group(1)
+    want = []
+    for decl in body.split(";"):
+        decl = decl.strip()
+        if decl:
+            want += [n.strip() for n in decl.split(None, 1)[1].split(",")]
+    assert fields == want
+    smp = re.search(r"pub struct bp_sampler \{(.*?)\n\}", text, flags=re.S).group(1)
+    assert [n for n, _ in re.findall(r"pub (\w+):\s*([^,\n]+)", smp)] == ["temperature", "top_k", "top_p", "seed"]
+    assert "pub mod model;" in open(LIB_RS).read()
