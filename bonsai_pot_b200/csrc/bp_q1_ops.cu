@@ -13,6 +13,7 @@
 // groups g = 0..15 / 16..31, the flip bit of element 4 g at bit 15 - g and of element 4 g + 1 at
 // bit 31 - g; words 2 / 3 the same for elements 4 g + 2, 4 g + 3. A lane works on four rows at
 // once (the activations it reads from shared memory serve all four).
+#include <cooperative_groups.h>
 #include <cuda_fp16.h>
 #include <math.h>
 
@@ -23,6 +24,7 @@
 namespace {
 
 using namespace bp;
+namespace cg = cooperative_groups;
 constexpr unsigned FULL = 0xffffffffu;
 constexpr uint32_t MV_THREADS = 128;          // the invocation count of the fused shader: its sum of squares is per invocation
 // rows per lane (R): 4 for tall tensors (the activations a lane reads serve all of them), fewer for the
@@ -832,88 +834,118 @@ __global__ void __launch_bounds__(UM_THREADS, 1) matmul_q1_q8_umma_kernel(const 
   if (warp == 0) tmem_dealloc(tmem, 512);
 }
 
-// topk_reduce.wgsl:59-196, the same steps on the same lists (256 per-thread min-heaps of 32, heapsort, then
-// log2(256) bitonic merge rounds), so that ties fall exactly where the shader's comparisons put them. What
-// differs is only how the steps are scheduled on a warp:
-//   - list j's element i sits at [i][j] in shared memory (bank = j) as one 8-byte (value, index) pair;
+// topk_reduce.wgsl:59-196, the same steps on the same lists (256 per-invocation min-heaps of 32, heapsort,
+// then log2(256) bitonic merge rounds), so that ties fall exactly where the shader's comparisons put them.
+// What differs is only how the steps are scheduled:
+//   - list j's element i sits at [i][slot of j] in shared memory as one 8-byte (value, index) pair;
 //   - a sift moves the inserted element down a chain of holes instead of swapping at every level (the same
 //     comparisons, hence the same final array);
-//   - a lane's list is scanned from a chunk of logits staged in shared memory, and the lanes of a warp are
-//     not held in step: per chunk a lane first marks, in one straight-line pass, the elements above its
-//     heap's root (only those can enter, the root only rises), then the lanes walk their marks: every lane
-//     skips to its next mark that still beats the root, and the lanes that have one sift together. In step,
-//     nearly every one of the 594 iterations made the whole warp wait for some lane's insertion (375 us per
-//     call at 151936 logits);
+//   - a list is scanned from a chunk of logits staged in shared memory, and the lanes of a warp are not held
+//     in step: per chunk a lane first marks, in one straight-line pass, the elements above its heap's root,
+//     then walks its marks (see the loop);
 //   - for the merge rounds each list is moved to a row of its own (33 entries apart: consecutive lanes then
 //     read consecutive entries of ONE list, as the shader's layout has it).
 constexpr uint32_t TK_WG = 256, TK_K = 32, TK_CHUNK = 32;  // chunk: words (two logits) per list and stage
 constexpr uint32_t TK_ROW = TK_K + 1;                      // entries between the rows of the merge rounds
+constexpr uint32_t TK_CTAS = 8;                            // the CTAs of the cluster: TK_WG / TK_CTAS lists each
+constexpr uint32_t TK_LISTS = TK_WG / TK_CTAS;             // lists per CTA
+#ifndef TK_LPW_DEF
+#define TK_LPW_DEF 4
+#endif
+constexpr uint32_t TK_LPW = TK_LPW_DEF;                             // lists per warp (one lane each; the other lanes load and copy)
+constexpr uint32_t TK_THREADS = 32 * (TK_LISTS / TK_LPW);
+static_assert(TK_THREADS >= TK_WG, "the merge rounds of the first CTA run on the shader's 256 invocations");
 struct __align__(8) TkEntry { float v; uint32_t i; };
-__device__ __forceinline__ void tk_sift_hole(TkEntry* heap, uint32_t j, uint32_t limit, TkEntry e) {
-  // heap[0] of list j is being replaced by e: walk down while a child is smaller (topk_reduce.wgsl:35-50)
+constexpr size_t TK_SMEM = (TK_WG * TK_ROW + TK_K * TK_LISTS) * sizeof(TkEntry) + TK_CHUNK * TK_LISTS * sizeof(__half2);
+// heap[0] of list j is being replaced by e: walk down while a child is smaller (topk_reduce.wgsl:35-50).
+// Both children are read at once (the right one only counts when it exists); returns the value left at the root.
+__device__ __forceinline__ float tk_sift_hole(TkEntry* heap, uint32_t j, uint32_t limit, TkEntry e) {
   uint32_t i = 0;
+  float root = e.v;
   for (;;) {
     const uint32_t l = 2 * i + 1, r = l + 1;
     if (l >= limit) break;
-    const TkEntry cl = heap[l * TK_WG + j];
+    const TkEntry cl = heap[l * TK_LISTS + j];
+    const TkEntry cr = heap[(r < limit ? r : l) * TK_LISTS + j];
     uint32_t smallest = i;
     float sv = e.v;
     TkEntry cs = e;
     if (cl.v < sv) { smallest = l; sv = cl.v; cs = cl; }
-    if (r < limit) {
-      const TkEntry cr = heap[r * TK_WG + j];
-      if (cr.v < sv) { smallest = r; cs = cr; }
-    }
+    if (r < limit && cr.v < sv) { smallest = r; cs = cr; }
     if (smallest == i) break;
-    heap[i * TK_WG + j] = cs;
+    heap[i * TK_LISTS + j] = cs;
+    if (i == 0) root = cs.v;
     i = smallest;
   }
-  heap[i * TK_WG + j] = e;
+  heap[i * TK_LISTS + j] = e;
+  return root;
 }
-__global__ void __launch_bounds__(TK_WG) topk_kernel(const __half* logits, uint32_t n, uint32_t k, float* out_val, uint32_t* out_idx) {
+__device__ __forceinline__ void tk_merge_sync() { asm volatile("bar.sync 1, %0;" ::"n"(TK_WG) : "memory"); }  // the merging threads only
+// One cluster of TK_CTAS CTAs. The 256 lists of the shader are independent until its merge rounds, and what
+// a list costs is a chain of about 130 dependent sifts (375 us per call at 151936 logits with 32 lists per
+// warp held in step, 176 us with the marks below, on ONE SM): so the lists are spread over the cluster, four
+// to a warp, each CTA hands its sorted lists to the first CTA's shared memory, and that CTA runs the merge
+// rounds on the shader's 256 invocations.
+__global__ void __cluster_dims__(TK_CTAS, 1, 1) __launch_bounds__(TK_THREADS)
+    topk_kernel(const __half* logits, uint32_t n, uint32_t k, float* out_val, uint32_t* out_idx) {
   extern __shared__ __align__(16) uint8_t tk_smem[];
-  TkEntry* heap = reinterpret_cast<TkEntry*>(tk_smem);                                    // [TK_K][TK_WG]
-  __half2* stage = reinterpret_cast<__half2*>(tk_smem + TK_WG * TK_K * sizeof(TkEntry));  // [TK_CHUNK][TK_WG]
+  TkEntry* rows = reinterpret_cast<TkEntry*>(tk_smem);        // [TK_WG][TK_ROW], used in the first CTA only
+  TkEntry* heap = rows + TK_WG * TK_ROW;                      // [TK_K][TK_LISTS]
+  __half2* stage_all = reinterpret_cast<__half2*>(heap + TK_K * TK_LISTS);
+  cg::cluster_group cluster = cg::this_cluster();
   pdl_launch_dependents();
   pdl_wait();
-  const uint32_t tid = threadIdx.x;
-  for (uint32_t i = 0; i < TK_K; i++) heap[i * TK_WG + tid] = TkEntry{-1e30f, 0u};
+  const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool owner = lane < TK_LPW;                           // this lane scans a list
+  const uint32_t jl = warp * TK_LPW + (owner ? lane : 0);     // the list's slot in this CTA
+  const uint32_t j0 = cluster.block_rank() * TK_LISTS + warp * TK_LPW;  // the warp's first list
+  const uint32_t j = j0 + (owner ? lane : 0);                 // the shader's invocation index of the list
+  __half2* stage = stage_all + warp * (TK_CHUNK * TK_LPW);    // [TK_CHUNK][TK_LPW], this warp's
+  if (owner)
+    for (uint32_t i = 0; i < TK_K; i++) heap[i * TK_LISTS + jl] = TkEntry{-1e30f, 0u};
   const uint32_t n_words = (n + 1) >> 1;
-  float cur_min = -1e30f;  // mirrors the root of this thread's heap
+  float cur_min = -1e30f;  // mirrors the root of this lane's heap
+  // lane c fetches word c of the chunk for each of the warp's lists (adjacent words)
+  __half2 nxt[TK_LPW];
+  auto fetch = [&](uint32_t w_base) {
+#pragma unroll
+    for (uint32_t jj = 0; jj < TK_LPW; jj++) {
+      const uint32_t w = w_base + lane * TK_WG + j0 + jj;
+      nxt[jj] = w < n_words ? __ldg(reinterpret_cast<const __half2*>(logits + 2 * w)) : __half2();
+    }
+  };
+  fetch(0);
   for (uint32_t w_base = 0; w_base < n_words; w_base += TK_CHUNK * TK_WG) {
-    __syncthreads();  // the previous chunk has been consumed
-    {
-      __half2 tmp[TK_CHUNK];  // every load of the chunk in flight before the first store
+    __syncwarp();  // the previous chunk has been consumed
+#pragma unroll
+    for (uint32_t jj = 0; jj < TK_LPW; jj++) stage[lane * TK_LPW + jj] = nxt[jj];
+    if (w_base + TK_CHUNK * TK_WG < n_words) fetch(w_base + TK_CHUNK * TK_WG);  // in flight under this chunk's sifts
+    __syncwarp();
+    // this lane's elements of the chunk, in the shader's order: word c (low half, then high half) = bit 2 c, 2 c + 1
+    const uint32_t words_here = owner && w_base + j < n_words ? min(TK_CHUNK, (n_words - w_base - j + TK_WG - 1) / TK_WG) : 0;
+    unsigned long long marks = 0;
+    if (owner) {
 #pragma unroll
       for (uint32_t c = 0; c < TK_CHUNK; c++) {
-        const uint32_t w = w_base + c * TK_WG + tid;
-        tmp[c] = w < n_words ? __ldg(reinterpret_cast<const __half2*>(logits + 2 * w)) : __half2();
+        const __half2 pair = stage[c * TK_LPW + lane];
+        const uint32_t i0 = 2 * (w_base + c * TK_WG + j);
+        const bool m0 = c < words_here && __low2float(pair) > cur_min;
+        const bool m1 = c < words_here && i0 + 1 < n && __high2float(pair) > cur_min;
+        marks |= (static_cast<unsigned long long>(m0) << (2 * c)) | (static_cast<unsigned long long>(m1) << (2 * c + 1));
       }
-#pragma unroll
-      for (uint32_t c = 0; c < TK_CHUNK; c++) stage[c * TK_WG + tid] = tmp[c];
     }
-    __syncthreads();
-    // this thread's elements of the chunk, in the shader's order: word c (low half, then high half) = bit 2 c, 2 c + 1
-    const uint32_t words_here = w_base + tid < n_words ? min(TK_CHUNK, (n_words - w_base - tid + TK_WG - 1) / TK_WG) : 0;
-    unsigned long long marks = 0;
-#pragma unroll
-    for (uint32_t c = 0; c < TK_CHUNK; c++) {
-      const __half2 pair = stage[c * TK_WG + tid];
-      const uint32_t i0 = 2 * (w_base + c * TK_WG + tid);
-      const bool m0 = c < words_here && __low2float(pair) > cur_min;
-      const bool m1 = c < words_here && i0 + 1 < n && __high2float(pair) > cur_min;
-      marks |= (static_cast<unsigned long long>(m0) << (2 * c)) | (static_cast<unsigned long long>(m1) << (2 * c + 1));
-    }
+    // Only the elements above the heap's root at the start of the chunk can enter (the root only rises): every
+    // lane skips to its next mark that still beats its root, and the lanes that have one sift together.
     for (;;) {
       float v = 0.f;
       uint32_t idx = 0;
       bool have = false;
-      while (marks != 0) {  // skip to the next mark that still beats the root
+      while (marks != 0) {
         const uint32_t pos = __ffsll(static_cast<long long>(marks)) - 1;
         marks &= marks - 1;
-        const __half2 pair = stage[(pos >> 1) * TK_WG + tid];
+        const __half2 pair = stage[(pos >> 1) * TK_LPW + lane];
         v = (pos & 1) ? __high2float(pair) : __low2float(pair);
-        idx = 2 * (w_base + (pos >> 1) * TK_WG + tid) + (pos & 1);
+        idx = 2 * (w_base + (pos >> 1) * TK_WG + j) + (pos & 1);
         if (v > cur_min) {
           have = true;
           break;
@@ -921,34 +953,33 @@ __global__ void __launch_bounds__(TK_WG) topk_kernel(const __half* logits, uint3
       }
       if (!__any_sync(FULL, have)) break;
       if (have) {
-        tk_sift_hole(heap, tid, TK_K, TkEntry{v, idx});
-        cur_min = heap[tid].v;
+        cur_min = tk_sift_hole(heap, jl, TK_K, TkEntry{v, idx});
       }
     }
   }
   // heapsort to descending order (topk_reduce.wgsl:106-126): swap the root with the last active slot, sift
-  for (uint32_t active = TK_K - 1; active > 0; active--) {
-    const TkEntry root = heap[tid], last = heap[active * TK_WG + tid];
-    heap[active * TK_WG + tid] = root;
-    tk_sift_hole(heap, tid, active, last);
+  if (owner) {
+    for (uint32_t active = TK_K - 1; active > 0; active--) {
+      const TkEntry root = heap[jl], last = heap[active * TK_LISTS + jl];
+      heap[active * TK_LISTS + jl] = root;
+      tk_sift_hole(heap, jl, active, last);
+    }
   }
-  {  // every list to a row of its own: rows[j * TK_ROW + i], over the heap and stage areas
-    TkEntry mine[TK_K];
+  __syncwarp();
+  {  // every list to a row of its own in the first CTA: rows[j * TK_ROW + i]; lane i carries entry i
+    TkEntry* rows0 = cluster.map_shared_rank(rows, 0);
 #pragma unroll
-    for (uint32_t i = 0; i < TK_K; i++) mine[i] = heap[i * TK_WG + tid];
-    __syncthreads();
-#pragma unroll
-    for (uint32_t i = 0; i < TK_K; i++) heap[tid * TK_ROW + i] = mine[i];
-    __syncthreads();
+    for (uint32_t jj = 0; jj < TK_LPW; jj++) rows0[(j0 + jj) * TK_ROW + lane] = heap[lane * TK_LISTS + warp * TK_LPW + jj];
   }
-  TkEntry* rows = heap;
+  cluster.sync();  // the rows are in the first CTA's shared memory; the other CTAs are done
+  if (cluster.block_rank() != 0 || tid >= TK_WG) return;
   for (uint32_t s = TK_WG / 2; s > 0; s >>= 1) {
     for (uint32_t kk = tid; kk < s * TK_K; kk += TK_WG) {
       const uint32_t pair = kk / TK_K, i = kk % TK_K, bi = TK_K - 1 - i;
       const TkEntry a = rows[pair * TK_ROW + i], b = rows[(pair + s) * TK_ROW + bi];
       if (b.v > a.v) rows[pair * TK_ROW + i] = b;
     }
-    __syncthreads();
+    tk_merge_sync();
     for (uint32_t stride = TK_K / 2; stride > 0; stride >>= 1) {
       for (uint32_t kk = tid; kk < s * (TK_K / 2); kk += TK_WG) {
         const uint32_t pair = kk / (TK_K / 2), local = kk % (TK_K / 2);
@@ -959,7 +990,7 @@ __global__ void __launch_bounds__(TK_WG) topk_kernel(const __half* logits, uint3
           rows[pair * TK_ROW + hi] = a;
         }
       }
-      __syncthreads();
+      tk_merge_sync();
     }
   }
   const uint32_t kk = k < TK_K ? k : TK_K;
@@ -1188,11 +1219,10 @@ cudaError_t bp_q1_matmul_multi(bool pdl, cudaStream_t s, const bp_q1_tensor* w, 
 
 cudaError_t bp_q1_topk(bool pdl, cudaStream_t s, const __half* logits, uint32_t n, uint32_t k, float* out_val, uint32_t* out_idx) {
   static bool configured = false;
-  const size_t smem = TK_WG * TK_K * sizeof(TkEntry) + TK_CHUNK * TK_WG * sizeof(__half2);
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    cudaError_t e = cudaFuncSetAttribute(topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(TK_SMEM));
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  return bp_launch(pdl, topk_kernel, dim3(1), dim3(TK_WG), smem, s, logits, n, k, out_val, out_idx);
+  return bp_launch(pdl, topk_kernel, dim3(TK_CTAS), dim3(TK_THREADS), TK_SMEM, s, logits, n, k, out_val, out_idx);
 }
