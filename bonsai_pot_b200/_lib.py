@@ -149,6 +149,8 @@ MODEL_SIGNATURES = {
     "bp_model_error_detail": (None, [_vp, C.POINTER(ErrorDetail)]),
     "bp_model_attn": (_vp, [_vp]),
     "bp_model_step_topk": (_int, [_vp, _u32, _u32, _u32, _f32p, _u32p]),
+    "bp_model_set_step_graph": (_int, [_vp, _u32]),
+    "bp_model_graph_steps": (_u64, [_vp]),
     "bp_model_prefill_topk": (_int, [_vp, _u32p, _u32, _u32, _f32p, _u32p]),
     "bp_model_prefill_loop_topk": (_int, [_vp, _u32p, _u32, _u32, _u32, _f32p, _u32p]),
     "bp_model_read_hidden": (_int, [_vp, _u32, _vp]),

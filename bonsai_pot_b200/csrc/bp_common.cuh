@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <vector>
+
 #include "../../include/bonsai_attn.h"
 
 constexpr uint32_t BP_HEAD_DIM = 128;
@@ -99,11 +101,46 @@ __host__ __device__ inline uint64_t bp_qs_off(const bp_attn_ctx* c, uint32_t il)
   return c->d_total + (uint64_t)il * c->cfg.max_seq * c->kv_dim;
 }
 
+// A launch as data: what a kernel node of a CUDA graph holds. A caller that keeps a captured step in a graph
+// re-derives the launches whose arguments change from one execution to the next (the position of an attention
+// call) through the ordinary launcher functions and patches the nodes with what they produced.
+struct bp_launch_record {
+  void* func = nullptr;
+  dim3 grid, block;
+  size_t smem = 0;
+  std::vector<std::vector<uint8_t>> args;  // the kernel arguments, one copy each, in order
+  cudaGraphNode_t node = nullptr;          // mode 2: the node the launch became in the stream's capture
+};
+// While a recorder is installed on the calling thread every bp_launch goes through it: mode 1 stores the launch
+// and launches NOTHING, mode 2 launches and stores the launch with its graph node (the stream must be capturing).
+struct bp_launch_recorder {
+  int mode = 1;
+  std::vector<bp_launch_record> records;
+};
+bp_launch_recorder*& bp_recorder();  // this thread's recorder, or null
+
+template <typename T>
+inline void bp_record_arg(bp_launch_record& r, const T& v) {
+  const uint8_t* b = reinterpret_cast<const uint8_t*>(&v);
+  r.args.emplace_back(b, b + sizeof(T));
+}
+
 // Launches `kernel`; with `pdl` the launch carries programmatic stream serialization, so that the
 // kernel's prologue overlaps the tail of its predecessor (the kernels call pdl_wait() themselves).
 template <typename... KArgs, typename... Args>
 inline cudaError_t bp_launch(bool pdl, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
                              Args&&... args) {
+  bp_launch_recorder* rec = bp_recorder();
+  if (rec != nullptr) {
+    rec->records.emplace_back();
+    bp_launch_record& r = rec->records.back();
+    r.func = reinterpret_cast<void*>(kernel);
+    r.grid = grid;
+    r.block = block;
+    r.smem = smem;
+    (bp_record_arg<KArgs>(r, static_cast<KArgs>(args)), ...);
+    if (rec->mode == 1) return cudaSuccess;
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -114,7 +151,16 @@ inline cudaError_t bp_launch(bool pdl, void (*kernel)(KArgs...), dim3 grid, dim3
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+  if (e == cudaSuccess && rec != nullptr) {  // mode 2: the node this launch became (the only dependency of the stream's next node)
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    const cudaGraphNode_t* deps = nullptr;
+    size_t n_deps = 0;
+    e = cudaStreamGetCaptureInfo_v3(s, &st, nullptr, nullptr, &deps, nullptr, &n_deps);
+    if (e == cudaSuccess && (st != cudaStreamCaptureStatusActive || n_deps != 1)) e = cudaErrorStreamCaptureUnsupported;
+    if (e == cudaSuccess) rec->records.back().node = deps[0];
+  }
+  return e;
 }
 
 // Kernel launchers (one per kernel file). Each returns the cudaError_t of its

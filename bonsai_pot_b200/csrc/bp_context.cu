@@ -137,6 +137,11 @@ uint32_t bp_fresh_from(const bp_attn_ctx* c, uint32_t layer) {
   return recent_write(c, layer) ? c->row_from[layer] : UINT32_MAX;
 }
 
+bp_launch_recorder*& bp_recorder() {
+  static thread_local bp_launch_recorder* r = nullptr;
+  return r;
+}
+
 void* bp_tensor_map_encoder() {
   static encode_tiled_fn encode = get_encode();
   return reinterpret_cast<void*>(encode);

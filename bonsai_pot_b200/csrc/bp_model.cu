@@ -278,6 +278,20 @@ struct bp_model {
   uint32_t* topk_idx = nullptr;
   uint32_t tap_mode = 0;
   uint8_t* tap_buf = nullptr;
+  // The one-token step as a CUDA graph (token copy, embed, layers, output suffix, result copies). The only
+  // launches whose arguments depend on the position are the attention calls: their nodes are patched per step
+  // with what the attention library's launcher produces for the new position.
+  struct StepGraph {
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    std::vector<std::vector<bp_launch_record>> attn;  // per layer: the attention launches as captured
+    bool valid = false;
+  } sg;
+  bool step_graph = true;     // bp_model_set_step_graph
+  uint64_t graph_steps = 0;   // steps that ran as a graph launch
+  uint32_t* token_pin = nullptr;  // pinned: the token of the step (read by the graph's copy node)
+  float* res_val_pin = nullptr;   // pinned: top-k results of the step
+  uint32_t* res_idx_pin = nullptr;
 };
 
 struct bp_session {
@@ -352,19 +366,39 @@ const __half* f16_view(const bp_model* m, const std::string& name) {
 
 // One layer of the one-token path: layer_pre_kv_in_pass, dispatch_kv_writeback_fused, layer_post_kv_in_pass
 // (src/forward.rs:608-631, 763-908). The three attention dispatches are one call of the attention library.
-int decode_layer(bp_model* m, uint32_t il, uint32_t pos) {
+// The attention call of layer il at position pos (Q norm + RoPE, cache write, attention: one launch by default).
+cudaError_t attention_call(bp_model* m, uint32_t il, uint32_t pos) {
+  const LayerTensors& lt = m->layers[il];
+  uint32_t launches = 0;
+  return bp_launch_decode_fused(m->attn, m->stream, il, m->q, m->q_roped, lt.q_norm, m->k_cur, m->v_cur, lt.k_norm, pos, m->attn_out,
+                                &launches);
+}
+
+// Which launches carry programmatic stream serialization was measured per kernel on the 8B shape (us per layer,
+// stream launches / graph replay): all four matvecs 55.0 / 53.2, all but the down projection 48.8 / 44.8, gate + up
+// only 49.9 / 41.1, none 51.2 / 42.3. The down projection's CTAs, resident early, take the SM slots that the
+// second wave of the gate + up launch is waiting for.
+int decode_layer(bp_model* m, uint32_t il, uint32_t pos, bool in_graph = false, std::vector<bp_launch_record>* attn_nodes = nullptr) {
   const Config& c = m->cfg;
   const LayerTensors& lt = m->layers[il];
   cudaStream_t s = m->stream;
-  const bool pdl = true;
+  const bool pdl = !in_graph;
   {
     const bp_q1_tensor w[3] = {lt.wq, lt.wk, lt.wv};
     __half* const out[3] = {m->q, m->k_cur, m->v_cur};
     M_CUDA(m, bp_q1_matvec_normed(pdl, s, w, out, 3, m->x, lt.attn_norm, c.rms_eps));
   }
-  uint32_t launches = 0;
-  M_CUDA(m, bp_launch_decode_fused(m->attn, s, il, m->q, m->q_roped, lt.q_norm, m->k_cur, m->v_cur, lt.k_norm, pos, m->attn_out,
-                                   &launches));
+  if (attn_nodes != nullptr) {  // capturing: keep the nodes of the attention launches
+    bp_launch_recorder rec;
+    rec.mode = 2;
+    bp_recorder() = &rec;
+    const cudaError_t e = attention_call(m, il, pos);
+    bp_recorder() = nullptr;
+    M_CUDA(m, e);
+    *attn_nodes = std::move(rec.records);
+  } else {
+    M_CUDA(m, attention_call(m, il, pos));
+  }
   if (m->tap_mode) {
     uint8_t* slot = m->tap_buf + static_cast<size_t>(il) * c.q_dim * 2;
     if (m->tap_mode == 1) {
@@ -378,8 +412,8 @@ int decode_layer(bp_model* m, uint32_t il, uint32_t pos) {
   // tensors and writes the f16 value that feeds the down projection (the same values dispatch_matvec_q1_0_silu
   // stages; that shader as one kernel had each of the 256 CTAs of the 4096-row down tensor recompute all 12288
   // of them: 27.6 us against 8 for the plain matvec).
-  M_CUDA(m, bp_q1_matvec_normed_silu(pdl, s, lt.wg, lt.wu, m->ffn_in, m->x, lt.ffn_norm, c.rms_eps));
-  M_CUDA(m, bp_q1_matvec(pdl, s, lt.wd, m->ffn_in, m->x, true));
+  M_CUDA(m, bp_q1_matvec_normed_silu(true, s, lt.wg, lt.wu, m->ffn_in, m->x, lt.ffn_norm, c.rms_eps));
+  M_CUDA(m, bp_q1_matvec(false, s, lt.wd, m->ffn_in, m->x, true));
   return BP_OK;
 }
 
@@ -405,6 +439,86 @@ int step_no_suffix(bp_model* m, uint32_t token, uint32_t pos) {
   for (uint32_t il = 0; il < m->cfg.n_layer; il++)
     if (int st = decode_layer(m, il, pos)) return st;
   return BP_OK;
+}
+
+void drop_step_graph(bp_model* m) {
+  if (m->sg.exec) cudaGraphExecDestroy(m->sg.exec);
+  if (m->sg.graph) cudaGraphDestroy(m->sg.graph);
+  m->sg = bp_model::StepGraph();
+}
+
+// The whole step (token copy, embed, layers, output norm, LM head, top-k of TOPK_MAX, result copies) captured
+// from the model's stream at position pos.
+int capture_step_graph(bp_model* m, uint32_t pos) {
+  const Config& c = m->cfg;
+  cudaStream_t s = m->stream;
+  drop_step_graph(m);
+  m->sg.attn.resize(c.n_layer);
+  M_CUDA(m, cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+  int st = BP_OK;
+  cudaError_t e = cudaMemcpyAsync(m->tokens_dev, m->token_pin, sizeof(uint32_t), cudaMemcpyHostToDevice, s);
+  if (e == cudaSuccess) e = bp_q1_embed(false, s, m->embed, m->tokens_dev, 1, m->x);
+  for (uint32_t il = 0; e == cudaSuccess && st == BP_OK && il < c.n_layer; il++) st = decode_layer(m, il, pos, true, &m->sg.attn[il]);
+  if (e == cudaSuccess && st == BP_OK) e = bp_q1_rms_norm(false, s, m->x, m->x, m->output_norm, c.n_embd, 1, c.rms_eps);
+  if (e == cudaSuccess && st == BP_OK) e = bp_q1_matvec(false, s, m->lm_head, m->x, m->logits, false);
+  if (e == cudaSuccess && st == BP_OK) e = bp_q1_topk(false, s, m->logits, c.n_vocab, TOPK_MAX, m->topk_val, m->topk_idx);
+  if (e == cudaSuccess && st == BP_OK) e = cudaMemcpyAsync(m->res_val_pin, m->topk_val, TOPK_MAX * sizeof(float), cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess && st == BP_OK) e = cudaMemcpyAsync(m->res_idx_pin, m->topk_idx, TOPK_MAX * sizeof(uint32_t), cudaMemcpyDeviceToHost, s);
+  const cudaError_t e_end = cudaStreamEndCapture(s, &m->sg.graph);  // always: the stream must leave capture mode
+  if (st != BP_OK) return st;
+  M_CUDA(m, e);
+  M_CUDA(m, e_end);
+  M_CUDA(m, cudaGraphInstantiate(&m->sg.exec, m->sg.graph, 0));
+  m->sg.valid = true;
+  return BP_OK;
+}
+
+// The attention nodes of the captured step, patched for position pos. False: the launches no longer have the
+// captured shape (another kernel instance, another number of launches): the step has to be captured again.
+int patch_step_graph(bp_model* m, uint32_t pos, bool* ok) {
+  *ok = false;
+  for (uint32_t il = 0; il < m->cfg.n_layer; il++) {
+    bp_launch_recorder rec;
+    rec.mode = 1;
+    bp_recorder() = &rec;
+    const cudaError_t e = attention_call(m, il, pos);
+    bp_recorder() = nullptr;
+    M_CUDA(m, e);
+    const std::vector<bp_launch_record>& was = m->sg.attn[il];
+    if (rec.records.size() != was.size()) return BP_OK;
+    for (size_t i = 0; i < was.size(); i++) {
+      bp_launch_record& r = rec.records[i];
+      if (r.func != was[i].func) return BP_OK;
+      std::vector<void*> argv(r.args.size());
+      for (size_t a = 0; a < r.args.size(); a++) argv[a] = r.args[a].data();
+      cudaKernelNodeParams kp = {};
+      kp.func = r.func;
+      kp.gridDim = r.grid;
+      kp.blockDim = r.block;
+      kp.sharedMemBytes = static_cast<unsigned int>(r.smem);
+      kp.kernelParams = argv.data();
+      M_CUDA(m, cudaGraphExecKernelNodeSetParams(m->sg.exec, was[i].node, &kp));
+    }
+  }
+  *ok = true;
+  return BP_OK;
+}
+
+int step_topk_graph(bp_model* m, uint32_t token, uint32_t pos, uint32_t k, float* logits, uint32_t* indices) {
+  *m->token_pin = token;
+  bool patched = false;
+  if (m->sg.valid)
+    if (int st = patch_step_graph(m, pos, &patched)) return st;
+  if (!patched)
+    if (int st = capture_step_graph(m, pos)) return st;
+  M_CUDA(m, cudaGraphLaunch(m->sg.exec, m->stream));
+  M_CUDA(m, cudaStreamSynchronize(m->stream));
+  m->graph_steps++;
+  for (uint32_t i = 0; i < k; i++) {
+    logits[i] = m->res_val_pin[i];
+    indices[i] = m->res_idx_pin[i];
+  }
+  return device_status(m);
 }
 
 int quantize_and_matmul(bp_model* m, const __half* act, uint32_t k, uint32_t mt, const bp_q1_tensor* w, __half* const* out, uint32_t n_w,
@@ -621,6 +735,9 @@ int bp_model_load(const char* dir, uint32_t max_seq, int32_t device, bp_model** 
   M_CUDA(m, cudaMalloc(&m->tokens_dev, mm * sizeof(uint32_t)));
   M_CUDA(m, cudaMalloc(&m->topk_val, TOPK_MAX * sizeof(float)));
   M_CUDA(m, cudaMalloc(&m->topk_idx, TOPK_MAX * sizeof(uint32_t)));
+  M_CUDA(m, cudaMallocHost(&m->token_pin, sizeof(uint32_t)));
+  M_CUDA(m, cudaMallocHost(&m->res_val_pin, TOPK_MAX * sizeof(float)));
+  M_CUDA(m, cudaMallocHost(&m->res_idx_pin, TOPK_MAX * sizeof(uint32_t)));
   M_CUDA(m, cudaStreamSynchronize(m->stream));
   return BP_OK;
 }
@@ -636,6 +753,10 @@ void bp_model_free(bp_model* m) {
   void* bufs[] = {m->x, m->x_norm, m->q, m->q_roped, m->k_cur, m->v_cur, m->attn_out, m->gate, m->up, m->ffn_in, m->logits,
                   m->a_d, m->a_qs, m->tokens_dev, m->topk_val, m->topk_idx};
   for (void* p : bufs) cudaFree(p);
+  drop_step_graph(m);
+  cudaFreeHost(m->token_pin);
+  cudaFreeHost(m->res_val_pin);
+  cudaFreeHost(m->res_idx_pin);
   if (m->stream) cudaStreamDestroy(m->stream);
   bp_attn_destroy(m->attn);
   delete m;
@@ -665,9 +786,19 @@ int bp_model_step_topk(bp_model* m, uint32_t token, uint32_t pos, uint32_t k, fl
   }
   k = k < 1 ? 1 : (k > TOPK_MAX ? TOPK_MAX : k);
   M_CUDA(m, cudaSetDevice(m->device));
+  // as a graph when every launch of the attention call goes through bp_launch (the tcgen05 decode path does)
+  if (m->step_graph && m->tap_mode == 0 && bp_use_umma(m->attn)) return step_topk_graph(m, token, pos, k, logits, indices);
   if (int st = step_no_suffix(m, token, pos)) return st;
   return output_suffix(m, 0, k, logits, indices);
 }
+
+int bp_model_set_step_graph(bp_model* m, uint32_t enable) {
+  if (int st = model_enter(m)) return st;
+  m->step_graph = enable != 0;
+  if (!m->step_graph) drop_step_graph(m);
+  return BP_OK;
+}
+uint64_t bp_model_graph_steps(const bp_model* m) { return m ? m->graph_steps : 0; }
 
 int bp_model_prefill_loop_topk(bp_model* m, const uint32_t* tokens, uint32_t n, uint32_t pos_base, uint32_t k, float* logits,
                                uint32_t* indices) {

@@ -140,6 +140,14 @@ class Model:
         """`step_matvec_topk`: (logits[k], indices[k]) of one token at `pos`."""
         return self._topk_call(self._lib.bp_model_step_topk, token, pos, k=k)
 
+    def set_step_graph(self, enable: bool) -> None:
+        """One-token steps as one CUDA graph launch (the default) or as stream launches."""
+        self._check(self._lib.bp_model_set_step_graph(self._h, 1 if enable else 0))
+
+    def graph_steps(self) -> int:
+        """Steps that ran as a graph launch since the model was loaded."""
+        return int(self._lib.bp_model_graph_steps(self._h))
+
     def prefill_topk(self, tokens, k=TOPK_MAX):
         """`prefill_matmul_topk`: batched prefill of positions 0 .. n - 1."""
         t = np.ascontiguousarray(tokens, dtype=np.uint32)

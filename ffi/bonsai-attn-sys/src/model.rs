@@ -80,6 +80,8 @@ extern "C" {
     pub fn bp_model_error_detail(m: *const bp_model, out: *mut bp_error_detail);
     pub fn bp_model_attn(m: *mut bp_model) -> *mut bp_attn_ctx;
     pub fn bp_model_step_topk(m: *mut bp_model, token: u32, pos: u32, k: u32, logits: *mut f32, indices: *mut u32) -> c_int;
+    pub fn bp_model_set_step_graph(m: *mut bp_model, enable: u32) -> c_int;
+    pub fn bp_model_graph_steps(m: *const bp_model) -> u64;
     pub fn bp_model_prefill_topk(m: *mut bp_model, tokens: *const u32, n: u32, k: u32, logits: *mut f32, indices: *mut u32) -> c_int;
     pub fn bp_model_prefill_loop_topk(m: *mut bp_model, tokens: *const u32, n: u32, pos_base: u32, k: u32, logits: *mut f32, indices: *mut u32) -> c_int;
     pub fn bp_model_read_hidden(m: *mut bp_model, row: u32, x_host: *mut c_void) -> c_int;

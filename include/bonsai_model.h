@@ -94,6 +94,15 @@ bp_attn_ctx* bp_model_attn(bp_model* m);
 /* step_matvec_topk (src/forward.rs:733-745; encode_step_matvec :578-672): one token at position `pos` through every layer, then
  * output_norm, LM head and top-k; logits / indices: host arrays of k <= 32 entries. Synchronous. */
 int bp_model_step_topk(bp_model* m, uint32_t token, uint32_t pos, uint32_t k, float* logits, uint32_t* indices);
+/* bp_model_step_topk runs as ONE CUDA graph launch by default (token copy, embed, every layer, output suffix,
+ * result copies), captured at the first step; before each later step the attention nodes are given the
+ * launch arguments of the new position, and the step is captured again when those launches change shape
+ * (another kernel instance past a context-length threshold). Same kernels, same arguments, same results as
+ * the stream launches; enable = 0 returns to those. The graph is used with the tcgen05 decode kernel
+ * (4 query heads per KV head, kernel family 0) and while the attention tap is off. */
+int bp_model_set_step_graph(bp_model* m, uint32_t enable);
+/* Steps that ran as a graph launch since the model was loaded. */
+uint64_t bp_model_graph_steps(const bp_model* m);
 /* prefill_matmul_topk (src/forward.rs:975-1073; layer_step_matmul_in_pass :1075-1253): n <= m_max tokens at positions 0 .. n - 1, batched. */
 int bp_model_prefill_topk(bp_model* m, const uint32_t* tokens, uint32_t n, uint32_t k, float* logits, uint32_t* indices);
 /* prefill_matvec_loop_topk (src/forward.rs:914-968): the one-token path over every token, any pos_base. */

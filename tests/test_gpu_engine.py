@@ -215,6 +215,35 @@ def test_one_token_pass_matches_the_cpu_pass_bit_for_bit(tmp_path, shape):
                 assert np.array_equal(qq, hm.sh.qs_section(kv, il)[:4])
 
 
+def test_graph_steps_are_identical_to_stream_steps(tmp_path):
+    """The one-token step as one CUDA graph launch (attention nodes patched per position, the step captured
+    again when the attention launch changes shape) against the same step as stream launches: same kernels and
+    arguments, so hidden state, logits and top-k must be identical bit for bit, over positions that cross
+    several 128-token stages of the decode kernel and after a reset to position 0."""
+    d = str(tmp_path / "m")
+    model_dir.write_synthetic_model(d, seed=5)
+    n = 300
+    rng = np.random.default_rng(1)
+    toks = rng.integers(0, 2048, n)
+    outs = []
+    for graph in (True, False):
+        with bp.Model(d, max_seq=512) as gm:
+            gm.set_step_graph(graph)
+            rows = []
+            for pos in list(range(n)) + [0, 1, 2]:
+                lg, ix = gm.step_topk(int(toks[pos]), pos, k=32 if pos % 3 else 5)
+                if pos % 16 == 0 or pos > n - 4:
+                    rows.append((lg.copy(), ix.copy(), gm.hidden(0), gm.logits()))
+                else:
+                    rows.append((lg.copy(), ix.copy()))
+            assert gm.graph_steps() == (n + 3 if graph else 0)
+            assert not gm.attention().status()
+            outs.append(rows)
+    for a, b in zip(*outs):
+        for u, v in zip(a, b):
+            assert u.shape == v.shape and np.array_equal(u.view(np.uint8), v.view(np.uint8))
+
+
 def test_free_running_passes_agree_on_the_top_candidates(tmp_path):
     """Without feeding attention across: GPU engine and CPU engine each with their own attention, one-token
     path and batched prefill. Attention differs within its tolerance, so logits are compared loosely and the
