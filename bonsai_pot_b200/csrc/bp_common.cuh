@@ -69,6 +69,8 @@ struct bp_attn_ctx {
   uint32_t opt_uring;  // tcgen05 decode: 0 = default ring sizes, else K stages * 16 + V slots
   uint32_t opt_umerge; // tcgen05 decode: merge the splits in the decode kernel (1) or with a second kernel (0)
   uint32_t opt_pdl;  // launch the kernels of a layer with programmatic stream serialization (1) or plainly (0)
+  uint32_t opt_token_graph;  // bp_decode_token_host: the layers' launches as one CUDA graph launch (1) or stream launches (0)
+  struct bp_token_graph* tok_graph;  // the captured launches of bp_decode_token_host, or null
   uint32_t opt_pf_nq; // prefill: query tiles per work item (1 or 2), 0 = by batch size
   uint32_t opt_wait_limit;  // polls of an mbarrier / a meeting counter before a kernel gives up (BP_ERR_TIMEOUT)
   uint32_t opt_poll_limit;  // polling rounds of the in-kernel merge before it gives up

@@ -313,6 +313,7 @@ int bp_attn_create(const bp_attn_config* cfg, bp_attn_ctx** out) {
   c->opt_nw = 8;
   c->opt_hpc = cfg->n_kv_head;
   c->opt_pdl = 1;
+  c->opt_token_graph = 1;
   c->opt_umerge = 1;
   c->opt_uhpc = 1;  // one KV head per CTA measured faster than two at every context length tried
   c->opt_wait_limit = 1u << 22;
@@ -329,6 +330,20 @@ int bp_attn_create(const bp_attn_config* cfg, bp_attn_ctx** out) {
   BP_CUDA(c, bp_prefill_init(c));
   BP_CUDA(c, cudaStreamCreateWithFlags(&c->host_stream, cudaStreamNonBlocking));
   return BP_OK;
+}
+
+// The decode launches of one token (one per layer, or two with the separate merge kernel) as a CUDA graph.
+struct bp_token_graph {
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  std::vector<bp_launch_record> launches;  // as captured, with their nodes
+};
+static void drop_token_graph(bp_attn_ctx* c) {
+  if (!c->tok_graph) return;
+  if (c->tok_graph->exec) cudaGraphExecDestroy(c->tok_graph->exec);
+  if (c->tok_graph->graph) cudaGraphDestroy(c->tok_graph->graph);
+  delete c->tok_graph;
+  c->tok_graph = nullptr;
 }
 
 void bp_attn_destroy(bp_attn_ctx* c) {
@@ -355,6 +370,7 @@ void bp_attn_destroy(bp_attn_ctx* c) {
   cudaFree(c->stage_out);
   cudaFree(c->stage_wq);
   cudaFree(c->stage_wk);
+  drop_token_graph(c);
   if (c->host_stream) cudaStreamDestroy(c->host_stream);
   delete c;
 }
@@ -589,6 +605,74 @@ int bp_decode_step_host(bp_attn_ctx* c, uint32_t layer, const void* q, const voi
   return layer_host(c, layer, q, k, v, wq, wk, pos, 1, false, out);
 }
 
+static cudaError_t token_layer_call(bp_attn_ctx* c, cudaStream_t st, uint32_t il, uint32_t pos, uint32_t* launches) {
+  return bp_launch_decode_fused(c, st, il, c->stage_q + static_cast<size_t>(il) * c->q_dim, nullptr, c->stage_wq,
+                                c->stage_k + static_cast<size_t>(il) * c->kv_dim, c->stage_v + static_cast<size_t>(il) * c->kv_dim,
+                                c->stage_wk, pos, c->stage_out + static_cast<size_t>(il) * c->q_dim, launches);
+}
+
+// The layers' launches of one token as ONE graph launch: kernels that follow one another in a graph start
+// about a microsecond sooner than the same kernels launched into a stream. The graph is captured at the first
+// token; for every later token the launcher functions run against a recorder that launches nothing, and the
+// nodes take the launches they produced (the position is in every one of them). A launch of another shape
+// (another kernel instance past a context-length threshold, another number of launches) captures anew.
+static int token_graph_launch(bp_attn_ctx* c, cudaStream_t st, uint32_t pos, uint32_t* launches) {
+  const uint32_t nl = c->cfg.n_layer;
+  bool patched = false;
+  if (c->tok_graph) {
+    bp_launch_recorder rec;
+    rec.mode = 1;
+    bp_recorder() = &rec;
+    cudaError_t e = cudaSuccess;
+    for (uint32_t il = 0; il < nl && e == cudaSuccess; il++) e = token_layer_call(c, st, il, pos, launches);
+    bp_recorder() = nullptr;
+    BP_CUDA(c, e);
+    const std::vector<bp_launch_record>& was = c->tok_graph->launches;
+    patched = rec.records.size() == was.size();
+    for (size_t i = 0; patched && i < was.size(); i++) {
+      bp_launch_record& r = rec.records[i];
+      if (r.func != was[i].func) {
+        patched = false;
+        break;
+      }
+      void* argv[16];
+      if (r.args.size() > 16) return fail(c, BP_ERR_CUDA, "a decode launch has more arguments than the token graph patches");
+      for (size_t a = 0; a < r.args.size(); a++) argv[a] = r.args[a].data();
+      cudaKernelNodeParams kp = {};
+      kp.func = r.func;
+      kp.gridDim = r.grid;
+      kp.blockDim = r.block;
+      kp.sharedMemBytes = static_cast<unsigned int>(r.smem);
+      kp.kernelParams = argv;
+      BP_CUDA(c, cudaGraphExecKernelNodeSetParams(c->tok_graph->exec, was[i].node, &kp));
+    }
+    if (!patched) *launches = 0;
+  }
+  if (!patched) {
+    drop_token_graph(c);
+    bp_token_graph* g = new bp_token_graph();
+    c->tok_graph = g;
+    bp_launch_recorder rec;
+    rec.mode = 2;
+    cudaError_t e = cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal);
+    if (e == cudaSuccess) {
+      bp_recorder() = &rec;
+      for (uint32_t il = 0; il < nl && e == cudaSuccess; il++) e = token_layer_call(c, st, il, pos, launches);
+      bp_recorder() = nullptr;
+      const cudaError_t e_end = cudaStreamEndCapture(st, &g->graph);  // always: the stream must leave capture mode
+      if (e == cudaSuccess) e = e_end;
+    }
+    if (e == cudaSuccess) e = cudaGraphInstantiate(&g->exec, g->graph, 0);
+    if (e != cudaSuccess) {
+      drop_token_graph(c);
+      BP_CUDA(c, e);
+    }
+    g->launches = std::move(rec.records);
+  }
+  BP_CUDA(c, cudaGraphLaunch(c->tok_graph->exec, st));
+  return BP_OK;
+}
+
 int bp_decode_token_host(bp_attn_ctx* c, const void* q, const void* k, const void* v, const void* wq, const void* wk,
                          uint32_t pos, void* out) {
   if (int s = enter(c)) return s;
@@ -606,11 +690,10 @@ int bp_decode_token_host(bp_attn_ctx* c, const void* q, const void* k, const voi
   uint32_t launches = 0;
   if (c->variant == 0 && bp_use_umma(c)) {
     // fused layer steps: the decode kernel normalises q and writes the new cache row itself
-    for (uint32_t il = 0; il < nl; il++) {
-      BP_CUDA(c, bp_launch_decode_fused(c, st, il, c->stage_q + static_cast<size_t>(il) * c->q_dim, nullptr, c->stage_wq,
-                                        c->stage_k + static_cast<size_t>(il) * c->kv_dim,
-                                        c->stage_v + static_cast<size_t>(il) * c->kv_dim, c->stage_wk, pos,
-                                        c->stage_out + static_cast<size_t>(il) * c->q_dim, &launches));
+    if (c->opt_token_graph) {
+      if (int s = token_graph_launch(c, st, pos, &launches)) return s;
+    } else {
+      for (uint32_t il = 0; il < nl; il++) BP_CUDA(c, token_layer_call(c, st, il, pos, &launches));
     }
   } else {
     // Q norm + RoPE of all layers' queries is one launch: every layer's row sits at the same position.
@@ -823,6 +906,10 @@ int bp_set_option(bp_attn_ctx* c, const char* name, uint32_t value) {
     return BP_OK;
   } else if (strcmp(name, "dependent_launch") == 0) {
     c->opt_pdl = value != 0;
+    return BP_OK;
+  } else if (strcmp(name, "token_graph") == 0) {
+    c->opt_token_graph = value != 0;
+    if (!c->opt_token_graph) drop_token_graph(c);
     return BP_OK;
   } else if (strcmp(name, "wait_limit") == 0) {
     if (value == 0) return fail_config(c, "wait_limit must be > 0");

@@ -167,38 +167,68 @@ __global__ void __launch_bounds__(MV_THREADS) matvec_q1_kernel(const MvParams p)
   pdl_wait();  // the activations come from the kernel before this one
   float inv_rms = 1.0f;
   // ---- stage the activations: block b at xs + b * XB_STRIDE ----
+  // Loads of a batch are all requested before the first is used: one load per loop iteration made the
+  // staging a chain of k / 512 L2 latencies (24 of them for the 12288-wide down projection).
   if (MODE == 1 || MODE == 3) {
     float ssq = 0.0f;
-    for (uint32_t v = tid; v < p.k / 4u; v += MV_THREADS) {
-      const uint2 raw = *reinterpret_cast<const uint2*>(p.x + 4u * v);
-      const uint2 wr = *reinterpret_cast<const uint2*>(p.aux + 4u * v);
-      const __half2 x01 = *reinterpret_cast<const __half2*>(&raw.x), x23 = *reinterpret_cast<const __half2*>(&raw.y);
-      const float2 f01 = __half22float2(x01), f23 = __half22float2(x23);
-      ssq = __fadd_rn(ssq, __fmul_rn(f01.x, f01.x));
-      ssq = __fadd_rn(ssq, __fmul_rn(f01.y, f01.y));
-      ssq = __fadd_rn(ssq, __fmul_rn(f23.x, f23.x));
-      ssq = __fadd_rn(ssq, __fmul_rn(f23.y, f23.y));
-      const __half2 y01 = __hmul2(x01, *reinterpret_cast<const __half2*>(&wr.x));
-      const __half2 y23 = __hmul2(x23, *reinterpret_cast<const __half2*>(&wr.y));
-      uint2 o;
-      o.x = *reinterpret_cast<const uint32_t*>(&y01);
-      o.y = *reinterpret_cast<const uint32_t*>(&y23);
-      *reinterpret_cast<uint2*>(xs + (v >> 5) * XB_STRIDE + 4u * (v & 31u)) = o;
+    constexpr uint32_t SB = 8;  // 4-element units of a thread per batch
+    for (uint32_t v0 = tid; v0 < p.k / 4u; v0 += MV_THREADS * SB) {
+      uint2 raw_q[SB], wr_q[SB];
+#pragma unroll
+      for (uint32_t u = 0; u < SB; u++) {
+        const uint32_t v = v0 + u * MV_THREADS;
+        if (v < p.k / 4u) {
+          raw_q[u] = *reinterpret_cast<const uint2*>(p.x + 4u * v);
+          wr_q[u] = __ldg(reinterpret_cast<const uint2*>(p.aux + 4u * v));
+        }
+      }
+#pragma unroll
+      for (uint32_t u = 0; u < SB; u++) {
+        const uint32_t v = v0 + u * MV_THREADS;
+        if (v >= p.k / 4u) break;
+        const uint2 raw = raw_q[u], wr = wr_q[u];
+        const __half2 x01 = *reinterpret_cast<const __half2*>(&raw.x), x23 = *reinterpret_cast<const __half2*>(&raw.y);
+        const float2 f01 = __half22float2(x01), f23 = __half22float2(x23);
+        ssq = __fadd_rn(ssq, __fmul_rn(f01.x, f01.x));
+        ssq = __fadd_rn(ssq, __fmul_rn(f01.y, f01.y));
+        ssq = __fadd_rn(ssq, __fmul_rn(f23.x, f23.x));
+        ssq = __fadd_rn(ssq, __fmul_rn(f23.y, f23.y));
+        const __half2 y01 = __hmul2(x01, *reinterpret_cast<const __half2*>(&wr.x));
+        const __half2 y23 = __hmul2(x23, *reinterpret_cast<const __half2*>(&wr.y));
+        uint2 o;
+        o.x = *reinterpret_cast<const uint32_t*>(&y01);
+        o.y = *reinterpret_cast<const uint32_t*>(&y23);
+        *reinterpret_cast<uint2*>(xs + (v >> 5) * XB_STRIDE + 4u * (v & 31u)) = o;
+      }
     }
     const float total = workgroup_sum<MV_THREADS / 32>(ssq, part);
     inv_rms = __frsqrt_rn(__fadd_rn(__fdiv_rn(total, static_cast<float>(p.k)), p.eps));
+  } else if (MODE == 0) {
+    constexpr uint32_t SB = 6;  // 8-element units of a thread per batch
+    for (uint32_t v0 = tid; v0 < p.k / 8u; v0 += MV_THREADS * SB) {
+      uint4 raw_q[SB];
+#pragma unroll
+      for (uint32_t u = 0; u < SB; u++) {
+        const uint32_t v = v0 + u * MV_THREADS;
+        if (v < p.k / 8u) raw_q[u] = *reinterpret_cast<const uint4*>(p.x + 8u * v);
+      }
+#pragma unroll
+      for (uint32_t u = 0; u < SB; u++) {
+        const uint32_t v = v0 + u * MV_THREADS;
+        if (v < p.k / 8u) *reinterpret_cast<uint4*>(xs + (v >> 4) * XB_STRIDE + 8u * (v & 15u)) = raw_q[u];
+      }
+    }
+    __syncthreads();
   } else {
     for (uint32_t v = tid; v < p.k / 4u; v += MV_THREADS) {
       uint2 o = *reinterpret_cast<const uint2*>(p.x + 4u * v);
-      if (MODE == 2) {
-        const uint2 u = *reinterpret_cast<const uint2*>(p.aux + 4u * v);
-        const __half* g4 = reinterpret_cast<const __half*>(&o);
-        const __half* u4 = reinterpret_cast<const __half*>(&u);
-        __half y[4];
+      const uint2 u = *reinterpret_cast<const uint2*>(p.aux + 4u * v);
+      const __half* g4 = reinterpret_cast<const __half*>(&o);
+      const __half* u4 = reinterpret_cast<const __half*>(&u);
+      __half y[4];
 #pragma unroll
-        for (int c = 0; c < 4; c++) y[c] = silu_times_up(g4[c], u4[c]);
-        o = *reinterpret_cast<const uint2*>(y);
-      }
+      for (int c = 0; c < 4; c++) y[c] = silu_times_up(g4[c], u4[c]);
+      o = *reinterpret_cast<const uint2*>(y);
       *reinterpret_cast<uint2*>(xs + (v >> 5) * XB_STRIDE + 4u * (v & 31u)) = o;
     }
     __syncthreads();
@@ -1062,6 +1092,7 @@ cudaError_t bp_q1_matvec(bool pdl, cudaStream_t s, const bp_q1_tensor& w, const 
   p.k = w.k;
   p.x = x;
   p.accumulate = accumulate ? 1u : 0u;
+  if (reinterpret_cast<uintptr_t>(x) % 16u != 0) return cudaErrorMisalignedAddress;  // the activations are staged 16 bytes at a time
   return launch_mv<0>(pdl, s, p);
 }
 

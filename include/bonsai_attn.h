@@ -257,7 +257,10 @@ int bp_set_variant(bp_attn_ctx* ctx, uint32_t variant);
  * query tile, one CTA per SM; 2 = two query tiles, one CTA per SM; 3 = one query
  * tile, two CTAs per SM; 0 = chosen by batch size: 3 when there are more work
  * items than SMs, else 1). Launch structure: "dependent_launch" (1 = kernels are
- * launched with programmatic stream serialization, the default), "decode_in_kernel_merge"
+ * launched with programmatic stream serialization, the default), "token_graph" (1 = the
+ * layers' launches of bp_decode_token_host go to the device as one CUDA graph launch, its
+ * nodes given the new position's launch arguments before every token, the default; 0 =
+ * stream launches), "decode_in_kernel_merge"
  * (1 = the tcgen05 decode kernel merges its splits itself, the default; 0 = a
  * second kernel does), "decode_ring" (K stages * 16 + V slots of the tcgen05
  * decode kernel, 0 = as many as fit), "decode_v_preload" (1 = the first round of

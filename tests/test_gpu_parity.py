@@ -507,6 +507,41 @@ def test_token_host_entry_point_equals_per_layer_calls():
             ctx.decode_token_host(q, k, v, w, w, 512, out)
 
 
+def test_token_host_graph_launch_is_identical_to_stream_launches():
+    """bp_decode_token_host sends the layers' launches as one CUDA graph launch whose nodes are patched for
+    every token's position (captured again when the launch changes shape): tokens at positions that cross
+    several 128-token stages and the 16-split threshold of the decode kernel, then back to a short context,
+    against the same calls as stream launches on a second context. Outputs and cache rows bit for bit."""
+    sh = O.Shape(n_layer=3, max_seq=4096)
+    rng = np.random.default_rng(21)
+    w = synth.ones_weight()
+    positions = list(range(0, 6)) + list(range(126, 131)) + list(range(2040, 2052)) + [3000, 3001, 4095, 7, 8]
+    seq = [(rng.standard_normal(3 * sh.q_dim).astype(np.float16), rng.standard_normal(3 * sh.kv_dim).astype(np.float16),
+            rng.standard_normal(3 * sh.kv_dim).astype(np.float16)) for _ in positions]
+    results = []
+    for graph in (1, 0):
+        with make_ctx(sh) as ctx:
+            ctx.set_option("token_graph", graph)
+            fill = np.random.default_rng(22)  # the same cache rows under both runs
+            for il in range(3):
+                for kind in range(2):
+                    ctx.kv_import(kind, il, 0, 4096, (fill.random((4096, sh.nb), dtype=np.float32) * 0.05 + 0.001))
+                    ctx.kv_import(kind, il, 1, 4096, fill.integers(-127, 128, (4096, sh.kv_dim), dtype=np.int8))
+            outs = []
+            for (q, k, v), pos in zip(seq, positions):
+                out = np.zeros((3, sh.q_dim), dtype=np.float16)
+                ctx.decode_token_host(q, k, v, w, w, pos, out)
+                outs.append(out.copy())
+            assert not ctx.status()
+            rows = [read_cache(ctx, sh, il, 4096) for il in range(3)]
+            results.append((outs, rows))
+    for a, b in zip(results[0][0], results[1][0]):
+        assert np.array_equal(a.view(np.uint16), b.view(np.uint16))
+    for ra, rb in zip(results[0][1], results[1][1]):
+        for (da, qa), (db, qb) in zip(ra, rb):
+            assert np.array_equal(da.view(np.uint32), db.view(np.uint32)) and np.array_equal(qa, qb)
+
+
 @pytest.mark.parametrize("warps,hpc", [(16, 8), (8, 4), (8, 2), (16, 1), (8, 1)])
 def test_decode_tuning_options_do_not_change_results(warps, hpc):
     sh = O.Shape(n_layer=2, max_seq=4096)
