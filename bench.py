@@ -715,7 +715,7 @@ def extras(torch, bp, stream, hbm_peak, tflops_peak, peak_kind, args):
     return out
 
 
-def engine_bench(torch, bp):
+def engine_bench(torch, bp, n_tokens=128, reps=3):
     """BASELINE config 4: a Bonsai-8B-shaped random-init model (Q1_0 signs Bernoulli(0.5), f16 block scales
     |N(0, 0.02)|, norms 1.0) written to a temporary model directory, loaded, prefilled with 512 tokens through
     the batched path and decoded greedily for 128 tokens through Session::generate, this library's attention
@@ -733,21 +733,21 @@ def engine_bench(torch, bp):
             greedy = bp.Sampler(temperature=0.0)
             sess = m.new_session()
             best_pp, best_tg, toks = None, None, None
-            for _ in range(3):
+            for _ in range(reps):
                 sess.reset()
                 torch.cuda.synchronize()
                 t0 = time.perf_counter()
                 first = sess.prefill(prompt, greedy)
                 t_pp = time.perf_counter() - t0
                 t0 = time.perf_counter()
-                toks, _reason = sess.generate(first, bp.GenerateOptions(max_new_tokens=128, stop_pred=lambda _t: False, sampler=greedy))
+                toks, _reason = sess.generate(first, bp.GenerateOptions(max_new_tokens=n_tokens, stop_pred=lambda _t: False, sampler=greedy))
                 t_tg = time.perf_counter() - t0
                 best_pp = t_pp if best_pp is None else min(best_pp, t_pp)
                 best_tg = t_tg if best_tg is None else min(best_tg, t_tg)
             weights_mb = sum(os.path.getsize(os.path.join(d, f)) for f in os.listdir(d) if f.endswith(".bin")) / 1e6
-        return {"pp512_tok_s": round(512 / best_pp, 1), "tg128_tok_s": round(128 / best_tg, 1), "pp512_ms": round(best_pp * 1e3, 2),
-                "tg128_ms_per_token": round(best_tg * 1e3 / 128, 3), "weights_mb": round(weights_mb, 1), "tokens_emitted": len(toks),
-                "weight_stream_gbs_decode": round(weights_mb / 1e3 / (best_tg / 128), 1),
+        return {"pp512_tok_s": round(512 / best_pp, 1), "tg128_tok_s": round(n_tokens / best_tg, 1), "pp512_ms": round(best_pp * 1e3, 2),
+                "tg128_ms_per_token": round(best_tg * 1e3 / n_tokens, 3), "generated_tokens": n_tokens, "weights_mb": round(weights_mb, 1), "tokens_emitted": len(toks),
+                "weight_stream_gbs_decode": round(weights_mb / 1e3 / (best_tg / n_tokens), 1),
                 "note": "whole engine through Session::prefill + Session::generate, host loop and sampling included"}
     finally:
         shutil.rmtree(d, ignore_errors=True)
@@ -777,6 +777,9 @@ def main():
     ap.add_argument("--variant", type=int, default=0, help="decode kernel family (0 = production)")
     ap.add_argument("--prefill-only", type=int, default=0, metavar="PP",
                     help="run only the prefill pass at this prompt length and print its JSON (profiler captures)")
+    ap.add_argument("--engine-only", type=int, default=0, metavar="TOKENS",
+                    help="run only the whole-engine side measurement (512-token prefill, then this many generated tokens, "
+                         "once) and print its JSON (profiler captures)")
     ap.add_argument("--no-extras", action="store_true", help="skip the ctx-4096 and prefill side measurements")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
@@ -788,6 +791,11 @@ def main():
         hbm_peak, tflops_peak, peak_kind = measured_peaks()
         torch.cuda.set_device(0)
         print(json.dumps(prefill_bench(torch, bp, torch.cuda.Stream(), tflops_peak, peak_kind, args.prefill_only, min(args.layers, 4))))
+    elif args.engine_only:
+        import torch
+        import bonsai_pot_b200 as bp
+        torch.cuda.set_device(0)
+        print(json.dumps(engine_bench(torch, bp, n_tokens=args.engine_only, reps=1)))
     elif args.impl == "reference":
         run_reference(args)
     else:

@@ -47,10 +47,17 @@ def test_matvec_q1_0_bit_exact(k, n, accumulate):
     x = rng.standard_normal(k).astype(np.float16)
     y0 = rng.standard_normal(n).astype(np.float16)
     want = E.matvec(blob, d_off, qs_off, k, n, x, y=y0 if accumulate else None)
-    y, xd = dev(y0.copy()), dev(x)  # named: a temporary's memory may be handed to the next allocation
-    assert _lib.load().bp_op_matvec_q1_0(None, d_dev.data_ptr(), bits.data_ptr(), k, n, xd.data_ptr(), y.data_ptr(), int(accumulate)) == 0
-    torch.cuda.synchronize()
-    assert bits_equal(y, want)
+    xd = dev(x)  # named: a temporary's memory may be handed to the next allocation
+    lib = _lib.load()
+    try:
+        for rows in (0, 1, 2, 4):  # every kernel layout: by height, rows per lane
+            lib.bp_op_set_matvec_rows(rows)
+            y = dev(y0.copy())
+            assert lib.bp_op_matvec_q1_0(None, d_dev.data_ptr(), bits.data_ptr(), k, n, xd.data_ptr(), y.data_ptr(), int(accumulate)) == 0
+            torch.cuda.synchronize()
+            assert bits_equal(y, want), rows
+    finally:
+        lib.bp_op_set_matvec_rows(0)
 
 
 @pytest.mark.parametrize("k,ns", [(4096, (4096, 1024, 1024)), (4096, (12288, 12288)), (512, (1024, 256, 256)), (2560, (32,))])
@@ -65,17 +72,23 @@ def test_matvec_fused_normed_bit_exact(k, ns):
     x = (rng.standard_normal(k) * 3).astype(np.float16)
     w_norm = (1 + 0.1 * rng.standard_normal(k)).astype(np.float16)
     want = E.matvec_fused_normed(blob, k, x, w_norm, 1e-6, offs)
-    outs = [torch.zeros(n, dtype=torch.float16, device="cuda") for n in ns]
     nr = len(ns)
     arr = lambda vals: (C.c_void_p * nr)(*vals)
     xd, wd = dev(x), dev(w_norm)
-    st = _lib.load().bp_op_matvec_q1_0_fused_normed(None, k, xd.data_ptr(), wd.data_ptr(), 1e-6, nr,
+    lib = _lib.load()
+    try:
+        for rows in (0, 1, 2, 4):
+            lib.bp_op_set_matvec_rows(rows)
+            outs = [torch.zeros(n, dtype=torch.float16, device="cuda") for n in ns]
+            st = lib.bp_op_matvec_q1_0_fused_normed(None, k, xd.data_ptr(), wd.data_ptr(), 1e-6, nr,
                                                     arr([p[3].data_ptr() for p in parts]), arr([p[5].data_ptr() for p in parts]),
                                                     (C.c_uint32 * nr)(*ns), arr([o.data_ptr() for o in outs]))
-    assert st == 0
-    torch.cuda.synchronize()
-    for o, w in zip(outs, want):
-        assert bits_equal(o, w)
+            assert st == 0
+            torch.cuda.synchronize()
+            for o, w in zip(outs, want):
+                assert bits_equal(o, w), rows
+    finally:
+        lib.bp_op_set_matvec_rows(0)
 
 
 @pytest.mark.parametrize("k,n", [(12288, 4096), (1536, 512), (9728, 24)])
