@@ -580,7 +580,8 @@ int bp_op_matvec_q1_0_silu(void* stream, const void* d, const void* bits, uint32
                                    static_cast<const __half*>(gate), static_cast<const __half*>(up), static_cast<__half*>(y), accumulate != 0));
 }
 void bp_op_set_matvec_rows(uint32_t rows_per_lane) {
-  bp_q1_set_matvec_rows(rows_per_lane == 1 || rows_per_lane == 2 || rows_per_lane == 4 ? rows_per_lane : 0);
+  const uint32_t r = rows_per_lane & 7u;
+  bp_q1_set_matvec_rows(rows_per_lane < 16 && (r == 0 || r == 1 || r == 2 || r == 4) ? rows_per_lane : 0);
 }
 int bp_op_rms_norm(void* stream, const void* in, void* out, const void* w, uint32_t group_size, uint32_t n_groups, float eps) {
   if (!in || !out || !w) return BP_ERR_NULL;

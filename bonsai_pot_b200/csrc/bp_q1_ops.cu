@@ -100,7 +100,10 @@ struct MvParams {
 // silu(f16(gate_i)) * f16(up_i), what the two dispatches of the reference leave in the buffer that feeds
 // the down projection.
 constexpr uint32_t MV_PF = 4;  // blocks of a lane in flight
-template <int MODE, uint32_t MV_ROWS_PER_LANE>
+// KB != 0: an instance for tensors of exactly 1024 KB inputs (KB blocks per lane: 4 and 12 at the 8B shape). With
+// the block count a constant the loop bounds, the reload conditions and most of the address arithmetic of the
+// general code fold away (about a tenth of the instructions of a call).
+template <int MODE, uint32_t MV_ROWS_PER_LANE, uint32_t KB = 0>
 __global__ void __launch_bounds__(MV_THREADS) matvec_q1_kernel(const MvParams p) {
   static_assert(MODE != 3 || MV_ROWS_PER_LANE == 2, "the paired mode computes one row of each of two tensors per lane");
   constexpr uint32_t MV_ROWS_PER_CTA = (MV_THREADS / 8) * (MODE == 3 ? 1 : MV_ROWS_PER_LANE);
@@ -108,7 +111,8 @@ __global__ void __launch_bounds__(MV_THREADS) matvec_q1_kernel(const MvParams p)
   __shared__ float part[32];
   __half* xs = reinterpret_cast<__half*>(mv_smem);
   pdl_launch_dependents();
-  const uint32_t tid = threadIdx.x, nb = p.k / 128u;
+  const uint32_t k_in = KB != 0 ? 1024u * KB : p.k;
+  const uint32_t tid = threadIdx.x, nb = k_in / 128u;
   // ---- rows: lane = (row slot rs = lane / 8, tx = lane % 8); a lane owns rows base + rs + 4 j ----
   const uint32_t warp = tid >> 5, lane = tid & 31, tx = lane & 7, rs = lane >> 3;
   const uint32_t row0 = blockIdx.x * MV_ROWS_PER_CTA + warp * (4 * (MODE == 3 ? 1 : MV_ROWS_PER_LANE)) + rs;
@@ -172,12 +176,12 @@ __global__ void __launch_bounds__(MV_THREADS) matvec_q1_kernel(const MvParams p)
   if (MODE == 1 || MODE == 3) {
     float ssq = 0.0f;
     constexpr uint32_t SB = 8;  // 4-element units of a thread per batch
-    for (uint32_t v0 = tid; v0 < p.k / 4u; v0 += MV_THREADS * SB) {
+    for (uint32_t v0 = tid; v0 < k_in / 4u; v0 += MV_THREADS * SB) {
       uint2 raw_q[SB], wr_q[SB];
 #pragma unroll
       for (uint32_t u = 0; u < SB; u++) {
         const uint32_t v = v0 + u * MV_THREADS;
-        if (v < p.k / 4u) {
+        if (v < k_in / 4u) {
           raw_q[u] = *reinterpret_cast<const uint2*>(p.x + 4u * v);
           wr_q[u] = __ldg(reinterpret_cast<const uint2*>(p.aux + 4u * v));
         }
@@ -185,7 +189,7 @@ __global__ void __launch_bounds__(MV_THREADS) matvec_q1_kernel(const MvParams p)
 #pragma unroll
       for (uint32_t u = 0; u < SB; u++) {
         const uint32_t v = v0 + u * MV_THREADS;
-        if (v >= p.k / 4u) break;
+        if (v >= k_in / 4u) break;
         const uint2 raw = raw_q[u], wr = wr_q[u];
         const __half2 x01 = *reinterpret_cast<const __half2*>(&raw.x), x23 = *reinterpret_cast<const __half2*>(&raw.y);
         const float2 f01 = __half22float2(x01), f23 = __half22float2(x23);
@@ -202,25 +206,25 @@ __global__ void __launch_bounds__(MV_THREADS) matvec_q1_kernel(const MvParams p)
       }
     }
     const float total = workgroup_sum<MV_THREADS / 32>(ssq, part);
-    inv_rms = __frsqrt_rn(__fadd_rn(__fdiv_rn(total, static_cast<float>(p.k)), p.eps));
+    inv_rms = __frsqrt_rn(__fadd_rn(__fdiv_rn(total, static_cast<float>(k_in)), p.eps));
   } else if (MODE == 0) {
     constexpr uint32_t SB = 6;  // 8-element units of a thread per batch
-    for (uint32_t v0 = tid; v0 < p.k / 8u; v0 += MV_THREADS * SB) {
+    for (uint32_t v0 = tid; v0 < k_in / 8u; v0 += MV_THREADS * SB) {
       uint4 raw_q[SB];
 #pragma unroll
       for (uint32_t u = 0; u < SB; u++) {
         const uint32_t v = v0 + u * MV_THREADS;
-        if (v < p.k / 8u) raw_q[u] = *reinterpret_cast<const uint4*>(p.x + 8u * v);
+        if (v < k_in / 8u) raw_q[u] = *reinterpret_cast<const uint4*>(p.x + 8u * v);
       }
 #pragma unroll
       for (uint32_t u = 0; u < SB; u++) {
         const uint32_t v = v0 + u * MV_THREADS;
-        if (v < p.k / 8u) *reinterpret_cast<uint4*>(xs + (v >> 4) * XB_STRIDE + 8u * (v & 15u)) = raw_q[u];
+        if (v < k_in / 8u) *reinterpret_cast<uint4*>(xs + (v >> 4) * XB_STRIDE + 8u * (v & 15u)) = raw_q[u];
       }
     }
     __syncthreads();
   } else {
-    for (uint32_t v = tid; v < p.k / 4u; v += MV_THREADS) {
+    for (uint32_t v = tid; v < k_in / 4u; v += MV_THREADS) {
       uint2 o = *reinterpret_cast<const uint2*>(p.x + 4u * v);
       const uint2 u = *reinterpret_cast<const uint2*>(p.aux + 4u * v);
       const __half* g4 = reinterpret_cast<const __half*>(&o);
@@ -1048,21 +1052,22 @@ __global__ void __launch_bounds__(256) relayout_kernel(const uint8_t* qs, uint4*
 
 size_t mv_smem_bytes(uint32_t k) { return static_cast<size_t>(k / 128u) * XB_STRIDE * sizeof(__half); }
 
-template <int MODE, uint32_t R>
+template <int MODE, uint32_t R, uint32_t KB = 0>
 cudaError_t launch_mv_r(bool pdl, cudaStream_t s, const MvParams& p) {
   const size_t smem = mv_smem_bytes(p.k);
   static size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(matvec_q1_kernel<MODE, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    cudaError_t e = cudaFuncSetAttribute(matvec_q1_kernel<MODE, R, KB>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return e;
     configured = smem;
   }
   const uint32_t rows_per_cta = (MV_THREADS / 8) * R;
   const uint32_t ctas = (p.n_total + rows_per_cta - 1) / rows_per_cta;
-  return bp_launch(pdl, matvec_q1_kernel<MODE, R>, dim3(ctas), dim3(MV_THREADS), smem, s, p);
+  return bp_launch(pdl, matvec_q1_kernel<MODE, R, KB>, dim3(ctas), dim3(MV_THREADS), smem, s, p);
 }
 
 uint32_t g_mv_rows_override = 0;  // tuning aid (bp_op_set_matvec_rows): 0 = by tensor height
+bool g_mv_const_k = true;         // tuning aid: use the constant-block-count instances where one exists
 
 template <int MODE>
 cudaError_t launch_mv(bool pdl, cudaStream_t s, const MvParams& p) {
@@ -1071,13 +1076,19 @@ cudaError_t launch_mv(bool pdl, cudaStream_t s, const MvParams& p) {
   // 24576 rows 12.9 / 10.6 / 10.9, 151936 rows 50 / 45 / 54
   if (r == 0) r = p.n_total >= 16384 ? 2 : 1;
   if (r >= 4) return launch_mv_r<MODE, 4>(pdl, s, p);
+  // the instances with a constant block count: the tensors of a one-token step at the 8B shape
+  // (measured: the two-rows-per-lane instances gain, LM head 47 -> 43 us; the one-row ones do not: Wo 3.7 -> 4.4 us)
+  if (g_mv_const_k && MODE == 0 && r == 2 && p.k == 4096) return launch_mv_r<0, 2, 4>(pdl, s, p);
   if (r == 2) return launch_mv_r<MODE, 2>(pdl, s, p);
   return launch_mv_r<MODE, 1>(pdl, s, p);
 }
 
 }  // namespace
 
-void bp_q1_set_matvec_rows(uint32_t rows_per_lane) { g_mv_rows_override = rows_per_lane; }
+void bp_q1_set_matvec_rows(uint32_t rows_per_lane) {
+  g_mv_rows_override = rows_per_lane & 7u;
+  g_mv_const_k = (rows_per_lane & 8u) == 0;  // + 8: the general instances only
+}
 
 cudaError_t bp_q1_relayout(cudaStream_t s, const uint8_t* qs, void* out, uint64_t n_blocks) {
   relayout_kernel<<<static_cast<unsigned>((n_blocks + 255) / 256), 256, 0, s>>>(qs, static_cast<uint4*>(out), n_blocks);
@@ -1135,7 +1146,9 @@ cudaError_t bp_q1_matvec_normed_silu(bool pdl, cudaStream_t s, const bp_q1_tenso
     configured = smem;
   }
   const uint32_t rows_per_cta = MV_THREADS / 8;
-  return bp_launch(pdl, matvec_q1_kernel<3, 2>, dim3((p.n_total + rows_per_cta - 1) / rows_per_cta), dim3(MV_THREADS), smem, s, p);
+  const dim3 grid((p.n_total + rows_per_cta - 1) / rows_per_cta);
+  if (g_mv_const_k && p.k == 4096) return bp_launch(pdl, matvec_q1_kernel<3, 2, 4>, grid, dim3(MV_THREADS), smem, s, p);
+  return bp_launch(pdl, matvec_q1_kernel<3, 2>, grid, dim3(MV_THREADS), smem, s, p);
 }
 
 cudaError_t bp_q1_matvec_silu(bool pdl, cudaStream_t s, const bp_q1_tensor& w, const __half* gate, const __half* up, __half* y,

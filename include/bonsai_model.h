@@ -39,7 +39,8 @@ int bp_op_matvec_q1_0_fused_normed(void* stream, uint32_t k, const void* x, cons
 int bp_op_matvec_q1_0_silu(void* stream, const void* d, const void* bits, uint32_t k, uint32_t n, const void* gate, const void* up,
                            void* y, uint32_t accumulate);
 /* Tuning aid of the three matvec kernels: rows a lane works on at once, 1, 2 or 4 (0 = chosen by the
- * tensor's height, the default). Results do not depend on it. Process-wide. */
+ * tensor's height, the default); + 8 = only the general kernel instances (tensors of 4096 and 12288 inputs
+ * otherwise run instances compiled for that width). Results do not depend on it. Process-wide. */
 void bp_op_set_matvec_rows(uint32_t rows_per_lane);
 /* dispatch_rms_norm (src/forward.rs:188-210, rms_norm.wgsl); in == out allowed */
 int bp_op_rms_norm(void* stream, const void* in, void* out, const void* w, uint32_t group_size, uint32_t n_groups, float eps);

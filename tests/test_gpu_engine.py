@@ -50,7 +50,7 @@ def test_matvec_q1_0_bit_exact(k, n, accumulate):
     xd = dev(x)  # named: a temporary's memory may be handed to the next allocation
     lib = _lib.load()
     try:
-        for rows in (0, 1, 2, 4):  # every kernel layout: by height, rows per lane
+        for rows in (0, 1, 2, 4, 8, 9, 10):  # every kernel layout: by height, rows per lane; + 8 = the general instances only
             lib.bp_op_set_matvec_rows(rows)
             y = dev(y0.copy())
             assert lib.bp_op_matvec_q1_0(None, d_dev.data_ptr(), bits.data_ptr(), k, n, xd.data_ptr(), y.data_ptr(), int(accumulate)) == 0
@@ -77,7 +77,7 @@ def test_matvec_fused_normed_bit_exact(k, ns):
     xd, wd = dev(x), dev(w_norm)
     lib = _lib.load()
     try:
-        for rows in (0, 1, 2, 4):
+        for rows in (0, 1, 2, 4, 8, 9, 10):
             lib.bp_op_set_matvec_rows(rows)
             outs = [torch.zeros(n, dtype=torch.float16, device="cuda") for n in ns]
             st = lib.bp_op_matvec_q1_0_fused_normed(None, k, xd.data_ptr(), wd.data_ptr(), 1e-6, nr,
