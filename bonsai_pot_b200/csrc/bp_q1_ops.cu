@@ -1078,7 +1078,7 @@ cudaError_t launch_mv(bool pdl, cudaStream_t s, const MvParams& p) {
   if (r >= 4) return launch_mv_r<MODE, 4>(pdl, s, p);
   // the instances with a constant block count: the tensors of a one-token step at the 8B shape
   // (measured: the two-rows-per-lane instances gain, LM head 47 -> 43 us; the one-row ones do not: Wo 3.7 -> 4.4 us)
-  if (g_mv_const_k && MODE == 0 && r == 2 && p.k == 4096) return launch_mv_r<0, 2, 4>(pdl, s, p);
+  if (g_mv_const_k && (MODE == 0 || MODE == 1) && r == 2 && p.k == 4096) return launch_mv_r<MODE, 2, 4>(pdl, s, p);
   if (r == 2) return launch_mv_r<MODE, 2>(pdl, s, p);
   return launch_mv_r<MODE, 1>(pdl, s, p);
 }
