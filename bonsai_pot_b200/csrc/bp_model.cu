@@ -457,11 +457,11 @@ int capture_step_graph(bp_model* m, uint32_t pos) {
   M_CUDA(m, cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
   int st = BP_OK;
   cudaError_t e = cudaMemcpyAsync(m->tokens_dev, m->token_pin, sizeof(uint32_t), cudaMemcpyHostToDevice, s);
-  if (e == cudaSuccess) e = bp_q1_embed(false, s, m->embed, m->tokens_dev, 1, m->x);
+  if (e == cudaSuccess) e = bp_q1_embed(true, s, m->embed, m->tokens_dev, 1, m->x);
   for (uint32_t il = 0; e == cudaSuccess && st == BP_OK && il < c.n_layer; il++) st = decode_layer(m, il, pos, true, &m->sg.attn[il]);
-  if (e == cudaSuccess && st == BP_OK) e = bp_q1_rms_norm(false, s, m->x, m->x, m->output_norm, c.n_embd, 1, c.rms_eps);
-  if (e == cudaSuccess && st == BP_OK) e = bp_q1_matvec(false, s, m->lm_head, m->x, m->logits, false);
-  if (e == cudaSuccess && st == BP_OK) e = bp_q1_topk(false, s, m->logits, c.n_vocab, TOPK_MAX, m->topk_val, m->topk_idx);
+  if (e == cudaSuccess && st == BP_OK) e = bp_q1_rms_norm(true, s, m->x, m->x, m->output_norm, c.n_embd, 1, c.rms_eps);
+  if (e == cudaSuccess && st == BP_OK) e = bp_q1_matvec(true, s, m->lm_head, m->x, m->logits, false);
+  if (e == cudaSuccess && st == BP_OK) e = bp_q1_topk(true, s, m->logits, c.n_vocab, TOPK_MAX, m->topk_val, m->topk_idx);
   if (e == cudaSuccess && st == BP_OK) e = cudaMemcpyAsync(m->res_val_pin, m->topk_val, TOPK_MAX * sizeof(float), cudaMemcpyDeviceToHost, s);
   if (e == cudaSuccess && st == BP_OK) e = cudaMemcpyAsync(m->res_idx_pin, m->topk_idx, TOPK_MAX * sizeof(uint32_t), cudaMemcpyDeviceToHost, s);
   const cudaError_t e_end = cudaStreamEndCapture(s, &m->sg.graph);  // always: the stream must leave capture mode
