@@ -892,7 +892,12 @@ static_assert(TK_THREADS >= TK_WG, "the merge rounds of the first CTA run on the
 struct __align__(8) TkEntry { float v; uint32_t i; };
 constexpr size_t TK_SMEM = (TK_WG * TK_ROW + TK_K * TK_LISTS) * sizeof(TkEntry) + TK_CHUNK * TK_LISTS * sizeof(__half2);
 // heap[0] of list j is being replaced by e: walk down while a child is smaller (topk_reduce.wgsl:35-50).
-// Both children are read at once (the right one only counts when it exists); returns the value left at the root.
+// The shader compares e with the left child, then the smaller of the two with the right child: it moves to the
+// smaller child (the left one on a tie) if that child is below e, and stops otherwise. Which child is the smaller
+// one does not depend on e, so the walk is written that way round: the chain from one level to the next is
+// load, compare the children, select, and the comparison with e only decides where the walk ends (half the
+// dependent instructions per level of the shader's order; the same moves, hence the same array).
+// Returns the value left at the root.
 __device__ __forceinline__ float tk_sift_hole(TkEntry* heap, uint32_t j, uint32_t limit, TkEntry e) {
   uint32_t i = 0;
   float root = e.v;
@@ -901,17 +906,58 @@ __device__ __forceinline__ float tk_sift_hole(TkEntry* heap, uint32_t j, uint32_
     if (l >= limit) break;
     const TkEntry cl = heap[l * TK_LISTS + j];
     const TkEntry cr = heap[(r < limit ? r : l) * TK_LISTS + j];
-    uint32_t smallest = i;
-    float sv = e.v;
-    TkEntry cs = e;
-    if (cl.v < sv) { smallest = l; sv = cl.v; cs = cl; }
-    if (r < limit && cr.v < sv) { smallest = r; cs = cr; }
-    if (smallest == i) break;
-    heap[i * TK_LISTS + j] = cs;
-    if (i == 0) root = cs.v;
-    i = smallest;
+    const bool right = r < limit && cr.v < cl.v;
+    const TkEntry m = right ? cr : cl;
+    if (!(m.v < e.v)) break;
+    heap[i * TK_LISTS + j] = m;
+    if (i == 0) root = m.v;
+    i = right ? r : l;
   }
   heap[i * TK_LISTS + j] = e;
+  return root;
+}
+// The same walk on a FULL heap of TK_K = 32 entries (every insertion of the scan): the levels are unrolled, no
+// slot has to be checked against a limit above the last level (only slot 15 has a child there, slot 31), and
+// the four grandchildren of a node (slots 4 i + 3 .. 4 i + 6) are requested before its children are compared:
+// a level of the walk is then compare, select, compare instead of address, load, compare, select, compare.
+__device__ __forceinline__ float tk_sift_full(TkEntry* heap, uint32_t j, TkEntry e) {
+  static_assert(TK_K == 32, "levels and slots below are those of a heap of 32");
+  TkEntry* E = heap + j;
+  uint32_t i = 0;
+  float root = e.v;
+  TkEntry cl = E[1 * TK_LISTS], cr = E[2 * TK_LISTS];
+#pragma unroll
+  for (uint32_t lvl = 0; lvl < 4; lvl++) {
+    TkEntry g0 = {}, g1 = {}, g2 = {}, g3 = {};
+    if (lvl < 3) {
+      const TkEntry* G = E + (4 * i + 3) * TK_LISTS;
+      g0 = G[0];
+      g1 = G[TK_LISTS];
+      g2 = G[2 * TK_LISTS];
+      g3 = G[3 * TK_LISTS];
+    }
+    const bool right = cr.v < cl.v;
+    const TkEntry m = right ? cr : cl;
+    if (!(m.v < e.v)) {
+      E[i * TK_LISTS] = e;
+      return root;
+    }
+    E[i * TK_LISTS] = m;
+    if (lvl == 0) root = m.v;
+    i = 2 * i + 1 + (right ? 1u : 0u);
+    if (lvl < 3) {
+      cl = right ? g2 : g0;
+      cr = right ? g3 : g1;
+    }
+  }
+  if (i == 15) {  // the one slot of the fourth level with a child
+    const TkEntry c = E[31 * TK_LISTS];
+    if (c.v < e.v) {
+      E[15 * TK_LISTS] = c;
+      i = 31;
+    }
+  }
+  E[i * TK_LISTS] = e;
   return root;
 }
 __device__ __forceinline__ void tk_merge_sync() { asm volatile("bar.sync 1, %0;" ::"n"(TK_WG) : "memory"); }  // the merging threads only
@@ -987,7 +1033,7 @@ __global__ void __cluster_dims__(TK_CTAS, 1, 1) __launch_bounds__(TK_THREADS)
       }
       if (!__any_sync(FULL, have)) break;
       if (have) {
-        cur_min = tk_sift_hole(heap, jl, TK_K, TkEntry{v, idx});
+        cur_min = tk_sift_full(heap, jl, TkEntry{v, idx});
       }
     }
   }
