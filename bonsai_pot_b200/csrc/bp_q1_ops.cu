@@ -479,14 +479,16 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
                : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
 }
+// d = a b + Q1_I2F_BIAS: the accumulator starts at the bit pattern of 1.5 * 2^23, so that the exact integer dot
+// comes out as bits of the float 12582912 + dot, one subtraction away from float(dot) (exact for |dot| < 2^22;
+// a sub-block's is below 2^12) with no conversion and no integer addition on the CUDA cores.
+constexpr int Q1_I2F_BIAS = 0x4B400000;
 __device__ __forceinline__ void mma_s8_s32(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
                : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
-               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0));
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(Q1_I2F_BIAS));
 }
-__device__ __forceinline__ float q1_s32_to_f32(int x) {  // exact for |x| < 2^22
-  return __int_as_float(x + 0x4B400000) - 12582912.0f;
-}
+__device__ __forceinline__ float q1_biased_s32_to_f32(int x) { return __int_as_float(x) - 12582912.0f; }
 // four int8 -> four f16, exactly: bias to unsigned, 0x6400 | byte = 1024 + byte, minus 1152
 __device__ __forceinline__ uint2 s8x4_to_f16x4(uint32_t x) {
   x ^= 0x80808080u;
@@ -626,10 +628,10 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) matmul_q1_q8_mma_kernel(const 
         for (uint32_t nt = 0; nt < 4; nt++) {
           int d[4];
           mma_s8_s32(d, af, bf[nt][0], bf[nt][1]);
-          acc[mt][nt][0] = __fadd_rn(acc[mt][nt][0], __fmul_rn(__fmul_rn(ad_lo, wdv[nt][0]), q1_s32_to_f32(d[0])));
-          acc[mt][nt][1] = __fadd_rn(acc[mt][nt][1], __fmul_rn(__fmul_rn(ad_lo, wdv[nt][1]), q1_s32_to_f32(d[1])));
-          acc[mt][nt][2] = __fadd_rn(acc[mt][nt][2], __fmul_rn(__fmul_rn(ad_hi, wdv[nt][0]), q1_s32_to_f32(d[2])));
-          acc[mt][nt][3] = __fadd_rn(acc[mt][nt][3], __fmul_rn(__fmul_rn(ad_hi, wdv[nt][1]), q1_s32_to_f32(d[3])));
+          acc[mt][nt][0] = __fadd_rn(acc[mt][nt][0], __fmul_rn(__fmul_rn(ad_lo, wdv[nt][0]), q1_biased_s32_to_f32(d[0])));
+          acc[mt][nt][1] = __fadd_rn(acc[mt][nt][1], __fmul_rn(__fmul_rn(ad_lo, wdv[nt][1]), q1_biased_s32_to_f32(d[1])));
+          acc[mt][nt][2] = __fadd_rn(acc[mt][nt][2], __fmul_rn(__fmul_rn(ad_hi, wdv[nt][0]), q1_biased_s32_to_f32(d[2])));
+          acc[mt][nt][3] = __fadd_rn(acc[mt][nt][3], __fmul_rn(__fmul_rn(ad_hi, wdv[nt][1]), q1_biased_s32_to_f32(d[3])));
         }
       }
     }
