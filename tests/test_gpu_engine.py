@@ -228,11 +228,14 @@ def test_one_token_pass_matches_the_cpu_pass_bit_for_bit(tmp_path, shape):
                 assert np.array_equal(qq, hm.sh.qs_section(kv, il)[:4])
 
 
-def test_graph_steps_are_identical_to_stream_steps(tmp_path):
+@pytest.mark.parametrize("exclusive_device", [1, 0])
+def test_graph_steps_are_identical_to_stream_steps(tmp_path, exclusive_device):
     """The one-token step as one CUDA graph launch (attention nodes patched per position, the step captured
     again when the attention launch changes shape) against the same step as stream launches: same kernels and
     arguments, so hidden state, logits and top-k must be identical bit for bit, over positions that cross
-    several 128-token stages of the decode kernel and after a reset to position 0."""
+    several 128-token stages of the decode kernel and after a reset to position 0. With exclusive_device = 0 an
+    attention call is two launches from three stages on (the splits are merged by a second kernel): the graph
+    then holds two patched nodes per layer and is captured again where the count changes."""
     d = str(tmp_path / "m")
     model_dir.write_synthetic_model(d, seed=5)
     n = 300
@@ -242,6 +245,7 @@ def test_graph_steps_are_identical_to_stream_steps(tmp_path):
     for graph in (True, False):
         with bp.Model(d, max_seq=512) as gm:
             gm.set_step_graph(graph)
+            gm.attention().set_option("exclusive_device", exclusive_device)
             rows = []
             for pos in list(range(n)) + [0, 1, 2]:
                 lg, ix = gm.step_topk(int(toks[pos]), pos, k=32 if pos % 3 else 5)
