@@ -6,6 +6,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <string.h>
 
 #include <vector>
 
@@ -106,12 +107,19 @@ __host__ __device__ inline uint64_t bp_qs_off(const bp_attn_ctx* c, uint32_t il)
 // A launch as data: what a kernel node of a CUDA graph holds. A caller that keeps a captured step in a graph
 // re-derives the launches whose arguments change from one execution to the next (the position of an attention
 // call) through the ordinary launcher functions and patches the nodes with what they produced.
+constexpr uint32_t BP_RECORD_MAX_ARGS = 12, BP_RECORD_ARG_BYTES = 1536;
 struct bp_launch_record {
   void* func = nullptr;
   dim3 grid, block;
   size_t smem = 0;
-  std::vector<std::vector<uint8_t>> args;  // the kernel arguments, one copy each, in order
+  // the kernel arguments, one copy each, in order, in storage of the record's own (a token's 36 launches are
+  // recorded before every token: no allocation on that path)
+  uint32_t n_args = 0, used = 0;
+  uint32_t arg_off[BP_RECORD_MAX_ARGS] = {};
+  bool overflow = false;                   // an argument did not fit: the record cannot be replayed
   cudaGraphNode_t node = nullptr;          // mode 2: the node the launch became in the stream's capture
+  alignas(64) uint8_t arg_bytes[BP_RECORD_ARG_BYTES];
+  void* arg(uint32_t i) { return arg_bytes + arg_off[i]; }
 };
 // While a recorder is installed on the calling thread every bp_launch goes through it: mode 1 stores the launch
 // and launches NOTHING, mode 2 launches and stores the launch with its graph node (the stream must be capturing).
@@ -123,8 +131,14 @@ bp_launch_recorder*& bp_recorder();  // this thread's recorder, or null
 
 template <typename T>
 inline void bp_record_arg(bp_launch_record& r, const T& v) {
-  const uint8_t* b = reinterpret_cast<const uint8_t*>(&v);
-  r.args.emplace_back(b, b + sizeof(T));
+  const uint32_t off = (r.used + static_cast<uint32_t>(alignof(T)) - 1u) & ~(static_cast<uint32_t>(alignof(T)) - 1u);
+  if (r.n_args >= BP_RECORD_MAX_ARGS || off + sizeof(T) > BP_RECORD_ARG_BYTES) {
+    r.overflow = true;
+    return;
+  }
+  memcpy(r.arg_bytes + off, &v, sizeof(T));
+  r.arg_off[r.n_args++] = off;
+  r.used = off + static_cast<uint32_t>(sizeof(T));
 }
 
 // Launches `kernel`; with `pdl` the launch carries programmatic stream serialization, so that the

@@ -337,6 +337,7 @@ struct bp_token_graph {
   cudaGraph_t graph = nullptr;
   cudaGraphExec_t exec = nullptr;
   std::vector<bp_launch_record> launches;  // as captured, with their nodes
+  bp_launch_recorder patch;                // the recorder of the per-token pass (its storage is reused)
 };
 static void drop_token_graph(bp_attn_ctx* c) {
   if (!c->tok_graph) return;
@@ -620,8 +621,9 @@ static int token_graph_launch(bp_attn_ctx* c, cudaStream_t st, uint32_t pos, uin
   const uint32_t nl = c->cfg.n_layer;
   bool patched = false;
   if (c->tok_graph) {
-    bp_launch_recorder rec;
+    bp_launch_recorder& rec = c->tok_graph->patch;
     rec.mode = 1;
+    rec.records.clear();
     bp_recorder() = &rec;
     cudaError_t e = cudaSuccess;
     for (uint32_t il = 0; il < nl && e == cudaSuccess; il++) e = token_layer_call(c, st, il, pos, launches);
@@ -635,9 +637,9 @@ static int token_graph_launch(bp_attn_ctx* c, cudaStream_t st, uint32_t pos, uin
         patched = false;
         break;
       }
-      void* argv[16];
-      if (r.args.size() > 16) return fail(c, BP_ERR_CUDA, "a decode launch has more arguments than the token graph patches");
-      for (size_t a = 0; a < r.args.size(); a++) argv[a] = r.args[a].data();
+      void* argv[BP_RECORD_MAX_ARGS];
+      if (r.overflow) return fail(c, BP_ERR_CUDA, "a decode launch has more arguments than a launch record holds");
+      for (uint32_t a = 0; a < r.n_args; a++) argv[a] = r.arg(a);
       cudaKernelNodeParams kp = {};
       kp.func = r.func;
       kp.gridDim = r.grid;

@@ -285,6 +285,7 @@ struct bp_model {
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
     std::vector<std::vector<bp_launch_record>> attn;  // per layer: the attention launches as captured
+    bp_launch_recorder patch;                         // the recorder of the per-step pass
     bool valid = false;
   } sg;
   bool step_graph = true;     // bp_model_set_step_graph
@@ -478,8 +479,9 @@ int capture_step_graph(bp_model* m, uint32_t pos) {
 int patch_step_graph(bp_model* m, uint32_t pos, bool* ok) {
   *ok = false;
   for (uint32_t il = 0; il < m->cfg.n_layer; il++) {
-    bp_launch_recorder rec;
+    bp_launch_recorder& rec = m->sg.patch;  // its storage is reused from step to step
     rec.mode = 1;
+    rec.records.clear();
     bp_recorder() = &rec;
     const cudaError_t e = attention_call(m, il, pos);
     bp_recorder() = nullptr;
@@ -489,14 +491,15 @@ int patch_step_graph(bp_model* m, uint32_t pos, bool* ok) {
     for (size_t i = 0; i < was.size(); i++) {
       bp_launch_record& r = rec.records[i];
       if (r.func != was[i].func) return BP_OK;
-      std::vector<void*> argv(r.args.size());
-      for (size_t a = 0; a < r.args.size(); a++) argv[a] = r.args[a].data();
+      void* argv[BP_RECORD_MAX_ARGS];
+      if (r.overflow) return mfail(m, BP_ERR_CUDA, "an attention launch has more arguments than a launch record holds");
+      for (uint32_t a = 0; a < r.n_args; a++) argv[a] = r.arg(a);
       cudaKernelNodeParams kp = {};
       kp.func = r.func;
       kp.gridDim = r.grid;
       kp.blockDim = r.block;
       kp.sharedMemBytes = static_cast<unsigned int>(r.smem);
-      kp.kernelParams = argv.data();
+      kp.kernelParams = argv;
       M_CUDA(m, cudaGraphExecKernelNodeSetParams(m->sg.exec, was[i].node, &kp));
     }
   }
