@@ -314,9 +314,9 @@ __device__ __forceinline__ void merge_part(const UmmaParams& p, uint32_t lane, u
 // Hence this pairing.
 template <uint32_t HPC, uint32_t MODE>
 __global__ void __launch_bounds__(U_THREADS, 1)
-decode_umma_kernel(const __grid_constant__ CUtensorMap map_kq, const __grid_constant__ CUtensorMap map_kd,
-                   const __grid_constant__ CUtensorMap map_vq, const __grid_constant__ CUtensorMap map_vd,
-                   const __grid_constant__ UmmaParams p) {
+decode_umma_kernel(const CUtensorMap* __restrict__ maps, const __grid_constant__ UmmaParams p) {
+  // tensor maps in device memory (written by the host before any launch that reads them): K quants, K scales, V quants, V scales
+  const CUtensorMap &map_kq = maps[0], &map_kd = maps[1], &map_vq = maps[2], &map_vd = maps[3];
   using L = ULayout<HPC>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[U_MAX_STAGES], k_empty[U_MAX_STAGES], v_full[U_MAX_STAGES], v_empty[U_MAX_STAGES];
@@ -1027,10 +1027,8 @@ static cudaError_t launch_umma(bp_attn_ctx* c, cudaStream_t s, UmmaParams& p, ui
   // Short launches (up to 16 splits of up to 4 stages) are merged by one CTA per head group, longer
   // ones by all CTAs of the group.
   if (n_splits <= 16 && spp <= 4)
-    return bp_launch(c->opt_pdl != 0, decode_umma_kernel<HPC, 3>, grid, dim3(U_THREADS), smem, s, c->umap_qs[0], c->umap_d[0],
-                     c->umap_qs[1], c->umap_d[1], p);
-  return bp_launch(c->opt_pdl != 0, decode_umma_kernel<HPC, 1>, grid, dim3(U_THREADS), smem, s, c->umap_qs[0], c->umap_d[0],
-                   c->umap_qs[1], c->umap_d[1], p);
+    return bp_launch(c->opt_pdl != 0, decode_umma_kernel<HPC, 3>, grid, dim3(U_THREADS), smem, s, c->umaps_dev, p);
+  return bp_launch(c->opt_pdl != 0, decode_umma_kernel<HPC, 1>, grid, dim3(U_THREADS), smem, s, c->umaps_dev, p);
 }
 
 cudaError_t bp_launch_decode_umma(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, const __half* q, __half* out,

@@ -192,7 +192,9 @@ __global__ void __launch_bounds__(256) prefill_expand_kernel(const uint8_t* __re
 
 template <uint32_t NQ, uint32_t CPS, bool PX>  // PX: with the peer exchange in the epilogue (an instance of its own: the plain one pays nothing)
 __global__ void __launch_bounds__(PLayout<NQ, CPS>::THREADS, CPS)
-prefill_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const PrefillParams p) {
+prefill_umma_kernel(const CUtensorMap* __restrict__ maps, const PrefillParams p) {
+  // tensor maps in device memory, written once by the host when the context is created: K rows, V rows
+  const CUtensorMap &map_k = maps[0], &map_v = maps[1];
   using L = PLayout<NQ, CPS>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t k_full[L::KV_SLOTS], v_full[L::KV_SLOTS];
@@ -602,6 +604,12 @@ cudaError_t bp_prefill_init(bp_attn_ctx* c) {
                            es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
   }
+  if (c->have_pmaps) {  // the kernel reads the maps from device memory (a smaller parameter block: these kernels feel its size)
+    e = cudaMalloc(&c->pmaps_dev, 2 * sizeof(CUtensorMap));
+    if (e != cudaSuccess) return e;
+    e = cudaMemcpy(c->pmaps_dev, c->pmap16, 2 * sizeof(CUtensorMap), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) return e;
+  }
   auto allow = [](auto kernel, uint32_t bytes) {
     return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
   };
@@ -658,7 +666,7 @@ cudaError_t bp_launch_prefill(bp_attn_ctx* c, cudaStream_t s, uint32_t layer, co
     const uint32_t n_items = p.n_groups * c->cfg.n_kv_head, slots = sms * cps, grid = n_items < slots ? n_items : slots;
     *launches += 1;
     bp_note_sm_launch(c, grid < sms ? grid : sms);
-    return bp_launch(c->opt_pdl != 0, kernel, dim3(grid), dim3(threads), smem, s, c->pmap16[0], c->pmap16[1], p);
+    return bp_launch(c->opt_pdl != 0, kernel, dim3(grid), dim3(threads), smem, s, c->pmaps_dev, p);
   };
   const bool px = p.n_px != 0;
   if (c->opt_pf_nq == 2)

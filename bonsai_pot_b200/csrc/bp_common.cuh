@@ -39,6 +39,7 @@ struct bp_attn_ctx {
   bool have_maps;
   CUtensorMap umap_qs[2];  // tcgen05 decode: 128-token boxes
   CUtensorMap umap_d[2];
+  CUtensorMap* umaps_dev;  // device copy of {umap_qs[0], umap_d[0], umap_qs[1], umap_d[1]}: the decode kernel takes the address
   bool have_umaps;
   // tcgen05 prefill: f16 expansion of the batch's cache rows [K | V][pf_rows][kv_dim], its
   // tensor maps (128-key boxes of one head) and the work-item counter behind it
@@ -46,6 +47,7 @@ struct bp_attn_ctx {
   uint32_t pf_rows;
   uint32_t* pf_counter;
   CUtensorMap pmap16[2];
+  CUtensorMap* pmaps_dev;  // device copy of pmap16[0..1]: the prefill kernel takes the address
   bool have_pmaps;
   // staging for the *_host entry points
   __half *stage_q, *stage_k, *stage_v, *stage_out, *stage_wq, *stage_wk;

@@ -198,6 +198,15 @@ static bool rebuild_decode_maps(bp_attn_ctx* c) {
   for (int kind = 0; kind < 2 && c->have_umaps; kind++)
     c->have_umaps = bp_make_kv_maps(c, kind, bp_decode_umma_stage_tokens(), 16 * c->opt_uhpc, false,
                                     &c->umap_qs[kind], &c->umap_d[kind]);
+  if (c->have_umaps) {
+    // The tcgen05 decode kernel reads its tensor maps from device memory: as kernel parameters they were 512
+    // of its 900 parameter bytes, and these kernels get slower with the size of their parameter block.
+    if (!c->umaps_dev && cudaMalloc(&c->umaps_dev, 4 * sizeof(CUtensorMap)) != cudaSuccess) c->have_umaps = false;
+    const CUtensorMap host[4] = {c->umap_qs[0], c->umap_d[0], c->umap_qs[1], c->umap_d[1]};
+    // synchronous, and after a device-wide synchronize: no launch that reads the old maps is in flight
+    if (c->have_umaps && (cudaDeviceSynchronize() != cudaSuccess || cudaMemcpy(c->umaps_dev, host, sizeof host, cudaMemcpyHostToDevice) != cudaSuccess))
+      c->have_umaps = false;
+  }
   return c->have_maps;
 }
 
@@ -356,6 +365,8 @@ void bp_attn_destroy(bp_attn_ctx* c) {
   cudaFree(c->partials);
   cudaFree(c->ppx_dev);
   cudaFree(c->px_dev);
+  cudaFree(c->umaps_dev);
+  cudaFree(c->pmaps_dev);
   cudaFree(c->ll);
   cudaFree(c->epochs);
   cudaFree(c->px_epoch);
