@@ -365,8 +365,6 @@ const __half* f16_view(const bp_model* m, const std::string& name) {
   return reinterpret_cast<const __half*>(m->dev_file[file_index(t.buffer)] + t.offset);
 }
 
-// One layer of the one-token path: layer_pre_kv_in_pass, dispatch_kv_writeback_fused, layer_post_kv_in_pass
-// (src/forward.rs:608-631, 763-908). The three attention dispatches are one call of the attention library.
 // The attention call of layer il at position pos (Q norm + RoPE, cache write, attention: one launch by default).
 cudaError_t attention_call(bp_model* m, uint32_t il, uint32_t pos) {
   const LayerTensors& lt = m->layers[il];
@@ -375,6 +373,10 @@ cudaError_t attention_call(bp_model* m, uint32_t il, uint32_t pos) {
                                 &launches);
 }
 
+// One layer of the one-token path: layer_pre_kv_in_pass, dispatch_kv_writeback_fused, layer_post_kv_in_pass
+// (src/forward.rs:608-631, 763-908). The three attention dispatches are one call of the attention library.
+// in_graph: the launches are being captured into the step's graph (attn_nodes then receives the attention
+// launches with their nodes); the choice of dependent launches differs between the two ways of launching.
 // Which launches carry programmatic stream serialization was measured per kernel on the 8B shape (us per layer,
 // stream launches / graph replay): all four matvecs 55.0 / 53.2, all but the down projection 48.8 / 44.8, gate + up
 // only 49.9 / 41.1, none 51.2 / 42.3. The down projection's CTAs, resident early, take the SM slots that the
