@@ -883,16 +883,14 @@ __global__ void __launch_bounds__(UM_THREADS, 1) matmul_q1_q8_umma_kernel(const 
 //     read consecutive entries of ONE list, as the shader's layout has it).
 constexpr uint32_t TK_WG = 256, TK_K = 32, TK_CHUNK = 32;  // chunk: words (two logits) per list and stage
 constexpr uint32_t TK_ROW = TK_K + 1;                      // entries between the rows of the merge rounds
-constexpr uint32_t TK_CTAS = 8;                            // the CTAs of the cluster: TK_WG / TK_CTAS lists each
-constexpr uint32_t TK_LISTS = TK_WG / TK_CTAS;             // lists per CTA
-#ifndef TK_LPW_DEF
-#define TK_LPW_DEF 4
-#endif
-constexpr uint32_t TK_LPW = TK_LPW_DEF;                             // lists per warp (one lane each; the other lanes load and copy)
-constexpr uint32_t TK_THREADS = 32 * (TK_LISTS / TK_LPW);
-static_assert(TK_THREADS >= TK_WG, "the merge rounds of the first CTA run on the shader's 256 invocations");
+// The kernel runs as one cluster of TK_CTAS CTAs of TK_THREADS threads, TK_WG / TK_CTAS lists per CTA, one lane per
+// list: 16 CTAs with two lists per warp where the device forms clusters of 16 (88 us at 151936 logits), else the
+// portable 8 with four lists per warp (98 us).
+constexpr uint32_t TK_THREADS = TK_WG;  // the merge rounds of the first CTA run on the shader's 256 invocations
 struct __align__(8) TkEntry { float v; uint32_t i; };
-constexpr size_t TK_SMEM = (TK_WG * TK_ROW + TK_K * TK_LISTS) * sizeof(TkEntry) + TK_CHUNK * TK_LISTS * sizeof(__half2);
+constexpr size_t tk_smem_bytes(uint32_t ctas) {
+  return (TK_WG * TK_ROW + TK_K * (TK_WG / ctas)) * sizeof(TkEntry) + TK_CHUNK * (TK_WG / ctas) * sizeof(__half2);
+}
 // heap[0] of list j is being replaced by e: walk down while a child is smaller (topk_reduce.wgsl:35-50).
 // The shader compares e with the left child, then the smaller of the two with the right child: it moves to the
 // smaller child (the left one on a tie) if that child is below e, and stops otherwise. Which child is the smaller
@@ -900,6 +898,7 @@ constexpr size_t TK_SMEM = (TK_WG * TK_ROW + TK_K * TK_LISTS) * sizeof(TkEntry) 
 // load, compare the children, select, and the comparison with e only decides where the walk ends (half the
 // dependent instructions per level of the shader's order; the same moves, hence the same array).
 // Returns the value left at the root.
+template <uint32_t TK_LISTS>
 __device__ __forceinline__ float tk_sift_hole(TkEntry* heap, uint32_t j, uint32_t limit, TkEntry e) {
   uint32_t i = 0;
   float root = e.v;
@@ -922,6 +921,7 @@ __device__ __forceinline__ float tk_sift_hole(TkEntry* heap, uint32_t j, uint32_
 // slot has to be checked against a limit above the last level (only slot 15 has a child there, slot 31), and
 // the four grandchildren of a node (slots 4 i + 3 .. 4 i + 6) are requested before its children are compared:
 // a level of the walk is then compare, select, compare instead of address, load, compare, select, compare.
+template <uint32_t TK_LISTS>
 __device__ __forceinline__ float tk_sift_full(TkEntry* heap, uint32_t j, TkEntry e) {
   static_assert(TK_K == 32, "levels and slots below are those of a heap of 32");
   TkEntry* E = heap + j;
@@ -968,8 +968,11 @@ __device__ __forceinline__ void tk_merge_sync() { asm volatile("bar.sync 1, %0;"
 // warp held in step, 176 us with the marks below, on ONE SM): so the lists are spread over the cluster, four
 // to a warp, each CTA hands its sorted lists to the first CTA's shared memory, and that CTA runs the merge
 // rounds on the shader's 256 invocations.
-__global__ void __cluster_dims__(TK_CTAS, 1, 1) __launch_bounds__(TK_THREADS)
-    topk_kernel(const __half* logits, uint32_t n, uint32_t k, float* out_val, uint32_t* out_idx) {
+template <uint32_t TK_CTAS>
+__global__ void __launch_bounds__(TK_THREADS) topk_kernel(const __half* logits, uint32_t n, uint32_t k, float* out_val, uint32_t* out_idx) {
+  constexpr uint32_t TK_LISTS = TK_WG / TK_CTAS;              // lists per CTA
+  constexpr uint32_t TK_LPW = TK_LISTS / (TK_THREADS / 32);   // lists per warp (one lane each; the other lanes load and copy)
+  static_assert(TK_LPW >= 1 && TK_LPW * (TK_THREADS / 32) == TK_LISTS, "every list has a lane");
   extern __shared__ __align__(16) uint8_t tk_smem[];
   TkEntry* rows = reinterpret_cast<TkEntry*>(tk_smem);        // [TK_WG][TK_ROW], used in the first CTA only
   TkEntry* heap = rows + TK_WG * TK_ROW;                      // [TK_K][TK_LISTS]
@@ -1035,7 +1038,7 @@ __global__ void __cluster_dims__(TK_CTAS, 1, 1) __launch_bounds__(TK_THREADS)
       }
       if (!__any_sync(FULL, have)) break;
       if (have) {
-        cur_min = tk_sift_full(heap, jl, TkEntry{v, idx});
+        cur_min = tk_sift_full<TK_LISTS>(heap, jl, TkEntry{v, idx});
       }
     }
   }
@@ -1044,7 +1047,7 @@ __global__ void __cluster_dims__(TK_CTAS, 1, 1) __launch_bounds__(TK_THREADS)
     for (uint32_t active = TK_K - 1; active > 0; active--) {
       const TkEntry root = heap[jl], last = heap[active * TK_LISTS + jl];
       heap[active * TK_LISTS + jl] = root;
-      tk_sift_hole(heap, jl, active, last);
+      tk_sift_hole<TK_LISTS>(heap, jl, active, last);
     }
   }
   __syncwarp();
@@ -1309,12 +1312,54 @@ cudaError_t bp_q1_matmul_multi(bool pdl, cudaStream_t s, const bp_q1_tensor* w, 
   return cudaSuccess;
 }
 
+template <uint32_t CTAS>
+static cudaError_t topk_launch(bool pdl, cudaStream_t s, const __half* logits, uint32_t n, uint32_t k, float* out_val, uint32_t* out_idx) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(CTAS);
+  cfg.blockDim = dim3(TK_THREADS);
+  cfg.dynamicSmemBytes = tk_smem_bytes(CTAS);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CTAS;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 2 : 1;
+  return cudaLaunchKernelEx(&cfg, topk_kernel<CTAS>, logits, n, k, out_val, out_idx);
+}
+
 cudaError_t bp_q1_topk(bool pdl, cudaStream_t s, const __half* logits, uint32_t n, uint32_t k, float* out_val, uint32_t* out_idx) {
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(TK_SMEM));
+  // Per device, once: 16 CTAs per cluster (beyond the portable 8) if the device can hold such a cluster.
+  static int ctas_of_device[64] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (ctas_of_device[dev] == 0) {
+    e = cudaFuncSetAttribute(topk_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(tk_smem_bytes(8)));
     if (e != cudaSuccess) return e;
-    configured = true;
+    int chosen = 8;
+    if (cudaFuncSetAttribute(topk_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(tk_smem_bytes(16))) == cudaSuccess &&
+        cudaFuncSetAttribute(topk_kernel<16>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(16);
+      cfg.blockDim = dim3(TK_THREADS);
+      cfg.dynamicSmemBytes = tk_smem_bytes(16);
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 16;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      int clusters = 0;
+      if (cudaOccupancyMaxActiveClusters(&clusters, topk_kernel<16>, &cfg) == cudaSuccess && clusters >= 1) chosen = 16;
+    }
+    (void)cudaGetLastError();  // a device without clusters of 16 is not an error of this call
+    ctas_of_device[dev] = chosen;
   }
-  return bp_launch(pdl, topk_kernel, dim3(TK_CTAS), dim3(TK_THREADS), TK_SMEM, s, logits, n, k, out_val, out_idx);
+  return ctas_of_device[dev] == 16 ? topk_launch<16>(pdl, s, logits, n, k, out_val, out_idx) : topk_launch<8>(pdl, s, logits, n, k, out_val, out_idx);
 }
