@@ -498,7 +498,7 @@ __device__ __forceinline__ uint2 s8x4_to_f16x4(uint32_t x) {
   return make_uint2(*reinterpret_cast<uint32_t*>(&l), *reinterpret_cast<uint32_t*>(&h));
 }
 
-constexpr uint32_t MMA_THREADS = 512, MMA_MT_W = 2;   // m16 tiles per warp (warps: 4 along the tokens x 4 along the weight rows)
+constexpr uint32_t MMA_THREADS = 512;   // 16 warps: 4 along the tokens x 4 along the weight rows
 constexpr uint32_t MMA_SEG = MT * 128 / MMA_THREADS;  // inputs of one row that a thread stages: 32
 
 // Up to three weight tensors over the same activations in one launch (Q, K and V of a layer: the K and V
@@ -512,9 +512,14 @@ struct MmaTensors {
   uint32_t tile_end[3];  // running total of 128-row tiles
 };
 
+// MMA_MT_W m16 tiles per warp: 2 = tiles of 128 tokens, 1 = tiles of 64 tokens (every warp half the outputs, the
+// weight tile staged as before), for launches whose 128-token tiles would leave most of the device idle in
+// their last wave (Q, K and V at 512 tokens: 192 tiles on 148 SMs).
+template <uint32_t MMA_MT_W>
 __global__ void __launch_bounds__(MMA_THREADS, 1) matmul_q1_q8_mma_kernel(const MmaTensors tensors, uint32_t k, uint32_t m,
                                                                   const float* __restrict__ a_d, const int8_t* __restrict__ a_qs,
                                                                   uint32_t accumulate) {
+  constexpr uint32_t TM = 64 * MMA_MT_W;  // tokens of a tile
   const uint32_t which = blockIdx.x < tensors.tile_end[0] ? 0u : blockIdx.x < tensors.tile_end[1] ? 1u : 2u;
   const __half* __restrict__ w_d = tensors.w_d[which];
   const uint8_t* __restrict__ w_qs = tensors.w_qs[which];
@@ -529,7 +534,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) matmul_q1_q8_mma_kernel(const 
   pdl_launch_dependents();
   pdl_wait();
   const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const uint32_t n_base = (blockIdx.x - (which == 0 ? 0u : tensors.tile_end[which - 1])) * MT, m_base = blockIdx.y * MT;
+  const uint32_t n_base = (blockIdx.x - (which == 0 ? 0u : tensors.tile_end[which - 1])) * MT, m_base = blockIdx.y * TM;
   const uint32_t nb1 = k / 128u, nb8 = k / 32u;
   if (tid < 16) {
     uint32_t v = 0;
@@ -541,7 +546,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) matmul_q1_q8_mma_kernel(const 
   constexpr uint32_t SEGS = 128 / MMA_SEG, A_LD = MMA_SEG / 16, B_BYTES = MMA_SEG / 8;
   static_assert(B_BYTES == 4, "a thread stages one 32-bit word of sign bits");
   const uint32_t srow = tid / SEGS, sseg = tid % SEGS;
-  const bool a_ok = m_base + srow < m, b_ok = n_base + srow < n;
+  const bool a_ok = srow < TM && m_base + srow < m, b_ok = n_base + srow < n;
   const int8_t* a_src = a_qs + static_cast<size_t>(m_base + srow) * k + MMA_SEG * sseg;
   const uint8_t* b_src = w_qs + static_cast<size_t>(n_base + srow) * nb1 * 16u + B_BYTES * sseg;
   uint4 ra[A_LD];
@@ -553,8 +558,8 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) matmul_q1_q8_mma_kernel(const 
     for (uint32_t c = 0; c < A_LD; c++) ra[c] = a_ok ? *reinterpret_cast<const uint4*>(a_src + 128u * b + 16u * c) : make_uint4(0, 0, 0, 0);
     rb = b_ok ? *reinterpret_cast<const uint32_t*>(b_src + 16u * b) : 0u;
     if (tid < MT) {
-      rad = m_base + tid < m ? *reinterpret_cast<const float4*>(a_d + static_cast<size_t>(m_base + tid) * nb8 + 4u * b)
-                             : make_float4(0.f, 0.f, 0.f, 0.f);
+      rad = tid < TM && m_base + tid < m ? *reinterpret_cast<const float4*>(a_d + static_cast<size_t>(m_base + tid) * nb8 + 4u * b)
+                                         : make_float4(0.f, 0.f, 0.f, 0.f);
     } else if (tid < 2 * MT) {
       const uint32_t ni = n_base + tid - MT;
       rwd = ni < n ? __half2float(w_d[static_cast<size_t>(ni) * nb1 + b]) : 0.0f;
@@ -1234,6 +1239,8 @@ cudaError_t bp_q1_quantize_q8(bool pdl, cudaStream_t s, const __half* x, uint32_
   return bp_launch(pdl, quantize_q8_kernel, dim3(static_cast<unsigned>((n_blocks + 7) / 8)), dim3(256), 0, s, x, n_blocks, d_out, qs_out);
 }
 
+static uint32_t g_matmul_variant = 0;  // 0 = by batch size; 1 dp4a, 2 mma.sync, 3 tcgen05; 4 / 5 = mma.sync with 64- / 128-token tiles only
+
 static cudaError_t launch_mma(bool pdl, cudaStream_t s, const bp_q1_tensor* w, __half* const* y, uint32_t n_w, uint32_t m, const float* a_d,
                               const int8_t* a_qs, uint32_t acc) {
   MmaTensors t;
@@ -1247,12 +1254,24 @@ static cudaError_t launch_mma(bool pdl, cudaStream_t s, const bp_q1_tensor* w, _
     if (i < n_w) tiles += (w[i].n + MT - 1) / MT;
     t.tile_end[i] = tiles;
   }
-  dim3 grid(tiles, (m + MT - 1) / MT);
-  return bp_launch(pdl, matmul_q1_q8_mma_kernel, grid, dim3(MMA_THREADS), MMA_SMEM, s, t, w[0].k, m, a_d, a_qs, acc);
+  // Tiles of 128 or of 64 tokens: whichever needs less time in waves of one CTA per SM (a 64-token tile costs
+  // 0.62 of a 128-token one, measured: the weight tile is staged all the same).
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 1;
+  }
+  const uint32_t full = tiles * ((m + 127) / 128), half = tiles * ((m + 63) / 64), n_sm = static_cast<uint32_t>(sms);
+  const float t_full = static_cast<float>((full + n_sm - 1) / n_sm), t_half = 0.62f * static_cast<float>((half + n_sm - 1) / n_sm);
+  if (g_matmul_variant == 4 || (g_matmul_variant != 5 && t_half < t_full)) {
+    dim3 grid(tiles, (m + 63) / 64);
+    return bp_launch(pdl, matmul_q1_q8_mma_kernel<1>, grid, dim3(MMA_THREADS), MMA_SMEM, s, t, w[0].k, m, a_d, a_qs, acc);
+  }
+  dim3 grid(tiles, (m + 127) / 128);
+  return bp_launch(pdl, matmul_q1_q8_mma_kernel<2>, grid, dim3(MMA_THREADS), MMA_SMEM, s, t, w[0].k, m, a_d, a_qs, acc);
 }
 
-static uint32_t g_matmul_variant = 0;
-void bp_q1_set_matmul_variant(uint32_t v) { g_matmul_variant = v <= 3 ? v : 0; }
+void bp_q1_set_matmul_variant(uint32_t v) { g_matmul_variant = v <= 5 ? v : 0; }
 
 cudaError_t bp_q1_take_error(uint32_t* code) {
   cudaError_t e = cudaMemcpyFromSymbol(code, g_q1_err, sizeof(uint32_t));
@@ -1269,10 +1288,12 @@ cudaError_t bp_q1_take_error(uint32_t* code) {
 // three give the same bits).
 cudaError_t bp_q1_matmul(bool pdl, cudaStream_t s, const bp_q1_tensor& w, uint32_t m, const float* a_d, const int8_t* a_qs, __half* y,
                          bool accumulate, uint32_t* err, uint32_t wait_limit) {
-  const uint32_t variant = g_matmul_variant != 0 ? g_matmul_variant : (m > MMA_MIN_M ? 2u : 1u);
+  const uint32_t variant = g_matmul_variant >= 4 ? 2u : g_matmul_variant != 0 ? g_matmul_variant : (m > MMA_MIN_M ? 2u : 1u);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(matmul_q1_q8_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(MMA_SMEM));
+    cudaError_t e = cudaFuncSetAttribute(matmul_q1_q8_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(MMA_SMEM));
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(matmul_q1_q8_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(MMA_SMEM));
     if (e != cudaSuccess) return e;
     e = cudaFuncSetAttribute(matmul_q1_q8_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(UM_SMEM));
     if (e != cudaSuccess) return e;
@@ -1297,7 +1318,7 @@ cudaError_t bp_q1_matmul(bool pdl, cudaStream_t s, const bp_q1_tensor& w, uint32
 // The same activations through up to three weight tensors of equal k: one launch where the kernel allows.
 cudaError_t bp_q1_matmul_multi(bool pdl, cudaStream_t s, const bp_q1_tensor* w, __half* const* y, uint32_t n_w, uint32_t m, const float* a_d,
                                const int8_t* a_qs, bool accumulate, uint32_t* err, uint32_t wait_limit) {
-  const uint32_t variant = g_matmul_variant != 0 ? g_matmul_variant : (m > MMA_MIN_M ? 2u : 1u);
+  const uint32_t variant = g_matmul_variant >= 4 ? 2u : g_matmul_variant != 0 ? g_matmul_variant : (m > MMA_MIN_M ? 2u : 1u);
   bool same_k = n_w >= 1 && n_w <= 3;
   for (uint32_t i = 1; i < n_w && same_k; i++) same_k = w[i].k == w[0].k;
   if (variant == 2 && same_k && n_w > 1) {

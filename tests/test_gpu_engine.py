@@ -160,7 +160,7 @@ def test_matmul_q1_0_q8_0_bit_exact(k, n, m, accumulate):
     want = E.matmul(blob, d_off, qs_off, k, n, m, a_d, a_qs, y=y0 if accumulate else None)
     add, aqd = dev(a_d), dev(a_qs)
     try:
-        for variant in (0, 1, 2, 3):  # by batch size, CUDA cores, mma.sync, tcgen05: the same bits
+        for variant in (0, 1, 2, 3, 4, 5):  # by batch size, CUDA cores, mma.sync, tcgen05, mma.sync with 64- / 128-token tiles: the same bits
             lib.bp_op_set_matmul_variant(variant)
             y = dev(y0.copy())
             assert lib.bp_op_matmul_q1_0_q8_0(None, d_dev.data_ptr(), qs_dev.data_ptr(), k, n, m, add.data_ptr(), aqd.data_ptr(),
@@ -293,7 +293,7 @@ def test_batched_prefill_is_identical_across_matmul_kernels(tmp_path):
     lib = _lib.load()
     got = {}
     try:
-        for variant in (1, 0, 3):
+        for variant in (1, 0, 3, 4, 5):
             lib.bp_op_set_matmul_variant(variant)
             with bp.Model(d, max_seq=64) as gm:
                 lg, ix = gm.prefill_topk(prompt)
