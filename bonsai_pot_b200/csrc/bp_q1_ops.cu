@@ -510,6 +510,7 @@ struct MmaTensors {
   __half* y[3];
   uint32_t n[3];
   uint32_t tile_end[3];  // running total of 128-row tiles
+  uint32_t tile0;        // the launch covers the tiles from this one on (blockIdx.x counts from it)
 };
 
 // MMA_MT_W m16 tiles per warp: 2 = tiles of 128 tokens, 1 = tiles of 64 tokens (every warp half the outputs, the
@@ -520,7 +521,8 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) matmul_q1_q8_mma_kernel(const 
                                                                   const float* __restrict__ a_d, const int8_t* __restrict__ a_qs,
                                                                   uint32_t accumulate) {
   constexpr uint32_t TM = 64 * MMA_MT_W;  // tokens of a tile
-  const uint32_t which = blockIdx.x < tensors.tile_end[0] ? 0u : blockIdx.x < tensors.tile_end[1] ? 1u : 2u;
+  const uint32_t tile = blockIdx.x + tensors.tile0;
+  const uint32_t which = tile < tensors.tile_end[0] ? 0u : tile < tensors.tile_end[1] ? 1u : 2u;
   const __half* __restrict__ w_d = tensors.w_d[which];
   const uint8_t* __restrict__ w_qs = tensors.w_qs[which];
   __half* y = tensors.y[which];
@@ -534,7 +536,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) matmul_q1_q8_mma_kernel(const 
   pdl_launch_dependents();
   pdl_wait();
   const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const uint32_t n_base = (blockIdx.x - (which == 0 ? 0u : tensors.tile_end[which - 1])) * MT, m_base = blockIdx.y * TM;
+  const uint32_t n_base = (tile - (which == 0 ? 0u : tensors.tile_end[which - 1])) * MT, m_base = blockIdx.y * TM;
   const uint32_t nb1 = k / 128u, nb8 = k / 32u;
   if (tid < 16) {
     uint32_t v = 0;
@@ -1254,21 +1256,34 @@ static cudaError_t launch_mma(bool pdl, cudaStream_t s, const bp_q1_tensor* w, _
     if (i < n_w) tiles += (w[i].n + MT - 1) / MT;
     t.tile_end[i] = tiles;
   }
-  // Tiles of 128 or of 64 tokens: whichever needs less time in waves of one CTA per SM (a 64-token tile costs
-  // 0.62 of a 128-token one, measured: the weight tile is staged all the same).
+  // Tiles of 128 tokens, of 64 tokens (0.62 of the time of a full one, measured: the weight tile is staged all
+  // the same), or full tiles for as many whole waves of one CTA per SM as there are and half tiles for the rest
+  // in a second launch (gate + up at 512 tokens: 768 full tiles are 5.2 waves; 740 full tiles and 56 half tiles
+  // are 5 waves and a short one): whichever needs the least time.
   static int sms = 0;
   if (sms == 0) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 1;
   }
-  const uint32_t full = tiles * ((m + 127) / 128), half = tiles * ((m + 63) / 64), n_sm = static_cast<uint32_t>(sms);
-  const float t_full = static_cast<float>((full + n_sm - 1) / n_sm), t_half = 0.62f * static_cast<float>((half + n_sm - 1) / n_sm);
-  if (g_matmul_variant == 4 || (g_matmul_variant != 5 && t_half < t_full)) {
-    dim3 grid(tiles, (m + 63) / 64);
-    return bp_launch(pdl, matmul_q1_q8_mma_kernel<1>, grid, dim3(MMA_THREADS), MMA_SMEM, s, t, w[0].k, m, a_d, a_qs, acc);
+  const uint32_t n_sm = static_cast<uint32_t>(sms), m_full = (m + 127) / 128, m_half = (m + 63) / 64;
+  auto waves = [&](uint32_t ctas) { return static_cast<float>((ctas + n_sm - 1) / n_sm); };
+  constexpr float HALF_COST = 0.62f;
+  const float t_full = waves(tiles * m_full), t_half = HALF_COST * waves(tiles * m_half);
+  const uint32_t n_a = (tiles * m_full / n_sm) * n_sm / m_full;  // column tiles that make whole waves of full tiles
+  const float t_mixed = n_a == 0 || n_a == tiles ? 1e30f : waves(n_a * m_full) + HALF_COST * waves((tiles - n_a) * m_half) + 0.03f;
+  auto launch = [&](bool half_tiles, uint32_t t0, uint32_t t1, bool dep) {
+    t.tile0 = t0;
+    if (half_tiles) return bp_launch(dep, matmul_q1_q8_mma_kernel<1>, dim3(t1 - t0, m_half), dim3(MMA_THREADS), MMA_SMEM, s, t, w[0].k, m, a_d, a_qs, acc);
+    return bp_launch(dep, matmul_q1_q8_mma_kernel<2>, dim3(t1 - t0, m_full), dim3(MMA_THREADS), MMA_SMEM, s, t, w[0].k, m, a_d, a_qs, acc);
+  };
+  if (g_matmul_variant == 4) return launch(true, 0, tiles, pdl);
+  if (g_matmul_variant == 5) return launch(false, 0, tiles, pdl);
+  if (t_mixed < t_full && t_mixed < t_half) {
+    cudaError_t e = launch(false, 0, n_a, pdl);
+    if (e != cudaSuccess) return e;
+    return launch(true, n_a, tiles, pdl);  // other outputs, the same inputs: it only has to follow in the stream
   }
-  dim3 grid(tiles, (m + 127) / 128);
-  return bp_launch(pdl, matmul_q1_q8_mma_kernel<2>, grid, dim3(MMA_THREADS), MMA_SMEM, s, t, w[0].k, m, a_d, a_qs, acc);
+  return t_half < t_full ? launch(true, 0, tiles, pdl) : launch(false, 0, tiles, pdl);
 }
 
 void bp_q1_set_matmul_variant(uint32_t v) { g_matmul_variant = v <= 5 ? v : 0; }

@@ -55,8 +55,8 @@ int bp_op_quantize_q8_0(void* stream, const void* x, uint32_t k, uint32_t m, voi
 int bp_op_matmul_q1_0_q8_0(void* stream, const void* d, const void* qs, uint32_t k, uint32_t n, uint32_t m, const void* a_d,
                            const void* a_qs, void* y, uint32_t accumulate);
 /* Tuning aid of the matmul: 0 = chosen by the batch (CUDA cores up to 32 tokens, mma.sync above, the
- * default), 1 = CUDA cores (dp4a), 2 = mma.sync (int8; tiles of 128 or 64 tokens, whichever fills the device's
- * waves better), 3 = tcgen05 (f16 operands), 4 / 5 = mma.sync with tiles of 64 / 128 tokens only. Results do not
+ * default), 1 = CUDA cores (dp4a), 2 = mma.sync (int8; tiles of 128 tokens, of 64, or whole waves of the former and
+ * the rest as the latter, whichever fills the device's waves best), 3 = tcgen05 (f16 operands), 4 / 5 = mma.sync with tiles of 64 / 128 tokens only. Results do not
  * depend on it. Process-wide. */
 void bp_op_set_matmul_variant(uint32_t variant);
 /* The tcgen05 matmul waits on barriers, with a bound. Synchronizes the device and returns BP_ERR_TIMEOUT

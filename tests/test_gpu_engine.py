@@ -171,6 +171,37 @@ def test_matmul_q1_0_q8_0_bit_exact(k, n, m, accumulate):
         lib.bp_op_set_matmul_variant(0)
 
 
+@pytest.mark.parametrize("k,n,m,accumulate", [(256, 24576, 512, True), (256, 6144, 512, False), (128, 6144, 300, True),
+                                              (128, 19000, 450, False)])
+def test_matmul_tile_choices_agree(k, n, m, accumulate):
+    """The mma.sync matmul picks its tiles by how they fill the device: 128-token tiles, 64-token tiles, or whole
+    waves of 128-token tiles followed by 64-token tiles for the rest in a second launch (these shapes reach that
+    choice on a 148-SM device). The three must give the same bits; the 128-token form is checked against the CPU
+    restatement in the test above."""
+    lib = _lib.load()
+    gen = torch.Generator(device="cuda").manual_seed(k + n + m)
+    nb = k // 128
+    d = (torch.rand(n, nb, device="cuda", generator=gen) * 0.02).half()
+    qs = torch.randint(0, 256, (n, nb, 16), device="cuda", dtype=torch.uint8, generator=gen)
+    a_d = torch.rand(m, k // 32, device="cuda", generator=gen) * 0.05
+    a_qs = torch.randint(-127, 128, (m, k), device="cuda", dtype=torch.int8, generator=gen)
+    y0 = torch.randn(m, n, device="cuda", generator=gen).half()
+    got = {}
+    try:
+        for variant in (5, 4, 0):
+            lib.bp_op_set_matmul_variant(variant)
+            y = y0.clone()
+            assert lib.bp_op_matmul_q1_0_q8_0(None, d.data_ptr(), qs.data_ptr(), k, n, m, a_d.data_ptr(), a_qs.data_ptr(), y.data_ptr(),
+                                              int(accumulate)) == 0
+            assert lib.bp_op_device_status() == 0
+            got[variant] = y
+    finally:
+        lib.bp_op_set_matmul_variant(0)
+    assert torch.equal(got[5].view(torch.int16), got[4].view(torch.int16))
+    assert torch.equal(got[5].view(torch.int16), got[0].view(torch.int16))
+    assert not torch.equal(got[5], y0)
+
+
 @pytest.mark.parametrize("n,k,ties", [(151936, 32, False), (5001, 32, True), (2048, 5, True), (7, 32, False)])
 def test_topk_reduce_identical_including_ties(n, k, ties):
     rng = np.random.default_rng(n)
