@@ -325,11 +325,24 @@ __global__ void __launch_bounds__(512) rms_norm_kernel(const __half* in, __half*
 }
 
 // silu_mul.wgsl:18-27
+// A thread takes eight values (16-byte loads and stores) where the buffers allow it, else one.
+template <bool VEC8>
 __global__ void __launch_bounds__(256) silu_mul_kernel(const __half* gate, const __half* up, __half* out, uint64_t n) {
   pdl_launch_dependents();
   pdl_wait();
   const uint64_t i = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x;
-  if (i < n) out[i] = silu_times_up(gate[i], up[i]);
+  if (VEC8) {
+    if (8u * i >= n) return;
+    const uint4 g = *reinterpret_cast<const uint4*>(gate + 8u * i), u = *reinterpret_cast<const uint4*>(up + 8u * i);
+    const __half* g8 = reinterpret_cast<const __half*>(&g);
+    const __half* u8 = reinterpret_cast<const __half*>(&u);
+    __half y[8];
+#pragma unroll
+    for (int c = 0; c < 8; c++) y[c] = silu_times_up(g8[c], u8[c]);
+    *reinterpret_cast<uint4*>(out + 8u * i) = *reinterpret_cast<const uint4*>(y);
+  } else {
+    if (i < n) out[i] = silu_times_up(gate[i], up[i]);
+  }
 }
 
 // embed.wgsl:37-52: thread = one 16-byte unit (8 weights) of an output row
@@ -1248,7 +1261,9 @@ cudaError_t bp_q1_rms_norm(bool pdl, cudaStream_t s, const __half* in, __half* o
 }
 
 cudaError_t bp_q1_silu_mul(bool pdl, cudaStream_t s, const __half* gate, const __half* up, __half* out, uint64_t n) {
-  return bp_launch(pdl, silu_mul_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, s, gate, up, out, n);
+  const bool vec8 = n % 8u == 0 && (reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(up) | reinterpret_cast<uintptr_t>(out)) % 16u == 0;
+  if (vec8) return bp_launch(pdl, silu_mul_kernel<true>, dim3(static_cast<unsigned>((n / 8u + 255) / 256)), dim3(256), 0, s, gate, up, out, n);
+  return bp_launch(pdl, silu_mul_kernel<false>, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, s, gate, up, out, n);
 }
 
 cudaError_t bp_q1_embed(bool pdl, cudaStream_t s, const bp_q1_tensor& w, const uint32_t* tokens, uint32_t m, __half* x) {
