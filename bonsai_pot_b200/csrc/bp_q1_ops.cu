@@ -521,7 +521,28 @@ __device__ __forceinline__ void mma_s8_s32(int (&d)[4], const uint32_t (&a)[4], 
                : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(Q1_I2F_BIAS));
 }
-__device__ __forceinline__ float q1_biased_s32_to_f32(int x) { return __int_as_float(x) - 12582912.0f; }
+// Packed FP32 pairs (sm_100): one instruction rounds two products, or two sums, each exactly as the scalar
+// instruction does (checked bit for bit on 32 million random operand pairs per operation). The assembler has
+// been seen to contract a packed multiply into a packed add that consumes it, rounding modifiers or not, so a
+// packed product is never fed to a packed add here: the accumulation uses the scalar add.
+__device__ __forceinline__ void q1_mul2(float& d0, float& d1, float a0, float a1, float b0, float b1) {
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmul.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+__device__ __forceinline__ void q1_add2(float& d0, float& d1, float a0, float a1, float b0, float b1) {
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tadd.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+// acc0 += (ad * w0) * float(dot0), acc1 += (ad * w1) * float(dot1), every product and sum rounded once, in that
+// order (the shader's): five instructions for the two outputs instead of eight.
+__device__ __forceinline__ void q1_accumulate2(float& acc0, float& acc1, float ad, float w0, float w1, int biased0, int biased1) {
+  float f0, f1, p0, p1, q0, q1;
+  q1_add2(f0, f1, __int_as_float(biased0), __int_as_float(biased1), -12582912.0f, -12582912.0f);
+  q1_mul2(p0, p1, ad, ad, w0, w1);
+  q1_mul2(q0, q1, p0, p1, f0, f1);
+  acc0 = __fadd_rn(acc0, q0);
+  acc1 = __fadd_rn(acc1, q1);
+}
 // four int8 -> four f16, exactly: bias to unsigned, 0x6400 | byte = 1024 + byte, minus 1152
 __device__ __forceinline__ uint2 s8x4_to_f16x4(uint32_t x) {
   x ^= 0x80808080u;
@@ -668,10 +689,8 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) matmul_q1_q8_mma_kernel(const 
         for (uint32_t nt = 0; nt < 4; nt++) {
           int d[4];
           mma_s8_s32(d, af, bf[nt][0], bf[nt][1]);
-          acc[mt][nt][0] = __fadd_rn(acc[mt][nt][0], __fmul_rn(__fmul_rn(ad_lo, wdv[nt][0]), q1_biased_s32_to_f32(d[0])));
-          acc[mt][nt][1] = __fadd_rn(acc[mt][nt][1], __fmul_rn(__fmul_rn(ad_lo, wdv[nt][1]), q1_biased_s32_to_f32(d[1])));
-          acc[mt][nt][2] = __fadd_rn(acc[mt][nt][2], __fmul_rn(__fmul_rn(ad_hi, wdv[nt][0]), q1_biased_s32_to_f32(d[2])));
-          acc[mt][nt][3] = __fadd_rn(acc[mt][nt][3], __fmul_rn(__fmul_rn(ad_hi, wdv[nt][1]), q1_biased_s32_to_f32(d[3])));
+          q1_accumulate2(acc[mt][nt][0], acc[mt][nt][1], ad_lo, wdv[nt][0], wdv[nt][1], d[0], d[1]);
+          q1_accumulate2(acc[mt][nt][2], acc[mt][nt][3], ad_hi, wdv[nt][0], wdv[nt][1], d[2], d[3]);
         }
       }
     }
